@@ -1,0 +1,97 @@
+"""ctypes binding of the engine's C ABI (include/c6_engine.h).
+
+The library is loaded from the package directory (connect6_b200/libc6engine.so).  There is no
+fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libc6engine.so"
+
+C6_MAX_LAYERS = 16
+C6_OK, C6_ERR_ARG, C6_ERR_CUDA, C6_ERR_UNSUPPORTED, C6_ERR_WEIGHTS, C6_ERR_DEVICE = range(6)
+C6_PREC_BF16, C6_PREC_FP32 = 0, 1
+C6_X_F32, C6_X_BF16 = 0, 1
+C6_HEAD_POLICY, C6_HEAD_VALUE = 100, 101
+C6_FLAG_MASK_LOGITS, C6_FLAG_INVERSE_MAP = 1, 2
+
+
+class C6Desc(C.Structure):
+    _fields_ = [
+        ("device", C.c_int32),
+        ("board_size", C.c_int32),
+        ("n_layers", C.c_int32),
+        ("kernels", C.c_int32 * C6_MAX_LAYERS),
+        ("channels", C.c_int32 * C6_MAX_LAYERS),
+        ("groups", C.c_int32),
+        ("precision", C.c_int32),
+        ("max_chunk", C.c_int32),
+    ]
+
+
+_vp, _i, _i64, _u64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_float
+
+# name -> (restype, argtypes); mirrors include/c6_engine.h declaration by declaration
+SIGNATURES = {
+    "c6_version": (_i, []),
+    "c6_create": (_i, [C.POINTER(C6Desc), C.POINTER(_vp)]),
+    "c6_set_weights": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
+    "c6_reserve": (_i, [_vp, _i64]),
+    "c6_forward": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp]),
+    "c6_forward_step": (_i, [_vp, _vp, _i, _i64, _vp, _i, _f, _u64, _u64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "c6_forward_grouped": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _i, _vp]),
+    "c6_sample_actions": (_i, [_vp, _vp, _i64, C.c_int32, _f, _u64, _u64, _i64, _vp, _vp, _vp]),
+    "c6_mask_logits": (_i, [_vp, _vp, _i64, _f, _vp, _vp]),
+    "c6_transform_actions": (_i, [_vp, _i64, C.c_int32, _vp, C.c_int32, C.c_int32, _vp, _vp]),
+    "c6_transform_boards": (_i, [_vp, _i64, C.c_int32, _vp, C.c_int32, _vp, _vp]),
+    "c6_network_input": (_i, [_vp, _vp, _vp, _i64, C.c_int32, _vp, _vp]),
+    "c6_debug_layer_output": (_i, [_vp, _vp, _i, _i64, _vp, _i, _vp, _vp]),
+    "c6_status": (_i, [_vp, C.POINTER(_i)]),
+    "c6_launch_count": (_i64, [_vp]),
+    "c6_device_bytes": (_i64, [_vp]),
+    "c6_last_error": (C.c_char_p, [_vp]),
+    "c6_destroy": (_i, [_vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library once and attach the prototypes."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m connect6_b200.build` "
+                "(the engine has no other execution path)"
+            )
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def last_error(handle=None) -> str:
+    msg = load().c6_last_error(handle)
+    return msg.decode("utf-8", "replace") if msg else ""
+
+
+def check(rc: int, handle=None, what: str = "") -> None:
+    if rc == C6_OK:
+        return
+    msg = last_error(handle)
+    names = {1: "bad argument", 2: "CUDA error", 3: "unsupported", 4: "weights missing", 5: "device status"}
+    text = f"{what or 'c6 call'} failed ({names.get(rc, rc)}): {msg}"
+    if rc in (C6_ERR_ARG, C6_ERR_UNSUPPORTED):
+        raise ValueError(text)
+    raise RuntimeError(text)
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a torch tensor (None passes a null pointer)."""
+    return None if t is None else t.data_ptr()

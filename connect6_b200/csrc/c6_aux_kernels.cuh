@@ -1,0 +1,382 @@
+// Memory-bound helper kernels around the convolution stack: input packing (with the per-board
+// D4 view), weight repacking, the fused policy/value finishing kernel (mask, log-softmax,
+// categorical draw, board mean + tanh) and the small standalone operators of the path.
+#pragma once
+
+#include "c6_common.cuh"
+
+namespace c6 {
+
+// ------------------------------------------------------------------------------------------------
+// Input packing for the tensor-core stem: x [boards,3,n,n] (fp32 or bf16, NCHW) -> K-chunk planes
+// xk[kc][mrows] (16-byte rows of 8 bf16, k = ci*n*n + view cell).  A board with orientation
+// `phase` is presented as view.flat[j] = x.flat[d4_inverse(j)] (connect6/train.py:222-230).
+// Grid: (ceil(kc*nb/256), G); one thread per (board, chunk).
+// ------------------------------------------------------------------------------------------------
+__global__ void pack_stem_input_kernel(const void* __restrict__ x, int x_bf16,
+                                       const uint8_t* __restrict__ orient, uint4* __restrict__ xk,
+                                       long long mrows, int mrows_per_group, int kc, int n,
+                                       int nb,                 // boards of this pass per group
+                                       long long group_stride, // boards between groups in x
+                                       long long board0) {     // first board of this pass in a group
+  const int g = blockIdx.y;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)kc * nb) return;
+  const int t = (int)(idx % nb);
+  const int c = (int)(idx / nb);
+  const int cells = n * n, ktot = 3 * cells;
+  const long long src_board = (long long)g * group_stride + board0 + t;
+  const int phase = orient ? (orient[src_board] & 7) : 0;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int k = c * 8 + j;
+    float val = 0.f;
+    if (k < ktot) {
+      const int ci = k / cells;
+      int cell = k - ci * cells;
+      if (phase) cell = d4_inverse(cell, n, phase);
+      val = load_x(x, x_bf16, src_board * ktot + (long long)ci * cells + cell);
+    }
+    v[j] = val;
+  }
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  xk[(size_t)c * mrows + (size_t)g * mrows_per_group + t] = o;
+}
+
+// fp32 mode: x -> fp32 NCHW copy in view orientation, boards of all groups laid out [g][t].
+__global__ void view_input_f32_kernel(const void* __restrict__ x, int x_bf16,
+                                      const uint8_t* __restrict__ orient, float* __restrict__ out,
+                                      int n, int nb, long long group_stride, long long board0) {
+  const int g = blockIdx.y;
+  const int cells = n * n, ktot = 3 * cells;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)nb * ktot) return;
+  const int t = (int)(idx / ktot);
+  const int k = (int)(idx - (long long)t * ktot);
+  const long long src_board = (long long)g * group_stride + board0 + t;
+  const int phase = orient ? (orient[src_board] & 7) : 0;
+  const int ci = k / cells;
+  int cell = k - ci * cells;
+  if (phase) cell = d4_inverse(cell, n, phase);
+  out[((size_t)g * nb + t) * ktot + k] = load_x(x, x_bf16, src_board * ktot + (long long)ci * cells + cell);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Weight repacking (reference layout: [Cout,Cin,K,K] fp32, connect6/model.py:56-63).
+// ------------------------------------------------------------------------------------------------
+
+// k x k layer -> rows [q][tap][j][co] of 8 bf16: element e of the row is input channel
+// (2q+j)*8+e.  Channels beyond the real counts are zero.
+__global__ void pack_conv_weights_kernel(const float* __restrict__ w, uint4* __restrict__ out,
+                                         int cout, int cin, int kside, int cout_p, int cin_p) {
+  const int taps = kside * kside;
+  const long long total = (long long)(cin_p / 16) * taps * 2 * cout_p;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int co = (int)(idx % cout_p);
+  long long r = idx / cout_p;
+  const int j = (int)(r % 2);
+  r /= 2;
+  const int tap = (int)(r % taps);
+  const int q = (int)(r / taps);
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int ci = (2 * q + j) * 8 + e;
+    v[e] = (co < cout && ci < cin) ? w[((size_t)co * cin + ci) * taps + tap] : 0.f;
+  }
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  out[idx] = o;
+}
+
+// Stem -> Toeplitz planes wt[kc][ntot] (row o = cell_out*c1 + co, element e: k = kc*8+e).
+__global__ void pack_stem_toeplitz_kernel(const float* __restrict__ w, uint4* __restrict__ out,
+                                          int cout, int kside, int n, int c1, int kc, int ntot) {
+  const long long total = (long long)kc * ntot;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int o = (int)(idx % ntot);
+  const int c = (int)(idx / ntot);
+  const int cells = n * n, pad = kside >> 1;
+  const int cell_out = o / c1, co = o - cell_out * c1;
+  const int ro = cell_out / n, cc = cell_out - ro * n;
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int k = c * 8 + e;
+    float val = 0.f;
+    if (k < 3 * cells && cell_out < cells && co < cout) {
+      const int ci = k / cells;
+      const int cell_in = k - ci * cells;
+      const int ri = cell_in / n, cin_c = cell_in - ri * n;
+      const int ky = ri - ro + pad, kx = cin_c - cc + pad;
+      if (ky >= 0 && ky < kside && kx >= 0 && kx < kside)
+        val = w[(((size_t)co * 3 + ci) * kside + ky) * kside + kx];
+    }
+    v[e] = val;
+  }
+  uint4 q;
+  q.x = pack_bf16x2(v[0], v[1]);
+  q.y = pack_bf16x2(v[2], v[3]);
+  q.z = pack_bf16x2(v[4], v[5]);
+  q.w = pack_bf16x2(v[6], v[7]);
+  out[idx] = q;
+}
+
+// dst[i] = i < n_src ? src[i] : 0 for i < n_dst (bias / head vectors padded with zeros)
+__global__ void copy_pad_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int n_src,
+                                    int n_dst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_dst) dst[i] = (src != nullptr && i < n_src) ? src[i] : 0.f;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Finishing kernel: one CTA of 128 threads per board.
+//   raw policy map + bias -> (optional D4 inverse map) -> mask -> logits out
+//   masked logits / max(T,1e-4) -> log-softmax -> one inverse-CDF draw -> action, log-prob
+//   value map -> board mean + bias -> tanh
+// Follows connect6/model.py:108-110,123-125 and connect6/train.py:195-203.
+// ------------------------------------------------------------------------------------------------
+struct FinishParams {
+  // sources (engine path): raw maps in a pitched layout; (standalone path): logits_in + legal_in
+  const float* logit_raw;
+  const float* vmap;
+  long long group_stride;  // elements between groups in the raw maps
+  int board_stride;        // elements between boards
+  int pitch;               // elements between board rows
+  const float* pol_bias;   // [G] or null
+  const float* val_bias;   // [G] or null
+  const float* logits_in;  // standalone: [B,A] logits
+  const uint8_t* legal_in; // standalone: [B,A] legality
+  const void* x;           // engine path: network input, for occupancy (plane0|plane1)
+  int x_bf16;
+  const uint8_t* orient;
+  long long x_group_stride; // boards between groups in x / outputs
+  long long board0;         // first board of this pass inside a group
+  int n;                    // board side (engine path); standalone: A = n_actions
+  int n_actions;
+  int nb;                   // boards per group in this pass
+  int flags;
+  int do_sample;
+  float temperature;
+  unsigned long long seed, offset;
+  long long board_index0;
+  float* logits_out;        // [.., A] or null
+  float* value_out;         // or null
+  long long* action_out;    // or null
+  float* logprob_out;       // or null
+};
+
+constexpr int kFinishThreads = 128;
+constexpr int kFinishMaxActions = 1024;
+
+__device__ __forceinline__ float block_reduce_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = red[0];
+  for (int i = 1; i < kFinishThreads / 32; ++i) r = fmaxf(r, red[i]);
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ float block_reduce_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+  for (int i = 0; i < kFinishThreads / 32; ++i) r += red[i];
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ int block_reduce_min_int(int v, int* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  int r = red[0];
+  for (int i = 1; i < kFinishThreads / 32; ++i) r = min(r, red[i]);
+  __syncthreads();
+  return r;
+}
+
+__global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishParams p) {
+  __shared__ float s_z[kFinishMaxActions];
+  __shared__ float s_e[kFinishMaxActions];
+  __shared__ uint8_t s_legal[kFinishMaxActions];
+  __shared__ float s_red[kFinishThreads / 32];
+  __shared__ int s_redi[kFinishThreads / 32];
+  __shared__ float s_scan[kFinishThreads];
+
+  const int g = blockIdx.y;
+  const int t = blockIdx.x;
+  const int A = p.n_actions;
+  const long long ob = (long long)g * p.x_group_stride + p.board0 + t;  // board index in x / outputs
+  const bool engine = p.logit_raw != nullptr;
+  const int n = p.n;
+  const int phase = (engine && p.orient) ? (p.orient[ob] & 7) : 0;
+  const bool canon = phase != 0 && (p.flags & 2 /*C6_FLAG_INVERSE_MAP*/);
+  const long long raw0 = (long long)g * p.group_stride + (long long)t * p.board_stride;
+  const float bp = (engine && p.pol_bias) ? p.pol_bias[g] : 0.f;
+
+  float vsum = 0.f;
+  for (int a = threadIdx.x; a < A; a += kFinishThreads) {
+    float raw;
+    bool legal;
+    if (engine) {
+      // output index a lives in the canonical frame when `canon`, else in the view frame
+      const int view_cell = canon ? d4_forward(a, n, phase) : a;
+      const int vr = view_cell / n, vc = view_cell - vr * n;
+      raw = p.logit_raw[raw0 + vr * p.pitch + vc] + bp;
+      const int orig_cell = (phase != 0 && !canon) ? d4_inverse(a, n, phase) : a;
+      const long long xb = ob * 3 * A;
+      legal = load_x(p.x, p.x_bf16, xb + orig_cell) == 0.f && load_x(p.x, p.x_bf16, xb + A + orig_cell) == 0.f;
+      if (p.vmap) {
+        const int r = a / n, c = a - r * n;
+        vsum += p.vmap[raw0 + r * p.pitch + c];
+      }
+    } else {
+      raw = p.logits_in[ob * A + a];
+      legal = p.legal_in[ob * A + a] != 0;
+    }
+    s_z[a] = raw;
+    s_legal[a] = legal ? 1 : 0;
+    if (p.logits_out) p.logits_out[ob * A + a] = ((p.flags & 1) && !legal) ? kFp32Min : raw;
+  }
+  if (engine && p.value_out) {
+    const float tot = block_reduce_sum(vsum, s_red);
+    if (threadIdx.x == 0) p.value_out[ob] = tanhf(tot / (float)A + (p.val_bias ? p.val_bias[g] : 0.f));
+  }
+  if (!p.do_sample) return;
+  __syncthreads();
+
+  // z = mask(logits) / max(T, 1e-4); with no legal cell every z equals the fill: uniform.
+  const float inv_t = 1.0f / fmaxf(p.temperature, 1e-4f);
+  float lmax = -INFINITY;
+  int nlegal = 0;
+  for (int a = threadIdx.x; a < A; a += kFinishThreads)
+    if (s_legal[a]) { lmax = fmaxf(lmax, s_z[a] * inv_t); ++nlegal; }
+  const float any = block_reduce_sum((float)nlegal, s_red);
+  const bool none_legal = any == 0.f;
+  const float zmax = none_legal ? 0.f : block_reduce_max(lmax, s_red);
+
+  // contiguous segment per thread so that the prefix order is the action order
+  const int per = (A + kFinishThreads - 1) / kFinishThreads;
+  const int a0 = threadIdx.x * per, a1 = min(A, a0 + per);
+  float local = 0.f;
+  for (int a = a0; a < a1; ++a) {
+    const float e = none_legal ? 1.f : (s_legal[a] ? expf(s_z[a] * inv_t - zmax) : 0.f);
+    s_e[a] = e;
+    local += e;
+  }
+  // inclusive block scan of `local`
+  s_scan[threadIdx.x] = local;
+  __syncthreads();
+  for (int o = 1; o < kFinishThreads; o <<= 1) {
+    const float add = threadIdx.x >= o ? s_scan[threadIdx.x - o] : 0.f;
+    __syncthreads();
+    s_scan[threadIdx.x] += add;
+    __syncthreads();
+  }
+  const float total = s_scan[kFinishThreads - 1];
+  const float before = s_scan[threadIdx.x] - local;
+  const float u = board_uniform(p.seed, p.offset, (unsigned long long)(p.board_index0 + ob));
+  const float target = u * total;
+  int cand = 0x7fffffff;
+  float run = before;
+  for (int a = a0; a < a1; ++a) {
+    run += s_e[a];
+    if (s_e[a] > 0.f && run > target) { cand = a; break; }
+  }
+  int pick = block_reduce_min_int(cand, s_redi);
+  if (pick == 0x7fffffff) {
+    // rounding left the target at or above the total: take the last cell with mass
+    int last = -1;
+    for (int a = a0; a < a1; ++a)
+      if (s_e[a] > 0.f) last = a;
+    __syncthreads();
+    pick = -block_reduce_min_int(-last, s_redi);
+  }
+  if (threadIdx.x == 0) {
+    if (p.action_out) p.action_out[ob] = pick;
+    // log-prob = z[a] - logsumexp(z), with z - zmax kept exact instead of log(exp(.))
+    const float zrel = none_legal ? 0.f : (s_z[pick] * inv_t - zmax);
+    if (p.logprob_out) p.logprob_out[ob] = zrel - logf(total);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Standalone operators
+// ------------------------------------------------------------------------------------------------
+__global__ void mask_logits_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ legal,
+                                   long long count, float fill, float* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) out[i] = legal[i] ? logits[i] : fill;
+}
+
+__global__ void transform_actions_kernel(const long long* __restrict__ actions, long long B, int n,
+                                         const uint8_t* __restrict__ phase, int phase_all, int inverse,
+                                         long long* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B) return;
+  const int ph = phase ? (phase[i] & 7) : (phase_all & 7);
+  const int a = (int)actions[i];
+  out[i] = inverse ? d4_inverse(a, n, ph) : d4_forward(a, n, ph);
+}
+
+__global__ void transform_boards_kernel(const int8_t* __restrict__ boards, long long B, int n,
+                                        const uint8_t* __restrict__ phase, int phase_all,
+                                        int8_t* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cells = n * n;
+  if (i >= B * cells) return;
+  const long long b = i / cells;
+  const int j = (int)(i - b * cells);
+  const int ph = phase ? (phase[b] & 7) : (phase_all & 7);
+  out[i] = boards[b * cells + d4_inverse(j, n, ph)];
+}
+
+__global__ void network_input_kernel(const int8_t* __restrict__ boards, const int8_t* __restrict__ player,
+                                     const int8_t* __restrict__ stones_left, long long B, int n,
+                                     float* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cells = n * n;
+  if (i >= B * cells) return;
+  const long long b = i / cells;
+  const int j = (int)(i - b * cells);
+  const int v = boards[i], me = player[b];
+  float* o = out + b * 3 * cells + j;
+  o[0] = v == me ? 1.f : 0.f;
+  o[cells] = v == -me ? 1.f : 0.f;
+  o[2 * cells] = stones_left[b] == 1 ? 1.f : 0.f;
+}
+
+// Debug aid: activation planes -> fp32 NCHW [G*nb, c, n, n]
+__global__ void unpack_activation_kernel(const uint4* __restrict__ planes, long long plane_rows, int front,
+                                         int group_pos, int slots, int wp, int n, int c_real, int nb,
+                                         float* __restrict__ out) {
+  const int g = blockIdx.y;
+  const int cells = n * n;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)nb * c_real * cells) return;
+  const int cell = (int)(idx % cells);
+  long long r = idx / cells;
+  const int ch = (int)(r % c_real);
+  const int t = (int)(r / c_real);
+  const int rr = cell / n, cc = cell - rr * n;
+  const long long row = (long long)front + (long long)g * group_pos + (long long)t * slots + rr * wp + cc;
+  const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(planes + (size_t)(ch >> 3) * plane_rows + row);
+  out[((size_t)g * nb + t) * c_real * cells + (size_t)ch * cells + cell] = __bfloat162float(e[ch & 7]);
+}
+
+}  // namespace c6

@@ -1,0 +1,84 @@
+// Shared device helpers: D4 index maps, Philox4x32-10, SiLU, bf16 packing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace c6 {
+
+constexpr float kFp32Min = -3.4028234663852886e38f;  // torch.finfo(torch.float32).min
+
+// device status bits (engine status word)
+constexpr int kStatWaitFull = 1;      // consumer wait on a "stage full" barrier ran out
+constexpr int kStatWaitEmpty = 2;     // producer wait on a "stage empty" barrier ran out
+constexpr int kStatWaitTmemFull = 4;  // epilogue wait on accumulator-ready ran out
+constexpr int kStatWaitTmemEmpty = 8; // MMA wait on accumulator-drained ran out
+constexpr int kStatWaitWeights = 16;  // wait on resident-weights barrier ran out
+constexpr int kStatWaitDrain = 32;    // final drain wait ran out
+
+// ---- D4 maps (connect6/train.py:216-277) ------------------------------------------
+// phase p in 0..7 -> k = p % 4 quarter turns (counter-clockwise), mirror columns if p >= 4.
+
+// canonical cell index -> index of the same cell inside view `phase`
+__host__ __device__ __forceinline__ int d4_forward(int a, int n, int phase) {
+  int r = a / n, c = a - r * n;
+  const int k = phase & 3;
+  int r2 = r, c2 = c;
+  if (k == 1) { r2 = n - 1 - c; c2 = r; }
+  else if (k == 2) { r2 = n - 1 - r; c2 = n - 1 - c; }
+  else if (k == 3) { r2 = c; c2 = n - 1 - r; }
+  if (phase & 4) c2 = n - 1 - c2;
+  return r2 * n + c2;
+}
+
+// view cell index -> canonical cell index (undo the mirror first, then the rotation)
+__host__ __device__ __forceinline__ int d4_inverse(int a, int n, int phase) {
+  int r = a / n, c = a - r * n;
+  const int k = phase & 3;
+  if (phase & 4) c = n - 1 - c;
+  int r2 = r, c2 = c;
+  if (k == 1) { r2 = c; c2 = n - 1 - r; }
+  else if (k == 2) { r2 = n - 1 - r; c2 = n - 1 - c; }
+  else if (k == 3) { r2 = n - 1 - c; c2 = r; }
+  return r2 * n + c2;
+}
+
+// ---- Philox4x32-10 ------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
+    const uint32_t hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += W0;
+    key.y += W1;
+  }
+  return ctr;
+}
+
+// The single uniform in [0,1) drawn for one board of one self-play step.
+__device__ __forceinline__ float board_uniform(uint64_t seed, uint64_t offset, uint64_t board) {
+  const uint4 ctr = make_uint4((uint32_t)board, (uint32_t)(board >> 32), (uint32_t)offset,
+                               (uint32_t)(offset >> 32));
+  const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
+  const uint4 r = philox4x32_10(ctr, key);
+  return (float)(r.x >> 8) * (1.0f / 16777216.0f);
+}
+
+// ---- activations ----------------------------------------------------------------------
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_exact(float x) { return x / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float load_x(const void* x, int x_bf16, int64_t idx) {
+  return x_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[idx])
+                : reinterpret_cast<const float*>(x)[idx];
+}
+
+}  // namespace c6

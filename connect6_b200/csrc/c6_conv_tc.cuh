@@ -1,0 +1,305 @@
+// k x k "same" convolution + bias + SiLU as an implicit GEMM on tcgen05 tensor cores
+// (backbone layers after the stem: connect6/model.py:52-67,104-106), optionally fused with
+// the two 1x1 heads (connect6/model.py:70-75,108-109).
+//
+// Data layout in HBM.  Activations are bf16 "channel-chunk planes": plane q holds channels
+// 8q..8q+7 of every board position as one 16-byte row, positions running linearly through a
+// zero-padded board image: cell (r,c) of board b is row  front + b*S + r*Wp + c  with
+// Wp = n + pad, S = Wp*Wp.  Column n..Wp-1 of every image row and image rows n..Wp-1 are
+// zero, so they serve as the right/left and bottom/top zero padding of neighbouring cells and
+// boards at once.  With this layout the input of filter tap (dy,dx) for 128 consecutive output
+// positions is the same plane shifted by dy*Wp+dx rows: ONE staged copy of 128+2*halo rows per
+// channel chunk feeds all k*k taps, and a tap is selected by moving the start address of the
+// MMA's shared-memory descriptor.
+//
+// GEMM view per tile: M = 128 positions (TMEM lanes), N = Cout, K = k*k*Cin walked as
+// (channel pair q) x (tap).  Weights are pre-packed [q][tap][2][Cout] rows of 8 bf16 and stay
+// resident in shared memory when they fit; otherwise the block of one q travels with the
+// activation stage.
+//
+// CTA = 192 threads: warp 0 issues bulk copies, warp 1 owns TMEM and issues MMAs, warps 2-5
+// drain the accumulator (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores).
+// Two TMEM accumulators let the epilogue of tile i overlap the MMAs of tile i+1.  Every wait
+// is bounded: when one runs out the CTA records a status bit, stops, frees TMEM and returns.
+#pragma once
+
+#include "c6_common.cuh"
+#include "c6_tc.cuh"
+
+namespace c6 {
+
+struct ConvTcParams {
+  const uint4* in;       // input planes  [cin/8][plane_rows] of 16-byte rows
+  uint4* out;            // output planes [n/8][plane_rows]; unused when head != 0
+  const uint4* w;        // packed weights, per group [cin/16][taps][2][n] rows
+  const float* bias;     // [G][n]
+  const float* head_wp;  // [G][n] policy 1x1 weights (head only)
+  const float* head_wv;  // [G][n] value 1x1 weights (head only)
+  float* logit_raw;      // [G * tiles_per_group * 128] (head only)
+  float* vmap;           // same shape (head only)
+  int* status;
+  long long plane_rows;
+  int front;             // plane row of position 0
+  int halo_rows;         // rows staged before and after the 128 tile rows (multiple of 8)
+  int cin, n;            // channel counts, padded to multiples of 32
+  int kside;             // filter side k
+  int wp, slots;         // padded row pitch Wp and slots per board S
+  int bsize;             // board side n
+  int nboards;           // boards per group in this pass
+  int tiles_per_group;
+  int ctas_per_group;
+  int resident;
+  int nstages;
+  int acc_stride;
+  int tmem_cols;
+  int head;
+};
+
+constexpr int kConvThreads = 192;
+constexpr int kConvSmemHeader = 3840;  // barriers, TMEM slot, abort flag, bias and head vectors
+constexpr int kMaxStages = 12;
+
+__host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 * halo_rows; }
+
+__global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte aligned view of dynamic shared memory
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  // barrier slots: [0,12) full, [12,24) empty, 24 weights, 25-26 acc full, 27-28 acc empty, 29 drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 512);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 516);
+  volatile int* never_flag = reinterpret_cast<volatile int*>(smem + 520);  // stays 0
+  float* s_bias = reinterpret_cast<float*>(smem + 640);
+  float* s_wp = s_bias + 256;
+  float* s_wv = s_wp + 256;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int taps = p.kside * p.kside;
+  const int nq = p.cin >> 4;
+  const int rows = conv_stage_rows(p.halo_rows);
+  const uint32_t a_bytes = 2u * rows * 16u;                     // two channel-chunk planes
+  const uint32_t wq_bytes = (uint32_t)taps * 2u * p.n * 16u;    // weights of one q
+  const uint32_t w_bytes = wq_bytes * nq;
+  const uint32_t stage_bytes = (a_bytes + (p.resident ? 0u : wq_bytes) + 127u) & ~127u;
+  const uint32_t w_region = p.resident ? ((w_bytes + 127u) & ~127u) : 0u;
+  uint8_t* s_w = smem + kConvSmemHeader;
+  uint8_t* s_stage = s_w + w_region;
+
+  const int group = blockIdx.x / p.ctas_per_group;
+  const int cta_in_group = blockIdx.x - group * p.ctas_per_group;
+  // contiguous, balanced tile range of this CTA inside its group
+  const int t_begin = (int)(((long long)p.tiles_per_group * cta_in_group) / p.ctas_per_group);
+  const int t_end = (int)(((long long)p.tiles_per_group * (cta_in_group + 1)) / p.ctas_per_group);
+
+  const uint32_t bar0 = tc::smem_u32(bars);
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (12 + s); };
+  const uint32_t bar_w = bar0 + 8u * 24;
+  auto bar_tfull = [&](int a) { return bar0 + 8u * (25 + a); };
+  auto bar_tempty = [&](int a) { return bar0 + 8u * (27 + a); };
+  const uint32_t bar_drain = bar0 + 8u * 29;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      tc::mbar_init(bar_full(s), 1);
+      tc::mbar_init(bar_empty(s), 1);
+    }
+    tc::mbar_init(bar_w, 1);
+    for (int a = 0; a < 2; ++a) {
+      tc::mbar_init(bar_tfull(a), 1);
+      tc::mbar_init(bar_tempty(a), 4);
+    }
+    tc::mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    *never_flag = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+    tc::tmem_relinquish();
+  }
+  if (warp >= 2) {
+    for (int i = threadIdx.x - 64; i < p.n; i += 128) {
+      s_bias[i] = p.bias[(size_t)group * p.n + i];
+      if (p.head) {
+        s_wp[i] = p.head_wp[(size_t)group * p.n + i];
+        s_wv[i] = p.head_wv[(size_t)group * p.n + i];
+      }
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint4* w_group = p.w + (size_t)group * (w_bytes / 16);
+  const long long group_row0 = (long long)p.front + (long long)group * p.tiles_per_group * 128;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------ producer ------------------------------
+    bool ok = true;
+    if (p.resident) {
+      tc::mbar_expect_tx(bar_w, w_bytes);
+      for (uint32_t off = 0; off < w_bytes; off += 32768u) {
+        const uint32_t len = (w_bytes - off) < 32768u ? (w_bytes - off) : 32768u;
+        tc::bulk_g2s(tc::smem_u32(s_w + off), reinterpret_cast<const uint8_t*>(w_group) + off, len, bar_w);
+      }
+    }
+    uint32_t it = 0;
+    for (int tile = t_begin; tile < t_end && ok; ++tile) {
+      const long long row0 = group_row0 + (long long)tile * 128 - p.halo_rows;
+      for (int q = 0; q < nq; ++q, ++it) {
+        const int s = it % p.nstages;
+        const uint32_t ph = (it / p.nstages) & 1u;
+        if (!tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag)) {
+          atomicOr(p.status, kStatWaitEmpty);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
+        tc::mbar_expect_tx(bar_full(s), a_bytes + (p.resident ? 0u : wq_bytes));
+        tc::bulk_g2s(dst, p.in + (size_t)(2 * q) * p.plane_rows + row0, rows * 16u, bar_full(s));
+        tc::bulk_g2s(dst + rows * 16u, p.in + (size_t)(2 * q + 1) * p.plane_rows + row0, rows * 16u,
+                     bar_full(s));
+        if (!p.resident)
+          tc::bulk_g2s(dst + a_bytes, reinterpret_cast<const uint8_t*>(w_group) + (size_t)q * wq_bytes,
+                       wq_bytes, bar_full(s));
+      }
+    }
+    if (!ok) {
+      // let copies already in flight land before the CTA's shared memory is released
+      for (int s = 0; s < p.nstages; ++s) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000) {
+          if (tc::mbar_try_wait(bar_full(s), 0) || tc::mbar_try_wait(bar_full(s), 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------ MMA issuer ------------------------------
+    const uint32_t idesc = tc::make_idesc_bf16(128, p.n);
+    const int kh = p.kside >> 1;
+    bool ok = true;
+    if (p.resident && !tc::mbar_wait(bar_w, 0, abort_flag)) {
+      atomicOr(p.status, kStatWaitWeights);
+      *abort_flag = 1;
+      ok = false;
+    }
+    uint32_t it = 0;
+    int tcount = 0;
+    for (int tile = t_begin; tile < t_end && ok; ++tile, ++tcount) {
+      const int acc = tcount & 1;
+      if (!tc::mbar_wait(bar_tempty(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag)) {
+        atomicOr(p.status, kStatWaitTmemEmpty);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc::fence_after_sync();
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
+      for (int q = 0; q < nq; ++q, ++it) {
+        const int s = it % p.nstages;
+        const uint32_t ph = (it / p.nstages) & 1u;
+        if (!tc::mbar_wait(bar_full(s), ph, abort_flag)) {
+          atomicOr(p.status, kStatWaitFull);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc::fence_after_sync();
+        const uint32_t a0 = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
+        const uint32_t b0 = p.resident ? tc::smem_u32(s_w) + (uint32_t)q * wq_bytes : a0 + a_bytes;
+        int tap = 0;
+        for (int dy = -kh; dy <= kh; ++dy) {
+          for (int dx = -kh; dx <= kh; ++dx, ++tap) {
+            const int shift = p.halo_rows + dy * p.wp + dx;  // >= 0 by construction
+            const uint64_t adesc = tc::make_desc(a0 + (uint32_t)shift * 16u, rows * 16u, 128u);
+            const uint64_t bdesc = tc::make_desc(b0 + (uint32_t)tap * 2u * p.n * 16u, p.n * 16u, 128u);
+            tc::mma_bf16(d_tmem, adesc, bdesc, idesc, (q | tap) != 0 ? 1u : 0u);
+          }
+        }
+        tc::mma_commit(bar_empty(s));  // stage reusable once these MMAs have read it
+      }
+      if (ok) tc::mma_commit(bar_tfull(acc));
+    }
+    // every MMA issued must have retired before TMEM is freed
+    tc::mma_commit(bar_drain);
+    if (!tc::mbar_wait(bar_drain, 0, never_flag)) {
+      atomicOr(p.status, kStatWaitDrain);
+      *abort_flag = 1;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------ epilogue ------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int row = quad * 32 + lane;
+    const int nchunk = p.n >> 5;
+    bool ok = true;
+    int tcount = 0;
+    for (int tile = t_begin; tile < t_end && ok; ++tile, ++tcount) {
+      const int acc = tcount & 1;
+      if (!tc::mbar_wait(bar_tfull(acc), (tcount >> 1) & 1u, abort_flag)) {
+        if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc::fence_after_sync();
+      const long long pos = (long long)tile * 128 + row;  // position inside the group
+      const int board = (int)(pos / p.slots);
+      const int slot = (int)(pos - (long long)board * p.slots);
+      const int r = slot / p.wp, c = slot - r * p.wp;
+      const bool valid = board < p.nboards && r < p.bsize && c < p.bsize;
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
+      uint4* out_row = p.out + group_row0 + pos;
+      float pol = 0.f, val = 0.f;
+      for (int ch = 0; ch < nchunk; ++ch) {
+        uint32_t v[32];
+        tc::tmem_ld32(taddr + (uint32_t)(ch * 32), v);
+        tc::tmem_wait_ld();
+        float y[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float x = __uint_as_float(v[j]) + s_bias[ch * 32 + j];
+          y[j] = valid ? silu_fast(x) : 0.f;
+        }
+        if (p.head) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            pol = fmaf(y[j], s_wp[ch * 32 + j], pol);
+            val = fmaf(y[j], s_wv[ch * 32 + j], val);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint4 o;
+            o.x = pack_bf16x2(y[8 * k + 0], y[8 * k + 1]);
+            o.y = pack_bf16x2(y[8 * k + 2], y[8 * k + 3]);
+            o.z = pack_bf16x2(y[8 * k + 4], y[8 * k + 5]);
+            o.w = pack_bf16x2(y[8 * k + 6], y[8 * k + 7]);
+            out_row[(size_t)(ch * 4 + k) * p.plane_rows] = o;
+          }
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
+      if (p.head) {
+        const long long o = (long long)group * p.tiles_per_group * 128 + pos;
+        p.logit_raw[o] = pol;
+        p.vmap[o] = val;
+      }
+    }
+  }
+
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+}  // namespace c6

@@ -1,0 +1,753 @@
+// Host side of the engine and its C ABI (see include/c6_engine.h for the contract).
+//
+// One engine = one architecture (board, kernels, channels), G stacked weight sets and one
+// arithmetic mode.  A forward call is cut into passes of at most `chunk` boards; a pass is a
+// fixed launch sequence on the caller's stream:
+//   bf16:  pack input -> stem GEMM (tcgen05) -> k x k conv layers (tcgen05, last one fused with
+//          both heads) -> finishing kernel
+//   fp32:  view copy -> direct conv layers (CUDA cores) -> head maps -> finishing kernel
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/c6_engine.h"
+#include "c6_aux_kernels.cuh"
+#include "c6_conv_tc.cuh"
+#include "c6_fp32_kernels.cuh"
+#include "c6_stem_tc.cuh"
+
+using namespace c6;
+
+namespace {
+
+constexpr int kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory per CTA on sm_100
+constexpr int kVersion = 10000;
+
+thread_local std::string g_create_error = "";
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline long long round_up_ll(long long v, long long m) { return (v + m - 1) / m * m; }
+inline int pow2_ceil(int v) {
+  int p = 32;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+struct LayerPlan {
+  int k = 0, cin = 0, cout = 0, cin_p = 0, cout_p = 0;
+  // tensor-core plan (layers >= 1)
+  int resident = 0, nstages = 0, smem = 0, acc_stride = 0, tmem_cols = 0;
+  size_t w_rows_per_group = 0;  // 16-byte rows of packed weights per group
+};
+
+}  // namespace
+
+struct C6Engine {
+  C6Desc d{};
+  int device = 0, sms = 148;
+  int n = 0, cells = 0, pad = 1, wp = 0, slots = 0, halo = 0, halo_rows = 0, front = 0;
+  int L = 0, G = 1, prec = 0, chunk = 0;
+  std::vector<LayerPlan> lp;
+  int cmax_p = 0, cmax = 0;
+  // stem GEMM plan
+  int kc0 = 0, nt = 0, ntiles = 0, ntot = 0, stem_stages = 0, stem_smem = 0, stem_acc_stride = 0,
+      stem_tmem_cols = 0;
+  // weights
+  uint4* wt = nullptr;              // [G][kc0][ntot]
+  std::vector<uint4*> wconv;        // per layer [G][rows]
+  std::vector<float*> bias;         // per layer [G][cout_p] (fp32 mode: [G][cout])
+  std::vector<float*> wraw;         // fp32 mode: per layer [G][cout*cin*k*k]
+  float *head_wp = nullptr, *head_wv = nullptr, *pol_bias = nullptr, *val_bias = nullptr;
+  std::vector<uint8_t> have;        // [G][L+2]
+  // workspace (capacity in boards per group)
+  long long cap = 0;
+  long long plane_rows = 0, mrows = 0;
+  uint4* xk = nullptr;
+  uint4* act[2] = {nullptr, nullptr};
+  float* f32buf[2] = {nullptr, nullptr};
+  float* f32x = nullptr;
+  float *logit_raw = nullptr, *vmap = nullptr;
+  long long last_group_pos = -1;
+  int* status_dev = nullptr;
+  long long launches = 0;
+  long long dev_bytes = 0;
+  long long ws_bytes = 0;
+  std::string err = "";
+};
+
+namespace {
+
+int fail(C6Engine* e, int code, const std::string& msg) {
+  if (e) e->err = msg; else g_create_error = msg;
+  return code;
+}
+
+#define C6_CUDA(e, call)                                                                         \
+  do {                                                                                           \
+    cudaError_t _st = (call);                                                                    \
+    if (_st != cudaSuccess)                                                                      \
+      return fail((e), C6_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(_st));        \
+  } while (0)
+
+#define C6_LAUNCHED(e, name)                                                                     \
+  do {                                                                                           \
+    cudaError_t _st = cudaGetLastError();                                                        \
+    if (_st != cudaSuccess)                                                                      \
+      return fail((e), C6_ERR_CUDA, std::string("launch ") + name + ": " + cudaGetErrorString(_st)); \
+    (e)->launches++;                                                                             \
+  } while (0)
+
+template <typename T>
+int dev_alloc(C6Engine* e, T** p, size_t count, bool zero, long long* tally) {
+  *p = nullptr;
+  if (count == 0) return C6_OK;
+  C6_CUDA(e, cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)));
+  if (zero) C6_CUDA(e, cudaMemset(*p, 0, count * sizeof(T)));
+  e->dev_bytes += (long long)(count * sizeof(T));
+  if (tally) *tally += (long long)(count * sizeof(T));
+  return C6_OK;
+}
+
+struct Geometry {
+  int tiles_per_group;
+  long long group_pos;        // positions reserved per group
+  int mrows_per_group;
+};
+
+Geometry geometry(const C6Engine* e, long long nb) {
+  Geometry g;
+  g.tiles_per_group = (int)((nb * e->slots + 127) / 128);
+  g.group_pos = (long long)g.tiles_per_group * 128;
+  g.mrows_per_group = (int)round_up_ll(nb, 128);
+  return g;
+}
+
+void free_workspace(C6Engine* e) {
+  cudaFree(e->xk);
+  cudaFree(e->act[0]);
+  cudaFree(e->act[1]);
+  cudaFree(e->f32buf[0]);
+  cudaFree(e->f32buf[1]);
+  cudaFree(e->f32x);
+  cudaFree(e->logit_raw);
+  cudaFree(e->vmap);
+  e->xk = nullptr;
+  e->act[0] = e->act[1] = nullptr;
+  e->f32buf[0] = e->f32buf[1] = nullptr;
+  e->f32x = nullptr;
+  e->logit_raw = e->vmap = nullptr;
+  e->dev_bytes -= e->ws_bytes;
+  e->ws_bytes = 0;
+  e->cap = 0;
+}
+
+// Grow the workspace to hold `nb` boards per group.  Synchronises the device when it grows.
+int ensure_workspace(C6Engine* e, long long nb) {
+  if (nb <= e->cap) return C6_OK;
+  C6_CUDA(e, cudaDeviceSynchronize());
+  free_workspace(e);
+  const Geometry g = geometry(e, nb);
+  if (e->prec == C6_PREC_BF16) {
+    e->plane_rows = (long long)e->front + (long long)e->G * g.group_pos + e->halo_rows;
+    e->mrows = (long long)e->G * g.mrows_per_group;
+    const size_t act_rows = (size_t)(e->cmax_p / 8) * e->plane_rows;
+    int rc;
+    if ((rc = dev_alloc(e, &e->xk, (size_t)e->kc0 * e->mrows, true, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->act[0], act_rows, true, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->act[1], act_rows, true, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->logit_raw, (size_t)e->G * g.group_pos, true, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->vmap, (size_t)e->G * g.group_pos, true, &e->ws_bytes))) return rc;
+  } else {
+    const size_t boards = (size_t)e->G * nb;
+    int rc;
+    if ((rc = dev_alloc(e, &e->f32x, boards * 3 * e->cells, false, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->f32buf[0], boards * e->cmax * e->cells, false, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->f32buf[1], boards * e->cmax * e->cells, false, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->logit_raw, boards * e->cells, false, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->vmap, boards * e->cells, false, &e->ws_bytes))) return rc;
+  }
+  e->cap = nb;
+  e->last_group_pos = -1;
+  return C6_OK;
+}
+
+int fp32_cit(const LayerPlan& l) { return l.k <= 5 ? std::min(l.cin, 16) : std::min(l.cin, 4); }
+size_t fp32_smem(const C6Engine* e, const LayerPlan& l) {
+  const int cit = fp32_cit(l), np = e->n + 2 * (l.k / 2);
+  return ((size_t)cit * np * np + (size_t)cit * l.k * l.k * kFp32CoT) * sizeof(float);
+}
+
+struct RunArgs {
+  const void* x = nullptr;
+  int x_bf16 = 0;
+  long long T = 0;  // boards per group
+  const uint8_t* orient = nullptr;
+  float* logits = nullptr;
+  float* value = nullptr;
+  int flags = 0;
+  int do_sample = 0;
+  float temperature = 1.f;
+  unsigned long long seed = 0, offset = 0;
+  long long board_index0 = 0;
+  long long* action = nullptr;
+  float* logprob = nullptr;
+  int stop_layer = -1;       // debug: stop after this backbone layer
+  float* layer_out = nullptr;  // debug: fp32 NCHW output of stop_layer
+};
+
+int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long group_stride,
+                  int board_stride, int pitch, cudaStream_t st) {
+  FinishParams f{};
+  f.logit_raw = e->logit_raw;
+  f.vmap = a.value ? e->vmap : nullptr;
+  f.group_stride = group_stride;
+  f.board_stride = board_stride;
+  f.pitch = pitch;
+  f.pol_bias = e->pol_bias;
+  f.val_bias = e->val_bias;
+  f.x = a.x;
+  f.x_bf16 = a.x_bf16;
+  f.orient = a.orient;
+  f.x_group_stride = a.T;
+  f.board0 = t0;
+  f.n = e->n;
+  f.n_actions = e->cells;
+  f.nb = nb;
+  f.flags = a.flags;
+  f.do_sample = a.do_sample;
+  f.temperature = a.temperature;
+  f.seed = a.seed;
+  f.offset = a.offset;
+  f.board_index0 = a.board_index0;
+  f.logits_out = a.logits;
+  f.value_out = a.value;
+  f.action_out = a.action;
+  f.logprob_out = a.logprob;
+  finish_kernel<<<dim3((unsigned)nb, (unsigned)e->G), kFinishThreads, 0, st>>>(f);
+  C6_LAUNCHED(e, "finish_kernel");
+  return C6_OK;
+}
+
+int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStream_t st) {
+  const Geometry g = geometry(e, nb);
+  if (e->G > 1 && g.group_pos != e->last_group_pos) {
+    // group bases moved: the zero padding between boards must be re-established
+    const size_t bytes = (size_t)(e->cmax_p / 8) * e->plane_rows * sizeof(uint4);
+    C6_CUDA(e, cudaMemsetAsync(e->act[0], 0, bytes, st));
+    C6_CUDA(e, cudaMemsetAsync(e->act[1], 0, bytes, st));
+  }
+  e->last_group_pos = g.group_pos;
+
+  {  // input planes
+    const long long total = (long long)e->kc0 * nb;
+    pack_stem_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
+        a.x, a.x_bf16, a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->n, nb, a.T, t0);
+    C6_LAUNCHED(e, "pack_stem_input_kernel");
+  }
+  int cur = 0;
+  {  // stem GEMM -> act[0]
+    StemTcParams p{};
+    p.xk = e->xk;
+    p.wt = e->wt;
+    p.bias = e->bias[0];
+    p.out = e->act[0];
+    p.status = e->status_dev;
+    p.plane_rows = e->plane_rows;
+    p.mrows = e->mrows;
+    p.mrows_per_group = g.mrows_per_group;
+    p.front = e->front;
+    p.group_pos = (int)g.group_pos;
+    p.kc = e->kc0;
+    p.ntot = e->ntot;
+    p.nt = e->nt;
+    p.ntiles = e->ntiles;
+    p.mtiles = g.mrows_per_group / 128;
+    p.groups = e->G;
+    p.c1 = e->lp[0].cout_p;
+    p.bsize = e->n;
+    p.wp = e->wp;
+    p.slots = e->slots;
+    p.nboards = nb;
+    p.nstages = e->stem_stages;
+    p.acc_stride = e->stem_acc_stride;
+    p.tmem_cols = e->stem_tmem_cols;
+    const long long items = (long long)e->G * p.mtiles * p.ntiles;
+    const int grid = (int)std::min<long long>(e->sms, items);
+    stem_tc_kernel<<<grid, kStemThreads, e->stem_smem, st>>>(p);
+    C6_LAUNCHED(e, "stem_tc_kernel");
+  }
+  const int last = a.stop_layer >= 0 ? a.stop_layer : e->L - 1;
+  for (int l = 1; l <= last; ++l) {
+    const LayerPlan& lp = e->lp[l];
+    ConvTcParams p{};
+    p.in = e->act[cur];
+    p.out = e->act[cur ^ 1];
+    p.w = e->wconv[l];
+    p.bias = e->bias[l];
+    p.head = (l == e->L - 1 && a.stop_layer < 0) ? 1 : 0;
+    p.head_wp = e->head_wp;
+    p.head_wv = e->head_wv;
+    p.logit_raw = e->logit_raw;
+    p.vmap = e->vmap;
+    p.status = e->status_dev;
+    p.plane_rows = e->plane_rows;
+    p.front = e->front;
+    p.halo_rows = e->halo_rows;
+    p.cin = lp.cin_p;
+    p.n = lp.cout_p;
+    p.kside = lp.k;
+    p.wp = e->wp;
+    p.slots = e->slots;
+    p.bsize = e->n;
+    p.nboards = nb;
+    p.tiles_per_group = g.tiles_per_group;
+    p.ctas_per_group = std::max(1, std::min(e->sms / e->G, g.tiles_per_group));
+    p.resident = lp.resident;
+    p.nstages = lp.nstages;
+    p.acc_stride = lp.acc_stride;
+    p.tmem_cols = lp.tmem_cols;
+    conv_tc_kernel<<<e->G * p.ctas_per_group, kConvThreads, lp.smem, st>>>(p);
+    C6_LAUNCHED(e, "conv_tc_kernel");
+    if (!p.head) cur ^= 1;
+  }
+  if (a.stop_layer >= 0) {
+    const LayerPlan& lp = e->lp[a.stop_layer];
+    const long long total = (long long)nb * lp.cout * e->cells;
+    unpack_activation_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
+        e->act[cur], e->plane_rows, e->front, (int)g.group_pos, e->slots, e->wp, e->n, lp.cout, nb,
+        a.layer_out);
+    C6_LAUNCHED(e, "unpack_activation_kernel");
+    return C6_OK;
+  }
+  return launch_finish(e, a, t0, nb, g.group_pos, e->slots, e->wp, st);
+}
+
+int run_pass_fp32(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStream_t st) {
+  const long long boards = (long long)e->G * nb;
+  {
+    const long long total = (long long)nb * 3 * e->cells;
+    view_input_f32_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
+        a.x, a.x_bf16, a.orient, e->f32x, e->n, nb, a.T, t0);
+    C6_LAUNCHED(e, "view_input_f32_kernel");
+  }
+  const float* in = e->f32x;
+  int cur = 0;
+  const int last = a.stop_layer >= 0 ? a.stop_layer : e->L - 1;
+  for (int l = 0; l <= last; ++l) {
+    const LayerPlan& lp = e->lp[l];
+    const dim3 grid((unsigned)boards, (unsigned)((lp.cout + kFp32CoT - 1) / kFp32CoT));
+    conv_fp32_kernel<<<grid, kFp32Threads, fp32_smem(e, lp), st>>>(in, e->wraw[l], e->bias[l], e->f32buf[cur],
+                                                                    lp.cin, lp.cout, lp.k, e->n, nb, fp32_cit(lp));
+    C6_LAUNCHED(e, "conv_fp32_kernel");
+    in = e->f32buf[cur];
+    cur ^= 1;
+  }
+  if (a.stop_layer >= 0) {
+    const LayerPlan& lp = e->lp[a.stop_layer];
+    C6_CUDA(e, cudaMemcpyAsync(a.layer_out, in, (size_t)boards * lp.cout * e->cells * sizeof(float),
+                               cudaMemcpyDeviceToDevice, st));
+    return C6_OK;
+  }
+  head_fp32_kernel<<<(unsigned)boards, kFp32Threads, 0, st>>>(in, e->head_wp, e->head_wv, e->logit_raw, e->vmap,
+                                                               e->lp[e->L - 1].cout, e->n, nb);
+  C6_LAUNCHED(e, "head_fp32_kernel");
+  return launch_finish(e, a, t0, nb, (long long)nb * e->cells, e->cells, e->n, st);
+}
+
+int run(C6Engine* e, const RunArgs& a, void* stream) {
+  if (!e) return C6_ERR_ARG;
+  if (a.T < 0) return fail(e, C6_ERR_ARG, "negative board count");
+  if (a.T == 0) return C6_OK;
+  if (!a.x) return fail(e, C6_ERR_ARG, "x is null");
+  for (size_t i = 0; i < e->have.size(); ++i)
+    if (!e->have[i]) return fail(e, C6_ERR_WEIGHTS, "forward before every layer and head of every group received weights");
+  C6_CUDA(e, cudaSetDevice(e->device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long per_pass = std::max<long long>(1, e->chunk / e->G);
+  int rc = ensure_workspace(e, std::min(a.T, per_pass));
+  if (rc) return rc;
+  for (long long t0 = 0; t0 < a.T; t0 += per_pass) {
+    const int nb = (int)std::min<long long>(per_pass, a.T - t0);
+    RunArgs b = a;
+    // outputs are indexed [g*T + t] by the kernels themselves (board0 = t0)
+    rc = e->prec == C6_PREC_BF16 ? run_pass_bf16(e, b, t0, nb, st) : run_pass_fp32(e, b, t0, nb, st);
+    if (rc) return rc;
+  }
+  return C6_OK;
+}
+
+}  // namespace
+
+// =================================================================================================
+// C ABI
+// =================================================================================================
+extern "C" {
+
+int c6_version(void) { return kVersion; }
+
+const char* c6_last_error(const C6Engine* eng) { return eng ? eng->err.c_str() : g_create_error.c_str(); }
+
+int c6_destroy(C6Engine* e) {
+  if (!e) return C6_OK;
+  cudaSetDevice(e->device);
+  cudaDeviceSynchronize();
+  free_workspace(e);
+  cudaFree(e->wt);
+  for (auto p : e->wconv) cudaFree(p);
+  for (auto p : e->bias) cudaFree(p);
+  for (auto p : e->wraw) cudaFree(p);
+  cudaFree(e->head_wp);
+  cudaFree(e->head_wv);
+  cudaFree(e->pol_bias);
+  cudaFree(e->val_bias);
+  cudaFree(e->status_dev);
+  delete e;
+  return C6_OK;
+}
+
+int c6_create(const C6Desc* d, C6Engine** out) {
+  if (!d || !out) return fail(nullptr, C6_ERR_ARG, "null argument");
+  *out = nullptr;
+  if (d->n_layers < 1 || d->n_layers > C6_MAX_LAYERS) return fail(nullptr, C6_ERR_ARG, "n_layers out of range");
+  if (d->board_size < 1 || d->board_size > 32) return fail(nullptr, C6_ERR_ARG, "board_size must be in 1..32");
+  if (d->groups < 1) return fail(nullptr, C6_ERR_ARG, "groups must be >= 1");
+  if (d->precision != C6_PREC_BF16 && d->precision != C6_PREC_FP32) return fail(nullptr, C6_ERR_ARG, "unknown precision");
+  for (int i = 0; i < d->n_layers; ++i) {
+    if (d->kernels[i] <= 0 || d->kernels[i] % 2 == 0) return fail(nullptr, C6_ERR_ARG, "every kernel must be a positive odd number");
+    if (d->channels[i] <= 0) return fail(nullptr, C6_ERR_ARG, "channel counts must be positive");
+  }
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || d->device < 0 || d->device >= ndev)
+    return fail(nullptr, C6_ERR_CUDA, "no such CUDA device (this engine has no CPU path)");
+
+  C6Engine* e = new (std::nothrow) C6Engine();
+  if (!e) return fail(nullptr, C6_ERR_ARG, "out of host memory");
+  e->d = *d;
+  e->device = d->device;
+  e->n = d->board_size;
+  e->cells = e->n * e->n;
+  e->L = d->n_layers;
+  e->G = d->groups;
+  e->prec = d->precision;
+  auto bail = [&](int code, const std::string& msg) {
+    g_create_error = msg.empty() ? e->err : msg;
+    c6_destroy(e);
+    return code;
+  };
+  if (cudaSetDevice(e->device) != cudaSuccess) return bail(C6_ERR_CUDA, "cudaSetDevice failed");
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, e->device) != cudaSuccess) return bail(C6_ERR_CUDA, "cudaGetDeviceProperties failed");
+  e->sms = prop.multiProcessorCount;
+  if (e->prec == C6_PREC_BF16 && prop.major != 10)
+    return bail(C6_ERR_UNSUPPORTED, "bf16 mode needs an sm_100 GPU (tcgen05 tensor cores)");
+
+  e->lp.resize(e->L);
+  int cin = 3;
+  for (int l = 0; l < e->L; ++l) {
+    LayerPlan& p = e->lp[l];
+    p.k = d->kernels[l];
+    p.cin = cin;
+    p.cout = d->channels[l];
+    p.cin_p = l == 0 ? 3 : round_up(cin, 32);
+    p.cout_p = round_up(p.cout, 32);
+    cin = p.cout;
+    e->cmax = std::max(e->cmax, p.cout);
+    e->cmax_p = std::max(e->cmax_p, p.cout_p);
+    if (l >= 1) e->pad = std::max(e->pad, p.k / 2);
+  }
+  e->wp = e->n + e->pad;
+  e->slots = e->wp * e->wp;
+  e->halo = e->pad * e->wp + e->pad;
+  e->halo_rows = round_up(e->halo, 8);
+  e->front = e->halo_rows;
+  e->chunk = d->max_chunk > 0 ? d->max_chunk : (e->prec == C6_PREC_BF16 ? 8192 : 1024);
+  e->have.assign((size_t)e->G * (e->L + 2), 0);
+
+  int rc;
+  if ((rc = dev_alloc(e, &e->status_dev, 1, true, nullptr))) return bail(rc, "");
+  if ((rc = dev_alloc(e, &e->pol_bias, e->G, true, nullptr))) return bail(rc, "");
+  if ((rc = dev_alloc(e, &e->val_bias, e->G, true, nullptr))) return bail(rc, "");
+  e->wconv.assign(e->L, nullptr);
+  e->bias.assign(e->L, nullptr);
+  e->wraw.assign(e->L, nullptr);
+
+  if (e->prec == C6_PREC_BF16) {
+    if (e->L < 2) return bail(C6_ERR_UNSUPPORTED, "bf16 mode needs at least two backbone layers");
+    if (e->cmax_p > 256) return bail(C6_ERR_UNSUPPORTED, "bf16 mode supports at most 256 channels per layer");
+    // stem GEMM
+    const int c1 = e->lp[0].cout_p;
+    e->kc0 = round_up(3 * e->cells, 32) / 8;
+    const int cpt = std::max(1, 256 / c1);
+    e->nt = c1 * cpt;
+    e->ntiles = (e->cells + cpt - 1) / cpt;
+    e->ntot = e->ntiles * e->nt;
+    const int sstage = 4 * 128 * 16 + 4 * e->nt * 16;
+    e->stem_stages = std::min(12, (kSmemLimit - 128 - kStemSmemHeader) / sstage);
+    e->stem_smem = 128 + kStemSmemHeader + e->stem_stages * sstage;
+    e->stem_acc_stride = pow2_ceil(e->nt);
+    e->stem_tmem_cols = 2 * e->stem_acc_stride;
+    if ((rc = dev_alloc(e, &e->wt, (size_t)e->G * e->kc0 * e->ntot, true, nullptr))) return bail(rc, "");
+    if ((rc = dev_alloc(e, &e->bias[0], (size_t)e->G * c1, true, nullptr))) return bail(rc, "");
+    // k x k layers
+    const int rows = conv_stage_rows(e->halo_rows);
+    const int a_bytes = 2 * rows * 16;
+    const int budget = kSmemLimit - 128 - kConvSmemHeader;
+    for (int l = 1; l < e->L; ++l) {
+      LayerPlan& p = e->lp[l];
+      const int taps = p.k * p.k, nq = p.cin_p / 16;
+      const long long wq = (long long)taps * 2 * p.cout_p * 16;
+      const long long wb = wq * nq;
+      p.w_rows_per_group = (size_t)(wb / 16);
+      const int a_stage = round_up(a_bytes, 128);
+      if (round_up_ll(wb, 128) + 4LL * a_stage <= budget) {
+        p.resident = 1;
+        p.nstages = (int)std::min<long long>(kMaxStages, (budget - round_up_ll(wb, 128)) / a_stage);
+        p.smem = 128 + kConvSmemHeader + (int)round_up_ll(wb, 128) + p.nstages * a_stage;
+      } else {
+        const long long s_stage = round_up_ll(a_bytes + wq, 128);
+        if (2 * s_stage > budget) return bail(C6_ERR_UNSUPPORTED, "a conv layer's per-chunk weights do not fit shared memory");
+        p.resident = 0;
+        p.nstages = (int)std::min<long long>(kMaxStages, budget / s_stage);
+        p.smem = 128 + kConvSmemHeader + p.nstages * (int)s_stage;
+      }
+      p.acc_stride = pow2_ceil(p.cout_p);
+      p.tmem_cols = 2 * p.acc_stride;
+      if ((rc = dev_alloc(e, &e->wconv[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
+      if ((rc = dev_alloc(e, &e->bias[l], (size_t)e->G * p.cout_p, true, nullptr))) return bail(rc, "");
+    }
+    const int cl = e->lp[e->L - 1].cout_p;
+    if ((rc = dev_alloc(e, &e->head_wp, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
+    if ((rc = dev_alloc(e, &e->head_wv, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
+    if (cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(stem_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+      return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+  } else {
+    size_t max_smem = 0;
+    for (int l = 0; l < e->L; ++l) {
+      const LayerPlan& p = e->lp[l];
+      if ((rc = dev_alloc(e, &e->wraw[l], (size_t)e->G * p.cout * p.cin * p.k * p.k, true, nullptr))) return bail(rc, "");
+      if ((rc = dev_alloc(e, &e->bias[l], (size_t)e->G * p.cout, true, nullptr))) return bail(rc, "");
+      max_smem = std::max(max_smem, fp32_smem(e, p));
+    }
+    if (max_smem > (size_t)kSmemLimit) return bail(C6_ERR_UNSUPPORTED, "fp32 mode: layer does not fit shared memory");
+    const int cl = e->lp[e->L - 1].cout;
+    if ((rc = dev_alloc(e, &e->head_wp, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
+    if ((rc = dev_alloc(e, &e->head_wv, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
+    if (cudaFuncSetAttribute(conv_fp32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max<size_t>(max_smem, 48 * 1024)) != cudaSuccess)
+      return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+  }
+  *out = e;
+  return C6_OK;
+}
+
+int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const float* bias, void* stream) {
+  if (!e) return C6_ERR_ARG;
+  if (group < 0 || group >= e->G) return fail(e, C6_ERR_ARG, "group out of range");
+  if (!w) return fail(e, C6_ERR_ARG, "weight pointer is null");
+  C6_CUDA(e, cudaSetDevice(e->device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool bf16 = e->prec == C6_PREC_BF16;
+  if (layer == C6_HEAD_POLICY || layer == C6_HEAD_VALUE) {
+    const LayerPlan& last = e->lp[e->L - 1];
+    const int cl = bf16 ? last.cout_p : last.cout;
+    float* dst = (layer == C6_HEAD_POLICY ? e->head_wp : e->head_wv) + (size_t)group * cl;
+    float* bdst = (layer == C6_HEAD_POLICY ? e->pol_bias : e->val_bias) + group;
+    copy_pad_f32_kernel<<<(cl + 127) / 128, 128, 0, st>>>(w, dst, last.cout, cl);
+    C6_LAUNCHED(e, "copy_pad_f32_kernel");
+    copy_pad_f32_kernel<<<1, 32, 0, st>>>(bias, bdst, 1, 1);
+    C6_LAUNCHED(e, "copy_pad_f32_kernel");
+    e->have[(size_t)group * (e->L + 2) + e->L + (layer == C6_HEAD_POLICY ? 0 : 1)] = 1;
+    return C6_OK;
+  }
+  if (layer < 0 || layer >= e->L) return fail(e, C6_ERR_ARG, "layer out of range");
+  const LayerPlan& p = e->lp[layer];
+  if (bf16) {
+    if (layer == 0) {
+      const long long total = (long long)e->kc0 * e->ntot;
+      pack_stem_toeplitz_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+          w, e->wt + (size_t)group * e->kc0 * e->ntot, p.cout, p.k, e->n, p.cout_p, e->kc0, e->ntot);
+      C6_LAUNCHED(e, "pack_stem_toeplitz_kernel");
+    } else {
+      const long long total = (long long)p.w_rows_per_group;
+      pack_conv_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+          w, e->wconv[layer] + (size_t)group * p.w_rows_per_group, p.cout, p.cin, p.k, p.cout_p, p.cin_p);
+      C6_LAUNCHED(e, "pack_conv_weights_kernel");
+    }
+    copy_pad_f32_kernel<<<(p.cout_p + 127) / 128, 128, 0, st>>>(bias, e->bias[layer] + (size_t)group * p.cout_p,
+                                                                 p.cout, p.cout_p);
+    C6_LAUNCHED(e, "copy_pad_f32_kernel");
+  } else {
+    const size_t wn = (size_t)p.cout * p.cin * p.k * p.k;
+    C6_CUDA(e, cudaMemcpyAsync(e->wraw[layer] + (size_t)group * wn, w, wn * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    copy_pad_f32_kernel<<<(p.cout + 127) / 128, 128, 0, st>>>(bias, e->bias[layer] + (size_t)group * p.cout, p.cout, p.cout);
+    C6_LAUNCHED(e, "copy_pad_f32_kernel");
+  }
+  e->have[(size_t)group * (e->L + 2) + layer] = 1;
+  return C6_OK;
+}
+
+int c6_reserve(C6Engine* e, int64_t boards) {
+  if (!e) return C6_ERR_ARG;
+  if (boards <= 0) return fail(e, C6_ERR_ARG, "boards must be positive");
+  C6_CUDA(e, cudaSetDevice(e->device));
+  const long long per_pass = std::max<long long>(1, e->chunk / e->G);
+  return ensure_workspace(e, std::min<long long>(boards, per_pass));
+}
+
+int c6_forward(C6Engine* e, const void* x, int x_dtype, int64_t B, const uint8_t* orient, float* logits,
+               float* value, int flags, void* stream) {
+  if (!e) return C6_ERR_ARG;
+  if (e->G != 1) return fail(e, C6_ERR_ARG, "c6_forward needs an engine with groups == 1");
+  if (x_dtype != C6_X_F32 && x_dtype != C6_X_BF16) return fail(e, C6_ERR_ARG, "unknown x dtype");
+  RunArgs a;
+  a.x = x;
+  a.x_bf16 = x_dtype == C6_X_BF16;
+  a.T = B;
+  a.orient = orient;
+  a.logits = logits;
+  a.value = value;
+  a.flags = flags;
+  return run(e, a, stream);
+}
+
+int c6_forward_step(C6Engine* e, const void* x, int x_dtype, int64_t B, const uint8_t* orient, int flags,
+                    float temperature, uint64_t seed, uint64_t offset, int64_t board_index0, int64_t* action,
+                    float* logprob, float* value, float* masked_logits, void* stream) {
+  if (!e) return C6_ERR_ARG;
+  if (e->G != 1) return fail(e, C6_ERR_ARG, "c6_forward_step needs an engine with groups == 1");
+  if (x_dtype != C6_X_F32 && x_dtype != C6_X_BF16) return fail(e, C6_ERR_ARG, "unknown x dtype");
+  if (B > 0 && !action) return fail(e, C6_ERR_ARG, "action pointer is null");
+  RunArgs a;
+  a.x = x;
+  a.x_bf16 = x_dtype == C6_X_BF16;
+  a.T = B;
+  a.orient = orient;
+  a.logits = masked_logits;
+  a.value = value;
+  a.flags = flags | C6_FLAG_MASK_LOGITS;
+  a.do_sample = 1;
+  a.temperature = temperature;
+  a.seed = seed;
+  a.offset = offset;
+  a.board_index0 = board_index0;
+  a.action = reinterpret_cast<long long*>(action);
+  a.logprob = logprob;
+  return run(e, a, stream);
+}
+
+int c6_forward_grouped(C6Engine* e, const void* x, int x_dtype, int64_t T, float* logits, float* value, int flags,
+                       void* stream) {
+  if (!e) return C6_ERR_ARG;
+  if (x_dtype != C6_X_F32 && x_dtype != C6_X_BF16) return fail(e, C6_ERR_ARG, "unknown x dtype");
+  RunArgs a;
+  a.x = x;
+  a.x_bf16 = x_dtype == C6_X_BF16;
+  a.T = T;
+  a.logits = logits;
+  a.value = value;
+  a.flags = flags;
+  return run(e, a, stream);
+}
+
+int c6_debug_layer_output(C6Engine* e, const void* x, int x_dtype, int64_t T, const uint8_t* orient, int layer,
+                          float* out_nchw, void* stream) {
+  if (!e) return C6_ERR_ARG;
+  if (layer < 0 || layer >= e->L) return fail(e, C6_ERR_ARG, "layer out of range");
+  if (!out_nchw) return fail(e, C6_ERR_ARG, "output pointer is null");
+  if (T > std::max<long long>(1, e->chunk / e->G)) return fail(e, C6_ERR_ARG, "debug output is limited to one pass");
+  RunArgs a;
+  a.x = x;
+  a.x_bf16 = x_dtype == C6_X_BF16;
+  a.T = T;
+  a.orient = orient;
+  a.stop_layer = layer;
+  a.layer_out = out_nchw;
+  return run(e, a, stream);
+}
+
+int c6_sample_actions(const float* logits, const uint8_t* legal, int64_t B, int32_t A, float temperature,
+                      uint64_t seed, uint64_t offset, int64_t board_index0, int64_t* action, float* logprob,
+                      void* stream) {
+  if (B < 0 || A <= 0 || A > kFinishMaxActions) return C6_ERR_ARG;
+  if (B == 0) return C6_OK;
+  if (!logits || !legal || !action) return C6_ERR_ARG;
+  FinishParams f{};
+  f.logits_in = logits;
+  f.legal_in = legal;
+  f.x_group_stride = B;
+  f.n = 1;
+  f.n_actions = A;
+  f.nb = (int)B;
+  f.do_sample = 1;
+  f.temperature = temperature;
+  f.seed = seed;
+  f.offset = offset;
+  f.board_index0 = board_index0;
+  f.action_out = reinterpret_cast<long long*>(action);
+  f.logprob_out = logprob;
+  finish_kernel<<<dim3((unsigned)B, 1), kFinishThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f);
+  return cudaGetLastError() == cudaSuccess ? C6_OK : C6_ERR_CUDA;
+}
+
+int c6_mask_logits(const float* logits, const uint8_t* legal, int64_t count, float fill, float* out, void* stream) {
+  if (count < 0) return C6_ERR_ARG;
+  if (count == 0) return C6_OK;
+  if (!logits || !legal || !out) return C6_ERR_ARG;
+  mask_logits_kernel<<<(unsigned)((count + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      logits, legal, count, fill, out);
+  return cudaGetLastError() == cudaSuccess ? C6_OK : C6_ERR_CUDA;
+}
+
+int c6_transform_actions(const int64_t* actions, int64_t B, int32_t n, const uint8_t* phase, int32_t phase_all,
+                         int32_t inverse, int64_t* out, void* stream) {
+  if (B < 0 || n <= 0) return C6_ERR_ARG;
+  if (B == 0) return C6_OK;
+  if (!actions || !out) return C6_ERR_ARG;
+  transform_actions_kernel<<<(unsigned)((B + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const long long*>(actions), B, n, phase, phase_all, inverse, reinterpret_cast<long long*>(out));
+  return cudaGetLastError() == cudaSuccess ? C6_OK : C6_ERR_CUDA;
+}
+
+int c6_transform_boards(const int8_t* boards, int64_t B, int32_t n, const uint8_t* phase, int32_t phase_all,
+                        int8_t* out, void* stream) {
+  if (B < 0 || n <= 0) return C6_ERR_ARG;
+  if (B == 0) return C6_OK;
+  if (!boards || !out) return C6_ERR_ARG;
+  const long long total = (long long)B * n * n;
+  transform_boards_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      boards, B, n, phase, phase_all, out);
+  return cudaGetLastError() == cudaSuccess ? C6_OK : C6_ERR_CUDA;
+}
+
+int c6_network_input(const int8_t* boards, const int8_t* current_player, const int8_t* stones_left, int64_t B,
+                     int32_t n, float* out, void* stream) {
+  if (B < 0 || n <= 0) return C6_ERR_ARG;
+  if (B == 0) return C6_OK;
+  if (!boards || !current_player || !stones_left || !out) return C6_ERR_ARG;
+  const long long total = (long long)B * n * n;
+  network_input_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      boards, current_player, stones_left, B, n, out);
+  return cudaGetLastError() == cudaSuccess ? C6_OK : C6_ERR_CUDA;
+}
+
+int c6_status(C6Engine* e, int* device_status) {
+  if (!e || !device_status) return C6_ERR_ARG;
+  C6_CUDA(e, cudaSetDevice(e->device));
+  C6_CUDA(e, cudaMemcpy(device_status, e->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*device_status != 0) {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "device status word 0x%x: a bounded wait inside a kernel ran out", *device_status);
+    return fail(e, C6_ERR_DEVICE, buf);
+  }
+  return C6_OK;
+}
+
+int64_t c6_launch_count(const C6Engine* e) { return e ? e->launches : 0; }
+int64_t c6_device_bytes(const C6Engine* e) { return e ? e->dev_bytes : 0; }
+
+}  // extern "C"

@@ -1,0 +1,254 @@
+// First backbone layer (the wide k0 x k0 stem, connect6/model.py:22,56-63) as ONE dense GEMM
+// on tcgen05 tensor cores.
+//
+// For an n x n board and a k0 x k0 filter with k0 >= n the filter footprint covers most of the
+// board from every output cell, so the layer is restated as a Toeplitz product
+//     out[b, cell_out*C1 + co] = sum_k  X[b, k] * T[cell_out*C1 + co, k],   k = ci*n*n + cell_in
+// with T[.., k] = w[co, ci, r_in - r_out + p, c_in - c_out + p] when that index lies inside the
+// filter and 0 otherwise (p = k0/2).  X is simply the flattened NCHW input, so no im2col exists
+// at run time; T is expanded once per weight update.  The product needs 3*n*n MACs per output
+// (1083 for n = 19) instead of the 3*k0*k0 = 1587 of the zero-padded definition.
+//
+// Operands use the same K-major no-swizzle chunk planes as the 3x3 kernel:
+//   X planes [K/8][Mrows] of 16-byte rows (row = board),  T planes [K/8][Ntot] (row = output).
+// Tile: 128 boards x NT outputs (NT = C1 * cells-per-tile <= 256), K walked 32 at a time
+// through a ring of bulk-copy stages.  The epilogue adds bias, applies SiLU and scatters each
+// 32-channel group to the padded activation planes the next layer reads.
+#pragma once
+
+#include "c6_common.cuh"
+#include "c6_tc.cuh"
+
+namespace c6 {
+
+struct StemTcParams {
+  const uint4* xk;    // [kc][mrows] input planes
+  const uint4* wt;    // [G][kc][ntot] Toeplitz planes
+  const float* bias;  // [G][c1]
+  uint4* out;         // activation planes [c1/8][plane_rows]
+  int* status;
+  long long plane_rows;
+  long long mrows;     // rows per X plane (= G * mrows_per_group)
+  int mrows_per_group; // multiple of 128
+  int front;
+  int group_pos;       // positions reserved per group in the activation planes
+  int kc;              // K chunks (multiple of 4)
+  int ntot;            // rows per T plane (= ntiles * nt)
+  int nt;              // outputs per tile (multiple of 32, <= 256)
+  int ntiles;
+  int mtiles;          // per group
+  int groups;
+  int c1;              // padded stem output channels
+  int bsize, wp, slots, nboards;
+  int nstages;
+  int acc_stride, tmem_cols;
+};
+
+constexpr int kStemThreads = 192;
+constexpr int kStemSmemHeader = 2048;
+
+__global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 512);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 516);
+  volatile int* never_flag = reinterpret_cast<volatile int*>(smem + 520);
+  float* s_bias = reinterpret_cast<float*>(smem + 640);  // [groups? no: one group per item] c1 floats, reloaded per item
+  uint8_t* s_stage = smem + kStemSmemHeader;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t a_plane = 128u * 16u;
+  const uint32_t b_plane = (uint32_t)p.nt * 16u;
+  const uint32_t a_bytes = 4u * a_plane, b_bytes = 4u * b_plane;
+  const uint32_t stage_bytes = a_bytes + b_bytes;  // multiples of 128 by construction
+  const int ksteps = p.kc >> 2;
+
+  const long long items = (long long)p.groups * p.mtiles * p.ntiles;
+  const long long i_begin = items * blockIdx.x / gridDim.x;
+  const long long i_end = items * (blockIdx.x + 1) / gridDim.x;
+
+  const uint32_t bar0 = tc::smem_u32(bars);
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (12 + s); };
+  auto bar_tfull = [&](int a) { return bar0 + 8u * (25 + a); };
+  auto bar_tempty = [&](int a) { return bar0 + 8u * (27 + a); };
+  const uint32_t bar_drain = bar0 + 8u * 29;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 12; ++s) {
+      tc::mbar_init(bar_full(s), 1);
+      tc::mbar_init(bar_empty(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      tc::mbar_init(bar_tfull(a), 1);
+      tc::mbar_init(bar_tempty(a), 4);
+    }
+    tc::mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    *never_flag = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+    tc::tmem_relinquish();
+  }
+  if (warp >= 2) {
+    for (int i = threadIdx.x - 64; i < p.groups * p.c1 && i < 320; i += 128) s_bias[i] = p.bias[i];
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool bias_in_smem = p.groups * p.c1 <= 320;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------ producer ------------------------------
+    bool ok = true;
+    uint32_t it = 0;
+    for (long long item = i_begin; item < i_end && ok; ++item) {
+      const int nt_i = (int)(item % p.ntiles);
+      const long long gm = item / p.ntiles;
+      const int mt = (int)(gm % p.mtiles);
+      const int g = (int)(gm / p.mtiles);
+      const uint4* xa = p.xk + (long long)g * p.mrows_per_group + (long long)mt * 128;
+      const uint4* wb = p.wt + (size_t)g * p.kc * p.ntot + (size_t)nt_i * p.nt;
+      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        const int s = it % p.nstages;
+        const uint32_t ph = (it / p.nstages) & 1u;
+        if (!tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag)) {
+          atomicOr(p.status, kStatWaitEmpty);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
+        tc::mbar_expect_tx(bar_full(s), stage_bytes);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kc = ks * 4 + j;
+          tc::bulk_g2s(dst + j * a_plane, xa + (size_t)kc * p.mrows, a_plane, bar_full(s));
+          tc::bulk_g2s(dst + a_bytes + j * b_plane, wb + (size_t)kc * p.ntot, b_plane, bar_full(s));
+        }
+      }
+    }
+    if (!ok) {
+      for (int s = 0; s < p.nstages; ++s) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000) {
+          if (tc::mbar_try_wait(bar_full(s), 0) || tc::mbar_try_wait(bar_full(s), 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------ MMA issuer ------------------------------
+    const uint32_t idesc = tc::make_idesc_bf16(128, p.nt);
+    bool ok = true;
+    uint32_t it = 0;
+    int tcount = 0;
+    for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
+      const int acc = tcount & 1;
+      if (!tc::mbar_wait(bar_tempty(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag)) {
+        atomicOr(p.status, kStatWaitTmemEmpty);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc::fence_after_sync();
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
+      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        const int s = it % p.nstages;
+        const uint32_t ph = (it / p.nstages) & 1u;
+        if (!tc::mbar_wait(bar_full(s), ph, abort_flag)) {
+          atomicOr(p.status, kStatWaitFull);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc::fence_after_sync();
+        const uint32_t a0 = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
+        const uint32_t b0 = a0 + a_bytes;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint64_t adesc = tc::make_desc(a0 + 2u * j * a_plane, a_plane, 128u);
+          const uint64_t bdesc = tc::make_desc(b0 + 2u * j * b_plane, b_plane, 128u);
+          tc::mma_bf16(d_tmem, adesc, bdesc, idesc, (ks | j) != 0 ? 1u : 0u);
+        }
+        tc::mma_commit(bar_empty(s));
+      }
+      if (ok) tc::mma_commit(bar_tfull(acc));
+    }
+    tc::mma_commit(bar_drain);
+    if (!tc::mbar_wait(bar_drain, 0, never_flag)) {
+      atomicOr(p.status, kStatWaitDrain);
+      *abort_flag = 1;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------ epilogue ------------------------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int nchunk = p.nt >> 5;
+    const int cells = p.bsize * p.bsize;
+    bool ok = true;
+    int tcount = 0;
+    for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
+      const int acc = tcount & 1;
+      const int nt_i = (int)(item % p.ntiles);
+      const long long gm = item / p.ntiles;
+      const int mt = (int)(gm % p.mtiles);
+      const int g = (int)(gm / p.mtiles);
+      if (!tc::mbar_wait(bar_tfull(acc), (tcount >> 1) & 1u, abort_flag)) {
+        if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc::fence_after_sync();
+      const int board = mt * 128 + row;
+      const bool bvalid = board < p.nboards;
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
+      const long long board_row = (long long)p.front + (long long)g * p.group_pos + (long long)board * p.slots;
+      const float* gbias = p.bias + (size_t)g * p.c1;
+      for (int ch = 0; ch < nchunk; ++ch) {
+        const int o = nt_i * p.nt + ch * 32;  // first output column of this chunk
+        const int cell = o / p.c1;
+        const int co0 = o - cell * p.c1;
+        uint32_t v[32];
+        tc::tmem_ld32(taddr + (uint32_t)(ch * 32), v);
+        tc::tmem_wait_ld();
+        if (bvalid && cell < cells) {
+          const int r = cell / p.bsize, c = cell - r * p.bsize;
+          uint4* dst = p.out + (size_t)(co0 >> 3) * p.plane_rows + board_row + r * p.wp + c;
+          float y[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float b = bias_in_smem ? s_bias[g * p.c1 + co0 + j] : gbias[co0 + j];
+            y[j] = silu_fast(__uint_as_float(v[j]) + b);
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint4 q;
+            q.x = pack_bf16x2(y[8 * k + 0], y[8 * k + 1]);
+            q.y = pack_bf16x2(y[8 * k + 2], y[8 * k + 3]);
+            q.z = pack_bf16x2(y[8 * k + 4], y[8 * k + 5]);
+            q.w = pack_bf16x2(y[8 * k + 6], y[8 * k + 7]);
+            dst[(size_t)k * p.plane_rows] = q;
+          }
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
+    }
+  }
+
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+}  // namespace c6

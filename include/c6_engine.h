@@ -1,0 +1,168 @@
+/*
+ * c6_engine.h -- C ABI of the B200 (sm_100a) inference engine for the Connect6
+ * policy/value CNN.
+ *
+ * The reference project (mgxmateusz/connect6) is pure Python on PyTorch and has
+ * no native interface; the entry points below are what a Python binding of its
+ * inference hot path needs, one per reference function that it replaces.  Every
+ * function is extern "C", takes plain pointers and sizes, returns an int status
+ * (0 = C6_OK), never throws, never exits the process and never traps the device.
+ * All data pointers are DEVICE pointers on the engine's device unless a
+ * parameter is documented as host memory.  The caller owns every input and
+ * output buffer; the engine owns packed weights and activation workspace only.
+ * Work is enqueued on the stream handed in (a cudaStream_t passed as void*);
+ * the engine never synchronises that stream except where documented
+ * (workspace growth).  One host thread at a time per engine handle.
+ */
+#ifndef C6_ENGINE_H_
+#define C6_ENGINE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define C6_MAX_LAYERS 16
+
+/* status codes */
+enum {
+  C6_OK = 0,
+  C6_ERR_ARG = 1,         /* bad argument (null pointer, bad size, bad enum)          */
+  C6_ERR_CUDA = 2,        /* a CUDA runtime call failed; see c6_last_error            */
+  C6_ERR_UNSUPPORTED = 3, /* architecture outside what the kernels implement          */
+  C6_ERR_WEIGHTS = 4,     /* forward called before every layer/head received weights  */
+  C6_ERR_DEVICE = 5       /* the device status word is non-zero (bounded wait ran out) */
+};
+
+/* arithmetic mode of an engine */
+enum {
+  C6_PREC_BF16 = 0, /* bf16 operands, fp32 accumulate, tcgen05 tensor cores            */
+  C6_PREC_FP32 = 1  /* fp32 operands and accumulate on CUDA cores (reference-exact mode) */
+};
+
+/* dtype of the network-input tensor x */
+enum { C6_X_F32 = 0, C6_X_BF16 = 1 };
+
+/* ids for c6_set_weights beyond the backbone layers 0..n_layers-1 */
+enum { C6_HEAD_POLICY = 100, C6_HEAD_VALUE = 101 };
+
+/* flags of the forward entry points */
+enum {
+  C6_FLAG_MASK_LOGITS = 1, /* write finfo(float32).min at occupied cells (model.py:123-125)   */
+  C6_FLAG_INVERSE_MAP = 2  /* with orient: return logits / actions in canonical cell indices   */
+};
+
+typedef struct C6Desc {
+  int32_t device;                  /* CUDA device ordinal                                   */
+  int32_t board_size;              /* n; the board is n x n (19)                             */
+  int32_t n_layers;                /* backbone depth, 1..C6_MAX_LAYERS                       */
+  int32_t kernels[C6_MAX_LAYERS];  /* odd kernel size per layer (connect6/model.py:22)       */
+  int32_t channels[C6_MAX_LAYERS]; /* output channels per layer (connect6/model.py:23)       */
+  int32_t groups;                  /* G stacked models; 1 = a single PolicyValueNet          */
+  int32_t precision;               /* C6_PREC_*                                              */
+  int32_t max_chunk;               /* boards per internal pass, 0 = default                  */
+} C6Desc;
+
+typedef struct C6Engine C6Engine;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int c6_version(void);
+
+/* Replaces: PolicyValueNet.__init__ / build_model (connect6/model.py:26-81, 114-120) and
+ * HistoricalPolicyEnsemble.__init__ (connect6/history.py:195-232) as far as device state goes.
+ * Validates the architecture the same way (odd positive kernels, positive channels). */
+int c6_create(const C6Desc* desc, C6Engine** out);
+
+/* Replaces: the parameter storage read by nn.Conv2d (connect6/model.py:56-75) and the weight
+ * stacking of connect6/history.py:224-240.  Packs one layer (or head) of one group from the
+ * reference state_dict layout: w is fp32 [Cout,Cin,K,K] (heads: [1,C,1,1]), bias fp32 [Cout]
+ * (heads: [1]; may be null = zeros).  Asynchronous on `stream`. */
+int c6_set_weights(C6Engine* eng, int group, int layer_or_head, const float* w_oihw,
+                   const float* bias, void* stream);
+
+/* Optional: grow the workspace for `boards` boards now (synchronises the device once).
+ * Forward calls grow it on demand otherwise. */
+int c6_reserve(C6Engine* eng, int64_t boards);
+
+/* Replaces: PolicyValueNet.forward (connect6/model.py:96-111), optionally fused with
+ * mask_logits (connect6/model.py:123-125) and the per-board D4 view of
+ * connect6/train.py:222-252.
+ *   x       [B,3,n,n] contiguous NCHW, dtype x_dtype
+ *   orient  nullable uint8 [B], D4 phase 0..7 per board (phase -> (k,flip) as train.py:216-219);
+ *           the planes are transformed on the fly before the network sees them
+ *   logits  nullable fp32 [B,n*n]; value nullable fp32 [B]
+ *   flags   C6_FLAG_* ; occupancy for masking is plane0|plane1 of x */
+int c6_forward(C6Engine* eng, const void* x, int x_dtype, int64_t B, const uint8_t* orient,
+               float* logits, float* value, int flags, void* stream);
+
+/* Replaces: one self-play inference step, connect6/train.py:792-795 = forward + _sample_actions
+ * (connect6/train.py:195-203): masked logits / max(T,1e-4), log-softmax, one categorical draw
+ * per board from a Philox4x32-10 stream keyed (seed, offset, board_index0 + b).
+ *   action int64 [B]; logprob nullable fp32 [B]; value nullable fp32 [B];
+ *   masked_logits nullable fp32 [B,n*n] (the masked, un-tempered logits) */
+int c6_forward_step(C6Engine* eng, const void* x, int x_dtype, int64_t B, const uint8_t* orient,
+                    int flags, float temperature, uint64_t seed, uint64_t offset,
+                    int64_t board_index0, int64_t* action, float* logprob, float* value,
+                    float* masked_logits, void* stream);
+
+/* Replaces: HistoricalPolicyEnsemble.forward_grouped (connect6/history.py:276-303): G
+ * independent models, T boards each, one launch sequence for all groups.
+ *   x [G,T,3,n,n]; logits fp32 [G,T,n*n]; value nullable fp32 [G,T] (the reference ensemble
+ *   has no value output; per-model PolicyValueNet.forward defines it) */
+int c6_forward_grouped(C6Engine* eng, const void* x, int x_dtype, int64_t T, float* logits,
+                       float* value, int flags, void* stream);
+
+/* Replaces: _sample_actions / _sample_actions_only on logits that already exist
+ * (connect6/train.py:195-213).  legal is uint8/bool [B,A]; logprob nullable. */
+int c6_sample_actions(const float* logits, const uint8_t* legal, int64_t B, int32_t A,
+                      float temperature, uint64_t seed, uint64_t offset, int64_t board_index0,
+                      int64_t* action, float* logprob, void* stream);
+
+/* Replaces: mask_logits (connect6/model.py:123-125) for fp32 logits; `fill` is the dtype
+ * minimum the caller's dtype implies (float32: -3.4028235e38, bfloat16: -3.3895314e38). */
+int c6_mask_logits(const float* logits, const uint8_t* legal, int64_t count, float fill,
+                   float* out, void* stream);
+
+/* Replaces: _transform_actions / _inverse_transform_actions (connect6/train.py:233-277).
+ * phase nullable uint8 [B] per action; if null `phase_all` applies to every action. */
+int c6_transform_actions(const int64_t* actions, int64_t B, int32_t n, const uint8_t* phase,
+                         int32_t phase_all, int32_t inverse, int64_t* out, void* stream);
+
+/* Replaces: _transform_boards (connect6/train.py:222-230) on int8 boards [B,n,n]. */
+int c6_transform_boards(const int8_t* boards, int64_t B, int32_t n, const uint8_t* phase,
+                        int32_t phase_all, int8_t* out, void* stream);
+
+/* Replaces: canonical_network_input (connect6/vector_env.py:196-218): int8 boards [B,n,n],
+ * current_player int8 [B], stones_left int8 [B] -> fp32 planes [B,3,n,n]. */
+int c6_network_input(const int8_t* boards, const int8_t* current_player, const int8_t* stones_left,
+                     int64_t B, int32_t n, float* out, void* stream);
+
+/* Test aid with no reference function of its own: runs the backbone up to and including
+ * `layer` and writes that layer's activation, SiLU applied (the `features` tensor inside the
+ * loop at connect6/model.py:104-106), as fp32 [G*T, channels[layer], n, n].  T is limited to
+ * one internal pass. */
+int c6_debug_layer_output(C6Engine* eng, const void* x, int x_dtype, int64_t T,
+                          const uint8_t* orient, int layer, float* out_nchw, void* stream);
+
+/* Reads the device status word (host int). Non-zero means a bounded wait inside a kernel ran
+ * out; the kernels then skip their work instead of hanging. The caller must have synchronised
+ * the stream it used. */
+int c6_status(C6Engine* eng, int* device_status);
+
+/* Number of kernel launches the engine has enqueued since creation (host counter). */
+int64_t c6_launch_count(const C6Engine* eng);
+
+/* Bytes of device memory the engine currently owns (weights + workspace). */
+int64_t c6_device_bytes(const C6Engine* eng);
+
+/* Last error text of this engine (or of c6_create when eng is null). Never null. */
+const char* c6_last_error(const C6Engine* eng);
+
+/* Frees everything the engine owns. */
+int c6_destroy(C6Engine* eng);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* C6_ENGINE_H_ */

@@ -1,0 +1,158 @@
+"""Generate the golden fixtures in this directory from the UNMODIFIED reference.
+
+Run where the reference checkout is importable:
+    python tests/golden/make_golden.py [/path/to/reference]
+It imports `connect6.*` from that path (default: $C6_REFERENCE or /root/reference), runs the
+reference's own functions on seeded inputs and stores inputs, weights and outputs as .npz.
+The tests only read the .npz files; they never need the reference.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+REPO = HERE.parent.parent
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("C6_REFERENCE", "/root/reference"))
+sys.path.insert(0, str(REF))
+sys.path.insert(1, str(REPO))
+
+from connect6.history import HistoricalCheckpoint, HistoricalPolicyEnsemble  # noqa: E402
+from connect6.model import PolicyValueNet, build_model, mask_logits  # noqa: E402
+from connect6.train import (  # noqa: E402
+    _inverse_transform_actions, _sample_actions, _symmetry_for_phase, _transform_actions, _transform_boards)
+from connect6.vector_env import canonical_network_input  # noqa: E402
+
+from connect6_b200.boards import generate_planes  # noqa: E402
+
+
+def state_np(model) -> dict:
+    return {k: v.detach().cpu().numpy().copy() for k, v in model.state_dict().items()}
+
+
+def state_hash(state: dict) -> str:
+    h = hashlib.sha256()
+    for k in sorted(state):
+        h.update(k.encode())
+        h.update(np.ascontiguousarray(state[k], dtype=np.float32).tobytes())
+    return h.hexdigest()
+
+
+def main() -> None:
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+
+    # 1. small net with an even-wider-than-board stem: weights stored, random real-valued input
+    torch.manual_seed(7)
+    small = PolicyValueNet(board_size=7, kernels=[9, 3, 3], channels=[8, 8, 16]).eval()
+    with torch.no_grad():
+        for p in small.parameters():  # non-zero biases so that bias handling is pinned too
+            if p.ndim == 1:
+                p.uniform_(-0.2, 0.2)
+        small.policy_output.weight.mul_(30.0)
+        small.value_output.weight.mul_(30.0)
+    xs = torch.randn(5, 3, 7, 7)
+    with torch.inference_mode():
+        ls, vs = small(xs)
+    np.savez_compressed(HERE / "small_net.npz", x=xs.numpy(), logits=ls.numpy(), value=vs.numpy(),
+                        kernels=np.array([9, 3, 3]), channels=np.array([8, 8, 16]), board_size=7,
+                        **{"w::" + k: v for k, v in state_np(small).items()})
+
+    # 2. default v4 net, torch seed 42 (configs/train.yaml:8), generated boards 0..5
+    torch.manual_seed(42)
+    net = PolicyValueNet(board_size=19).eval()
+    st = state_np(net)
+    xd = torch.from_numpy(generate_planes(0, 6))
+    with torch.inference_mode():
+        ld, vd = net(xd)
+        feats = xd
+        layer_stats = []
+        for conv in net.convs:
+            feats = torch.nn.functional.silu(conv(feats))
+            layer_stats.append([float(feats.mean()), float(feats.std()), float(feats.abs().max())])
+    np.savez_compressed(HERE / "default_net_seed42.npz", logits=ld.numpy(), value=vd.numpy(),
+                        weights_sha256=state_hash(st), layer_stats=np.array(layer_stats),
+                        first_board_indices=np.arange(6), torch_version=torch.__version__,
+                        first_weights=st["convs.0.weight"][:2, :, :2, :2],
+                        policy_weight=st["policy_output.weight"].reshape(-1))
+
+    # 3. D4 tables for n = 19 and n = 7, all 8 phases, straight from the reference helpers
+    d4 = {}
+    for n in (7, 19):
+        a = torch.arange(n * n)
+        board = torch.arange(n * n, dtype=torch.int16).reshape(1, n, n)
+        fwd, inv, views = [], [], []
+        for phase in range(8):
+            k, flip = _symmetry_for_phase(phase)
+            fwd.append(_transform_actions(a, n, k, flip).numpy())
+            inv.append(_inverse_transform_actions(a, n, k, flip).numpy())
+            views.append(_transform_boards(board, k, flip).reshape(-1).numpy())
+        d4[f"fwd{n}"] = np.stack(fwd).astype(np.int32)
+        d4[f"inv{n}"] = np.stack(inv).astype(np.int32)
+        d4[f"view{n}"] = np.stack(views).astype(np.int32)
+    d4["phases"] = np.array([list(map(int, _symmetry_for_phase(p))) for p in range(10)])
+    np.savez_compressed(HERE / "d4_tables.npz", **d4)
+
+    # 4. grouped ensemble on the reference test's own configuration
+    #    (tests/test_training_features.py:120-151), three models
+    torch.manual_seed(123)
+    cfg = {"architecture_version": 4, "kernels": [3, 3, 3], "channels": [8, 8, 16], "compile": False,
+           "compile_mode": "default"}
+    game = {"board_size": 5, "win_length": 3}
+    models = [build_model(cfg, 5) for _ in range(3)]
+    cps = [HistoricalCheckpoint(path=Path(f"model_update_{i + 1:08d}.pt"), update=i + 1,
+                                model_state=m.state_dict(), model_config=cfg, game_config=game)
+           for i, m in enumerate(models)]
+    ens = HistoricalPolicyEnsemble(cps, torch.device("cpu"))
+    xg = torch.randn(3, 4, 3, 5, 5)
+    with torch.inference_mode():
+        lg = ens.forward_grouped(xg)
+        vg = torch.stack([m.eval()(xg[i])[1] for i, m in enumerate(models)])
+    blob = {"x": xg.numpy(), "logits": lg.numpy(), "value": vg.numpy(), "kernels": np.array([3, 3, 3]),
+            "channels": np.array([8, 8, 16]), "board_size": 5}
+    for i, m in enumerate(models):
+        blob.update({f"w{i}::" + k: v for k, v in state_np(m).items()})
+    np.savez_compressed(HERE / "grouped_small.npz", **blob)
+
+    # 5. masking and the masked categorical's log-probabilities
+    torch.manual_seed(5)
+    lo = torch.randn(6, 361) * 2.0
+    legal = torch.rand(6, 361) > 0.4
+    legal[4] = False
+    legal[4, 17] = True      # a single legal move
+    legal[5] = False         # no legal move at all: torch yields a uniform distribution
+    masked = mask_logits(lo, legal)
+    masked_bf16 = mask_logits(lo.bfloat16(), legal).float()
+    out = {"logits": lo.numpy(), "legal": legal.numpy(), "masked": masked.numpy(), "masked_bf16": masked_bf16.numpy()}
+    for T in (1.0, 0.5, 2.0):
+        # with T < 1 the fill overflows to -inf and torch rejects the all-occupied row (NaN), so
+        # that row is pinned for T >= 1 only
+        rows = slice(0, 5) if T < 1.0 else slice(0, 6)
+        z = mask_logits(lo.float(), legal)[rows] / max(T, 1e-4)
+        dist = torch.distributions.Categorical(logits=z)
+        out[f"logp_T{T}"] = dist.logits.numpy()
+    torch.manual_seed(11)
+    acts, lps = _sample_actions(lo[:4], legal[:4], 1.0)
+    out["sampled_actions"] = acts.numpy()
+    out["sampled_logprob"] = lps.numpy()
+    np.savez_compressed(HERE / "masking.npz", **out)
+
+    # 6. network planes from raw boards
+    torch.manual_seed(3)
+    boards = torch.randint(-1, 2, (5, 19, 19), dtype=torch.int8)
+    player = torch.tensor([1, -1, 1, -1, 1], dtype=torch.int8)
+    stones_left = torch.tensor([1, 2, 2, 1, 1], dtype=torch.int8)
+    planes = canonical_network_input(boards, player, stones_left)
+    np.savez_compressed(HERE / "network_input.npz", boards=boards.numpy(), player=player.numpy(),
+                        stones_left=stones_left.numpy(), planes=planes.numpy())
+    print("fixtures written to", HERE)
+    for f in sorted(HERE.glob("*.npz")):
+        print(f"  {f.name}: {f.stat().st_size} bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -179,7 +179,8 @@ int ensure_workspace(C6Engine* e, long long nb) {
 int fp32_cit(const LayerPlan& l) { return l.k <= 5 ? std::min(l.cin, 16) : std::min(l.cin, 4); }
 size_t fp32_smem(const C6Engine* e, const LayerPlan& l) {
   const int cit = fp32_cit(l), np = e->n + 2 * (l.k / 2);
-  return ((size_t)cit * np * np + (size_t)cit * l.k * l.k * kFp32CoT) * sizeof(float);
+  const size_t in_floats = ((size_t)cit * np * np + 3) & ~(size_t)3;  // weights start 16-byte aligned
+  return (in_floats + (size_t)cit * l.k * l.k * kFp32CoT) * sizeof(float);
 }
 
 struct RunArgs {

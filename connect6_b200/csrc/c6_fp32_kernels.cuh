@@ -17,10 +17,10 @@ constexpr int kFp32MaxCells = 8;  // cells per thread -> boards up to 32 x 32
 __global__ void __launch_bounds__(kFp32Threads) conv_fp32_kernel(
     const float* __restrict__ in, const float* __restrict__ w, const float* __restrict__ bias,
     float* __restrict__ out, int cin, int cout, int kside, int n, int nb, int cit) {
-  extern __shared__ float smem_f[];
+  extern __shared__ __align__(16) float smem_f[];
   const int pad = kside >> 1, np = n + 2 * pad, taps = kside * kside, cells = n * n;
-  float* s_in = smem_f;                     // [cit][np*np]
-  float* s_w = smem_f + (size_t)cit * np * np;  // [cit][taps][kFp32CoT]
+  float* s_in = smem_f;                                            // [cit][np*np]
+  float* s_w = smem_f + (((size_t)cit * np * np + 3) & ~(size_t)3);  // [cit][taps][kFp32CoT], 16-byte aligned
 
   const int board = blockIdx.x;
   const int g = board / nb;

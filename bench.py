@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the Connect6 policy/value CNN hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl engine|reference]
+
+One "step" is one self-play inference step over one batch of synthetic boards: the bf16 CNN
+forward, masked policy log-softmax, one categorical draw per board from the engine's Philox
+stream, and the value head (connect6/train.py:792-795 in the reference).  Per GPU the batch is
+8192 boards; with N GPUs every rank owns its own 8192 boards of the global index range (weak
+scaling), weights are replicated and the only collective is the sum of a 9 x int64 statistics
+vector per step.  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU restatement of the reference's own PyTorch path (oracle/
+torch_port.py: the same torch CPU operators the reference calls) on the host cores, one bounded
+sample of the workload per step.
+"""
+from __future__ import annotations
+
+import argparse
+import datetime as dt
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "board-evals/sec (CNN fwd, bf16, B=8192)"
+UNIT = "boards/s"
+BATCH = 8192
+FLOP_PER_BOARD = 269_692_992            # dense conv count of the default v4 net incl. heads
+CONV_LAYER_MACS = [18_333_024, 3_326_976, 6_653_952, 13_307_904, 13_307_904, 19_961_856, 29_942_784, 29_942_784]
+HEAD_MACS = 69_312
+INPUT_BUFFERS = 5                       # 5 x 35.5 MB of inputs rotate: larger than the 126 MB L2
+# DRAM traffic of conv_tc_kernel per launch, from the ncu capture summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the 7 launches of one step).
+CONV_TRAFFIC_BYTES_PER_LAUNCH = None
+WEIGHT_SEED = 42
+CPU_SAMPLE_BOARDS = 256
+
+
+def load_peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text()), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# clock sampling during the timed region
+# ------------------------------------------------------------------------------------------------
+_SMI_FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+class ClockSampler:
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.path = ROOT / "gpurun_out" / f"clocks_bench_gpu{gpu_index}.csv"
+        try:
+            self.path.parent.mkdir(exist_ok=True)
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={_SMI_FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(gpu_index)], stdout=self.fh, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self, t_begin: dt.datetime, t_end: dt.datetime) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        rows_all, rows_in = [], []
+        for line in self.path.read_text().splitlines():
+            parts = [s.strip() for s in line.split(",")]
+            if len(parts) < 10:
+                continue
+            try:
+                ts = dt.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                row = (float(parts[2]), float(parts[3]), float(parts[4]), parts[5:10])
+            except Exception:
+                continue
+            rows_all.append(row)
+            if t_begin <= ts <= t_end:
+                rows_in.append(row)
+        rows = rows_in if len(rows_in) >= 2 else rows_all
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["active", "hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = set()
+        for r in rows:
+            for name, val in zip(names[1:], r[3][1:]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(r[0] for r in rows), "sm_max_mhz": rows[0][1],
+                "power_w_max": max(r[2] for r in rows), "reasons": sorted(reasons), "samples": len(rows),
+                "samples_in_timed_region": len(rows_in)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs (the only places that touch oracle/)
+# ------------------------------------------------------------------------------------------------
+def _cpu_step_fn():
+    """One bounded sample of the workload on the host: fp32 forward + masked categorical draw for
+    CPU_SAMPLE_BOARDS boards, through the torch-CPU restatement of the reference."""
+    import torch
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import torch_port as TP
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.model import PolicyValueNet
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    torch.manual_seed(WEIGHT_SEED)
+    params = {k: v.detach() for k, v in PolicyValueNet(19).state_dict().items()}
+    x = torch.from_numpy(generate_planes(0, CPU_SAMPLE_BOARDS))
+    legal = ((x[:, 0] == 0) & (x[:, 1] == 0)).reshape(CPU_SAMPLE_BOARDS, -1)
+
+    def step():
+        logits, value = TP.policy_value_forward(x, params)
+        logp = TP.masked_log_softmax(logits, legal, 1.0)
+        actions = torch.multinomial(logp.exp(), 1)
+        return actions, value
+
+    return step, torch.get_num_threads()
+
+
+def cpu_baseline(budget_s: float = 12.0) -> dict:
+    step, threads = _cpu_step_fn()
+    for _ in range(2):
+        step()
+    times = []
+    t_all = time.perf_counter()
+    while (time.perf_counter() - t_all < budget_s and len(times) < 40) or len(times) < 3:
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return {"value": CPU_SAMPLE_BOARDS / med, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{len(times)} x {CPU_SAMPLE_BOARDS} boards, fp32 torch-CPU restatement of the reference "
+                      f"forward + masked categorical draw, median step {med * 1e3:.1f} ms"}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    step, threads = _cpu_step_fn()
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    el = time.perf_counter() - t0
+    value = CPU_SAMPLE_BOARDS * args.steps / el
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "self-play inference step: default v4 CNN forward + masked log-softmax + 1 draw/board",
+                   "sample_boards_per_step": CPU_SAMPLE_BOARDS, "note": "host CPU, all threads"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{args.steps} x {CPU_SAMPLE_BOARDS} boards per step"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# engine arm
+# ------------------------------------------------------------------------------------------------
+def run_engine(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from connect6_b200 import shard
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.model import PolicyValueNet
+
+    rank, world, local_rank = shard.init_from_env()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    peaks, peak_kind = load_peaks()
+
+    torch.manual_seed(WEIGHT_SEED)
+    model = PolicyValueNet(19).to(dev).eval()
+    eng = model.engine_for(dev)
+    eng.reserve(BATCH)
+
+    # this rank's boards: global indices [rank*BATCH*INPUT_BUFFERS, ...), INPUT_BUFFERS batches
+    first = rank * BATCH * INPUT_BUFFERS
+    host_batches = [torch.from_numpy(generate_planes(first + i * BATCH, BATCH)).pin_memory()
+                    for i in range(INPUT_BUFFERS)]
+    dev_batches = [h.to(dev) for h in host_batches]
+    stats = torch.zeros(9, dtype=torch.int64, device=dev)
+
+    def step(i: int):
+        x = dev_batches[i % INPUT_BUFFERS]
+        action, logprob, value, _ = eng.forward_step(x, temperature=1.0, seed=0xC6, offset=i,
+                                                     board_index0=first + (i % INPUT_BUFFERS) * BATCH)
+        stats[0] = action.numel()          # stand-in for the collector's per-step statistics vector
+        shard.reduce_rollout_stats(stats)
+        return action, logprob, value
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize(dev)
+    shard.barrier()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = eng.launch_count
+    eng.profile(True)
+    eng.profile_read()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    shard.barrier()
+    t_begin = dt.datetime.now()
+    ev0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    t_end = dt.datetime.now()
+    shard.barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    prof = eng.profile_read()
+    eng.profile(False)
+    launches = eng.launch_count - launches0
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
+    elapsed_ms = shard.max_over_ranks(elapsed_ms, dev)
+    status = eng.status()
+
+    # ---- end to end: host buffers in, host results out, through the public drop-in API ----------
+    out_host = {
+        "action": torch.empty(BATCH, dtype=torch.int64).pin_memory(),
+        "logprob": torch.empty(BATCH, dtype=torch.float32).pin_memory(),
+        "value": torch.empty(BATCH, dtype=torch.float32).pin_memory(),
+    }
+    x_dev = torch.empty_like(dev_batches[0])
+
+    def e2e_step(i: int):
+        x_dev.copy_(host_batches[i % INPUT_BUFFERS], non_blocking=True)
+        action, logprob, value, _ = model.selfplay_step(x_dev, temperature=1.0, seed=0xC6, offset=i,
+                                                        board_index0=first + (i % INPUT_BUFFERS) * BATCH)
+        out_host["action"].copy_(action, non_blocking=True)
+        out_host["logprob"].copy_(logprob, non_blocking=True)
+        out_host["value"].copy_(value, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()   # the caller reads the step's result
+
+    e2e_steps = max(3, min(args.steps, 100))
+    for i in range(3):
+        e2e_step(i)
+    torch.cuda.synchronize(dev)
+    shard.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    e2e_ms = shard.max_over_ranks(e0.elapsed_time(e1), dev)
+    h2d = host_batches[0].numel() * 4
+    d2h = BATCH * (8 + 4 + 4)
+
+    if rank != 0:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+        return
+
+    total_boards = BATCH * world * args.steps
+    value = total_boards / (elapsed_ms * 1e-3)
+    ms_per_step = elapsed_ms / args.steps
+    # dominant kernel: conv_tc_kernel (backbone layers 1..7, 7 launches per step)
+    conv_ms = sum(ms for k, (ms, n) in prof.items() if k.startswith("conv"))
+    conv_launches = sum(n for k, (ms, n) in prof.items() if k.startswith("conv"))
+    conv_flop_per_step = 2 * (sum(CONV_LAYER_MACS[1:]) + HEAD_MACS) * BATCH
+    peak = float(peaks["bf16_tflops"])
+    roof = None
+    if conv_launches:
+        avg_ms = conv_ms / conv_launches
+        flop_per_launch = conv_flop_per_step * args.steps / conv_launches
+        achieved = flop_per_launch / (avg_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "conv_tc_kernel (backbone layers 1-7 + fused heads)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": f"MEASURED_PEAKS.json bf16_tflops (burst), of {peak_kind}",
+                "frac_of_sustained": achieved / float(peaks.get("bf16_tflops_sustained", peak)),
+                "traffic": CONV_TRAFFIC_BYTES_PER_LAUNCH, "launches": conv_launches, "avg_launch_ms": avg_ms,
+                "flop_per_launch": flop_per_launch}
+    kernels = {}
+    for k, (ms, n) in sorted(prof.items()):
+        entry = {"ms_per_step": ms / args.steps, "launches_per_step": n / args.steps}
+        if k == "stem":
+            entry["tflops_nominal"] = 2 * CONV_LAYER_MACS[0] * BATCH / (ms / args.steps * 1e-3) / 1e12
+        elif k.startswith("conv"):
+            li = int(k[4:])
+            macs = CONV_LAYER_MACS[li] + (HEAD_MACS if li == 7 else 0)
+            entry["tflops_nominal"] = 2 * macs * BATCH / (ms / args.steps * 1e-3) / 1e12
+        kernels[k] = entry
+    whole_tflops = value / world * FLOP_PER_BOARD / 1e12
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "self-play inference step: default v4 CNN (kernels [23,3x7], channels "
+                               "[32,32,64,64,64,96,96,96]) bf16 forward + masked log-softmax + 1 Philox draw/board "
+                               "+ value",
+                   "global_batch": BATCH * world, "per_gpu_batch": BATCH, "parallelism": f"boards sharded x{world}",
+                   "l2": f"inputs rotate over {INPUT_BUFFERS} resident batches ({INPUT_BUFFERS * h2d / 1e6:.0f} MB "
+                         "> 126 MB L2); inter-layer activations are 0.2-0.6 GB each",
+                   "weights": f"PolicyValueNet default init, torch seed {WEIGHT_SEED}"},
+        "clocks": clocks,
+        "e2e": {"value": BATCH * world * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                "api": "PolicyValueNet.selfplay_step on pinned host fp32 planes"},
+        "gpu_launches": launches,
+        "roofline": roof,
+        "whole_step": {"tflops_per_gpu": whole_tflops, "frac_of_peak": whole_tflops / peak,
+                       "flop_per_board": FLOP_PER_BOARD},
+        "kernels": kernels,
+        "device_status": status,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = 20 if args.steps is None else args.steps
+        args.warmup = 3 if args.warmup is None else args.warmup
+        run_reference(args)
+    else:
+        args.steps = 300 if args.steps is None else args.steps
+        args.warmup = 10 if args.warmup is None else max(args.warmup, 3)   # never fewer than 3 warm-ups
+        run_engine(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -16,6 +16,8 @@ C6_PREC_BF16, C6_PREC_FP32 = 0, 1
 C6_X_F32, C6_X_BF16 = 0, 1
 C6_HEAD_POLICY, C6_HEAD_VALUE = 100, 101
 C6_FLAG_MASK_LOGITS, C6_FLAG_INVERSE_MAP = 1, 2
+C6_KIND_PACK, C6_KIND_STEM, C6_KIND_FINISH, C6_KIND_OTHER, C6_KIND_CONV0 = 0, 1, 2, 3, 8
+C6_KIND_COUNT = 8 + C6_MAX_LAYERS
 
 
 class C6Desc(C.Structure):
@@ -48,6 +50,8 @@ SIGNATURES = {
     "c6_transform_boards": (_i, [_vp, _i64, C.c_int32, _vp, C.c_int32, _vp, _vp]),
     "c6_network_input": (_i, [_vp, _vp, _vp, _i64, C.c_int32, _vp, _vp]),
     "c6_debug_layer_output": (_i, [_vp, _vp, _i, _i64, _vp, _i, _vp, _vp]),
+    "c6_profile_enable": (_i, [_vp, _i]),
+    "c6_profile_read": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(_i64), _i]),
     "c6_status": (_i, [_vp, C.POINTER(_i)]),
     "c6_launch_count": (_i64, [_vp]),
     "c6_device_bytes": (_i64, [_vp]),

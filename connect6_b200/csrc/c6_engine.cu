@@ -75,6 +75,11 @@ struct C6Engine {
   long long last_group_pos = -1;
   int* status_dev = nullptr;
   long long launches = 0;
+  // optional per-kernel timing: event pairs recorded around every launch
+  bool profiling = false;
+  struct ProfRec { int kind; cudaEvent_t a, b; };
+  std::vector<ProfRec> prof;
+  std::vector<cudaEvent_t> ev_pool;
   long long dev_bytes = 0;
   long long ws_bytes = 0;
   std::string err = "";
@@ -101,6 +106,33 @@ int fail(C6Engine* e, int code, const std::string& msg) {
       return fail((e), C6_ERR_CUDA, std::string("launch ") + name + ": " + cudaGetErrorString(_st)); \
     (e)->launches++;                                                                             \
   } while (0)
+
+cudaEvent_t prof_event(C6Engine* e) {
+  if (!e->ev_pool.empty()) {
+    cudaEvent_t ev = e->ev_pool.back();
+    e->ev_pool.pop_back();
+    return ev;
+  }
+  cudaEvent_t ev = nullptr;
+  cudaEventCreate(&ev);
+  return ev;
+}
+// Scope object: records an event pair on `st` around the launches made while it lives.
+struct ProfScope {
+  C6Engine* e;
+  cudaStream_t st;
+  cudaEvent_t b = nullptr;
+  ProfScope(C6Engine* e_, int kind, cudaStream_t st_) : e(e_), st(st_) {
+    if (!e->profiling) return;
+    cudaEvent_t a = prof_event(e);
+    b = prof_event(e);
+    cudaEventRecord(a, st);
+    e->prof.push_back({kind, a, b});
+  }
+  ~ProfScope() {
+    if (b) cudaEventRecord(b, st);
+  }
+};
 
 template <typename T>
 int dev_alloc(C6Engine* e, T** p, size_t count, bool zero, long long* tally) {
@@ -229,7 +261,10 @@ int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long
   f.value_out = a.value;
   f.action_out = a.action;
   f.logprob_out = a.logprob;
-  finish_kernel<<<dim3((unsigned)nb, (unsigned)e->G), kFinishThreads, 0, st>>>(f);
+  {
+    ProfScope _ps(e, C6_KIND_FINISH, st);
+    finish_kernel<<<dim3((unsigned)nb, (unsigned)e->G), kFinishThreads, 0, st>>>(f);
+  }
   C6_LAUNCHED(e, "finish_kernel");
   return C6_OK;
 }
@@ -246,6 +281,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
 
   {  // input planes
     const long long total = (long long)e->kc0 * nb;
+    ProfScope _ps(e, C6_KIND_PACK, st);
     pack_stem_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
         a.x, a.x_bf16, a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->n, nb, a.T, t0);
     C6_LAUNCHED(e, "pack_stem_input_kernel");
@@ -279,6 +315,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.tmem_cols = e->stem_tmem_cols;
     const long long items = (long long)e->G * p.mtiles * p.ntiles;
     const int grid = (int)std::min<long long>(e->sms, items);
+    ProfScope _ps(e, C6_KIND_STEM, st);
     stem_tc_kernel<<<grid, kStemThreads, e->stem_smem, st>>>(p);
     C6_LAUNCHED(e, "stem_tc_kernel");
   }
@@ -312,7 +349,10 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.nstages = lp.nstages;
     p.acc_stride = lp.acc_stride;
     p.tmem_cols = lp.tmem_cols;
-    conv_tc_kernel<<<e->G * p.ctas_per_group, kConvThreads, lp.smem, st>>>(p);
+    {
+      ProfScope _ps(e, C6_KIND_CONV0 + l, st);
+      conv_tc_kernel<<<e->G * p.ctas_per_group, kConvThreads, lp.smem, st>>>(p);
+    }
     C6_LAUNCHED(e, "conv_tc_kernel");
     if (!p.head) cur ^= 1;
   }
@@ -332,6 +372,7 @@ int run_pass_fp32(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
   const long long boards = (long long)e->G * nb;
   {
     const long long total = (long long)nb * 3 * e->cells;
+    ProfScope _ps(e, C6_KIND_PACK, st);
     view_input_f32_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
         a.x, a.x_bf16, a.orient, e->f32x, e->n, nb, a.T, t0);
     C6_LAUNCHED(e, "view_input_f32_kernel");
@@ -342,8 +383,11 @@ int run_pass_fp32(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
   for (int l = 0; l <= last; ++l) {
     const LayerPlan& lp = e->lp[l];
     const dim3 grid((unsigned)boards, (unsigned)((lp.cout + kFp32CoT - 1) / kFp32CoT));
-    conv_fp32_kernel<<<grid, kFp32Threads, fp32_smem(e, lp), st>>>(in, e->wraw[l], e->bias[l], e->f32buf[cur],
-                                                                    lp.cin, lp.cout, lp.k, e->n, nb, fp32_cit(lp));
+    {
+      ProfScope _ps(e, l == 0 ? C6_KIND_STEM : C6_KIND_CONV0 + l, st);
+      conv_fp32_kernel<<<grid, kFp32Threads, fp32_smem(e, lp), st>>>(in, e->wraw[l], e->bias[l], e->f32buf[cur],
+                                                                      lp.cin, lp.cout, lp.k, e->n, nb, fp32_cit(lp));
+    }
     C6_LAUNCHED(e, "conv_fp32_kernel");
     in = e->f32buf[cur];
     cur ^= 1;
@@ -354,8 +398,11 @@ int run_pass_fp32(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
                                cudaMemcpyDeviceToDevice, st));
     return C6_OK;
   }
-  head_fp32_kernel<<<(unsigned)boards, kFp32Threads, 0, st>>>(in, e->head_wp, e->head_wv, e->logit_raw, e->vmap,
-                                                               e->lp[e->L - 1].cout, e->n, nb);
+  {
+    ProfScope _ps(e, C6_KIND_OTHER, st);
+    head_fp32_kernel<<<(unsigned)boards, kFp32Threads, 0, st>>>(in, e->head_wp, e->head_wv, e->logit_raw, e->vmap,
+                                                                 e->lp[e->L - 1].cout, e->n, nb);
+  }
   C6_LAUNCHED(e, "head_fp32_kernel");
   return launch_finish(e, a, t0, nb, (long long)nb * e->cells, e->cells, e->n, st);
 }
@@ -407,6 +454,8 @@ int c6_destroy(C6Engine* e) {
   cudaFree(e->pol_bias);
   cudaFree(e->val_bias);
   cudaFree(e->status_dev);
+  for (auto& r : e->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  for (auto ev : e->ev_pool) cudaEventDestroy(ev);
   delete e;
   return C6_OK;
 }
@@ -745,6 +794,29 @@ int c6_status(C6Engine* e, int* device_status) {
     snprintf(buf, sizeof(buf), "device status word 0x%x: a bounded wait inside a kernel ran out", *device_status);
     return fail(e, C6_ERR_DEVICE, buf);
   }
+  return C6_OK;
+}
+
+int c6_profile_enable(C6Engine* e, int on) {
+  if (!e) return C6_ERR_ARG;
+  e->profiling = on != 0;
+  return C6_OK;
+}
+
+int c6_profile_read(C6Engine* e, float* ms_per_kind, int64_t* launches_per_kind, int n_kinds) {
+  if (!e || !ms_per_kind || !launches_per_kind || n_kinds < C6_KIND_COUNT) return C6_ERR_ARG;
+  C6_CUDA(e, cudaSetDevice(e->device));
+  for (int i = 0; i < n_kinds; ++i) { ms_per_kind[i] = 0.f; launches_per_kind[i] = 0; }
+  for (auto& r : e->prof) {
+    C6_CUDA(e, cudaEventSynchronize(r.b));
+    float ms = 0.f;
+    C6_CUDA(e, cudaEventElapsedTime(&ms, r.a, r.b));
+    ms_per_kind[r.kind] += ms;
+    launches_per_kind[r.kind] += 1;
+    e->ev_pool.push_back(r.a);
+    e->ev_pool.push_back(r.b);
+  }
+  e->prof.clear();
   return C6_OK;
 }
 

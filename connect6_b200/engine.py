@@ -188,6 +188,23 @@ class Engine:
                     "c6_debug_layer_output")
         return out
 
+    # -- per-kernel timing ------------------------------------------------------------------
+    def profile(self, on: bool) -> None:
+        L.check(self._lib.c6_profile_enable(self._h, 1 if on else 0), self._h, "c6_profile_enable")
+
+    def profile_read(self) -> dict[str, tuple[float, int]]:
+        """{kernel kind: (total ms, launches)} since the last read; waits for the recorded events."""
+        ms = (C.c_float * L.C6_KIND_COUNT)()
+        cnt = (C.c_int64 * L.C6_KIND_COUNT)()
+        L.check(self._lib.c6_profile_read(self._h, ms, cnt, L.C6_KIND_COUNT), self._h, "c6_profile_read")
+        names = {L.C6_KIND_PACK: "pack_input", L.C6_KIND_STEM: "stem", L.C6_KIND_FINISH: "finish",
+                 L.C6_KIND_OTHER: "head_maps"}
+        out = {}
+        for k in range(L.C6_KIND_COUNT):
+            if cnt[k]:
+                out[names.get(k, f"conv{k - L.C6_KIND_CONV0}")] = (float(ms[k]), int(cnt[k]))
+        return out
+
     # -- introspection --------------------------------------------------------------------------
     def status(self) -> int:
         """Device status word; synchronises the engine's device first. Raises if non-zero."""

@@ -145,6 +145,22 @@ int c6_network_input(const int8_t* boards, const int8_t* current_player, const i
 int c6_debug_layer_output(C6Engine* eng, const void* x, int x_dtype, int64_t T,
                           const uint8_t* orient, int layer, float* out_nchw, void* stream);
 
+/* Per-kernel timing (no reference counterpart; the reference only has wall-clock phase timers,
+ * connect6/train.py:586-1191).  While enabled, every forward-path launch is bracketed by a CUDA
+ * event pair on the caller's stream.  c6_profile_read waits for the recorded events, adds the
+ * elapsed milliseconds and launch counts per kind into the caller's HOST arrays (length
+ * n_kinds >= C6_KIND_COUNT) and clears the record. */
+enum {
+  C6_KIND_PACK = 0,   /* input packing / view copy                      */
+  C6_KIND_STEM = 1,   /* first backbone layer                           */
+  C6_KIND_FINISH = 2, /* mask + log-softmax + draw + value              */
+  C6_KIND_OTHER = 3,  /* fp32 head maps                                 */
+  C6_KIND_CONV0 = 8,  /* backbone layer l >= 1 is kind C6_KIND_CONV0+l  */
+  C6_KIND_COUNT = 8 + C6_MAX_LAYERS
+};
+int c6_profile_enable(C6Engine* eng, int on);
+int c6_profile_read(C6Engine* eng, float* ms_per_kind, int64_t* launches_per_kind, int n_kinds);
+
 /* Reads the device status word (host int). Non-zero means a bounded wait inside a kernel ran
  * out; the kernels then skip their work instead of hanging. The caller must have synchronised
  * the stream it used. */

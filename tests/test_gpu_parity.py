@@ -1,0 +1,276 @@
+"""Parity of the CUDA engine with the oracle (GPU tests; every call goes through the C ABI).
+
+Tolerances (from the task's contract): fp32 mode 1e-3 on logits and values; bf16 mode
+max-abs-error 3e-2 on logits and values and masked-argmax agreement with the fp32 oracle.  At
+default initialisation the logits only span a few 1e-3, which makes the 3e-2 bound vacuous, so
+the bf16 tests additionally bound the error RELATIVE to the spread of the logits.  Masks and D4
+index maps are integer work and must be bit-exact.
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import c6_oracle as O
+import torch_port as TP
+from conftest import ROOT, load_golden, params_from
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-3
+BF16_ABS_TOL = 3e-2
+BF16_REL_TOL = 0.12          # max |dlogit| / std(logits): bf16 rounding through 8 layers
+REPORT = ROOT / "gpurun_out" / "parity_report.json"
+
+
+def _report(key: str, value) -> None:
+    try:
+        REPORT.parent.mkdir(exist_ok=True)
+        data = json.loads(REPORT.read_text()) if REPORT.exists() else {}
+        data[key] = value
+        REPORT.write_text(json.dumps(data, indent=1, sort_keys=True))
+    except Exception:
+        pass
+
+
+def _model_from(params: dict, board: int, kernels, channels, precision: str, dev):
+    from connect6_b200.model import PolicyValueNet
+    m = PolicyValueNet(board, list(kernels), list(channels), engine_precision=precision)
+    m.load_state_dict({k: torch.from_numpy(np.asarray(v)) for k, v in params.items()})
+    return m.to(dev).eval()
+
+
+def _default_model(precision: str, dev, seed: int = 42):
+    from connect6_b200.model import PolicyValueNet
+    torch.manual_seed(seed)
+    m = PolicyValueNet(19, engine_precision=precision).eval()
+    params = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    return m.to(dev), params
+
+
+def _oracle64(x: torch.Tensor, params: dict):
+    l, v = TP.policy_value_forward(x.double(), {k: p.double() for k, p in params.items()})
+    return l.numpy(), v.numpy()
+
+
+# ------------------------------------------------------------------------------------------------
+# golden fixtures through the engine
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_small_net_golden(cuda_device, precision):
+    """Non-default architecture: 7x7 board, 9x9 stem, channels padded up to the MMA granule."""
+    g = load_golden("small_net.npz")
+    m = _model_from(params_from(g), 7, g["kernels"], g["channels"], precision, cuda_device)
+    with torch.inference_mode():
+        logits, value = m(torch.from_numpy(g["x"]).to(cuda_device))
+    dl = np.abs(logits.cpu().numpy() - g["logits"]).max()
+    dv = np.abs(value.cpu().numpy() - g["value"]).max()
+    if precision == "fp32":
+        assert dl < 1e-4 and dv < 1e-5
+    else:
+        assert dl < BF16_ABS_TOL and dl < BF16_REL_TOL * g["logits"].std() * 3 and dv < BF16_ABS_TOL
+    assert m.engine_for(cuda_device).status() == 0
+
+
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_default_net_golden(cuda_device, precision):
+    from connect6_b200.boards import generate_planes
+    g = load_golden("default_net_seed42.npz")
+    if str(g["torch_version"]) != torch.__version__:
+        pytest.skip("fixture generated with another torch version")
+    m, _ = _default_model(precision, cuda_device)
+    x = torch.from_numpy(generate_planes(0, 6)).to(cuda_device)
+    with torch.inference_mode():
+        logits, value = m(x)
+    dl = np.abs(logits.cpu().numpy() - g["logits"]).max()
+    dv = np.abs(value.cpu().numpy() - g["value"]).max()
+    if precision == "fp32":
+        assert dl < 1e-5 and dv < 1e-5
+    else:
+        assert dl < BF16_ABS_TOL and dl < BF16_REL_TOL * g["logits"].std() and dv < BF16_ABS_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_grouped_golden(cuda_device, dtype):
+    """The reference's grouped == per-model test configuration (tests/test_training_features.py:120-151)."""
+    from connect6_b200.history import HistoricalCheckpoint, HistoricalPolicyEnsemble
+    g = load_golden("grouped_small.npz")
+    cfg = {"architecture_version": 4, "kernels": [3, 3, 3], "channels": [8, 8, 16]}
+    cps = [HistoricalCheckpoint(path=Path(f"model_update_{i + 1:08d}.pt"), update=i + 1,
+                                model_state={k: torch.from_numpy(v) for k, v in params_from(g, f"w{i}::").items()},
+                                model_config=cfg, game_config={"board_size": 5, "win_length": 3}) for i in range(3)]
+    ens = HistoricalPolicyEnsemble(cps, cuda_device, dtype=dtype)
+    x = torch.from_numpy(g["x"]).to(cuda_device)
+    logits = ens.forward_grouped(x)
+    assert logits.shape == (3, 4, 25) and logits.dtype == dtype
+    _, value = ens.forward_grouped_with_value(x)
+    dl = np.abs(logits.float().cpu().numpy() - g["logits"]).max()
+    dv = np.abs(value.cpu().numpy() - g["value"]).max()
+    if dtype == torch.float32:
+        assert dl < 1e-5 and dv < 1e-5          # the reference test's own tolerance
+    else:
+        assert dl < BF16_ABS_TOL and dv < BF16_ABS_TOL
+    with pytest.raises(ValueError):
+        ens.forward_grouped(x[:2])
+    with pytest.raises(ValueError):
+        ens.forward_grouped(x[0])
+
+
+# ------------------------------------------------------------------------------------------------
+# layer-by-layer and whole-network parity at larger sizes
+# ------------------------------------------------------------------------------------------------
+def test_bf16_layers_against_oracle(cuda_device):
+    from connect6_b200.boards import generate_planes
+    m, params = _default_model("bf16", cuda_device)
+    x = torch.from_numpy(generate_planes(1000, 40))
+    eng = m.engine_for(cuda_device)
+    f = x.double()
+    worst = {}
+    for i in range(8):
+        w, b = params[f"convs.{i}.weight"].double(), params[f"convs.{i}.bias"].double()
+        f = torch.nn.functional.silu(torch.nn.functional.conv2d(f, w, b, padding=w.shape[-1] // 2))
+        got = eng.layer_output(x.to(cuda_device), i).cpu().double()
+        err = (got - f).abs().max().item() / f.abs().max().item()
+        worst[f"layer{i}"] = err
+        assert err < 2e-2, f"layer {i}: relative error {err}"
+    _report("bf16_layer_rel_err", worst)
+    assert eng.status() == 0
+
+
+def test_fp32_mode_against_oracle(cuda_device):
+    from connect6_b200.boards import generate_planes
+    m, params = _default_model("fp32", cuda_device)
+    x = torch.from_numpy(generate_planes(5000, 96))
+    rl, rv = _oracle64(x, params)
+    with torch.inference_mode():
+        logits, value = m(x.to(cuda_device))
+    dl = np.abs(logits.cpu().numpy() - rl).max()
+    dv = np.abs(value.cpu().numpy() - rv).max()
+    _report("fp32_mode", {"max_abs_dlogit": float(dl), "max_abs_dvalue": float(dv)})
+    assert dl < FP32_TOL and dv < FP32_TOL and dl < 1e-5
+
+
+@pytest.mark.parametrize("seed", [42, 0])
+def test_bf16_forward_against_oracle_2048_boards(cuda_device, seed):
+    """bf16 mode vs the fp32/fp64 oracle on 2048 generated boards: absolute and relative error,
+    and agreement of the masked argmax move."""
+    from connect6_b200.boards import generate_planes
+    m, params = _default_model("bf16", cuda_device, seed)
+    B = 2048
+    x = torch.from_numpy(generate_planes(20000, B))
+    rl, rv = _oracle64(x, params)
+    with torch.inference_mode():
+        logits, value = m.forward_masked(x.to(cuda_device))
+    logits, value = logits.cpu().numpy(), value.cpu().numpy()
+    legal = O.legal_from_planes(x.numpy())
+    assert np.array_equal(logits == O.FP32_MIN, ~legal)                       # mask bit-exact
+    dl = np.abs(logits - rl)[legal].max()
+    dv = np.abs(value - rv).max()
+    std = rl.std()
+    ref_masked = np.where(legal, rl, -np.inf)
+    agree = (ref_masked.argmax(1) == logits.argmax(1))
+    srt = np.sort(ref_masked, axis=1)
+    gap = srt[:, -1] - srt[:, -2]
+    clear = gap > 2 * dl                                                       # boards whose best move is not within the noise
+    _report(f"bf16_vs_fp32_seed{seed}", {
+        "boards": B, "max_abs_dlogit": float(dl), "logit_std": float(std), "rel": float(dl / std),
+        "max_abs_dvalue": float(dv), "masked_argmax_agreement": float(agree.mean()),
+        "agreement_where_gap_gt_2x_noise": float(agree[clear].mean()), "boards_with_clear_gap": int(clear.sum()),
+        "median_top2_gap": float(np.median(gap))})
+    assert dl < BF16_ABS_TOL and dv < BF16_ABS_TOL
+    assert dl < BF16_REL_TOL * std
+    assert agree[clear].mean() == 1.0
+    # At default init the median top-2 gap is ~2e-4 against ~1e-4 of bf16 noise, so a few percent of
+    # near-tied boards flip; the reference's own bf16 autocast agrees on ~98.2 %.
+    assert agree.mean() >= 0.975
+
+
+def test_chunked_passes_equal_single_pass(cuda_device):
+    """A batch cut into several internal passes gives bit-identical results."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    m, params = _default_model("bf16", cuda_device)
+    x = torch.from_numpy(generate_planes(300, 150)).to(cuda_device)
+    whole = m.engine_for(cuda_device).forward(x)
+    small = Engine(cuda_device, 19, m.kernels, m.channels, 1, "bf16", max_chunk=64)
+    small.load_state_dict(params)
+    parts = small.forward(x)
+    assert torch.equal(whole[0], parts[0]) and torch.equal(whole[1], parts[1])
+    # shrinking and growing batches reuse the same workspace without stale data
+    for b in (1, 2, 3, 64, 65, 7):
+        l, v = small.forward(x[:b])
+        assert torch.equal(l, whole[0][:b]) and torch.equal(v, whole[1][:b])
+    assert small.status() == 0
+
+
+def test_empty_and_bad_inputs(cuda_device):
+    m, _ = _default_model("bf16", cuda_device)
+    with torch.inference_mode():
+        logits, value = m(torch.zeros(0, 3, 19, 19, device=cuda_device))
+    assert logits.shape == (0, 361) and value.shape == (0,)
+    for bad in (torch.zeros(2, 4, 19, 19), torch.zeros(3, 19, 19), torch.zeros(2, 3, 19, 18)):
+        with pytest.raises(ValueError):
+            m(bad.to(cuda_device))
+    with pytest.raises(RuntimeError):
+        with torch.inference_mode():
+            m(torch.zeros(1, 3, 19, 19))                                    # CPU tensor: no CPU path
+    with torch.inference_mode():
+        l1, v1 = m(torch.zeros(3, 3, 19, 19, device=cuda_device))            # reference test_model_shapes
+    assert l1.shape == (3, 361) and v1.shape == (3,) and bool((v1.abs() <= 1).all())
+
+
+def test_weights_repacked_after_in_place_update(cuda_device):
+    """An optimizer step (in-place parameter update) must reach the engine on the next call."""
+    from connect6_b200.boards import generate_planes
+    m, _ = _default_model("bf16", cuda_device)
+    x = torch.from_numpy(generate_planes(0, 4)).to(cuda_device)
+    with torch.inference_mode():
+        before, _ = m(x)
+    with torch.no_grad():
+        m.policy_output.bias.add_(0.5)
+    with torch.inference_mode():
+        after, _ = m(x)
+    assert torch.allclose(after, before + 0.5, atol=1e-6)
+    # autograd path still runs on the torch modules and agrees with the engine
+    m.train()
+    lt, vt = m(x)
+    assert lt.requires_grad and (lt.detach() - after).abs().max().item() < 3e-2
+
+
+# ------------------------------------------------------------------------------------------------
+# D4 orientation fused into the forward
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_per_board_orientation_and_inverse_map(cuda_device, precision):
+    from connect6_b200.boards import generate_planes
+    m, params = _default_model(precision, cuda_device)
+    B = 64
+    x = torch.from_numpy(generate_planes(7000, B))
+    orient = (np.arange(B) % 8).astype(np.uint8)
+    # oracle: transform the planes per board, forward, map the logits back
+    xv = x.numpy().copy()
+    for b in range(B):
+        xv[b] = O.transform_boards(x.numpy()[b], *O.symmetry_for_phase(int(orient[b])))
+    lv, vv = _oracle64(torch.from_numpy(xv), params)
+    table = O.d4_forward_table(19)
+    canon = np.take_along_axis(lv, table[orient].astype(np.int64), axis=1)
+    od = torch.from_numpy(orient).to(cuda_device)
+    tol = 1e-5 if precision == "fp32" else BF16_REL_TOL * lv.std()
+    with torch.inference_mode():
+        l_view, v_view = m.forward_masked(x.to(cuda_device), od, inverse_map=False)
+        l_canon, v_canon = m.forward_masked(x.to(cuda_device), od, inverse_map=True)
+    legal = O.legal_from_planes(x.numpy())
+    legal_view = O.legal_from_planes(xv)
+    l_view, l_canon = l_view.cpu().numpy(), l_canon.cpu().numpy()
+    assert np.array_equal(l_canon == O.FP32_MIN, ~legal)                       # bit-exact masks
+    assert np.array_equal(l_view == O.FP32_MIN, ~legal_view)
+    assert np.abs(l_view - lv)[legal_view].max() < tol
+    assert np.abs(l_canon - canon)[legal].max() < tol
+    # the inverse map is a pure permutation of the view logits: bit-exact
+    assert np.array_equal(np.take_along_axis(l_view, table[orient].astype(np.int64), axis=1), l_canon)
+    assert np.abs(v_view.cpu().numpy() - vv).max() < max(tol, 1e-5)
+    assert torch.equal(v_view, v_canon)

@@ -309,9 +309,13 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
   }
   if (threadIdx.x == 0) {
     if (p.action_out) p.action_out[ob] = pick;
-    // log-prob = z[a] - logsumexp(z), with z - zmax kept exact instead of log(exp(.))
-    const float zrel = none_legal ? 0.f : (s_z[pick] * inv_t - zmax);
-    if (p.logprob_out) p.logprob_out[ob] = zrel - logf(total);
+    // log-prob = z[a] - logsumexp(z) with logsumexp = max + log(sum exp(z - max)), as torch
+    // computes it.  With no legal cell z is the fill everywhere: log(A) is absorbed by the fill
+    // and the result is 0, which is what the reference's Categorical returns for that row.
+    const float fill_z = fmaxf(kFp32Min * inv_t, -3.4028234663852886e38f);
+    const float zpick = none_legal ? fill_z : s_z[pick] * inv_t;
+    const float lse = (none_legal ? fill_z : zmax) + logf(total);
+    if (p.logprob_out) p.logprob_out[ob] = zpick - lse;
   }
 }
 

@@ -17,7 +17,7 @@
 // resident in shared memory when they fit; otherwise the block of one q travels with the
 // activation stage.
 //
-// CTA = 192 threads: warp 0 issues bulk copies, warp 1 owns TMEM and issues MMAs, warps 2-5
+// CTA = 320 threads: warp 0 issues bulk copies, warp 1 owns TMEM and issues MMAs, warps 2-9
 // drain the accumulator (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores).
 // Two TMEM accumulators let the epilogue of tile i overlap the MMAs of tile i+1.  Every wait
 // is bounded: when one runs out the CTA records a status bit, stops, frees TMEM and returns.
@@ -38,6 +38,7 @@ struct ConvTcParams {
   float* logit_raw;      // [G * tiles_per_group * 128] (head only)
   float* vmap;           // same shape (head only)
   int* status;
+  long long* wait_cycles;  // nullable [4]: CTA 0's clocks spent waiting {producer: empty, MMA: full, MMA: acc empty, epilogue: acc full}
   long long plane_rows;
   int front;             // plane row of position 0
   int halo_rows;         // rows staged before and after the 128 tile rows (multiple of 8)
@@ -55,24 +56,29 @@ struct ConvTcParams {
   int head;
 };
 
-constexpr int kConvThreads = 192;
-constexpr int kConvSmemHeader = 3840;  // barriers, TMEM slot, abort flag, bias and head vectors
+constexpr int kConvThreads = 320;  // producer warp, MMA warp, eight epilogue warps
+constexpr int kConvSmemHeader = 5888;  // barriers, TMEM slot, abort flag, bias and head vectors, head partials
 constexpr int kMaxStages = 12;
 
 __host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 * halo_rows; }
 
+// KS = filter side known at compile time (1, 3, 5) so that the tap loop unrolls and the per-tap
+// descriptor offsets live in registers; KS = 0 is the generic run-time loop.
+template <int KS>
 __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte aligned view of dynamic shared memory
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-  // barrier slots: [0,12) full, [12,24) empty, 24 weights, 25-26 acc full, 27-28 acc empty, 29 drain
+  // barrier slots: [0,12) full, [12,24) empty, 24 weights, 25-26 acc full, 27-28 acc empty, 29 drain,
+  // 30-31 head partials ready
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 516);
   volatile int* never_flag = reinterpret_cast<volatile int*>(smem + 520);  // stays 0
   float* s_bias = reinterpret_cast<float*>(smem + 640);
   float* s_wp = s_bias + 256;
   float* s_wv = s_wp + 256;
+  float* s_part = s_wv + 256;  // [2 accumulators][2 heads][128] partial sums of each quadrant's second warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int taps = p.kside * p.kside;
@@ -99,6 +105,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   auto bar_tfull = [&](int a) { return bar0 + 8u * (25 + a); };
   auto bar_tempty = [&](int a) { return bar0 + 8u * (27 + a); };
   const uint32_t bar_drain = bar0 + 8u * 29;
+  auto bar_part = [&](int a) { return bar0 + 8u * (30 + a); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
@@ -108,7 +115,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     tc::mbar_init(bar_w, 1);
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(bar_tfull(a), 1);
-      tc::mbar_init(bar_tempty(a), 4);
+      tc::mbar_init(bar_tempty(a), 8);
+      tc::mbar_init(bar_part(a), 4);
     }
     tc::mbar_init(bar_drain, 1);
     *abort_flag = 0;
@@ -120,8 +128,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     tc::tmem_relinquish();
   }
   if (warp >= 2) {
-    for (int i = threadIdx.x - 64; i < p.n; i += 128) {
-      s_bias[i] = p.bias[(size_t)group * p.n + i];
+    for (int i = threadIdx.x - 64; i < p.n; i += 256) {
+      s_bias[i] = 0.5f * p.bias[(size_t)group * p.n + i];  // the epilogue works on h = x/2
       if (p.head) {
         s_wp[i] = p.head_wp[(size_t)group * p.n + i];
         s_wv[i] = p.head_wv[(size_t)group * p.n + i];
@@ -146,13 +154,17 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         tc::bulk_g2s(tc::smem_u32(s_w + off), reinterpret_cast<const uint8_t*>(w_group) + off, len, bar_w);
       }
     }
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
+    long long waited = 0;
+    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     for (int tile = t_begin; tile < t_end && ok; ++tile) {
       const long long row0 = group_row0 + (long long)tile * 128 - p.halo_rows;
-      for (int q = 0; q < nq; ++q, ++it) {
-        const int s = it % p.nstages;
-        const uint32_t ph = (it / p.nstages) & 1u;
-        if (!tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag)) {
+      for (int q = 0; q < nq; ++q) {
+        const long long w0 = timing ? clock64() : 0;
+        const bool got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag);
+        if (timing) waited += clock64() - w0;
+        if (!got) {
           atomicOr(p.status, kStatWaitEmpty);
           *abort_flag = 1;
           ok = false;
@@ -166,80 +178,129 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         if (!p.resident)
           tc::bulk_g2s(dst + a_bytes, reinterpret_cast<const uint8_t*>(w_group) + (size_t)q * wq_bytes,
                        wq_bytes, bar_full(s));
+        if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
     }
+    if (timing) p.wait_cycles[0] += waited;
     if (!ok) {
       // let copies already in flight land before the CTA's shared memory is released
-      for (int s = 0; s < p.nstages; ++s) {
+      for (int st = 0; st < p.nstages; ++st) {
         const long long t0 = clock64();
         while (clock64() - t0 < 200000) {
-          if (tc::mbar_try_wait(bar_full(s), 0) || tc::mbar_try_wait(bar_full(s), 1)) break;
+          if (tc::mbar_try_wait(bar_full(st), 0) || tc::mbar_try_wait(bar_full(st), 1)) break;
         }
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
+    // The whole warp walks the loop in lock step (warp-uniform control flow keeps descriptors and
+    // barrier addresses in uniform registers); one elected lane issues the MMAs and commits.
     const uint32_t idesc = tc::make_idesc_bf16(128, p.n);
     const int kh = p.kside >> 1;
+    const uint32_t desc_hi = (uint32_t)(tc::make_desc(0, 0, 128u) >> 32);   // SBO = 128 B, version 1
+    const uint32_t a_lbo_field = ((uint32_t)(rows * 16) >> 4) << 16;          // LBO = plane pitch of a stage
+    const uint32_t b_lbo_field = ((uint32_t)(p.n * 16) >> 4) << 16;           // LBO = Cout rows
+    const uint32_t b_step = 2u * (uint32_t)p.n;                                // rows between taps
+    const uint32_t w_lo = (tc::smem_u32(s_w) >> 4) | b_lbo_field;
+    const uint32_t wq_rows = wq_bytes >> 4;
+    const uint32_t stage0_lo = (tc::smem_u32(s_stage) >> 4) | a_lbo_field;
+    const uint32_t stage_rows = stage_bytes >> 4;
+    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     bool ok = true;
     if (p.resident && !tc::mbar_wait(bar_w, 0, abort_flag)) {
-      atomicOr(p.status, kStatWaitWeights);
+      if (lane == 0) atomicOr(p.status, kStatWaitWeights);
       *abort_flag = 1;
       ok = false;
     }
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
     int tcount = 0;
+    long long wait_full = 0, wait_acc = 0;
     for (int tile = t_begin; tile < t_end && ok; ++tile, ++tcount) {
       const int acc = tcount & 1;
-      if (!tc::mbar_wait(bar_tempty(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag)) {
-        atomicOr(p.status, kStatWaitTmemEmpty);
+      const long long w0 = timing ? clock64() : 0;
+      const bool got_acc = tc::mbar_wait(bar_tempty(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag);
+      if (timing) wait_acc += clock64() - w0;
+      if (!got_acc) {
+        if (lane == 0) atomicOr(p.status, kStatWaitTmemEmpty);
         *abort_flag = 1;
         ok = false;
         break;
       }
       tc::fence_after_sync();
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
-      for (int q = 0; q < nq; ++q, ++it) {
-        const int s = it % p.nstages;
-        const uint32_t ph = (it / p.nstages) & 1u;
-        if (!tc::mbar_wait(bar_full(s), ph, abort_flag)) {
-          atomicOr(p.status, kStatWaitFull);
+      for (int q = 0; q < nq; ++q) {
+        const long long w1 = timing ? clock64() : 0;
+        const bool got = tc::mbar_wait(bar_full(s), ph, abort_flag);
+        if (timing) wait_full += clock64() - w1;
+        if (!got) {
+          if (lane == 0) atomicOr(p.status, kStatWaitFull);
           *abort_flag = 1;
           ok = false;
           break;
         }
         tc::fence_after_sync();
-        const uint32_t a0 = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
-        const uint32_t b0 = p.resident ? tc::smem_u32(s_w) + (uint32_t)q * wq_bytes : a0 + a_bytes;
-        int tap = 0;
-        for (int dy = -kh; dy <= kh; ++dy) {
-          for (int dx = -kh; dx <= kh; ++dx, ++tap) {
-            const int shift = p.halo_rows + dy * p.wp + dx;  // >= 0 by construction
-            const uint64_t adesc = tc::make_desc(a0 + (uint32_t)shift * 16u, rows * 16u, 128u);
-            const uint64_t bdesc = tc::make_desc(b0 + (uint32_t)tap * 2u * p.n * 16u, p.n * 16u, 128u);
-            tc::mma_bf16(d_tmem, adesc, bdesc, idesc, (q | tap) != 0 ? 1u : 0u);
+        // Descriptors of one stage differ only in the start-address field (16-byte units, low word),
+        // so a tap costs two integer adds: the issue loop must stay far below the ~50 clocks an MMA
+        // of this shape takes, or the tensor pipe starves.
+        const uint32_t a_lo = stage0_lo + (uint32_t)s * stage_rows;
+        const uint32_t b_lo = p.resident ? w_lo + (uint32_t)q * wq_rows : a_lo - a_lbo_field + (a_bytes >> 4) + b_lbo_field;
+        if (tc::elect_one()) {
+          if (KS > 0) {
+#pragma unroll
+            for (int tap = 0; tap < KS * KS; ++tap) {
+              const int dy = tap / (KS > 0 ? KS : 1) - KS / 2, dx = tap % (KS > 0 ? KS : 1) - KS / 2;
+              const uint32_t shift = (uint32_t)(p.halo_rows + dy * p.wp + dx);
+              tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + shift),
+                           ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
+                           (q | tap) != 0 ? 1u : 0u);
+            }
+          } else {
+            int tap = 0;
+            for (int dy = -kh; dy <= kh; ++dy)
+              for (int dx = -kh; dx <= kh; ++dx, ++tap)
+                tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + (uint32_t)(p.halo_rows + dy * p.wp + dx)),
+                             ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
+                             (q | tap) != 0 ? 1u : 0u);
           }
+          tc::mma_commit(bar_empty(s));  // stage reusable once these MMAs have read it
+          if (q == nq - 1) tc::mma_commit(bar_tfull(acc));
         }
-        tc::mma_commit(bar_empty(s));  // stage reusable once these MMAs have read it
+        __syncwarp();
+        if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
-      if (ok) tc::mma_commit(bar_tfull(acc));
+    }
+    if (timing && lane == 0) {
+      p.wait_cycles[1] += wait_full;
+      p.wait_cycles[2] += wait_acc;
     }
     // every MMA issued must have retired before TMEM is freed
-    tc::mma_commit(bar_drain);
-    if (!tc::mbar_wait(bar_drain, 0, never_flag)) {
-      atomicOr(p.status, kStatWaitDrain);
-      *abort_flag = 1;
+    if (lane == 0) {
+      tc::mma_commit(bar_drain);
+      if (!tc::mbar_wait(bar_drain, 0, never_flag)) {
+        atomicOr(p.status, kStatWaitDrain);
+        *abort_flag = 1;
+      }
     }
+    __syncwarp();
   } else if (warp >= 2) {
     // ------------------------------ epilogue ------------------------------
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    // Eight warps: warp w may read TMEM lanes 32*(w%4)..+31 only, so two warps share each lane
+    // quadrant and split its columns in 16-channel units (unit u goes to the warp with half == u%2).
+    // Per element: h = 0.5*acc + 0.5*bias (one FMA), y = h + h*tanh(h) (one MUFU, one FMA).
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
-    const int nchunk = p.n >> 5;
+    const int nunits = p.n >> 4;
     bool ok = true;
     int tcount = 0;
+    long long wait_tfull = 0;
     for (int tile = t_begin; tile < t_end && ok; ++tile, ++tcount) {
       const int acc = tcount & 1;
-      if (!tc::mbar_wait(bar_tfull(acc), (tcount >> 1) & 1u, abort_flag)) {
+      const long long w0 = clock64();
+      const bool got = tc::mbar_wait(bar_tfull(acc), (tcount >> 1) & 1u, abort_flag);
+      wait_tfull += clock64() - w0;
+      if (!got) {
         if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
         *abort_flag = 1;
         ok = false;
@@ -254,43 +315,73 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       uint4* out_row = p.out + group_row0 + pos;
       float pol = 0.f, val = 0.f;
-      for (int ch = 0; ch < nchunk; ++ch) {
-        uint32_t v[32];
-        tc::tmem_ld32(taddr + (uint32_t)(ch * 32), v);
+      for (int u = half; u < nunits; u += 2) {
+        uint32_t v[16];
+        tc::tmem_ld16(taddr + (uint32_t)(u * 16), v);
         tc::tmem_wait_ld();
-        float y[32];
+        float y[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float x = __uint_as_float(v[j]) + s_bias[ch * 32 + j];
-          y[j] = valid ? silu_fast(x) : 0.f;
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 hb = *reinterpret_cast<const float4*>(s_bias + u * 16 + j4 * 4);  // 0.5 * bias
+          y[j4 * 4 + 0] = silu_from_half(fmaf(__uint_as_float(v[j4 * 4 + 0]), 0.5f, hb.x));
+          y[j4 * 4 + 1] = silu_from_half(fmaf(__uint_as_float(v[j4 * 4 + 1]), 0.5f, hb.y));
+          y[j4 * 4 + 2] = silu_from_half(fmaf(__uint_as_float(v[j4 * 4 + 2]), 0.5f, hb.z));
+          y[j4 * 4 + 3] = silu_from_half(fmaf(__uint_as_float(v[j4 * 4 + 3]), 0.5f, hb.w));
         }
         if (p.head) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            pol = fmaf(y[j], s_wp[ch * 32 + j], pol);
-            val = fmaf(y[j], s_wv[ch * 32 + j], val);
+          for (int j4 = 0; j4 < 4; ++j4) {
+            const float4 wp4 = *reinterpret_cast<const float4*>(s_wp + u * 16 + j4 * 4);
+            const float4 wv4 = *reinterpret_cast<const float4*>(s_wv + u * 16 + j4 * 4);
+            pol = fmaf(y[j4 * 4 + 0], wp4.x, pol);
+            pol = fmaf(y[j4 * 4 + 1], wp4.y, pol);
+            pol = fmaf(y[j4 * 4 + 2], wp4.z, pol);
+            pol = fmaf(y[j4 * 4 + 3], wp4.w, pol);
+            val = fmaf(y[j4 * 4 + 0], wv4.x, val);
+            val = fmaf(y[j4 * 4 + 1], wv4.y, val);
+            val = fmaf(y[j4 * 4 + 2], wv4.z, val);
+            val = fmaf(y[j4 * 4 + 3], wv4.w, val);
           }
         } else {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 2; ++k) {
             uint4 o;
-            o.x = pack_bf16x2(y[8 * k + 0], y[8 * k + 1]);
-            o.y = pack_bf16x2(y[8 * k + 2], y[8 * k + 3]);
-            o.z = pack_bf16x2(y[8 * k + 4], y[8 * k + 5]);
-            o.w = pack_bf16x2(y[8 * k + 6], y[8 * k + 7]);
-            out_row[(size_t)(ch * 4 + k) * p.plane_rows] = o;
+            o.x = valid ? pack_bf16x2(y[8 * k + 0], y[8 * k + 1]) : 0u;
+            o.y = valid ? pack_bf16x2(y[8 * k + 2], y[8 * k + 3]) : 0u;
+            o.z = valid ? pack_bf16x2(y[8 * k + 4], y[8 * k + 5]) : 0u;
+            o.w = valid ? pack_bf16x2(y[8 * k + 6], y[8 * k + 7]) : 0u;
+            out_row[(size_t)(u * 2 + k) * p.plane_rows] = o;
+          }
+        }
+      }
+      if (p.head) {
+        // The two warps of a quadrant hold partial channel sums of the same 32 positions.  The
+        // second warp parks its partials in shared memory (one buffer per accumulator) and signals
+        // an mbarrier; the first warp waits (bounded), adds and writes the maps.  The buffer is
+        // reused two tiles later, after this tile's accumulator-empty barrier has all 8 arrivals.
+        float* part = s_part + acc * 256;
+        if (half == 1) {
+          part[row] = pol;
+          part[128 + row] = val;
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(bar_part(acc));
+        } else {
+          if (!tc::mbar_wait(bar_part(acc), (tcount >> 1) & 1u, abort_flag)) {
+            if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
+            *abort_flag = 1;
+            ok = false;
+          } else {
+            const long long o = (long long)group * p.tiles_per_group * 128 + pos;
+            p.logit_raw[o] = valid ? pol + part[row] : 0.f;
+            p.vmap[o] = valid ? val + part[128 + row] : 0.f;
           }
         }
       }
       tc::fence_before_sync();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
-      if (p.head) {
-        const long long o = (long long)group * p.tiles_per_group * 128 + pos;
-        p.logit_raw[o] = pol;
-        p.vmap[o] = val;
-      }
     }
+    if (p.wait_cycles && blockIdx.x == 0 && threadIdx.x == 64) p.wait_cycles[3] += wait_tfull;
   }
 
   tc::fence_before_sync();

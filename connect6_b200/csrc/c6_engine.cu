@@ -74,6 +74,7 @@ struct C6Engine {
   float *logit_raw = nullptr, *vmap = nullptr;
   long long last_group_pos = -1;
   int* status_dev = nullptr;
+  long long* wait_dev = nullptr;   // [4] pipeline wait counters of CTA 0 (conv kernel)
   long long launches = 0;
   // optional per-kernel timing: event pairs recorded around every launch
   bool profiling = false;
@@ -333,6 +334,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.logit_raw = e->logit_raw;
     p.vmap = e->vmap;
     p.status = e->status_dev;
+    p.wait_cycles = e->profiling ? e->wait_dev : nullptr;
     p.plane_rows = e->plane_rows;
     p.front = e->front;
     p.halo_rows = e->halo_rows;
@@ -351,7 +353,13 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.tmem_cols = lp.tmem_cols;
     {
       ProfScope _ps(e, C6_KIND_CONV0 + l, st);
-      conv_tc_kernel<<<e->G * p.ctas_per_group, kConvThreads, lp.smem, st>>>(p);
+      const int grid = e->G * p.ctas_per_group;
+      switch (lp.k) {
+        case 1: conv_tc_kernel<1><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+        case 3: conv_tc_kernel<3><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+        case 5: conv_tc_kernel<5><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+        default: conv_tc_kernel<0><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+      }
     }
     C6_LAUNCHED(e, "conv_tc_kernel");
     if (!p.head) cur ^= 1;
@@ -454,6 +462,7 @@ int c6_destroy(C6Engine* e) {
   cudaFree(e->pol_bias);
   cudaFree(e->val_bias);
   cudaFree(e->status_dev);
+  cudaFree(e->wait_dev);
   for (auto& r : e->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
   for (auto ev : e->ev_pool) cudaEventDestroy(ev);
   delete e;
@@ -520,6 +529,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
 
   int rc;
   if ((rc = dev_alloc(e, &e->status_dev, 1, true, nullptr))) return bail(rc, "");
+  if ((rc = dev_alloc(e, &e->wait_dev, 4, true, nullptr))) return bail(rc, "");
   if ((rc = dev_alloc(e, &e->pol_bias, e->G, true, nullptr))) return bail(rc, "");
   if ((rc = dev_alloc(e, &e->val_bias, e->G, true, nullptr))) return bail(rc, "");
   e->wconv.assign(e->L, nullptr);
@@ -573,7 +583,10 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     const int cl = e->lp[e->L - 1].cout_p;
     if ((rc = dev_alloc(e, &e->head_wp, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->head_wv, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
-    if (cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+    if (cudaFuncSetAttribute(conv_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
         cudaFuncSetAttribute(stem_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
       return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   } else {
@@ -817,6 +830,14 @@ int c6_profile_read(C6Engine* e, float* ms_per_kind, int64_t* launches_per_kind,
     e->ev_pool.push_back(r.b);
   }
   e->prof.clear();
+  return C6_OK;
+}
+
+int c6_debug_wait_cycles(C6Engine* e, int64_t* out4, int reset) {
+  if (!e || !out4) return C6_ERR_ARG;
+  C6_CUDA(e, cudaSetDevice(e->device));
+  C6_CUDA(e, cudaMemcpy(out4, e->wait_dev, 4 * sizeof(long long), cudaMemcpyDeviceToHost));
+  if (reset) C6_CUDA(e, cudaMemset(e->wait_dev, 0, 4 * sizeof(long long)));
   return C6_OK;
 }
 

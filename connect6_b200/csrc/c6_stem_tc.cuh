@@ -44,7 +44,7 @@ struct StemTcParams {
   int acc_stride, tmem_cols;
 };
 
-constexpr int kStemThreads = 192;
+constexpr int kStemThreads = 320;  // producer warp, MMA warp, eight epilogue warps
 constexpr int kStemSmemHeader = 2048;
 
 __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcParams p) {
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     }
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(bar_tfull(a), 1);
-      tc::mbar_init(bar_tempty(a), 4);
+      tc::mbar_init(bar_tempty(a), 8);
     }
     tc::mbar_init(bar_drain, 1);
     *abort_flag = 0;
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     tc::tmem_relinquish();
   }
   if (warp >= 2) {
-    for (int i = threadIdx.x - 64; i < p.groups * p.c1 && i < 320; i += 128) s_bias[i] = p.bias[i];
+    for (int i = threadIdx.x - 64; i < p.groups * p.c1 && i < 320; i += 256) s_bias[i] = 0.5f * p.bias[i];  // h = x/2
   }
   tc::fence_before_sync();
   __syncthreads();
@@ -105,7 +105,8 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
   if (warp == 0 && lane == 0) {
     // ------------------------------ producer ------------------------------
     bool ok = true;
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
     for (long long item = i_begin; item < i_end && ok; ++item) {
       const int nt_i = (int)(item % p.ntiles);
       const long long gm = item / p.ntiles;
@@ -113,9 +114,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       const int g = (int)(gm / p.mtiles);
       const uint4* xa = p.xk + (long long)g * p.mrows_per_group + (long long)mt * 128;
       const uint4* wb = p.wt + (size_t)g * p.kc * p.ntot + (size_t)nt_i * p.nt;
-      for (int ks = 0; ks < ksteps; ++ks, ++it) {
-        const int s = it % p.nstages;
-        const uint32_t ph = (it / p.nstages) & 1u;
+      for (int ks = 0; ks < ksteps; ++ks) {
         if (!tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag)) {
           atomicOr(p.status, kStatWaitEmpty);
           *abort_flag = 1;
@@ -130,64 +129,79 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
           tc::bulk_g2s(dst + j * a_plane, xa + (size_t)kc * p.mrows, a_plane, bar_full(s));
           tc::bulk_g2s(dst + a_bytes + j * b_plane, wb + (size_t)kc * p.ntot, b_plane, bar_full(s));
         }
+        if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
     }
     if (!ok) {
-      for (int s = 0; s < p.nstages; ++s) {
+      for (int st = 0; st < p.nstages; ++st) {
         const long long t0 = clock64();
         while (clock64() - t0 < 200000) {
-          if (tc::mbar_try_wait(bar_full(s), 0) || tc::mbar_try_wait(bar_full(s), 1)) break;
+          if (tc::mbar_try_wait(bar_full(st), 0) || tc::mbar_try_wait(bar_full(st), 1)) break;
         }
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
+    // Warp-uniform loop, one elected lane issues (see the k x k kernel for the reasoning).
     const uint32_t idesc = tc::make_idesc_bf16(128, p.nt);
+    const uint32_t desc_hi = (uint32_t)(tc::make_desc(0, 0, 128u) >> 32);
+    const uint32_t a_lbo_field = (a_plane >> 4) << 16, b_lbo_field = (b_plane >> 4) << 16;
+    const uint32_t stage0_lo = tc::smem_u32(s_stage) >> 4;
+    const uint32_t stage_rows = stage_bytes >> 4;
     bool ok = true;
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
     int tcount = 0;
     for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
       const int acc = tcount & 1;
       if (!tc::mbar_wait(bar_tempty(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag)) {
-        atomicOr(p.status, kStatWaitTmemEmpty);
+        if (lane == 0) atomicOr(p.status, kStatWaitTmemEmpty);
         *abort_flag = 1;
         ok = false;
         break;
       }
       tc::fence_after_sync();
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
-      for (int ks = 0; ks < ksteps; ++ks, ++it) {
-        const int s = it % p.nstages;
-        const uint32_t ph = (it / p.nstages) & 1u;
+      for (int ks = 0; ks < ksteps; ++ks) {
         if (!tc::mbar_wait(bar_full(s), ph, abort_flag)) {
-          atomicOr(p.status, kStatWaitFull);
+          if (lane == 0) atomicOr(p.status, kStatWaitFull);
           *abort_flag = 1;
           ok = false;
           break;
         }
         tc::fence_after_sync();
-        const uint32_t a0 = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
-        const uint32_t b0 = a0 + a_bytes;
+        const uint32_t a_lo = (stage0_lo + (uint32_t)s * stage_rows) | a_lbo_field;
+        const uint32_t b_lo = (stage0_lo + (uint32_t)s * stage_rows + (a_bytes >> 4)) | b_lbo_field;
+        if (tc::elect_one()) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const uint64_t adesc = tc::make_desc(a0 + 2u * j * a_plane, a_plane, 128u);
-          const uint64_t bdesc = tc::make_desc(b0 + 2u * j * b_plane, b_plane, 128u);
-          tc::mma_bf16(d_tmem, adesc, bdesc, idesc, (ks | j) != 0 ? 1u : 0u);
+          for (int j = 0; j < 2; ++j)
+            tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + 2u * j * (a_plane >> 4)),
+                         ((uint64_t)desc_hi << 32) | (b_lo + 2u * j * (b_plane >> 4)), idesc,
+                         (ks | j) != 0 ? 1u : 0u);
+          tc::mma_commit(bar_empty(s));
+          if (ks == ksteps - 1) tc::mma_commit(bar_tfull(acc));
         }
-        tc::mma_commit(bar_empty(s));
+        __syncwarp();
+        if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
-      if (ok) tc::mma_commit(bar_tfull(acc));
     }
-    tc::mma_commit(bar_drain);
-    if (!tc::mbar_wait(bar_drain, 0, never_flag)) {
-      atomicOr(p.status, kStatWaitDrain);
-      *abort_flag = 1;
+    if (lane == 0) {
+      tc::mma_commit(bar_drain);
+      if (!tc::mbar_wait(bar_drain, 0, never_flag)) {
+        atomicOr(p.status, kStatWaitDrain);
+        *abort_flag = 1;
+      }
     }
+    __syncwarp();
   } else if (warp >= 2) {
     // ------------------------------ epilogue ------------------------------
+    // Eight warps; the two warps of a TMEM lane quadrant alternate over 16-column units.  A unit is
+    // 16 consecutive channels of one output cell (c1 is a multiple of 32, so units never straddle
+    // cells): h = 0.5*acc + 0.5*bias, y = h + h*tanh(h), two 16-byte stores.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
-    const int nchunk = p.nt >> 5;
+    const int nunits = p.nt >> 4;
     const int cells = p.bsize * p.bsize;
     bool ok = true;
     int tcount = 0;
@@ -209,24 +223,24 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       const long long board_row = (long long)p.front + (long long)g * p.group_pos + (long long)board * p.slots;
       const float* gbias = p.bias + (size_t)g * p.c1;
-      for (int ch = 0; ch < nchunk; ++ch) {
-        const int o = nt_i * p.nt + ch * 32;  // first output column of this chunk
+      for (int u = half; u < nunits; u += 2) {
+        const int o = nt_i * p.nt + u * 16;  // first output column of this unit
         const int cell = o / p.c1;
         const int co0 = o - cell * p.c1;
-        uint32_t v[32];
-        tc::tmem_ld32(taddr + (uint32_t)(ch * 32), v);
+        uint32_t v[16];
+        tc::tmem_ld16(taddr + (uint32_t)(u * 16), v);
         tc::tmem_wait_ld();
         if (bvalid && cell < cells) {
           const int r = cell / p.bsize, c = cell - r * p.bsize;
           uint4* dst = p.out + (size_t)(co0 >> 3) * p.plane_rows + board_row + r * p.wp + c;
-          float y[32];
+          float y[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float b = bias_in_smem ? s_bias[g * p.c1 + co0 + j] : gbias[co0 + j];
-            y[j] = silu_fast(__uint_as_float(v[j]) + b);
+          for (int j = 0; j < 16; ++j) {
+            const float hb = bias_in_smem ? s_bias[g * p.c1 + co0 + j] : 0.5f * gbias[co0 + j];
+            y[j] = silu_from_half(fmaf(__uint_as_float(v[j]), 0.5f, hb));
           }
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 2; ++k) {
             uint4 q;
             q.x = pack_bf16x2(y[8 * k + 0], y[8 * k + 1]);
             q.y = pack_bf16x2(y[8 * k + 2], y[8 * k + 3]);

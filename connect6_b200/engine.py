@@ -205,6 +205,12 @@ class Engine:
                 out[names.get(k, f"conv{k - L.C6_KIND_CONV0}")] = (float(ms[k]), int(cnt[k]))
         return out
 
+    def wait_cycles(self, reset: bool = True) -> dict[str, int]:
+        """Pipeline wait counters of CTA 0 of the conv kernel (accumulated while profiling is on)."""
+        buf = (C.c_int64 * 4)()
+        L.check(self._lib.c6_debug_wait_cycles(self._h, buf, 1 if reset else 0), self._h, "c6_debug_wait_cycles")
+        return dict(zip(("producer_wait_empty", "mma_wait_full", "mma_wait_acc", "epilogue_wait_acc"), map(int, buf)))
+
     # -- introspection --------------------------------------------------------------------------
     def status(self) -> int:
         """Device status word; synchronises the engine's device first. Raises if non-zero."""

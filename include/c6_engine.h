@@ -161,6 +161,13 @@ enum {
 int c6_profile_enable(C6Engine* eng, int on);
 int c6_profile_read(C6Engine* eng, float* ms_per_kind, int64_t* launches_per_kind, int n_kinds);
 
+/* Diagnostic with no reference counterpart: while profiling is enabled, CTA 0 of every k x k
+ * tensor-core conv launch adds the SM clocks its roles spent waiting on their pipeline barriers to
+ * four device counters {producer: stage empty, MMA: stage full, MMA: accumulator drained,
+ * epilogue: accumulator ready}.  Copies them to the HOST array out4 (synchronous) and optionally
+ * clears them. */
+int c6_debug_wait_cycles(C6Engine* eng, int64_t* out4, int reset);
+
 /* Reads the device status word (host int). Non-zero means a bounded wait inside a kernel ran
  * out; the kernels then skip their work instead of hanging. The caller must have synchronised
  * the stream it used. */

@@ -140,20 +140,25 @@ def mask_logits(logits: np.ndarray, legal: np.ndarray, fill: float = FP32_MIN) -
 
 
 def masked_log_softmax(logits: np.ndarray, legal: np.ndarray, temperature: float = 1.0) -> np.ndarray:
-    """Normalised log-probabilities of Categorical(logits=mask(logits)/max(T,1e-4))
-    (connect6/train.py:200-203).  Computed in float64; illegal cells get -inf-like
-    values whose exp is exactly 0.  If no cell is legal every entry equals the
-    fill, so the distribution is uniform, as in torch."""
+    """Normalised logits of Categorical(logits=mask(logits)/max(T,1e-4)) (connect6/train.py:200-203),
+    i.e. z - logsumexp(z) with logsumexp = max + log(sum(exp(z - max))), in float64.
+
+    Illegal cells come out near -3.4e38 (their exp is exactly 0).  Edge case kept from the
+    reference: if NO cell is legal every z equals the fill, log(361) is absorbed when added to
+    -3.4e38, and the result is 0 for every cell (torch returns the same); the probabilities
+    softmax(z) are still uniform.  A fill that overflowed to -inf (T < 1) is clamped to the most
+    negative finite value, where torch would raise for the all-occupied row."""
     z = mask_logits(logits, legal).astype(np.float64) / max(float(temperature), 1e-4)
-    with np.errstate(over="ignore", invalid="ignore"):
-        z = np.where(np.isneginf(z), np.finfo(np.float64).min, z)   # fill / T overflowed: still "never"
-        d = z - z.max(axis=-1, keepdims=True)                       # subtract the max before the sum
-        return d - np.log(np.exp(d).sum(axis=-1, keepdims=True))
+    z = np.maximum(z, np.finfo(np.float64).min)
+    m = z.max(axis=-1, keepdims=True)
+    lse = m + np.log(np.exp(z - m).sum(axis=-1, keepdims=True))
+    return z - lse
 
 
 def sample_inverse_cdf(logp: np.ndarray, u: np.ndarray) -> np.ndarray:
-    """Inverse-CDF draw: smallest a with cdf[a] > u * cdf[-1], one u per row."""
-    p = np.exp(logp)
+    """Inverse-CDF draw: smallest a with cdf[a] > u * cdf[-1], one u per row.  The weights are
+    exp(logp - max) so that the degenerate all-occupied row (logp == 0 everywhere) is uniform."""
+    p = np.exp(logp - logp.max(axis=-1, keepdims=True))
     cdf = np.cumsum(p, axis=-1)
     target = np.asarray(u, dtype=np.float64)[:, None] * cdf[:, -1:]
     a = (cdf <= target).sum(axis=-1)

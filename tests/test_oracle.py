@@ -105,8 +105,12 @@ def test_masking_and_log_softmax_match_reference():
         legal = g["legal"][:rows]
         np.testing.assert_allclose(got[legal], ref[legal], atol=2e-5, rtol=1e-6)
         assert np.all(np.exp(got[~legal & legal.any(axis=1, keepdims=True)]) == 0.0)
-    uniform = O.masked_log_softmax(g["logits"][5:6], g["legal"][5:6], 1.0)
-    np.testing.assert_allclose(uniform, -np.log(361.0), atol=1e-6)
+    # all-occupied board: the reference's normalised logits are 0 everywhere (log(361) is absorbed
+    # by the -3.4e38 fill) while its probabilities stay uniform
+    degenerate = O.masked_log_softmax(g["logits"][5:6], g["legal"][5:6], 1.0)
+    assert np.array_equal(degenerate, g["logp_T1.0"][5:6]) and np.all(degenerate == 0.0)
+    picks = O.sample_inverse_cdf(degenerate.repeat(4, 0), np.array([0.0, 0.25, 0.5, 0.999]))
+    assert list(picks) == [0, 90, 180, 360]
     # log-prob of the reference's own sampled actions
     lp = O.masked_log_softmax(g["logits"][:4], g["legal"][:4], 1.0)
     acts = g["sampled_actions"]

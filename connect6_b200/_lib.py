@@ -53,6 +53,7 @@ SIGNATURES = {
     "c6_profile_enable": (_i, [_vp, _i]),
     "c6_profile_read": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(_i64), _i]),
     "c6_debug_wait_cycles": (_i, [_vp, C.POINTER(_i64), _i]),
+    "c6_debug_cta_times": (_i, [_vp, C.POINTER(_i64), _i]),
     "c6_status": (_i, [_vp, C.POINTER(_i)]),
     "c6_launch_count": (_i64, [_vp]),
     "c6_device_bytes": (_i64, [_vp]),

@@ -13,9 +13,9 @@
 // MMA's shared-memory descriptor.
 //
 // GEMM view per tile: M = 128 positions (TMEM lanes), N = Cout, K = k*k*Cin walked as
-// (channel pair q) x (tap).  Weights are pre-packed [q][tap][2][Cout] rows of 8 bf16 and stay
-// resident in shared memory when they fit; otherwise the block of one q travels with the
-// activation stage.
+// (16-channel group q) x (tap).  Weights are pre-packed [q][tap][2][Cout] rows of 8 bf16 and stay
+// resident in shared memory when they fit; otherwise the blocks of a step travel with its
+// activation stage.  A pipeline step stages 32 input channels (two q: 4 planes of 128+2*halo rows).
 //
 // CTA = 320 threads: warp 0 issues bulk copies, warp 1 owns TMEM and issues MMAs, warps 2-9
 // drain the accumulator (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores).
@@ -38,7 +38,7 @@ struct ConvTcParams {
   float* logit_raw;      // [G * tiles_per_group * 128] (head only)
   float* vmap;           // same shape (head only)
   int* status;
-  long long* wait_cycles;  // nullable [4]: CTA 0's clocks spent waiting {producer: empty, MMA: full, MMA: acc empty, epilogue: acc full}
+  long long* wait_cycles;  // nullable [8]: CTA 0's clocks {producer waits empty, MMA waits full, MMA waits acc empty, epilogue waits acc full, MMA issue blocks, MMA loop total, -, -}
   long long plane_rows;
   int front;             // plane row of position 0
   int halo_rows;         // rows staged before and after the 128 tile rows (multiple of 8)
@@ -81,13 +81,16 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   float* s_part = s_wv + 256;  // [2 accumulators][2 heads][128] partial sums of each quadrant's second warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned long long gt_start = 0;
+  if (p.wait_cycles) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_start));
   const int taps = p.kside * p.kside;
   const int nq = p.cin >> 4;
   const int rows = conv_stage_rows(p.halo_rows);
-  const uint32_t a_bytes = 2u * rows * 16u;                     // two channel-chunk planes
-  const uint32_t wq_bytes = (uint32_t)taps * 2u * p.n * 16u;    // weights of one q
+  const uint32_t a_bytes = 4u * rows * 16u;                     // four channel-chunk planes = 32 input channels
+  const uint32_t wq_bytes = (uint32_t)taps * 2u * p.n * 16u;    // weights of one q (16 input channels)
+  const int nsteps = nq >> 1;                                    // pipeline steps per tile: two q each
   const uint32_t w_bytes = wq_bytes * nq;
-  const uint32_t stage_bytes = (a_bytes + (p.resident ? 0u : wq_bytes) + 127u) & ~127u;
+  const uint32_t stage_bytes = (a_bytes + (p.resident ? 0u : 2u * wq_bytes) + 127u) & ~127u;
   const uint32_t w_region = p.resident ? ((w_bytes + 127u) & ~127u) : 0u;
   uint8_t* s_w = smem + kConvSmemHeader;
   uint8_t* s_stage = s_w + w_region;
@@ -160,7 +163,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     for (int tile = t_begin; tile < t_end && ok; ++tile) {
       const long long row0 = group_row0 + (long long)tile * 128 - p.halo_rows;
-      for (int q = 0; q < nq; ++q) {
+      for (int step = 0; step < nsteps; ++step) {
         const long long w0 = timing ? clock64() : 0;
         const bool got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag);
         if (timing) waited += clock64() - w0;
@@ -171,13 +174,14 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
           break;
         }
         const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
-        tc::mbar_expect_tx(bar_full(s), a_bytes + (p.resident ? 0u : wq_bytes));
-        tc::bulk_g2s(dst, p.in + (size_t)(2 * q) * p.plane_rows + row0, rows * 16u, bar_full(s));
-        tc::bulk_g2s(dst + rows * 16u, p.in + (size_t)(2 * q + 1) * p.plane_rows + row0, rows * 16u,
-                     bar_full(s));
+        tc::mbar_expect_tx(bar_full(s), a_bytes + (p.resident ? 0u : 2u * wq_bytes));
+        const uint4* src = p.in + (size_t)(4 * step) * p.plane_rows + row0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          tc::bulk_g2s(dst + (uint32_t)j * rows * 16u, src + (size_t)j * p.plane_rows, rows * 16u, bar_full(s));
         if (!p.resident)
-          tc::bulk_g2s(dst + a_bytes, reinterpret_cast<const uint8_t*>(w_group) + (size_t)q * wq_bytes,
-                       wq_bytes, bar_full(s));
+          tc::bulk_g2s(dst + a_bytes, reinterpret_cast<const uint8_t*>(w_group) + (size_t)(2 * step) * wq_bytes,
+                       2u * wq_bytes, bar_full(s));
         if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
     }
@@ -207,7 +211,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const uint32_t stage_rows = stage_bytes >> 4;
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     bool ok = true;
-    if (p.resident && !tc::mbar_wait(bar_w, 0, abort_flag)) {
+    if (p.resident && !tc::mbar_wait_warp(bar_w, 0, abort_flag, 32)) {
       if (lane == 0) atomicOr(p.status, kStatWaitWeights);
       *abort_flag = 1;
       ok = false;
@@ -215,7 +219,13 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     int s = 0;
     uint32_t ph = 0;
     int tcount = 0;
-    long long wait_full = 0, wait_acc = 0;
+    long long wait_full = 0, wait_acc = 0, issue_clk = 0;
+    const long long loop_t0 = clock64();
+    if (p.wait_cycles && lane == 0 && blockIdx.x < 512) {
+      unsigned long long g;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g));
+      p.wait_cycles[8 + 4 * blockIdx.x + 2] = (long long)g;   // MMA loop begins (weights resident)
+    }
     for (int tile = t_begin; tile < t_end && ok; ++tile, ++tcount) {
       const int acc = tcount & 1;
       const long long w0 = timing ? clock64() : 0;
@@ -229,7 +239,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       }
       tc::fence_after_sync();
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
-      for (int q = 0; q < nq; ++q) {
+      for (int step = 0; step < nsteps; ++step) {
         const long long w1 = timing ? clock64() : 0;
         const bool got = tc::mbar_wait(bar_full(s), ph, abort_flag);
         if (timing) wait_full += clock64() - w1;
@@ -243,36 +253,51 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         // Descriptors of one stage differ only in the start-address field (16-byte units, low word),
         // so a tap costs two integer adds: the issue loop must stay far below the ~50 clocks an MMA
         // of this shape takes, or the tensor pipe starves.
-        const uint32_t a_lo = stage0_lo + (uint32_t)s * stage_rows;
-        const uint32_t b_lo = p.resident ? w_lo + (uint32_t)q * wq_rows : a_lo - a_lbo_field + (a_bytes >> 4) + b_lbo_field;
+        const uint32_t a_lo0 = stage0_lo + (uint32_t)s * stage_rows;
+        const uint32_t b_lo0 = p.resident ? w_lo + (uint32_t)(2 * step) * wq_rows
+                                          : a_lo0 - a_lbo_field + (a_bytes >> 4) + b_lbo_field;
+        const long long w2 = timing ? clock64() : 0;
         if (tc::elect_one()) {
-          if (KS > 0) {
 #pragma unroll
-            for (int tap = 0; tap < KS * KS; ++tap) {
-              const int dy = tap / (KS > 0 ? KS : 1) - KS / 2, dx = tap % (KS > 0 ? KS : 1) - KS / 2;
-              const uint32_t shift = (uint32_t)(p.halo_rows + dy * p.wp + dx);
-              tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + shift),
-                           ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
-                           (q | tap) != 0 ? 1u : 0u);
-            }
-          } else {
-            int tap = 0;
-            for (int dy = -kh; dy <= kh; ++dy)
-              for (int dx = -kh; dx <= kh; ++dx, ++tap)
-                tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + (uint32_t)(p.halo_rows + dy * p.wp + dx)),
+          for (int qq = 0; qq < 2; ++qq) {
+            const uint32_t a_lo = a_lo0 + (uint32_t)qq * 2u * (uint32_t)rows;
+            const uint32_t b_lo = b_lo0 + (uint32_t)qq * wq_rows;
+            if (KS > 0) {
+#pragma unroll
+              for (int tap = 0; tap < KS * KS; ++tap) {
+                const int dy = tap / (KS > 0 ? KS : 1) - KS / 2, dx = tap % (KS > 0 ? KS : 1) - KS / 2;
+                const uint32_t shift = (uint32_t)(p.halo_rows + dy * p.wp + dx);
+                tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + shift),
                              ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
-                             (q | tap) != 0 ? 1u : 0u);
+                             (step | qq | tap) != 0 ? 1u : 0u);
+              }
+            } else {
+              int tap = 0;
+              for (int dy = -kh; dy <= kh; ++dy)
+                for (int dx = -kh; dx <= kh; ++dx, ++tap)
+                  tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + (uint32_t)(p.halo_rows + dy * p.wp + dx)),
+                               ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
+                               (step | qq | tap) != 0 ? 1u : 0u);
+            }
           }
           tc::mma_commit(bar_empty(s));  // stage reusable once these MMAs have read it
-          if (q == nq - 1) tc::mma_commit(bar_tfull(acc));
+          if (step == nsteps - 1) tc::mma_commit(bar_tfull(acc));
         }
         __syncwarp();
+        if (timing) issue_clk += clock64() - w2;
         if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
     }
     if (timing && lane == 0) {
       p.wait_cycles[1] += wait_full;
       p.wait_cycles[2] += wait_acc;
+      p.wait_cycles[4] += issue_clk;
+      p.wait_cycles[5] += clock64() - loop_t0;
+    }
+    if (p.wait_cycles && lane == 0 && blockIdx.x < 512) {
+      unsigned long long g;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g));
+      p.wait_cycles[8 + 4 * blockIdx.x + 3] = (long long)g;   // MMA loop ends (all MMAs issued)
     }
     // every MMA issued must have retired before TMEM is freed
     if (lane == 0) {
@@ -285,6 +310,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     __syncwarp();
   } else if (warp >= 2) {
     // ------------------------------ epilogue ------------------------------
+    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     // Eight warps: warp w may read TMEM lanes 32*(w%4)..+31 only, so two warps share each lane
     // quadrant and split its columns in 16-channel units (unit u goes to the warp with half == u%2).
     // Per element: h = 0.5*acc + 0.5*bias (one FMA), y = h + h*tanh(h) (one MUFU, one FMA).
@@ -295,11 +321,18 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     bool ok = true;
     int tcount = 0;
     long long wait_tfull = 0;
+    // position of this thread's row inside the group, tracked as (board, slot) without divisions
+    int board = 0, slot = 0;
+    {
+      const long long pos0 = (long long)t_begin * 128 + row;
+      board = (int)(pos0 / p.slots);
+      slot = (int)(pos0 - (long long)board * p.slots);
+    }
     for (int tile = t_begin; tile < t_end && ok; ++tile, ++tcount) {
       const int acc = tcount & 1;
-      const long long w0 = clock64();
+      const long long w0 = timing ? clock64() : 0;
       const bool got = tc::mbar_wait(bar_tfull(acc), (tcount >> 1) & 1u, abort_flag);
-      wait_tfull += clock64() - w0;
+      if (timing) wait_tfull += clock64() - w0;
       if (!got) {
         if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
         *abort_flag = 1;
@@ -307,50 +340,67 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         break;
       }
       tc::fence_after_sync();
-      const long long pos = (long long)tile * 128 + row;  // position inside the group
-      const int board = (int)(pos / p.slots);
-      const int slot = (int)(pos - (long long)board * p.slots);
+      const long long pos = (long long)tile * 128 + row;
       const int r = slot / p.wp, c = slot - r * p.wp;
       const bool valid = board < p.nboards && r < p.bsize && c < p.bsize;
+      slot += 128;
+      while (slot >= p.slots) { slot -= p.slots; ++board; }
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       uint4* out_row = p.out + group_row0 + pos;
       float pol = 0.f, val = 0.f;
-      for (int u = half; u < nunits; u += 2) {
-        uint32_t v[16];
-        tc::tmem_ld16(taddr + (uint32_t)(u * 16), v);
+      // Units of this warp: half, half+2, half+4, ...  Up to three are fetched from TMEM with one
+      // wait so that their latencies overlap; when that covers the whole tile the accumulator is
+      // handed back to the MMA warp before the arithmetic starts (not on the head layer, whose
+      // partial-sum exchange below relies on the release coming last).
+      for (int u0 = half; u0 < nunits; u0 += 6) {
+        uint32_t v[3][16];
+#pragma unroll
+        for (int b = 0; b < 3; ++b)
+          if (u0 + 2 * b < nunits) tc::tmem_ld16(taddr + (uint32_t)((u0 + 2 * b) * 16), v[b]);
         tc::tmem_wait_ld();
-        float y[16];
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 hb = *reinterpret_cast<const float4*>(s_bias + u * 16 + j4 * 4);  // 0.5 * bias
-          y[j4 * 4 + 0] = silu_from_half(fmaf(__uint_as_float(v[j4 * 4 + 0]), 0.5f, hb.x));
-          y[j4 * 4 + 1] = silu_from_half(fmaf(__uint_as_float(v[j4 * 4 + 1]), 0.5f, hb.y));
-          y[j4 * 4 + 2] = silu_from_half(fmaf(__uint_as_float(v[j4 * 4 + 2]), 0.5f, hb.z));
-          y[j4 * 4 + 3] = silu_from_half(fmaf(__uint_as_float(v[j4 * 4 + 3]), 0.5f, hb.w));
+        if (u0 + 6 >= nunits && !p.head) {
+          tc::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
         }
-        if (p.head) {
 #pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4) {
-            const float4 wp4 = *reinterpret_cast<const float4*>(s_wp + u * 16 + j4 * 4);
-            const float4 wv4 = *reinterpret_cast<const float4*>(s_wv + u * 16 + j4 * 4);
-            pol = fmaf(y[j4 * 4 + 0], wp4.x, pol);
-            pol = fmaf(y[j4 * 4 + 1], wp4.y, pol);
-            pol = fmaf(y[j4 * 4 + 2], wp4.z, pol);
-            pol = fmaf(y[j4 * 4 + 3], wp4.w, pol);
-            val = fmaf(y[j4 * 4 + 0], wv4.x, val);
-            val = fmaf(y[j4 * 4 + 1], wv4.y, val);
-            val = fmaf(y[j4 * 4 + 2], wv4.z, val);
-            val = fmaf(y[j4 * 4 + 3], wv4.w, val);
-          }
-        } else {
+        for (int b = 0; b < 3; ++b) {
+          const int u = u0 + 2 * b;
+          if (u < nunits) {
+            float y[16];
 #pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            uint4 o;
-            o.x = valid ? pack_bf16x2(y[8 * k + 0], y[8 * k + 1]) : 0u;
-            o.y = valid ? pack_bf16x2(y[8 * k + 2], y[8 * k + 3]) : 0u;
-            o.z = valid ? pack_bf16x2(y[8 * k + 4], y[8 * k + 5]) : 0u;
-            o.w = valid ? pack_bf16x2(y[8 * k + 6], y[8 * k + 7]) : 0u;
-            out_row[(size_t)(u * 2 + k) * p.plane_rows] = o;
+            for (int j4 = 0; j4 < 4; ++j4) {
+              const float4 hb = *reinterpret_cast<const float4*>(s_bias + u * 16 + j4 * 4);  // 0.5 * bias
+              y[j4 * 4 + 0] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 0]), 0.5f, hb.x));
+              y[j4 * 4 + 1] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 1]), 0.5f, hb.y));
+              y[j4 * 4 + 2] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 2]), 0.5f, hb.z));
+              y[j4 * 4 + 3] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 3]), 0.5f, hb.w));
+            }
+            if (p.head) {
+#pragma unroll
+              for (int j4 = 0; j4 < 4; ++j4) {
+                const float4 wp4 = *reinterpret_cast<const float4*>(s_wp + u * 16 + j4 * 4);
+                const float4 wv4 = *reinterpret_cast<const float4*>(s_wv + u * 16 + j4 * 4);
+                pol = fmaf(y[j4 * 4 + 0], wp4.x, pol);
+                pol = fmaf(y[j4 * 4 + 1], wp4.y, pol);
+                pol = fmaf(y[j4 * 4 + 2], wp4.z, pol);
+                pol = fmaf(y[j4 * 4 + 3], wp4.w, pol);
+                val = fmaf(y[j4 * 4 + 0], wv4.x, val);
+                val = fmaf(y[j4 * 4 + 1], wv4.y, val);
+                val = fmaf(y[j4 * 4 + 2], wv4.z, val);
+                val = fmaf(y[j4 * 4 + 3], wv4.w, val);
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {
+                uint4 o;
+                o.x = valid ? pack_bf16x2(y[8 * k + 0], y[8 * k + 1]) : 0u;
+                o.y = valid ? pack_bf16x2(y[8 * k + 2], y[8 * k + 3]) : 0u;
+                o.z = valid ? pack_bf16x2(y[8 * k + 4], y[8 * k + 5]) : 0u;
+                o.w = valid ? pack_bf16x2(y[8 * k + 6], y[8 * k + 7]) : 0u;
+                out_row[(size_t)(u * 2 + k) * p.plane_rows] = o;
+              }
+            }
           }
         }
       }
@@ -376,16 +426,23 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
             p.vmap[o] = valid ? val + part[128 + row] : 0.f;
           }
         }
+        // head layer: the accumulator (and with it the partial-sum buffer) is released only now
+        tc::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
       }
-      tc::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
     }
-    if (p.wait_cycles && blockIdx.x == 0 && threadIdx.x == 64) p.wait_cycles[3] += wait_tfull;
+    if (timing && threadIdx.x == 64) p.wait_cycles[3] += wait_tfull;
   }
 
   tc::fence_before_sync();
   __syncthreads();
+  if (p.wait_cycles && threadIdx.x == 0 && blockIdx.x < 512) {
+    unsigned long long gt_end;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_end));
+    p.wait_cycles[8 + 4 * blockIdx.x] = (long long)gt_start;       // ns timestamps of this CTA
+    p.wait_cycles[8 + 4 * blockIdx.x + 1] = (long long)gt_end;
+  }
   if (warp == 1) {
     __syncwarp();
     tc::fence_after_sync();

@@ -78,6 +78,7 @@ struct C6Engine {
   long long launches = 0;
   // optional per-kernel timing: event pairs recorded around every launch
   bool profiling = false;
+  bool wait_counters = false;      // level 2: also the in-kernel pipeline wait counters
   struct ProfRec { int kind; cudaEvent_t a, b; };
   std::vector<ProfRec> prof;
   std::vector<cudaEvent_t> ev_pool;
@@ -334,7 +335,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.logit_raw = e->logit_raw;
     p.vmap = e->vmap;
     p.status = e->status_dev;
-    p.wait_cycles = e->profiling ? e->wait_dev : nullptr;
+    p.wait_cycles = e->wait_counters ? e->wait_dev : nullptr;
     p.plane_rows = e->plane_rows;
     p.front = e->front;
     p.halo_rows = e->halo_rows;
@@ -529,7 +530,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
 
   int rc;
   if ((rc = dev_alloc(e, &e->status_dev, 1, true, nullptr))) return bail(rc, "");
-  if ((rc = dev_alloc(e, &e->wait_dev, 4, true, nullptr))) return bail(rc, "");
+  if ((rc = dev_alloc(e, &e->wait_dev, 8 + 2048, true, nullptr))) return bail(rc, "");
   if ((rc = dev_alloc(e, &e->pol_bias, e->G, true, nullptr))) return bail(rc, "");
   if ((rc = dev_alloc(e, &e->val_bias, e->G, true, nullptr))) return bail(rc, "");
   e->wconv.assign(e->L, nullptr);
@@ -555,7 +556,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     if ((rc = dev_alloc(e, &e->bias[0], (size_t)e->G * c1, true, nullptr))) return bail(rc, "");
     // k x k layers
     const int rows = conv_stage_rows(e->halo_rows);
-    const int a_bytes = 2 * rows * 16;
+    const int a_bytes = 4 * rows * 16;   // one pipeline step stages 32 input channels
     const int budget = kSmemLimit - 128 - kConvSmemHeader;
     for (int l = 1; l < e->L; ++l) {
       LayerPlan& p = e->lp[l];
@@ -564,12 +565,12 @@ int c6_create(const C6Desc* d, C6Engine** out) {
       const long long wb = wq * nq;
       p.w_rows_per_group = (size_t)(wb / 16);
       const int a_stage = round_up(a_bytes, 128);
-      if (round_up_ll(wb, 128) + 4LL * a_stage <= budget) {
+      if (round_up_ll(wb, 128) + 3LL * a_stage <= budget) {
         p.resident = 1;
         p.nstages = (int)std::min<long long>(kMaxStages, (budget - round_up_ll(wb, 128)) / a_stage);
         p.smem = 128 + kConvSmemHeader + (int)round_up_ll(wb, 128) + p.nstages * a_stage;
       } else {
-        const long long s_stage = round_up_ll(a_bytes + wq, 128);
+        const long long s_stage = round_up_ll(a_bytes + 2 * wq, 128);
         if (2 * s_stage > budget) return bail(C6_ERR_UNSUPPORTED, "a conv layer's per-chunk weights do not fit shared memory");
         p.resident = 0;
         p.nstages = (int)std::min<long long>(kMaxStages, budget / s_stage);
@@ -813,6 +814,7 @@ int c6_status(C6Engine* e, int* device_status) {
 int c6_profile_enable(C6Engine* e, int on) {
   if (!e) return C6_ERR_ARG;
   e->profiling = on != 0;
+  e->wait_counters = on >= 2;
   return C6_OK;
 }
 
@@ -833,11 +835,18 @@ int c6_profile_read(C6Engine* e, float* ms_per_kind, int64_t* launches_per_kind,
   return C6_OK;
 }
 
-int c6_debug_wait_cycles(C6Engine* e, int64_t* out4, int reset) {
-  if (!e || !out4) return C6_ERR_ARG;
+int c6_debug_wait_cycles(C6Engine* e, int64_t* out8, int reset) {
+  if (!e || !out8) return C6_ERR_ARG;
   C6_CUDA(e, cudaSetDevice(e->device));
-  C6_CUDA(e, cudaMemcpy(out4, e->wait_dev, 4 * sizeof(long long), cudaMemcpyDeviceToHost));
-  if (reset) C6_CUDA(e, cudaMemset(e->wait_dev, 0, 4 * sizeof(long long)));
+  C6_CUDA(e, cudaMemcpy(out8, e->wait_dev, 8 * sizeof(long long), cudaMemcpyDeviceToHost));
+  if (reset) C6_CUDA(e, cudaMemset(e->wait_dev, 0, 8 * sizeof(long long)));
+  return C6_OK;
+}
+
+int c6_debug_cta_times(C6Engine* e, int64_t* out, int n_ctas) {
+  if (!e || !out || n_ctas < 1 || n_ctas > 512) return C6_ERR_ARG;
+  C6_CUDA(e, cudaSetDevice(e->device));
+  C6_CUDA(e, cudaMemcpy(out, e->wait_dev + 8, (size_t)n_ctas * 4 * sizeof(long long), cudaMemcpyDeviceToHost));
   return C6_OK;
 }
 

@@ -56,17 +56,41 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the wait ran out or another role already aborted; the
 // caller then records a status bit, raises the CTA's abort flag and leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   for (;;) {
+    if (backoff_ns) __nanosleep(backoff_ns);
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 31u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitTimeoutCycles) return false;
     }
   }
+}
+
+// Warp-level bounded wait: only lane 0 polls (every poll is a shared-memory operation, and shared
+// memory bandwidth is what feeds the tensor core), optionally backing off between polls; the
+// result is broadcast and the warp leaves converged.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               uint32_t backoff_ns) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    if (!mbar_try_wait(bar, parity)) {
+      const long long t0 = clock64();
+      uint32_t spins = 0;
+      for (;;) {
+        if (backoff_ns) __nanosleep(backoff_ns);
+        if (mbar_try_wait(bar, parity)) break;
+        if ((++spins & 15u) == 0u) {
+          if (*abort_flag || clock64() - t0 > kWaitTimeoutCycles) { ok = 0; break; }
+        }
+      }
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---- bulk async copy global -> shared (completes on an mbarrier) ------------------------------

@@ -189,8 +189,9 @@ class Engine:
         return out
 
     # -- per-kernel timing ------------------------------------------------------------------
-    def profile(self, on: bool) -> None:
-        L.check(self._lib.c6_profile_enable(self._h, 1 if on else 0), self._h, "c6_profile_enable")
+    def profile(self, on: bool | int) -> None:
+        """0/False off, 1/True per-launch events, 2 events plus in-kernel pipeline wait counters."""
+        L.check(self._lib.c6_profile_enable(self._h, int(on)), self._h, "c6_profile_enable")
 
     def profile_read(self) -> dict[str, tuple[float, int]]:
         """{kernel kind: (total ms, launches)} since the last read; waits for the recorded events."""
@@ -207,9 +208,15 @@ class Engine:
 
     def wait_cycles(self, reset: bool = True) -> dict[str, int]:
         """Pipeline wait counters of CTA 0 of the conv kernel (accumulated while profiling is on)."""
-        buf = (C.c_int64 * 4)()
+        buf = (C.c_int64 * 8)()
         L.check(self._lib.c6_debug_wait_cycles(self._h, buf, 1 if reset else 0), self._h, "c6_debug_wait_cycles")
-        return dict(zip(("producer_wait_empty", "mma_wait_full", "mma_wait_acc", "epilogue_wait_acc"), map(int, buf)))
+        return dict(zip(("producer_wait_empty", "mma_wait_full", "mma_wait_acc", "epilogue_wait_acc", "mma_issue", "mma_loop_total"), map(int, buf)))
+
+    def cta_times(self, n_ctas: int = 148) -> list[tuple[int, int]]:
+        """(entry, exit, MMA loop begin, MMA loop end) in ns for each CTA of the last profiled conv launch."""
+        buf = (C.c_int64 * (4 * n_ctas))()
+        L.check(self._lib.c6_debug_cta_times(self._h, buf, n_ctas), self._h, "c6_debug_cta_times")
+        return [tuple(int(buf[4 * i + j]) for j in range(4)) for i in range(n_ctas)]
 
     # -- introspection --------------------------------------------------------------------------
     def status(self) -> int:

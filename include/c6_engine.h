@@ -158,15 +158,20 @@ enum {
   C6_KIND_CONV0 = 8,  /* backbone layer l >= 1 is kind C6_KIND_CONV0+l  */
   C6_KIND_COUNT = 8 + C6_MAX_LAYERS
 };
-int c6_profile_enable(C6Engine* eng, int on);
+int c6_profile_enable(C6Engine* eng, int on); /* 0 off, 1 events, 2 events + in-kernel wait counters */
 int c6_profile_read(C6Engine* eng, float* ms_per_kind, int64_t* launches_per_kind, int n_kinds);
 
-/* Diagnostic with no reference counterpart: while profiling is enabled, CTA 0 of every k x k
- * tensor-core conv launch adds the SM clocks its roles spent waiting on their pipeline barriers to
- * four device counters {producer: stage empty, MMA: stage full, MMA: accumulator drained,
- * epilogue: accumulator ready}.  Copies them to the HOST array out4 (synchronous) and optionally
- * clears them. */
-int c6_debug_wait_cycles(C6Engine* eng, int64_t* out4, int reset);
+/* Diagnostic with no reference counterpart: while profiling level 2 is enabled, CTA 0 of every k x k
+ * tensor-core conv launch adds SM clocks to eight device counters: {producer waiting for an empty
+ * stage, MMA warp waiting for a full stage, MMA warp waiting for a drained accumulator, epilogue
+ * waiting for a ready accumulator, MMA warp inside its issue blocks, MMA warp loop total, 0, 0}.
+ * Copies them to the HOST array out8 (synchronous) and optionally clears them. */
+int c6_debug_wait_cycles(C6Engine* eng, int64_t* out8, int reset);
+
+/* Diagnostic: four global-timer stamps (ns) per CTA {kernel entry, kernel exit, MMA loop begin,
+ * MMA loop end} for the first n_ctas (<= 512) CTAs of the most recent k x k conv launch made
+ * while profiling was enabled; HOST array of 4*n_ctas. */
+int c6_debug_cta_times(C6Engine* eng, int64_t* out, int n_ctas);
 
 /* Reads the device status word (host int). Non-zero means a bounded wait inside a kernel ran
  * out; the kernels then skip their work instead of hanging. The caller must have synchronised

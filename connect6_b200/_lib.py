@@ -42,6 +42,7 @@ SIGNATURES = {
     "c6_set_weights": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "c6_reserve": (_i, [_vp, _i64]),
     "c6_forward": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp]),
+    "c6_forward_noalloc": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp]),
     "c6_forward_step": (_i, [_vp, _vp, _i, _i64, _vp, _i, _f, _u64, _u64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "c6_forward_grouped": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _i, _vp]),
     "c6_sample_actions": (_i, [_vp, _vp, _i64, C.c_int32, _f, _u64, _u64, _i64, _vp, _vp, _vp]),

@@ -217,6 +217,15 @@ size_t fp32_smem(const C6Engine* e, const LayerPlan& l) {
   return (in_floats + (size_t)cit * l.k * l.k * kFp32CoT) * sizeof(float);
 }
 
+// ---- scratch for the entry point that must not allocate -------------------------------------------
+// Held by every GPU that loads this library until the process exits.  In host code the symbol
+// below is only a host-side stand-in; kernels get the device address from cudaGetSymbolAddress.
+constexpr size_t kNoAllocScratchBytes = 2621440;  // 2.5 MiB
+constexpr size_t kNoAllocScratchFloats = kNoAllocScratchBytes / sizeof(float);
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {nullptr};
+
 struct RunArgs {
   const void* x = nullptr;
   int x_bf16 = 0;
@@ -716,6 +725,87 @@ int c6_forward_grouped(C6Engine* e, const void* x, int x_dtype, int64_t T, float
   a.value = value;
   a.flags = flags;
   return run(e, a, stream);
+}
+
+int c6_forward_noalloc(C6Engine* e, const void* x, int x_dtype, int64_t B, const uint8_t* orient, float* logits,
+                       float* value, int flags, void* stream) {
+  if (!e) return C6_ERR_ARG;
+  if (e->prec != C6_PREC_FP32 || e->G != 1)
+    return fail(e, C6_ERR_UNSUPPORTED, "c6_forward_noalloc needs an fp32-mode engine with groups == 1");
+  if (x_dtype != C6_X_F32 && x_dtype != C6_X_BF16) return fail(e, C6_ERR_ARG, "unknown x dtype");
+  if (B < 0) return fail(e, C6_ERR_ARG, "negative board count");
+  if (B == 0) return C6_OK;
+  if (!x) return fail(e, C6_ERR_ARG, "x is null");
+  if (e->device < 0 || e->device >= kNoAllocMaxDevices) return fail(e, C6_ERR_UNSUPPORTED, "device ordinal too large");
+  for (size_t i = 0; i < e->have.size(); ++i)
+    if (!e->have[i]) return fail(e, C6_ERR_WEIGHTS, "forward before every layer and head received weights");
+  // floats needed: view of x, two ping-pong activations, the two raw head maps
+  const size_t per_board = (size_t)e->cells * (3 + 2 * (size_t)e->cmax + 2);
+  const size_t need = per_board * (size_t)B;
+  if (need > kNoAllocScratchFloats) {
+    char buf[200];
+    snprintf(buf, sizeof(buf), "c6_forward_noalloc: %lld boards need %zu bytes of scratch, the fixed scratch holds %zu "
+             "(at most %zu boards of this architecture)", (long long)B, need * sizeof(float), kNoAllocScratchBytes,
+             kNoAllocScratchFloats / per_board);
+    return fail(e, C6_ERR_ARG, buf);
+  }
+  C6_CUDA(e, cudaSetDevice(e->device));
+  if (!g_noalloc_scratch_ptr[e->device]) {
+    // once per device, with that device current: resolve the device address of the static array
+    float* ptr = nullptr;
+    C6_CUDA(e, cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch));
+    g_noalloc_scratch_ptr[e->device] = ptr;
+  }
+  float* base = g_noalloc_scratch_ptr[e->device];
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int nb = (int)B;
+  float* xview = base;
+  float* buf[2] = {xview + (size_t)nb * 3 * e->cells, xview + (size_t)nb * (3 + e->cmax) * e->cells};
+  float* raw_pol = buf[1] + (size_t)nb * e->cmax * e->cells;
+  float* raw_val = raw_pol + (size_t)nb * e->cells;
+  // every buffer below is fully written before it is read, so nothing has to be cleared
+  {
+    const long long total = (long long)nb * 3 * e->cells;
+    view_input_f32_kernel<<<dim3((unsigned)((total + 255) / 256), 1), 256, 0, st>>>(x, x_dtype == C6_X_BF16, orient, xview,
+                                                                                   e->n, nb, B, 0);
+    C6_LAUNCHED(e, "view_input_f32_kernel");
+  }
+  const float* in = xview;
+  int cur = 0;
+  for (int l = 0; l < e->L; ++l) {
+    const LayerPlan& lp = e->lp[l];
+    const dim3 grid((unsigned)nb, (unsigned)((lp.cout + kFp32CoT - 1) / kFp32CoT));
+    conv_fp32_kernel<<<grid, kFp32Threads, fp32_smem(e, lp), st>>>(in, e->wraw[l], e->bias[l], buf[cur], lp.cin, lp.cout,
+                                                                    lp.k, e->n, nb, fp32_cit(lp));
+    C6_LAUNCHED(e, "conv_fp32_kernel");
+    in = buf[cur];
+    cur ^= 1;
+  }
+  head_fp32_kernel<<<(unsigned)nb, kFp32Threads, 0, st>>>(in, e->head_wp, e->head_wv, raw_pol, raw_val,
+                                                           e->lp[e->L - 1].cout, e->n, nb);
+  C6_LAUNCHED(e, "head_fp32_kernel");
+  FinishParams f{};
+  f.logit_raw = raw_pol;
+  f.vmap = value ? raw_val : nullptr;
+  f.group_stride = (long long)nb * e->cells;
+  f.board_stride = e->cells;
+  f.pitch = e->n;
+  f.pol_bias = e->pol_bias;
+  f.val_bias = e->val_bias;
+  f.x = x;
+  f.x_bf16 = x_dtype == C6_X_BF16;
+  f.orient = orient;
+  f.x_group_stride = B;
+  f.board0 = 0;
+  f.n = e->n;
+  f.n_actions = e->cells;
+  f.nb = nb;
+  f.flags = flags;
+  f.logits_out = logits;
+  f.value_out = value;
+  finish_kernel<<<dim3((unsigned)nb, 1), kFinishThreads, 0, st>>>(f);
+  C6_LAUNCHED(e, "finish_kernel");
+  return C6_OK;
 }
 
 int c6_debug_layer_output(C6Engine* e, const void* x, int x_dtype, int64_t T, const uint8_t* orient, int layer,

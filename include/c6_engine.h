@@ -113,6 +113,24 @@ int c6_forward_step(C6Engine* eng, const void* x, int x_dtype, int64_t B, const 
 int c6_forward_grouped(C6Engine* eng, const void* x, int x_dtype, int64_t T, float* logits,
                        float* value, int flags, void* stream);
 
+/* No counterpart in the reference.  Same result as c6_forward for an fp32-mode engine with
+ * groups == 1, for callers that must not trigger a device allocation while they run: a host
+ * thread inside a latency-critical loop (cudaMalloc may synchronise the whole device), a process
+ * whose device memory is already handed out to another allocator or pool, or code that runs
+ * where the CUDA allocator must not be entered at all.  c6_forward may grow the engine's
+ * workspace with cudaMalloc on the first call or on a larger batch; this entry point never calls
+ * cudaMalloc, cudaFree or any allocating library routine.  Its activations live in a fixed
+ * 2.5 MiB array that is part of the library image on every GPU that loads it.
+ *   Limit: B * n*n * (3 + 2*max(channels) + 2) floats must fit in 2.5 MiB (9 boards of the
+ *   default 19x19 network); larger calls are rejected with C6_ERR_ARG and a message.
+ *   The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ *   that first call before any stream capture begins.
+ *   All calls share the one array and it keeps the previous call's contents (every buffer is
+ *   rewritten before it is read, so nothing needs clearing); two calls whose kernels overlap on
+ *   the GPU -- different streams, or different engines on one device -- race on it. */
+int c6_forward_noalloc(C6Engine* eng, const void* x, int x_dtype, int64_t B, const uint8_t* orient,
+                       float* logits, float* value, int flags, void* stream);
+
 /* Replaces: _sample_actions / _sample_actions_only on logits that already exist
  * (connect6/train.py:195-213).  legal is uint8/bool [B,A]; logprob nullable. */
 int c6_sample_actions(const float* logits, const uint8_t* legal, int64_t B, int32_t A,

@@ -17,9 +17,11 @@
 // resident in shared memory when they fit; otherwise the blocks of a step travel with its
 // activation stage.  A pipeline step stages 32 input channels (two q: 4 planes of 128+2*halo rows).
 //
-// CTA = 320 threads: warp 0 issues bulk copies, warp 1 owns TMEM and issues MMAs, warps 2-9
-// drain the accumulator (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores).
-// Two TMEM accumulators let the epilogue of tile i overlap the MMAs of tile i+1.  Every wait
+// CTA = 352 threads: warp 0 issues bulk copies; warps 1 and 2 issue the MMAs of alternate tiles
+// (while one is between pipeline steps -- barrier wait, fence, commit -- the other keeps the tensor
+// pipe fed); warps 3-10 drain the accumulators (bias + SiLU in fp32, one bf16 rounding, 16-byte
+// coalesced stores).
+// A ring of 2 or 4 TMEM accumulators lets the epilogue teams overlap the MMAs of later tiles.  Every wait
 // is bounded: when one runs out the CTA records a status bit, stops, frees TMEM and returns.
 #pragma once
 
@@ -51,12 +53,13 @@ struct ConvTcParams {
   int ctas_per_group;
   int resident;
   int nstages;
-  int acc_stride;
+  int acc_stride;        // TMEM columns between accumulator buffers
+  int nacc;              // accumulator buffers in the ring: 2 or 4
   int tmem_cols;
   int head;
 };
 
-constexpr int kConvThreads = 320;  // producer warp, MMA warp, eight epilogue warps
+constexpr int kConvThreads = 352;  // producer warp, two MMA warps, eight epilogue warps
 constexpr int kConvSmemHeader = 5888;  // barriers, TMEM slot, abort flag, bias and head vectors, head partials
 constexpr int kMaxStages = 12;
 
@@ -70,15 +73,13 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   // 128-byte aligned view of dynamic shared memory
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-  // barrier slots: [0,12) full, [12,24) empty, 24 weights, 25-26 acc full, 27-28 acc empty, 29 drain,
-  // 30-31 head partials ready
+  // barrier slots: [0,12) full, [12,24) empty, 24 weights, 25-28 acc full, 29-32 acc empty, 33-34 drain
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 516);
   volatile int* never_flag = reinterpret_cast<volatile int*>(smem + 520);  // stays 0
   float* s_bias = reinterpret_cast<float*>(smem + 640);
   float* s_wp = s_bias + 256;
   float* s_wv = s_wp + 256;
-  float* s_part = s_wv + 256;  // [2 accumulators][2 heads][128] partial sums of each quadrant's second warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned long long gt_start = 0;
@@ -106,9 +107,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   auto bar_empty = [&](int s) { return bar0 + 8u * (12 + s); };
   const uint32_t bar_w = bar0 + 8u * 24;
   auto bar_tfull = [&](int a) { return bar0 + 8u * (25 + a); };
-  auto bar_tempty = [&](int a) { return bar0 + 8u * (27 + a); };
-  const uint32_t bar_drain = bar0 + 8u * 29;
-  auto bar_part = [&](int a) { return bar0 + 8u * (30 + a); };
+  auto bar_tempty = [&](int a) { return bar0 + 8u * (29 + a); };
+  auto bar_drain = [&](int i) { return bar0 + 8u * (33 + i); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
@@ -116,12 +116,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       tc::mbar_init(bar_empty(s), 1);
     }
     tc::mbar_init(bar_w, 1);
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < 4; ++a) {
       tc::mbar_init(bar_tfull(a), 1);
-      tc::mbar_init(bar_tempty(a), 8);
-      tc::mbar_init(bar_part(a), 4);
+      tc::mbar_init(bar_tempty(a), 4);   // the four warps of the team that drained it
     }
-    tc::mbar_init(bar_drain, 1);
+    tc::mbar_init(bar_drain(0), 1);
+    tc::mbar_init(bar_drain(1), 1);
     *abort_flag = 0;
     *never_flag = 0;
     tc::fence_barrier_init();
@@ -130,8 +130,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     tc::tmem_alloc(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
     tc::tmem_relinquish();
   }
-  if (warp >= 2) {
-    for (int i = threadIdx.x - 64; i < p.n; i += 256) {
+  if (warp >= 3) {
+    for (int i = threadIdx.x - 96; i < p.n; i += 256) {
       s_bias[i] = 0.5f * p.bias[(size_t)group * p.n + i];  // the epilogue works on h = x/2
       if (p.head) {
         s_wp[i] = p.head_wp[(size_t)group * p.n + i];
@@ -195,10 +195,13 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    // The whole warp walks the loop in lock step (warp-uniform control flow keeps descriptors and
-    // barrier addresses in uniform registers); one elected lane issues the MMAs and commits.
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------ MMA issuers ------------------------------
+    // Each of the two warps walks its own tiles (issuer = tile parity) in lock step (warp-uniform
+    // control flow keeps descriptors and barrier addresses in uniform registers); one elected lane
+    // issues the MMAs and commits.  Stages are consumed in the producer's order: a warp skips the
+    // ring positions that belong to the other warp's tile.
+    const int issuer = warp - 1;
     const uint32_t idesc = tc::make_idesc_bf16(128, p.n);
     const int kh = p.kside >> 1;
     const uint32_t desc_hi = (uint32_t)(tc::make_desc(0, 0, 128u) >> 32);   // SBO = 128 B, version 1
@@ -209,7 +212,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const uint32_t wq_rows = wq_bytes >> 4;
     const uint32_t stage0_lo = (tc::smem_u32(s_stage) >> 4) | a_lbo_field;
     const uint32_t stage_rows = stage_bytes >> 4;
-    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
+    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0 && issuer == 0;
     bool ok = true;
     if (p.resident && !tc::mbar_wait_warp(bar_w, 0, abort_flag, 32)) {
       if (lane == 0) atomicOr(p.status, kStatWaitWeights);
@@ -218,18 +221,23 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     }
     int s = 0;
     uint32_t ph = 0;
-    int tcount = 0;
+    auto skip_tile = [&]() {   // advance the stage ring over one tile's steps
+      for (int k = 0; k < nsteps; ++k)
+        if (++s == p.nstages) { s = 0; ph ^= 1u; }
+    };
+    if (issuer == 1) skip_tile();
     long long wait_full = 0, wait_acc = 0, issue_clk = 0;
     const long long loop_t0 = clock64();
-    if (p.wait_cycles && lane == 0 && blockIdx.x < 512) {
+    if (p.wait_cycles && lane == 0 && issuer == 0 && blockIdx.x < 512) {
       unsigned long long g;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g));
       p.wait_cycles[8 + 4 * blockIdx.x + 2] = (long long)g;   // MMA loop begins (weights resident)
     }
-    for (int tile = t_begin; tile < t_end && ok; ++tile, ++tcount) {
-      const int acc = tcount & 1;
+    for (int tile = t_begin + issuer, tcount = issuer; tile < t_end && ok; tile += 2, tcount += 2) {
+      const int acc = tcount % p.nacc;
+      const uint32_t acc_ph = (uint32_t)(tcount / p.nacc) & 1u;
       const long long w0 = timing ? clock64() : 0;
-      const bool got_acc = tc::mbar_wait(bar_tempty(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag);
+      const bool got_acc = tc::mbar_wait(bar_tempty(acc), acc_ph ^ 1u, abort_flag);
       if (timing) wait_acc += clock64() - w0;
       if (!got_acc) {
         if (lane == 0) atomicOr(p.status, kStatWaitTmemEmpty);
@@ -287,6 +295,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         if (timing) issue_clk += clock64() - w2;
         if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
+      skip_tile();
     }
     if (timing && lane == 0) {
       p.wait_cycles[1] += wait_full;
@@ -294,44 +303,47 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       p.wait_cycles[4] += issue_clk;
       p.wait_cycles[5] += clock64() - loop_t0;
     }
-    if (p.wait_cycles && lane == 0 && blockIdx.x < 512) {
+    if (p.wait_cycles && lane == 0 && issuer == 0 && blockIdx.x < 512) {
       unsigned long long g;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g));
       p.wait_cycles[8 + 4 * blockIdx.x + 3] = (long long)g;   // MMA loop ends (all MMAs issued)
     }
     // every MMA issued must have retired before TMEM is freed
     if (lane == 0) {
-      tc::mma_commit(bar_drain);
-      if (!tc::mbar_wait(bar_drain, 0, never_flag)) {
+      tc::mma_commit(bar_drain(issuer));
+      if (!tc::mbar_wait(bar_drain(issuer), 0, never_flag)) {
         atomicOr(p.status, kStatWaitDrain);
         *abort_flag = 1;
       }
     }
     __syncwarp();
-  } else if (warp >= 2) {
+  } else if (warp >= 3) {
     // ------------------------------ epilogue ------------------------------
+    // Two teams of four warps take alternate tiles (team = tile parity).  A warp may read TMEM
+    // lanes 32*(w%4)..+31 only, so inside a team each warp owns one lane quadrant = 32 positions
+    // and all their channels; the accumulator ring (2 or 4 buffers) lets the MMA warp run ahead
+    // while both teams are busy.  Per element: h = 0.5*acc + 0.5*bias (one FMA),
+    // y = h + h*tanh(h) (one MUFU, one FMA).  On the head layer the thread already holds every
+    // channel of its position, so both 1x1 heads reduce inside the thread.
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
-    // Eight warps: warp w may read TMEM lanes 32*(w%4)..+31 only, so two warps share each lane
-    // quadrant and split its columns in 16-channel units (unit u goes to the warp with half == u%2).
-    // Per element: h = 0.5*acc + 0.5*bias (one FMA), y = h + h*tanh(h) (one MUFU, one FMA).
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int team = (warp - 3) >> 2;
     const int row = quad * 32 + lane;
     const int nunits = p.n >> 4;
     bool ok = true;
-    int tcount = 0;
     long long wait_tfull = 0;
     // position of this thread's row inside the group, tracked as (board, slot) without divisions
     int board = 0, slot = 0;
     {
-      const long long pos0 = (long long)t_begin * 128 + row;
+      const long long pos0 = (long long)(t_begin + team) * 128 + row;
       board = (int)(pos0 / p.slots);
       slot = (int)(pos0 - (long long)board * p.slots);
     }
-    for (int tile = t_begin; tile < t_end && ok; ++tile, ++tcount) {
-      const int acc = tcount & 1;
+    for (int tile = t_begin + team, tcount = team; tile < t_end && ok; tile += 2, tcount += 2) {
+      const int acc = tcount % p.nacc;
+      const uint32_t acc_ph = (uint32_t)(tcount / p.nacc) & 1u;
       const long long w0 = timing ? clock64() : 0;
-      const bool got = tc::mbar_wait(bar_tfull(acc), (tcount >> 1) & 1u, abort_flag);
+      const bool got = tc::mbar_wait(bar_tfull(acc), acc_ph, abort_flag);
       if (timing) wait_tfull += clock64() - w0;
       if (!got) {
         if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
@@ -343,29 +355,28 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       const long long pos = (long long)tile * 128 + row;
       const int r = slot / p.wp, c = slot - r * p.wp;
       const bool valid = board < p.nboards && r < p.bsize && c < p.bsize;
-      slot += 128;
+      slot += 256;
       while (slot >= p.slots) { slot -= p.slots; ++board; }
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       uint4* out_row = p.out + group_row0 + pos;
       float pol = 0.f, val = 0.f;
-      // Units of this warp: half, half+2, half+4, ...  Up to three are fetched from TMEM with one
-      // wait so that their latencies overlap; when that covers the whole tile the accumulator is
-      // handed back to the MMA warp before the arithmetic starts (not on the head layer, whose
-      // partial-sum exchange below relies on the release coming last).
-      for (int u0 = half; u0 < nunits; u0 += 6) {
+      // Up to three 16-channel units are fetched from TMEM with one wait so that their latencies
+      // overlap; after the last fetch the accumulator goes back to the MMA warp before the
+      // arithmetic starts.
+      for (int u0 = 0; u0 < nunits; u0 += 3) {
         uint32_t v[3][16];
 #pragma unroll
         for (int b = 0; b < 3; ++b)
-          if (u0 + 2 * b < nunits) tc::tmem_ld16(taddr + (uint32_t)((u0 + 2 * b) * 16), v[b]);
+          if (u0 + b < nunits) tc::tmem_ld16(taddr + (uint32_t)((u0 + b) * 16), v[b]);
         tc::tmem_wait_ld();
-        if (u0 + 6 >= nunits && !p.head) {
+        if (u0 + 3 >= nunits) {
           tc::fence_before_sync();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
         }
 #pragma unroll
         for (int b = 0; b < 3; ++b) {
-          const int u = u0 + 2 * b;
+          const int u = u0 + b;
           if (u < nunits) {
             float y[16];
 #pragma unroll
@@ -405,34 +416,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         }
       }
       if (p.head) {
-        // The two warps of a quadrant hold partial channel sums of the same 32 positions.  The
-        // second warp parks its partials in shared memory (one buffer per accumulator) and signals
-        // an mbarrier; the first warp waits (bounded), adds and writes the maps.  The buffer is
-        // reused two tiles later, after this tile's accumulator-empty barrier has all 8 arrivals.
-        float* part = s_part + acc * 256;
-        if (half == 1) {
-          part[row] = pol;
-          part[128 + row] = val;
-          __syncwarp();
-          if (lane == 0) tc::mbar_arrive(bar_part(acc));
-        } else {
-          if (!tc::mbar_wait(bar_part(acc), (tcount >> 1) & 1u, abort_flag)) {
-            if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
-            *abort_flag = 1;
-            ok = false;
-          } else {
-            const long long o = (long long)group * p.tiles_per_group * 128 + pos;
-            p.logit_raw[o] = valid ? pol + part[row] : 0.f;
-            p.vmap[o] = valid ? val + part[128 + row] : 0.f;
-          }
-        }
-        // head layer: the accumulator (and with it the partial-sum buffer) is released only now
-        tc::fence_before_sync();
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
+        const long long o = (long long)group * p.tiles_per_group * 128 + pos;
+        p.logit_raw[o] = valid ? pol : 0.f;
+        p.vmap[o] = valid ? val : 0.f;
       }
     }
-    if (timing && threadIdx.x == 64) p.wait_cycles[3] += wait_tfull;
+    if (timing && threadIdx.x == 96) p.wait_cycles[3] += wait_tfull;
   }
 
   tc::fence_before_sync();

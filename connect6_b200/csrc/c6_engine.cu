@@ -41,7 +41,7 @@ inline int pow2_ceil(int v) {
 struct LayerPlan {
   int k = 0, cin = 0, cout = 0, cin_p = 0, cout_p = 0;
   // tensor-core plan (layers >= 1)
-  int resident = 0, nstages = 0, smem = 0, acc_stride = 0, tmem_cols = 0;
+  int resident = 0, nstages = 0, smem = 0, acc_stride = 0, tmem_cols = 0, nacc = 2;
   size_t w_rows_per_group = 0;  // 16-byte rows of packed weights per group
 };
 
@@ -360,6 +360,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.resident = lp.resident;
     p.nstages = lp.nstages;
     p.acc_stride = lp.acc_stride;
+    p.nacc = lp.nacc;
     p.tmem_cols = lp.tmem_cols;
     {
       ProfScope _ps(e, C6_KIND_CONV0 + l, st);
@@ -586,7 +587,8 @@ int c6_create(const C6Desc* d, C6Engine** out) {
         p.smem = 128 + kConvSmemHeader + p.nstages * (int)s_stage;
       }
       p.acc_stride = pow2_ceil(p.cout_p);
-      p.tmem_cols = 2 * p.acc_stride;
+      p.nacc = p.acc_stride <= 128 ? 4 : 2;          // 512 TMEM columns in total
+      p.tmem_cols = p.nacc * p.acc_stride;
       if ((rc = dev_alloc(e, &e->wconv[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
       if ((rc = dev_alloc(e, &e->bias[l], (size_t)e->G * p.cout_p, true, nullptr))) return bail(rc, "");
     }

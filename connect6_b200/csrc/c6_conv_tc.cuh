@@ -17,10 +17,11 @@
 // resident in shared memory when they fit; otherwise the blocks of a step travel with its
 // activation stage.  A pipeline step stages 32 input channels (two q: 4 planes of 128+2*halo rows).
 //
-// CTA = 352 threads: warp 0 issues bulk copies; warps 1 and 2 issue the MMAs of alternate tiles
-// (while one is between pipeline steps -- barrier wait, fence, commit -- the other keeps the tensor
-// pipe fed); warps 3-10 drain the accumulators (bias + SiLU in fp32, one bf16 rounding, 16-byte
-// coalesced stores).
+// CTA = 416 threads: warp 0 issues bulk copies; warps 1-4 (one per SM sub-partition) issue the
+// MMAs of tiles t = i mod 4, each into its own accumulator -- a lone issuer that shares its
+// scheduler with busy epilogue warps only reaches half the tensor pipe's rate (measured), four keep
+// it saturated and hide each other's per-step barrier work; warps 5-12 drain the accumulators
+// (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores).
 // A ring of 2 or 4 TMEM accumulators lets the epilogue teams overlap the MMAs of later tiles.  Every wait
 // is bounded: when one runs out the CTA records a status bit, stops, frees TMEM and returns.
 #pragma once
@@ -40,7 +41,7 @@ struct ConvTcParams {
   float* logit_raw;      // [G * tiles_per_group * 128] (head only)
   float* vmap;           // same shape (head only)
   int* status;
-  long long* wait_cycles;  // nullable [8]: CTA 0's clocks {producer waits empty, MMA waits full, MMA waits acc empty, epilogue waits acc full, MMA issue blocks, MMA loop total, -, -}
+  long long* wait_cycles;  // nullable [8]: CTA 0's clocks {producer waits empty, MMA waits full, MMA waits acc empty, epilogue waits acc full, MMA issue blocks, MMA loop total, epilogue first TMEM fetch, epilogue arithmetic}
   long long plane_rows;
   int front;             // plane row of position 0
   int halo_rows;         // rows staged before and after the 128 tile rows (multiple of 8)
@@ -52,16 +53,27 @@ struct ConvTcParams {
   int tiles_per_group;
   int ctas_per_group;
   int resident;
-  int nstages;
+  int nstages;           // = nissue * spi
+  int nissue;            // MMA issuer warps in use (1, 2 or 4; divides nacc)
+  int spi;               // pipeline stages owned by each issuer (its private ring)
+  int qps;               // 16-channel groups per pipeline step: 1 or 2
   int acc_stride;        // TMEM columns between accumulator buffers
-  int nacc;              // accumulator buffers in the ring: 2 or 4
+  int nacc;              // accumulator buffers in the ring: 2, 4 or 8 (twice the issuers when possible)
   int tmem_cols;
   int head;
+  // Single-model engines pass the epilogue vectors by value: kernel parameters live in the
+  // constant bank, whose cache is separate from shared memory -- the MMAs already use the whole
+  // shared-memory bandwidth, so epilogue reads from shared memory would queue behind them.
+  int use_const;         // 1: read the three arrays below instead of the shared-memory copies
+  alignas(16) float c_hbias[256];    // 0.5 * bias
+  float c_wp[256];       // policy head weights
+  float c_wv[256];       // value head weights
 };
 
-constexpr int kConvThreads = 352;  // producer warp, two MMA warps, eight epilogue warps
+constexpr int kConvThreads = 416;  // producer warp, four MMA warps, eight epilogue warps
 constexpr int kConvSmemHeader = 5888;  // barriers, TMEM slot, abort flag, bias and head vectors, head partials
-constexpr int kMaxStages = 12;
+constexpr int kMaxStages = 16;
+constexpr int kMaxAcc = 8;
 
 __host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 * halo_rows; }
 
@@ -73,7 +85,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   // 128-byte aligned view of dynamic shared memory
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-  // barrier slots: [0,12) full, [12,24) empty, 24 weights, 25-28 acc full, 29-32 acc empty, 33-34 drain
+  // barrier slots: [0,16) full, [16,32) empty, 32 weights, 33-40 acc full, 41-48 acc empty, 49-52 drain
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 516);
   volatile int* never_flag = reinterpret_cast<volatile int*>(smem + 520);  // stays 0
@@ -87,11 +99,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   const int taps = p.kside * p.kside;
   const int nq = p.cin >> 4;
   const int rows = conv_stage_rows(p.halo_rows);
-  const uint32_t a_bytes = 4u * rows * 16u;                     // four channel-chunk planes = 32 input channels
+  const uint32_t a_bytes = 2u * (uint32_t)p.qps * rows * 16u;    // 2 * qps channel-chunk planes per step
   const uint32_t wq_bytes = (uint32_t)taps * 2u * p.n * 16u;    // weights of one q (16 input channels)
-  const int nsteps = nq >> 1;                                    // pipeline steps per tile: two q each
+  const int nsteps = nq / p.qps;                                 // pipeline steps per tile
   const uint32_t w_bytes = wq_bytes * nq;
-  const uint32_t stage_bytes = (a_bytes + (p.resident ? 0u : 2u * wq_bytes) + 127u) & ~127u;
+  const uint32_t stage_bytes = (a_bytes + (p.resident ? 0u : (uint32_t)p.qps * wq_bytes) + 127u) & ~127u;
   const uint32_t w_region = p.resident ? ((w_bytes + 127u) & ~127u) : 0u;
   uint8_t* s_w = smem + kConvSmemHeader;
   uint8_t* s_stage = s_w + w_region;
@@ -104,11 +116,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
 
   const uint32_t bar0 = tc::smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
-  auto bar_empty = [&](int s) { return bar0 + 8u * (12 + s); };
-  const uint32_t bar_w = bar0 + 8u * 24;
-  auto bar_tfull = [&](int a) { return bar0 + 8u * (25 + a); };
-  auto bar_tempty = [&](int a) { return bar0 + 8u * (29 + a); };
-  auto bar_drain = [&](int i) { return bar0 + 8u * (33 + i); };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (16 + s); };
+  const uint32_t bar_w = bar0 + 8u * 32;
+  auto bar_tfull = [&](int a) { return bar0 + 8u * (33 + a); };
+  auto bar_tempty = [&](int a) { return bar0 + 8u * (41 + a); };
+  auto bar_drain = [&](int i) { return bar0 + 8u * (49 + i); };   // one per issuer
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
@@ -116,12 +128,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       tc::mbar_init(bar_empty(s), 1);
     }
     tc::mbar_init(bar_w, 1);
-    for (int a = 0; a < 4; ++a) {
+    for (int a = 0; a < kMaxAcc; ++a) {
       tc::mbar_init(bar_tfull(a), 1);
       tc::mbar_init(bar_tempty(a), 4);   // the four warps of the team that drained it
     }
-    tc::mbar_init(bar_drain(0), 1);
-    tc::mbar_init(bar_drain(1), 1);
+    for (int i = 0; i < 4; ++i) tc::mbar_init(bar_drain(i), 1);
     *abort_flag = 0;
     *never_flag = 0;
     tc::fence_barrier_init();
@@ -130,8 +141,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     tc::tmem_alloc(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
     tc::tmem_relinquish();
   }
-  if (warp >= 3) {
-    for (int i = threadIdx.x - 96; i < p.n; i += 256) {
+  if (warp >= 5) {
+    for (int i = threadIdx.x - 160; i < p.n; i += 256) {
       s_bias[i] = 0.5f * p.bias[(size_t)group * p.n + i];  // the epilogue works on h = x/2
       if (p.head) {
         s_wp[i] = p.head_wp[(size_t)group * p.n + i];
@@ -147,46 +158,63 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   const uint4* w_group = p.w + (size_t)group * (w_bytes / 16);
   const long long group_row0 = (long long)p.front + (long long)group * p.tiles_per_group * 128;
 
-  if (warp == 0 && lane == 0) {
+  if (warp == 0) {
     // ------------------------------ producer ------------------------------
+    // The warp walks the loop together: lane 0 waits for the stage and arms its barrier, then lanes
+    // 0 .. 2*qps-1 each issue the bulk copy of one channel-chunk plane (issuing a copy costs a few
+    // hundred clocks per thread, so the planes of a stage are issued in parallel).
     bool ok = true;
-    if (p.resident) {
+    if (p.resident && lane == 0) {
       tc::mbar_expect_tx(bar_w, w_bytes);
       for (uint32_t off = 0; off < w_bytes; off += 32768u) {
         const uint32_t len = (w_bytes - off) < 32768u ? (w_bytes - off) : 32768u;
         tc::bulk_g2s(tc::smem_u32(s_w + off), reinterpret_cast<const uint8_t*>(w_group) + off, len, bar_w);
       }
     }
-    int s = 0;
-    uint32_t ph = 0;
     long long waited = 0;
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
-    for (int tile = t_begin; tile < t_end && ok; ++tile) {
-      const long long row0 = group_row0 + (long long)tile * 128 - p.halo_rows;
-      for (int step = 0; step < nsteps; ++step) {
-        const long long w0 = timing ? clock64() : 0;
-        const bool got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag);
-        if (timing) waited += clock64() - w0;
-        if (!got) {
-          atomicOr(p.status, kStatWaitEmpty);
-          *abort_flag = 1;
-          ok = false;
-          break;
+    // Every issuer owns a private ring of `spi` stages, so each stage barrier has exactly one
+    // producer and one consumer that sees all of its phases.  Tiles are fed in waves of `nissue`
+    // (tile tb + i belongs to issuer i), step by step across the wave, so that all issuers advance
+    // together; every ring has received the same number of steps, hence one (position, parity) pair.
+    int sl = 0;
+    uint32_t ph = 0;
+    const int nplanes = 2 * p.qps;
+    for (int tb = t_begin; tb < t_end && ok; tb += p.nissue) {
+      for (int step = 0; step < nsteps && ok; ++step) {
+        for (int iss = 0; iss < p.nissue; ++iss) {
+          const int tile = tb + iss;
+          if (tile >= t_end) break;
+          const long long row0 = group_row0 + (long long)tile * 128 - p.halo_rows;
+          const int s = iss * p.spi + sl;
+          const long long w0 = timing ? clock64() : 0;
+          int got = 1;
+          if (lane == 0) {
+            got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
+            if (got) tc::mbar_expect_tx(bar_full(s), a_bytes + (p.resident ? 0u : (uint32_t)p.qps * wq_bytes));
+          }
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (timing) waited += clock64() - w0;
+          if (!got) {
+            if (lane == 0) atomicOr(p.status, kStatWaitEmpty);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
+          if (lane < nplanes) {
+            const uint4* src = p.in + (size_t)(nplanes * step + lane) * p.plane_rows + row0;
+            tc::bulk_g2s(dst + (uint32_t)lane * rows * 16u, src, rows * 16u, bar_full(s));
+          } else if (lane == nplanes && !p.resident) {
+            tc::bulk_g2s(dst + a_bytes, reinterpret_cast<const uint8_t*>(w_group) + (size_t)(p.qps * step) * wq_bytes,
+                         (uint32_t)p.qps * wq_bytes, bar_full(s));
+          }
         }
-        const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
-        tc::mbar_expect_tx(bar_full(s), a_bytes + (p.resident ? 0u : 2u * wq_bytes));
-        const uint4* src = p.in + (size_t)(4 * step) * p.plane_rows + row0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          tc::bulk_g2s(dst + (uint32_t)j * rows * 16u, src + (size_t)j * p.plane_rows, rows * 16u, bar_full(s));
-        if (!p.resident)
-          tc::bulk_g2s(dst + a_bytes, reinterpret_cast<const uint8_t*>(w_group) + (size_t)(2 * step) * wq_bytes,
-                       2u * wq_bytes, bar_full(s));
-        if (++s == p.nstages) { s = 0; ph ^= 1u; }
+        if (++sl == p.spi) { sl = 0; ph ^= 1u; }
       }
     }
-    if (timing) p.wait_cycles[0] += waited;
-    if (!ok) {
+    if (timing && lane == 0) p.wait_cycles[0] += waited;
+    if (!ok && lane == 0) {
       // let copies already in flight land before the CTA's shared memory is released
       for (int st = 0; st < p.nstages; ++st) {
         const long long t0 = clock64();
@@ -195,12 +223,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         }
       }
     }
-  } else if (warp == 1 || warp == 2) {
+    __syncwarp();
+  } else if (warp >= 1 && warp <= 4 && warp - 1 < p.nissue) {
     // ------------------------------ MMA issuers ------------------------------
-    // Each of the two warps walks its own tiles (issuer = tile parity) in lock step (warp-uniform
-    // control flow keeps descriptors and barrier addresses in uniform registers); one elected lane
-    // issues the MMAs and commits.  Stages are consumed in the producer's order: a warp skips the
-    // ring positions that belong to the other warp's tile.
+    // Issuer i walks tiles t_begin + i, + i + nissue, ... in lock step (warp-uniform control flow
+    // keeps descriptors and barrier addresses in uniform registers); one elected lane issues the
+    // MMAs and commits.  It consumes its private stage ring [i*spi, (i+1)*spi).
     const int issuer = warp - 1;
     const uint32_t idesc = tc::make_idesc_bf16(128, p.n);
     const int kh = p.kside >> 1;
@@ -219,13 +247,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       *abort_flag = 1;
       ok = false;
     }
-    int s = 0;
+    int sl = 0;             // position in the private ring and parity of its current round
     uint32_t ph = 0;
-    auto skip_tile = [&]() {   // advance the stage ring over one tile's steps
-      for (int k = 0; k < nsteps; ++k)
-        if (++s == p.nstages) { s = 0; ph ^= 1u; }
-    };
-    if (issuer == 1) skip_tile();
     long long wait_full = 0, wait_acc = 0, issue_clk = 0;
     const long long loop_t0 = clock64();
     if (p.wait_cycles && lane == 0 && issuer == 0 && blockIdx.x < 512) {
@@ -233,7 +256,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g));
       p.wait_cycles[8 + 4 * blockIdx.x + 2] = (long long)g;   // MMA loop begins (weights resident)
     }
-    for (int tile = t_begin + issuer, tcount = issuer; tile < t_end && ok; tile += 2, tcount += 2) {
+    for (int tile = t_begin + issuer, tcount = issuer; tile < t_end && ok; tile += p.nissue, tcount += p.nissue) {
       const int acc = tcount % p.nacc;
       const uint32_t acc_ph = (uint32_t)(tcount / p.nacc) & 1u;
       const long long w0 = timing ? clock64() : 0;
@@ -248,6 +271,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       tc::fence_after_sync();
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
       for (int step = 0; step < nsteps; ++step) {
+        const int s = issuer * p.spi + sl;
         const long long w1 = timing ? clock64() : 0;
         const bool got = tc::mbar_wait(bar_full(s), ph, abort_flag);
         if (timing) wait_full += clock64() - w1;
@@ -262,12 +286,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         // so a tap costs two integer adds: the issue loop must stay far below the ~50 clocks an MMA
         // of this shape takes, or the tensor pipe starves.
         const uint32_t a_lo0 = stage0_lo + (uint32_t)s * stage_rows;
-        const uint32_t b_lo0 = p.resident ? w_lo + (uint32_t)(2 * step) * wq_rows
+        const uint32_t b_lo0 = p.resident ? w_lo + (uint32_t)(p.qps * step) * wq_rows
                                           : a_lo0 - a_lbo_field + (a_bytes >> 4) + b_lbo_field;
         const long long w2 = timing ? clock64() : 0;
         if (tc::elect_one()) {
-#pragma unroll
-          for (int qq = 0; qq < 2; ++qq) {
+          for (int qq = 0; qq < p.qps; ++qq) {
             const uint32_t a_lo = a_lo0 + (uint32_t)qq * 2u * (uint32_t)rows;
             const uint32_t b_lo = b_lo0 + (uint32_t)qq * wq_rows;
             if (KS > 0) {
@@ -293,9 +316,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         }
         __syncwarp();
         if (timing) issue_clk += clock64() - w2;
-        if (++s == p.nstages) { s = 0; ph ^= 1u; }
+        if (++sl == p.spi) { sl = 0; ph ^= 1u; }
       }
-      skip_tile();
     }
     if (timing && lane == 0) {
       p.wait_cycles[1] += wait_full;
@@ -317,7 +339,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       }
     }
     __syncwarp();
-  } else if (warp >= 3) {
+  } else if (warp >= 5) {
     // ------------------------------ epilogue ------------------------------
     // Two teams of four warps take alternate tiles (team = tile parity).  A warp may read TMEM
     // lanes 32*(w%4)..+31 only, so inside a team each warp owns one lane quadrant = 32 positions
@@ -327,11 +349,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     // channel of its position, so both 1x1 heads reduce inside the thread.
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     const int quad = warp & 3;
-    const int team = (warp - 3) >> 2;
+    const int team = (warp - 5) >> 2;
     const int row = quad * 32 + lane;
     const int nunits = p.n >> 4;
     bool ok = true;
-    long long wait_tfull = 0;
+    long long wait_tfull = 0, ep_ld = 0, ep_math = 0;
     // position of this thread's row inside the group, tracked as (board, slot) without divisions
     int board = 0, slot = 0;
     {
@@ -352,6 +374,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         break;
       }
       tc::fence_after_sync();
+      const long long e0 = timing ? clock64() : 0;
+      long long e1 = e0, e2 = e0;
       const long long pos = (long long)tile * 128 + row;
       const int r = slot / p.wp, c = slot - r * p.wp;
       const bool valid = board < p.nboards && r < p.bsize && c < p.bsize;
@@ -369,37 +393,58 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         for (int b = 0; b < 3; ++b)
           if (u0 + b < nunits) tc::tmem_ld16(taddr + (uint32_t)((u0 + b) * 16), v[b]);
         tc::tmem_wait_ld();
+        if (timing && u0 == 0) e1 = clock64();
         if (u0 + 3 >= nunits) {
           tc::fence_before_sync();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
         }
+        if (timing && u0 == 0) e2 = clock64();
 #pragma unroll
         for (int b = 0; b < 3; ++b) {
           const int u = u0 + b;
           if (u < nunits) {
             float y[16];
-#pragma unroll
-            for (int j4 = 0; j4 < 4; ++j4) {
-              const float4 hb = *reinterpret_cast<const float4*>(s_bias + u * 16 + j4 * 4);  // 0.5 * bias
-              y[j4 * 4 + 0] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 0]), 0.5f, hb.x));
-              y[j4 * 4 + 1] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 1]), 0.5f, hb.y));
-              y[j4 * 4 + 2] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 2]), 0.5f, hb.z));
-              y[j4 * 4 + 3] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 3]), 0.5f, hb.w));
-            }
-            if (p.head) {
+            if (p.use_const) {
 #pragma unroll
               for (int j4 = 0; j4 < 4; ++j4) {
-                const float4 wp4 = *reinterpret_cast<const float4*>(s_wp + u * 16 + j4 * 4);
-                const float4 wv4 = *reinterpret_cast<const float4*>(s_wv + u * 16 + j4 * 4);
-                pol = fmaf(y[j4 * 4 + 0], wp4.x, pol);
-                pol = fmaf(y[j4 * 4 + 1], wp4.y, pol);
-                pol = fmaf(y[j4 * 4 + 2], wp4.z, pol);
-                pol = fmaf(y[j4 * 4 + 3], wp4.w, pol);
-                val = fmaf(y[j4 * 4 + 0], wv4.x, val);
-                val = fmaf(y[j4 * 4 + 1], wv4.y, val);
-                val = fmaf(y[j4 * 4 + 2], wv4.z, val);
-                val = fmaf(y[j4 * 4 + 3], wv4.w, val);
+                const float4 hb = reinterpret_cast<const float4*>(p.c_hbias)[u * 4 + j4];
+                y[j4 * 4 + 0] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 0]), 0.5f, hb.x));
+                y[j4 * 4 + 1] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 1]), 0.5f, hb.y));
+                y[j4 * 4 + 2] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 2]), 0.5f, hb.z));
+                y[j4 * 4 + 3] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 3]), 0.5f, hb.w));
+              }
+            } else {
+#pragma unroll
+              for (int j4 = 0; j4 < 4; ++j4) {
+                const float4 hb = *reinterpret_cast<const float4*>(s_bias + u * 16 + j4 * 4);  // 0.5 * bias
+                y[j4 * 4 + 0] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 0]), 0.5f, hb.x));
+                y[j4 * 4 + 1] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 1]), 0.5f, hb.y));
+                y[j4 * 4 + 2] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 2]), 0.5f, hb.z));
+                y[j4 * 4 + 3] = silu_from_half(fmaf(__uint_as_float(v[b][j4 * 4 + 3]), 0.5f, hb.w));
+              }
+            }
+            if (p.head) {
+              if (p.use_const) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  pol = fmaf(y[j], p.c_wp[u * 16 + j], pol);
+                  val = fmaf(y[j], p.c_wv[u * 16 + j], val);
+                }
+              } else {
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {
+                  const float4 wp4 = *reinterpret_cast<const float4*>(s_wp + u * 16 + j4 * 4);
+                  const float4 wv4 = *reinterpret_cast<const float4*>(s_wv + u * 16 + j4 * 4);
+                  pol = fmaf(y[j4 * 4 + 0], wp4.x, pol);
+                  pol = fmaf(y[j4 * 4 + 1], wp4.y, pol);
+                  pol = fmaf(y[j4 * 4 + 2], wp4.z, pol);
+                  pol = fmaf(y[j4 * 4 + 3], wp4.w, pol);
+                  val = fmaf(y[j4 * 4 + 0], wv4.x, val);
+                  val = fmaf(y[j4 * 4 + 1], wv4.y, val);
+                  val = fmaf(y[j4 * 4 + 2], wv4.z, val);
+                  val = fmaf(y[j4 * 4 + 3], wv4.w, val);
+                }
               }
             } else {
 #pragma unroll
@@ -420,8 +465,16 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         p.logit_raw[o] = valid ? pol : 0.f;
         p.vmap[o] = valid ? val : 0.f;
       }
+      if (timing) {
+        ep_ld += e2 - e1;            // release: fence + syncwarp + arrive
+        ep_math += clock64() - e2;   // arithmetic + stores
+      }
     }
-    if (timing && threadIdx.x == 96) p.wait_cycles[3] += wait_tfull;
+    if (timing && threadIdx.x == 160) {
+      p.wait_cycles[3] += wait_tfull;
+      p.wait_cycles[6] += ep_ld;     // first TMEM fetch of each tile: issue to data
+      p.wait_cycles[7] += ep_math;   // arithmetic + stores (+ later fetches)
+    }
   }
 
   tc::fence_before_sync();

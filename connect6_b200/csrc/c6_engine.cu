@@ -10,6 +10,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -41,7 +42,7 @@ inline int pow2_ceil(int v) {
 struct LayerPlan {
   int k = 0, cin = 0, cout = 0, cin_p = 0, cout_p = 0;
   // tensor-core plan (layers >= 1)
-  int resident = 0, nstages = 0, smem = 0, acc_stride = 0, tmem_cols = 0, nacc = 2;
+  int resident = 0, nstages = 0, smem = 0, acc_stride = 0, tmem_cols = 0, nacc = 2, nissue = 1, spi = 2, qps = 2;
   size_t w_rows_per_group = 0;  // 16-byte rows of packed weights per group
 };
 
@@ -64,6 +65,9 @@ struct C6Engine {
   std::vector<float*> wraw;         // fp32 mode: per layer [G][cout*cin*k*k]
   float *head_wp = nullptr, *head_wv = nullptr, *pol_bias = nullptr, *val_bias = nullptr;
   std::vector<uint8_t> have;        // [G][L+2]
+  // host mirrors of bias / head vectors of single-model engines (passed to kernels by value)
+  std::vector<std::vector<float>> h_bias;   // per layer, padded
+  std::vector<float> h_wp, h_wv;
   // workspace (capacity in boards per group)
   long long cap = 0;
   long long plane_rows = 0, mrows = 0;
@@ -359,6 +363,17 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.ctas_per_group = std::max(1, std::min(e->sms / e->G, g.tiles_per_group));
     p.resident = lp.resident;
     p.nstages = lp.nstages;
+    p.nissue = lp.nissue;
+    p.spi = lp.spi;
+    p.qps = lp.qps;
+    p.use_const = e->G == 1 ? 1 : 0;
+    if (p.use_const) {
+      std::memcpy(p.c_hbias, e->h_bias[l].data(), sizeof(p.c_hbias));
+      if (p.head) {
+        std::memcpy(p.c_wp, e->h_wp.data(), sizeof(p.c_wp));
+        std::memcpy(p.c_wv, e->h_wv.data(), sizeof(p.c_wv));
+      }
+    }
     p.acc_stride = lp.acc_stride;
     p.nacc = lp.nacc;
     p.tmem_cols = lp.tmem_cols;
@@ -537,6 +552,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   e->front = e->halo_rows;
   e->chunk = d->max_chunk > 0 ? d->max_chunk : (e->prec == C6_PREC_BF16 ? 8192 : 1024);
   e->have.assign((size_t)e->G * (e->L + 2), 0);
+  e->h_bias.assign(e->L, std::vector<float>());
 
   int rc;
   if ((rc = dev_alloc(e, &e->status_dev, 1, true, nullptr))) return bail(rc, "");
@@ -566,7 +582,6 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     if ((rc = dev_alloc(e, &e->bias[0], (size_t)e->G * c1, true, nullptr))) return bail(rc, "");
     // k x k layers
     const int rows = conv_stage_rows(e->halo_rows);
-    const int a_bytes = 4 * rows * 16;   // one pipeline step stages 32 input channels
     const int budget = kSmemLimit - 128 - kConvSmemHeader;
     for (int l = 1; l < e->L; ++l) {
       LayerPlan& p = e->lp[l];
@@ -574,21 +589,37 @@ int c6_create(const C6Desc* d, C6Engine** out) {
       const long long wq = (long long)taps * 2 * p.cout_p * 16;
       const long long wb = wq * nq;
       p.w_rows_per_group = (size_t)(wb / 16);
-      const int a_stage = round_up(a_bytes, 128);
-      if (round_up_ll(wb, 128) + 3LL * a_stage <= budget) {
-        p.resident = 1;
-        p.nstages = (int)std::min<long long>(kMaxStages, (budget - round_up_ll(wb, 128)) / a_stage);
-        p.smem = 128 + kConvSmemHeader + (int)round_up_ll(wb, 128) + p.nstages * a_stage;
-      } else {
-        const long long s_stage = round_up_ll(a_bytes + 2 * wq, 128);
-        if (2 * s_stage > budget) return bail(C6_ERR_UNSUPPORTED, "a conv layer's per-chunk weights do not fit shared memory");
-        p.resident = 0;
-        p.nstages = (int)std::min<long long>(kMaxStages, budget / s_stage);
-        p.smem = 128 + kConvSmemHeader + p.nstages * (int)s_stage;
-      }
       p.acc_stride = pow2_ceil(p.cout_p);
-      p.nacc = p.acc_stride <= 128 ? 4 : 2;          // 512 TMEM columns in total
+      p.nacc = std::min(kMaxAcc, 512 / p.acc_stride);  // 512 TMEM columns in total: 8, 4 or 2 accumulators
       p.tmem_cols = p.nacc * p.acc_stride;
+      // Pipeline shape: prefer resident weights and 32-channel steps; every MMA issuer (up to one per
+      // accumulator, at most 4) needs a private ring of at least 2 stages.
+      bool planned = false;
+      for (int resident = 1; resident >= 0 && !planned; --resident) {
+        for (int qps = 2; qps >= 1 && !planned; --qps) {
+          const long long a_bytes = 2LL * qps * rows * 16;
+          const long long stage = round_up_ll(a_bytes + (resident ? 0 : qps * wq), 128);
+          const long long fixed = resident ? round_up_ll(wb, 128) : 0;
+          if (fixed + 2 * stage > budget) continue;
+          const int ns = (int)std::min<long long>(kMaxStages, (budget - fixed) / stage);
+          const int want = std::max(1, std::min(p.nacc / 2, 4));   // two accumulators per issuer
+          if (qps == 2 && ns < 2 * want && resident) {
+            // smaller steps may buy enough stages for all issuers: try qps = 1 first
+            const long long stage1 = round_up_ll(2LL * rows * 16, 128);
+            if ((budget - fixed) / stage1 >= 2 * want) continue;
+          }
+          int nissue = want;
+          while (nissue > 1 && ns < 2 * nissue) nissue >>= 1;
+          p.resident = resident;
+          p.qps = qps;
+          p.nissue = nissue;
+          p.spi = std::min(3, ns / nissue);
+          p.nstages = p.nissue * p.spi;
+          p.smem = 128 + kConvSmemHeader + (int)fixed + p.nstages * (int)stage;
+          planned = true;
+        }
+      }
+      if (!planned) return bail(C6_ERR_UNSUPPORTED, "a conv layer does not fit shared memory");
       if ((rc = dev_alloc(e, &e->wconv[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
       if ((rc = dev_alloc(e, &e->bias[l], (size_t)e->G * p.cout_p, true, nullptr))) return bail(rc, "");
     }
@@ -636,6 +667,13 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
     C6_LAUNCHED(e, "copy_pad_f32_kernel");
     copy_pad_f32_kernel<<<1, 32, 0, st>>>(bias, bdst, 1, 1);
     C6_LAUNCHED(e, "copy_pad_f32_kernel");
+    if (bf16 && e->G == 1) {
+      // single-model engines keep a host copy: the conv kernel takes these vectors by value
+      std::vector<float>& h = layer == C6_HEAD_POLICY ? e->h_wp : e->h_wv;
+      h.assign(256, 0.f);
+      C6_CUDA(e, cudaMemcpyAsync(h.data(), dst, (size_t)cl * sizeof(float), cudaMemcpyDeviceToHost, st));
+      C6_CUDA(e, cudaStreamSynchronize(st));
+    }
     e->have[(size_t)group * (e->L + 2) + e->L + (layer == C6_HEAD_POLICY ? 0 : 1)] = 1;
     return C6_OK;
   }
@@ -656,6 +694,13 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
     copy_pad_f32_kernel<<<(p.cout_p + 127) / 128, 128, 0, st>>>(bias, e->bias[layer] + (size_t)group * p.cout_p,
                                                                  p.cout, p.cout_p);
     C6_LAUNCHED(e, "copy_pad_f32_kernel");
+    if (e->G == 1 && layer >= 1) {
+      e->h_bias[layer].assign(256, 0.f);
+      C6_CUDA(e, cudaMemcpyAsync(e->h_bias[layer].data(), e->bias[layer], (size_t)p.cout_p * sizeof(float),
+                                 cudaMemcpyDeviceToHost, st));
+      C6_CUDA(e, cudaStreamSynchronize(st));
+      for (auto& v : e->h_bias[layer]) v *= 0.5f;   // the epilogue works on h = x/2
+    }
   } else {
     const size_t wn = (size_t)p.cout * p.cin * p.k * p.k;
     C6_CUDA(e, cudaMemcpyAsync(e->wraw[layer] + (size_t)group * wn, w, wn * sizeof(float), cudaMemcpyDeviceToDevice, st));

@@ -210,7 +210,7 @@ class Engine:
         """Pipeline wait counters of CTA 0 of the conv kernel (accumulated while profiling is on)."""
         buf = (C.c_int64 * 8)()
         L.check(self._lib.c6_debug_wait_cycles(self._h, buf, 1 if reset else 0), self._h, "c6_debug_wait_cycles")
-        return dict(zip(("producer_wait_empty", "mma_wait_full", "mma_wait_acc", "epilogue_wait_acc", "mma_issue", "mma_loop_total"), map(int, buf)))
+        return dict(zip(("producer_wait_empty", "mma_wait_full", "mma_wait_acc", "epilogue_wait_acc", "mma_issue", "mma_loop_total", "epilogue_tmem_fetch", "epilogue_math"), map(int, buf)))
 
     def cta_times(self, n_ctas: int = 148) -> list[tuple[int, int]]:
         """(entry, exit, MMA loop begin, MMA loop end) in ns for each CTA of the last profiled conv launch."""

@@ -77,7 +77,8 @@ int c6_create(const C6Desc* desc, C6Engine** out);
 /* Replaces: the parameter storage read by nn.Conv2d (connect6/model.py:56-75) and the weight
  * stacking of connect6/history.py:224-240.  Packs one layer (or head) of one group from the
  * reference state_dict layout: w is fp32 [Cout,Cin,K,K] (heads: [1,C,1,1]), bias fp32 [Cout]
- * (heads: [1]; may be null = zeros).  Asynchronous on `stream`. */
+ * (heads: [1]; may be null = zeros).  Enqueued on `stream`; engines with groups == 1 in bf16 mode
+ * also copy the small bias / head vectors back to the host and wait for `stream` once per call. */
 int c6_set_weights(C6Engine* eng, int group, int layer_or_head, const float* w_oihw,
                    const float* bias, void* stream);
 

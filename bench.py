@@ -247,32 +247,26 @@ def run_engine(args) -> None:
     elapsed_ms = shard.max_over_ranks(elapsed_ms, dev)
     status = eng.status()
 
-    # ---- end to end: host buffers in, host results out, through the public drop-in API ----------
-    out_host = {
-        "action": torch.empty(BATCH, dtype=torch.int64).pin_memory(),
-        "logprob": torch.empty(BATCH, dtype=torch.float32).pin_memory(),
-        "value": torch.empty(BATCH, dtype=torch.float32).pin_memory(),
-    }
-    x_dev = torch.empty_like(dev_batches[0])
+    # ---- end to end: host buffers in, host results out, through the public host-buffer API ---------
+    # HostStepPipeline uploads step i+1's planes on a side stream while step i computes; every step
+    # still does its own pinned-host -> device upload and its own device -> pinned-host download.
+    from connect6_b200.hostpipe import HostStepPipeline
+    pipe = HostStepPipeline(model, BATCH, dev)
 
-    def e2e_step(i: int):
-        x_dev.copy_(host_batches[i % INPUT_BUFFERS], non_blocking=True)
-        action, logprob, value, _ = model.selfplay_step(x_dev, temperature=1.0, seed=0xC6, offset=i,
-                                                        board_index0=first + (i % INPUT_BUFFERS) * BATCH)
-        out_host["action"].copy_(action, non_blocking=True)
-        out_host["logprob"].copy_(logprob, non_blocking=True)
-        out_host["value"].copy_(value, non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()   # the caller reads the step's result
+    def e2e_run(n_steps: int, start: int) -> None:
+        pipe.submit(host_batches[start % INPUT_BUFFERS])
+        for i in range(start, start + n_steps):
+            if i + 1 < start + n_steps:
+                pipe.submit(host_batches[(i + 1) % INPUT_BUFFERS])
+            pipe.step(temperature=1.0, seed=0xC6, offset=i, board_index0=first + (i % INPUT_BUFFERS) * BATCH)
 
     e2e_steps = max(3, min(args.steps, 100))
-    for i in range(3):
-        e2e_step(i)
+    e2e_run(3, 0)
     torch.cuda.synchronize(dev)
     shard.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
+    e2e_run(e2e_steps, 3)
     e1.record()
     torch.cuda.synchronize(dev)
     e2e_ms = shard.max_over_ranks(e0.elapsed_time(e1), dev)
@@ -329,7 +323,7 @@ def run_engine(args) -> None:
         "clocks": clocks,
         "e2e": {"value": BATCH * world * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
-                "api": "PolicyValueNet.selfplay_step on pinned host fp32 planes"},
+                "api": "HostStepPipeline(PolicyValueNet.selfplay_step): pinned host fp32 planes in, pinned host results out, upload of step i+1 overlaps step i"},
         "gpu_launches": launches,
         "roofline": roof,
         "whole_step": {"tflops_per_gpu": whole_tflops, "frac_of_peak": whole_tflops / peak,

@@ -74,6 +74,7 @@ constexpr int kConvThreads = 416;  // producer warp, four MMA warps, eight epilo
 constexpr int kConvSmemHeader = 5888;  // barriers, TMEM slot, abort flag, bias and head vectors, head partials
 constexpr int kMaxStages = 16;
 constexpr int kMaxAcc = 8;
+constexpr uint32_t kIdleBackoffNs = 40;   // sleep between polls of the roles that wait long (saves issue slots and power)
 
 __host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 * halo_rows; }
 
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
           const long long w0 = timing ? clock64() : 0;
           int got = 1;
           if (lane == 0) {
-            got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
+            got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, kIdleBackoffNs) ? 1 : 0;
             if (got) tc::mbar_expect_tx(bar_full(s), a_bytes + (p.resident ? 0u : (uint32_t)p.qps * wq_bytes));
           }
           got = __shfl_sync(0xffffffffu, got, 0);
@@ -365,7 +366,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       const int acc = tcount % p.nacc;
       const uint32_t acc_ph = (uint32_t)(tcount / p.nacc) & 1u;
       const long long w0 = timing ? clock64() : 0;
-      const bool got = tc::mbar_wait(bar_tfull(acc), acc_ph, abort_flag);
+      const bool got = tc::mbar_wait(bar_tfull(acc), acc_ph, abort_flag, kIdleBackoffNs);
       if (timing) wait_tfull += clock64() - w0;
       if (!got) {
         if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);

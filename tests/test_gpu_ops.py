@@ -180,3 +180,25 @@ def test_grouped_default_architecture(cuda_device):
     l3, _ = eng.forward_grouped(x.to(cuda_device))
     assert torch.equal(l3, logits)
     assert eng.status() == 0
+
+
+def test_host_step_pipeline_matches_direct_steps(cuda_device):
+    """Pinned host planes in, pinned host results out, uploads overlapped: same results as direct calls."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.hostpipe import HostStepPipeline
+    m = _default_model(cuda_device)
+    B = 96
+    batches = [torch.from_numpy(generate_planes(1000 * i, B)).pin_memory() for i in range(4)]
+    pipe = HostStepPipeline(m, B, cuda_device)
+    pipe.submit(batches[0])
+    for i in range(4):
+        if i + 1 < 4:
+            pipe.submit(batches[i + 1])
+        a, lp, v = pipe.step(seed=5, offset=i, board_index0=1000 * i)
+        da, dlp, dv, _ = m.selfplay_step(batches[i].to(cuda_device), seed=5, offset=i, board_index0=1000 * i)
+        assert torch.equal(a, da.cpu()) and torch.equal(lp, dlp.cpu()) and torch.equal(v, dv.cpu())
+    with pytest.raises(RuntimeError):
+        pipe.step()
+    pipe.submit(batches[0][:10])             # a smaller batch reuses the buffers
+    a, lp, v = pipe.step(seed=5, offset=0, board_index0=0)
+    assert a.shape == (10,)

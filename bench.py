@@ -338,6 +338,102 @@ def run_engine(args) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------
+# the other BASELINE configurations (parity-test cases; timed here for the record)
+# ------------------------------------------------------------------------------------------------
+WIDE_CHANNELS = (64, 64, 128, 128, 128, 192, 192, 192)
+FLOP_PER_BOARD_WIDE = 1_005_162_624
+
+
+def run_workload(args) -> None:
+    """--workload cfg3 | cfg4 | cfg5: grouped ensemble 16 x 512, D4 inference on 65536 boards, the
+    widened network on 32768 boards.  cfg4/cfg5 split their fixed board count over the ranks
+    (strong scaling); cfg3 runs per rank (weak scaling)."""
+    import torch
+    import torch.distributed as dist
+    from connect6_b200 import shard
+    from connect6_b200.boards import generate_planes, shard_range
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import DEFAULT_CHANNELS, DEFAULT_KERNELS, PolicyValueNet
+
+    rank, world, local_rank = shard.init_from_env()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    peaks, peak_kind = load_peaks()
+    wl = args.workload
+
+    def state_for(seed, channels=None):
+        torch.manual_seed(seed)
+        return {k: v.detach() for k, v in PolicyValueNet(19, DEFAULT_KERNELS, channels).state_dict().items()}
+
+    if wl == "cfg3":
+        G, T = 16, 512
+        eng = Engine(dev, 19, DEFAULT_KERNELS, DEFAULT_CHANNELS, G, "bf16")
+        for g in range(G):
+            eng.load_state_dict(state_for(1000 + g), group=g)
+        x = torch.from_numpy(generate_planes(rank * G * T, G * T)).reshape(G, T, 3, 19, 19).to(dev)
+        boards, flop, scaling = G * T, FLOP_PER_BOARD, "weak"
+        step = lambda i: eng.forward_grouped(x, want_value=True)
+        desc = "16 stacked default-architecture checkpoints x 512 boards, bf16, per-group logits and values"
+    elif wl == "cfg4":
+        total = 65536
+        lo, hi = shard_range(total, rank, world)
+        eng = Engine(dev, 19, DEFAULT_KERNELS, DEFAULT_CHANNELS, 1, "bf16")
+        eng.load_state_dict(state_for(WEIGHT_SEED))
+        x = torch.from_numpy(generate_planes(lo, hi - lo)).to(dev)
+        orient = torch.from_numpy(((torch.arange(lo, hi) % 8).numpy()).astype("uint8")).to(dev)
+        boards, flop, scaling = hi - lo, FLOP_PER_BOARD, "strong"
+        step = lambda i: eng.forward(x, orient, mask=True, inverse_map=True)
+        desc = "65536 boards, orientation i mod 8 applied to the planes, bf16 CNN, masked logits mapped back to canonical indices"
+    else:
+        total = 32768
+        lo, hi = shard_range(total, rank, world)
+        eng = Engine(dev, 19, DEFAULT_KERNELS, WIDE_CHANNELS, 1, "bf16")
+        eng.load_state_dict(state_for(WEIGHT_SEED, WIDE_CHANNELS))
+        x = torch.from_numpy(generate_planes(lo, hi - lo, max_stones=200)).to(dev)
+        boards, flop, scaling = hi - lo, FLOP_PER_BOARD_WIDE, "strong"
+        step = lambda i: eng.forward_step(x, seed=0xC6, offset=i, board_index0=lo)
+        desc = "channels [64,64,128,128,128,192,192,192], 32768 boards with up to 200 stones, bf16 self-play step"
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize(dev)
+    shard.barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = eng.launch_count
+    eng.profile(True)
+    eng.profile_read()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = dt.datetime.now()
+    ev0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    t_end = dt.datetime.now()
+    shard.barrier()
+    prof = eng.profile_read()
+    ms = shard.max_over_ranks(ev0.elapsed_time(ev1), dev)
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
+    status = eng.status()
+    if rank == 0:
+        total_boards = (boards * world if scaling == "weak" else (65536 if wl == "cfg4" else 32768)) * args.steps
+        value = total_boards / (ms * 1e-3)
+        peak = float(peaks["bf16_tflops"])
+        line = {"metric": METRIC.replace("B=8192", wl), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": scaling,
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": desc},
+                "clocks": clocks, "gpu_launches": eng.launch_count - launches0,
+                "whole_step": {"tflops_per_gpu": value / world * flop / 1e12, "frac_of_peak": value / world * flop / 1e12 / peak,
+                               "flop_per_board": flop, "peak_source": f"bf16_tflops burst, of {peak_kind}"},
+                "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
+                            for k, v in sorted(prof.items())},
+                "device_status": status}
+        print(json.dumps(line), flush=True)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -345,11 +441,17 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"],
+                    help="cfg2 (default) is the contract's benchmark; the others are BASELINE's other configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = 20 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else args.warmup
         run_reference(args)
+    elif args.workload != "cfg2":
+        args.steps = 50 if args.steps is None else args.steps
+        args.warmup = 5 if args.warmup is None else max(args.warmup, 3)
+        run_workload(args)
     else:
         args.steps = 300 if args.steps is None else args.steps
         args.warmup = 10 if args.warmup is None else max(args.warmup, 3)   # never fewer than 3 warm-ups

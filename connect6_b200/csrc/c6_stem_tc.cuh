@@ -102,8 +102,10 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
   const uint32_t tmem_base = *tmem_slot;
   const bool bias_in_smem = p.groups * p.c1 <= 320;
 
-  if (warp == 0 && lane == 0) {
+  if (warp == 0) {
     // ------------------------------ producer ------------------------------
+    // Lane 0 waits for the stage and arms its barrier; lanes 0-7 then issue the stage's eight bulk
+    // copies in parallel (issuing a copy costs a thread a few hundred clocks).
     bool ok = true;
     int s = 0;
     uint32_t ph = 0;
@@ -115,24 +117,30 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       const uint4* xa = p.xk + (long long)g * p.mrows_per_group + (long long)mt * 128;
       const uint4* wb = p.wt + (size_t)g * p.kc * p.ntot + (size_t)nt_i * p.nt;
       for (int ks = 0; ks < ksteps; ++ks) {
-        if (!tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag)) {
-          atomicOr(p.status, kStatWaitEmpty);
+        int got = 1;
+        if (lane == 0) {
+          got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, 40) ? 1 : 0;
+          if (got) tc::mbar_expect_tx(bar_full(s), stage_bytes);
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) {
+          if (lane == 0) atomicOr(p.status, kStatWaitEmpty);
           *abort_flag = 1;
           ok = false;
           break;
         }
         const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
-        tc::mbar_expect_tx(bar_full(s), stage_bytes);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int kc = ks * 4 + j;
-          tc::bulk_g2s(dst + j * a_plane, xa + (size_t)kc * p.mrows, a_plane, bar_full(s));
-          tc::bulk_g2s(dst + a_bytes + j * b_plane, wb + (size_t)kc * p.ntot, b_plane, bar_full(s));
+        if (lane < 4) {
+          const int kc = ks * 4 + lane;
+          tc::bulk_g2s(dst + lane * a_plane, xa + (size_t)kc * p.mrows, a_plane, bar_full(s));
+        } else if (lane < 8) {
+          const int kc = ks * 4 + (lane - 4);
+          tc::bulk_g2s(dst + a_bytes + (lane - 4) * b_plane, wb + (size_t)kc * p.ntot, b_plane, bar_full(s));
         }
         if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
     }
-    if (!ok) {
+    if (!ok && lane == 0) {
       for (int st = 0; st < p.nstages; ++st) {
         const long long t0 = clock64();
         while (clock64() - t0 < 200000) {
@@ -140,6 +148,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     // Warp-uniform loop, one elected lane issues (see the k x k kernel for the reasoning).

@@ -1,0 +1,130 @@
+"""GPU tests at the benchmark configurations' own shapes (BASELINE configs 3, 4 and 5).
+
+Small slices are compared with the oracle; the full sizes are checked through size-independent
+properties: a fused path must equal the same result assembled from simpler engine calls, bit for
+bit (both sides run the same arithmetic), masks and index maps must be exact.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import c6_oracle as O
+import torch_port as TP
+
+pytestmark = pytest.mark.gpu
+
+WIDE_CHANNELS = (64, 64, 128, 128, 128, 192, 192, 192)
+KERNELS = (23, 3, 3, 3, 3, 3, 3, 3)
+
+
+def _state(seed, channels=None):
+    from connect6_b200.model import PolicyValueNet
+    torch.manual_seed(seed)
+    m = PolicyValueNet(19, KERNELS, channels)
+    return {k: v.detach().clone() for k, v in m.state_dict().items()}
+
+
+def test_config5_widened_network_against_oracle(cuda_device):
+    """Channels [64,64,128,128,128,192,192,192]: weights no longer fit shared memory (streamed with the
+    activation stages), N = 192 uses two TMEM accumulators, boards drawn with up to 200 stones."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    state = _state(5, WIDE_CHANNELS)
+    eng = Engine(cuda_device, 19, KERNELS, WIDE_CHANNELS, 1, "bf16")
+    eng.load_state_dict(state)
+    x = torch.from_numpy(generate_planes(0, 160, max_stones=200))
+    rl, rv = TP.policy_value_forward(x.double(), {k: v.double() for k, v in state.items()})
+    f = x.double()
+    for i in range(8):
+        w, b = state[f"convs.{i}.weight"].double(), state[f"convs.{i}.bias"].double()
+        f = torch.nn.functional.silu(torch.nn.functional.conv2d(f, w, b, padding=w.shape[-1] // 2))
+        if i in (0, 1, 4, 7):
+            got = eng.layer_output(x.to(cuda_device), i).cpu().double()
+            err = (got - f).abs().max().item() / f.abs().max().item()
+            assert err < 2e-2, f"layer {i}: relative error {err}"
+    logits, value = eng.forward(x.to(cuda_device), mask=True)
+    legal = O.legal_from_planes(x.numpy())
+    lg = logits.cpu().numpy()
+    assert np.array_equal(lg == O.FP32_MIN, ~legal)
+    dl = np.abs(lg - rl.numpy())[legal].max()
+    assert dl < 3e-2 and dl < 0.12 * rl.std().item()
+    assert (value.cpu().double() - rv).abs().max().item() < 3e-2
+    assert eng.status() == 0
+
+
+def test_config5_full_batch_properties(cuda_device):
+    """B = 32768 boards of the widened network in 4 internal passes: equal to the same boards run in
+    separate calls, draws legal and reproducible."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    state = _state(5, WIDE_CHANNELS)
+    eng = Engine(cuda_device, 19, KERNELS, WIDE_CHANNELS, 1, "bf16")
+    eng.load_state_dict(state)
+    B = 32768
+    x = torch.from_numpy(generate_planes(0, B, max_stones=200)).to(cuda_device)
+    a, lp, v, _ = eng.forward_step(x, seed=11, offset=3)
+    legal = ((x[:, 0] == 0) & (x[:, 1] == 0)).reshape(B, -1)
+    assert bool(legal.gather(1, a[:, None]).all())
+    for lo in (0, 8192 * 2 + 100, B - 777):
+        hi = min(B, lo + 777)
+        a2, lp2, v2, _ = eng.forward_step(x[lo:hi], seed=11, offset=3, board_index0=lo)
+        assert torch.equal(a2, a[lo:hi]) and torch.equal(lp2, lp[lo:hi]) and torch.equal(v2, v[lo:hi])
+    assert eng.status() == 0
+
+
+def test_config4_d4_inference_65536_boards(cuda_device):
+    """65536 boards, orientation i mod 8, logits mapped back to canonical indices: must equal (bit for
+    bit) transforming the planes up front, running the plain forward and permuting with the oracle's
+    index tables; masks exact."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import PolicyValueNet
+    state = _state(42)
+    eng = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, 1, "bf16")
+    eng.load_state_dict(state)
+    B = 65536
+    xh = generate_planes(0, B)
+    orient = (np.arange(B) % 8).astype(np.uint8)
+    x = torch.from_numpy(xh).to(cuda_device)
+    od = torch.from_numpy(orient).to(cuda_device)
+    logits, value = eng.forward(x, od, mask=True, inverse_map=True)
+    # reference route inside the engine: explicit views, plain forward
+    xv = np.empty_like(xh)
+    for p in range(8):
+        xv[p::8] = O.transform_boards(xh[p::8], *O.symmetry_for_phase(p))
+    lv, vv = eng.forward(torch.from_numpy(xv).to(cuda_device), mask=False)
+    table = torch.from_numpy(O.d4_forward_table(19).astype(np.int64)).to(cuda_device)
+    canon = torch.gather(lv, 1, table[od.long()])
+    legal = ((x[:, 0] == 0) & (x[:, 1] == 0)).reshape(B, -1)
+    assert torch.equal(logits == O.FP32_MIN, ~legal)
+    assert torch.equal(torch.where(legal, logits, torch.zeros_like(logits)), torch.where(legal, canon, torch.zeros_like(canon)))
+    assert torch.equal(value, vv)
+    assert eng.status() == 0
+
+
+def test_config3_grouped_16x512(cuda_device):
+    """G = 16 stacked checkpoints x 512 boards: every group equals a single-model engine with that
+    group's weights on that group's boards, logits and values, bit for bit."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import PolicyValueNet
+    G, T = 16, 512
+    states = [_state(1000 + g) for g in range(G)]
+    eng = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, G, "bf16")
+    for g in range(G):
+        eng.load_state_dict(states[g], group=g)
+    x = torch.from_numpy(generate_planes(0, G * T)).reshape(G, T, 3, 19, 19).to(cuda_device)
+    logits, value = eng.forward_grouped(x, want_value=True)
+    single = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, 1, "bf16")
+    for g in (0, 7, 15):
+        single.load_state_dict(states[g])
+        l1, v1 = single.forward(x[g])
+        assert torch.equal(l1, logits[g]) and torch.equal(v1, value[g])
+    rl, rv = TP.policy_value_forward(x[3, :32].cpu().double(), {k: v.double() for k, v in states[3].items()})
+    assert (logits[3, :32].cpu().double() - rl).abs().max().item() < 0.12 * rl.std().item()
+    # the training shape of the reference: many models, few tables each (G = 16 here, T = 4)
+    l4, _ = eng.forward_grouped(x[:, :4].contiguous())
+    assert torch.equal(l4, logits[:, :4])
+    assert eng.status() == 0 and single.status() == 0

@@ -98,6 +98,36 @@ __global__ void pack_conv_weights_kernel(const float* __restrict__ w, uint4* __r
   out[idx] = o;
 }
 
+// Same rows for the CTA-pair kernel: [half][q][tap][j][co % (cout_p/2)], half = co / (cout_p/2).
+__global__ void pack_conv_weights_pair_kernel(const float* __restrict__ w, uint4* __restrict__ out,
+                                              int cout, int cin, int kside, int cout_p, int cin_p) {
+  const int taps = kside * kside, nh = cout_p / 2;
+  const long long total = (long long)(cin_p / 16) * taps * 2 * cout_p;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int col = (int)(idx % nh);
+  long long r = idx / nh;
+  const int j = (int)(r % 2);
+  r /= 2;
+  const int tap = (int)(r % taps);
+  r /= taps;
+  const int q = (int)(r % (cin_p / 16));
+  const int half = (int)(r / (cin_p / 16));
+  const int co = half * nh + col;
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int ci = (2 * q + j) * 8 + e;
+    v[e] = (co < cout && ci < cin) ? w[((size_t)co * cin + ci) * taps + tap] : 0.f;
+  }
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  out[idx] = o;
+}
+
 // Stem -> Toeplitz planes wt[kc][ntot] (row o = cell_out*c1 + co, element e: k = kc*8+e).
 __global__ void pack_stem_toeplitz_kernel(const float* __restrict__ w, uint4* __restrict__ out,
                                           int cout, int kside, int n, int c1, int kc, int ntot) {

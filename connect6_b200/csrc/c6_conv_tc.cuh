@@ -21,7 +21,7 @@
 // MMAs of tiles t = i mod 4, each into its own accumulator -- a lone issuer that shares its
 // scheduler with busy epilogue warps only reaches half the tensor pipe's rate (measured), four keep
 // it saturated and hide each other's per-step barrier work; warps 5-12 drain the accumulators
-// (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores).
+// (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores); warp 13 is a second producer.
 // A ring of 2 or 4 TMEM accumulators lets the epilogue teams overlap the MMAs of later tiles.  Every wait
 // is bounded: when one runs out the CTA records a status bit, stops, frees TMEM and returns.
 #pragma once
@@ -35,6 +35,7 @@ struct ConvTcParams {
   const uint4* in;       // input planes  [cin/8][plane_rows] of 16-byte rows
   uint4* out;            // output planes [n/8][plane_rows]; unused when head != 0
   const uint4* w;        // packed weights, per group [cin/16][taps][2][n] rows
+  const uint4* w_pair;   // pair mode: per group [2 halves][cin/16][taps][2][n/2] rows
   const float* bias;     // [G][n]
   const float* head_wp;  // [G][n] policy 1x1 weights (head only)
   const float* head_wv;  // [G][n] value 1x1 weights (head only)
@@ -70,7 +71,7 @@ struct ConvTcParams {
   float c_wv[256];       // value head weights
 };
 
-constexpr int kConvThreads = 416;  // producer warp, four MMA warps, eight epilogue warps
+constexpr int kConvThreads = 448;  // producer warp, four MMA warps, eight epilogue warps, second producer warp
 constexpr int kConvSmemHeader = 5888;  // barriers, TMEM slot, abort flag, bias and head vectors, head partials
 constexpr int kMaxStages = 16;
 constexpr int kMaxAcc = 8;
@@ -80,7 +81,12 @@ __host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 *
 
 // KS = filter side known at compile time (1, 3, 5) so that the tap loop unrolls and the per-tap
 // descriptor offsets live in registers; KS = 0 is the generic run-time loop.
-template <int KS>
+// PAIR = true: the kernel runs as clusters of two CTAs that drive one cta_group::2 MMA (M = 256 =
+// two tiles).  CTA r of the pair stages the activations of tile 2j + r and keeps rows
+// [r*N/2, (r+1)*N/2) of every weight block; the leader (r = 0) issues the MMAs, which read both
+// CTAs' shared memory at the same offsets.  Halving the B operand per CTA cuts the shared-memory
+// operand traffic that bounds a 128 x N MMA for N < 128 and frees shared memory for more stages.
+template <int KS, bool PAIR>
 __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte aligned view of dynamic shared memory
@@ -97,11 +103,14 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned long long gt_start = 0;
   if (p.wait_cycles) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_start));
+  const uint32_t crank = PAIR ? tc::cluster_ctarank() : 0u;
+  const bool leader = crank == 0;
+  const int nloc = PAIR ? p.n / 2 : p.n;   // weight rows this CTA holds
   const int taps = p.kside * p.kside;
   const int nq = p.cin >> 4;
   const int rows = conv_stage_rows(p.halo_rows);
   const uint32_t a_bytes = 2u * (uint32_t)p.qps * rows * 16u;    // 2 * qps channel-chunk planes per step
-  const uint32_t wq_bytes = (uint32_t)taps * 2u * p.n * 16u;    // weights of one q (16 input channels)
+  const uint32_t wq_bytes = (uint32_t)taps * 2u * nloc * 16u;   // this CTA's weights of one q (16 input channels)
   const int nsteps = nq / p.qps;                                 // pipeline steps per tile
   const uint32_t w_bytes = wq_bytes * nq;
   const uint32_t stage_bytes = (a_bytes + (p.resident ? 0u : (uint32_t)p.qps * wq_bytes) + 127u) & ~127u;
@@ -111,9 +120,20 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
 
   const int group = blockIdx.x / p.ctas_per_group;
   const int cta_in_group = blockIdx.x - group * p.ctas_per_group;
-  // contiguous, balanced tile range of this CTA inside its group
-  const int t_begin = (int)(((long long)p.tiles_per_group * cta_in_group) / p.ctas_per_group);
-  const int t_end = (int)(((long long)p.tiles_per_group * (cta_in_group + 1)) / p.ctas_per_group);
+  // Contiguous, balanced tile range inside the group.  Local tile number tl = 0 .. ntl-1 maps to
+  // tile t_first + tl * t_stride; in pair mode the pair owns a range of tile PAIRS and this CTA takes
+  // the even or odd member of each.
+  int t_first, ntl;
+  constexpr int t_stride = PAIR ? 2 : 1;
+  if (PAIR) {
+    const int npairs = p.ctas_per_group >> 1, pair = cta_in_group >> 1, ptiles = p.tiles_per_group >> 1;
+    const int pb = (int)(((long long)ptiles * pair) / npairs), pe = (int)(((long long)ptiles * (pair + 1)) / npairs);
+    t_first = 2 * pb + (int)crank;
+    ntl = pe - pb;
+  } else {
+    t_first = (int)(((long long)p.tiles_per_group * cta_in_group) / p.ctas_per_group);
+    ntl = (int)(((long long)p.tiles_per_group * (cta_in_group + 1)) / p.ctas_per_group) - t_first;
+  }
 
   const uint32_t bar0 = tc::smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
@@ -124,14 +144,17 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   auto bar_drain = [&](int i) { return bar0 + 8u * (49 + i); };   // one per issuer
 
   if (threadIdx.x == 0) {
+    // pair mode, leader: "full" and "weights" also need the peer's relay arrival, "accumulator
+    // drained" the four warps of the draining team in BOTH CTAs
+    const uint32_t both = (PAIR && leader) ? 2u : 1u;
     for (int s = 0; s < kMaxStages; ++s) {
-      tc::mbar_init(bar_full(s), 1);
+      tc::mbar_init(bar_full(s), both);
       tc::mbar_init(bar_empty(s), 1);
     }
-    tc::mbar_init(bar_w, 1);
+    tc::mbar_init(bar_w, both);
     for (int a = 0; a < kMaxAcc; ++a) {
       tc::mbar_init(bar_tfull(a), 1);
-      tc::mbar_init(bar_tempty(a), 4);   // the four warps of the team that drained it
+      tc::mbar_init(bar_tempty(a), 4 * both);
     }
     for (int i = 0; i < 4; ++i) tc::mbar_init(bar_drain(i), 1);
     *abort_flag = 0;
@@ -139,10 +162,15 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     tc::fence_barrier_init();
   }
   if (warp == 1) {
-    tc::tmem_alloc(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
-    tc::tmem_relinquish();
+    if (PAIR) {
+      tc::tmem_alloc2(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+      tc::tmem_relinquish2();
+    } else {
+      tc::tmem_alloc(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+      tc::tmem_relinquish();
+    }
   }
-  if (warp >= 5) {
+  if (warp >= 5 && warp <= 12) {
     for (int i = threadIdx.x - 160; i < p.n; i += 256) {
       s_bias[i] = 0.5f * p.bias[(size_t)group * p.n + i];  // the epilogue works on h = x/2
       if (p.head) {
@@ -152,20 +180,24 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     }
   }
   tc::fence_before_sync();
-  __syncthreads();
+  if (PAIR) tc::cluster_sync(); else __syncthreads();   // barriers of both CTAs exist before anyone arrives
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const uint4* w_group = p.w + (size_t)group * (w_bytes / 16);
+  const uint4* w_group = PAIR ? p.w_pair + ((size_t)group * 2 + crank) * (w_bytes / 16) : p.w + (size_t)group * (w_bytes / 16);
   const long long group_row0 = (long long)p.front + (long long)group * p.tiles_per_group * 128;
 
-  if (warp == 0) {
-    // ------------------------------ producer ------------------------------
+  if (warp == 0 || warp == 13) {
+    // ------------------------------ producers ------------------------------
     // The warp walks the loop together: lane 0 waits for the stage and arms its barrier, then lanes
     // 0 .. 2*qps-1 each issue the bulk copy of one channel-chunk plane (issuing a copy costs a few
     // hundred clocks per thread, so the planes of a stage are issued in parallel).
-    bool ok = true;
-    if (p.resident && lane == 0) {
+    // Two producer warps split the issuers' rings between them (ring i belongs to producer i % 2):
+    // one warp alone cannot issue copies fast enough for four consumers.
+    const int prod = warp == 0 ? 0 : 1;
+    const int nprod = p.nissue >= 2 ? 2 : 1;
+    bool ok = prod < nprod;
+    if (p.resident && lane == 0 && prod == 0) {
       tc::mbar_expect_tx(bar_w, w_bytes);
       for (uint32_t off = 0; off < w_bytes; off += 32768u) {
         const uint32_t len = (w_bytes - off) < 32768u ? (w_bytes - off) : 32768u;
@@ -173,7 +205,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       }
     }
     long long waited = 0;
-    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
+    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0 && prod == 0;
     // Every issuer owns a private ring of `spi` stages, so each stage barrier has exactly one
     // producer and one consumer that sees all of its phases.  Tiles are fed in waves of `nissue`
     // (tile tb + i belongs to issuer i), step by step across the wave, so that all issuers advance
@@ -181,11 +213,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     int sl = 0;
     uint32_t ph = 0;
     const int nplanes = 2 * p.qps;
-    for (int tb = t_begin; tb < t_end && ok; tb += p.nissue) {
+    for (int tb = 0; tb < ntl && ok; tb += p.nissue) {
       for (int step = 0; step < nsteps && ok; ++step) {
-        for (int iss = 0; iss < p.nissue; ++iss) {
-          const int tile = tb + iss;
-          if (tile >= t_end) break;
+        for (int iss = prod; iss < p.nissue; iss += nprod) {
+          if (tb + iss >= ntl) break;
+          const int tile = t_first + (tb + iss) * t_stride;
           const long long row0 = group_row0 + (long long)tile * 128 - p.halo_rows;
           const int s = iss * p.spi + sl;
           const long long w0 = timing ? clock64() : 0;
@@ -225,18 +257,18 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       }
     }
     __syncwarp();
-  } else if (warp >= 1 && warp <= 4 && warp - 1 < p.nissue) {
+  } else if (warp >= 1 && warp <= 4 && warp - 1 < p.nissue && leader) {
     // ------------------------------ MMA issuers ------------------------------
-    // Issuer i walks tiles t_begin + i, + i + nissue, ... in lock step (warp-uniform control flow
+    // Issuer i walks local tiles i, i + nissue, ... in lock step (warp-uniform control flow
     // keeps descriptors and barrier addresses in uniform registers); one elected lane issues the
     // MMAs and commits.  It consumes its private stage ring [i*spi, (i+1)*spi).
     const int issuer = warp - 1;
-    const uint32_t idesc = tc::make_idesc_bf16(128, p.n);
+    const uint32_t idesc = tc::make_idesc_bf16(PAIR ? 256 : 128, p.n);
     const int kh = p.kside >> 1;
     const uint32_t desc_hi = (uint32_t)(tc::make_desc(0, 0, 128u) >> 32);   // SBO = 128 B, version 1
     const uint32_t a_lbo_field = ((uint32_t)(rows * 16) >> 4) << 16;          // LBO = plane pitch of a stage
-    const uint32_t b_lbo_field = ((uint32_t)(p.n * 16) >> 4) << 16;           // LBO = Cout rows
-    const uint32_t b_step = 2u * (uint32_t)p.n;                                // rows between taps
+    const uint32_t b_lbo_field = ((uint32_t)(nloc * 16) >> 4) << 16;          // LBO = this CTA's Cout rows
+    const uint32_t b_step = 2u * (uint32_t)nloc;                               // rows between taps
     const uint32_t w_lo = (tc::smem_u32(s_w) >> 4) | b_lbo_field;
     const uint32_t wq_rows = wq_bytes >> 4;
     const uint32_t stage0_lo = (tc::smem_u32(s_stage) >> 4) | a_lbo_field;
@@ -257,7 +289,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g));
       p.wait_cycles[8 + 4 * blockIdx.x + 2] = (long long)g;   // MMA loop begins (weights resident)
     }
-    for (int tile = t_begin + issuer, tcount = issuer; tile < t_end && ok; tile += p.nissue, tcount += p.nissue) {
+    for (int tcount = issuer; tcount < ntl && ok; tcount += p.nissue) {
       const int acc = tcount % p.nacc;
       const uint32_t acc_ph = (uint32_t)(tcount / p.nacc) & 1u;
       const long long w0 = timing ? clock64() : 0;
@@ -299,21 +331,37 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
               for (int tap = 0; tap < KS * KS; ++tap) {
                 const int dy = tap / (KS > 0 ? KS : 1) - KS / 2, dx = tap % (KS > 0 ? KS : 1) - KS / 2;
                 const uint32_t shift = (uint32_t)(p.halo_rows + dy * p.wp + dx);
-                tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + shift),
-                             ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
-                             (step | qq | tap) != 0 ? 1u : 0u);
+                if (PAIR)
+                  tc::mma_bf16_pair(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + shift),
+                                    ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
+                                    (step | qq | tap) != 0 ? 1u : 0u);
+                else
+                  tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + shift),
+                               ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
+                               (step | qq | tap) != 0 ? 1u : 0u);
               }
             } else {
               int tap = 0;
               for (int dy = -kh; dy <= kh; ++dy)
                 for (int dx = -kh; dx <= kh; ++dx, ++tap)
-                  tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + (uint32_t)(p.halo_rows + dy * p.wp + dx)),
-                               ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
-                               (step | qq | tap) != 0 ? 1u : 0u);
+                  if (PAIR)
+                    tc::mma_bf16_pair(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + (uint32_t)(p.halo_rows + dy * p.wp + dx)),
+                                      ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
+                                      (step | qq | tap) != 0 ? 1u : 0u);
+                  else
+                    tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + (uint32_t)(p.halo_rows + dy * p.wp + dx)),
+                                 ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
+                                 (step | qq | tap) != 0 ? 1u : 0u);
             }
           }
-          tc::mma_commit(bar_empty(s));  // stage reusable once these MMAs have read it
-          if (step == nsteps - 1) tc::mma_commit(bar_tfull(acc));
+          // stage reusable / accumulator ready once these MMAs have completed (in both CTAs of a pair)
+          if (PAIR) {
+            tc::mma_commit_pair_both(bar_empty(s));
+            if (step == nsteps - 1) tc::mma_commit_pair_both(bar_tfull(acc));
+          } else {
+            tc::mma_commit(bar_empty(s));
+            if (step == nsteps - 1) tc::mma_commit(bar_tfull(acc));
+          }
         }
         __syncwarp();
         if (timing) issue_clk += clock64() - w2;
@@ -333,14 +381,44 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     }
     // every MMA issued must have retired before TMEM is freed
     if (lane == 0) {
-      tc::mma_commit(bar_drain(issuer));
+      if (PAIR) tc::mma_commit_pair_local(bar_drain(issuer)); else tc::mma_commit(bar_drain(issuer));
       if (!tc::mbar_wait(bar_drain(issuer), 0, never_flag)) {
         atomicOr(p.status, kStatWaitDrain);
         *abort_flag = 1;
       }
     }
     __syncwarp();
-  } else if (warp >= 5) {
+  } else if (PAIR && !leader && warp >= 1 && warp <= 4 && warp - 1 < p.nissue) {
+    // ------------------------------ peer relays ------------------------------
+    // The leader's issuer i must know when the PEER's copy of a stage has landed: this warp follows
+    // ring i of its own CTA and forwards every completed phase to the leader's barrier.
+    const int issuer = warp - 1;
+    bool ok = true;
+    if (issuer == 0 && p.resident) {
+      if (tc::mbar_wait_warp(bar_w, 0, abort_flag, 32)) {
+        if (lane == 0) tc::mbar_arrive_cluster(tc::mapa(bar_w, 0));
+      } else {
+        if (lane == 0) atomicOr(p.status, kStatWaitWeights);
+        *abort_flag = 1;
+        ok = false;
+      }
+    }
+    int sl = 0;
+    uint32_t ph = 0;
+    for (int tcount = issuer; tcount < ntl && ok; tcount += p.nissue) {
+      for (int step = 0; step < nsteps; ++step) {
+        const int s = issuer * p.spi + sl;
+        if (!tc::mbar_wait_warp(bar_full(s), ph, abort_flag, 0)) {
+          if (lane == 0) atomicOr(p.status, kStatWaitFull);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        if (lane == 0) tc::mbar_arrive_cluster(tc::mapa(bar_full(s), 0));
+        if (++sl == p.spi) { sl = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp >= 5 && warp <= 12) {
     // ------------------------------ epilogue ------------------------------
     // Two teams of four warps take alternate tiles (team = tile parity).  A warp may read TMEM
     // lanes 32*(w%4)..+31 only, so inside a team each warp owns one lane quadrant = 32 positions
@@ -358,11 +436,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     // position of this thread's row inside the group, tracked as (board, slot) without divisions
     int board = 0, slot = 0;
     {
-      const long long pos0 = (long long)(t_begin + team) * 128 + row;
+      const long long pos0 = (long long)(t_first + team * t_stride) * 128 + row;
       board = (int)(pos0 / p.slots);
       slot = (int)(pos0 - (long long)board * p.slots);
     }
-    for (int tile = t_begin + team, tcount = team; tile < t_end && ok; tile += 2, tcount += 2) {
+    for (int tcount = team; tcount < ntl && ok; tcount += 2) {
+      const int tile = t_first + tcount * t_stride;
       const int acc = tcount % p.nacc;
       const uint32_t acc_ph = (uint32_t)(tcount / p.nacc) & 1u;
       const long long w0 = timing ? clock64() : 0;
@@ -380,7 +459,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       const long long pos = (long long)tile * 128 + row;
       const int r = slot / p.wp, c = slot - r * p.wp;
       const bool valid = board < p.nboards && r < p.bsize && c < p.bsize;
-      slot += 256;
+      slot += 256 * t_stride;   // this thread's row in the team's next tile
       while (slot >= p.slots) { slot -= p.slots; ++board; }
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       uint4* out_row = p.out + group_row0 + pos;
@@ -398,7 +477,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         if (u0 + 3 >= nunits) {
           tc::fence_before_sync();
           __syncwarp();
-          if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
+          if (lane == 0) {
+            if (PAIR) tc::mbar_arrive_cluster(tc::mapa(bar_tempty(acc), 0)); else tc::mbar_arrive(bar_tempty(acc));
+          }
         }
         if (timing && u0 == 0) e2 = clock64();
 #pragma unroll
@@ -479,7 +560,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   }
 
   tc::fence_before_sync();
-  __syncthreads();
+  if (PAIR) tc::cluster_sync(); else __syncthreads();   // the peer's shared memory outlives the leader's MMAs
   if (p.wait_cycles && threadIdx.x == 0 && blockIdx.x < 512) {
     unsigned long long gt_end;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_end));
@@ -489,7 +570,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   if (warp == 1) {
     __syncwarp();
     tc::fence_after_sync();
-    tc::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    if (PAIR) tc::tmem_dealloc2(tmem_base, (uint32_t)p.tmem_cols); else tc::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
 }
 

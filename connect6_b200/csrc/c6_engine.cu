@@ -43,6 +43,7 @@ struct LayerPlan {
   int k = 0, cin = 0, cout = 0, cin_p = 0, cout_p = 0;
   // tensor-core plan (layers >= 1)
   int resident = 0, nstages = 0, smem = 0, acc_stride = 0, tmem_cols = 0, nacc = 2, nissue = 1, spi = 2, qps = 2;
+  int pair = 0;                 // run as 2-CTA clusters (cta_group::2)
   size_t w_rows_per_group = 0;  // 16-byte rows of packed weights per group
 };
 
@@ -61,6 +62,8 @@ struct C6Engine {
   // weights
   uint4* wt = nullptr;              // [G][kc0][ntot]
   std::vector<uint4*> wconv;        // per layer [G][rows]
+  std::vector<uint4*> wconv_pair;   // per layer, pair mode: [G][2 halves][rows/2]
+  bool pair_mode = false;           // tile counts are kept even so that layers may run as CTA pairs
   std::vector<float*> bias;         // per layer [G][cout_p] (fp32 mode: [G][cout])
   std::vector<float*> wraw;         // fp32 mode: per layer [G][cout*cin*k*k]
   float *head_wp = nullptr, *head_wv = nullptr, *pol_bias = nullptr, *val_bias = nullptr;
@@ -160,6 +163,7 @@ struct Geometry {
 Geometry geometry(const C6Engine* e, long long nb) {
   Geometry g;
   g.tiles_per_group = (int)((nb * e->slots + 127) / 128);
+  if (e->pair_mode) g.tiles_per_group += g.tiles_per_group & 1;   // CTA pairs take tiles two at a time
   g.group_pos = (long long)g.tiles_per_group * 128;
   g.mrows_per_group = (int)round_up_ll(nb, 128);
   return g;
@@ -361,6 +365,8 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.nboards = nb;
     p.tiles_per_group = g.tiles_per_group;
     p.ctas_per_group = std::max(1, std::min(e->sms / e->G, g.tiles_per_group));
+    if (lp.pair) p.ctas_per_group = std::max(2, p.ctas_per_group & ~1);   // whole pairs (tile counts are even)
+    p.w_pair = e->wconv_pair[l];
     p.resident = lp.resident;
     p.nstages = lp.nstages;
     p.nissue = lp.nissue;
@@ -380,11 +386,32 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     {
       ProfScope _ps(e, C6_KIND_CONV0 + l, st);
       const int grid = e->G * p.ctas_per_group;
-      switch (lp.k) {
-        case 1: conv_tc_kernel<1><<<grid, kConvThreads, lp.smem, st>>>(p); break;
-        case 3: conv_tc_kernel<3><<<grid, kConvThreads, lp.smem, st>>>(p); break;
-        case 5: conv_tc_kernel<5><<<grid, kConvThreads, lp.smem, st>>>(p); break;
-        default: conv_tc_kernel<0><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+      if (lp.pair) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(kConvThreads);
+        cfg.dynamicSmemBytes = (size_t)lp.smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        switch (lp.k) {
+          case 1: cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, true>, p); break;
+          case 3: cudaLaunchKernelEx(&cfg, conv_tc_kernel<3, true>, p); break;
+          case 5: cudaLaunchKernelEx(&cfg, conv_tc_kernel<5, true>, p); break;
+          default: cudaLaunchKernelEx(&cfg, conv_tc_kernel<0, true>, p); break;
+        }
+      } else {
+        switch (lp.k) {
+          case 1: conv_tc_kernel<1, false><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+          case 3: conv_tc_kernel<3, false><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+          case 5: conv_tc_kernel<5, false><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+          default: conv_tc_kernel<0, false><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+        }
       }
     }
     C6_LAUNCHED(e, "conv_tc_kernel");
@@ -481,6 +508,7 @@ int c6_destroy(C6Engine* e) {
   free_workspace(e);
   cudaFree(e->wt);
   for (auto p : e->wconv) cudaFree(p);
+  for (auto p : e->wconv_pair) cudaFree(p);
   for (auto p : e->bias) cudaFree(p);
   for (auto p : e->wraw) cudaFree(p);
   cudaFree(e->head_wp);
@@ -560,6 +588,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   if ((rc = dev_alloc(e, &e->pol_bias, e->G, true, nullptr))) return bail(rc, "");
   if ((rc = dev_alloc(e, &e->val_bias, e->G, true, nullptr))) return bail(rc, "");
   e->wconv.assign(e->L, nullptr);
+  e->wconv_pair.assign(e->L, nullptr);
   e->bias.assign(e->L, nullptr);
   e->wraw.assign(e->L, nullptr);
 
@@ -581,6 +610,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     if ((rc = dev_alloc(e, &e->wt, (size_t)e->G * e->kc0 * e->ntot, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->bias[0], (size_t)e->G * c1, true, nullptr))) return bail(rc, "");
     // k x k layers
+    e->pair_mode = e->sms / e->G >= 2;   // at least one CTA pair per group
     const int rows = conv_stage_rows(e->halo_rows);
     const int budget = kSmemLimit - 128 - kConvSmemHeader;
     for (int l = 1; l < e->L; ++l) {
@@ -595,6 +625,24 @@ int c6_create(const C6Desc* d, C6Engine** out) {
       // Pipeline shape: prefer resident weights and 32-channel steps; every MMA issuer (up to one per
       // accumulator, at most 4) needs a private ring of at least 2 stages.
       bool planned = false;
+      // First choice: CTA pairs with resident weights (each CTA keeps half of the rows).
+      if (e->pair_mode) {
+        for (int qps = 2; qps >= 1 && !planned; --qps) {
+          const long long stage = round_up_ll(2LL * qps * rows * 16, 128);
+          const long long fixed = round_up_ll(wb / 2, 128);
+          const int want = std::max(1, std::min(p.nacc / 2, 4));
+          if (fixed + 2LL * want * stage > budget) continue;
+          const int ns = (int)std::min<long long>(kMaxStages, (budget - fixed) / stage);
+          p.pair = 1;
+          p.resident = 1;
+          p.qps = qps;
+          p.nissue = want;
+          p.spi = std::min(4, ns / want);
+          p.nstages = p.nissue * p.spi;
+          p.smem = 128 + kConvSmemHeader + (int)fixed + p.nstages * (int)stage;
+          planned = true;
+        }
+      }
       for (int resident = 1; resident >= 0 && !planned; --resident) {
         for (int qps = 2; qps >= 1 && !planned; --qps) {
           const long long a_bytes = 2LL * qps * rows * 16;
@@ -621,15 +669,20 @@ int c6_create(const C6Desc* d, C6Engine** out) {
       }
       if (!planned) return bail(C6_ERR_UNSUPPORTED, "a conv layer does not fit shared memory");
       if ((rc = dev_alloc(e, &e->wconv[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
+      if (p.pair && (rc = dev_alloc(e, &e->wconv_pair[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
       if ((rc = dev_alloc(e, &e->bias[l], (size_t)e->G * p.cout_p, true, nullptr))) return bail(rc, "");
     }
     const int cl = e->lp[e->L - 1].cout_p;
     if ((rc = dev_alloc(e, &e->head_wp, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->head_wv, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
-    if (cudaFuncSetAttribute(conv_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+    if (cudaFuncSetAttribute(conv_tc_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<5, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_tc_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
         cudaFuncSetAttribute(stem_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
       return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   } else {
@@ -690,6 +743,11 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
       pack_conv_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
           w, e->wconv[layer] + (size_t)group * p.w_rows_per_group, p.cout, p.cin, p.k, p.cout_p, p.cin_p);
       C6_LAUNCHED(e, "pack_conv_weights_kernel");
+      if (p.pair) {
+        pack_conv_weights_pair_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+            w, e->wconv_pair[layer] + (size_t)group * p.w_rows_per_group, p.cout, p.cin, p.k, p.cout_p, p.cin_p);
+        C6_LAUNCHED(e, "pack_conv_weights_pair_kernel");
+      }
     }
     copy_pad_f32_kernel<<<(p.cout_p + 127) / 128, 128, 0, st>>>(bias, e->bias[layer] + (size_t)group * p.cout_p,
                                                                  p.cout, p.cout_p);

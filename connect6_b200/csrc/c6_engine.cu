@@ -58,7 +58,7 @@ struct C6Engine {
   int cmax_p = 0, cmax = 0;
   // stem GEMM plan
   int kc0 = 0, nt = 0, ntiles = 0, ntot = 0, stem_stages = 0, stem_smem = 0, stem_acc_stride = 0,
-      stem_tmem_cols = 0;
+      stem_tmem_cols = 0, stem_kcs = 4, stem_pair = 0;
   // weights
   uint4* wt = nullptr;              // [G][kc0][ntot]
   std::vector<uint4*> wconv;        // per layer [G][rows]
@@ -165,7 +165,7 @@ Geometry geometry(const C6Engine* e, long long nb) {
   g.tiles_per_group = (int)((nb * e->slots + 127) / 128);
   if (e->pair_mode) g.tiles_per_group += g.tiles_per_group & 1;   // CTA pairs take tiles two at a time
   g.group_pos = (long long)g.tiles_per_group * 128;
-  g.mrows_per_group = (int)round_up_ll(nb, 128);
+  g.mrows_per_group = (int)round_up_ll(nb, e->stem_pair ? 256 : 128);   // CTA pairs take 256 boards per tile
   return g;
 }
 
@@ -319,6 +319,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.front = e->front;
     p.group_pos = (int)g.group_pos;
     p.kc = e->kc0;
+    p.kcs = e->stem_kcs;
     p.ntot = e->ntot;
     p.nt = e->nt;
     p.ntiles = e->ntiles;
@@ -332,10 +333,28 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.nstages = e->stem_stages;
     p.acc_stride = e->stem_acc_stride;
     p.tmem_cols = e->stem_tmem_cols;
-    const long long items = (long long)e->G * p.mtiles * p.ntiles;
-    const int grid = (int)std::min<long long>(e->sms, items);
     ProfScope _ps(e, C6_KIND_STEM, st);
-    stem_tc_kernel<<<grid, kStemThreads, e->stem_smem, st>>>(p);
+    if (e->stem_pair) {
+      const long long items = (long long)e->G * (p.mtiles / 2) * p.ntiles;
+      const int grid = 2 * (int)std::min<long long>(e->sms / 2, items);
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3((unsigned)grid);
+      cfg.blockDim = dim3(kStemThreads);
+      cfg.dynamicSmemBytes = (size_t)e->stem_smem;
+      cfg.stream = st;
+      cudaLaunchAttribute attr{};
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      cudaLaunchKernelEx(&cfg, stem_tc_kernel<true>, p);
+    } else {
+      const long long items = (long long)e->G * p.mtiles * p.ntiles;
+      const int grid = (int)std::min<long long>(e->sms, items);
+      stem_tc_kernel<false><<<grid, kStemThreads, e->stem_smem, st>>>(p);
+    }
     C6_LAUNCHED(e, "stem_tc_kernel");
   }
   const int last = a.stop_layer >= 0 ? a.stop_layer : e->L - 1;
@@ -602,8 +621,12 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     e->nt = c1 * cpt;
     e->ntiles = (e->cells + cpt - 1) / cpt;
     e->ntot = e->ntiles * e->nt;
-    const int sstage = 4 * 128 * 16 + 4 * e->nt * 16;
-    e->stem_stages = std::min(12, (kSmemLimit - 128 - kStemSmemHeader) / sstage);
+    // CTA pairs (each stages half of the Toeplitz rows, 64 K per stage) when at least one pair exists
+    e->stem_pair = e->sms >= 2 ? 1 : 0;
+    e->stem_kcs = e->stem_pair ? 8 : 4;
+    e->kc0 = round_up(e->kc0, e->stem_kcs);
+    const int sstage = e->stem_kcs * 128 * 16 + e->stem_kcs * (e->stem_pair ? e->nt / 2 : e->nt) * 16;
+    e->stem_stages = std::min(kStemMaxStages, (kSmemLimit - 128 - kStemSmemHeader) / sstage);
     e->stem_smem = 128 + kStemSmemHeader + e->stem_stages * sstage;
     e->stem_acc_stride = pow2_ceil(e->nt);
     e->stem_tmem_cols = 2 * e->stem_acc_stride;
@@ -683,7 +706,8 @@ int c6_create(const C6Desc* d, C6Engine** out) {
         cudaFuncSetAttribute(conv_tc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
         cudaFuncSetAttribute(conv_tc_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
         cudaFuncSetAttribute(conv_tc_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(stem_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+        cudaFuncSetAttribute(stem_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(stem_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
       return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   } else {
     size_t max_smem = 0;

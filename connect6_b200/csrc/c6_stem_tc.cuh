@@ -29,14 +29,15 @@ struct StemTcParams {
   int* status;
   long long plane_rows;
   long long mrows;     // rows per X plane (= G * mrows_per_group)
-  int mrows_per_group; // multiple of 128
+  int mrows_per_group; // multiple of 128 (256 in pair mode)
   int front;
   int group_pos;       // positions reserved per group in the activation planes
-  int kc;              // K chunks (multiple of 4)
+  int kc;              // K chunks (multiple of kcs)
+  int kcs;             // K chunks per pipeline stage: 4 or 8
   int ntot;            // rows per T plane (= ntiles * nt)
   int nt;              // outputs per tile (multiple of 32, <= 256)
   int ntiles;
-  int mtiles;          // per group
+  int mtiles;          // per group (even in pair mode)
   int groups;
   int c1;              // padded stem output channels
   int bsize, wp, slots, nboards;
@@ -46,27 +47,42 @@ struct StemTcParams {
 
 constexpr int kStemThreads = 320;  // producer warp, MMA warp, eight epilogue warps
 constexpr int kStemSmemHeader = 2048;
+constexpr int kStemMaxStages = 12;
 
+// PAIR = true: clusters of two CTAs share one 256-board x NT-output tile through cta_group::2 MMAs.
+// CTA r stages the X rows of boards [128 r, 128 r + 128) and rows [r NT/2, (r+1) NT/2) of the
+// Toeplitz tile, so every byte of T is fetched once per 256 boards instead of once per 128: the
+// kernel is fed from L2 and this cuts its traffic by a third.
+template <bool PAIR>
 __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  // barrier slots: [0,12) full, [12,24) empty, 25-26 acc full, 27-28 acc empty, 29 drain
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 516);
   volatile int* never_flag = reinterpret_cast<volatile int*>(smem + 520);
-  float* s_bias = reinterpret_cast<float*>(smem + 640);  // [groups? no: one group per item] c1 floats, reloaded per item
+  float* s_bias = reinterpret_cast<float*>(smem + 640);  // 0.5 * bias of all groups when that fits
   uint8_t* s_stage = smem + kStemSmemHeader;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = PAIR ? tc::cluster_ctarank() : 0u;
+  const bool leader = crank == 0;
+  const int nloc = PAIR ? p.nt / 2 : p.nt;           // Toeplitz rows this CTA stages
   const uint32_t a_plane = 128u * 16u;
-  const uint32_t b_plane = (uint32_t)p.nt * 16u;
-  const uint32_t a_bytes = 4u * a_plane, b_bytes = 4u * b_plane;
-  const uint32_t stage_bytes = a_bytes + b_bytes;  // multiples of 128 by construction
-  const int ksteps = p.kc >> 2;
+  const uint32_t b_plane = (uint32_t)nloc * 16u;
+  const uint32_t a_bytes = (uint32_t)p.kcs * a_plane, b_bytes = (uint32_t)p.kcs * b_plane;
+  const uint32_t stage_bytes = a_bytes + b_bytes;    // multiples of 128 by construction
+  const int ksteps = p.kc / p.kcs;
 
-  const long long items = (long long)p.groups * p.mtiles * p.ntiles;
-  const long long i_begin = items * blockIdx.x / gridDim.x;
-  const long long i_end = items * (blockIdx.x + 1) / gridDim.x;
+  // work items: (group, board tile, output tile), output tile fastest; in pair mode a pair owns a
+  // range of (group, board-tile PAIR, output tile) items and CTA r takes board tile 2*mp + r
+  const int mt_items = PAIR ? p.mtiles / 2 : p.mtiles;
+  const long long items = (long long)p.groups * mt_items * p.ntiles;
+  const long long workers = PAIR ? gridDim.x / 2 : gridDim.x;
+  const long long me = PAIR ? blockIdx.x / 2 : blockIdx.x;
+  const long long i_begin = items * me / workers;
+  const long long i_end = items * (me + 1) / workers;
 
   const uint32_t bar0 = tc::smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
@@ -76,13 +92,14 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
   const uint32_t bar_drain = bar0 + 8u * 29;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 12; ++s) {
-      tc::mbar_init(bar_full(s), 1);
+    const uint32_t both = (PAIR && leader) ? 2u : 1u;   // leader: the peer's relay arrives too
+    for (int s = 0; s < kStemMaxStages; ++s) {
+      tc::mbar_init(bar_full(s), both);
       tc::mbar_init(bar_empty(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(bar_tfull(a), 1);
-      tc::mbar_init(bar_tempty(a), 8);
+      tc::mbar_init(bar_tempty(a), 8 * both);
     }
     tc::mbar_init(bar_drain, 1);
     *abort_flag = 0;
@@ -90,32 +107,43 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     tc::fence_barrier_init();
   }
   if (warp == 1) {
-    tc::tmem_alloc(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
-    tc::tmem_relinquish();
+    if (PAIR) {
+      tc::tmem_alloc2(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+      tc::tmem_relinquish2();
+    } else {
+      tc::tmem_alloc(tc::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+      tc::tmem_relinquish();
+    }
   }
   if (warp >= 2) {
     for (int i = threadIdx.x - 64; i < p.groups * p.c1 && i < 320; i += 256) s_bias[i] = 0.5f * p.bias[i];  // h = x/2
   }
   tc::fence_before_sync();
-  __syncthreads();
+  if (PAIR) tc::cluster_sync(); else __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool bias_in_smem = p.groups * p.c1 <= 320;
 
+  auto decode = [&](long long item, int& g, int& mt, int& nt_i) {
+    nt_i = (int)(item % p.ntiles);
+    const long long gm = item / p.ntiles;
+    const int mp = (int)(gm % mt_items);
+    g = (int)(gm / mt_items);
+    mt = PAIR ? 2 * mp + (int)crank : mp;
+  };
+
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
-    // Lane 0 waits for the stage and arms its barrier; lanes 0-7 then issue the stage's eight bulk
+    // Lane 0 waits for the stage and arms its barrier; lanes 0 .. 2*kcs-1 then issue the stage's bulk
     // copies in parallel (issuing a copy costs a thread a few hundred clocks).
     bool ok = true;
     int s = 0;
     uint32_t ph = 0;
     for (long long item = i_begin; item < i_end && ok; ++item) {
-      const int nt_i = (int)(item % p.ntiles);
-      const long long gm = item / p.ntiles;
-      const int mt = (int)(gm % p.mtiles);
-      const int g = (int)(gm / p.mtiles);
+      int g, mt, nt_i;
+      decode(item, g, mt, nt_i);
       const uint4* xa = p.xk + (long long)g * p.mrows_per_group + (long long)mt * 128;
-      const uint4* wb = p.wt + (size_t)g * p.kc * p.ntot + (size_t)nt_i * p.nt;
+      const uint4* wb = p.wt + (size_t)g * p.kc * p.ntot + (size_t)nt_i * p.nt + (size_t)crank * nloc;
       for (int ks = 0; ks < ksteps; ++ks) {
         int got = 1;
         if (lane == 0) {
@@ -130,12 +158,12 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
           break;
         }
         const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
-        if (lane < 4) {
-          const int kc = ks * 4 + lane;
+        if (lane < p.kcs) {
+          const int kc = ks * p.kcs + lane;
           tc::bulk_g2s(dst + lane * a_plane, xa + (size_t)kc * p.mrows, a_plane, bar_full(s));
-        } else if (lane < 8) {
-          const int kc = ks * 4 + (lane - 4);
-          tc::bulk_g2s(dst + a_bytes + (lane - 4) * b_plane, wb + (size_t)kc * p.ntot, b_plane, bar_full(s));
+        } else if (lane < 2 * p.kcs) {
+          const int kc = ks * p.kcs + (lane - p.kcs);
+          tc::bulk_g2s(dst + a_bytes + (lane - p.kcs) * b_plane, wb + (size_t)kc * p.ntot, b_plane, bar_full(s));
         }
         if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
@@ -149,10 +177,10 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 && leader) {
     // ------------------------------ MMA issuer ------------------------------
     // Warp-uniform loop, one elected lane issues (see the k x k kernel for the reasoning).
-    const uint32_t idesc = tc::make_idesc_bf16(128, p.nt);
+    const uint32_t idesc = tc::make_idesc_bf16(PAIR ? 256 : 128, p.nt);
     const uint32_t desc_hi = (uint32_t)(tc::make_desc(0, 0, 128u) >> 32);
     const uint32_t a_lbo_field = (a_plane >> 4) << 16, b_lbo_field = (b_plane >> 4) << 16;
     const uint32_t stage0_lo = tc::smem_u32(s_stage) >> 4;
@@ -182,26 +210,50 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
         const uint32_t a_lo = (stage0_lo + (uint32_t)s * stage_rows) | a_lbo_field;
         const uint32_t b_lo = (stage0_lo + (uint32_t)s * stage_rows + (a_bytes >> 4)) | b_lbo_field;
         if (tc::elect_one()) {
-#pragma unroll
-          for (int j = 0; j < 2; ++j)
-            tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + 2u * j * (a_plane >> 4)),
-                         ((uint64_t)desc_hi << 32) | (b_lo + 2u * j * (b_plane >> 4)), idesc,
-                         (ks | j) != 0 ? 1u : 0u);
-          tc::mma_commit(bar_empty(s));
-          if (ks == ksteps - 1) tc::mma_commit(bar_tfull(acc));
+          for (int j = 0; j < p.kcs / 2; ++j) {
+            const uint64_t ad = ((uint64_t)desc_hi << 32) | (a_lo + 2u * j * (a_plane >> 4));
+            const uint64_t bd = ((uint64_t)desc_hi << 32) | (b_lo + 2u * j * (b_plane >> 4));
+            if (PAIR) tc::mma_bf16_pair(d_tmem, ad, bd, idesc, (ks | j) != 0 ? 1u : 0u);
+            else tc::mma_bf16(d_tmem, ad, bd, idesc, (ks | j) != 0 ? 1u : 0u);
+          }
+          if (PAIR) {
+            tc::mma_commit_pair_both(bar_empty(s));
+            if (ks == ksteps - 1) tc::mma_commit_pair_both(bar_tfull(acc));
+          } else {
+            tc::mma_commit(bar_empty(s));
+            if (ks == ksteps - 1) tc::mma_commit(bar_tfull(acc));
+          }
         }
         __syncwarp();
         if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
     }
     if (lane == 0) {
-      tc::mma_commit(bar_drain);
+      if (PAIR) tc::mma_commit_pair_local(bar_drain); else tc::mma_commit(bar_drain);
       if (!tc::mbar_wait(bar_drain, 0, never_flag)) {
         atomicOr(p.status, kStatWaitDrain);
         *abort_flag = 1;
       }
     }
     __syncwarp();
+  } else if (PAIR && warp == 1) {
+    // ------------------------------ peer relay ------------------------------
+    // Forwards every completed "stage full" phase of this CTA to the leader's barrier.
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (long long item = i_begin; item < i_end && ok; ++item) {
+      for (int ks = 0; ks < ksteps; ++ks) {
+        if (!tc::mbar_wait_warp(bar_full(s), ph, abort_flag, 0)) {
+          if (lane == 0) atomicOr(p.status, kStatWaitFull);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        if (lane == 0) tc::mbar_arrive_cluster(tc::mapa(bar_full(s), 0));
+        if (++s == p.nstages) { s = 0; ph ^= 1u; }
+      }
+    }
   } else if (warp >= 2) {
     // ------------------------------ epilogue ------------------------------
     // Eight warps; the two warps of a TMEM lane quadrant alternate over 16-column units.  A unit is
@@ -216,11 +268,9 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     int tcount = 0;
     for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
       const int acc = tcount & 1;
-      const int nt_i = (int)(item % p.ntiles);
-      const long long gm = item / p.ntiles;
-      const int mt = (int)(gm % p.mtiles);
-      const int g = (int)(gm / p.mtiles);
-      if (!tc::mbar_wait(bar_tfull(acc), (tcount >> 1) & 1u, abort_flag)) {
+      int g, mt, nt_i;
+      decode(item, g, mt, nt_i);
+      if (!tc::mbar_wait(bar_tfull(acc), (tcount >> 1) & 1u, abort_flag, 40)) {
         if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
         *abort_flag = 1;
         ok = false;
@@ -261,16 +311,18 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       }
       tc::fence_before_sync();
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(bar_tempty(acc));
+      if (lane == 0) {
+        if (PAIR) tc::mbar_arrive_cluster(tc::mapa(bar_tempty(acc), 0)); else tc::mbar_arrive(bar_tempty(acc));
+      }
     }
   }
 
   tc::fence_before_sync();
-  __syncthreads();
+  if (PAIR) tc::cluster_sync(); else __syncthreads();
   if (warp == 1) {
     __syncwarp();
     tc::fence_after_sync();
-    tc::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    if (PAIR) tc::tmem_dealloc2(tmem_base, (uint32_t)p.tmem_cols); else tc::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
 }
 

@@ -8,8 +8,9 @@
 namespace c6 {
 
 // ------------------------------------------------------------------------------------------------
-// Input packing for the tensor-core stem: x [boards,3,n,n] (fp32 or bf16, NCHW) -> K-chunk planes
-// xk[kc][mrows] (16-byte rows of 8 bf16, k = ci*n*n + view cell).  A board with orientation
+// Input packing for the tensor-core stem: x [boards,3,n,n] (fp32 or bf16, NCHW) -> 16-byte rows of
+// 8 bf16 (k = ci*n*n + view cell) laid out [board tile of 128][K chunk][128 boards], so that all K
+// chunks of one pipeline stage of one board tile are contiguous and travel in ONE bulk copy.  A board with orientation
 // `phase` is presented as view.flat[j] = x.flat[d4_inverse(j)] (connect6/train.py:222-230).
 // Grid: (ceil(kc*nb/256), G); one thread per (board, chunk).
 // ------------------------------------------------------------------------------------------------
@@ -45,7 +46,8 @@ __global__ void pack_stem_input_kernel(const void* __restrict__ x, int x_bf16,
   o.y = pack_bf16x2(v[2], v[3]);
   o.z = pack_bf16x2(v[4], v[5]);
   o.w = pack_bf16x2(v[6], v[7]);
-  xk[(size_t)c * mrows + (size_t)g * mrows_per_group + t] = o;
+  const size_t brow = (size_t)g * mrows_per_group + t;   // board row over all groups
+  xk[((brow >> 7) * kc + c) * 128 + (brow & 127)] = o;
 }
 
 // fp32 mode: x -> fp32 NCHW copy in view orientation, boards of all groups laid out [g][t].
@@ -128,9 +130,11 @@ __global__ void pack_conv_weights_pair_kernel(const float* __restrict__ w, uint4
   out[idx] = o;
 }
 
-// Stem -> Toeplitz planes wt[kc][ntot] (row o = cell_out*c1 + co, element e: k = kc*8+e).
+// Stem -> Toeplitz rows (row o = cell_out*c1 + co, element e: k = kc*8+e) laid out
+// [output tile of nt][half][K chunk][nt/halves rows]: the K chunks of one pipeline stage of one
+// (tile, half) are contiguous.  halves = 2 when CTA pairs split the tile's rows, else 1.
 __global__ void pack_stem_toeplitz_kernel(const float* __restrict__ w, uint4* __restrict__ out,
-                                          int cout, int kside, int n, int c1, int kc, int ntot) {
+                                          int cout, int kside, int n, int c1, int kc, int ntot, int nt, int halves) {
   const long long total = (long long)kc * ntot;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -159,7 +163,9 @@ __global__ void pack_stem_toeplitz_kernel(const float* __restrict__ w, uint4* __
   q.y = pack_bf16x2(v[2], v[3]);
   q.z = pack_bf16x2(v[4], v[5]);
   q.w = pack_bf16x2(v[6], v[7]);
-  out[idx] = q;
+  const int tile = o / nt, ol = o - tile * nt, nloc = nt / halves;
+  const int h = ol / nloc, rr = ol - h * nloc;
+  out[(((size_t)tile * halves + h) * kc + c) * nloc + rr] = q;
 }
 
 // dst[i] = i < n_src ? src[i] : 0 for i < n_dst (bias / head vectors padded with zeros)

@@ -313,6 +313,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.bias = e->bias[0];
     p.out = e->act[0];
     p.status = e->status_dev;
+    p.wait_cycles = e->wait_counters ? e->wait_dev : nullptr;
     p.plane_rows = e->plane_rows;
     p.mrows = e->mrows;
     p.mrows_per_group = g.mrows_per_group;
@@ -760,7 +761,7 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
     if (layer == 0) {
       const long long total = (long long)e->kc0 * e->ntot;
       pack_stem_toeplitz_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-          w, e->wt + (size_t)group * e->kc0 * e->ntot, p.cout, p.k, e->n, p.cout_p, e->kc0, e->ntot);
+          w, e->wt + (size_t)group * e->kc0 * e->ntot, p.cout, p.k, e->n, p.cout_p, e->kc0, e->ntot, e->nt, e->stem_pair ? 2 : 1);
       C6_LAUNCHED(e, "pack_stem_toeplitz_kernel");
     } else {
       const long long total = (long long)p.w_rows_per_group;

@@ -9,8 +9,9 @@
 // at run time; T is expanded once per weight update.  The product needs 3*n*n MACs per output
 // (1083 for n = 19) instead of the 3*k0*k0 = 1587 of the zero-padded definition.
 //
-// Operands use the same K-major no-swizzle chunk planes as the 3x3 kernel:
-//   X planes [K/8][Mrows] of 16-byte rows (row = board),  T planes [K/8][Ntot] (row = output).
+// Operands are K-major no-swizzle core-matrix rows (16 bytes = 8 bf16 along K) as in the 3x3
+// kernel, stored tile-major in HBM so that one pipeline stage of one tile is one contiguous block:
+//   X [board tile of 128][K/8][128 boards],   T [output tile][half][K/8][rows of that half].
 // Tile: 128 boards x NT outputs (NT = C1 * cells-per-tile <= 256), K walked 32 at a time
 // through a ring of bulk-copy stages.  The epilogue adds bias, applies SiLU and scatters each
 // 32-channel group to the padded activation planes the next layer reads.
@@ -22,11 +23,12 @@
 namespace c6 {
 
 struct StemTcParams {
-  const uint4* xk;    // [kc][mrows] input planes
-  const uint4* wt;    // [G][kc][ntot] Toeplitz planes
+  const uint4* xk;    // [board tile][kc][128] input rows
+  const uint4* wt;    // [G][output tile][half][kc][nt/halves] Toeplitz rows
   const float* bias;  // [G][c1]
   uint4* out;         // activation planes [c1/8][plane_rows]
   int* status;
+  long long* wait_cycles;  // nullable [8]: slots 1,2,4,5 as in the k x k kernel (MMA warp of CTA 0)
   long long plane_rows;
   long long mrows;     // rows per X plane (= G * mrows_per_group)
   int mrows_per_group; // multiple of 128 (256 in pair mode)
@@ -134,16 +136,17 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
-    // Lane 0 waits for the stage and arms its barrier; lanes 0 .. 2*kcs-1 then issue the stage's bulk
-    // copies in parallel (issuing a copy costs a thread a few hundred clocks).
+    // Lane 0 waits for the stage and arms its barrier; lanes 0 and 1 then issue the stage's two bulk
+    // copies (the operands are stored tile-major so that a stage is one contiguous block each).
     bool ok = true;
     int s = 0;
     uint32_t ph = 0;
     for (long long item = i_begin; item < i_end && ok; ++item) {
       int g, mt, nt_i;
       decode(item, g, mt, nt_i);
-      const uint4* xa = p.xk + (long long)g * p.mrows_per_group + (long long)mt * 128;
-      const uint4* wb = p.wt + (size_t)g * p.kc * p.ntot + (size_t)nt_i * p.nt + (size_t)crank * nloc;
+      // tile-major operands: [board tile][K chunk][128] and [group][output tile][half][K chunk][nloc]
+      const uint4* xa = p.xk + ((size_t)g * p.mtiles + mt) * p.kc * 128;
+      const uint4* wb = p.wt + (size_t)g * p.kc * p.ntot + (((size_t)nt_i * (PAIR ? 2 : 1) + crank) * p.kc) * nloc;
       for (int ks = 0; ks < ksteps; ++ks) {
         int got = 1;
         if (lane == 0) {
@@ -158,12 +161,10 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
           break;
         }
         const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
-        if (lane < p.kcs) {
-          const int kc = ks * p.kcs + lane;
-          tc::bulk_g2s(dst + lane * a_plane, xa + (size_t)kc * p.mrows, a_plane, bar_full(s));
-        } else if (lane < 2 * p.kcs) {
-          const int kc = ks * p.kcs + (lane - p.kcs);
-          tc::bulk_g2s(dst + a_bytes + (lane - p.kcs) * b_plane, wb + (size_t)kc * p.ntot, b_plane, bar_full(s));
+        if (lane == 0) {
+          tc::bulk_g2s(dst, xa + (size_t)ks * p.kcs * 128, a_bytes, bar_full(s));
+        } else if (lane == 1) {
+          tc::bulk_g2s(dst + a_bytes, wb + (size_t)ks * p.kcs * nloc, b_bytes, bar_full(s));
         }
         if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
@@ -189,9 +190,15 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     int s = 0;
     uint32_t ph = 0;
     int tcount = 0;
+    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
+    long long wait_full = 0, wait_acc = 0, issue_clk = 0;
+    const long long loop_t0 = clock64();
     for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
       const int acc = tcount & 1;
-      if (!tc::mbar_wait(bar_tempty(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag)) {
+      const long long w0 = timing ? clock64() : 0;
+      const bool got_acc = tc::mbar_wait(bar_tempty(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag);
+      if (timing) wait_acc += clock64() - w0;
+      if (!got_acc) {
         if (lane == 0) atomicOr(p.status, kStatWaitTmemEmpty);
         *abort_flag = 1;
         ok = false;
@@ -200,13 +207,17 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       tc::fence_after_sync();
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
       for (int ks = 0; ks < ksteps; ++ks) {
-        if (!tc::mbar_wait(bar_full(s), ph, abort_flag)) {
+        const long long w1 = timing ? clock64() : 0;
+        const bool got = tc::mbar_wait(bar_full(s), ph, abort_flag);
+        if (timing) wait_full += clock64() - w1;
+        if (!got) {
           if (lane == 0) atomicOr(p.status, kStatWaitFull);
           *abort_flag = 1;
           ok = false;
           break;
         }
         tc::fence_after_sync();
+        const long long w2 = timing ? clock64() : 0;
         const uint32_t a_lo = (stage0_lo + (uint32_t)s * stage_rows) | a_lbo_field;
         const uint32_t b_lo = (stage0_lo + (uint32_t)s * stage_rows + (a_bytes >> 4)) | b_lbo_field;
         if (tc::elect_one()) {
@@ -225,8 +236,15 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
           }
         }
         __syncwarp();
+        if (timing) issue_clk += clock64() - w2;
         if (++s == p.nstages) { s = 0; ph ^= 1u; }
       }
+    }
+    if (timing && lane == 0) {
+      p.wait_cycles[1] += wait_full;
+      p.wait_cycles[2] += wait_acc;
+      p.wait_cycles[4] += issue_clk;
+      p.wait_cycles[5] += clock64() - loop_t0;
     }
     if (lane == 0) {
       if (PAIR) tc::mma_commit_pair_local(bar_drain); else tc::mma_commit(bar_drain);
@@ -282,37 +300,48 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       const long long board_row = (long long)p.front + (long long)g * p.group_pos + (long long)board * p.slots;
       const float* gbias = p.bias + (size_t)g * p.c1;
-      for (int u = half; u < nunits; u += 2) {
-        const int o = nt_i * p.nt + u * 16;  // first output column of this unit
-        const int cell = o / p.c1;
-        const int co0 = o - cell * p.c1;
-        uint32_t v[16];
-        tc::tmem_ld16(taddr + (uint32_t)(u * 16), v);
+      // this warp's units: half, half+2, ...; four are fetched from TMEM per wait so that their
+      // latencies overlap, and the accumulator is released as soon as the last fetch has landed
+      for (int u0 = half; u0 < nunits; u0 += 8) {
+        uint32_t v[4][16];
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (u0 + 2 * b < nunits) tc::tmem_ld16(taddr + (uint32_t)((u0 + 2 * b) * 16), v[b]);
         tc::tmem_wait_ld();
-        if (bvalid && cell < cells) {
-          const int r = cell / p.bsize, c = cell - r * p.bsize;
-          uint4* dst = p.out + (size_t)(co0 >> 3) * p.plane_rows + board_row + r * p.wp + c;
-          float y[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float hb = bias_in_smem ? s_bias[g * p.c1 + co0 + j] : 0.5f * gbias[co0 + j];
-            y[j] = silu_from_half(fmaf(__uint_as_float(v[j]), 0.5f, hb));
-          }
-#pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            uint4 q;
-            q.x = pack_bf16x2(y[8 * k + 0], y[8 * k + 1]);
-            q.y = pack_bf16x2(y[8 * k + 2], y[8 * k + 3]);
-            q.z = pack_bf16x2(y[8 * k + 4], y[8 * k + 5]);
-            q.w = pack_bf16x2(y[8 * k + 6], y[8 * k + 7]);
-            dst[(size_t)k * p.plane_rows] = q;
+        if (u0 + 8 >= nunits) {
+          tc::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if (PAIR) tc::mbar_arrive_cluster(tc::mapa(bar_tempty(acc), 0)); else tc::mbar_arrive(bar_tempty(acc));
           }
         }
-      }
-      tc::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if (PAIR) tc::mbar_arrive_cluster(tc::mapa(bar_tempty(acc), 0)); else tc::mbar_arrive(bar_tempty(acc));
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int u = u0 + 2 * b;
+          if (u >= nunits) continue;
+          const int o = nt_i * p.nt + u * 16;  // first output column of this unit
+          const int cell = o / p.c1;
+          const int co0 = o - cell * p.c1;
+          if (bvalid && cell < cells) {
+            const int r = cell / p.bsize, c = cell - r * p.bsize;
+            uint4* dst = p.out + (size_t)(co0 >> 3) * p.plane_rows + board_row + r * p.wp + c;
+            float y[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float hb = bias_in_smem ? s_bias[g * p.c1 + co0 + j] : 0.5f * gbias[co0 + j];
+              y[j] = silu_from_half(fmaf(__uint_as_float(v[b][j]), 0.5f, hb));
+            }
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              uint4 q;
+              q.x = pack_bf16x2(y[8 * k + 0], y[8 * k + 1]);
+              q.y = pack_bf16x2(y[8 * k + 2], y[8 * k + 3]);
+              q.z = pack_bf16x2(y[8 * k + 4], y[8 * k + 5]);
+              q.w = pack_bf16x2(y[8 * k + 6], y[8 * k + 7]);
+              dst[(size_t)k * p.plane_rows] = q;
+            }
+          }
+        }
       }
     }
   }

@@ -270,6 +270,33 @@ def run_engine(args) -> None:
     e1.record()
     torch.cuda.synchronize(dev)
     e2e_ms = shard.max_over_ranks(e0.elapsed_time(e1), dev)
+    # the same step fed with the environment's raw int8 state (363 B/board instead of 4332 B)
+    hb = host_batches[0]
+    boards_h = (hb[:, 0] - hb[:, 1]).to(torch.int8).pin_memory()
+    player_h = torch.ones(BATCH, dtype=torch.int8).pin_memory()
+    stones_h = torch.where(hb[:, 2, 0, 0] > 0, 1, 2).to(torch.int8).pin_memory()
+    boards_d, player_d, stones_d = (torch.empty_like(t, device=dev) for t in (boards_h, player_h, stones_h))
+
+    def e2e_boards_step(i: int):
+        boards_d.copy_(boards_h, non_blocking=True)
+        player_d.copy_(player_h, non_blocking=True)
+        stones_d.copy_(stones_h, non_blocking=True)
+        a, lp, v, _ = model.selfplay_step_from_boards(boards_d, player_d, stones_d, temperature=1.0, seed=0xC6, offset=i,
+                                                      board_index0=first)
+        pipe.actions.copy_(a, non_blocking=True)
+        pipe.logprob.copy_(lp, non_blocking=True)
+        pipe.value.copy_(v, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+
+    for i in range(3):
+        e2e_boards_step(i)
+    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    b0.record()
+    for i in range(e2e_steps):
+        e2e_boards_step(i)
+    b1.record()
+    torch.cuda.synchronize(dev)
+    e2e_boards_ms = shard.max_over_ranks(b0.elapsed_time(b1), dev)
     h2d = host_batches[0].numel() * 4
     d2h = BATCH * (8 + 4 + 4)
 
@@ -324,6 +351,9 @@ def run_engine(args) -> None:
         "e2e": {"value": BATCH * world * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                 "api": "HostStepPipeline(PolicyValueNet.selfplay_step): pinned host fp32 planes in, pinned host results out, upload of step i+1 overlaps step i"},
+        "e2e_int8_boards": {"value": BATCH * world * e2e_steps / (e2e_boards_ms * 1e-3), "unit": UNIT,
+                            "h2d_bytes_per_step": int(boards_h.numel() + 2 * BATCH), "d2h_bytes_per_step": d2h,
+                            "api": "PolicyValueNet.selfplay_step_from_boards: pinned host int8 boards + player + stones_left in, host results out"},
         "gpu_launches": launches,
         "roofline": roof,
         "whole_step": {"tflops_per_gpu": whole_tflops, "frac_of_peak": whole_tflops / peak,

@@ -44,6 +44,7 @@ SIGNATURES = {
     "c6_forward": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp]),
     "c6_forward_noalloc": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp]),
     "c6_forward_step": (_i, [_vp, _vp, _i, _i64, _vp, _i, _f, _u64, _u64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "c6_forward_step_boards": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _f, _u64, _u64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "c6_forward_grouped": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _i, _vp]),
     "c6_sample_actions": (_i, [_vp, _vp, _i64, C.c_int32, _f, _u64, _u64, _i64, _vp, _vp, _vp]),
     "c6_mask_logits": (_i, [_vp, _vp, _i64, _f, _vp, _vp]),
@@ -55,6 +56,8 @@ SIGNATURES = {
     "c6_profile_read": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(_i64), _i]),
     "c6_debug_wait_cycles": (_i, [_vp, C.POINTER(_i64), _i]),
     "c6_debug_cta_times": (_i, [_vp, C.POINTER(_i64), _i]),
+    "c6_clear_status": (_i, [_vp]),
+    "c6_debug_expire_wait": (_i, [_vp, _vp]),
     "c6_status": (_i, [_vp, C.POINTER(_i)]),
     "c6_launch_count": (_i64, [_vp]),
     "c6_device_bytes": (_i64, [_vp]),

@@ -14,7 +14,7 @@ namespace c6 {
 // `phase` is presented as view.flat[j] = x.flat[d4_inverse(j)] (connect6/train.py:222-230).
 // Grid: (ceil(kc*nb/256), G); one thread per (board, chunk).
 // ------------------------------------------------------------------------------------------------
-__global__ void pack_stem_input_kernel(const void* __restrict__ x, int x_bf16,
+__global__ void pack_stem_input_kernel(const InputSrc in,
                                        const uint8_t* __restrict__ orient, uint4* __restrict__ xk,
                                        long long mrows, int mrows_per_group, int kc, int n,
                                        int nb,                 // boards of this pass per group
@@ -37,7 +37,7 @@ __global__ void pack_stem_input_kernel(const void* __restrict__ x, int x_bf16,
       const int ci = k / cells;
       int cell = k - ci * cells;
       if (phase) cell = d4_inverse(cell, n, phase);
-      val = load_x(x, x_bf16, src_board * ktot + (long long)ci * cells + cell);
+      val = input_value(in, src_board, ci, cell, cells);
     }
     v[j] = val;
   }
@@ -51,7 +51,7 @@ __global__ void pack_stem_input_kernel(const void* __restrict__ x, int x_bf16,
 }
 
 // fp32 mode: x -> fp32 NCHW copy in view orientation, boards of all groups laid out [g][t].
-__global__ void view_input_f32_kernel(const void* __restrict__ x, int x_bf16,
+__global__ void view_input_f32_kernel(const InputSrc in,
                                       const uint8_t* __restrict__ orient, float* __restrict__ out,
                                       int n, int nb, long long group_stride, long long board0) {
   const int g = blockIdx.y;
@@ -65,7 +65,7 @@ __global__ void view_input_f32_kernel(const void* __restrict__ x, int x_bf16,
   const int ci = k / cells;
   int cell = k - ci * cells;
   if (phase) cell = d4_inverse(cell, n, phase);
-  out[((size_t)g * nb + t) * ktot + k] = load_x(x, x_bf16, src_board * ktot + (long long)ci * cells + cell);
+  out[((size_t)g * nb + t) * ktot + k] = input_value(in, src_board, ci, cell, cells);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -193,8 +193,7 @@ struct FinishParams {
   const float* val_bias;   // [G] or null
   const float* logits_in;  // standalone: [B,A] logits
   const uint8_t* legal_in; // standalone: [B,A] legality
-  const void* x;           // engine path: network input, for occupancy (plane0|plane1)
-  int x_bf16;
+  InputSrc in;             // engine path: network input, for occupancy (plane0|plane1)
   const uint8_t* orient;
   long long x_group_stride; // boards between groups in x / outputs
   long long board0;         // first board of this pass inside a group
@@ -275,8 +274,7 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
       const int vr = view_cell / n, vc = view_cell - vr * n;
       raw = p.logit_raw[raw0 + vr * p.pitch + vc] + bp;
       const int orig_cell = (phase != 0 && !canon) ? d4_inverse(a, n, phase) : a;
-      const long long xb = ob * 3 * A;
-      legal = load_x(p.x, p.x_bf16, xb + orig_cell) == 0.f && load_x(p.x, p.x_bf16, xb + A + orig_cell) == 0.f;
+      legal = input_value(p.in, ob, 0, orig_cell, A) == 0.f && input_value(p.in, ob, 1, orig_cell, A) == 0.f;
       if (p.vmap) {
         const int r = a / n, c = a - r * n;
         vsum += p.vmap[raw0 + r * p.pitch + c];
@@ -399,6 +397,25 @@ __global__ void network_input_kernel(const int8_t* __restrict__ boards, const in
   o[0] = v == me ? 1.f : 0.f;
   o[cells] = v == -me ? 1.f : 0.f;
   o[2 * cells] = stones_left[b] == 1 ? 1.f : 0.f;
+}
+
+// Self-test of the bounded-wait path: waits on an mbarrier that nobody arrives on, with a short
+// limit, then records the same status bit a real kernel would and returns normally.
+__global__ void expire_wait_kernel(int* status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    const uint32_t b = static_cast<uint32_t>(__cvta_generic_to_shared(&bar));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b) : "memory");
+    const long long t0 = clock64();
+    bool done = false;
+    while (!done && clock64() - t0 < limit_cycles) {
+      uint32_t ok;
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                   : "=r"(ok) : "r"(b) : "memory");
+      done = ok != 0;
+    }
+    if (!done) atomicOr(status, kStatWaitFull);
+  }
 }
 
 // Debug aid: activation planes -> fp32 NCHW [G*nb, c, n, n]

@@ -90,4 +90,25 @@ __device__ __forceinline__ float load_x(const void* x, int x_bf16, int64_t idx) 
                 : reinterpret_cast<const float*>(x)[idx];
 }
 
+// Where the network input comes from: float planes [B,3,n,n] (the reference's model(x) argument), or
+// the environment's raw state -- int8 boards (+1/-1/0), current player, stones left, optionally
+// gathered through an index vector -- from which the three planes are derived on the fly
+// (connect6/vector_env.py:196-218, gathers of connect6/train.py:793).
+struct InputSrc {
+  const void* x;             // planes, or null in board mode
+  int x_bf16;
+  const int8_t* boards;      // [envs, n, n]
+  const int8_t* player;      // [envs]
+  const int8_t* stones_left; // [envs]
+  const long long* index;    // nullable [B]: board b of the batch is environment index[b]
+};
+
+__device__ __forceinline__ float input_value(const InputSrc& in, long long b, int ci, int cell, int cells) {
+  if (in.boards == nullptr) return load_x(in.x, in.x_bf16, (b * 3 + ci) * cells + cell);
+  const long long e = in.index ? in.index[b] : b;
+  if (ci == 2) return in.stones_left[e] == 1 ? 1.f : 0.f;
+  const int v = in.boards[e * cells + cell], me = in.player[e];
+  return (ci == 0 ? v == me : v == -me) ? 1.f : 0.f;
+}
+
 }  // namespace c6

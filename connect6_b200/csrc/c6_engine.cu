@@ -234,9 +234,15 @@ static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
 constexpr int kNoAllocMaxDevices = 64;
 static float* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {nullptr};
 
+InputSrc input_of(const struct RunArgs& a);
+
 struct RunArgs {
   const void* x = nullptr;
   int x_bf16 = 0;
+  const int8_t* boards = nullptr;       // board-input mode (x stays null)
+  const int8_t* player = nullptr;
+  const int8_t* stones_left = nullptr;
+  const long long* index = nullptr;
   long long T = 0;  // boards per group
   const uint8_t* orient = nullptr;
   float* logits = nullptr;
@@ -252,6 +258,17 @@ struct RunArgs {
   float* layer_out = nullptr;  // debug: fp32 NCHW output of stop_layer
 };
 
+InputSrc input_of(const RunArgs& a) {
+  InputSrc in{};
+  in.x = a.x;
+  in.x_bf16 = a.x_bf16;
+  in.boards = a.boards;
+  in.player = a.player;
+  in.stones_left = a.stones_left;
+  in.index = a.index;
+  return in;
+}
+
 int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long group_stride,
                   int board_stride, int pitch, cudaStream_t st) {
   FinishParams f{};
@@ -262,8 +279,7 @@ int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long
   f.pitch = pitch;
   f.pol_bias = e->pol_bias;
   f.val_bias = e->val_bias;
-  f.x = a.x;
-  f.x_bf16 = a.x_bf16;
+  f.in = input_of(a);
   f.orient = a.orient;
   f.x_group_stride = a.T;
   f.board0 = t0;
@@ -302,7 +318,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     const long long total = (long long)e->kc0 * nb;
     ProfScope _ps(e, C6_KIND_PACK, st);
     pack_stem_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
-        a.x, a.x_bf16, a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->n, nb, a.T, t0);
+        input_of(a), a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->n, nb, a.T, t0);
     C6_LAUNCHED(e, "pack_stem_input_kernel");
   }
   int cur = 0;
@@ -455,7 +471,7 @@ int run_pass_fp32(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     const long long total = (long long)nb * 3 * e->cells;
     ProfScope _ps(e, C6_KIND_PACK, st);
     view_input_f32_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
-        a.x, a.x_bf16, a.orient, e->f32x, e->n, nb, a.T, t0);
+        input_of(a), a.orient, e->f32x, e->n, nb, a.T, t0);
     C6_LAUNCHED(e, "view_input_f32_kernel");
   }
   const float* in = e->f32x;
@@ -492,7 +508,7 @@ int run(C6Engine* e, const RunArgs& a, void* stream) {
   if (!e) return C6_ERR_ARG;
   if (a.T < 0) return fail(e, C6_ERR_ARG, "negative board count");
   if (a.T == 0) return C6_OK;
-  if (!a.x) return fail(e, C6_ERR_ARG, "x is null");
+  if (!a.x && !a.boards) return fail(e, C6_ERR_ARG, "x is null");
   for (size_t i = 0; i < e->have.size(); ++i)
     if (!e->have[i]) return fail(e, C6_ERR_WEIGHTS, "forward before every layer and head of every group received weights");
   C6_CUDA(e, cudaSetDevice(e->device));
@@ -843,6 +859,34 @@ int c6_forward_step(C6Engine* e, const void* x, int x_dtype, int64_t B, const ui
   return run(e, a, stream);
 }
 
+int c6_forward_step_boards(C6Engine* e, const int8_t* boards, const int8_t* current_player, const int8_t* stones_left,
+                           const int64_t* index, int64_t B, const uint8_t* orient, int flags, float temperature,
+                           uint64_t seed, uint64_t offset, int64_t board_index0, int64_t* action, float* logprob,
+                           float* value, float* masked_logits, void* stream) {
+  if (!e) return C6_ERR_ARG;
+  if (e->G != 1) return fail(e, C6_ERR_ARG, "c6_forward_step_boards needs an engine with groups == 1");
+  if (B > 0 && (!boards || !current_player || !stones_left)) return fail(e, C6_ERR_ARG, "board state pointer is null");
+  if (B > 0 && !action) return fail(e, C6_ERR_ARG, "action pointer is null");
+  RunArgs a;
+  a.boards = boards;
+  a.player = current_player;
+  a.stones_left = stones_left;
+  a.index = reinterpret_cast<const long long*>(index);
+  a.T = B;
+  a.orient = orient;
+  a.logits = masked_logits;
+  a.value = value;
+  a.flags = flags | C6_FLAG_MASK_LOGITS;
+  a.do_sample = 1;
+  a.temperature = temperature;
+  a.seed = seed;
+  a.offset = offset;
+  a.board_index0 = board_index0;
+  a.action = reinterpret_cast<long long*>(action);
+  a.logprob = logprob;
+  return run(e, a, stream);
+}
+
 int c6_forward_grouped(C6Engine* e, const void* x, int x_dtype, int64_t T, float* logits, float* value, int flags,
                        void* stream) {
   if (!e) return C6_ERR_ARG;
@@ -896,8 +940,10 @@ int c6_forward_noalloc(C6Engine* e, const void* x, int x_dtype, int64_t B, const
   // every buffer below is fully written before it is read, so nothing has to be cleared
   {
     const long long total = (long long)nb * 3 * e->cells;
-    view_input_f32_kernel<<<dim3((unsigned)((total + 255) / 256), 1), 256, 0, st>>>(x, x_dtype == C6_X_BF16, orient, xview,
-                                                                                   e->n, nb, B, 0);
+    InputSrc in{};
+    in.x = x;
+    in.x_bf16 = x_dtype == C6_X_BF16;
+    view_input_f32_kernel<<<dim3((unsigned)((total + 255) / 256), 1), 256, 0, st>>>(in, orient, xview, e->n, nb, B, 0);
     C6_LAUNCHED(e, "view_input_f32_kernel");
   }
   const float* in = xview;
@@ -922,8 +968,8 @@ int c6_forward_noalloc(C6Engine* e, const void* x, int x_dtype, int64_t B, const
   f.pitch = e->n;
   f.pol_bias = e->pol_bias;
   f.val_bias = e->val_bias;
-  f.x = x;
-  f.x_bf16 = x_dtype == C6_X_BF16;
+  f.in.x = x;
+  f.in.x_bf16 = x_dtype == C6_X_BF16;
   f.orient = orient;
   f.x_group_stride = B;
   f.board0 = 0;
@@ -1067,6 +1113,22 @@ int c6_debug_cta_times(C6Engine* e, int64_t* out, int n_ctas) {
   if (!e || !out || n_ctas < 1 || n_ctas > 512) return C6_ERR_ARG;
   C6_CUDA(e, cudaSetDevice(e->device));
   C6_CUDA(e, cudaMemcpy(out, e->wait_dev + 8, (size_t)n_ctas * 4 * sizeof(long long), cudaMemcpyDeviceToHost));
+  return C6_OK;
+}
+
+int c6_debug_expire_wait(C6Engine* e, void* stream) {
+  if (!e) return C6_ERR_ARG;
+  C6_CUDA(e, cudaSetDevice(e->device));
+  expire_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(e->status_dev, 1000000LL);
+  C6_LAUNCHED(e, "expire_wait_kernel");
+  return C6_OK;
+}
+
+int c6_clear_status(C6Engine* e) {
+  if (!e) return C6_ERR_ARG;
+  C6_CUDA(e, cudaSetDevice(e->device));
+  C6_CUDA(e, cudaMemset(e->status_dev, 0, sizeof(int)));
+  e->err.clear();
   return C6_OK;
 }
 

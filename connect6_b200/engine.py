@@ -158,6 +158,35 @@ class Engine:
                                               _stream_ptr(self.device)), self._h, "c6_forward_step")
         return action, logprob, value, logits
 
+    def forward_step_boards(self, boards: torch.Tensor, current_player: torch.Tensor, stones_left: torch.Tensor,
+                            index: torch.Tensor | None = None, *, temperature: float = 1.0, seed: int = 0,
+                            offset: int = 0, board_index0: int = 0, orient: torch.Tensor | None = None,
+                            inverse_map: bool = False, want_logits: bool = False, want_logprob: bool = True,
+                            want_value: bool = True):
+        """Self-play step straight from the environment's int8 state (no fp32 planes)."""
+        for t, name in ((boards, "boards"), (current_player, "current_player"), (stones_left, "stones_left")):
+            if t.dtype != torch.int8 or t.device != self.device:
+                raise ValueError(f"{name} must be an int8 tensor on {self.device}")
+        boards, current_player, stones_left = boards.contiguous(), current_player.contiguous(), stones_left.contiguous()
+        if index is not None:
+            if index.dtype != torch.int64 or index.device != self.device:
+                raise ValueError("index must be an int64 tensor on the engine's device")
+            index = index.contiguous()
+        B = int(index.numel()) if index is not None else int(boards.shape[0])
+        orient = self._check_orient(orient, B)
+        action = torch.empty((B,), device=self.device, dtype=torch.int64)
+        logprob = torch.empty((B,), device=self.device, dtype=torch.float32) if want_logprob else None
+        value = torch.empty((B,), device=self.device, dtype=torch.float32) if want_value else None
+        logits = torch.empty((B, self.n_actions), device=self.device, dtype=torch.float32) if want_logits else None
+        flags = L.C6_FLAG_INVERSE_MAP if inverse_map else 0
+        with torch.cuda.device(self.device):
+            L.check(self._lib.c6_forward_step_boards(self._h, L.ptr(boards), L.ptr(current_player), L.ptr(stones_left),
+                                                     L.ptr(index), B, L.ptr(orient), flags, float(temperature), int(seed),
+                                                     int(offset), int(board_index0), L.ptr(action), L.ptr(logprob),
+                                                     L.ptr(value), L.ptr(logits), _stream_ptr(self.device)),
+                    self._h, "c6_forward_step_boards")
+        return action, logprob, value, logits
+
     def forward_grouped(self, x: torch.Tensor, *, want_value: bool = False, mask: bool = False):
         x = self._check_x(x, 2)
         G, T = x.shape[0], x.shape[1]
@@ -225,6 +254,14 @@ class Engine:
         st = C.c_int(0)
         L.check(self._lib.c6_status(self._h, C.byref(st)), self._h, "c6_status")
         return st.value
+
+    def clear_status(self) -> None:
+        L.check(self._lib.c6_clear_status(self._h), self._h, "c6_clear_status")
+
+    def expire_wait_selftest(self) -> None:
+        """Enqueue the bounded-wait self-test kernel (its wait runs out by design)."""
+        with torch.cuda.device(self.device):
+            L.check(self._lib.c6_debug_expire_wait(self._h, _stream_ptr(self.device)), self._h, "c6_debug_expire_wait")
 
     @property
     def launch_count(self) -> int:

@@ -174,6 +174,16 @@ class PolicyValueNet(nn.Module):
             board_index0=board_index0, orient=orient, inverse_map=inverse_map, want_logits=want_logits)
 
 
+    @torch.no_grad()
+    def selfplay_step_from_boards(self, boards: torch.Tensor, current_player: torch.Tensor, stones_left: torch.Tensor,
+                                  index: torch.Tensor | None = None, **kwargs):
+        """The same step fed with the environment's raw int8 state (boards [E,n,n], current_player [E],
+        stones_left [E]) and an optional int64 index vector selecting the boards to evaluate: fuses
+        canonical_network_input (connect6/vector_env.py:196-218) and the gather of
+        connect6/train.py:793 into the first kernel."""
+        return self.engine_for(boards.device).forward_step_boards(boards, current_player, stones_left, index, **kwargs)
+
+
 def build_model(model_cfg: dict[str, Any], board_size: int) -> PolicyValueNet:
     """Build the network from the `model` section of the YAML config (connect6/model.py:114-120):
     bookkeeping keys are dropped, the rest are constructor arguments."""

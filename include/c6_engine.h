@@ -107,6 +107,19 @@ int c6_forward_step(C6Engine* eng, const void* x, int x_dtype, int64_t B, const 
                     int64_t board_index0, int64_t* action, float* logprob, float* value,
                     float* masked_logits, void* stream);
 
+/* Replaces: canonical_network_input (connect6/vector_env.py:196-218), the batch gather
+ * network_input[current_idx] (connect6/train.py:793) and the self-play step above in one call: the
+ * three input planes are derived from the environment's raw state inside the first kernel, so the
+ * fp32 planes (4.3 KB per board) never exist in memory.
+ *   boards int8 [envs,n,n] (+1/-1/0), current_player int8 [envs] (+1/-1), stones_left int8 [envs];
+ *   index nullable int64 [B]: board b of the batch is environment index[b] (null: b itself);
+ *   occupancy for masking is boards != 0; outputs as in c6_forward_step. */
+int c6_forward_step_boards(C6Engine* eng, const int8_t* boards, const int8_t* current_player,
+                           const int8_t* stones_left, const int64_t* index, int64_t B,
+                           const uint8_t* orient, int flags, float temperature, uint64_t seed,
+                           uint64_t offset, int64_t board_index0, int64_t* action, float* logprob,
+                           float* value, float* masked_logits, void* stream);
+
 /* Replaces: HistoricalPolicyEnsemble.forward_grouped (connect6/history.py:276-303): G
  * independent models, T boards each, one launch sequence for all groups.
  *   x [G,T,3,n,n]; logits fp32 [G,T,n*n]; value nullable fp32 [G,T] (the reference ensemble
@@ -196,6 +209,15 @@ int c6_debug_cta_times(C6Engine* eng, int64_t* out, int n_ctas);
  * out; the kernels then skip their work instead of hanging. The caller must have synchronised
  * the stream it used. */
 int c6_status(C6Engine* eng, int* device_status);
+
+/* Clears the device status word (synchronous) after the caller has dealt with a non-zero status. */
+int c6_clear_status(C6Engine* eng);
+
+/* Self-test of the failure path, no reference counterpart: enqueues a one-CTA kernel that waits, with
+ * a limit of about half a millisecond, on a barrier nobody arrives on.  The wait runs out, the kernel
+ * sets a status bit and returns normally -- the same path a real kernel takes if its pipeline stalls.
+ * Nothing faults or hangs; c6_status then reports C6_ERR_DEVICE until c6_clear_status. */
+int c6_debug_expire_wait(C6Engine* eng, void* stream);
 
 /* Number of kernel launches the engine has enqueued since creation (host counter). */
 int64_t c6_launch_count(const C6Engine* eng);

@@ -202,3 +202,45 @@ def test_host_step_pipeline_matches_direct_steps(cuda_device):
     pipe.submit(batches[0][:10])             # a smaller batch reuses the buffers
     a, lp, v = pipe.step(seed=5, offset=0, board_index0=0)
     assert a.shape == (10,)
+
+
+def test_bounded_wait_expiry_is_reported_not_hung(cuda_device):
+    """Failure detection without a fault: a wait that nothing satisfies runs out after its limit, the
+    kernel returns, the status word says so, and the engine keeps working after the status is cleared."""
+    from connect6_b200.boards import generate_planes
+    m = _default_model(cuda_device)
+    eng = m.engine_for(cuda_device)
+    x = torch.from_numpy(generate_planes(0, 16)).to(cuda_device)
+    before = eng.forward(x)
+    assert eng.status() == 0
+    eng.expire_wait_selftest()
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        eng.status()
+    eng.clear_status()
+    assert eng.status() == 0
+    after = eng.forward(x)
+    assert torch.equal(before[0], after[0]) and torch.equal(before[1], after[1])
+
+
+@pytest.mark.parametrize("precision", ["bf16", "fp32"])
+def test_step_from_raw_boards_equals_planes_path(cuda_device, precision):
+    """int8 environment state (+ gather index, + orientation) gives exactly what the plane-fed step gives."""
+    from connect6_b200.selfplay import canonical_network_input
+    m = _default_model(cuda_device, precision)
+    rng = np.random.default_rng(4)
+    E, B = 300, 128
+    boards = torch.from_numpy(rng.choice([-1, 0, 0, 0, 1], size=(E, 19, 19)).astype(np.int8)).to(cuda_device)
+    player = torch.from_numpy(rng.choice([-1, 1], size=E).astype(np.int8)).to(cuda_device)
+    stones = torch.from_numpy(rng.choice([1, 2], size=E).astype(np.int8)).to(cuda_device)
+    index = torch.from_numpy(rng.permutation(E)[:B].astype(np.int64)).to(cuda_device)
+    orient = torch.from_numpy((np.arange(B) % 8).astype(np.uint8)).to(cuda_device)
+    planes = canonical_network_input(boards, player, stones)[index]
+    for kw in (dict(), dict(orient=orient, inverse_map=True)):
+        want = m.selfplay_step(planes, seed=21, offset=2, board_index0=50, want_logits=True, **kw)
+        got = m.selfplay_step_from_boards(boards, player, stones, index, seed=21, offset=2, board_index0=50,
+                                          want_logits=True, **kw)
+        for w, g in zip(want, got):
+            assert torch.equal(w, g)
+    whole = m.selfplay_step_from_boards(boards, player, stones, seed=1, offset=1)
+    ref = m.selfplay_step(canonical_network_input(boards, player, stones), seed=1, offset=1)
+    assert torch.equal(whole[0], ref[0]) and torch.equal(whole[2], ref[2])

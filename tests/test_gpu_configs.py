@@ -128,3 +128,24 @@ def test_config3_grouped_16x512(cuda_device):
     l4, _ = eng.forward_grouped(x[:, :4].contiguous())
     assert torch.equal(l4, logits[:, :4])
     assert eng.status() == 0 and single.status() == 0
+
+
+def test_training_ensemble_128x4(cuda_device):
+    """The ensemble shape the reference trains against (connect6/history.py:276-303 with 128 stacked
+    opponents and 4 tables each): every sampled group equals a single-model engine bit for bit."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import PolicyValueNet
+    G, T = 128, 4
+    states = [_state(2000 + g) for g in range(G)]
+    eng = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, G, "bf16")
+    for g in range(G):
+        eng.load_state_dict(states[g], group=g)
+    x = torch.from_numpy(generate_planes(0, G * T)).reshape(G, T, 3, 19, 19).to(cuda_device)
+    logits, value = eng.forward_grouped(x, want_value=True)
+    single = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, 1, "bf16")
+    for g in (0, 63, 127):
+        single.load_state_dict(states[g])
+        l1, v1 = single.forward(x[g])
+        assert torch.equal(l1, logits[g]) and torch.equal(v1, value[g])
+    assert eng.status() == 0 and single.status() == 0

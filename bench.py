@@ -154,6 +154,52 @@ def cpu_baseline(budget_s: float = 12.0) -> dict:
                       f"forward + masked categorical draw, median step {med * 1e3:.1f} ms"}
 
 
+def library_gpu_bar(model, batches, steps: int = 10) -> dict:
+    """The same self-play step through stock PyTorch/cuDNN on this GPU: the module stack of
+    connect6/model.py:52-75 under bf16 autocast and inference_mode as in connect6/train.py:791-795,
+    then the masked temperature-1 draw of connect6/train.py:195-205.  Reported beside the engine's
+    number as the library bar on the same box; never part of the timed engine region."""
+    import torch
+
+    def lib_step(x, channels_last):
+        if channels_last:
+            x = x.contiguous(memory_format=torch.channels_last)
+        with torch.inference_mode(), torch.autocast("cuda", dtype=torch.bfloat16):
+            logits, value = model.forward_autograd(x)
+        legal = ((x[:, 0] == 0) & (x[:, 1] == 0)).flatten(1)
+        z = logits.float().masked_fill(~legal, torch.finfo(torch.float32).min)
+        logp = torch.log_softmax(z, dim=-1)
+        # rows with no legal cell would make multinomial raise; the synthetic boards have <= 200 stones
+        action = torch.multinomial(logp.exp(), 1).squeeze(1)
+        return action, logp.gather(1, action[:, None]).squeeze(1), value.float()
+
+    out = {}
+    for name, cl in (("nchw", False), ("channels_last", True)):
+        if cl:
+            model.to(memory_format=torch.channels_last)
+        try:
+            for i in range(3):
+                lib_step(batches[i % len(batches)], cl)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(steps):
+                lib_step(batches[i % len(batches)], cl)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            out[name] = {"value": batches[0].shape[0] / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms}
+        except Exception as exc:  # noqa: BLE001 - a library failure must not take the engine's line down
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        finally:
+            if cl:
+                model.to(memory_format=torch.contiguous_format)
+    out["what"] = ("stock torch " + torch.__version__ + " / cuDNN modules, bf16 autocast, inference_mode, "
+                   "mask + log_softmax + torch.multinomial; inputs resident on the device")
+    out["steps"] = steps
+    return out
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -361,6 +407,8 @@ def run_engine(args) -> None:
         "kernels": kernels,
         "device_status": status,
     }
+    if world == 1 and not args.no_library_bar:
+        line["library_gpu_bar"] = library_gpu_bar(model, dev_batches)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line), flush=True)
@@ -471,6 +519,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-library-bar", action="store_true",
+                    help="skip the stock PyTorch/cuDNN timing of the same step on this GPU")
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg2 (default) is the contract's benchmark; the others are BASELINE's other configurations")
     args = ap.parse_args()

@@ -1,4 +1,4 @@
-"""ctypes binding of the engine's C ABI (include/c6_engine.h).
+"""ctypes binding of the engine's C ABI (include/c6_engine.h, include/c6_env.h).
 
 The library is loaded from the package directory (connect6_b200/libc6engine.so).  There is no
 fallback: if the library is missing or a call fails, an exception is raised.
@@ -33,9 +33,31 @@ class C6Desc(C.Structure):
     ]
 
 
+class C6EnvState(C.Structure):
+    """include/c6_env.h: the state tensors of VectorConnect6 as device pointers."""
+    _fields_ = [
+        ("boards", C.c_void_p), ("current_player", C.c_void_p), ("stones_left", C.c_void_p),
+        ("empty_count", C.c_void_p), ("move_count", C.c_void_p),
+        ("num_envs", C.c_int64), ("board_size", C.c_int32), ("win_length", C.c_int32),
+    ]
+
+
+class C6CollectorState(C.Structure):
+    """include/c6_env.h: the rollout collector's per-environment bookkeeping tensors."""
+    _fields_ = [
+        ("current_episode_ids", C.c_void_p), ("current_segment_lengths", C.c_void_p),
+        ("historical_mask", C.c_void_p), ("historical_current_colors", C.c_void_p),
+        ("episode_results", C.c_void_p), ("episode_terminal_moves", C.c_void_p),
+        ("episode_capacity", C.c_int64), ("next_episode_id", C.c_void_p),
+    ]
+
+
+C6_ENV_FAULT_OCCUPIED, C6_ENV_FAULT_ACTION, C6_ENV_FAULT_EPISODE, C6_ENV_FAULT_COUNT = 0, 1, 2, 4
+C6_STAT_COUNT, C6_STAT_DONE_COUNT = 10, 9
+
 _vp, _i, _i64, _u64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_float
 
-# name -> (restype, argtypes); mirrors include/c6_engine.h declaration by declaration
+# name -> (restype, argtypes); mirrors include/c6_engine.h and include/c6_env.h declaration by declaration
 SIGNATURES = {
     "c6_version": (_i, []),
     "c6_create": (_i, [C.POINTER(C6Desc), C.POINTER(_vp)]),
@@ -63,6 +85,12 @@ SIGNATURES = {
     "c6_device_bytes": (_i64, [_vp]),
     "c6_last_error": (C.c_char_p, [_vp]),
     "c6_destroy": (_i, [_vp]),
+    "c6_env_step": (_i, [C.POINTER(C6EnvState), _vp, C.c_int32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "c6_env_reset": (_i, [C.POINTER(C6EnvState), _vp, _i64, _vp]),
+    "c6_env_legal_mask": (_i, [C.POINTER(C6EnvState), _vp, _vp]),
+    "c6_env_collect_workspace_bytes": (_i64, [_i64]),
+    "c6_env_collect_done": (_i, [C.POINTER(C6EnvState), C.POINTER(C6CollectorState), _vp, _vp, _vp, _vp, _vp, _vp,
+                                 _vp, _vp]),
 }
 
 _lib = None

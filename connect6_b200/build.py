@@ -1,6 +1,6 @@
 """Build recipe for the engine's shared library (in-tree, nvcc, sm_100a only).
 
-`python -m connect6_b200.build` compiles connect6_b200/csrc/c6_engine.cu into
+`python -m connect6_b200.build` compiles connect6_b200/csrc/c6_engine.cu and c6_env.cu into
 connect6_b200/libc6engine.so.  The library links the CUDA runtime statically and has no
 dependency on libtorch, so it loads with ctypes from any process.
 """
@@ -15,8 +15,8 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libc6engine.so"
-SOURCES = [CSRC / "c6_engine.cu"]
-HEADERS = sorted(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "c6_engine.h"]
+SOURCES = [CSRC / "c6_engine.cu", CSRC / "c6_env.cu"]
+HEADERS = sorted(CSRC.glob("*.cuh")) + sorted((PKG_DIR.parent / "include").glob("*.h"))
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -52,3 +52,46 @@ def masked_log_softmax(logits: torch.Tensor, legal: torch.Tensor, temperature: f
     """Normalised logits of Categorical(logits=mask_logits(logits.float(), legal)/max(T,1e-4))."""
     z = logits.float().masked_fill(~legal, torch.finfo(torch.float32).min) / max(float(temperature), 1e-4)
     return z - z.logsumexp(dim=-1, keepdim=True)
+
+
+# ---- environment step (connect6/vector_env.py:106-193) with stock torch ops -----------------------
+# Restated with shifted views of a zero-padded board instead of the reference's index gather; the
+# result is the same integer state.  Works on CPU and CUDA tensors: on the GPU it serves as the
+# "stock PyTorch" timing bar for the environment kernels, on the CPU as a fast checker for large
+# batches (it is itself checked against the numpy oracle and the recorded reference games).
+_ENV_DIRECTIONS = ((1, 0), (0, 1), (1, 1), (1, -1))
+
+
+@torch.no_grad()
+def env_step_torch(boards: torch.Tensor, current_player: torch.Tensor, stones_left: torch.Tensor,
+                   empty_count: torch.Tensor, move_count: torch.Tensor, actions: torch.Tensor, win_length: int = 6):
+    """In-place step of the five state tensors; returns (reward, done, winner, transition_sign,
+    game_lengths) with the reference's dtypes."""
+    E, n, _ = boards.shape
+    env_ids = torch.arange(E, device=boards.device)
+    r, c = actions // n, actions % n
+    actor = current_player.clone()
+    boards[env_ids, r, c] = actor
+    empty_count -= 1
+    move_count += 1
+    reach = win_length - 1
+    padded = torch.nn.functional.pad(boards, (reach, reach, reach, reach))
+    won = torch.zeros(E, dtype=torch.bool, device=boards.device)
+    for dr, dc in _ENV_DIRECTIONS:
+        total = torch.ones(E, dtype=torch.int16, device=boards.device)
+        for sgn in (1, -1):
+            alive = torch.ones(E, dtype=torch.bool, device=boards.device)
+            for s in range(1, win_length):
+                cell = padded[env_ids, r + reach + sgn * dr * s, c + reach + sgn * dc * s]
+                alive = alive & (cell == actor)
+                total = total + alive.to(torch.int16)
+        won |= total >= win_length
+    done = won | ((empty_count == 0) & ~won)
+    winner = torch.where(won, actor, torch.zeros_like(actor))
+    remaining = stones_left - 1
+    stay = ~done & (remaining > 0)
+    switch = ~done & ~(remaining > 0)
+    stones_left.copy_(torch.where(stay, remaining, torch.where(switch, torch.full_like(remaining, 2), stones_left)))
+    current_player.copy_(torch.where(switch, -current_player, current_player))
+    sign = stay.to(torch.int8) - switch.to(torch.int8)
+    return won.to(torch.float32), done, winner, sign, move_count.clone()

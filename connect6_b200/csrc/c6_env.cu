@@ -15,6 +15,7 @@ namespace c6 {
 namespace {
 
 constexpr int kEnvThreads = 256;
+constexpr int kStepThreads = 64;  // small blocks: 8192 environments still spread over 128 SMs
 
 struct EnvView {
   int8_t* boards;
@@ -40,7 +41,7 @@ __device__ __forceinline__ int run_length(const int8_t* __restrict__ b, int n, i
   return k;
 }
 
-__global__ void __launch_bounds__(kEnvThreads)
+__global__ void __launch_bounds__(kStepThreads)
 env_step_kernel(EnvView s, const long long* __restrict__ actions, int phase, float* __restrict__ reward,
                 uint8_t* __restrict__ done, int8_t* __restrict__ winner, int8_t* __restrict__ tsign,
                 int16_t* __restrict__ lengths, int* __restrict__ faults) {
@@ -264,7 +265,8 @@ int c6_env_step(const C6EnvState* env, const int64_t* actions, int32_t view_phas
   if (!env_ok(env) || view_phase < 0 || view_phase > 7) return C6_ERR_ARG;
   if (env->num_envs == 0) return C6_OK;
   if (!actions || !reward || !done || !winner || !transition_sign || !game_lengths) return C6_ERR_ARG;
-  env_step_kernel<<<blocks_for(env->num_envs), kEnvThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  env_step_kernel<<<(unsigned)((env->num_envs + kStepThreads - 1) / kStepThreads), kStepThreads, 0,
+                    reinterpret_cast<cudaStream_t>(stream)>>>(
       view_of(env), reinterpret_cast<const long long*>(actions), view_phase, reward, done, winner, transition_sign,
       game_lengths, faults);
   return launched();

@@ -55,11 +55,27 @@ def masked_log_softmax(logits: torch.Tensor, legal: torch.Tensor, temperature: f
 
 
 # ---- environment step (connect6/vector_env.py:106-193) with stock torch ops -----------------------
-# Restated with shifted views of a zero-padded board instead of the reference's index gather; the
-# result is the same integer state.  Works on CPU and CUDA tensors: on the GPU it serves as the
-# "stock PyTorch" timing bar for the environment kernels, on the CPU as a fast checker for large
-# batches (it is itself checked against the numpy oracle and the recorded reference games).
+# Restated over a zero-padded board (no bounds masks needed: the padding never equals a player) with
+# one gather for all probe cells; the result is the same integer state.  Works on CPU and CUDA
+# tensors: on the GPU it serves as the "stock PyTorch" timing bar for the environment kernels, on the
+# CPU as a fast checker for large batches (it is itself checked against the numpy oracle and the
+# recorded reference games).
 _ENV_DIRECTIONS = ((1, 0), (0, 1), (1, 1), (1, -1))
+_probe_cache: dict = {}
+
+
+def _probe_offsets(n: int, win_length: int, device) -> torch.Tensor:
+    """Flat offsets, inside the padded (n + 2*reach)^2 board, of the probe cells around a stone:
+    [8 rays, reach] ordered near to far; rays 2d and 2d+1 are the two halves of line direction d."""
+    key = (n, win_length, str(device))
+    if key not in _probe_cache:
+        reach, pitch = win_length - 1, n + 2 * (win_length - 1)
+        rays = []
+        for dr, dc in _ENV_DIRECTIONS:
+            for sgn in (1, -1):
+                rays.append([sgn * s * (dr * pitch + dc) for s in range(1, reach + 1)])
+        _probe_cache[key] = torch.tensor(rays, dtype=torch.long, device=device).reshape(8, reach)
+    return _probe_cache[key]
 
 
 @torch.no_grad()
@@ -68,25 +84,23 @@ def env_step_torch(boards: torch.Tensor, current_player: torch.Tensor, stones_le
     """In-place step of the five state tensors; returns (reward, done, winner, transition_sign,
     game_lengths) with the reference's dtypes."""
     E, n, _ = boards.shape
+    reach, pitch = win_length - 1, n + 2 * (win_length - 1)
     env_ids = torch.arange(E, device=boards.device)
     r, c = actions // n, actions % n
     actor = current_player.clone()
     boards[env_ids, r, c] = actor
     empty_count -= 1
     move_count += 1
-    reach = win_length - 1
-    padded = torch.nn.functional.pad(boards, (reach, reach, reach, reach))
-    won = torch.zeros(E, dtype=torch.bool, device=boards.device)
-    for dr, dc in _ENV_DIRECTIONS:
-        total = torch.ones(E, dtype=torch.int16, device=boards.device)
-        for sgn in (1, -1):
-            alive = torch.ones(E, dtype=torch.bool, device=boards.device)
-            for s in range(1, win_length):
-                cell = padded[env_ids, r + reach + sgn * dr * s, c + reach + sgn * dc * s]
-                alive = alive & (cell == actor)
-                total = total + alive.to(torch.int16)
-        won |= total >= win_length
-    done = won | ((empty_count == 0) & ~won)
+    if reach > 0:
+        padded = torch.nn.functional.pad(boards, (reach, reach, reach, reach)).reshape(E, -1)
+        centre = (r + reach) * pitch + (c + reach)
+        probes = centre.view(E, 1, 1) + _probe_offsets(n, win_length, boards.device)
+        same = padded.gather(1, probes.reshape(E, -1)).reshape(E, 8, reach) == actor.view(E, 1, 1)
+        runs = same.to(torch.int16).cumprod(-1).sum(-1)              # contiguous stones along each ray
+        won = ((1 + runs[:, 0::2] + runs[:, 1::2]) >= win_length).any(1)
+    else:
+        won = torch.ones(E, dtype=torch.bool, device=boards.device)
+    done = won | (empty_count == 0)
     winner = torch.where(won, actor, torch.zeros_like(actor))
     remaining = stones_left - 1
     stay = ~done & (remaining > 0)

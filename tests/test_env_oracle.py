@@ -71,10 +71,14 @@ def test_collector_oracle_invariants():
     assert len(set(col.current_episode_ids.tolist())) == E
 
 
+@pytest.mark.parametrize("impl", ["oracle_port", "bench_bar"])
 @pytest.mark.parametrize("name", ENV_FIXTURES)
-def test_torch_env_port_replays_reference_games(name):
+def test_torch_env_port_replays_reference_games(name, impl):
+    """Both torch restatements -- the checker under oracle/ and the library timing bar inside
+    bench.py -- reproduce the reference's games (win_length >= 2)."""
     import torch
     import torch_port as TP
+    import bench
     fx = np.load(GOLDEN / f"{name}.npz")
     win = int(fx["win_length"])
 
@@ -87,7 +91,10 @@ def test_torch_env_port_replays_reference_games(name):
             self.moves = torch.zeros(E, dtype=torch.int16)
 
     def step(s, a):
-        out = TP.env_step_torch(s.boards, s.player, s.stones, s.empty, s.moves, torch.from_numpy(a), win)
+        if impl == "oracle_port":
+            out = TP.env_step_torch(s.boards, s.player, s.stones, s.empty, s.moves, torch.from_numpy(a), win)
+        else:
+            out = bench.stock_torch_env_step([s.boards, s.player, s.stones, s.empty, s.moves], torch.from_numpy(a), win)
         return dict(zip(("reward", "done", "winner", "transition_sign", "game_lengths"), (o.numpy() for o in out)))
 
     def reset(s, idx):

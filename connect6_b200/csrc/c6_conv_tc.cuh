@@ -17,12 +17,17 @@
 // resident in shared memory when they fit; otherwise the blocks of a step travel with its
 // activation stage.  A pipeline step stages 32 input channels (two q: 4 planes of 128+2*halo rows).
 //
-// CTA = 416 threads: warp 0 issues bulk copies; warps 1-4 (one per SM sub-partition) issue the
+// CTA = 704 threads: warp 0 issues bulk copies; warps 1-4 (one per SM sub-partition) issue the
 // MMAs of tiles t = i mod 4, each into its own accumulator -- a lone issuer that shares its
 // scheduler with busy epilogue warps only reaches half the tensor pipe's rate (measured), four keep
-// it saturated and hide each other's per-step barrier work; warps 5-12 drain the accumulators
-// (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores); warp 13 is a second producer.
-// A ring of 2 or 4 TMEM accumulators lets the epilogue teams overlap the MMAs of later tiles.  Every wait
+// it saturated and hide each other's per-step barrier work; warps 5-20 drain the accumulators
+// (bias + SiLU in fp32, one bf16 rounding, 16-byte coalesced stores) as four teams of four warps;
+// warp 21 is a second producer.  The epilogue of one tile is a chain of long latencies (a TMEM
+// fetch takes ~450 clocks, the tanh unit 8 clocks per warp instruction): with two teams it, not
+// the tensor pipe, bounded every layer of up to 64 output channels (measured with the MMAs and
+// copies switched off: no change), with four teams -- four epilogue warps per scheduler -- the
+// layers run at their MMA or HBM floor.
+// A ring of 2, 4 or 8 TMEM accumulators lets the teams overlap the MMAs of later tiles.  Every wait
 // is bounded: when one runs out the CTA records a status bit, stops, frees TMEM and returns.
 #pragma once
 
@@ -71,7 +76,11 @@ struct ConvTcParams {
   float c_wv[256];       // value head weights
 };
 
-constexpr int kConvThreads = 448;  // producer warp, four MMA warps, eight epilogue warps, second producer warp
+constexpr int kEpiTeams = 4;                   // epilogue teams of four warps (as many as the accumulator ring allows are used)
+constexpr int kEpiWarp0 = 5;                   // first epilogue warp
+constexpr int kProducer2Warp = kEpiWarp0 + 4 * kEpiTeams;
+constexpr int kConvThreads = 32 * (kProducer2Warp + 1);  // producer, four MMA warps, 4*kEpiTeams epilogue warps, second producer
+constexpr int kEpiBatch = 1;                   // 16-column units fetched from TMEM per wait (80 registers per thread at 704 threads)
 constexpr int kConvSmemHeader = 5888;  // barriers, TMEM slot, abort flag, bias and head vectors, head partials
 constexpr int kMaxStages = 16;
 constexpr int kMaxAcc = 8;
@@ -170,8 +179,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       tc::tmem_relinquish();
     }
   }
-  if (warp >= 5 && warp <= 12) {
-    for (int i = threadIdx.x - 160; i < p.n; i += 256) {
+  if (warp >= kEpiWarp0 && warp < kProducer2Warp) {
+    for (int i = threadIdx.x - 32 * kEpiWarp0; i < p.n; i += 128 * kEpiTeams) {
       s_bias[i] = 0.5f * p.bias[(size_t)group * p.n + i];  // the epilogue works on h = x/2
       if (p.head) {
         s_wp[i] = p.head_wp[(size_t)group * p.n + i];
@@ -187,7 +196,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   const uint4* w_group = PAIR ? p.w_pair + ((size_t)group * 2 + crank) * (w_bytes / 16) : p.w + (size_t)group * (w_bytes / 16);
   const long long group_row0 = (long long)p.front + (long long)group * p.tiles_per_group * 128;
 
-  if (warp == 0 || warp == 13) {
+  if (warp == 0 || warp == kProducer2Warp) {
     // ------------------------------ producers ------------------------------
     // The warp walks the loop together: lane 0 waits for the stage and arms its barrier, then lanes
     // 0 .. 2*qps-1 each issue the bulk copy of one channel-chunk plane (issuing a copy costs a few
@@ -418,9 +427,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         if (++sl == p.spi) { sl = 0; ph ^= 1u; }
       }
     }
-  } else if (warp >= 5 && warp <= 12) {
+  } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4 * (p.nacc < kEpiTeams ? p.nacc : kEpiTeams)) {
     // ------------------------------ epilogue ------------------------------
-    // Two teams of four warps take alternate tiles (team = tile parity).  A warp may read TMEM
+    // Teams of four warps take tiles round robin (team = tile mod nteams; nteams divides the
+    // accumulator ring, so an accumulator's barriers always see the same team).  A warp may read TMEM
     // lanes 32*(w%4)..+31 only, so inside a team each warp owns one lane quadrant = 32 positions
     // and all their channels; the accumulator ring (2 or 4 buffers) lets the MMA warp run ahead
     // while both teams are busy.  Per element: h = 0.5*acc + 0.5*bias (one FMA),
@@ -428,7 +438,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     // channel of its position, so both 1x1 heads reduce inside the thread.
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     const int quad = warp & 3;
-    const int team = (warp - 5) >> 2;
+    const int team = (warp - kEpiWarp0) >> 2;
+    const int nteams = p.nacc < kEpiTeams ? p.nacc : kEpiTeams;
     const int row = quad * 32 + lane;
     const int nunits = p.n >> 4;
     bool ok = true;
@@ -440,7 +451,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       board = (int)(pos0 / p.slots);
       slot = (int)(pos0 - (long long)board * p.slots);
     }
-    for (int tcount = team; tcount < ntl && ok; tcount += 2) {
+    for (int tcount = team; tcount < ntl && ok; tcount += nteams) {
       const int tile = t_first + tcount * t_stride;
       const int acc = tcount % p.nacc;
       const uint32_t acc_ph = (uint32_t)(tcount / p.nacc) & 1u;
@@ -459,7 +470,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       const long long pos = (long long)tile * 128 + row;
       const int r = slot / p.wp, c = slot - r * p.wp;
       const bool valid = board < p.nboards && r < p.bsize && c < p.bsize;
-      slot += 256 * t_stride;   // this thread's row in the team's next tile
+      slot += 128 * nteams * t_stride;   // this thread's row in the team's next tile
       while (slot >= p.slots) { slot -= p.slots; ++board; }
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       uint4* out_row = p.out + group_row0 + pos;
@@ -467,14 +478,14 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       // Up to three 16-channel units are fetched from TMEM with one wait so that their latencies
       // overlap; after the last fetch the accumulator goes back to the MMA warp before the
       // arithmetic starts.
-      for (int u0 = 0; u0 < nunits; u0 += 3) {
-        uint32_t v[3][16];
+      for (int u0 = 0; u0 < nunits; u0 += kEpiBatch) {
+        uint32_t v[kEpiBatch][16];
 #pragma unroll
-        for (int b = 0; b < 3; ++b)
+        for (int b = 0; b < kEpiBatch; ++b)
           if (u0 + b < nunits) tc::tmem_ld16(taddr + (uint32_t)((u0 + b) * 16), v[b]);
         tc::tmem_wait_ld();
         if (timing && u0 == 0) e1 = clock64();
-        if (u0 + 3 >= nunits) {
+        if (u0 + kEpiBatch >= nunits) {
           tc::fence_before_sync();
           __syncwarp();
           if (lane == 0) {
@@ -483,7 +494,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         }
         if (timing && u0 == 0) e2 = clock64();
 #pragma unroll
-        for (int b = 0; b < 3; ++b) {
+        for (int b = 0; b < kEpiBatch; ++b) {
           const int u = u0 + b;
           if (u < nunits) {
             float y[16];
@@ -548,11 +559,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         p.vmap[o] = valid ? val : 0.f;
       }
       if (timing) {
-        ep_ld += e2 - e1;            // release: fence + syncwarp + arrive
-        ep_math += clock64() - e2;   // arithmetic + stores
+        ep_ld += e1 - e0;            // first TMEM fetch: issue to data
+        ep_math += clock64() - e1;   // release + arithmetic + stores (+ later fetches)
       }
     }
-    if (timing && threadIdx.x == 160) {
+    if (timing && threadIdx.x == 32 * kEpiWarp0) {
       p.wait_cycles[3] += wait_tfull;
       p.wait_cycles[6] += ep_ld;     // first TMEM fetch of each tile: issue to data
       p.wait_cycles[7] += ep_math;   // arithmetic + stores (+ later fetches)

@@ -253,6 +253,8 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
   __shared__ int s_redi[kFinishThreads / 32];
   __shared__ float s_scan[kFinishThreads];
 
+  grid_dep_launch();
+  grid_dep_wait();   // raw logits and value maps come from the last conv kernel
   const int g = blockIdx.y;
   const int t = blockIdx.x;
   const int A = p.n_actions;

@@ -67,6 +67,13 @@ __device__ __forceinline__ float board_uniform(uint64_t seed, uint64_t offset, u
   return (float)(r.x >> 8) * (1.0f / 16777216.0f);
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may start while its predecessor in the stream still runs; grid_dep_wait() blocks until
+// the predecessor has completed and its writes are visible (a no-op for an ordinary launch).
+// grid_dep_launch() lets the successor's CTAs take over SMs as this grid's CTAs exit.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- activations ----------------------------------------------------------------------
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 // SiLU through the hardware tanh: x*sigmoid(x) = h + h*tanh(h) with h = x/2.  One MUFU and two

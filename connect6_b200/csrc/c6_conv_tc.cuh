@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   float* s_wv = s_wp + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  grid_dep_launch();   // the next kernel's CTAs may move in as ours exit; its own wait orders the data
   unsigned long long gt_start = 0;
   if (p.wait_cycles) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_start));
   const uint32_t crank = PAIR ? tc::cluster_ctarank() : 0u;
@@ -213,6 +214,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         tc::bulk_g2s(tc::smem_u32(s_w + off), reinterpret_cast<const uint8_t*>(w_group) + off, len, bar_w);
       }
     }
+    grid_dep_wait();   // weights do not depend on the previous kernel, the activations do
     long long waited = 0;
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0 && prod == 0;
     // Every issuer owns a private ring of `spi` stages, so each stage barrier has exactly one
@@ -439,6 +441,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     const int quad = warp & 3;
     const int team = (warp - kEpiWarp0) >> 2;
+    grid_dep_wait();   // redundant with the producers' wait (no accumulator fills before it); every role that touches global memory orders itself
     const int nteams = p.nacc < kEpiTeams ? p.nacc : kEpiTeams;
     const int row = quad * 32 + lane;
     const int nunits = p.n >> 4;

@@ -85,6 +85,7 @@ struct C6Engine {
   long long launches = 0;
   // optional per-kernel timing: event pairs recorded around every launch
   bool profiling = false;
+  bool dependent_launch = true;    // programmatic dependent launch along the kernel chain (C6_DEPENDENT_LAUNCH=0 turns it off)
   bool wait_counters = false;      // level 2: also the in-kernel pipeline wait counters
   struct ProfRec { int kind; cudaEvent_t a, b; };
   std::vector<ProfRec> prof;
@@ -142,6 +143,36 @@ struct ProfScope {
     if (b) cudaEventRecord(b, st);
   }
 };
+
+// Launch with optional 2-CTA clusters and optional programmatic dependent launch (the kernel then
+// orders itself behind its predecessor with grid_dep_wait(), so its prologue -- barrier setup, TMEM
+// allocation, resident weights -- overlaps the predecessor's tail).
+template <typename Params>
+void launch_chain(void (*kernel)(Params), unsigned grid_x, unsigned grid_y, unsigned threads, size_t smem,
+                  cudaStream_t st, bool cluster2, bool dependent, const Params& p) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid_x, grid_y);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  if (cluster2) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = 2;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (dependent) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = (unsigned)n;
+  cudaLaunchKernelEx(&cfg, kernel, p);
+}
 
 template <typename T>
 int dev_alloc(C6Engine* e, T** p, size_t count, bool zero, long long* tally) {
@@ -298,7 +329,7 @@ int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long
   f.logprob_out = a.logprob;
   {
     ProfScope _ps(e, C6_KIND_FINISH, st);
-    finish_kernel<<<dim3((unsigned)nb, (unsigned)e->G), kFinishThreads, 0, st>>>(f);
+    launch_chain(finish_kernel, (unsigned)nb, (unsigned)e->G, kFinishThreads, 0, st, false, e->dependent_launch, f);
   }
   C6_LAUNCHED(e, "finish_kernel");
   return C6_OK;
@@ -354,23 +385,13 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     if (e->stem_pair) {
       const long long items = (long long)e->G * (p.mtiles / 2) * p.ntiles;
       const int grid = 2 * (int)std::min<long long>(e->sms / 2, items);
-      cudaLaunchConfig_t cfg{};
-      cfg.gridDim = dim3((unsigned)grid);
-      cfg.blockDim = dim3(kStemThreads);
-      cfg.dynamicSmemBytes = (size_t)e->stem_smem;
-      cfg.stream = st;
-      cudaLaunchAttribute attr{};
-      attr.id = cudaLaunchAttributeClusterDimension;
-      attr.val.clusterDim.x = 2;
-      attr.val.clusterDim.y = 1;
-      attr.val.clusterDim.z = 1;
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
-      cudaLaunchKernelEx(&cfg, stem_tc_kernel<true>, p);
+      launch_chain(stem_tc_kernel<true>, (unsigned)grid, 1u, kStemThreads, (size_t)e->stem_smem, st, true,
+                   e->dependent_launch, p);
     } else {
       const long long items = (long long)e->G * p.mtiles * p.ntiles;
       const int grid = (int)std::min<long long>(e->sms, items);
-      stem_tc_kernel<false><<<grid, kStemThreads, e->stem_smem, st>>>(p);
+      launch_chain(stem_tc_kernel<false>, (unsigned)grid, 1u, kStemThreads, (size_t)e->stem_smem, st, false,
+                   e->dependent_launch, p);
     }
     C6_LAUNCHED(e, "stem_tc_kernel");
   }
@@ -422,31 +443,20 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     {
       ProfScope _ps(e, C6_KIND_CONV0 + l, st);
       const int grid = e->G * p.ctas_per_group;
+      const bool dep = e->dependent_launch;
       if (lp.pair) {
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3((unsigned)grid);
-        cfg.blockDim = dim3(kConvThreads);
-        cfg.dynamicSmemBytes = (size_t)lp.smem;
-        cfg.stream = st;
-        cudaLaunchAttribute attr{};
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2;
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
         switch (lp.k) {
-          case 1: cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, true>, p); break;
-          case 3: cudaLaunchKernelEx(&cfg, conv_tc_kernel<3, true>, p); break;
-          case 5: cudaLaunchKernelEx(&cfg, conv_tc_kernel<5, true>, p); break;
-          default: cudaLaunchKernelEx(&cfg, conv_tc_kernel<0, true>, p); break;
+          case 1: launch_chain(conv_tc_kernel<1, true>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, true, dep, p); break;
+          case 3: launch_chain(conv_tc_kernel<3, true>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, true, dep, p); break;
+          case 5: launch_chain(conv_tc_kernel<5, true>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, true, dep, p); break;
+          default: launch_chain(conv_tc_kernel<0, true>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, true, dep, p); break;
         }
       } else {
         switch (lp.k) {
-          case 1: conv_tc_kernel<1, false><<<grid, kConvThreads, lp.smem, st>>>(p); break;
-          case 3: conv_tc_kernel<3, false><<<grid, kConvThreads, lp.smem, st>>>(p); break;
-          case 5: conv_tc_kernel<5, false><<<grid, kConvThreads, lp.smem, st>>>(p); break;
-          default: conv_tc_kernel<0, false><<<grid, kConvThreads, lp.smem, st>>>(p); break;
+          case 1: launch_chain(conv_tc_kernel<1, false>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, false, dep, p); break;
+          case 3: launch_chain(conv_tc_kernel<3, false>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, false, dep, p); break;
+          case 5: launch_chain(conv_tc_kernel<5, false>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, false, dep, p); break;
+          default: launch_chain(conv_tc_kernel<0, false>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, false, dep, p); break;
         }
       }
     }
@@ -651,6 +661,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     if ((rc = dev_alloc(e, &e->bias[0], (size_t)e->G * c1, true, nullptr))) return bail(rc, "");
     // k x k layers
     e->pair_mode = e->sms / e->G >= 2;   // at least one CTA pair per group
+    if (const char* v = std::getenv("C6_DEPENDENT_LAUNCH")) e->dependent_launch = std::strcmp(v, "0") != 0;
     const int rows = conv_stage_rows(e->halo_rows);
     const int budget = kSmemLimit - 128 - kConvSmemHeader;
     for (int l = 1; l < e->L; ++l) {

@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
   uint8_t* s_stage = smem + kStemSmemHeader;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  grid_dep_launch();
   const uint32_t crank = PAIR ? tc::cluster_ctarank() : 0u;
   const bool leader = crank == 0;
   const int nloc = PAIR ? p.nt / 2 : p.nt;           // Toeplitz rows this CTA stages
@@ -141,6 +142,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     bool ok = true;
     int s = 0;
     uint32_t ph = 0;
+    grid_dep_wait();   // the input rows come from the pack kernel in front of this one
     for (long long item = i_begin; item < i_end && ok; ++item) {
       int g, mt, nt_i;
       decode(item, g, mt, nt_i);
@@ -279,6 +281,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     // cells): h = 0.5*acc + 0.5*bias, y = h + h*tanh(h), two 16-byte stores.
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
+    grid_dep_wait();
     const int row = quad * 32 + lane;
     const int nunits = p.nt >> 4;
     const int cells = p.bsize * p.bsize;

@@ -211,70 +211,68 @@ struct FinishParams {
   float* logprob_out;       // or null
 };
 
-constexpr int kFinishThreads = 128;
+constexpr int kFinishWarps = 4;                    // boards per block: one warp each
+constexpr int kFinishThreads = 32 * kFinishWarps;
 constexpr int kFinishMaxActions = 1024;
 
-__device__ __forceinline__ float block_reduce_max(float v, float* red) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = red[0];
-  for (int i = 1; i < kFinishThreads / 32; ++i) r = fmaxf(r, red[i]);
-  __syncthreads();
-  return r;
+// dynamic shared memory of finish_kernel: per warp, A scaled logits (then their exponentials) and
+// A running sums
+__host__ __device__ inline size_t finish_smem_bytes(int n_actions) {
+  return (size_t)kFinishWarps * 2 * (size_t)n_actions * sizeof(float);
 }
-__device__ __forceinline__ float block_reduce_sum(float v, float* red) {
+// blocks for nb boards per group
+__host__ __device__ inline unsigned finish_blocks(long long nb) {
+  return (unsigned)((nb + kFinishWarps - 1) / kFinishWarps);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = 0.f;
-  for (int i = 0; i < kFinishThreads / 32; ++i) r += red[i];
-  __syncthreads();
-  return r;
+  return v;
 }
-__device__ __forceinline__ int block_reduce_min_int(int v, int* red) {
+__device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  int r = red[0];
-  for (int i = 1; i < kFinishThreads / 32; ++i) r = min(r, red[i]);
-  __syncthreads();
-  return r;
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
 }
 
+// One warp per board, no block-wide synchronisation: lane l owns actions l, l + 32, ... (coalesced
+// reads); sums, the maximum and the running sum of the inverse-CDF draw go through shuffles.
 __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishParams p) {
-  __shared__ float s_z[kFinishMaxActions];
-  __shared__ float s_e[kFinishMaxActions];
-  __shared__ uint8_t s_legal[kFinishMaxActions];
-  __shared__ float s_red[kFinishThreads / 32];
-  __shared__ int s_redi[kFinishThreads / 32];
-  __shared__ float s_scan[kFinishThreads];
-
+  extern __shared__ float s_finish[];
   grid_dep_launch();
   grid_dep_wait();   // raw logits and value maps come from the last conv kernel
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.y;
-  const int t = blockIdx.x;
+  const long long t = (long long)blockIdx.x * kFinishWarps + warp;   // board inside the group
+  if (t >= p.nb) return;                                           // whole warps leave together
   const int A = p.n_actions;
+  float* s_e = s_finish + (size_t)warp * 2 * A;   // z = logit / T of legal cells (-inf otherwise), then exp(z - max)
+  float* s_c = s_e + A;                           // running sum of s_e in action order
   const long long ob = (long long)g * p.x_group_stride + p.board0 + t;  // board index in x / outputs
   const bool engine = p.logit_raw != nullptr;
   const int n = p.n;
   const int phase = (engine && p.orient) ? (p.orient[ob] & 7) : 0;
   const bool canon = phase != 0 && (p.flags & 2 /*C6_FLAG_INVERSE_MAP*/);
-  const long long raw0 = (long long)g * p.group_stride + (long long)t * p.board_stride;
+  const long long raw0 = (long long)g * p.group_stride + t * p.board_stride;
   const float bp = (engine && p.pol_bias) ? p.pol_bias[g] : 0.f;
+  const float inv_t = 1.0f / fmaxf(p.temperature, 1e-4f);
 
-  float vsum = 0.f;
-  for (int a = threadIdx.x; a < A; a += kFinishThreads) {
-    float raw;
+  // raw logit of output index a (canonical frame when `canon`, else the view frame)
+  auto raw_logit = [&](int a) {
+    if (!engine) return p.logits_in[ob * A + a];
+    const int view_cell = canon ? d4_forward(a, n, phase) : a;
+    const int vr = view_cell / n, vc = view_cell - vr * n;
+    return p.logit_raw[raw0 + vr * p.pitch + vc] + bp;
+  };
+
+  float vsum = 0.f, lmax = -INFINITY;
+  int nlegal = 0;
+#pragma unroll 4
+  for (int a = lane; a < A; a += 32) {
+    const float raw = raw_logit(a);
     bool legal;
     if (engine) {
-      // output index a lives in the canonical frame when `canon`, else in the view frame
-      const int view_cell = canon ? d4_forward(a, n, phase) : a;
-      const int vr = view_cell / n, vc = view_cell - vr * n;
-      raw = p.logit_raw[raw0 + vr * p.pitch + vc] + bp;
       const int orig_cell = (phase != 0 && !canon) ? d4_inverse(a, n, phase) : a;
       legal = input_value(p.in, ob, 0, orig_cell, A) == 0.f && input_value(p.in, ob, 1, orig_cell, A) == 0.f;
       if (p.vmap) {
@@ -282,74 +280,70 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
         vsum += p.vmap[raw0 + r * p.pitch + c];
       }
     } else {
-      raw = p.logits_in[ob * A + a];
       legal = p.legal_in[ob * A + a] != 0;
     }
-    s_z[a] = raw;
-    s_legal[a] = legal ? 1 : 0;
     if (p.logits_out) p.logits_out[ob * A + a] = ((p.flags & 1) && !legal) ? kFp32Min : raw;
+    const float z = legal ? raw * inv_t : -INFINITY;
+    s_e[a] = z;
+    lmax = fmaxf(lmax, z);
+    nlegal += legal ? 1 : 0;
   }
   if (engine && p.value_out) {
-    const float tot = block_reduce_sum(vsum, s_red);
-    if (threadIdx.x == 0) p.value_out[ob] = tanhf(tot / (float)A + (p.val_bias ? p.val_bias[g] : 0.f));
+    const float tot = warp_sum(vsum);
+    if (lane == 0) p.value_out[ob] = tanhf(tot / (float)A + (p.val_bias ? p.val_bias[g] : 0.f));
   }
   if (!p.do_sample) return;
-  __syncthreads();
 
   // z = mask(logits) / max(T, 1e-4); with no legal cell every z equals the fill: uniform.
-  const float inv_t = 1.0f / fmaxf(p.temperature, 1e-4f);
-  float lmax = -INFINITY;
-  int nlegal = 0;
-  for (int a = threadIdx.x; a < A; a += kFinishThreads)
-    if (s_legal[a]) { lmax = fmaxf(lmax, s_z[a] * inv_t); ++nlegal; }
-  const float any = block_reduce_sum((float)nlegal, s_red);
-  const bool none_legal = any == 0.f;
-  const float zmax = none_legal ? 0.f : block_reduce_max(lmax, s_red);
-
-  // contiguous segment per thread so that the prefix order is the action order
-  const int per = (A + kFinishThreads - 1) / kFinishThreads;
-  const int a0 = threadIdx.x * per, a1 = min(A, a0 + per);
-  float local = 0.f;
-  for (int a = a0; a < a1; ++a) {
-    const float e = none_legal ? 1.f : (s_legal[a] ? expf(s_z[a] * inv_t - zmax) : 0.f);
-    s_e[a] = e;
-    local += e;
+  const bool none_legal = __reduce_add_sync(0xffffffffu, nlegal) == 0;
+  const float zmax = none_legal ? 0.f : warp_max(lmax);
+  __syncwarp();
+  // running sums in action order: 32 actions per round, a shuffle scan inside the round
+  float carry = 0.f;
+  for (int a0 = 0; a0 < A; a0 += 32) {
+    const int a = a0 + lane;
+    float e = 0.f;
+    if (a < A) {
+      e = none_legal ? 1.f : expf(s_e[a] - zmax);   // exp(-inf) = 0 for occupied cells
+      s_e[a] = e;
+    }
+    float run = e;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, run, o);
+      if (lane >= o) run += up;
+    }
+    run += carry;
+    if (a < A) s_c[a] = run;
+    carry = __shfl_sync(0xffffffffu, run, 31);
   }
-  // inclusive block scan of `local`
-  s_scan[threadIdx.x] = local;
-  __syncthreads();
-  for (int o = 1; o < kFinishThreads; o <<= 1) {
-    const float add = threadIdx.x >= o ? s_scan[threadIdx.x - o] : 0.f;
-    __syncthreads();
-    s_scan[threadIdx.x] += add;
-    __syncthreads();
-  }
-  const float total = s_scan[kFinishThreads - 1];
-  const float before = s_scan[threadIdx.x] - local;
+  const float total = carry;
   const float u = board_uniform(p.seed, p.offset, (unsigned long long)(p.board_index0 + ob));
   const float target = u * total;
-  int cand = 0x7fffffff;
-  float run = before;
-  for (int a = a0; a < a1; ++a) {
-    run += s_e[a];
-    if (s_e[a] > 0.f && run > target) { cand = a; break; }
+  __syncwarp();
+  // first action with mass whose running sum exceeds the target
+  int pick = -1;
+  for (int a0 = 0; a0 < A && pick < 0; a0 += 32) {
+    const int a = a0 + lane;
+    const bool hit = a < A && s_e[a] > 0.f && s_c[a] > target;
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    if (m) pick = a0 + __ffs(m) - 1;
   }
-  int pick = block_reduce_min_int(cand, s_redi);
-  if (pick == 0x7fffffff) {
+  if (pick < 0) {
     // rounding left the target at or above the total: take the last cell with mass
-    int last = -1;
-    for (int a = a0; a < a1; ++a)
-      if (s_e[a] > 0.f) last = a;
-    __syncthreads();
-    pick = -block_reduce_min_int(-last, s_redi);
+    for (int a0 = ((A - 1) / 32) * 32; a0 >= 0 && pick < 0; a0 -= 32) {
+      const int a = a0 + lane;
+      const unsigned m = __ballot_sync(0xffffffffu, a < A && s_e[a] > 0.f);
+      if (m) pick = a0 + 31 - __clz(m);
+    }
   }
-  if (threadIdx.x == 0) {
+  if (lane == 0) {
     if (p.action_out) p.action_out[ob] = pick;
     // log-prob = z[a] - logsumexp(z) with logsumexp = max + log(sum exp(z - max)), as torch
     // computes it.  With no legal cell z is the fill everywhere: log(A) is absorbed by the fill
     // and the result is 0, which is what the reference's Categorical returns for that row.
     const float fill_z = fmaxf(kFp32Min * inv_t, -3.4028234663852886e38f);
-    const float zpick = none_legal ? fill_z : s_z[pick] * inv_t;
+    const float zpick = none_legal ? fill_z : raw_logit(pick) * inv_t;
     const float lse = (none_legal ? fill_z : zmax) + logf(total);
     if (p.logprob_out) p.logprob_out[ob] = zpick - lse;
   }

@@ -44,7 +44,7 @@ struct ConvTcParams {
   const float* bias;     // [G][n]
   const float* head_wp;  // [G][n] policy 1x1 weights (head only)
   const float* head_wv;  // [G][n] value 1x1 weights (head only)
-  float* logit_raw;      // [G * tiles_per_group * 128] (head only)
+  float* logit_raw;      // [G * group_pos] (head only)
   float* vmap;           // same shape (head only)
   int* status;
   long long* wait_cycles;  // nullable [8]: CTA 0's clocks {producer waits empty, MMA waits full, MMA waits acc empty, epilogue waits acc full, MMA issue blocks, MMA loop total, epilogue first TMEM fetch, epilogue arithmetic}
@@ -57,6 +57,9 @@ struct ConvTcParams {
   int bsize;             // board side n
   int nboards;           // boards per group in this pass
   int tiles_per_group;
+  int tiles_per_board;   // > 0: tile t covers positions (t / tpb) * slots + (t % tpb) * 128 ... + 127 of its group
+                         // (the all-padding tail of every board image is never computed); 0: tile t covers 128 t ...
+  int group_pos;         // positions reserved per group in the planes
   int ctas_per_group;
   int resident;
   int nstages;           // = nissue * spi
@@ -195,7 +198,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   const uint32_t tmem_base = *tmem_slot;
 
   const uint4* w_group = PAIR ? p.w_pair + ((size_t)group * 2 + crank) * (w_bytes / 16) : p.w + (size_t)group * (w_bytes / 16);
-  const long long group_row0 = (long long)p.front + (long long)group * p.tiles_per_group * 128;
+  const long long group_row0 = (long long)p.front + (long long)group * p.group_pos;
+  // first position (inside the group) of a tile
+  auto tile_pos = [&](int tile) {
+    return p.tiles_per_board ? (tile / p.tiles_per_board) * p.slots + (tile % p.tiles_per_board) * 128 : tile * 128;
+  };
 
   if (warp == 0 || warp == kProducer2Warp) {
     // ------------------------------ producers ------------------------------
@@ -229,7 +236,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         for (int iss = prod; iss < p.nissue; iss += nprod) {
           if (tb + iss >= ntl) break;
           const int tile = t_first + (tb + iss) * t_stride;
-          const long long row0 = group_row0 + (long long)tile * 128 - p.halo_rows;
+          const long long row0 = group_row0 + tile_pos(tile) - p.halo_rows;
           const int s = iss * p.spi + sl;
           const long long w0 = timing ? clock64() : 0;
           int got = 1;
@@ -447,13 +454,6 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const int nunits = p.n >> 4;
     bool ok = true;
     long long wait_tfull = 0, ep_ld = 0, ep_math = 0;
-    // position of this thread's row inside the group, tracked as (board, slot) without divisions
-    int board = 0, slot = 0;
-    {
-      const long long pos0 = (long long)(t_first + team * t_stride) * 128 + row;
-      board = (int)(pos0 / p.slots);
-      slot = (int)(pos0 - (long long)board * p.slots);
-    }
     for (int tcount = team; tcount < ntl && ok; tcount += nteams) {
       const int tile = t_first + tcount * t_stride;
       const int acc = tcount % p.nacc;
@@ -470,11 +470,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       tc::fence_after_sync();
       const long long e0 = timing ? clock64() : 0;
       long long e1 = e0, e2 = e0;
-      const long long pos = (long long)tile * 128 + row;
+      const int pos = tile_pos(tile) + row;            // position inside the group
+      const int board = pos / p.slots, slot = pos - board * p.slots;
       const int r = slot / p.wp, c = slot - r * p.wp;
       const bool valid = board < p.nboards && r < p.bsize && c < p.bsize;
-      slot += 128 * nteams * t_stride;   // this thread's row in the team's next tile
-      while (slot >= p.slots) { slot -= p.slots; ++board; }
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       uint4* out_row = p.out + group_row0 + pos;
       float pol = 0.f, val = 0.f;
@@ -557,7 +556,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         }
       }
       if (p.head) {
-        const long long o = (long long)group * p.tiles_per_group * 128 + pos;
+        const long long o = (long long)group * p.group_pos + pos;
         p.logit_raw[o] = valid ? pol : 0.f;
         p.vmap[o] = valid ? val : 0.f;
       }

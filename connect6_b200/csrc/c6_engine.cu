@@ -187,15 +187,25 @@ int dev_alloc(C6Engine* e, T** p, size_t count, bool zero, long long* tally) {
 
 struct Geometry {
   int tiles_per_group;
+  int tiles_per_board;        // > 0: tiles are aligned to board images and skip each image's all-padding tail
   long long group_pos;        // positions reserved per group
   int mrows_per_group;
 };
 
 Geometry geometry(const C6Engine* e, long long nb) {
   Geometry g;
-  g.tiles_per_group = (int)((nb * e->slots + 127) / 128);
+  // Positions of a board image that hold cells: rows 0..n-1 of pitch wp, i.e. (n-1)*wp + n of the
+  // wp*wp slots.  When whole 128-position tiles cover them in fewer positions than the image has
+  // (19x19: 3 tiles = 384 of 400), tiles are aligned to the images and the tail is never computed.
+  const int used = (e->n - 1) * e->wp + e->n;
+  const int tpb = (used + 127) / 128;
+  g.tiles_per_board = tpb * 128 < e->slots ? tpb : 0;
+  g.tiles_per_group = g.tiles_per_board ? (int)(nb * tpb) : (int)((nb * e->slots + 127) / 128);
   if (e->pair_mode) g.tiles_per_group += g.tiles_per_group & 1;   // CTA pairs take tiles two at a time
-  g.group_pos = (long long)g.tiles_per_group * 128;
+  // the odd tile added for a pair starts a board image of its own: reserve it
+  g.group_pos = g.tiles_per_board
+                    ? round_up_ll((long long)((g.tiles_per_group + tpb - 1) / tpb) * e->slots, 128)
+                    : (long long)g.tiles_per_group * 128;
   g.mrows_per_group = (int)round_up_ll(nb, e->stem_pair ? 256 : 128);   // CTA pairs take 256 boards per tile
   return g;
 }
@@ -329,7 +339,8 @@ int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long
   f.logprob_out = a.logprob;
   {
     ProfScope _ps(e, C6_KIND_FINISH, st);
-    launch_chain(finish_kernel, (unsigned)nb, (unsigned)e->G, kFinishThreads, 0, st, false, e->dependent_launch, f);
+    launch_chain(finish_kernel, finish_blocks(nb), (unsigned)e->G, kFinishThreads, finish_smem_bytes(f.n_actions), st, false,
+                 e->dependent_launch, f);
   }
   C6_LAUNCHED(e, "finish_kernel");
   return C6_OK;
@@ -421,6 +432,8 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.bsize = e->n;
     p.nboards = nb;
     p.tiles_per_group = g.tiles_per_group;
+    p.tiles_per_board = g.tiles_per_board;
+    p.group_pos = (int)g.group_pos;
     p.ctas_per_group = std::max(1, std::min(e->sms / e->G, g.tiles_per_group));
     if (lp.pair) p.ctas_per_group = std::max(2, p.ctas_per_group & ~1);   // whole pairs (tile counts are even)
     p.w_pair = e->wconv_pair[l];
@@ -990,7 +1003,7 @@ int c6_forward_noalloc(C6Engine* e, const void* x, int x_dtype, int64_t B, const
   f.flags = flags;
   f.logits_out = logits;
   f.value_out = value;
-  finish_kernel<<<dim3((unsigned)nb, 1), kFinishThreads, 0, st>>>(f);
+  finish_kernel<<<dim3(finish_blocks(nb), 1), kFinishThreads, finish_smem_bytes(f.n_actions), st>>>(f);
   C6_LAUNCHED(e, "finish_kernel");
   return C6_OK;
 }
@@ -1031,7 +1044,8 @@ int c6_sample_actions(const float* logits, const uint8_t* legal, int64_t B, int3
   f.board_index0 = board_index0;
   f.action_out = reinterpret_cast<long long*>(action);
   f.logprob_out = logprob;
-  finish_kernel<<<dim3((unsigned)B, 1), kFinishThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f);
+  finish_kernel<<<dim3(finish_blocks(B), 1), kFinishThreads, finish_smem_bytes(f.n_actions),
+                  reinterpret_cast<cudaStream_t>(stream)>>>(f);
   return cudaGetLastError() == cudaSuccess ? C6_OK : C6_ERR_CUDA;
 }
 

@@ -20,6 +20,7 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
                                        int nb,                 // boards of this pass per group
                                        long long group_stride, // boards between groups in x
                                        long long board0) {     // first board of this pass in a group
+  grid_dep_launch();
   const int g = blockIdx.y;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)kc * nb) return;
@@ -268,25 +269,43 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
 
   float vsum = 0.f, lmax = -INFINITY;
   int nlegal = 0;
-#pragma unroll 4
-  for (int a = lane; a < A; a += 32) {
-    const float raw = raw_logit(a);
-    bool legal;
-    if (engine) {
-      const int orig_cell = (phase != 0 && !canon) ? d4_inverse(a, n, phase) : a;
-      legal = input_value(p.in, ob, 0, orig_cell, A) == 0.f && input_value(p.in, ob, 1, orig_cell, A) == 0.f;
-      if (p.vmap) {
-        const int r = a / n, c = a - r * n;
-        vsum += p.vmap[raw0 + r * p.pitch + c];
+  // All loads of a block of 8 x 32 actions are issued before any is used: the kernel is bound by
+  // memory latency, and a load that waits for the previous one's value doubles it.
+  constexpr int kJ = 8;
+  for (int base = 0; base < A; base += kJ * 32) {
+    float raw[kJ], occ0[kJ], occ1[kJ], vm[kJ];
+#pragma unroll
+    for (int j = 0; j < kJ; ++j) {
+      const int a = base + j * 32 + lane;
+      raw[j] = occ0[j] = occ1[j] = vm[j] = 0.f;
+      if (a < A) {
+        raw[j] = raw_logit(a);
+        if (engine) {
+          const int orig_cell = (phase != 0 && !canon) ? d4_inverse(a, n, phase) : a;
+          occ0[j] = input_value(p.in, ob, 0, orig_cell, A);
+          occ1[j] = input_value(p.in, ob, 1, orig_cell, A);
+          if (p.vmap) {
+            const int r = a / n, c = a - r * n;
+            vm[j] = p.vmap[raw0 + r * p.pitch + c];
+          }
+        } else {
+          occ0[j] = p.legal_in[ob * A + a] != 0 ? 0.f : 1.f;
+        }
       }
-    } else {
-      legal = p.legal_in[ob * A + a] != 0;
     }
-    if (p.logits_out) p.logits_out[ob * A + a] = ((p.flags & 1) && !legal) ? kFp32Min : raw;
-    const float z = legal ? raw * inv_t : -INFINITY;
-    s_e[a] = z;
-    lmax = fmaxf(lmax, z);
-    nlegal += legal ? 1 : 0;
+#pragma unroll
+    for (int j = 0; j < kJ; ++j) {
+      const int a = base + j * 32 + lane;
+      if (a < A) {
+        const bool legal = occ0[j] == 0.f && occ1[j] == 0.f;
+        vsum += vm[j];
+        if (p.logits_out) p.logits_out[ob * A + a] = ((p.flags & 1) && !legal) ? kFp32Min : raw[j];
+        const float z = legal ? raw[j] * inv_t : -INFINITY;
+        s_e[a] = z;
+        lmax = fmaxf(lmax, z);
+        nlegal += legal ? 1 : 0;
+      }
+    }
   }
   if (engine && p.value_out) {
     const float tot = warp_sum(vsum);

@@ -144,6 +144,17 @@ struct ProfScope {
   }
 };
 
+// The finishing kernel stages a board per warp in shared memory and wants many resident blocks per
+// SM; without a hint the driver may pick a shared-memory carve-out that fits only a few.  Function attributes are
+// per device context, so this runs once per device a kernel is first used on.
+void prefer_shared_memory() {
+  static bool done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+  done[dev] = true;
+  cudaFuncSetAttribute(finish_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 // Launch with optional 2-CTA clusters and optional programmatic dependent launch (the kernel then
 // orders itself behind its predecessor with grid_dep_wait(), so its prologue -- barrier setup, TMEM
 // allocation, resident weights -- overlaps the predecessor's tail).
@@ -641,6 +652,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   e->have.assign((size_t)e->G * (e->L + 2), 0);
   e->h_bias.assign(e->L, std::vector<float>());
 
+  prefer_shared_memory();
   int rc;
   if ((rc = dev_alloc(e, &e->status_dev, 1, true, nullptr))) return bail(rc, "");
   if ((rc = dev_alloc(e, &e->wait_dev, 8 + 2048, true, nullptr))) return bail(rc, "");
@@ -1030,6 +1042,7 @@ int c6_sample_actions(const float* logits, const uint8_t* legal, int64_t B, int3
   if (B < 0 || A <= 0 || A > kFinishMaxActions) return C6_ERR_ARG;
   if (B == 0) return C6_OK;
   if (!logits || !legal || !action) return C6_ERR_ARG;
+  prefer_shared_memory();
   FinishParams f{};
   f.logits_in = logits;
   f.legal_in = legal;

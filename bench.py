@@ -38,7 +38,7 @@ HEAD_MACS = 69_312
 INPUT_BUFFERS = 5                       # 5 x 35.5 MB of inputs rotate: larger than the 126 MB L2
 # DRAM traffic of conv_tc_kernel per launch, from the ncu capture summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the 7 launches of one step).
-CONV_TRAFFIC_BYTES_PER_LAUNCH = 641_000_000   # 160.2 MB measured at B = 2048, scaled by boards to 8192
+CONV_TRAFFIC_BYTES_PER_LAUNCH = 633_000_000   # 158.3 MB measured at B = 2048, scaled by boards to 8192
 WEIGHT_SEED = 42
 CPU_SAMPLE_BOARDS = 256
 

@@ -207,6 +207,25 @@ def test_chunked_passes_equal_single_pass(cuda_device):
     assert small.status() == 0
 
 
+def test_dependent_launch_off_gives_identical_results(cuda_device, monkeypatch):
+    """The kernel chain gives bit-identical results whether each kernel's prologue overlaps its
+    predecessor (programmatic dependent launch, the default) or launches are fully serialised."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    m, params = _default_model("bf16", cuda_device)
+    x = torch.from_numpy(generate_planes(900, 700)).to(cuda_device)
+    base = m.engine_for(cuda_device).forward_step(x, seed=3, offset=1, want_logits=True)
+    monkeypatch.setenv("C6_DEPENDENT_LAUNCH", "0")
+    plain = Engine(cuda_device, 19, m.kernels, m.channels, 1, "bf16")
+    plain.load_state_dict(params)
+    for _ in range(3):   # back-to-back steps: the chain of one step follows the previous one's directly
+        got = plain.forward_step(x, seed=3, offset=1, want_logits=True)
+        again = m.engine_for(cuda_device).forward_step(x, seed=3, offset=1, want_logits=True)
+    for a, b, c in zip(base, got, again):
+        assert torch.equal(a, b) and torch.equal(a, c)
+    assert plain.status() == 0
+
+
 def test_empty_and_bad_inputs(cuda_device):
     m, _ = _default_model("bf16", cuda_device)
     with torch.inference_mode():

@@ -8,40 +8,80 @@
 namespace c6 {
 
 // ------------------------------------------------------------------------------------------------
+// K order of the stem GEMM.  Chunks of 8: [planes 0 and 1: k = ci*cells + cell; then two slots that
+// carry the third plane's "level"; zero padded to kc_short chunks][plane 2: cell, zero padded].
+// The third plane of a real position is constant over the board (connect6/vector_env.py:212-216).
+// Every board's third plane is split into a level c (its first cell) and a residual x2 - c: the
+// level rides in the two extra K slots against the row sums of the plane-2 Toeplitz block (split
+// into a bf16 high and low part), the residual in the plane-2 chunks.  When every residual of a pass
+// is zero -- always, for real positions -- the GEMM stops after the first kc_short chunks.
+// ------------------------------------------------------------------------------------------------
+// kind: 0 = zero padding, 1 = input element (ci, cell), 2 = level slot (cell = 0: high part, 1: low part)
+__host__ __device__ __forceinline__ int stem_k_decode(int chunk, int e, int kc_short, int cells, int& ci, int& cell) {
+  if (chunk < kc_short) {
+    const int k = chunk * 8 + e;
+    if (k < 2 * cells) {
+      ci = k >= cells ? 1 : 0;
+      cell = k - ci * cells;
+      return 1;
+    }
+    ci = 2;
+    cell = k - 2 * cells;
+    return k < 2 * cells + 2 ? 2 : 0;
+  }
+  cell = (chunk - kc_short) * 8 + e;
+  ci = 2;
+  return cell < cells ? 1 : 0;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Input packing for the tensor-core stem: x [boards,3,n,n] (fp32 or bf16, NCHW) -> 16-byte rows of
-// 8 bf16 (k = ci*n*n + view cell) laid out [board tile of 128][K chunk][128 boards], so that all K
-// chunks of one pipeline stage of one board tile are contiguous and travel in ONE bulk copy.  A board with orientation
+// 8 bf16 laid out [board tile of 128][K chunk][128 boards], so that all K chunks of one pipeline
+// stage of one board tile are contiguous and travel in ONE bulk copy.  A board with orientation
 // `phase` is presented as view.flat[j] = x.flat[d4_inverse(j)] (connect6/train.py:222-230).
+// Stores `epoch` into *p2_epoch when some board's third plane is not constant.
 // Grid: (ceil(kc*nb/256), G); one thread per (board, chunk).
 // ------------------------------------------------------------------------------------------------
 __global__ void pack_stem_input_kernel(const InputSrc in,
                                        const uint8_t* __restrict__ orient, uint4* __restrict__ xk,
-                                       long long mrows, int mrows_per_group, int kc, int n,
+                                       long long mrows, int mrows_per_group, int kc, int kc_short, int n,
                                        int nb,                 // boards of this pass per group
                                        long long group_stride, // boards between groups in x
-                                       long long board0) {     // first board of this pass in a group
-  grid_dep_launch();
+                                       long long board0,       // first board of this pass in a group
+                                       unsigned int epoch, unsigned int* __restrict__ p2_epoch) {
+  // No early launch of the stem from here: its CTAs (576 threads, most of the register file) would
+  // move in beside this kernel's blocks and starve them.
   const int g = blockIdx.y;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)kc * nb) return;
   const int t = (int)(idx % nb);
   const int c = (int)(idx / nb);
-  const int cells = n * n, ktot = 3 * cells;
+  const int cells = n * n;
   const long long src_board = (long long)g * group_stride + board0 + t;
   const int phase = orient ? (orient[src_board] & 7) : 0;
+  // level of the third plane: needed by the chunk that holds the level slots and by the plane-2 chunks
+  const bool wants_level = c >= kc_short || (c + 1) * 8 > 2 * cells;
+  const float level = wants_level ? input_value(in, src_board, 2, 0, cells) : 0.f;
   float v[8];
+  bool varies = false;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const int k = c * 8 + j;
+    int ci, cell;
+    const int kind = stem_k_decode(c, j, kc_short, cells, ci, cell);
     float val = 0.f;
-    if (k < ktot) {
-      const int ci = k / cells;
-      int cell = k - ci * cells;
+    if (kind == 1) {
       if (phase) cell = d4_inverse(cell, n, phase);
       val = input_value(in, src_board, ci, cell, cells);
+      if (ci == 2) {
+        val -= level;
+        varies |= val != 0.f;
+      }
+    } else if (kind == 2) {
+      val = level;
     }
     v[j] = val;
   }
+  if (varies) atomicExch(p2_epoch, epoch);
   uint4 o;
   o.x = pack_bf16x2(v[0], v[1]);
   o.y = pack_bf16x2(v[2], v[3]);
@@ -131,31 +171,45 @@ __global__ void pack_conv_weights_pair_kernel(const float* __restrict__ w, uint4
   out[idx] = o;
 }
 
-// Stem -> Toeplitz rows (row o = cell_out*c1 + co, element e: k = kc*8+e) laid out
+// Stem -> Toeplitz rows (row o = cell_out*c1 + co, element e of chunk c: see stem_k_decode) laid out
 // [output tile of nt][half][K chunk][nt/halves rows]: the K chunks of one pipeline stage of one
 // (tile, half) are contiguous.  halves = 2 when CTA pairs split the tile's rows, else 1.
+__device__ __forceinline__ float stem_toeplitz_value(const float* __restrict__ w, int cout, int kside, int n, int co,
+                                                     int cell_out, int ci, int cell_in) {
+  const int pad = kside >> 1;
+  const int ro = cell_out / n, cc = cell_out - ro * n;
+  const int ri = cell_in / n, cin_c = cell_in - ri * n;
+  const int ky = ri - ro + pad, kx = cin_c - cc + pad;
+  if (co >= cout || ky < 0 || ky >= kside || kx < 0 || kx >= kside) return 0.f;
+  return w[(((size_t)co * 3 + ci) * kside + ky) * kside + kx];
+}
+
 __global__ void pack_stem_toeplitz_kernel(const float* __restrict__ w, uint4* __restrict__ out,
-                                          int cout, int kside, int n, int c1, int kc, int ntot, int nt, int halves) {
+                                          int cout, int kside, int n, int c1, int kc, int kc_short, int ntot, int nt,
+                                          int halves) {
   const long long total = (long long)kc * ntot;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int o = (int)(idx % ntot);
   const int c = (int)(idx / ntot);
-  const int cells = n * n, pad = kside >> 1;
+  const int cells = n * n;
   const int cell_out = o / c1, co = o - cell_out * c1;
-  const int ro = cell_out / n, cc = cell_out - ro * n;
   float v[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    const int k = c * 8 + e;
+    int ci, cell_in;
+    const int kind = cell_out < cells ? stem_k_decode(c, e, kc_short, cells, ci, cell_in) : 0;
     float val = 0.f;
-    if (k < 3 * cells && cell_out < cells && co < cout) {
-      const int ci = k / cells;
-      const int cell_in = k - ci * cells;
-      const int ri = cell_in / n, cin_c = cell_in - ri * n;
-      const int ky = ri - ro + pad, kx = cin_c - cc + pad;
-      if (ky >= 0 && ky < kside && kx >= 0 && kx < kside)
-        val = w[(((size_t)co * 3 + ci) * kside + ky) * kside + kx];
+    if (kind == 1) {
+      val = stem_toeplitz_value(w, cout, kside, n, co, cell_out, ci, cell_in);
+    } else if (kind == 2) {
+      // what a third plane of constant value 1 adds to this output: the sum of its plane-2 weights as
+      // the tensor cores see them (bf16), carried as a bf16 high part and the bf16 of the remainder
+      float sum = 0.f;
+      for (int ck = 0; ck < cells; ++ck)
+        sum += __bfloat162float(__float2bfloat16_rn(stem_toeplitz_value(w, cout, kside, n, co, cell_out, 2, ck)));
+      const float hi = __bfloat162float(__float2bfloat16_rn(sum));
+      val = cell_in == 0 ? hi : sum - hi;
     }
     v[e] = val;
   }

@@ -57,6 +57,9 @@ struct C6Engine {
   std::vector<LayerPlan> lp;
   int cmax_p = 0, cmax = 0;
   // stem GEMM plan
+  int kc_short = 0;                 // stem K chunks of input planes 0 and 1; kc0 - kc_short chunks hold plane 2
+  unsigned int stem_epoch = 0;      // pass counter: tells the stem whether THIS pass saw a non-constant third plane
+  unsigned int* p2_epoch = nullptr; // device word written by the input pack kernel
   int kc0 = 0, nt = 0, ntiles = 0, ntot = 0, stem_stages = 0, stem_smem = 0, stem_acc_stride = 0,
       stem_tmem_cols = 0, stem_kcs = 4, stem_pair = 0;
   // weights
@@ -371,7 +374,8 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     const long long total = (long long)e->kc0 * nb;
     ProfScope _ps(e, C6_KIND_PACK, st);
     pack_stem_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
-        input_of(a), a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->n, nb, a.T, t0);
+        input_of(a), a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->kc_short, e->n, nb, a.T, t0,
+        ++e->stem_epoch, e->p2_epoch);
     C6_LAUNCHED(e, "pack_stem_input_kernel");
   }
   int cur = 0;
@@ -389,6 +393,9 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.front = e->front;
     p.group_pos = (int)g.group_pos;
     p.kc = e->kc0;
+    p.kc_short = e->kc_short;
+    p.p2_epoch = e->p2_epoch;
+    p.epoch = e->stem_epoch;
     p.kcs = e->stem_kcs;
     p.ntot = e->ntot;
     p.nt = e->nt;
@@ -577,6 +584,7 @@ int c6_destroy(C6Engine* e) {
   cudaDeviceSynchronize();
   free_workspace(e);
   cudaFree(e->wt);
+  cudaFree(e->p2_epoch);
   for (auto p : e->wconv) cudaFree(p);
   for (auto p : e->wconv_pair) cudaFree(p);
   for (auto p : e->bias) cudaFree(p);
@@ -668,7 +676,6 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     if (e->cmax_p > 256) return bail(C6_ERR_UNSUPPORTED, "bf16 mode supports at most 256 channels per layer");
     // stem GEMM
     const int c1 = e->lp[0].cout_p;
-    e->kc0 = round_up(3 * e->cells, 32) / 8;
     const int cpt = std::max(1, 256 / c1);
     e->nt = c1 * cpt;
     e->ntiles = (e->cells + cpt - 1) / cpt;
@@ -676,13 +683,17 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     // CTA pairs (each stages half of the Toeplitz rows, 64 K per stage) when at least one pair exists
     e->stem_pair = e->sms >= 2 ? 1 : 0;
     e->stem_kcs = e->stem_pair ? 8 : 4;
-    e->kc0 = round_up(e->kc0, e->stem_kcs);
+    // K = [planes 0 and 1 | plane 2], each part padded to whole pipeline stages
+    e->kc_short = round_up(2 * e->cells + 2, 8 * e->stem_kcs) / 8;   // + the two level slots of the third plane
+    e->kc0 = e->kc_short + round_up(e->cells, 8 * e->stem_kcs) / 8;
     const int sstage = e->stem_kcs * 128 * 16 + e->stem_kcs * (e->stem_pair ? e->nt / 2 : e->nt) * 16;
-    e->stem_stages = std::min(kStemMaxStages, (kSmemLimit - 128 - kStemSmemHeader) / sstage);
-    e->stem_smem = 128 + kStemSmemHeader + e->stem_stages * sstage;
+    e->stem_stages = std::min(kStemMaxStages, (kSmemLimit - 128 - kStemSmemHeader - kStemPatchBytes) / sstage);
+    if (e->stem_stages < 2) return bail(C6_ERR_UNSUPPORTED, "the stem's pipeline stages do not fit shared memory");
+    e->stem_smem = 128 + kStemSmemHeader + e->stem_stages * sstage + kStemPatchBytes;
     e->stem_acc_stride = pow2_ceil(e->nt);
     e->stem_tmem_cols = 2 * e->stem_acc_stride;
     if ((rc = dev_alloc(e, &e->wt, (size_t)e->G * e->kc0 * e->ntot, true, nullptr))) return bail(rc, "");
+    if ((rc = dev_alloc(e, &e->p2_epoch, 1, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->bias[0], (size_t)e->G * c1, true, nullptr))) return bail(rc, "");
     // k x k layers
     e->pair_mode = e->sms / e->G >= 2;   // at least one CTA pair per group
@@ -813,7 +824,8 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
     if (layer == 0) {
       const long long total = (long long)e->kc0 * e->ntot;
       pack_stem_toeplitz_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-          w, e->wt + (size_t)group * e->kc0 * e->ntot, p.cout, p.k, e->n, p.cout_p, e->kc0, e->ntot, e->nt, e->stem_pair ? 2 : 1);
+          w, e->wt + (size_t)group * e->kc0 * e->ntot, p.cout, p.k, e->n, p.cout_p, e->kc0, e->kc_short, e->ntot, e->nt,
+          e->stem_pair ? 2 : 1);
       C6_LAUNCHED(e, "pack_stem_toeplitz_kernel");
     } else {
       const long long total = (long long)p.w_rows_per_group;

@@ -35,6 +35,12 @@ struct StemTcParams {
   int front;
   int group_pos;       // positions reserved per group in the activation planes
   int kc;              // K chunks (multiple of kcs)
+  int kc_short;        // chunks of input planes 0 and 1 and the third plane's level (multiple of kcs)
+  // The remaining chunks hold the third plane's residual (plane minus its level).  When
+  // *p2_epoch != epoch every residual of this pass is zero -- the plane is constant on every board --
+  // and the GEMM walks only kc_short chunks; otherwise all kc.
+  const unsigned int* p2_epoch;
+  unsigned int epoch;
   int kcs;             // K chunks per pipeline stage: 4 or 8
   int ntot;            // rows per T plane (= ntiles * nt)
   int nt;              // outputs per tile (multiple of 32, <= 256)
@@ -47,7 +53,9 @@ struct StemTcParams {
   int acc_stride, tmem_cols;
 };
 
-constexpr int kStemThreads = 320;  // producer warp, MMA warp, eight epilogue warps
+constexpr int kStemEpiParts = 4;   // epilogue warps per TMEM lane quadrant: they take the 16-column units round robin
+constexpr int kStemPatchBytes = 4 * kStemEpiParts * 4096;  // one 4 KB transposition patch per epilogue warp, behind the stages
+constexpr int kStemThreads = 32 * (2 + 4 * kStemEpiParts);  // producer warp, MMA warp, sixteen epilogue warps
 constexpr int kStemSmemHeader = 2048;
 constexpr int kStemMaxStages = 12;
 
@@ -76,7 +84,12 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
   const uint32_t b_plane = (uint32_t)nloc * 16u;
   const uint32_t a_bytes = (uint32_t)p.kcs * a_plane, b_bytes = (uint32_t)p.kcs * b_plane;
   const uint32_t stage_bytes = a_bytes + b_bytes;    // multiples of 128 by construction
-  const int ksteps = p.kc / p.kcs;
+  // pipeline steps per tile, known only once the pack kernel in front of this one has finished
+  auto steps_per_tile = [&](bool& short_k) {
+    grid_dep_wait();
+    short_k = __ldcg(p.p2_epoch) != p.epoch;
+    return (short_k ? p.kc_short : p.kc) / p.kcs;
+  };
 
   // work items: (group, board tile, output tile), output tile fastest; in pair mode a pair owns a
   // range of (group, board-tile PAIR, output tile) items and CTA r takes board tile 2*mp + r
@@ -102,7 +115,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     }
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(bar_tfull(a), 1);
-      tc::mbar_init(bar_tempty(a), 8 * both);
+      tc::mbar_init(bar_tempty(a), 4 * kStemEpiParts * both);
     }
     tc::mbar_init(bar_drain, 1);
     *abort_flag = 0;
@@ -119,7 +132,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     }
   }
   if (warp >= 2) {
-    for (int i = threadIdx.x - 64; i < p.groups * p.c1 && i < 320; i += 256) s_bias[i] = 0.5f * p.bias[i];  // h = x/2
+    for (int i = threadIdx.x - 64; i < p.groups * p.c1 && i < 320; i += kStemThreads - 64) s_bias[i] = 0.5f * p.bias[i];  // h = x/2
   }
   tc::fence_before_sync();
   if (PAIR) tc::cluster_sync(); else __syncthreads();
@@ -142,7 +155,8 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     bool ok = true;
     int s = 0;
     uint32_t ph = 0;
-    grid_dep_wait();   // the input rows come from the pack kernel in front of this one
+    bool short_k;
+    const int ksteps = steps_per_tile(short_k);   // waits: the input rows come from the pack kernel in front of this one
     for (long long item = i_begin; item < i_end && ok; ++item) {
       int g, mt, nt_i;
       decode(item, g, mt, nt_i);
@@ -194,6 +208,8 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     int tcount = 0;
     const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
     long long wait_full = 0, wait_acc = 0, issue_clk = 0;
+    bool short_k;
+    const int ksteps = steps_per_tile(short_k);
     const long long loop_t0 = clock64();
     for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
       const int acc = tcount & 1;
@@ -262,6 +278,8 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
+    bool short_k;
+    const int ksteps = steps_per_tile(short_k);
     for (long long item = i_begin; item < i_end && ok; ++item) {
       for (int ks = 0; ks < ksteps; ++ks) {
         if (!tc::mbar_wait_warp(bar_full(s), ph, abort_flag, 0)) {
@@ -276,15 +294,28 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     }
   } else if (warp >= 2) {
     // ------------------------------ epilogue ------------------------------
-    // Eight warps; the two warps of a TMEM lane quadrant alternate over 16-column units.  A unit is
-    // 16 consecutive channels of one output cell (c1 is a multiple of 32, so units never straddle
-    // cells): h = 0.5*acc + 0.5*bias, y = h + h*tanh(h), two 16-byte stores.
+    // Sixteen warps: the four warps ("parts") of a TMEM lane quadrant share its 32 boards.  A board's
+    // tile output is nt/8 pieces of 16 bytes = 8 channels of one cell, ordered plane-major
+    // (piece = chunk plane * cells-per-tile + cell); a part owns a contiguous quarter of them, so its
+    // pieces of one chunk plane are consecutive cells = consecutive rows of that plane.  Scattering them
+    // straight from the TMEM layout (lane = board: 32 addresses 6.4 KB apart per store instruction)
+    // made the stores -- 11.8 M separate 16-byte requests per launch -- the kernel's bottleneck
+    // (measured: 0.229 ms with them, 0.124 ms without).  Instead every warp parks its pieces in a
+    // private, XOR-swizzled 4 KB patch of shared memory and writes them out with lanes running along
+    // the consecutive cells: up to 128 contiguous bytes per (board, plane), full sectors.
+    // h = 0.5*acc + 0.5*bias, y = h + h*tanh(h).
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
-    grid_dep_wait();
+    const int part = (warp - 2) >> 2;
+    bool short_k;
+    steps_per_tile(short_k);
     const int row = quad * 32 + lane;
-    const int nunits = p.nt >> 4;
     const int cells = p.bsize * p.bsize;
+    const int cpt = p.nt / p.c1;                    // cells per tile
+    const int npieces = p.nt >> 3;                  // pieces per board per tile
+    const int per_part = (npieces + kStemEpiParts - 1) / kStemEpiParts;   // <= 8
+    const int piece0 = part * per_part;
+    const int my_pieces = max(0, min(per_part, npieces - piece0));
+    uint4* patch = reinterpret_cast<uint4*>(s_stage + (size_t)p.nstages * stage_bytes) + (size_t)(warp - 2) * 256;
     bool ok = true;
     int tcount = 0;
     for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
@@ -301,17 +332,21 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       const int board = mt * 128 + row;
       const bool bvalid = board < p.nboards;
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
-      const long long board_row = (long long)p.front + (long long)g * p.group_pos + (long long)board * p.slots;
       const float* gbias = p.bias + (size_t)g * p.c1;
-      // this warp's units: half, half+2, ...; four are fetched from TMEM per wait so that their
-      // latencies overlap, and the accumulator is released as soon as the last fetch has landed
-      for (int u0 = half; u0 < nunits; u0 += 8) {
-        uint32_t v[4][16];
+      // fetch this part's pieces (8 accumulator columns each), four per wait; the accumulator goes
+      // back to the MMA warp as soon as the last fetch has landed
+      for (int i0 = 0; i0 < per_part; i0 += 4) {
+        uint32_t v[4][8];
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-          if (u0 + 2 * b < nunits) tc::tmem_ld16(taddr + (uint32_t)((u0 + 2 * b) * 16), v[b]);
+        for (int b = 0; b < 4; ++b) {
+          const int pc = piece0 + i0 + b;
+          if (i0 + b < my_pieces) {
+            const int q = pc / cpt, cl = pc - q * cpt;
+            tc::tmem_ld8(taddr + (uint32_t)(cl * p.c1 + q * 8), v[b]);
+          }
+        }
         tc::tmem_wait_ld();
-        if (u0 + 8 >= nunits) {
+        if (i0 + 4 >= per_part) {
           tc::fence_before_sync();
           __syncwarp();
           if (lane == 0) {
@@ -320,32 +355,38 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
         }
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          const int u = u0 + 2 * b;
-          if (u >= nunits) continue;
-          const int o = nt_i * p.nt + u * 16;  // first output column of this unit
-          const int cell = o / p.c1;
-          const int co0 = o - cell * p.c1;
-          if (bvalid && cell < cells) {
-            const int r = cell / p.bsize, c = cell - r * p.bsize;
-            uint4* dst = p.out + (size_t)(co0 >> 3) * p.plane_rows + board_row + r * p.wp + c;
-            float y[16];
+          const int pc = piece0 + i0 + b;
+          if (i0 + b >= my_pieces) continue;
+          const int q = pc / cpt, cl = pc - q * cpt;
+          float y[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float hb = bias_in_smem ? s_bias[g * p.c1 + co0 + j] : 0.5f * gbias[co0 + j];
-              y[j] = silu_from_half(fmaf(__uint_as_float(v[b][j]), 0.5f, hb));
-            }
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-              uint4 q;
-              q.x = pack_bf16x2(y[8 * k + 0], y[8 * k + 1]);
-              q.y = pack_bf16x2(y[8 * k + 2], y[8 * k + 3]);
-              q.z = pack_bf16x2(y[8 * k + 4], y[8 * k + 5]);
-              q.w = pack_bf16x2(y[8 * k + 6], y[8 * k + 7]);
-              dst[(size_t)k * p.plane_rows] = q;
-            }
+          for (int j = 0; j < 8; ++j) {
+            const float hb = bias_in_smem ? s_bias[g * p.c1 + q * 8 + j] : 0.5f * gbias[q * 8 + j];
+            y[j] = silu_from_half(fmaf(__uint_as_float(v[b][j]), 0.5f, hb));
           }
+          uint4 o;
+          o.x = pack_bf16x2(y[0], y[1]);
+          o.y = pack_bf16x2(y[2], y[3]);
+          o.z = pack_bf16x2(y[4], y[5]);
+          o.w = pack_bf16x2(y[6], y[7]);
+          patch[lane * 8 + ((i0 + b) ^ (lane & 7))] = o;   // [board][piece], swizzled against bank conflicts
         }
       }
+      __syncwarp();
+      // write out: 8 rounds of 4 boards x 8 pieces; lanes 8k..8k+7 hold consecutive pieces of one board
+      const long long tile_row0 = (long long)p.front + (long long)g * p.group_pos + (long long)(mt * 128 + quad * 32) * p.slots;
+#pragma unroll 2
+      for (int rd = 0; rd < 8; ++rd) {
+        const int bl = rd * 4 + (lane >> 3), i = lane & 7;
+        const int pc = piece0 + i;
+        const int q = pc / cpt, cl = pc - q * cpt;
+        const int cell = nt_i * cpt + cl;
+        if (i < my_pieces && mt * 128 + quad * 32 + bl < p.nboards && cell < cells) {
+          const int r = cell / p.bsize, c = cell - r * p.bsize;
+          p.out[(size_t)q * p.plane_rows + tile_row0 + (long long)bl * p.slots + r * p.wp + c] = patch[bl * 8 + (i ^ (bl & 7))];
+        }
+      }
+      __syncwarp();   // the patch is reused by the next tile
     }
   }
 

@@ -226,6 +226,33 @@ def test_dependent_launch_off_gives_identical_results(cuda_device, monkeypatch):
     assert plain.status() == 0
 
 
+def test_constant_third_plane_shortcut_matches_full_product(cuda_device):
+    """Boards whose third plane is constant take the short stem product (two planes through the
+    tensor cores, the third as value x row sum); one board with a varying third plane in the batch
+    switches the whole pass to the full product.  Both agree to within bf16 noise, and both stay
+    within the oracle tolerance; arbitrary constants (not only 0/1) are handled."""
+    from connect6_b200.boards import generate_planes
+    m, params = _default_model("bf16", cuda_device)
+    x = torch.from_numpy(generate_planes(5000, 96))
+    x[:, 2] = torch.linspace(-1.5, 2.0, 96).view(96, 1, 1)          # constant per board, arbitrary values
+    odd = x[:1].clone()
+    odd[0, 2, 3, 4] += 0.25                                          # one cell breaks the constancy
+    eng = m.engine_for(cuda_device)
+    short_l, short_v = eng.forward(x.to(cuda_device))
+    full_l, full_v = eng.forward(torch.cat((x, odd)).to(cuda_device))
+    ref_l, ref_v = _oracle64(torch.cat((x, odd)), params)
+    sigma = ref_l.std()
+    assert np.abs(full_l.cpu().numpy() - ref_l).max() < 0.12 * sigma
+    assert np.abs(short_l.cpu().numpy() - ref_l[:96]).max() < 0.12 * sigma
+    assert np.abs(short_v.cpu().numpy() - ref_v[:96]).max() < 3e-2
+    # the full product sees the plane value rounded to bf16, the short one keeps it in fp32
+    assert (short_l - full_l[:96]).abs().max().item() < 0.15 * sigma
+    exact = [i for i in range(96) if float(x[i, 2, 0, 0]) == float(x[i, 2, 0, 0].bfloat16())]
+    assert len(exact) >= 2 and (short_l[exact] - full_l[exact]).abs().max().item() < 0.03 * sigma
+    assert not torch.equal(full_l[96], full_l[0])                    # the odd board is really different
+    assert eng.status() == 0
+
+
 def test_empty_and_bad_inputs(cuda_device):
     m, _ = _default_model("bf16", cuda_device)
     with torch.inference_mode():

@@ -49,8 +49,7 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
                                        long long group_stride, // boards between groups in x
                                        long long board0,       // first board of this pass in a group
                                        unsigned int epoch, unsigned int* __restrict__ p2_epoch) {
-  // No early launch of the stem from here: its CTAs (576 threads, most of the register file) would
-  // move in beside this kernel's blocks and starve them.
+  grid_dep_launch();
   const int g = blockIdx.y;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)kc * nb) return;
@@ -62,8 +61,9 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
   // level of the third plane: needed by the chunk that holds the level slots and by the plane-2 chunks
   const bool wants_level = c >= kc_short || (c + 1) * 8 > 2 * cells;
   const float level = wants_level ? input_value(in, src_board, 2, 0, cells) : 0.f;
+  // all eight loads are issued before any value is used (the kernel is bound by memory latency)
   float v[8];
-  bool varies = false;
+  int kinds[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     int ci, cell;
@@ -72,14 +72,19 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
     if (kind == 1) {
       if (phase) cell = d4_inverse(cell, n, phase);
       val = input_value(in, src_board, ci, cell, cells);
-      if (ci == 2) {
-        val -= level;
-        varies |= val != 0.f;
-      }
-    } else if (kind == 2) {
-      val = level;
     }
     v[j] = val;
+    kinds[j] = kind == 1 && ci == 2 ? 3 : kind;   // 3: element of the third plane
+  }
+  bool varies = false;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (kinds[j] == 3) {
+      v[j] -= level;
+      varies |= v[j] != 0.f;
+    } else if (kinds[j] == 2) {
+      v[j] = level;
+    }
   }
   if (varies) atomicExch(p2_epoch, epoch);
   uint4 o;

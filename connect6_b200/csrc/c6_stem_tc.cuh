@@ -308,7 +308,6 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     const int part = (warp - 2) >> 2;
     bool short_k;
     steps_per_tile(short_k);
-    const int row = quad * 32 + lane;
     const int cells = p.bsize * p.bsize;
     const int cpt = p.nt / p.c1;                    // cells per tile
     const int npieces = p.nt >> 3;                  // pieces per board per tile
@@ -316,6 +315,12 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     const int piece0 = part * per_part;
     const int my_pieces = max(0, min(per_part, npieces - piece0));
     uint4* patch = reinterpret_cast<uint4*>(s_stage + (size_t)p.nstages * stage_bytes) + (size_t)(warp - 2) * 256;
+    // cells per tile is a power of two (256 / c1 rounded down to one): piece -> (chunk plane, cell)
+    // is a shift and a mask
+    const int lcpt = 31 - __clz(cpt);
+    const int wi = lane & 7;                                   // piece this lane writes out
+    const int wpc = piece0 + (wi < my_pieces ? wi : 0);
+    const int wq = wpc >> lcpt, wcl = wpc & (cpt - 1);
     bool ok = true;
     int tcount = 0;
     for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
@@ -329,62 +334,64 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
         break;
       }
       tc::fence_after_sync();
-      const int board = mt * 128 + row;
-      const bool bvalid = board < p.nboards;
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
       const float* gbias = p.bias + (size_t)g * p.c1;
+      const float* sbias = s_bias + g * p.c1;
       // fetch this part's pieces (8 accumulator columns each), four per wait; the accumulator goes
       // back to the MMA warp as soon as the last fetch has landed
-      for (int i0 = 0; i0 < per_part; i0 += 4) {
-        uint32_t v[4][8];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const int pc = piece0 + i0 + b;
-          if (i0 + b < my_pieces) {
-            const int q = pc / cpt, cl = pc - q * cpt;
-            tc::tmem_ld8(taddr + (uint32_t)(cl * p.c1 + q * 8), v[b]);
-          }
-        }
-        tc::tmem_wait_ld();
-        if (i0 + 4 >= per_part) {
-          tc::fence_before_sync();
-          __syncwarp();
-          if (lane == 0) {
-            if (PAIR) tc::mbar_arrive_cluster(tc::mapa(bar_tempty(acc), 0)); else tc::mbar_arrive(bar_tempty(acc));
-          }
-        }
+      for (int i0 = 0; i0 < 8; i0 += 4) {
+        if (i0 < per_part) {
+          uint32_t v[4][8];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const int pc = piece0 + i0 + b;
-          if (i0 + b >= my_pieces) continue;
-          const int q = pc / cpt, cl = pc - q * cpt;
-          float y[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float hb = bias_in_smem ? s_bias[g * p.c1 + q * 8 + j] : 0.5f * gbias[q * 8 + j];
-            y[j] = silu_from_half(fmaf(__uint_as_float(v[b][j]), 0.5f, hb));
+          for (int b = 0; b < 4; ++b)
+            if (i0 + b < my_pieces) tc::tmem_ld8(taddr + (uint32_t)(((piece0 + i0 + b) & (cpt - 1)) * p.c1 + ((piece0 + i0 + b) >> lcpt) * 8), v[b]);
+          tc::tmem_wait_ld();
+          if (i0 + 4 >= per_part) {
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if (PAIR) tc::mbar_arrive_cluster(tc::mapa(bar_tempty(acc), 0)); else tc::mbar_arrive(bar_tempty(acc));
+            }
           }
-          uint4 o;
-          o.x = pack_bf16x2(y[0], y[1]);
-          o.y = pack_bf16x2(y[2], y[3]);
-          o.z = pack_bf16x2(y[4], y[5]);
-          o.w = pack_bf16x2(y[6], y[7]);
-          patch[lane * 8 + ((i0 + b) ^ (lane & 7))] = o;   // [board][piece], swizzled against bank conflicts
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            if (i0 + b >= my_pieces) continue;
+            float hb[8];
+            const int ch = ((piece0 + i0 + b) >> lcpt) * 8;
+            if (bias_in_smem) {
+              const float4 b0 = *reinterpret_cast<const float4*>(sbias + ch);
+              const float4 b1 = *reinterpret_cast<const float4*>(sbias + ch + 4);
+              hb[0] = b0.x; hb[1] = b0.y; hb[2] = b0.z; hb[3] = b0.w;
+              hb[4] = b1.x; hb[5] = b1.y; hb[6] = b1.z; hb[7] = b1.w;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) hb[j] = 0.5f * gbias[ch + j];
+            }
+            float y[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = silu_from_half(fmaf(__uint_as_float(v[b][j]), 0.5f, hb[j]));
+            uint4 o;
+            o.x = pack_bf16x2(y[0], y[1]);
+            o.y = pack_bf16x2(y[2], y[3]);
+            o.z = pack_bf16x2(y[4], y[5]);
+            o.w = pack_bf16x2(y[6], y[7]);
+            patch[lane * 8 + ((i0 + b) ^ (lane & 7))] = o;   // [board][piece], swizzled against bank conflicts
+          }
         }
       }
       __syncwarp();
       // write out: 8 rounds of 4 boards x 8 pieces; lanes 8k..8k+7 hold consecutive pieces of one board
-      const long long tile_row0 = (long long)p.front + (long long)g * p.group_pos + (long long)(mt * 128 + quad * 32) * p.slots;
-#pragma unroll 2
+      const int cell = nt_i * cpt + wcl;
+      const int r = cell / p.bsize, c = cell - r * p.bsize;
+      const int board0 = mt * 128 + quad * 32 + (lane >> 3);       // this lane's board in round 0
+      uint4* dst = p.out + (size_t)wq * p.plane_rows + (long long)p.front + (long long)g * p.group_pos +
+                   (long long)board0 * p.slots + r * p.wp + c;
+      const bool lane_ok = wi < my_pieces && cell < cells;
+#pragma unroll 4
       for (int rd = 0; rd < 8; ++rd) {
-        const int bl = rd * 4 + (lane >> 3), i = lane & 7;
-        const int pc = piece0 + i;
-        const int q = pc / cpt, cl = pc - q * cpt;
-        const int cell = nt_i * cpt + cl;
-        if (i < my_pieces && mt * 128 + quad * 32 + bl < p.nboards && cell < cells) {
-          const int r = cell / p.bsize, c = cell - r * p.bsize;
-          p.out[(size_t)q * p.plane_rows + tile_row0 + (long long)bl * p.slots + r * p.wp + c] = patch[bl * 8 + (i ^ (bl & 7))];
-        }
+        const int bl = rd * 4 + (lane >> 3);
+        if (lane_ok && board0 + rd * 4 < p.nboards) dst[(size_t)rd * 4 * p.slots] = patch[bl * 8 + (wi ^ (bl & 7))];
       }
       __syncwarp();   // the patch is reused by the next tile
     }

@@ -258,6 +258,7 @@ struct FinishParams {
   long long x_group_stride; // boards between groups in x / outputs
   long long board0;         // first board of this pass inside a group
   int n;                    // board side (engine path); standalone: A = n_actions
+  int n_magic;              // 65536 / n + 1: a / n == (a * n_magic) >> 16 for a < n * n, n <= 32
   int n_actions;
   int nb;                   // boards per group in this pass
   int flags;
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
   auto raw_logit = [&](int a) {
     if (!engine) return p.logits_in[ob * A + a];
     const int view_cell = canon ? d4_forward(a, n, phase) : a;
-    const int vr = view_cell / n, vc = view_cell - vr * n;
+    const int vr = (view_cell * p.n_magic) >> 16, vc = view_cell - vr * n;
     return p.logit_raw[raw0 + vr * p.pitch + vc] + bp;
   };
 
@@ -344,7 +345,7 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
           occ0[j] = input_value(p.in, ob, 0, orig_cell, A);
           occ1[j] = input_value(p.in, ob, 1, orig_cell, A);
           if (p.vmap) {
-            const int r = a / n, c = a - r * n;
+            const int r = (a * p.n_magic) >> 16, c = a - r * n;
             vm[j] = p.vmap[raw0 + r * p.pitch + c];
           }
         } else {

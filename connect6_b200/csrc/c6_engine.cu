@@ -339,6 +339,7 @@ int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long
   f.x_group_stride = a.T;
   f.board0 = t0;
   f.n = e->n;
+  f.n_magic = 65536 / e->n + 1;
   f.n_actions = e->cells;
   f.nb = nb;
   f.flags = a.flags;
@@ -1022,6 +1023,7 @@ int c6_forward_noalloc(C6Engine* e, const void* x, int x_dtype, int64_t B, const
   f.x_group_stride = B;
   f.board0 = 0;
   f.n = e->n;
+  f.n_magic = 65536 / e->n + 1;
   f.n_actions = e->cells;
   f.nb = nb;
   f.flags = flags;
@@ -1060,6 +1062,7 @@ int c6_sample_actions(const float* logits, const uint8_t* legal, int64_t B, int3
   f.legal_in = legal;
   f.x_group_stride = B;
   f.n = 1;
+  f.n_magic = 65537;
   f.n_actions = A;
   f.nb = (int)B;
   f.do_sample = 1;

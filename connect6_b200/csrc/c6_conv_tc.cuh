@@ -98,7 +98,9 @@ __host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 *
 // [r*N/2, (r+1)*N/2) of every weight block; the leader (r = 0) issues the MMAs, which read both
 // CTAs' shared memory at the same offsets.  Halving the B operand per CTA cuts the shared-memory
 // operand traffic that bounds a 128 x N MMA for N < 128 and frees shared memory for more stages.
-template <int KS, bool PAIR>
+// TIMED = true compiles the in-kernel clock counters in (p.wait_cycles); the plain instantiation
+// carries none of them: even untaken, they cost the epilogue 2-3 % on the narrow layers.
+template <int KS, bool PAIR, bool TIMED>
 __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte aligned view of dynamic shared memory
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   grid_dep_launch();   // the next kernel's CTAs may move in as ours exit; its own wait orders the data
   unsigned long long gt_start = 0;
-  if (p.wait_cycles) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_start));
+  if (TIMED && p.wait_cycles) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_start));
   const uint32_t crank = PAIR ? tc::cluster_ctarank() : 0u;
   const bool leader = crank == 0;
   const int nloc = PAIR ? p.n / 2 : p.n;   // weight rows this CTA holds
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     }
     grid_dep_wait();   // weights do not depend on the previous kernel, the activations do
     long long waited = 0;
-    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0 && prod == 0;
+    const bool timing = TIMED && p.wait_cycles != nullptr && blockIdx.x == 0 && prod == 0;
     // Every issuer owns a private ring of `spi` stages, so each stage barrier has exactly one
     // producer and one consumer that sees all of its phases.  Tiles are fed in waves of `nissue`
     // (tile tb + i belongs to issuer i), step by step across the wave, so that all issuers advance
@@ -291,7 +293,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const uint32_t wq_rows = wq_bytes >> 4;
     const uint32_t stage0_lo = (tc::smem_u32(s_stage) >> 4) | a_lbo_field;
     const uint32_t stage_rows = stage_bytes >> 4;
-    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0 && issuer == 0;
+    const bool timing = TIMED && p.wait_cycles != nullptr && blockIdx.x == 0 && issuer == 0;
     bool ok = true;
     if (p.resident && !tc::mbar_wait_warp(bar_w, 0, abort_flag, 32)) {
       if (lane == 0) atomicOr(p.status, kStatWaitWeights);
@@ -302,7 +304,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     uint32_t ph = 0;
     long long wait_full = 0, wait_acc = 0, issue_clk = 0;
     const long long loop_t0 = clock64();
-    if (p.wait_cycles && lane == 0 && issuer == 0 && blockIdx.x < 512) {
+    if (TIMED && p.wait_cycles && lane == 0 && issuer == 0 && blockIdx.x < 512) {
       unsigned long long g;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g));
       p.wait_cycles[8 + 4 * blockIdx.x + 2] = (long long)g;   // MMA loop begins (weights resident)
@@ -392,7 +394,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       p.wait_cycles[4] += issue_clk;
       p.wait_cycles[5] += clock64() - loop_t0;
     }
-    if (p.wait_cycles && lane == 0 && issuer == 0 && blockIdx.x < 512) {
+    if (TIMED && p.wait_cycles && lane == 0 && issuer == 0 && blockIdx.x < 512) {
       unsigned long long g;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g));
       p.wait_cycles[8 + 4 * blockIdx.x + 3] = (long long)g;   // MMA loop ends (all MMAs issued)
@@ -445,7 +447,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     // while both teams are busy.  Per element: h = 0.5*acc + 0.5*bias (one FMA),
     // y = h + h*tanh(h) (one MUFU, one FMA).  On the head layer the thread already holds every
     // channel of its position, so both 1x1 heads reduce inside the thread.
-    const bool timing = p.wait_cycles != nullptr && blockIdx.x == 0;
+    const bool timing = TIMED && p.wait_cycles != nullptr && blockIdx.x == 0;
     const int quad = warp & 3;
     const int team = (warp - kEpiWarp0) >> 2;
     grid_dep_wait();   // redundant with the producers' wait (no accumulator fills before it); every role that touches global memory orders itself
@@ -453,14 +455,14 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const int row = quad * 32 + lane;
     const int nunits = p.n >> 4;
     bool ok = true;
-    long long wait_tfull = 0, ep_ld = 0, ep_math = 0;
+    unsigned int wait_tfull = 0, ep_ld = 0, ep_math = 0;   // 32-bit clocks: registers are scarce here
     for (int tcount = team; tcount < ntl && ok; tcount += nteams) {
       const int tile = t_first + tcount * t_stride;
       const int acc = tcount % p.nacc;
       const uint32_t acc_ph = (uint32_t)(tcount / p.nacc) & 1u;
-      const long long w0 = timing ? clock64() : 0;
+      const unsigned int w0 = timing ? (unsigned int)clock() : 0u;
       const bool got = tc::mbar_wait(bar_tfull(acc), acc_ph, abort_flag, kIdleBackoffNs);
-      if (timing) wait_tfull += clock64() - w0;
+      if (timing) wait_tfull += (unsigned int)clock() - w0;
       if (!got) {
         if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
         *abort_flag = 1;
@@ -468,8 +470,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         break;
       }
       tc::fence_after_sync();
-      const long long e0 = timing ? clock64() : 0;
-      long long e1 = e0, e2 = e0;
+      const unsigned int e0 = timing ? (unsigned int)clock() : 0u;
+      unsigned int e1 = e0;
       const int pos = tile_pos(tile) + row;            // position inside the group
       const int board = pos / p.slots, slot = pos - board * p.slots;
       const int r = slot / p.wp, c = slot - r * p.wp;
@@ -486,7 +488,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         for (int b = 0; b < kEpiBatch; ++b)
           if (u0 + b < nunits) tc::tmem_ld16(taddr + (uint32_t)((u0 + b) * 16), v[b]);
         tc::tmem_wait_ld();
-        if (timing && u0 == 0) e1 = clock64();
+        if (timing && u0 == 0) e1 = (unsigned int)clock();
         if (u0 + kEpiBatch >= nunits) {
           tc::fence_before_sync();
           __syncwarp();
@@ -494,7 +496,6 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
             if (PAIR) tc::mbar_arrive_cluster(tc::mapa(bar_tempty(acc), 0)); else tc::mbar_arrive(bar_tempty(acc));
           }
         }
-        if (timing && u0 == 0) e2 = clock64();
 #pragma unroll
         for (int b = 0; b < kEpiBatch; ++b) {
           const int u = u0 + b;
@@ -562,7 +563,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       }
       if (timing) {
         ep_ld += e1 - e0;            // first TMEM fetch: issue to data
-        ep_math += clock64() - e1;   // release + arithmetic + stores (+ later fetches)
+        ep_math += (unsigned int)clock() - e1;   // release + arithmetic + stores (+ later fetches)
       }
     }
     if (timing && threadIdx.x == 32 * kEpiWarp0) {
@@ -574,7 +575,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
 
   tc::fence_before_sync();
   if (PAIR) tc::cluster_sync(); else __syncthreads();   // the peer's shared memory outlives the leader's MMAs
-  if (p.wait_cycles && threadIdx.x == 0 && blockIdx.x < 512) {
+  if (TIMED && p.wait_cycles && threadIdx.x == 0 && blockIdx.x < 512) {
     unsigned long long gt_end;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_end));
     p.wait_cycles[8 + 4 * blockIdx.x] = (long long)gt_start;       // ns timestamps of this CTA

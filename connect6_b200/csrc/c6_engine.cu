@@ -158,6 +158,15 @@ void prefer_shared_memory() {
   cudaFuncSetAttribute(finish_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
+// Opt every instantiation of the k x k kernel for one filter side into the large dynamic shared memory.
+template <int KS>
+bool conv_smem_opt_in() {
+  return cudaFuncSetAttribute(conv_tc_kernel<KS, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess &&
+         cudaFuncSetAttribute(conv_tc_kernel<KS, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess &&
+         cudaFuncSetAttribute(conv_tc_kernel<KS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess &&
+         cudaFuncSetAttribute(conv_tc_kernel<KS, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess;
+}
+
 // Launch with optional 2-CTA clusters and optional programmatic dependent launch (the kernel then
 // orders itself behind its predecessor with grid_dep_wait(), so its prologue -- barrier setup, TMEM
 // allocation, resident weights -- overlaps the predecessor's tail).
@@ -476,21 +485,16 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
       ProfScope _ps(e, C6_KIND_CONV0 + l, st);
       const int grid = e->G * p.ctas_per_group;
       const bool dep = e->dependent_launch;
-      if (lp.pair) {
-        switch (lp.k) {
-          case 1: launch_chain(conv_tc_kernel<1, true>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, true, dep, p); break;
-          case 3: launch_chain(conv_tc_kernel<3, true>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, true, dep, p); break;
-          case 5: launch_chain(conv_tc_kernel<5, true>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, true, dep, p); break;
-          default: launch_chain(conv_tc_kernel<0, true>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, true, dep, p); break;
-        }
-      } else {
-        switch (lp.k) {
-          case 1: launch_chain(conv_tc_kernel<1, false>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, false, dep, p); break;
-          case 3: launch_chain(conv_tc_kernel<3, false>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, false, dep, p); break;
-          case 5: launch_chain(conv_tc_kernel<5, false>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, false, dep, p); break;
-          default: launch_chain(conv_tc_kernel<0, false>, (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st, false, dep, p); break;
-        }
-      }
+      // instantiation: filter side known at compile time (0 = generic), CTA pairs or not, clock counters or not
+      using ConvKernel = void (*)(ConvTcParams);
+      static const ConvKernel table[2][2][4] = {
+          {{conv_tc_kernel<0, false, false>, conv_tc_kernel<1, false, false>, conv_tc_kernel<3, false, false>, conv_tc_kernel<5, false, false>},
+           {conv_tc_kernel<0, true, false>, conv_tc_kernel<1, true, false>, conv_tc_kernel<3, true, false>, conv_tc_kernel<5, true, false>}},
+          {{conv_tc_kernel<0, false, true>, conv_tc_kernel<1, false, true>, conv_tc_kernel<3, false, true>, conv_tc_kernel<5, false, true>},
+           {conv_tc_kernel<0, true, true>, conv_tc_kernel<1, true, true>, conv_tc_kernel<3, true, true>, conv_tc_kernel<5, true, true>}}};
+      const int ks = lp.k == 1 ? 1 : lp.k == 3 ? 2 : lp.k == 5 ? 3 : 0;
+      launch_chain(table[p.wait_cycles ? 1 : 0][lp.pair ? 1 : 0][ks], (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st,
+                   lp.pair != 0, dep, p);
     }
     C6_LAUNCHED(e, "conv_tc_kernel");
     if (!p.head) cur ^= 1;
@@ -763,14 +767,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     const int cl = e->lp[e->L - 1].cout_p;
     if ((rc = dev_alloc(e, &e->head_wp, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->head_wv, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
-    if (cudaFuncSetAttribute(conv_tc_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<5, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_tc_kernel<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+    if (!conv_smem_opt_in<0>() || !conv_smem_opt_in<1>() || !conv_smem_opt_in<3>() || !conv_smem_opt_in<5>() ||
         cudaFuncSetAttribute(stem_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
         cudaFuncSetAttribute(stem_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
       return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");

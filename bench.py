@@ -365,7 +365,10 @@ def run_engine(args) -> None:
     conv_ms = sum(ms for k, (ms, n) in prof.items() if k.startswith("conv"))
     conv_launches = sum(n for k, (ms, n) in prof.items() if k.startswith("conv"))
     conv_flop_per_step = 2 * (sum(CONV_LAYER_MACS[1:]) + HEAD_MACS) * BATCH
-    peak = float(peaks["bf16_tflops"])
+    # The kernel is timed inside a seconds-long, power-capped step loop: the denominator is the
+    # SUSTAINED cuBLAS figure (a GEMM loop under the same cap); the burst figure is reported beside it.
+    burst = float(peaks["bf16_tflops"])
+    peak = float(peaks.get("bf16_tflops_sustained", burst))
     roof = None
     if conv_launches:
         avg_ms = conv_ms / conv_launches
@@ -373,8 +376,8 @@ def run_engine(args) -> None:
         achieved = flop_per_launch / (avg_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": "conv_tc_kernel (backbone layers 1-7 + fused heads)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": f"MEASURED_PEAKS.json bf16_tflops (burst), of {peak_kind}",
-                "frac_of_sustained": achieved / float(peaks.get("bf16_tflops_sustained", peak)),
+                "peak_source": f"MEASURED_PEAKS.json bf16_tflops_sustained (kernel timed inside a long step), of {peak_kind}",
+                "burst_peak": burst, "frac_of_burst": achieved / burst,
                 "traffic": CONV_TRAFFIC_BYTES_PER_LAUNCH, "launches": conv_launches, "avg_launch_ms": avg_ms,
                 "timed_with": f"CUDA events around every launch of {sampled_steps} of the {args.steps} timed steps",
                 "flop_per_launch": flop_per_launch}
@@ -410,7 +413,7 @@ def run_engine(args) -> None:
                             "api": "PolicyValueNet.selfplay_step_from_boards: pinned host int8 boards + player + stones_left in, host results out"},
         "gpu_launches": launches,
         "roofline": roof,
-        "whole_step": {"tflops_per_gpu": whole_tflops, "frac_of_peak": whole_tflops / peak,
+        "whole_step": {"tflops_per_gpu": whole_tflops, "frac_of_peak": whole_tflops / peak, "frac_of_burst": whole_tflops / burst,
                        "flop_per_board": FLOP_PER_BOARD},
         "kernels": kernels,
         "device_status": status,
@@ -505,13 +508,15 @@ def run_workload(args) -> None:
     if rank == 0:
         total_boards = (boards * world if scaling == "weak" else (65536 if wl == "cfg4" else 32768)) * args.steps
         value = total_boards / (ms * 1e-3)
-        peak = float(peaks["bf16_tflops"])
+        burst = float(peaks["bf16_tflops"])
+        peak = float(peaks.get("bf16_tflops_sustained", burst))
         line = {"metric": METRIC.replace("B=8192", wl), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": scaling,
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": desc},
                 "clocks": clocks, "gpu_launches": eng.launch_count - launches0,
                 "whole_step": {"tflops_per_gpu": value / world * flop / 1e12, "frac_of_peak": value / world * flop / 1e12 / peak,
-                               "flop_per_board": flop, "peak_source": f"bf16_tflops burst, of {peak_kind}"},
+                               "frac_of_burst": value / world * flop / 1e12 / burst,
+                               "flop_per_board": flop, "peak_source": f"bf16_tflops_sustained, of {peak_kind}"},
                 "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                             for k, v in sorted(prof.items())},
                 "device_status": status}

@@ -49,7 +49,7 @@ def _random_legal(env, gen, corner: int = 0):
     return torch.multinomial(legal, 1, generator=gen).squeeze(1)
 
 
-@pytest.mark.parametrize("E,n,win", [(1, 19, 6), (257, 9, 5), (3000, 19, 6)])
+@pytest.mark.parametrize("E,n,win", [(1, 19, 6), (257, 9, 5), (3000, 19, 6), (513, 3, 3), (130, 40, 7), (64, 6, 1)])
 def test_env_step_matches_torch_port_on_large_batches(cuda_device, E, n, win):
     """Random legal play with view-phase actions; the CPU torch restatement steps the same games."""
     from connect6_b200.vector_env import VectorConnect6

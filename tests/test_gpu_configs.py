@@ -149,3 +149,37 @@ def test_training_ensemble_128x4(cuda_device):
         l1, v1 = single.forward(x[g])
         assert torch.equal(l1, logits[g]) and torch.equal(v1, value[g])
     assert eng.status() == 0 and single.status() == 0
+
+
+@pytest.mark.parametrize("channels,kernels", [((96, 32), (23, 3)), ((160, 64, 32), (23, 3, 3)), ((256, 32), (23, 1))])
+def test_stem_widths_against_oracle(cuda_device, channels, kernels):
+    """Stem widths that change the tile shape of the Toeplitz GEMM (2 cells x 96 channels, 1 cell x 160,
+    1 cell x 256 per tile; the epilogue warps then own 6, 5 and 8 pieces each), both with a constant
+    third plane (short product) and with a varying one (full product)."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import PolicyValueNet
+    torch.manual_seed(11)
+    m = PolicyValueNet(19, list(kernels), list(channels))
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.ndim == 1:
+                p.uniform_(-0.2, 0.2)
+    state = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    eng = Engine(cuda_device, 19, kernels, channels, 1, "bf16")
+    eng.load_state_dict(state)
+    x = torch.from_numpy(generate_planes(40, 130))
+    xv = x.clone()
+    xv[:, 2] += 0.125 * torch.randn(130, 19, 19).round()            # third plane no longer constant
+    for inp in (x, xv):
+        w, b = state["convs.0.weight"].double(), state["convs.0.bias"].double()
+        want = torch.nn.functional.silu(torch.nn.functional.conv2d(inp.double(), w, b, padding=kernels[0] // 2))
+        got = eng.layer_output(inp.to(cuda_device), 0).cpu().double()
+        assert got.shape == want.shape
+        err = (got - want).abs().max().item() / want.abs().max().item()
+        assert err < 1e-2, f"stem {channels[0]} channels: relative error {err}"
+        rl, rv = TP.policy_value_forward(inp.double(), {k: v.double() for k, v in state.items()})
+        logits, value = eng.forward(inp.to(cuda_device))
+        assert (logits.cpu().double() - rl).abs().max().item() < max(3e-2, 0.12 * rl.std().item())
+        assert (value.cpu().double() - rv).abs().max().item() < 3e-2
+    assert eng.status() == 0

@@ -75,7 +75,6 @@ __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.w
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- activations ----------------------------------------------------------------------
-__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 // SiLU through the hardware tanh: x*sigmoid(x) = h + h*tanh(h) with h = x/2.  One MUFU and two
 // FMAs per element when the caller folds the bias into h.  tanh.approx.f32 is accurate to about
 // 2^-11 relative, well below the bf16 rounding applied to the result.

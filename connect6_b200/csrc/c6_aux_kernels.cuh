@@ -39,7 +39,8 @@ __host__ __device__ __forceinline__ int stem_k_decode(int chunk, int e, int kc_s
 // 8 bf16 laid out [board tile of 128][K chunk][128 boards], so that all K chunks of one pipeline
 // stage of one board tile are contiguous and travel in ONE bulk copy.  A board with orientation
 // `phase` is presented as view.flat[j] = x.flat[d4_inverse(j)] (connect6/train.py:222-230).
-// Stores `epoch` into *p2_epoch when some board's third plane is not constant.
+// Stores `epoch` into *p2_epoch when some board's third plane is not constant, and one byte of
+// occupancy bits per (board, chunk of planes 0/1).
 // Grid: (ceil(kc*nb/256), G); one thread per (board, chunk).
 // ------------------------------------------------------------------------------------------------
 __global__ void pack_stem_input_kernel(const InputSrc in,
@@ -48,7 +49,8 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
                                        int nb,                 // boards of this pass per group
                                        long long group_stride, // boards between groups in x
                                        long long board0,       // first board of this pass in a group
-                                       unsigned int epoch, unsigned int* __restrict__ p2_epoch) {
+                                       unsigned int epoch, unsigned int* __restrict__ p2_epoch,
+                                       uint8_t* __restrict__ occ) {   // [kc_short][mrows] bit j of a byte: element 8c+j != 0
   grid_dep_launch();
   const int g = blockIdx.y;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -75,6 +77,14 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
     }
     v[j] = val;
     kinds[j] = kind == 1 && ci == 2 ? 3 : kind;   // 3: element of the third plane
+  }
+  if (c < kc_short) {
+    // occupancy bits of the first two planes, in the view frame: the finishing kernel derives the
+    // legal-move mask from these 2 x cells bits instead of re-reading the planes
+    unsigned bits = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bits |= (kinds[j] == 1 && v[j] != 0.f) ? (1u << j) : 0u;
+    occ[(size_t)c * mrows + (size_t)g * mrows_per_group + t] = (uint8_t)bits;
   }
   bool varies = false;
 #pragma unroll
@@ -253,7 +263,10 @@ struct FinishParams {
   const float* val_bias;   // [G] or null
   const float* logits_in;  // standalone: [B,A] logits
   const uint8_t* legal_in; // standalone: [B,A] legality
-  InputSrc in;             // engine path: network input, for occupancy (plane0|plane1)
+  InputSrc in;             // engine path: network input, for occupancy (plane0|plane1) when occ is null
+  const uint8_t* occ;      // nullable [chunk][occ_stride]: occupancy bits written by the input pack kernel (view frame)
+  long long occ_stride;    // board rows per chunk
+  int mrows_per_group;     // board rows reserved per group
   const uint8_t* orient;
   long long x_group_stride; // boards between groups in x / outputs
   long long board0;         // first board of this pass inside a group
@@ -275,12 +288,8 @@ struct FinishParams {
 constexpr int kFinishWarps = 4;                    // boards per block: one warp each
 constexpr int kFinishThreads = 32 * kFinishWarps;
 constexpr int kFinishMaxActions = 1024;
+constexpr int kFinishSmallJ = 12;                  // actions per lane of the small instantiation: up to 384 actions
 
-// dynamic shared memory of finish_kernel: per warp, A scaled logits (then their exponentials) and
-// A running sums
-__host__ __device__ inline size_t finish_smem_bytes(int n_actions) {
-  return (size_t)kFinishWarps * 2 * (size_t)n_actions * sizeof(float);
-}
 // blocks for nb boards per group
 __host__ __device__ inline unsigned finish_blocks(long long nb) {
   return (unsigned)((nb + kFinishWarps - 1) / kFinishWarps);
@@ -297,10 +306,11 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// One warp per board, no block-wide synchronisation: lane l owns actions l, l + 32, ... (coalesced
-// reads); sums, the maximum and the running sum of the inverse-CDF draw go through shuffles.
+// One warp per board; lane l owns the J consecutive actions J*l .. J*l + J-1 and keeps them in
+// registers (J * 32 >= n_actions), so the running sum of the inverse-CDF draw is J additions per
+// lane plus one shuffle scan over the lane totals: no shared memory, no block-wide barrier.
+template <int J>
 __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishParams p) {
-  extern __shared__ float s_finish[];
   grid_dep_launch();
   grid_dep_wait();   // raw logits and value maps come from the last conv kernel
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -308,8 +318,6 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
   const long long t = (long long)blockIdx.x * kFinishWarps + warp;   // board inside the group
   if (t >= p.nb) return;                                           // whole warps leave together
   const int A = p.n_actions;
-  float* s_e = s_finish + (size_t)warp * 2 * A;   // z = logit / T of legal cells (-inf otherwise), then exp(z - max)
-  float* s_c = s_e + A;                           // running sum of s_e in action order
   const long long ob = (long long)g * p.x_group_stride + p.board0 + t;  // board index in x / outputs
   const bool engine = p.logit_raw != nullptr;
   const int n = p.n;
@@ -318,6 +326,7 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
   const long long raw0 = (long long)g * p.group_stride + t * p.board_stride;
   const float bp = (engine && p.pol_bias) ? p.pol_bias[g] : 0.f;
   const float inv_t = 1.0f / fmaxf(p.temperature, 1e-4f);
+  const int a0 = lane * J;
 
   // raw logit of output index a (canonical frame when `canon`, else the view frame)
   auto raw_logit = [&](int a) {
@@ -327,45 +336,86 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
     return p.logit_raw[raw0 + vr * p.pitch + vc] + bp;
   };
 
-  float vsum = 0.f, lmax = -INFINITY;
-  int nlegal = 0;
-  // All loads of a block of 8 x 32 actions are issued before any is used: the kernel is bound by
-  // memory latency, and a load that waits for the previous one's value doubles it.
-  constexpr int kJ = 8;
-  for (int base = 0; base < A; base += kJ * 32) {
-    float raw[kJ], occ0[kJ], occ1[kJ], vm[kJ];
+  // All loads are issued before any value is used: the kernel is bound by memory latency.
+  float raw[J], vm[J];
+  unsigned occupied = 0;   // bit j: action a0 + j is not legal
+  if (engine && p.occ && phase == 0) {
+    // Common case (no per-board orientation): the lane's actions are consecutive cells of one or two
+    // board rows, so the row/column pair is stepped instead of divided out, and the occupancy bits
+    // of its J cells sit in at most ceil((J + 7) / 8) + 1 consecutive bytes per plane.
+    int r = (a0 * p.n_magic) >> 16, c = a0 - r * n;
+    const uint8_t* ob_occ = p.occ + (size_t)g * p.mrows_per_group + t;
+    constexpr int kBytes = (J + 14) / 8;
+    unsigned long long w0 = 0, w1 = 0;
+    const int k1 = A + a0;
 #pragma unroll
-    for (int j = 0; j < kJ; ++j) {
-      const int a = base + j * 32 + lane;
-      raw[j] = occ0[j] = occ1[j] = vm[j] = 0.f;
+    for (int b = 0; b < kBytes; ++b) {
+      if (((a0 >> 3) + b) * 8 < 2 * A) w0 |= (unsigned long long)ob_occ[(size_t)((a0 >> 3) + b) * p.occ_stride] << (8 * b);
+      if (((k1 >> 3) + b) * 8 < 2 * A) w1 |= (unsigned long long)ob_occ[(size_t)((k1 >> 3) + b) * p.occ_stride] << (8 * b);
+    }
+    const long long base = raw0 + (long long)r * p.pitch + c;
+    int step = 0;   // offset of the current cell from `base` in the pitched maps
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      raw[j] = vm[j] = 0.f;
+      if (a0 + j < A) {
+        raw[j] = p.logit_raw[base + step] + bp;
+        if (p.vmap) vm[j] = p.vmap[base + step];
+      }
+      ++step;
+      if (++c == n) { c = 0; step += p.pitch - n; }
+    }
+    const unsigned occ_bits = (unsigned)((w0 >> (a0 & 7)) | (w1 >> (k1 & 7)));
+    occupied = occ_bits & (J < 32 ? ((1u << (J & 31)) - 1u) : 0xffffffffu);
+#pragma unroll
+    for (int j = 0; j < J; ++j)
+      if (a0 + j >= A) occupied |= 1u << j;
+  } else {
+    float o0[J], o1[J];
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int a = a0 + j;
+      raw[j] = vm[j] = o0[j] = o1[j] = 0.f;
       if (a < A) {
         raw[j] = raw_logit(a);
         if (engine) {
-          const int orig_cell = (phase != 0 && !canon) ? d4_inverse(a, n, phase) : a;
-          occ0[j] = input_value(p.in, ob, 0, orig_cell, A);
-          occ1[j] = input_value(p.in, ob, 1, orig_cell, A);
+          if (p.occ) {
+            const int view_cell = canon ? d4_forward(a, n, phase) : a;
+            const int k1 = A + view_cell;
+            const uint8_t* ob_occ = p.occ + (size_t)g * p.mrows_per_group + t;
+            o0[j] = (float)((ob_occ[(size_t)(view_cell >> 3) * p.occ_stride] >> (view_cell & 7)) & 1);
+            o1[j] = (float)((ob_occ[(size_t)(k1 >> 3) * p.occ_stride] >> (k1 & 7)) & 1);
+          } else {
+            const int orig_cell = (phase != 0 && !canon) ? d4_inverse(a, n, phase) : a;
+            o0[j] = input_value(p.in, ob, 0, orig_cell, A);
+            o1[j] = input_value(p.in, ob, 1, orig_cell, A);
+          }
           if (p.vmap) {
             const int r = (a * p.n_magic) >> 16, c = a - r * n;
             vm[j] = p.vmap[raw0 + r * p.pitch + c];
           }
         } else {
-          occ0[j] = p.legal_in[ob * A + a] != 0 ? 0.f : 1.f;
+          o0[j] = p.legal_in[ob * A + a] != 0 ? 0.f : 1.f;
         }
       }
     }
 #pragma unroll
-    for (int j = 0; j < kJ; ++j) {
-      const int a = base + j * 32 + lane;
-      if (a < A) {
-        const bool legal = occ0[j] == 0.f && occ1[j] == 0.f;
-        vsum += vm[j];
-        if (p.logits_out) p.logits_out[ob * A + a] = ((p.flags & 1) && !legal) ? kFp32Min : raw[j];
-        const float z = legal ? raw[j] * inv_t : -INFINITY;
-        s_e[a] = z;
-        lmax = fmaxf(lmax, z);
-        nlegal += legal ? 1 : 0;
-      }
+    for (int j = 0; j < J; ++j)
+      if (a0 + j >= A || o0[j] != 0.f || o1[j] != 0.f) occupied |= 1u << j;
+  }
+  float vsum = 0.f, lmax = -INFINITY;
+  int nlegal = 0;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int a = a0 + j;
+    const bool legal = !((occupied >> j) & 1u);
+    if (a < A) {
+      vsum += vm[j];
+      if (p.logits_out) p.logits_out[ob * A + a] = ((p.flags & 1) && !legal) ? kFp32Min : raw[j];
     }
+    raw[j] = legal ? raw[j] * inv_t : -INFINITY;   // z = mask(logits) / max(T, 1e-4)
+    lmax = fmaxf(lmax, raw[j]);
+    nlegal += legal ? 1 : 0;
   }
   if (engine && p.value_out) {
     const float tot = warp_sum(vsum);
@@ -373,49 +423,40 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
   }
   if (!p.do_sample) return;
 
-  // z = mask(logits) / max(T, 1e-4); with no legal cell every z equals the fill: uniform.
+  // With no legal cell every z equals the fill: uniform over all A actions.
   const bool none_legal = __reduce_add_sync(0xffffffffu, nlegal) == 0;
   const float zmax = none_legal ? 0.f : warp_max(lmax);
-  __syncwarp();
-  // running sums in action order: 32 actions per round, a shuffle scan inside the round
-  float carry = 0.f;
-  for (int a0 = 0; a0 < A; a0 += 32) {
-    const int a = a0 + lane;
-    float e = 0.f;
-    if (a < A) {
-      e = none_legal ? 1.f : expf(s_e[a] - zmax);   // exp(-inf) = 0 for occupied cells
-      s_e[a] = e;
-    }
-    float run = e;
+  // e = exp(z - max), then this lane's running sums; the lanes' totals are scanned with shuffles
+  float local = 0.f;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float up = __shfl_up_sync(0xffffffffu, run, o);
-      if (lane >= o) run += up;
-    }
-    run += carry;
-    if (a < A) s_c[a] = run;
-    carry = __shfl_sync(0xffffffffu, run, 31);
+  for (int j = 0; j < J; ++j) {
+    const float e = a0 + j < A ? (none_legal ? 1.f : expf(raw[j] - zmax)) : 0.f;   // exp(-inf) = 0 for occupied cells
+    vm[j] = e;              // vm is free now: it keeps e
+    local += e;
+    raw[j] = local;         // inclusive running sum inside the lane
   }
-  const float total = carry;
+  float incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  const float before = incl - local;
+  const float total = __shfl_sync(0xffffffffu, incl, 31);
   const float u = board_uniform(p.seed, p.offset, (unsigned long long)(p.board_index0 + ob));
   const float target = u * total;
-  __syncwarp();
-  // first action with mass whose running sum exceeds the target
-  int pick = -1;
-  for (int a0 = 0; a0 < A && pick < 0; a0 += 32) {
-    const int a = a0 + lane;
-    const bool hit = a < A && s_e[a] > 0.f && s_c[a] > target;
-    const unsigned m = __ballot_sync(0xffffffffu, hit);
-    if (m) pick = a0 + __ffs(m) - 1;
-  }
-  if (pick < 0) {
-    // rounding left the target at or above the total: take the last cell with mass
-    for (int a0 = ((A - 1) / 32) * 32; a0 >= 0 && pick < 0; a0 -= 32) {
-      const int a = a0 + lane;
-      const unsigned m = __ballot_sync(0xffffffffu, a < A && s_e[a] > 0.f);
-      if (m) pick = a0 + 31 - __clz(m);
+  // first action with mass whose running sum exceeds the target; if rounding left the target at or
+  // above the total, the last action with mass
+  int cand = 0x7fffffff, last = -1;
+#pragma unroll
+  for (int j = J - 1; j >= 0; --j) {
+    if (vm[j] > 0.f) {
+      if (before + raw[j] > target) cand = a0 + j;
+      if (last < 0) last = a0 + j;
     }
   }
+  int pick = __reduce_min_sync(0xffffffffu, cand);
+  if (pick == 0x7fffffff) pick = __reduce_max_sync(0xffffffffu, last);
   if (lane == 0) {
     if (p.action_out) p.action_out[ob] = pick;
     // log-prob = z[a] - logsumexp(z) with logsumexp = max + log(sum exp(z - max)), as torch
@@ -426,6 +467,11 @@ __global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishPara
     const float lse = (none_legal ? fill_z : zmax) + logf(total);
     if (p.logprob_out) p.logprob_out[ob] = zpick - lse;
   }
+}
+
+// Picks the instantiation whose lanes hold all the actions.
+inline void (*finish_kernel_for(int n_actions))(FinishParams) {
+  return n_actions <= 32 * kFinishSmallJ ? finish_kernel<kFinishSmallJ> : finish_kernel<kFinishMaxActions / 32>;
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -60,6 +60,7 @@ struct C6Engine {
   int kc_short = 0;                 // stem K chunks of input planes 0 and 1; kc0 - kc_short chunks hold plane 2
   unsigned int stem_epoch = 0;      // pass counter: tells the stem whether THIS pass saw a non-constant third plane
   unsigned int* p2_epoch = nullptr; // device word written by the input pack kernel
+  uint8_t* occ = nullptr;           // [kc_short][mrows] occupancy bits of planes 0/1 (workspace, written by the input pack kernel)
   int kc0 = 0, nt = 0, ntiles = 0, ntot = 0, stem_stages = 0, stem_smem = 0, stem_acc_stride = 0,
       stem_tmem_cols = 0, stem_kcs = 4, stem_pair = 0;
   // weights
@@ -147,17 +148,6 @@ struct ProfScope {
   }
 };
 
-// The finishing kernel stages a board per warp in shared memory and wants many resident blocks per
-// SM; without a hint the driver may pick a shared-memory carve-out that fits only a few.  Function attributes are
-// per device context, so this runs once per device a kernel is first used on.
-void prefer_shared_memory() {
-  static bool done[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
-  done[dev] = true;
-  cudaFuncSetAttribute(finish_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-}
-
 // Opt every instantiation of the k x k kernel for one filter side into the large dynamic shared memory.
 template <int KS>
 bool conv_smem_opt_in() {
@@ -235,6 +225,8 @@ Geometry geometry(const C6Engine* e, long long nb) {
 
 void free_workspace(C6Engine* e) {
   cudaFree(e->xk);
+  cudaFree(e->occ);
+  e->occ = nullptr;
   cudaFree(e->act[0]);
   cudaFree(e->act[1]);
   cudaFree(e->f32buf[0]);
@@ -264,6 +256,7 @@ int ensure_workspace(C6Engine* e, long long nb) {
     const size_t act_rows = (size_t)(e->cmax_p / 8) * e->plane_rows;
     int rc;
     if ((rc = dev_alloc(e, &e->xk, (size_t)e->kc0 * e->mrows, true, &e->ws_bytes))) return rc;
+    if ((rc = dev_alloc(e, &e->occ, (size_t)e->kc_short * e->mrows, true, &e->ws_bytes))) return rc;
     if ((rc = dev_alloc(e, &e->act[0], act_rows, true, &e->ws_bytes))) return rc;
     if ((rc = dev_alloc(e, &e->act[1], act_rows, true, &e->ws_bytes))) return rc;
     if ((rc = dev_alloc(e, &e->logit_raw, (size_t)e->G * g.group_pos, true, &e->ws_bytes))) return rc;
@@ -334,8 +327,11 @@ InputSrc input_of(const RunArgs& a) {
 }
 
 int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long group_stride,
-                  int board_stride, int pitch, cudaStream_t st) {
+                  int board_stride, int pitch, const uint8_t* occ, int mrows_per_group, cudaStream_t st) {
   FinishParams f{};
+  f.occ = occ;
+  f.occ_stride = e->mrows;
+  f.mrows_per_group = mrows_per_group;
   f.logit_raw = e->logit_raw;
   f.vmap = a.value ? e->vmap : nullptr;
   f.group_stride = group_stride;
@@ -363,7 +359,7 @@ int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long
   f.logprob_out = a.logprob;
   {
     ProfScope _ps(e, C6_KIND_FINISH, st);
-    launch_chain(finish_kernel, finish_blocks(nb), (unsigned)e->G, kFinishThreads, finish_smem_bytes(f.n_actions), st, false,
+    launch_chain(finish_kernel_for(f.n_actions), finish_blocks(nb), (unsigned)e->G, kFinishThreads, 0, st, false,
                  e->dependent_launch, f);
   }
   C6_LAUNCHED(e, "finish_kernel");
@@ -385,7 +381,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     ProfScope _ps(e, C6_KIND_PACK, st);
     pack_stem_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
         input_of(a), a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->kc_short, e->n, nb, a.T, t0,
-        ++e->stem_epoch, e->p2_epoch);
+        ++e->stem_epoch, e->p2_epoch, e->occ);
     C6_LAUNCHED(e, "pack_stem_input_kernel");
   }
   int cur = 0;
@@ -508,7 +504,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     C6_LAUNCHED(e, "unpack_activation_kernel");
     return C6_OK;
   }
-  return launch_finish(e, a, t0, nb, g.group_pos, e->slots, e->wp, st);
+  return launch_finish(e, a, t0, nb, g.group_pos, e->slots, e->wp, e->occ, g.mrows_per_group, st);
 }
 
 int run_pass_fp32(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStream_t st) {
@@ -547,7 +543,7 @@ int run_pass_fp32(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
                                                                  e->lp[e->L - 1].cout, e->n, nb);
   }
   C6_LAUNCHED(e, "head_fp32_kernel");
-  return launch_finish(e, a, t0, nb, (long long)nb * e->cells, e->cells, e->n, st);
+  return launch_finish(e, a, t0, nb, (long long)nb * e->cells, e->cells, e->n, nullptr, 0, st);
 }
 
 int run(C6Engine* e, const RunArgs& a, void* stream) {
@@ -665,7 +661,6 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   e->have.assign((size_t)e->G * (e->L + 2), 0);
   e->h_bias.assign(e->L, std::vector<float>());
 
-  prefer_shared_memory();
   int rc;
   if ((rc = dev_alloc(e, &e->status_dev, 1, true, nullptr))) return bail(rc, "");
   if ((rc = dev_alloc(e, &e->wait_dev, 8 + 2048, true, nullptr))) return bail(rc, "");
@@ -1026,7 +1021,7 @@ int c6_forward_noalloc(C6Engine* e, const void* x, int x_dtype, int64_t B, const
   f.flags = flags;
   f.logits_out = logits;
   f.value_out = value;
-  finish_kernel<<<dim3(finish_blocks(nb), 1), kFinishThreads, finish_smem_bytes(f.n_actions), st>>>(f);
+  finish_kernel_for(f.n_actions)<<<dim3(finish_blocks(nb), 1), kFinishThreads, 0, st>>>(f);
   C6_LAUNCHED(e, "finish_kernel");
   return C6_OK;
 }
@@ -1053,7 +1048,6 @@ int c6_sample_actions(const float* logits, const uint8_t* legal, int64_t B, int3
   if (B < 0 || A <= 0 || A > kFinishMaxActions) return C6_ERR_ARG;
   if (B == 0) return C6_OK;
   if (!logits || !legal || !action) return C6_ERR_ARG;
-  prefer_shared_memory();
   FinishParams f{};
   f.logits_in = logits;
   f.legal_in = legal;
@@ -1069,8 +1063,7 @@ int c6_sample_actions(const float* logits, const uint8_t* legal, int64_t B, int3
   f.board_index0 = board_index0;
   f.action_out = reinterpret_cast<long long*>(action);
   f.logprob_out = logprob;
-  finish_kernel<<<dim3(finish_blocks(B), 1), kFinishThreads, finish_smem_bytes(f.n_actions),
-                  reinterpret_cast<cudaStream_t>(stream)>>>(f);
+  finish_kernel_for(f.n_actions)<<<dim3(finish_blocks(B), 1), kFinishThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f);
   return cudaGetLastError() == cudaSuccess ? C6_OK : C6_ERR_CUDA;
 }
 

@@ -7,9 +7,12 @@ Nothing in the shipped package imports it.
 
 Pinning: EnvOracle.step / reset / legal_mask are checked move by move against games played by
 the unmodified reference environment on CPU (tests/golden/env_*.npz, made by
-tests/golden/make_golden_env.py).  collect_done restates a block of statements inside the
-reference's training loop that is not callable on its own: parity unpinned for that function
-(checked by reading, by its invariants, and against the kernels).
+tests/golden/make_golden_env.py).  CollectorOracle.collect_done restates a block of statements
+inside the reference's training loop that is not callable on its own; it is pinned by
+tests/golden/collector_*.npz, recorded while those very statements -- cut out of the reference's
+syntax tree by the fixture generator and executed unchanged -- ran on the reference environment
+with the reference's historical-table layout (finished indices, the nine sums, episode ids and
+records, segment lengths, colour swaps, resets after every step).
 
 Reference citations (paths inside the reference project):
   connect6/vector_env.py:34-53    state tensors and dtypes          -> EnvOracle.__init__

@@ -46,6 +46,64 @@ def test_fixtures_cover_wins_draws_and_overwrites():
     assert wins > 100 and draws > 20
 
 
+COLLECTOR_FIXTURES = ["collector_7x7_win4_history", "collector_5x5_win5_draws", "collector_19x19_win6_plain"]
+
+
+def replay_collector(fx, make, bump_segments, step_fn, collect_fn, state_fn):
+    """Drive an environment + collector through a game recorded while the reference's own
+    bookkeeping statements (connect6/train.py:871-943) ran, and compare what they did after every
+    step: finished indices, the nine sums, episode ids, segment lengths, colours, the id counter."""
+    E = int(fx["num_envs"])
+    obj = make(E, int(fx["board_size"]), int(fx["win_length"]), int(fx["episode_capacity"]), fx["historical_mask"],
+               fx["initial_colors"])
+    for t in range(fx["actions"].shape[0]):
+        bump_segments(obj, fx["seg_inc"][t])
+        out = step_fn(obj, fx["actions"][t])
+        for k in ("done", "winner", "game_lengths"):
+            assert np.array_equal(np.asarray(out[k]), fx[k][t]), (k, t)
+        done_idx, stats = collect_fn(obj, out)
+        want_idx = fx["done_idx"][t]
+        want_idx = want_idx[want_idx >= 0]
+        assert np.array_equal(np.asarray(stats), fx["stats"][t]), (t, stats, fx["stats"][t])
+        assert np.array_equal(np.asarray(done_idx)[: want_idx.size], want_idx), t
+        st = state_fn(obj)
+        assert np.array_equal(st["episode_ids"], fx["episode_ids"][t]), t
+        assert np.array_equal(st["segment_lengths"], fx["segment_lengths"][t]), t
+        assert np.array_equal(st["colors"], fx["colors"][t]), t
+        assert int(st["next_episode_id"]) == int(fx["next_episode_id"][t]), t
+    st = state_fn(obj)
+    assert np.array_equal(st["episode_results"], fx["episode_results"])
+    assert np.array_equal(st["episode_terminal_moves"], fx["episode_terminal_moves"])
+    assert np.array_equal(st["boards"], fx["final_boards"]) and np.array_equal(st["moves"], fx["final_moves"])
+    # the reference's host-side running totals are the column sums of the per-step statistics
+    totals = fx["stats"].sum(0)
+    assert np.array_equal(fx["counters"][-1], totals[[0, 9, 1, 2, 3, 4, 5, 6, 7, 8]])
+
+
+@pytest.mark.parametrize("name", COLLECTOR_FIXTURES)
+def test_collector_oracle_replays_reference_bookkeeping(name):
+    fx = np.load(GOLDEN / f"{name}.npz")
+
+    def make(E, n, win, capacity, hist, colours):
+        env = EO.EnvOracle(E, n, win)
+        return env, EO.CollectorOracle(env, capacity, hist, colours)
+
+    def bump(obj, mask):
+        obj[1].current_segment_lengths[mask] += 1
+
+    replay_collector(fx, make, bump, lambda obj, a: obj[0].step(a), lambda obj, out: obj[1].collect_done(out),
+                     lambda obj: {"episode_ids": obj[1].current_episode_ids, "segment_lengths": obj[1].current_segment_lengths,
+                                  "colors": obj[1].historical_current_colors, "next_episode_id": obj[1].next_episode_id,
+                                  "episode_results": obj[1].episode_results,
+                                  "episode_terminal_moves": obj[1].episode_terminal_moves,
+                                  "boards": obj[0].boards, "moves": obj[0].move_count})
+
+
+def test_collector_fixtures_cover_history_outcomes():
+    tot = sum(np.load(GOLDEN / f"{n}.npz")["stats"].sum(0) for n in COLLECTOR_FIXTURES)
+    assert tot[9] > 300 and tot[6] > 20 and tot[7] > 20 and tot[8] > 5 and tot[3] > 20
+
+
 def test_collector_oracle_invariants():
     rng = np.random.default_rng(5)
     E = 40

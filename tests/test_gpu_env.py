@@ -10,7 +10,7 @@ import c6_env_oracle as EO
 import c6_oracle as O
 import torch_port as TP
 from conftest import GOLDEN
-from test_env_oracle import ENV_FIXTURES, replay
+from test_env_oracle import COLLECTOR_FIXTURES, ENV_FIXTURES, replay, replay_collector
 
 pytestmark = pytest.mark.gpu
 
@@ -162,6 +162,39 @@ def test_collect_done_matches_collector_oracle(cuda_device, E, n, win, with_hist
     assert np.array_equal(book.episode_results.cpu().numpy(), o_col.episode_results)
     assert np.array_equal(book.episode_terminal_moves.cpu().numpy(), o_col.episode_terminal_moves)
     assert total_done > 0 and int(env.faults.sum()) == 0
+
+
+@pytest.mark.parametrize("name", COLLECTOR_FIXTURES)
+def test_collect_done_replays_reference_bookkeeping(cuda_device, name):
+    """c6_env_collect_done against fixtures recorded while the reference's own collector statements
+    (connect6/train.py:871-943) ran on the reference environment."""
+    from connect6_b200.vector_env import RolloutBookkeeper, VectorConnect6
+    fx = np.load(GOLDEN / f"{name}.npz")
+
+    def make(E, n, win, capacity, hist, colours):
+        env = VectorConnect6(E, n, win, device=cuda_device)
+        return env, RolloutBookkeeper(env, capacity, torch.from_numpy(hist), torch.from_numpy(colours))
+
+    def bump(obj, mask):
+        obj[1].current_segment_lengths[torch.from_numpy(mask).to(cuda_device)] += 1
+
+    def step(obj, a):
+        s = obj[0].step(torch.from_numpy(np.asarray(a, np.int64)))
+        return {"done": s.done.cpu().numpy(), "winner": s.winner.cpu().numpy(),
+                "game_lengths": s.game_lengths.cpu().numpy(), "_step": s}
+
+    def collect(obj, out):
+        idx, stats = obj[1].collect(out["_step"])
+        return idx.cpu().numpy(), stats.cpu().numpy()
+
+    replay_collector(fx, lambda *a: list(make(*a)), bump, step, collect,
+                     lambda obj: {"episode_ids": obj[1].current_episode_ids.cpu().numpy(),
+                                  "segment_lengths": obj[1].current_segment_lengths.cpu().numpy(),
+                                  "colors": obj[1].historical_current_colors.cpu().numpy(),
+                                  "next_episode_id": int(obj[1].next_episode_id),
+                                  "episode_results": obj[1].episode_results.cpu().numpy(),
+                                  "episode_terminal_moves": obj[1].episode_terminal_moves.cpu().numpy(),
+                                  "boards": obj[0].boards.cpu().numpy(), "moves": obj[0].move_count.cpu().numpy()})
 
 
 def test_collect_done_flags_episode_ids_beyond_capacity(cuda_device):

@@ -56,59 +56,123 @@ def load_peaks() -> tuple[dict, str]:
 # ------------------------------------------------------------------------------------------------
 # clock sampling during the timed region
 # ------------------------------------------------------------------------------------------------
+# A child process polls NVML (read-only queries) every few milliseconds and writes one line per sample:
+# unix time, SM MHz, max SM MHz, power in W, clock-event-reason bit mask.  nvidia-smi's own loop mode is
+# the fallback when the NVML binding is missing; it is too slow to land inside a 35 ms region.
+_NVML_POLLER = r"""
+import sys, time
+import pynvml as N
+N.nvmlInit()
+h = N.nvmlDeviceGetHandleByUUID(sys.argv[1]) if sys.argv[1].startswith("GPU-") else N.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+period = float(sys.argv[2])
+mx = N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM)
+out = sys.stdout
+while True:
+    t = time.time()
+    try:
+        reasons = N.nvmlDeviceGetCurrentClocksEventReasons(h)
+    except Exception:
+        reasons = N.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+    out.write("%.6f,%d,%d,%.1f,%d\n" % (t, N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM), mx,
+                                        N.nvmlDeviceGetPowerUsage(h) / 1000.0, reasons))
+    out.flush()
+    time.sleep(period)
+"""
+# NVML clock-event-reason bits (nvml.h): software power cap 0x4, hardware slowdown 0x8, software thermal
+# slowdown 0x20, hardware thermal slowdown 0x40
+_REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 _SMI_FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
                "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
                "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
 
+def report_dir() -> Path:
+    """Where side files of a run go (clock samples): $C6_REPORT_DIR, else the temp directory."""
+    import tempfile
+    d = Path(os.environ.get("C6_REPORT_DIR", tempfile.gettempdir()))
+    d.mkdir(parents=True, exist_ok=True)
+    return d
+
+
 class ClockSampler:
-    def __init__(self, gpu_index: int):
-        self.proc = None
-        self.path = ROOT / "gpurun_out" / f"clocks_bench_gpu{gpu_index}.csv"
+    def __init__(self, gpu_index: int, period_s: float = 0.004):
+        self.proc, self.kind = None, None
+        self.path = report_dir() / f"c6_bench_clocks_gpu{gpu_index}.csv"
+        who = str(gpu_index)
+        try:   # NVML numbers devices by PCI order, CUDA may not: address the device by its UUID when torch knows it
+            import torch
+            who = "GPU-" + str(torch.cuda.get_device_properties(gpu_index).uuid)
+        except Exception:
+            pass
         try:
-            self.path.parent.mkdir(exist_ok=True)
             self.fh = open(self.path, "w")
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={_SMI_FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
-                 "-i", str(gpu_index)], stdout=self.fh, stderr=subprocess.DEVNULL)
+            try:
+                import pynvml  # noqa: F401
+                self.proc = subprocess.Popen([sys.executable, "-c", _NVML_POLLER, who, str(period_s)],
+                                             stdout=self.fh, stderr=subprocess.DEVNULL)
+                self.kind = "nvml"
+            except ImportError:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", f"--query-gpu={_SMI_FIELDS}", "--format=csv,noheader,nounits", "-lms", "10",
+                     "-i", str(gpu_index)], stdout=self.fh, stderr=subprocess.DEVNULL)
+                self.kind = "nvidia-smi"
+            time.sleep(0.5)      # the child is polling before the warm-up ends
         except Exception:
             self.proc = None
 
-    def stop(self, t_begin: dt.datetime, t_end: dt.datetime) -> dict:
+    def _rows(self):
+        for line in self.path.read_text().splitlines():
+            parts = [s.strip() for s in line.split(",")]
+            try:
+                if self.kind == "nvml":
+                    mask = int(parts[4])
+                    yield (float(parts[0]), float(parts[1]), float(parts[2]), float(parts[3]),
+                           [name for name, bit in _REASON_BITS.items() if mask & bit])
+                else:
+                    ts = dt.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+                    yield (ts, float(parts[2]), float(parts[3]), float(parts[4]),
+                           [n for n, v in zip(names, parts[6:10]) if v.lower().startswith("active")])
+            except Exception:
+                continue
+
+    def stop(self, t_begin: float, t_end: float) -> dict:
+        """Summary of the samples taken between the two unix times; samples from outside the timed
+        region are never substituted for missing ones."""
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.12)
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampler unavailable"], "samples_in_timed_region": 0}
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
         self.fh.close()
-        rows_all, rows_in = [], []
-        for line in self.path.read_text().splitlines():
-            parts = [s.strip() for s in line.split(",")]
-            if len(parts) < 10:
-                continue
-            try:
-                ts = dt.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
-                row = (float(parts[2]), float(parts[3]), float(parts[4]), parts[5:10])
-            except Exception:
-                continue
-            rows_all.append(row)
-            if t_begin <= ts <= t_end:
-                rows_in.append(row)
-        rows = rows_in if len(rows_in) >= 2 else rows_all
+        rows_all = list(self._rows())
+        rows = [r for r in rows_all if t_begin <= r[0] <= t_end]
         if not rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        names = ["active", "hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = set()
-        for r in rows:
-            for name, val in zip(names[1:], r[3][1:]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(r[0] for r in rows), "sm_max_mhz": rows[0][1],
-                "power_w_max": max(r[2] for r in rows), "reasons": sorted(reasons), "samples": len(rows),
-                "samples_in_timed_region": len(rows_in)}
+            return {"sm_mhz": None, "sm_max_mhz": rows_all[0][2] if rows_all else None, "reasons": [],
+                    "samples_in_timed_region": 0, "sampler": self.kind,
+                    "note": "no clock evidence: no sample fell inside the timed region"}
+        reasons = sorted({name for r in rows for name in r[4]})
+        return {"sm_mhz": statistics.median(r[1] for r in rows), "sm_min_mhz": min(r[1] for r in rows),
+                "sm_max_mhz": rows[0][2], "power_w_max": max(r[3] for r in rows), "reasons": reasons,
+                "samples_in_timed_region": len(rows), "sampler": self.kind}
+
+
+def pick_tensor_peak(peaks: dict, peak_kind: str, clocks: dict | None, region_s: float) -> tuple[float, str]:
+    """Denominator of a tensor-bound roofline fraction, chosen from what was sampled: the burst cuBLAS
+    figure when the timed region ran at (nearly) the maximum SM clock or was too short for the power
+    cap to bite (< 1 s), else the sustained one (a seconds-long cuBLAS loop under the same cap)."""
+    burst = float(peaks["bf16_tflops"])
+    sustained = float(peaks.get("bf16_tflops_sustained", burst))
+    mhz, mx = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
+    if region_s < 1.0:
+        return burst, f"MEASURED_PEAKS.json bf16_tflops (burst: timed region {region_s:.2f} s < 1 s), of {peak_kind}"
+    if mhz is not None and mx and mhz >= 0.95 * mx:
+        return burst, f"MEASURED_PEAKS.json bf16_tflops (burst: median SM clock {mhz:.0f} of {mx:.0f} MHz), of {peak_kind}"
+    why = f"median SM clock {mhz:.0f} of {mx:.0f} MHz" if mhz is not None and mx else "no clock sample, region >= 1 s"
+    return sustained, f"MEASURED_PEAKS.json bf16_tflops_sustained ({why} over {region_s:.1f} s), of {peak_kind}"
 
 
 # ------------------------------------------------------------------------------------------------
@@ -245,8 +309,9 @@ def run_engine(args) -> None:
     torch.cuda.set_device(dev)
     peaks, peak_kind = load_peaks()
 
+    precision = args.precision
     torch.manual_seed(WEIGHT_SEED)
-    model = PolicyValueNet(19).to(dev).eval()
+    model = PolicyValueNet(19, engine_precision=precision).to(dev).eval()
     eng = model.engine_for(dev)
     eng.reserve(BATCH)
 
@@ -281,7 +346,7 @@ def run_engine(args) -> None:
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(dev)
     shard.barrier()
-    t_begin = dt.datetime.now()
+    t_begin = time.time()
     ev0.record()
     for i in range(args.steps):
         sample = i % every == 0
@@ -290,7 +355,7 @@ def run_engine(args) -> None:
         step(args.warmup + i)
     ev1.record()
     torch.cuda.synchronize(dev)
-    t_end = dt.datetime.now()
+    t_end = time.time()
     shard.barrier()
     elapsed_ms = ev0.elapsed_time(ev1)
     prof = eng.profile_read()
@@ -361,26 +426,36 @@ def run_engine(args) -> None:
     total_boards = BATCH * world * args.steps
     value = total_boards / (elapsed_ms * 1e-3)
     ms_per_step = elapsed_ms / args.steps
-    # dominant kernel: conv_tc_kernel (backbone layers 1..7, 7 launches per step)
+    # dominant kernel: the backbone layers after the stem (7 launches per step): conv_tc_kernel on the
+    # tensor cores, conv_fp32_kernel on the CUDA cores in fp32 mode
     conv_ms = sum(ms for k, (ms, n) in prof.items() if k.startswith("conv"))
     conv_launches = sum(n for k, (ms, n) in prof.items() if k.startswith("conv"))
-    conv_flop_per_step = 2 * (sum(CONV_LAYER_MACS[1:]) + HEAD_MACS) * BATCH
-    # The kernel is timed inside a seconds-long, power-capped step loop: the denominator is the
-    # SUSTAINED cuBLAS figure (a GEMM loop under the same cap); the burst figure is reported beside it.
+    conv_flop_per_step = 2 * (sum(CONV_LAYER_MACS[1:]) + (HEAD_MACS if precision != "fp32" else 0)) * BATCH
     burst = float(peaks["bf16_tflops"])
-    peak = float(peaks.get("bf16_tflops_sustained", burst))
+    if precision == "fp32":
+        # no measured fp32 figure exists for this pool: nominal FMA rate, 148 SMs x 128 lanes x 2 x max SM clock
+        peak = 148 * 128 * 2 * float(peaks.get("sm_max_mhz", 1965.0)) * 1e6 / 1e12
+        peak_source = "nominal fp32 FMA rate (148 SMs x 128 lanes x 2 x max SM clock): no measured fp32 peak on this pool"
+    else:
+        peak, peak_source = pick_tensor_peak(peaks, peak_kind, clocks, elapsed_ms * 1e-3)
     roof = None
     if conv_launches:
         avg_ms = conv_ms / conv_launches
         flop_per_launch = conv_flop_per_step * sampled_steps / conv_launches
         achieved = flop_per_launch / (avg_ms * 1e-3) / 1e12
-        roof = {"bound": "tensor", "kernel": "conv_tc_kernel (backbone layers 1-7 + fused heads)",
+        roof = {"bound": "tensor" if precision != "fp32" else "fp32 FMA (CUDA cores)",
+                "kernel": ("conv_tc_kernel (backbone layers 1-7 + fused heads)" if precision != "fp32"
+                           else "conv_fp32_kernel (backbone layers 1-7)"),
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": f"MEASURED_PEAKS.json bf16_tflops_sustained (kernel timed inside a long step), of {peak_kind}",
-                "burst_peak": burst, "frac_of_burst": achieved / burst,
-                "traffic": CONV_TRAFFIC_BYTES_PER_LAUNCH, "launches": conv_launches, "avg_launch_ms": avg_ms,
+                "peak_source": peak_source,
+                "traffic": CONV_TRAFFIC_BYTES_PER_LAUNCH if precision != "fp32" else None,
+                "launches": conv_launches, "avg_launch_ms": avg_ms,
                 "timed_with": f"CUDA events around every launch of {sampled_steps} of the {args.steps} timed steps",
                 "flop_per_launch": flop_per_launch}
+        if precision != "fp32":
+            roof.update({"burst_peak": burst, "frac_of_burst": achieved / burst,
+                         "sustained_peak": float(peaks.get("bf16_tflops_sustained", burst)),
+                         "frac_of_sustained": achieved / float(peaks.get("bf16_tflops_sustained", burst))})
     kernels = {}
     for k, (ms, n) in sorted(prof.items()):
         entry = {"ms_per_step": ms / sampled_steps, "launches_per_step": n / sampled_steps}
@@ -394,11 +469,12 @@ def run_engine(args) -> None:
     whole_tflops = value / world * FLOP_PER_BOARD / 1e12
 
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if precision == "bf16" else METRIC.replace("bf16", precision), "value": value, "unit": UNIT,
+        "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": None, "dtype": {"bf16": "bf16", "f16": "f16", "fp32": "f32"}[precision], "data": "synthetic",
         "config": {"workload": "self-play inference step: default v4 CNN (kernels [23,3x7], channels "
-                               "[32,32,64,64,64,96,96,96]) bf16 forward + masked log-softmax + 1 Philox draw/board "
+                               f"[32,32,64,64,64,96,96,96]) {precision} forward + masked log-softmax + 1 Philox draw/board "
                                "+ value",
                    "global_batch": BATCH * world, "per_gpu_batch": BATCH, "parallelism": f"boards sharded x{world}",
                    "l2": f"inputs rotate over {INPUT_BUFFERS} resident batches ({INPUT_BUFFERS * h2d / 1e6:.0f} MB "
@@ -414,11 +490,13 @@ def run_engine(args) -> None:
         "gpu_launches": launches,
         "roofline": roof,
         "whole_step": {"tflops_per_gpu": whole_tflops, "frac_of_peak": whole_tflops / peak, "frac_of_burst": whole_tflops / burst,
-                       "flop_per_board": FLOP_PER_BOARD},
+                       "flop_per_board": FLOP_PER_BOARD,
+                       # runs at different clocks compare through time x clock: SM megacycles per step
+                       "sm_mcycles_per_step": (ms_per_step * 1e-3 * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None},
         "kernels": kernels,
         "device_status": status,
     }
-    if world == 1 and not args.no_library_bar:
+    if world == 1 and not args.no_library_bar and precision != "fp32":
         line["library_gpu_bar"] = library_gpu_bar(model, dev_batches)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline()
@@ -493,13 +571,13 @@ def run_workload(args) -> None:
     eng.profile(True)
     eng.profile_read()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_begin = dt.datetime.now()
+    t_begin = time.time()
     ev0.record()
     for i in range(args.steps):
         step(args.warmup + i)
     ev1.record()
     torch.cuda.synchronize(dev)
-    t_end = dt.datetime.now()
+    t_end = time.time()
     shard.barrier()
     prof = eng.profile_read()
     ms = shard.max_over_ranks(ev0.elapsed_time(ev1), dev)
@@ -509,20 +587,47 @@ def run_workload(args) -> None:
         total_boards = (boards * world if scaling == "weak" else (65536 if wl == "cfg4" else 32768)) * args.steps
         value = total_boards / (ms * 1e-3)
         burst = float(peaks["bf16_tflops"])
-        peak = float(peaks.get("bf16_tflops_sustained", burst))
+        peak, peak_source = pick_tensor_peak(peaks, peak_kind, clocks, ms * 1e-3)
         line = {"metric": METRIC.replace("B=8192", wl), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": scaling,
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": desc},
                 "clocks": clocks, "gpu_launches": eng.launch_count - launches0,
                 "whole_step": {"tflops_per_gpu": value / world * flop / 1e12, "frac_of_peak": value / world * flop / 1e12 / peak,
                                "frac_of_burst": value / world * flop / 1e12 / burst,
-                               "flop_per_board": flop, "peak_source": f"bf16_tflops_sustained, of {peak_kind}"},
+                               "flop_per_board": flop, "peak_source": peak_source},
                 "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                             for k, v in sorted(prof.items())},
                 "device_status": status}
         print(json.dumps(line), flush=True)
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def run_small_case(args) -> None:
+    """--workload small: a short, self-ending run for profilers -- `--steps` self-play inference steps of the
+    default network on `--boards` generated boards (default 2048: the widest activations exceed L2 while
+    the process holds well under 1 GB on the device), nothing else.  Prints one JSON line with a checksum,
+    the device status word and the mean step time between CUDA events."""
+    import torch
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.model import PolicyValueNet
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(WEIGHT_SEED)
+    model = PolicyValueNet(19, engine_precision=args.precision).to(dev).eval()
+    x = torch.from_numpy(generate_planes(0, args.boards)).to(dev)
+    for i in range(args.warmup):
+        model.selfplay_step(x, seed=1, offset=i)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        actions, logprob, value, _ = model.selfplay_step(x, seed=1, offset=args.warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / max(1, args.steps)
+    print(json.dumps({"workload": "small", "precision": args.precision, "boards": args.boards, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": ms, "boards_per_s": args.boards / (ms * 1e-3),
+                      "checksum": [int(actions.sum()), float(value.sum())],
+                      "device_status": model.engine_for(dev).status()}), flush=True)
 
 
 _LINE_DIRECTIONS = ((1, 0), (0, 1), (1, 1), (1, -1))
@@ -614,13 +719,13 @@ def run_selfplay_loop(args) -> None:
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = eng.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_begin = dt.datetime.now()
+    t_begin = time.time()
     e0.record()
     for i in range(args.steps):
         loop_step(args.warmup + i, ev_env[i])
     e1.record()
     torch.cuda.synchronize(dev)
-    t_end = dt.datetime.now()
+    t_end = time.time()
     shard.barrier()
     ms = shard.max_over_ranks(e0.elapsed_time(e1), dev)
     clocks = sampler.stop(t_begin, t_end) if sampler else None
@@ -701,14 +806,23 @@ def main() -> None:
                     help="record per-kernel CUDA events on one timed step in this many (1 = every step)")
     ap.add_argument("--no-library-bar", action="store_true",
                     help="skip the stock PyTorch/cuDNN timing of the same step on this GPU")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "selfplay"],
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "f16", "fp32"],
+                    help="arithmetic mode of the engine for --workload cfg2: bf16 is the contract's benchmark; f16 the "
+                         "fp16 tensor-core mode; fp32 the CUDA-core exact mode")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "selfplay", "small"],
                     help="cfg2 (default) is the contract's benchmark; cfg3-5 are BASELINE's other configurations; "
-                         "selfplay adds the environment step and bookkeeping around the network")
+                         "selfplay adds the environment step and bookkeeping around the network; small is a short "
+                         "self-ending run of --boards boards for profilers")
+    ap.add_argument("--boards", type=int, default=2048, help="boards of --workload small")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = 20 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else args.warmup
         run_reference(args)
+    elif args.workload == "small":
+        args.steps = 2 if args.steps is None else args.steps
+        args.warmup = 1 if args.warmup is None else args.warmup
+        run_small_case(args)
     elif args.workload == "selfplay":
         args.steps = 200 if args.steps is None else args.steps
         args.warmup = 10 if args.warmup is None else max(args.warmup, 3)
@@ -718,8 +832,9 @@ def main() -> None:
         args.warmup = 5 if args.warmup is None else max(args.warmup, 3)
         run_workload(args)
     else:
-        args.steps = 300 if args.steps is None else args.steps
-        args.warmup = 10 if args.warmup is None else max(args.warmup, 3)   # never fewer than 3 warm-ups
+        # default: a timed region of a few seconds, so that the power cap and the sampled clocks apply to it
+        args.steps = (1500 if args.precision != "fp32" else 12) if args.steps is None else args.steps
+        args.warmup = (10 if args.precision != "fp32" else 3) if args.warmup is None else max(args.warmup, 3)
         run_engine(args)
 
 

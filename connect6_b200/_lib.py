@@ -1,4 +1,4 @@
-"""ctypes binding of the engine's C ABI (include/c6_engine.h, include/c6_env.h).
+"""ctypes binding of the engine's C ABI (include/c6_engine.h, include/c6_env.h, include/c6_debug.h).
 
 The library is loaded from the package directory (connect6_b200/libc6engine.so).  There is no
 fallback: if the library is missing or a call fails, an exception is raised.
@@ -12,7 +12,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libc6engine.so"
 
 C6_MAX_LAYERS = 16
 C6_OK, C6_ERR_ARG, C6_ERR_CUDA, C6_ERR_UNSUPPORTED, C6_ERR_WEIGHTS, C6_ERR_DEVICE = range(6)
-C6_PREC_BF16, C6_PREC_FP32 = 0, 1
+C6_PREC_BF16, C6_PREC_FP32, C6_PREC_F16 = 0, 1, 2
+C6_STATUS_WAIT_MASK, C6_STATUS_BAD_INDEX, C6_STATUS_F16_RANGE = 63, 64, 128
 C6_X_F32, C6_X_BF16 = 0, 1
 C6_HEAD_POLICY, C6_HEAD_VALUE = 100, 101
 C6_FLAG_MASK_LOGITS, C6_FLAG_INVERSE_MAP = 1, 2
@@ -57,7 +58,7 @@ C6_STAT_COUNT, C6_STAT_DONE_COUNT = 10, 9
 
 _vp, _i, _i64, _u64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_float
 
-# name -> (restype, argtypes); mirrors include/c6_engine.h and include/c6_env.h declaration by declaration
+# name -> (restype, argtypes); mirrors include/*.h declaration by declaration
 SIGNATURES = {
     "c6_version": (_i, []),
     "c6_create": (_i, [C.POINTER(C6Desc), C.POINTER(_vp)]),
@@ -66,7 +67,7 @@ SIGNATURES = {
     "c6_forward": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp]),
     "c6_forward_noalloc": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp]),
     "c6_forward_step": (_i, [_vp, _vp, _i, _i64, _vp, _i, _f, _u64, _u64, _i64, _vp, _vp, _vp, _vp, _vp]),
-    "c6_forward_step_boards": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _f, _u64, _u64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "c6_forward_step_boards": (_i, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i, _f, _u64, _u64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "c6_forward_grouped": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _i, _vp]),
     "c6_sample_actions": (_i, [_vp, _vp, _i64, C.c_int32, _f, _u64, _u64, _i64, _vp, _vp, _vp]),
     "c6_mask_logits": (_i, [_vp, _vp, _i64, _f, _vp, _vp]),

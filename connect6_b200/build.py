@@ -2,7 +2,9 @@
 
 `python -m connect6_b200.build` compiles connect6_b200/csrc/c6_engine.cu and c6_env.cu into
 connect6_b200/libc6engine.so.  The library links the CUDA runtime statically and has no
-dependency on libtorch, so it loads with ctypes from any process.
+dependency on libtorch, so it loads with ctypes from any process.  With C6_TIMED_BUILD=1 in the
+environment the clock-counter instantiations of the k x k kernel (include/c6_debug.h) are compiled
+in as well; the default library carries none.
 """
 from __future__ import annotations
 
@@ -45,6 +47,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not is_stale():
         return LIB_PATH
     cmd = [find_nvcc(), *NVCC_FLAGS]
+    if os.environ.get("C6_TIMED_BUILD", "0") not in ("", "0"):
+        cmd.append("-DC6_TIMED_BUILD")
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", str(LIB_PATH), *map(str, SOURCES)]

@@ -4,6 +4,7 @@
 #pragma once
 
 #include "c6_common.cuh"
+#include "c6_tc.cuh"
 
 namespace c6 {
 
@@ -50,7 +51,9 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
                                        long long group_stride, // boards between groups in x
                                        long long board0,       // first board of this pass in a group
                                        unsigned int epoch, unsigned int* __restrict__ p2_epoch,
-                                       uint8_t* __restrict__ occ) {   // [kc_short][mrows] bit j of a byte: element 8c+j != 0
+                                       uint8_t* __restrict__ occ,     // [kc_short][mrows] bit j of a byte: element 8c+j != 0
+                                       int f16,                       // operand type of the engine: 0 bf16, 1 fp16
+                                       int* __restrict__ status) {
   grid_dep_launch();
   const int g = blockIdx.y;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -60,6 +63,7 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
   const int cells = n * n;
   const long long src_board = (long long)g * group_stride + board0 + t;
   const int phase = orient ? (orient[src_board] & 7) : 0;
+  if (c == 0 && in.boards != nullptr && input_env(in, src_board) < 0) atomicOr(status, kStatBadIndex);
   // level of the third plane: needed by the chunk that holds the level slots and by the plane-2 chunks
   const bool wants_level = c >= kc_short || (c + 1) * 8 > 2 * cells;
   const float level = wants_level ? input_value(in, src_board, 2, 0, cells) : 0.f;
@@ -98,10 +102,10 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
   }
   if (varies) atomicExch(p2_epoch, epoch);
   uint4 o;
-  o.x = pack_bf16x2(v[0], v[1]);
-  o.y = pack_bf16x2(v[2], v[3]);
-  o.z = pack_bf16x2(v[4], v[5]);
-  o.w = pack_bf16x2(v[6], v[7]);
+  o.x = pack_h2(v[0], v[1], f16);
+  o.y = pack_h2(v[2], v[3], f16);
+  o.z = pack_h2(v[4], v[5], f16);
+  o.w = pack_h2(v[6], v[7], f16);
   const size_t brow = (size_t)g * mrows_per_group + t;   // board row over all groups
   xk[((brow >> 7) * kc + c) * 128 + (brow & 127)] = o;
 }
@@ -131,7 +135,7 @@ __global__ void view_input_f32_kernel(const InputSrc in,
 // k x k layer -> rows [q][tap][j][co] of 8 bf16: element e of the row is input channel
 // (2q+j)*8+e.  Channels beyond the real counts are zero.
 __global__ void pack_conv_weights_kernel(const float* __restrict__ w, uint4* __restrict__ out,
-                                         int cout, int cin, int kside, int cout_p, int cin_p) {
+                                         int cout, int cin, int kside, int cout_p, int cin_p, int f16) {
   const int taps = kside * kside;
   const long long total = (long long)(cin_p / 16) * taps * 2 * cout_p;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -149,16 +153,16 @@ __global__ void pack_conv_weights_kernel(const float* __restrict__ w, uint4* __r
     v[e] = (co < cout && ci < cin) ? w[((size_t)co * cin + ci) * taps + tap] : 0.f;
   }
   uint4 o;
-  o.x = pack_bf16x2(v[0], v[1]);
-  o.y = pack_bf16x2(v[2], v[3]);
-  o.z = pack_bf16x2(v[4], v[5]);
-  o.w = pack_bf16x2(v[6], v[7]);
+  o.x = pack_h2(v[0], v[1], f16);
+  o.y = pack_h2(v[2], v[3], f16);
+  o.z = pack_h2(v[4], v[5], f16);
+  o.w = pack_h2(v[6], v[7], f16);
   out[idx] = o;
 }
 
 // Same rows for the CTA-pair kernel: [half][q][tap][j][co % (cout_p/2)], half = co / (cout_p/2).
 __global__ void pack_conv_weights_pair_kernel(const float* __restrict__ w, uint4* __restrict__ out,
-                                              int cout, int cin, int kside, int cout_p, int cin_p) {
+                                              int cout, int cin, int kside, int cout_p, int cin_p, int f16) {
   const int taps = kside * kside, nh = cout_p / 2;
   const long long total = (long long)(cin_p / 16) * taps * 2 * cout_p;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -179,10 +183,10 @@ __global__ void pack_conv_weights_pair_kernel(const float* __restrict__ w, uint4
     v[e] = (co < cout && ci < cin) ? w[((size_t)co * cin + ci) * taps + tap] : 0.f;
   }
   uint4 o;
-  o.x = pack_bf16x2(v[0], v[1]);
-  o.y = pack_bf16x2(v[2], v[3]);
-  o.z = pack_bf16x2(v[4], v[5]);
-  o.w = pack_bf16x2(v[6], v[7]);
+  o.x = pack_h2(v[0], v[1], f16);
+  o.y = pack_h2(v[2], v[3], f16);
+  o.z = pack_h2(v[4], v[5], f16);
+  o.w = pack_h2(v[6], v[7], f16);
   out[idx] = o;
 }
 
@@ -201,7 +205,7 @@ __device__ __forceinline__ float stem_toeplitz_value(const float* __restrict__ w
 
 __global__ void pack_stem_toeplitz_kernel(const float* __restrict__ w, uint4* __restrict__ out,
                                           int cout, int kside, int n, int c1, int kc, int kc_short, int ntot, int nt,
-                                          int halves) {
+                                          int halves, int f16) {
   const long long total = (long long)kc * ntot;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -219,20 +223,21 @@ __global__ void pack_stem_toeplitz_kernel(const float* __restrict__ w, uint4* __
       val = stem_toeplitz_value(w, cout, kside, n, co, cell_out, ci, cell_in);
     } else if (kind == 2) {
       // what a third plane of constant value 1 adds to this output: the sum of its plane-2 weights as
-      // the tensor cores see them (bf16), carried as a bf16 high part and the bf16 of the remainder
+      // the tensor cores see them (rounded to the operand type), carried as a high part in that type
+      // and the remainder
       float sum = 0.f;
       for (int ck = 0; ck < cells; ++ck)
-        sum += __bfloat162float(__float2bfloat16_rn(stem_toeplitz_value(w, cout, kside, n, co, cell_out, 2, ck)));
-      const float hi = __bfloat162float(__float2bfloat16_rn(sum));
+        sum += round_h(stem_toeplitz_value(w, cout, kside, n, co, cell_out, 2, ck), f16);
+      const float hi = round_h(sum, f16);
       val = cell_in == 0 ? hi : sum - hi;
     }
     v[e] = val;
   }
   uint4 q;
-  q.x = pack_bf16x2(v[0], v[1]);
-  q.y = pack_bf16x2(v[2], v[3]);
-  q.z = pack_bf16x2(v[4], v[5]);
-  q.w = pack_bf16x2(v[6], v[7]);
+  q.x = pack_h2(v[0], v[1], f16);
+  q.y = pack_h2(v[2], v[3], f16);
+  q.z = pack_h2(v[4], v[5], f16);
+  q.w = pack_h2(v[6], v[7], f16);
   const int tile = o / nt, ol = o - tile * nt, nloc = nt / halves;
   const int h = ol / nloc, rr = ol - h * nloc;
   out[(((size_t)tile * halves + h) * kc + c) * nloc + rr] = q;
@@ -520,29 +525,36 @@ __global__ void network_input_kernel(const int8_t* __restrict__ boards, const in
   o[2 * cells] = stones_left[b] == 1 ? 1.f : 0.f;
 }
 
-// Self-test of the bounded-wait path: waits on an mbarrier that nobody arrives on, with a short
-// limit, then records the same status bit a real kernel would and returns normally.
+// Self-test of the bounded-wait path: the kernels' own wait helper (tc::mbar_wait) on an mbarrier
+// that nobody arrives on, with a short limit.  The wait runs out, and the kernel does what every
+// role of the tensor-core kernels does then: records its status bit, raises the CTA's abort flag
+// (which a second waiter observes and leaves on) and returns normally.
 __global__ void expire_wait_kernel(int* status, long long limit_cycles) {
   __shared__ uint64_t bar;
+  __shared__ int abort_flag;
   if (threadIdx.x == 0) {
-    const uint32_t b = static_cast<uint32_t>(__cvta_generic_to_shared(&bar));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b) : "memory");
-    const long long t0 = clock64();
-    bool done = false;
-    while (!done && clock64() - t0 < limit_cycles) {
-      uint32_t ok;
-      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                   : "=r"(ok) : "r"(b) : "memory");
-      done = ok != 0;
+    abort_flag = 0;
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    tc::fence_barrier_init();
+  }
+  __syncthreads();
+  const uint32_t b = tc::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    // first waiter: runs into the time limit
+    if (!tc::mbar_wait(b, 0, &abort_flag, 0, limit_cycles)) {
+      atomicOr(status, kStatWaitFull);
+      abort_flag = 1;
     }
-    if (!done) atomicOr(status, kStatWaitFull);
+  } else if (threadIdx.x == 32) {
+    // second waiter, with the kernels' full limit: must leave because the first raised the abort flag
+    if (!tc::mbar_wait(b, 0, &abort_flag, 20) && abort_flag) atomicOr(status, kStatWaitEmpty);
   }
 }
 
 // Debug aid: activation planes -> fp32 NCHW [G*nb, c, n, n]
 __global__ void unpack_activation_kernel(const uint4* __restrict__ planes, long long plane_rows, int front,
                                          int group_pos, int slots, int wp, int n, int c_real, int nb,
-                                         float* __restrict__ out) {
+                                         float* __restrict__ out, int f16) {
   const int g = blockIdx.y;
   const int cells = n * n;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -553,8 +565,10 @@ __global__ void unpack_activation_kernel(const uint4* __restrict__ planes, long 
   const int t = (int)(r / c_real);
   const int rr = cell / n, cc = cell - rr * n;
   const long long row = (long long)front + (long long)g * group_pos + (long long)t * slots + rr * wp + cc;
-  const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(planes + (size_t)(ch >> 3) * plane_rows + row);
-  out[((size_t)g * nb + t) * c_real * cells + (size_t)ch * cells + cell] = __bfloat162float(e[ch & 7]);
+  const void* e = planes + (size_t)(ch >> 3) * plane_rows + row;
+  out[((size_t)g * nb + t) * c_real * cells + (size_t)ch * cells + cell] =
+      f16 ? __half2float(reinterpret_cast<const __half*>(e)[ch & 7])
+          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e)[ch & 7]);
 }
 
 }  // namespace c6

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -16,6 +17,8 @@ constexpr int kStatWaitTmemFull = 4;  // epilogue wait on accumulator-ready ran 
 constexpr int kStatWaitTmemEmpty = 8; // MMA wait on accumulator-drained ran out
 constexpr int kStatWaitWeights = 16;  // wait on resident-weights barrier ran out
 constexpr int kStatWaitDrain = 32;    // final drain wait ran out
+constexpr int kStatBadIndex = 64;     // a gather index pointed outside [0, num_envs): that board was read as empty
+constexpr int kStatF16Range = 128;    // fp16 mode: an activation exceeded the fp16 range and was clamped to +-65504
 
 // ---- D4 maps (connect6/train.py:216-277) ------------------------------------------
 // phase p in 0..7 -> k = p % 4 quarter turns (counter-clockwise), mirror columns if p >= 4.
@@ -90,6 +93,25 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
+// fp16 pair, round to nearest even; values beyond the fp16 range become +-65504 instead of infinity
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// The 16-bit operand type of a tensor-core engine: bf16 (8-bit significand, fp32's exponent range) or
+// fp16 (11-bit significand, range +-65504).
+template <bool F16>
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  return F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi, int f16) {
+  return f16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+}
+// value -> 16-bit operand type -> float (what the tensor cores will see)
+__device__ __forceinline__ float round_h(float v, int f16) {
+  return f16 ? __half2float(__float2half_rn(v)) : __bfloat162float(__float2bfloat16_rn(v));
+}
 
 __device__ __forceinline__ float load_x(const void* x, int x_bf16, int64_t idx) {
   return x_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[idx])
@@ -107,11 +129,19 @@ struct InputSrc {
   const int8_t* player;      // [envs]
   const int8_t* stones_left; // [envs]
   const long long* index;    // nullable [B]: board b of the batch is environment index[b]
+  long long num_envs;        // environments behind `boards`: an index outside [0, num_envs) reads as an empty board
 };
+
+// environment of batch board b, or -1 when its index entry lies outside the state tensors
+__device__ __forceinline__ long long input_env(const InputSrc& in, long long b) {
+  const long long e = in.index ? in.index[b] : b;
+  return (e >= 0 && e < in.num_envs) ? e : -1;
+}
 
 __device__ __forceinline__ float input_value(const InputSrc& in, long long b, int ci, int cell, int cells) {
   if (in.boards == nullptr) return load_x(in.x, in.x_bf16, (b * 3 + ci) * cells + cell);
-  const long long e = in.index ? in.index[b] : b;
+  const long long e = input_env(in, b);
+  if (e < 0) return 0.f;   // never dereferenced: the pack kernel records kStatBadIndex for it
   if (ci == 2) return in.stones_left[e] == 1 ? 1.f : 0.f;
   const int v = in.boards[e * cells + cell], me = in.player[e];
   return (ci == 0 ? v == me : v == -me) ? 1.f : 0.f;

@@ -98,9 +98,11 @@ __host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 *
 // [r*N/2, (r+1)*N/2) of every weight block; the leader (r = 0) issues the MMAs, which read both
 // CTAs' shared memory at the same offsets.  Halving the B operand per CTA cuts the shared-memory
 // operand traffic that bounds a 128 x N MMA for N < 128 and frees shared memory for more stages.
+// F16 = true: operands and stored activations are fp16 instead of bf16 (same MMA rate, 11-bit instead
+// of 8-bit significands, range +-65504: stores saturate and the CTA reports kStatF16Range).
 // TIMED = true compiles the in-kernel clock counters in (p.wait_cycles); the plain instantiation
 // carries none of them: even untaken, they cost the epilogue 2-3 % on the narrow layers.
-template <int KS, bool PAIR, bool TIMED>
+template <int KS, bool PAIR, bool F16, bool TIMED>
 __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte aligned view of dynamic shared memory
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     // keeps descriptors and barrier addresses in uniform registers); one elected lane issues the
     // MMAs and commits.  It consumes its private stage ring [i*spi, (i+1)*spi).
     const int issuer = warp - 1;
-    const uint32_t idesc = tc::make_idesc_bf16(PAIR ? 256 : 128, p.n);
+    const uint32_t idesc = tc::make_idesc_16(PAIR ? 256 : 128, p.n, F16);
     const int kh = p.kside >> 1;
     const uint32_t desc_hi = (uint32_t)(tc::make_desc(0, 0, 128u) >> 32);   // SBO = 128 B, version 1
     const uint32_t a_lbo_field = ((uint32_t)(rows * 16) >> 4) << 16;          // LBO = plane pitch of a stage
@@ -456,6 +458,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const int nunits = p.n >> 4;
     bool ok = true;
     unsigned int wait_tfull = 0, ep_ld = 0, ep_math = 0;   // 32-bit clocks: registers are scarce here
+    float amax = 0.f;                                      // fp16 mode: largest |activation| this thread stored
     for (int tcount = team; tcount < ntl && ok; tcount += nteams) {
       const int tile = t_first + tcount * t_stride;
       const int acc = tcount % p.nacc;
@@ -543,13 +546,17 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
                 }
               }
             } else {
+              if (F16) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(y[j]));
+              }
 #pragma unroll
               for (int k = 0; k < 2; ++k) {
                 uint4 o;
-                o.x = valid ? pack_bf16x2(y[8 * k + 0], y[8 * k + 1]) : 0u;
-                o.y = valid ? pack_bf16x2(y[8 * k + 2], y[8 * k + 3]) : 0u;
-                o.z = valid ? pack_bf16x2(y[8 * k + 4], y[8 * k + 5]) : 0u;
-                o.w = valid ? pack_bf16x2(y[8 * k + 6], y[8 * k + 7]) : 0u;
+                o.x = valid ? pack_h2<F16>(y[8 * k + 0], y[8 * k + 1]) : 0u;
+                o.y = valid ? pack_h2<F16>(y[8 * k + 2], y[8 * k + 3]) : 0u;
+                o.z = valid ? pack_h2<F16>(y[8 * k + 4], y[8 * k + 5]) : 0u;
+                o.w = valid ? pack_h2<F16>(y[8 * k + 6], y[8 * k + 7]) : 0u;
                 out_row[(size_t)(u * 2 + k) * p.plane_rows] = o;
               }
             }
@@ -566,6 +573,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
         ep_math += (unsigned int)clock() - e1;   // release + arithmetic + stores (+ later fetches)
       }
     }
+    if (F16 && !(amax <= 65504.f)) atomicOr(p.status, kStatF16Range);
     if (timing && threadIdx.x == 32 * kEpiWarp0) {
       p.wait_cycles[3] += wait_tfull;
       p.wait_cycles[6] += ep_ld;     // first TMEM fetch of each tile: issue to data

@@ -16,6 +16,7 @@
 #include <string>
 #include <vector>
 
+#include "../../include/c6_debug.h"
 #include "../../include/c6_engine.h"
 #include "c6_aux_kernels.cuh"
 #include "c6_conv_tc.cuh"
@@ -27,7 +28,12 @@ using namespace c6;
 namespace {
 
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory per CTA on sm_100
-constexpr int kVersion = 10000;
+constexpr int kVersion = 10100;
+#ifdef C6_TIMED_BUILD
+constexpr bool kTimedBuild = true;    // the clock-counter instantiations of the k x k kernel are compiled in
+#else
+constexpr bool kTimedBuild = false;
+#endif
 
 thread_local std::string g_create_error = "";
 
@@ -54,6 +60,7 @@ struct C6Engine {
   int device = 0, sms = 148;
   int n = 0, cells = 0, pad = 1, wp = 0, slots = 0, halo = 0, halo_rows = 0, front = 0;
   int L = 0, G = 1, prec = 0, chunk = 0;
+  int f16 = 0;                      // tensor-core modes: 16-bit operand type, 0 = bf16, 1 = fp16
   std::vector<LayerPlan> lp;
   int cmax_p = 0, cmax = 0;
   // stem GEMM plan
@@ -149,12 +156,38 @@ struct ProfScope {
 };
 
 // Opt every instantiation of the k x k kernel for one filter side into the large dynamic shared memory.
+template <int KS, bool F16, bool TIMED>
+bool conv_smem_opt_in2() {
+  return cudaFuncSetAttribute(conv_tc_kernel<KS, false, F16, TIMED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess &&
+         cudaFuncSetAttribute(conv_tc_kernel<KS, true, F16, TIMED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess;
+}
 template <int KS>
 bool conv_smem_opt_in() {
-  return cudaFuncSetAttribute(conv_tc_kernel<KS, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess &&
-         cudaFuncSetAttribute(conv_tc_kernel<KS, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess &&
-         cudaFuncSetAttribute(conv_tc_kernel<KS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess &&
-         cudaFuncSetAttribute(conv_tc_kernel<KS, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) == cudaSuccess;
+  bool ok = conv_smem_opt_in2<KS, false, false>() && conv_smem_opt_in2<KS, true, false>();
+#ifdef C6_TIMED_BUILD
+  ok = ok && conv_smem_opt_in2<KS, false, true>() && conv_smem_opt_in2<KS, true, true>();
+#endif
+  return ok;
+}
+
+// The instantiation for (clock counters, CTA pairs, fp16, filter side: 0 generic, 1, 3, 5).
+using ConvKernel = void (*)(ConvTcParams);
+template <bool PAIR, bool F16, bool TIMED>
+ConvKernel conv_kernel_ks(int k) {
+  return k == 1 ? conv_tc_kernel<1, PAIR, F16, TIMED> : k == 3 ? conv_tc_kernel<3, PAIR, F16, TIMED>
+       : k == 5 ? conv_tc_kernel<5, PAIR, F16, TIMED> : conv_tc_kernel<0, PAIR, F16, TIMED>;
+}
+template <bool TIMED>
+ConvKernel conv_kernel_pf(bool pair, bool f16, int k) {
+  return pair ? (f16 ? conv_kernel_ks<true, true, TIMED>(k) : conv_kernel_ks<true, false, TIMED>(k))
+              : (f16 ? conv_kernel_ks<false, true, TIMED>(k) : conv_kernel_ks<false, false, TIMED>(k));
+}
+ConvKernel conv_kernel_for(bool timed, bool pair, bool f16, int k) {
+#ifdef C6_TIMED_BUILD
+  if (timed) return conv_kernel_pf<true>(pair, f16, k);
+#endif
+  (void)timed;
+  return conv_kernel_pf<false>(pair, f16, k);
 }
 
 // Launch with optional 2-CTA clusters and optional programmatic dependent launch (the kernel then
@@ -250,7 +283,7 @@ int ensure_workspace(C6Engine* e, long long nb) {
   C6_CUDA(e, cudaDeviceSynchronize());
   free_workspace(e);
   const Geometry g = geometry(e, nb);
-  if (e->prec == C6_PREC_BF16) {
+  if (e->prec != C6_PREC_FP32) {
     e->plane_rows = (long long)e->front + (long long)e->G * g.group_pos + e->halo_rows;
     e->mrows = (long long)e->G * g.mrows_per_group;
     const size_t act_rows = (size_t)(e->cmax_p / 8) * e->plane_rows;
@@ -300,6 +333,7 @@ struct RunArgs {
   const int8_t* player = nullptr;
   const int8_t* stones_left = nullptr;
   const long long* index = nullptr;
+  long long num_envs = 0;               // board-input mode: environments behind the state pointers
   long long T = 0;  // boards per group
   const uint8_t* orient = nullptr;
   float* logits = nullptr;
@@ -323,6 +357,7 @@ InputSrc input_of(const RunArgs& a) {
   in.player = a.player;
   in.stones_left = a.stones_left;
   in.index = a.index;
+  in.num_envs = a.num_envs;
   return in;
 }
 
@@ -381,7 +416,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     ProfScope _ps(e, C6_KIND_PACK, st);
     pack_stem_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
         input_of(a), a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->kc_short, e->n, nb, a.T, t0,
-        ++e->stem_epoch, e->p2_epoch, e->occ);
+        ++e->stem_epoch, e->p2_epoch, e->occ, e->f16, e->status_dev);
     C6_LAUNCHED(e, "pack_stem_input_kernel");
   }
   int cur = 0;
@@ -420,13 +455,13 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     if (e->stem_pair) {
       const long long items = (long long)e->G * (p.mtiles / 2) * p.ntiles;
       const int grid = 2 * (int)std::min<long long>(e->sms / 2, items);
-      launch_chain(stem_tc_kernel<true>, (unsigned)grid, 1u, kStemThreads, (size_t)e->stem_smem, st, true,
-                   e->dependent_launch, p);
+      launch_chain(e->f16 ? stem_tc_kernel<true, true> : stem_tc_kernel<true, false>, (unsigned)grid, 1u, kStemThreads,
+                   (size_t)e->stem_smem, st, true, e->dependent_launch, p);
     } else {
       const long long items = (long long)e->G * p.mtiles * p.ntiles;
       const int grid = (int)std::min<long long>(e->sms, items);
-      launch_chain(stem_tc_kernel<false>, (unsigned)grid, 1u, kStemThreads, (size_t)e->stem_smem, st, false,
-                   e->dependent_launch, p);
+      launch_chain(e->f16 ? stem_tc_kernel<false, true> : stem_tc_kernel<false, false>, (unsigned)grid, 1u, kStemThreads,
+                   (size_t)e->stem_smem, st, false, e->dependent_launch, p);
     }
     C6_LAUNCHED(e, "stem_tc_kernel");
   }
@@ -481,16 +516,8 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
       ProfScope _ps(e, C6_KIND_CONV0 + l, st);
       const int grid = e->G * p.ctas_per_group;
       const bool dep = e->dependent_launch;
-      // instantiation: filter side known at compile time (0 = generic), CTA pairs or not, clock counters or not
-      using ConvKernel = void (*)(ConvTcParams);
-      static const ConvKernel table[2][2][4] = {
-          {{conv_tc_kernel<0, false, false>, conv_tc_kernel<1, false, false>, conv_tc_kernel<3, false, false>, conv_tc_kernel<5, false, false>},
-           {conv_tc_kernel<0, true, false>, conv_tc_kernel<1, true, false>, conv_tc_kernel<3, true, false>, conv_tc_kernel<5, true, false>}},
-          {{conv_tc_kernel<0, false, true>, conv_tc_kernel<1, false, true>, conv_tc_kernel<3, false, true>, conv_tc_kernel<5, false, true>},
-           {conv_tc_kernel<0, true, true>, conv_tc_kernel<1, true, true>, conv_tc_kernel<3, true, true>, conv_tc_kernel<5, true, true>}}};
-      const int ks = lp.k == 1 ? 1 : lp.k == 3 ? 2 : lp.k == 5 ? 3 : 0;
-      launch_chain(table[p.wait_cycles ? 1 : 0][lp.pair ? 1 : 0][ks], (unsigned)grid, 1u, kConvThreads, (size_t)lp.smem, st,
-                   lp.pair != 0, dep, p);
+      launch_chain(conv_kernel_for(p.wait_cycles != nullptr, lp.pair != 0, e->f16 != 0, lp.k), (unsigned)grid, 1u,
+                   kConvThreads, (size_t)lp.smem, st, lp.pair != 0, dep, p);
     }
     C6_LAUNCHED(e, "conv_tc_kernel");
     if (!p.head) cur ^= 1;
@@ -500,7 +527,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     const long long total = (long long)nb * lp.cout * e->cells;
     unpack_activation_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
         e->act[cur], e->plane_rows, e->front, (int)g.group_pos, e->slots, e->wp, e->n, lp.cout, nb,
-        a.layer_out);
+        a.layer_out, e->f16);
     C6_LAUNCHED(e, "unpack_activation_kernel");
     return C6_OK;
   }
@@ -562,7 +589,7 @@ int run(C6Engine* e, const RunArgs& a, void* stream) {
     const int nb = (int)std::min<long long>(per_pass, a.T - t0);
     RunArgs b = a;
     // outputs are indexed [g*T + t] by the kernels themselves (board0 = t0)
-    rc = e->prec == C6_PREC_BF16 ? run_pass_bf16(e, b, t0, nb, st) : run_pass_fp32(e, b, t0, nb, st);
+    rc = e->prec != C6_PREC_FP32 ? run_pass_bf16(e, b, t0, nb, st) : run_pass_fp32(e, b, t0, nb, st);
     if (rc) return rc;
   }
   return C6_OK;
@@ -608,7 +635,8 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   if (d->n_layers < 1 || d->n_layers > C6_MAX_LAYERS) return fail(nullptr, C6_ERR_ARG, "n_layers out of range");
   if (d->board_size < 1 || d->board_size > 32) return fail(nullptr, C6_ERR_ARG, "board_size must be in 1..32");
   if (d->groups < 1) return fail(nullptr, C6_ERR_ARG, "groups must be >= 1");
-  if (d->precision != C6_PREC_BF16 && d->precision != C6_PREC_FP32) return fail(nullptr, C6_ERR_ARG, "unknown precision");
+  if (d->precision != C6_PREC_BF16 && d->precision != C6_PREC_FP32 && d->precision != C6_PREC_F16)
+    return fail(nullptr, C6_ERR_ARG, "unknown precision");
   for (int i = 0; i < d->n_layers; ++i) {
     if (d->kernels[i] <= 0 || d->kernels[i] % 2 == 0) return fail(nullptr, C6_ERR_ARG, "every kernel must be a positive odd number");
     if (d->channels[i] <= 0) return fail(nullptr, C6_ERR_ARG, "channel counts must be positive");
@@ -626,6 +654,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   e->L = d->n_layers;
   e->G = d->groups;
   e->prec = d->precision;
+  e->f16 = d->precision == C6_PREC_F16 ? 1 : 0;
   auto bail = [&](int code, const std::string& msg) {
     g_create_error = msg.empty() ? e->err : msg;
     c6_destroy(e);
@@ -635,8 +664,8 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, e->device) != cudaSuccess) return bail(C6_ERR_CUDA, "cudaGetDeviceProperties failed");
   e->sms = prop.multiProcessorCount;
-  if (e->prec == C6_PREC_BF16 && prop.major != 10)
-    return bail(C6_ERR_UNSUPPORTED, "bf16 mode needs an sm_100 GPU (tcgen05 tensor cores)");
+  if (e->prec != C6_PREC_FP32 && prop.major != 10)
+    return bail(C6_ERR_UNSUPPORTED, "the bf16 and fp16 modes need an sm_100 GPU (tcgen05 tensor cores)");
 
   e->lp.resize(e->L);
   int cin = 3;
@@ -657,7 +686,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   e->halo = e->pad * e->wp + e->pad;
   e->halo_rows = round_up(e->halo, 8);
   e->front = e->halo_rows;
-  e->chunk = d->max_chunk > 0 ? d->max_chunk : (e->prec == C6_PREC_BF16 ? 8192 : 1024);
+  e->chunk = d->max_chunk > 0 ? d->max_chunk : (e->prec != C6_PREC_FP32 ? 8192 : 1024);
   e->have.assign((size_t)e->G * (e->L + 2), 0);
   e->h_bias.assign(e->L, std::vector<float>());
 
@@ -671,9 +700,9 @@ int c6_create(const C6Desc* d, C6Engine** out) {
   e->bias.assign(e->L, nullptr);
   e->wraw.assign(e->L, nullptr);
 
-  if (e->prec == C6_PREC_BF16) {
-    if (e->L < 2) return bail(C6_ERR_UNSUPPORTED, "bf16 mode needs at least two backbone layers");
-    if (e->cmax_p > 256) return bail(C6_ERR_UNSUPPORTED, "bf16 mode supports at most 256 channels per layer");
+  if (e->prec != C6_PREC_FP32) {
+    if (e->L < 2) return bail(C6_ERR_UNSUPPORTED, "the tensor-core modes need at least two backbone layers");
+    if (e->cmax_p > 256) return bail(C6_ERR_UNSUPPORTED, "the tensor-core modes support at most 256 channels per layer");
     // stem GEMM
     const int c1 = e->lp[0].cout_p;
     const int cpt = std::max(1, 256 / c1);
@@ -763,8 +792,10 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     if ((rc = dev_alloc(e, &e->head_wp, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->head_wv, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
     if (!conv_smem_opt_in<0>() || !conv_smem_opt_in<1>() || !conv_smem_opt_in<3>() || !conv_smem_opt_in<5>() ||
-        cudaFuncSetAttribute(stem_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
-        cudaFuncSetAttribute(stem_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+        cudaFuncSetAttribute(stem_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(stem_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(stem_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(stem_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
       return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   } else {
     size_t max_smem = 0;
@@ -778,7 +809,9 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     const int cl = e->lp[e->L - 1].cout;
     if ((rc = dev_alloc(e, &e->head_wp, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->head_wv, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
-    if (cudaFuncSetAttribute(conv_fp32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max<size_t>(max_smem, 48 * 1024)) != cudaSuccess)
+    // The attribute belongs to the function on this device, not to this engine: always the full limit, so
+    // that a second engine with smaller layers never lowers it under the first one's needs.
+    if (cudaFuncSetAttribute(conv_fp32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
       return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   }
   *out = e;
@@ -791,7 +824,7 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
   if (!w) return fail(e, C6_ERR_ARG, "weight pointer is null");
   C6_CUDA(e, cudaSetDevice(e->device));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const bool bf16 = e->prec == C6_PREC_BF16;
+  const bool bf16 = e->prec != C6_PREC_FP32;   // tensor-core mode (bf16 or fp16 operands)
   if (layer == C6_HEAD_POLICY || layer == C6_HEAD_VALUE) {
     const LayerPlan& last = e->lp[e->L - 1];
     const int cl = bf16 ? last.cout_p : last.cout;
@@ -818,16 +851,16 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
       const long long total = (long long)e->kc0 * e->ntot;
       pack_stem_toeplitz_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
           w, e->wt + (size_t)group * e->kc0 * e->ntot, p.cout, p.k, e->n, p.cout_p, e->kc0, e->kc_short, e->ntot, e->nt,
-          e->stem_pair ? 2 : 1);
+          e->stem_pair ? 2 : 1, e->f16);
       C6_LAUNCHED(e, "pack_stem_toeplitz_kernel");
     } else {
       const long long total = (long long)p.w_rows_per_group;
       pack_conv_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-          w, e->wconv[layer] + (size_t)group * p.w_rows_per_group, p.cout, p.cin, p.k, p.cout_p, p.cin_p);
+          w, e->wconv[layer] + (size_t)group * p.w_rows_per_group, p.cout, p.cin, p.k, p.cout_p, p.cin_p, e->f16);
       C6_LAUNCHED(e, "pack_conv_weights_kernel");
       if (p.pair) {
         pack_conv_weights_pair_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-            w, e->wconv_pair[layer] + (size_t)group * p.w_rows_per_group, p.cout, p.cin, p.k, p.cout_p, p.cin_p);
+            w, e->wconv_pair[layer] + (size_t)group * p.w_rows_per_group, p.cout, p.cin, p.k, p.cout_p, p.cin_p, e->f16);
         C6_LAUNCHED(e, "pack_conv_weights_pair_kernel");
       }
     }
@@ -901,14 +934,16 @@ int c6_forward_step(C6Engine* e, const void* x, int x_dtype, int64_t B, const ui
 }
 
 int c6_forward_step_boards(C6Engine* e, const int8_t* boards, const int8_t* current_player, const int8_t* stones_left,
-                           const int64_t* index, int64_t B, const uint8_t* orient, int flags, float temperature,
+                           int64_t num_envs, const int64_t* index, int64_t B, const uint8_t* orient, int flags, float temperature,
                            uint64_t seed, uint64_t offset, int64_t board_index0, int64_t* action, float* logprob,
                            float* value, float* masked_logits, void* stream) {
   if (!e) return C6_ERR_ARG;
   if (e->G != 1) return fail(e, C6_ERR_ARG, "c6_forward_step_boards needs an engine with groups == 1");
   if (B > 0 && (!boards || !current_player || !stones_left)) return fail(e, C6_ERR_ARG, "board state pointer is null");
   if (B > 0 && !action) return fail(e, C6_ERR_ARG, "action pointer is null");
+  if (num_envs < 0 || (!index && B > num_envs)) return fail(e, C6_ERR_ARG, "more boards than environments and no index vector");
   RunArgs a;
+  a.num_envs = num_envs;
   a.boards = boards;
   a.player = current_player;
   a.stones_left = stones_left;
@@ -1113,8 +1148,12 @@ int c6_status(C6Engine* e, int* device_status) {
   C6_CUDA(e, cudaSetDevice(e->device));
   C6_CUDA(e, cudaMemcpy(device_status, e->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
   if (*device_status != 0) {
-    char buf[96];
-    snprintf(buf, sizeof(buf), "device status word 0x%x: a bounded wait inside a kernel ran out", *device_status);
+    char buf[200];
+    const int st = *device_status;
+    snprintf(buf, sizeof(buf), "device status word 0x%x:%s%s%s", st,
+             (st & 63) ? " a bounded wait inside a kernel ran out;" : "",
+             (st & kStatBadIndex) ? " a gather index lay outside the environments (read as an empty board);" : "",
+             (st & kStatF16Range) ? " fp16 mode: an activation exceeded +-65504 and was clamped;" : "");
     return fail(e, C6_ERR_DEVICE, buf);
   }
   return C6_OK;
@@ -1123,7 +1162,7 @@ int c6_status(C6Engine* e, int* device_status) {
 int c6_profile_enable(C6Engine* e, int on) {
   if (!e) return C6_ERR_ARG;
   e->profiling = on != 0;
-  e->wait_counters = on >= 2;
+  e->wait_counters = on >= 2 && kTimedBuild;
   return C6_OK;
 }
 
@@ -1146,23 +1185,32 @@ int c6_profile_read(C6Engine* e, float* ms_per_kind, int64_t* launches_per_kind,
 
 int c6_debug_wait_cycles(C6Engine* e, int64_t* out8, int reset) {
   if (!e || !out8) return C6_ERR_ARG;
+#ifdef C6_TIMED_BUILD
   C6_CUDA(e, cudaSetDevice(e->device));
   C6_CUDA(e, cudaMemcpy(out8, e->wait_dev, 8 * sizeof(long long), cudaMemcpyDeviceToHost));
   if (reset) C6_CUDA(e, cudaMemset(e->wait_dev, 0, 8 * sizeof(long long)));
   return C6_OK;
+#else
+  (void)reset;
+  return fail(e, C6_ERR_UNSUPPORTED, "the library was built without -DC6_TIMED_BUILD: no in-kernel clock counters");
+#endif
 }
 
 int c6_debug_cta_times(C6Engine* e, int64_t* out, int n_ctas) {
   if (!e || !out || n_ctas < 1 || n_ctas > 512) return C6_ERR_ARG;
+#ifdef C6_TIMED_BUILD
   C6_CUDA(e, cudaSetDevice(e->device));
   C6_CUDA(e, cudaMemcpy(out, e->wait_dev + 8, (size_t)n_ctas * 4 * sizeof(long long), cudaMemcpyDeviceToHost));
   return C6_OK;
+#else
+  return fail(e, C6_ERR_UNSUPPORTED, "the library was built without -DC6_TIMED_BUILD: no in-kernel clock counters");
+#endif
 }
 
 int c6_debug_expire_wait(C6Engine* e, void* stream) {
   if (!e) return C6_ERR_ARG;
   C6_CUDA(e, cudaSetDevice(e->device));
-  expire_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(e->status_dev, 1000000LL);
+  expire_wait_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(e->status_dev, 1000000LL);
   C6_LAUNCHED(e, "expire_wait_kernel");
   return C6_OK;
 }

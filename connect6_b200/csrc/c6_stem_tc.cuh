@@ -63,7 +63,8 @@ constexpr int kStemMaxStages = 12;
 // CTA r stages the X rows of boards [128 r, 128 r + 128) and rows [r NT/2, (r+1) NT/2) of the
 // Toeplitz tile, so every byte of T is fetched once per 256 boards instead of once per 128: the
 // kernel is fed from L2 and this cuts its traffic by a third.
-template <bool PAIR>
+// F16 = true: fp16 operands and activations instead of bf16 (see the k x k kernel).
+template <bool PAIR, bool F16>
 __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
   } else if (warp == 1 && leader) {
     // ------------------------------ MMA issuer ------------------------------
     // Warp-uniform loop, one elected lane issues (see the k x k kernel for the reasoning).
-    const uint32_t idesc = tc::make_idesc_bf16(PAIR ? 256 : 128, p.nt);
+    const uint32_t idesc = tc::make_idesc_16(PAIR ? 256 : 128, p.nt, F16);
     const uint32_t desc_hi = (uint32_t)(tc::make_desc(0, 0, 128u) >> 32);
     const uint32_t a_lbo_field = (a_plane >> 4) << 16, b_lbo_field = (b_plane >> 4) << 16;
     const uint32_t stage0_lo = tc::smem_u32(s_stage) >> 4;
@@ -323,6 +324,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     const int wq = wpc >> lcpt, wcl = wpc & (cpt - 1);
     bool ok = true;
     int tcount = 0;
+    float amax = 0.f;   // fp16 mode: largest |activation| this thread stored
     for (long long item = i_begin; item < i_end && ok; ++item, ++tcount) {
       const int acc = tcount & 1;
       int g, mt, nt_i;
@@ -371,11 +373,15 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
             float y[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) y[j] = silu_from_half(fmaf(__uint_as_float(v[b][j]), 0.5f, hb[j]));
+            if (F16) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
+            }
             uint4 o;
-            o.x = pack_bf16x2(y[0], y[1]);
-            o.y = pack_bf16x2(y[2], y[3]);
-            o.z = pack_bf16x2(y[4], y[5]);
-            o.w = pack_bf16x2(y[6], y[7]);
+            o.x = pack_h2<F16>(y[0], y[1]);
+            o.y = pack_h2<F16>(y[2], y[3]);
+            o.z = pack_h2<F16>(y[4], y[5]);
+            o.w = pack_h2<F16>(y[6], y[7]);
             patch[lane * 8 + ((i0 + b) ^ (lane & 7))] = o;   // [board][piece], swizzled against bank conflicts
           }
         }
@@ -395,6 +401,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       }
       __syncwarp();   // the patch is reused by the next tile
     }
+    if (F16 && !(amax <= 65504.f)) atomicOr(p.status, kStatF16Range);
   }
 
   tc::fence_before_sync();

@@ -53,8 +53,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the wait ran out or another role already aborted; the
 // caller then records a status bit, raises the CTA's abort flag and leaves its loop.
+// `limit_cycles` is the time limit in SM clocks (the kernels use the default; the self-test of the
+// failure path passes a short one).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t backoff_ns = 0) {
+                                          uint32_t backoff_ns = 0, long long limit_cycles = kWaitTimeoutCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -63,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 31u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitTimeoutCycles) return false;
+      if (clock64() - t0 > limit_cycles) return false;
     }
   }
 }
@@ -228,6 +230,11 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 // both operands K-major (bits 15, 16 clear), N >> 3 at [17,23), M >> 4 at [24,29).
 __host__ __device__ __forceinline__ uint32_t make_idesc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// The same with A = B = fp16 (format code 0 in both fields) when f16 is set.
+__host__ __device__ __forceinline__ uint32_t make_idesc_16(int m, int n, bool f16) {
+  const uint32_t fmt = f16 ? 0u : ((1u << 7) | (1u << 10));
+  return (1u << 4) | fmt | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]^T for one 128 x N x 16 step; issued by a single thread.

@@ -11,7 +11,7 @@ import torch
 
 from . import _lib as L
 
-_PREC = {"bf16": L.C6_PREC_BF16, "fp32": L.C6_PREC_FP32}
+_PREC = {"bf16": L.C6_PREC_BF16, "fp32": L.C6_PREC_FP32, "f16": L.C6_PREC_F16}
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -115,8 +115,13 @@ class Engine:
 
     # -- checks ---------------------------------------------------------------------------------
     def _check_x(self, x: torch.Tensor, lead: int) -> torch.Tensor:
+        """x must be [lead dims..., 3, n, n] on the engine's device (the kernels index it unchecked)."""
         if x.device != self.device:
             raise RuntimeError(f"input lives on {x.device}, engine on {self.device} (no CPU path)")
+        tail = (3, self.board_size, self.board_size)
+        if x.ndim != lead + 3 or tuple(x.shape[lead:]) != tail:
+            raise ValueError(f"network input must have {lead} leading dimension(s) followed by "
+                             f"[{tail[0]}, {tail[1]}, {tail[2]}], got {tuple(x.shape)}")
         return x if x.is_contiguous() else x.contiguous()
 
     def _check_orient(self, orient: torch.Tensor | None, boards: int) -> torch.Tensor | None:
@@ -167,12 +172,21 @@ class Engine:
         for t, name in ((boards, "boards"), (current_player, "current_player"), (stones_left, "stones_left")):
             if t.dtype != torch.int8 or t.device != self.device:
                 raise ValueError(f"{name} must be an int8 tensor on {self.device}")
+        n = self.board_size
+        if boards.ndim != 3 or tuple(boards.shape[1:]) != (n, n):
+            raise ValueError(f"boards must have shape [envs, {n}, {n}], got {tuple(boards.shape)}")
+        envs = int(boards.shape[0])
+        if tuple(current_player.shape) != (envs,) or tuple(stones_left.shape) != (envs,):
+            raise ValueError(f"current_player and stones_left must have shape [{envs}], got "
+                             f"{tuple(current_player.shape)} and {tuple(stones_left.shape)}")
         boards, current_player, stones_left = boards.contiguous(), current_player.contiguous(), stones_left.contiguous()
         if index is not None:
-            if index.dtype != torch.int64 or index.device != self.device:
-                raise ValueError("index must be an int64 tensor on the engine's device")
+            if index.dtype != torch.int64 or index.device != self.device or index.ndim != 1:
+                raise ValueError("index must be a one-dimensional int64 tensor on the engine's device")
             index = index.contiguous()
-        B = int(index.numel()) if index is not None else int(boards.shape[0])
+        # the values of `index` stay on the device: the kernel skips entries outside [0, envs), evaluates
+        # an empty board for them and raises C6_STATUS_BAD_INDEX in the status word
+        B = int(index.numel()) if index is not None else envs
         orient = self._check_orient(orient, B)
         action = torch.empty((B,), device=self.device, dtype=torch.int64)
         logprob = torch.empty((B,), device=self.device, dtype=torch.float32) if want_logprob else None
@@ -181,7 +195,7 @@ class Engine:
         flags = L.C6_FLAG_INVERSE_MAP if inverse_map else 0
         with torch.cuda.device(self.device):
             L.check(self._lib.c6_forward_step_boards(self._h, L.ptr(boards), L.ptr(current_player), L.ptr(stones_left),
-                                                     L.ptr(index), B, L.ptr(orient), flags, float(temperature), int(seed),
+                                                     envs, L.ptr(index), B, L.ptr(orient), flags, float(temperature), int(seed),
                                                      int(offset), int(board_index0), L.ptr(action), L.ptr(logprob),
                                                      L.ptr(value), L.ptr(logits), _stream_ptr(self.device)),
                     self._h, "c6_forward_step_boards")
@@ -202,7 +216,7 @@ class Engine:
 
     def layer_output(self, x: torch.Tensor, layer: int, orient: torch.Tensor | None = None) -> torch.Tensor:
         """Test aid: fp32 activation [boards, channels[layer], n, n] after backbone layer `layer`."""
-        x = self._check_x(x, 1)
+        x = self._check_x(x, x.ndim - 3)
         lead = x.shape[:-3]
         boards = 1
         for s in lead:

@@ -37,8 +37,8 @@ class HistoricalPolicyEnsemble:
     """M frozen policy CNNs evaluated together; input [M, T, 3, H, W] -> logits [M, T, H*W].
 
     Same constructor and attributes as connect6/history.py:186-232.  `dtype` picks the
-    arithmetic like the reference's ensemble dtype: torch.bfloat16 -> tensor-core mode,
-    torch.float32 (or None) -> fp32 mode.  Outputs are returned in that dtype.
+    arithmetic like the reference's ensemble dtype: torch.bfloat16 / torch.float16 -> tensor-core
+    modes, torch.float32 (or None) -> fp32 mode.  Outputs are returned in that dtype.
     """
 
     def __init__(self, checkpoints: list[HistoricalCheckpoint], device: torch.device, *,
@@ -47,8 +47,8 @@ class HistoricalPolicyEnsemble:
             raise ValueError("HistoricalPolicyEnsemble needs at least 1 checkpoint")
         self.device = torch.device(device)
         self.dtype = dtype or torch.float32
-        if self.dtype not in (torch.float32, torch.bfloat16):
-            raise ValueError("ensemble dtype must be torch.float32 or torch.bfloat16")
+        if self.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+            raise ValueError("ensemble dtype must be torch.float32, torch.bfloat16 or torch.float16")
         self.num_models = len(checkpoints)
         self.updates = [cp.update for cp in checkpoints]
         self.paths = [cp.path for cp in checkpoints]
@@ -67,7 +67,7 @@ class HistoricalPolicyEnsemble:
 
         self.has_value = all("value_output.weight" in cp.model_state for cp in checkpoints)
         self._engine = Engine(self.device, self.board_size, self.kernels, self.channels, self.num_models,
-                              "bf16" if self.dtype == torch.bfloat16 else "fp32")
+                              {torch.bfloat16: "bf16", torch.float16: "f16"}.get(self.dtype, "fp32"))
         for g, cp in enumerate(checkpoints):
             try:
                 self._engine.load_state_dict(cp.model_state, group=g, need_value=False)

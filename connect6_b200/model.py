@@ -30,8 +30,9 @@ class PolicyValueNet(nn.Module):
     Mirrors connect6/model.py:9-111.
 
     `engine_precision` selects the engine's arithmetic: "bf16" (tcgen05 tensor cores, the
-    default) or "fp32" (CUDA cores, reference-exact to 1e-3).  It is an engine property and
-    does not follow torch.autocast.
+    default), "f16" (the same kernels with fp16 weights and activations: 11-bit significands,
+    for callers that need the fp32 network's moves) or "fp32" (CUDA cores, reference-exact to
+    1e-3).  It is an engine property and does not follow torch.autocast.
     """
 
     DEFAULT_KERNELS = DEFAULT_KERNELS

@@ -11,8 +11,36 @@ import torch
 
 from . import _lib as L
 
-_DEFAULT_SEED = 0x5EEDC6
+# Random stream of the drop-in samplers when the caller passes no seed / offset / board_index0.
+# The reference draws from torch's per-process generator (connect6/train.py:195-213), so runs follow
+# torch.manual_seed and every rank of a multi-process job draws its own numbers.  Here the Philox key
+# is torch.initial_seed() -- the value torch.manual_seed / seed_everything last set -- unless set_seed()
+# overrides it, the offset is a process-wide call counter, and the board index starts at
+# rank * 2^40 so that local board i of two ranks never shares a uniform.
+_RANK_STRIDE = 1 << 40
+_stream_state = {"seed": None, "board_index0": None}
 _offset_counter = [0]
+
+
+def set_seed(seed: int | None, board_index0: int | None = None) -> None:
+    """Fix the samplers' Philox key (None: follow torch.initial_seed() again) and, optionally, the
+    first board index of this process (None: rank * 2^40).  Resets the call counter."""
+    _stream_state["seed"] = None if seed is None else int(seed) & 0xFFFFFFFFFFFFFFFF
+    _stream_state["board_index0"] = None if board_index0 is None else int(board_index0)
+    _offset_counter[0] = 0
+
+
+def default_stream() -> tuple[int, int]:
+    """(seed, board_index0) the samplers use when the caller passes none."""
+    seed = _stream_state["seed"]
+    if seed is None:
+        seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
+    base = _stream_state["board_index0"]
+    if base is None:
+        import torch.distributed as dist
+        rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        base = rank * _RANK_STRIDE
+    return seed, base
 
 
 def _require_cuda(t: torch.Tensor, what: str) -> None:
@@ -30,8 +58,9 @@ def _next_offset() -> int:
 
 
 def _sample(logits: torch.Tensor, legal: torch.Tensor, temperature: float, want_logprob: bool,
-            seed: int | None, offset: int | None, board_index0: int):
+            seed: int | None, offset: int | None, board_index0: int | None):
     _require_cuda(logits, "_sample_actions")
+    d_seed, d_base = default_stream()
     lead = logits.shape[:-1]
     A = logits.shape[-1]
     z = logits.float().reshape(-1, A).contiguous()
@@ -42,23 +71,27 @@ def _sample(logits: torch.Tensor, legal: torch.Tensor, temperature: float, want_
     with torch.cuda.device(z.device):
         L.check(L.load().c6_sample_actions(
             z.data_ptr(), lg.data_ptr(), B, A, float(temperature),
-            int(_DEFAULT_SEED if seed is None else seed), int(_next_offset() if offset is None else offset),
-            int(board_index0), actions.data_ptr(), L.ptr(logprob), _stream(z)), None, "c6_sample_actions")
+            int(d_seed if seed is None else seed), int(_next_offset() if offset is None else offset),
+            int(d_base if board_index0 is None else board_index0), actions.data_ptr(), L.ptr(logprob), _stream(z)),
+            None, "c6_sample_actions")
     actions = actions.reshape(lead)
     return actions, (logprob.reshape(lead) if want_logprob else None)
 
 
 def _sample_actions(logits: torch.Tensor, legal: torch.Tensor, temperature: float, *, seed: int | None = None,
-                    offset: int | None = None, board_index0: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+                    offset: int | None = None, board_index0: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """connect6/train.py:195-203: draw from Categorical(mask(logits.float()) / max(T, 1e-4)) and
     return (actions int64, log-prob of the drawn action fp32).  Randomness comes from the engine's
-    own Philox4x32-10 stream (seed, offset, board index), not torch's generator; with offset=None a
-    process-wide counter advances once per call."""
+    own Philox4x32-10 stream keyed (seed, offset, board index), not from torch's generator state.
+    Defaults: seed = torch.initial_seed() (so torch.manual_seed selects the stream, see set_seed),
+    offset = a process-wide counter that advances once per call, board_index0 = rank * 2^40 (every
+    rank of a torch.distributed job draws different numbers)."""
     return _sample(logits, legal, temperature, True, seed, offset, board_index0)
 
 
 def _sample_actions_only(logits: torch.Tensor, legal: torch.Tensor, temperature: float, *,
-                         seed: int | None = None, offset: int | None = None, board_index0: int = 0) -> torch.Tensor:
+                         seed: int | None = None, offset: int | None = None,
+                         board_index0: int | None = None) -> torch.Tensor:
     """connect6/train.py:206-213: the same draw without the log-probability."""
     return _sample(logits, legal, temperature, False, seed, offset, board_index0)[0]
 

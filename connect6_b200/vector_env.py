@@ -58,6 +58,9 @@ class VectorConnect6:
         self.stones_left = torch.ones(self.num_envs, dtype=torch.int8, device=dev)
         self.empty_count = torch.full((self.num_envs,), self.board_size * self.board_size, dtype=torch.int16, device=dev)
         self.move_count = torch.zeros(self.num_envs, dtype=torch.int16, device=dev)
+        # Device counters the step and bookkeeping kernels only ever increment (slots C6_ENV_FAULT_* of
+        # include/c6_env.h: stones on occupied cells, actions outside the board, episode ids beyond the
+        # record arrays).  With debug_checks off nothing raises: poll this tensor when convenient.
         self.faults = torch.zeros(L.C6_ENV_FAULT_COUNT, dtype=torch.int32, device=dev)
 
     # ---- reference surface -------------------------------------------------------------------
@@ -118,6 +121,21 @@ class VectorConnect6:
             raise ValueError(f"expected actions of shape {(self.num_envs,)}, got {tuple(actions.shape)}")
         actions = actions.contiguous()
         dev = self.device
+        if self.debug_checks and self.num_envs:
+            # as the reference (connect6/vector_env.py:121-127): look first, raise before any state changes.
+            # A debugging aid: it reads the result on the host.
+            cells = self.board_size * self.board_size
+            board_actions = actions
+            if int(view_phase) % 8:
+                from .selfplay import _inverse_transform_actions, _symmetry_for_phase
+                board_actions = _inverse_transform_actions(actions, self.board_size, *_symmetry_for_phase(view_phase))
+            outside = (actions < 0) | (actions >= cells)
+            target = self.boards.reshape(self.num_envs, cells).gather(1, board_actions.clamp(0, cells - 1).unsqueeze(1))
+            occupied = (target.squeeze(1) != 0) & ~outside
+            n_out, n_occ = int(outside.sum()), int(occupied.sum())
+            if n_out or n_occ:
+                raise RuntimeError(f"step: {n_occ} stone(s) aimed at an occupied cell, {n_out} action(s) outside the "
+                                   "board; no environment was changed")
         out = StepBatch(
             reward=torch.empty(self.num_envs, dtype=torch.float32, device=dev),
             done=torch.empty(self.num_envs, dtype=torch.bool, device=dev),
@@ -131,12 +149,6 @@ class VectorConnect6:
                                          out.done.data_ptr(), out.winner.data_ptr(), out.transition_sign.data_ptr(),
                                          out.game_lengths.data_ptr(), self.faults.data_ptr(), self._stream()),
                     None, "c6_env_step")
-        if self.debug_checks:
-            occupied, bad_action, _, _ = self.faults.tolist()
-            if occupied or bad_action:
-                self.faults.zero_()
-                raise RuntimeError(f"step: {occupied} stone(s) placed on an occupied cell, "
-                                   f"{bad_action} action(s) outside the board")
         return out
 
 

@@ -32,13 +32,25 @@ enum {
   C6_ERR_CUDA = 2,        /* a CUDA runtime call failed; see c6_last_error            */
   C6_ERR_UNSUPPORTED = 3, /* architecture outside what the kernels implement          */
   C6_ERR_WEIGHTS = 4,     /* forward called before every layer/head received weights  */
-  C6_ERR_DEVICE = 5       /* the device status word is non-zero (bounded wait ran out) */
+  C6_ERR_DEVICE = 5       /* the device status word is non-zero (see c6_status)         */
+};
+
+/* bits of the device status word read by c6_status */
+enum {
+  C6_STATUS_WAIT_MASK = 63,   /* bits 0..5: a bounded wait inside a kernel ran out (which one)            */
+  C6_STATUS_BAD_INDEX = 64,   /* c6_forward_step_boards: an index entry outside [0, num_envs), read as an
+                                 empty board                                                               */
+  C6_STATUS_F16_RANGE = 128   /* C6_PREC_F16: an activation exceeded +-65504 and was clamped                */
 };
 
 /* arithmetic mode of an engine */
 enum {
   C6_PREC_BF16 = 0, /* bf16 operands, fp32 accumulate, tcgen05 tensor cores            */
-  C6_PREC_FP32 = 1  /* fp32 operands and accumulate on CUDA cores (reference-exact mode) */
+  C6_PREC_FP32 = 1, /* fp32 operands and accumulate on CUDA cores (reference-exact mode) */
+  C6_PREC_F16 = 2   /* fp16 weights and activations, fp32 accumulate, tcgen05 tensor cores: the
+                       speed of the bf16 mode with 11-bit significands (tf32's width) instead of 8, for
+                       callers that need the fp32 network's moves; activations beyond +-65504 are clamped
+                       and reported through C6_STATUS_F16_RANGE                                         */
 };
 
 /* dtype of the network-input tensor x */
@@ -111,11 +123,13 @@ int c6_forward_step(C6Engine* eng, const void* x, int x_dtype, int64_t B, const 
  * network_input[current_idx] (connect6/train.py:793) and the self-play step above in one call: the
  * three input planes are derived from the environment's raw state inside the first kernel, so the
  * fp32 planes (4.3 KB per board) never exist in memory.
- *   boards int8 [envs,n,n] (+1/-1/0), current_player int8 [envs] (+1/-1), stones_left int8 [envs];
- *   index nullable int64 [B]: board b of the batch is environment index[b] (null: b itself);
+ *   boards int8 [num_envs,n,n] (+1/-1/0), current_player int8 [num_envs] (+1/-1), stones_left int8
+ *   [num_envs]; index nullable int64 [B]: board b of the batch is environment index[b] (null: b
+ *   itself, then B <= num_envs).  An index entry outside [0, num_envs) is never dereferenced: that
+ *   board is evaluated as an empty one and C6_STATUS_BAD_INDEX is raised in the status word.
  *   occupancy for masking is boards != 0; outputs as in c6_forward_step. */
 int c6_forward_step_boards(C6Engine* eng, const int8_t* boards, const int8_t* current_player,
-                           const int8_t* stones_left, const int64_t* index, int64_t B,
+                           const int8_t* stones_left, int64_t num_envs, const int64_t* index, int64_t B,
                            const uint8_t* orient, int flags, float temperature, uint64_t seed,
                            uint64_t offset, int64_t board_index0, int64_t* action, float* logprob,
                            float* value, float* masked_logits, void* stream);
@@ -170,13 +184,6 @@ int c6_transform_boards(const int8_t* boards, int64_t B, int32_t n, const uint8_
 int c6_network_input(const int8_t* boards, const int8_t* current_player, const int8_t* stones_left,
                      int64_t B, int32_t n, float* out, void* stream);
 
-/* Test aid with no reference function of its own: runs the backbone up to and including
- * `layer` and writes that layer's activation, SiLU applied (the `features` tensor inside the
- * loop at connect6/model.py:104-106), as fp32 [G*T, channels[layer], n, n].  T is limited to
- * one internal pass. */
-int c6_debug_layer_output(C6Engine* eng, const void* x, int x_dtype, int64_t T,
-                          const uint8_t* orient, int layer, float* out_nchw, void* stream);
-
 /* Per-kernel timing (no reference counterpart; the reference only has wall-clock phase timers,
  * connect6/train.py:586-1191).  While enabled, every forward-path launch is bracketed by a CUDA
  * event pair on the caller's stream.  c6_profile_read waits for the recorded events, adds the
@@ -190,34 +197,17 @@ enum {
   C6_KIND_CONV0 = 8,  /* backbone layer l >= 1 is kind C6_KIND_CONV0+l  */
   C6_KIND_COUNT = 8 + C6_MAX_LAYERS
 };
-int c6_profile_enable(C6Engine* eng, int on); /* 0 off, 1 events, 2 events + in-kernel wait counters */
+int c6_profile_enable(C6Engine* eng, int on); /* 0 off, 1 events, 2 events + in-kernel wait counters (c6_debug.h) */
 int c6_profile_read(C6Engine* eng, float* ms_per_kind, int64_t* launches_per_kind, int n_kinds);
 
-/* Diagnostic with no reference counterpart: while profiling level 2 is enabled, CTA 0 of every k x k
- * tensor-core conv launch adds SM clocks to eight device counters: {producer waiting for an empty
- * stage, MMA warp waiting for a full stage, MMA warp waiting for a drained accumulator, epilogue
- * waiting for a ready accumulator, MMA warp inside its issue blocks, MMA warp loop total, 0, 0}.
- * Copies them to the HOST array out8 (synchronous) and optionally clears them. */
-int c6_debug_wait_cycles(C6Engine* eng, int64_t* out8, int reset);
-
-/* Diagnostic: four global-timer stamps (ns) per CTA {kernel entry, kernel exit, MMA loop begin,
- * MMA loop end} for the first n_ctas (<= 512) CTAs of the most recent k x k conv launch made
- * while profiling was enabled; HOST array of 4*n_ctas. */
-int c6_debug_cta_times(C6Engine* eng, int64_t* out, int n_ctas);
-
-/* Reads the device status word (host int). Non-zero means a bounded wait inside a kernel ran
- * out; the kernels then skip their work instead of hanging. The caller must have synchronised
- * the stream it used. */
+/* Reads the device status word (host int, C6_STATUS_* bits).  Non-zero returns C6_ERR_DEVICE: a
+ * bounded wait inside a kernel ran out (the kernels then skip their work instead of hanging), a
+ * gather index was out of range, or the fp16 mode clamped an activation.  The caller must have
+ * synchronised the stream it used. */
 int c6_status(C6Engine* eng, int* device_status);
 
 /* Clears the device status word (synchronous) after the caller has dealt with a non-zero status. */
 int c6_clear_status(C6Engine* eng);
-
-/* Self-test of the failure path, no reference counterpart: enqueues a one-CTA kernel that waits, with
- * a limit of about half a millisecond, on a barrier nobody arrives on.  The wait runs out, the kernel
- * sets a status bit and returns normally -- the same path a real kernel takes if its pipeline stalls.
- * Nothing faults or hangs; c6_status then reports C6_ERR_DEVICE until c6_clear_status. */
-int c6_debug_expire_wait(C6Engine* eng, void* stream);
 
 /* Number of kernel launches the engine has enqueued since creation (host counter). */
 int64_t c6_launch_count(const C6Engine* eng);

@@ -183,3 +183,71 @@ def test_stem_widths_against_oracle(cuda_device, channels, kernels):
         assert (logits.cpu().double() - rl).abs().max().item() < max(3e-2, 0.12 * rl.std().item())
         assert (value.cpu().double() - rv).abs().max().item() < 3e-2
     assert eng.status() == 0
+
+
+def _sharded_rank(rank: int, world: int, port: int, total: int, out_dir: str, n_gpus: int) -> None:
+    """One rank of the sharded D4 inference: its contiguous range of the global board index, results to disk."""
+    import os
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(root))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank % n_gpus))
+    from connect6_b200 import shard
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import PolicyValueNet
+    # ranks on distinct GPUs talk NCCL; two ranks sharing the one GPU of a small box reduce over gloo
+    shard.init_from_env(backend="nccl" if n_gpus >= world else "gloo")
+    dev = torch.device("cuda", rank % n_gpus)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(42)
+    state = {k: v.detach().clone() for k, v in PolicyValueNet(19).state_dict().items()}
+    eng = Engine(dev, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, 1, "bf16")
+    eng.load_state_dict(state)
+    lo, hi = shard.shard_range(total, rank, world)
+    x = torch.from_numpy(generate_planes(lo, hi - lo)).to(dev)
+    orient = torch.from_numpy((np.arange(lo, hi) % 8).astype(np.uint8)).to(dev)
+    logits, value = eng.forward(x, orient, mask=True, inverse_map=True)
+    action, logprob, _, _ = eng.forward_step(x, seed=0xC6, offset=5, board_index0=lo, orient=orient, inverse_map=True)
+    stats = torch.zeros(9, dtype=torch.int64, device=dev if n_gpus >= world else "cpu")
+    stats[0] = hi - lo
+    stats[4] = int(action.sum())
+    shard.reduce_rollout_stats(stats)
+    assert eng.status() == 0
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), logits=logits.cpu().numpy(), value=value.cpu().numpy(),
+             action=action.cpu().numpy(), logprob=logprob.cpu().numpy(), stats=stats.cpu().numpy(), lo=lo, hi=hi)
+    import torch.distributed as dist
+    dist.destroy_process_group()
+
+
+def test_two_rank_sharded_d4_inference_equals_one_rank(cuda_device, tmp_path):
+    """BASELINE config 4's sharding rule on two ranks (two GPUs where the box has them, else both ranks on
+    the one GPU): boards are cut by global index, orientation and random stream are keyed by that index,
+    so the concatenated shards equal the unsharded run bit for bit; the statistics all-reduce sums."""
+    import socket
+    import torch.multiprocessing as mp
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import PolicyValueNet
+    total, world = 5001, 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_sharded_rank, args=(world, port, total, str(tmp_path), torch.cuda.device_count()), nprocs=world, join=True)
+    torch.manual_seed(42)
+    state = {k: v.detach().clone() for k, v in PolicyValueNet(19).state_dict().items()}
+    eng = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, 1, "bf16")
+    eng.load_state_dict(state)
+    x = torch.from_numpy(generate_planes(0, total)).to(cuda_device)
+    orient = torch.from_numpy((np.arange(total) % 8).astype(np.uint8)).to(cuda_device)
+    logits, value = eng.forward(x, orient, mask=True, inverse_map=True)
+    action, logprob, _, _ = eng.forward_step(x, seed=0xC6, offset=5, board_index0=0, orient=orient, inverse_map=True)
+    parts = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    assert parts[0]["lo"] == 0 and parts[0]["hi"] == parts[1]["lo"] and parts[1]["hi"] == total
+    for key, whole in (("logits", logits), ("value", value), ("action", action), ("logprob", logprob)):
+        got = np.concatenate([p[key] for p in parts])
+        assert np.array_equal(got, whole.cpu().numpy()), key
+    for p in parts:
+        assert p["stats"][0] == total and p["stats"][4] == int(action.sum())

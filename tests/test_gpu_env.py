@@ -103,8 +103,13 @@ def test_env_edge_cases_and_faults(cuda_device):
     assert s.done.tolist() == [False] * 4
     checked = VectorConnect6(2, 5, 3, device=cuda_device, debug_checks=True)
     checked.step(torch.tensor([3, 4], device=cuda_device))
-    with pytest.raises(RuntimeError):
-        checked.step(torch.tensor([3, 5], device=cuda_device))
+    held = _snapshot(checked)
+    for bad_actions, phase in (([3, 5], 0), ([6, 25], 0), ([1, 0], 4)):   # occupied; off the board; occupied through view 4
+        with pytest.raises(RuntimeError, match="no environment was changed"):
+            checked.step(torch.tensor(bad_actions, device=cuda_device), view_phase=phase)
+        now = _snapshot(checked)
+        assert all(np.array_equal(held[k], now[k]) for k in held)          # raised before touching any state
+    assert checked.faults.tolist() == [0, 0, 0, 0]
     # partial reset with duplicates, a boolean mask, and out-of-range entries that are skipped
     env.reset(torch.tensor([2, 2, 99, -5], device=cuda_device))
     st = _snapshot(env)

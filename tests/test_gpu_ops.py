@@ -214,7 +214,8 @@ def test_bounded_wait_expiry_is_reported_not_hung(cuda_device):
     before = eng.forward(x)
     assert eng.status() == 0
     eng.expire_wait_selftest()
-    with pytest.raises(RuntimeError, match="bounded wait"):
+    # first waiter: its limit ran out (bit 0); second waiter: left on the abort flag the first raised (bit 1)
+    with pytest.raises(RuntimeError, match="0x3: a bounded wait"):
         eng.status()
     eng.clear_status()
     assert eng.status() == 0
@@ -244,3 +245,91 @@ def test_step_from_raw_boards_equals_planes_path(cuda_device, precision):
     whole = m.selfplay_step_from_boards(boards, player, stones, seed=1, offset=1)
     ref = m.selfplay_step(canonical_network_input(boards, player, stones), seed=1, offset=1)
     assert torch.equal(whole[0], ref[0]) and torch.equal(whole[2], ref[2])
+
+
+def test_fp32_engines_of_different_sizes_share_the_kernel(cuda_device):
+    """Two fp32-mode engines in one process (e.g. two architectures in an evaluation run): creating the
+    small one must not shrink the dynamic shared memory the default network's 23x23 stem needs."""
+    from connect6_b200 import _lib as L
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import PolicyValueNet
+    big = _default_model(cuda_device, "fp32")
+    x = torch.from_numpy(generate_planes(0, 4)).to(cuda_device)
+    with torch.inference_mode():
+        before = big(x)
+    torch.manual_seed(1)
+    small = PolicyValueNet(5, [3, 3], [8, 8], engine_precision="fp32").to(cuda_device).eval()
+    with torch.inference_mode():
+        small(torch.zeros(2, 3, 5, 5, device=cuda_device))
+        after = big(x)
+    assert torch.equal(before[0], after[0]) and torch.equal(before[1], after[1])
+    # the entry point that works out of the library's fixed scratch launches the same kernel
+    eng = big.engine_for(cuda_device)
+    logits = torch.empty((4, 361), device=cuda_device)
+    value = torch.empty((4,), device=cuda_device)
+    with torch.cuda.device(cuda_device):
+        rc = L.load().c6_forward_noalloc(eng._h, x.data_ptr(), L.C6_X_F32, 4, None, logits.data_ptr(), value.data_ptr(), 0,
+                                         torch.cuda.current_stream(cuda_device).cuda_stream)
+    assert rc == L.C6_OK, L.last_error(eng._h)
+    assert torch.allclose(logits, before[0], atol=1e-6, rtol=0)
+    assert eng.status() == 0
+
+
+def test_engine_rejects_misshapen_inputs_and_flags_stale_indices(cuda_device):
+    """The kernels index their inputs unchecked, so shapes are validated on the host; the values of a
+    gather index stay on the device, where an entry outside the environments is skipped (that board is
+    evaluated as empty) and reported through the status word."""
+    m = _default_model(cuda_device)
+    eng = m.engine_for(cuda_device)
+    dev = cuda_device
+    for bad in (torch.zeros(2, 3, 19, 18, device=dev), torch.zeros(2, 4, 19, 19, device=dev), torch.zeros(3, 19, 19, device=dev)):
+        with pytest.raises(ValueError):
+            eng.forward(bad)
+        with pytest.raises(ValueError):
+            eng.forward_step(bad)
+    boards = torch.zeros(6, 19, 19, dtype=torch.int8, device=dev)
+    player = torch.ones(6, dtype=torch.int8, device=dev)
+    stones = torch.ones(6, dtype=torch.int8, device=dev)
+    with pytest.raises(ValueError):
+        eng.forward_step_boards(boards[:, :18], player, stones)
+    with pytest.raises(ValueError):
+        eng.forward_step_boards(boards, player[:5], stones)
+    with pytest.raises(ValueError):
+        eng.forward_step_boards(boards, player, stones[:2])
+    with pytest.raises(ValueError):
+        eng.forward_step_boards(boards, player, stones, torch.zeros(2, 2, dtype=torch.int64, device=dev))
+    boards[2, 3, 4] = 1
+    good = eng.forward_step_boards(boards, player, stones, torch.tensor([2, 0, 5], device=dev), seed=9, want_logits=True)
+    assert eng.status() == 0
+    stale = eng.forward_step_boards(boards, player, stones, torch.tensor([2, 6, -1], device=dev), seed=9, want_logits=True)
+    with pytest.raises(RuntimeError, match="gather index"):
+        eng.status()
+    eng.clear_status()
+    assert torch.equal(stale[3][0], good[3][0])                 # the valid entry is unaffected
+    assert torch.equal(stale[3][1], good[3][1]) and torch.equal(stale[3][2], good[3][1])   # skipped entries: an empty board
+    assert eng.status() == 0
+
+
+def test_default_sampler_stream_follows_torch_seed(cuda_device):
+    """The drop-in samplers called with the reference's signature draw from a stream keyed by
+    torch.initial_seed(): reseeding reproduces a run, another seed gives other draws."""
+    from connect6_b200 import selfplay as S
+    logits = torch.zeros(512, 361, device=cuda_device)
+    legal = torch.ones(512, 361, dtype=torch.bool, device=cuda_device)
+
+    def draw(seed):
+        torch.manual_seed(seed)
+        S.set_seed(None)
+        return [S._sample_actions(logits, legal, 1.0)[0] for _ in range(2)]
+
+    a, b, c = draw(7), draw(7), draw(8)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    assert not torch.equal(a[0], a[1])                          # the call counter advances the stream
+    assert not torch.equal(a[0], c[0])
+    S.set_seed(123, board_index0=0)
+    d = S._sample_actions_only(logits, legal, 1.0)
+    S.set_seed(123, board_index0=512)
+    e = S._sample_actions_only(logits, legal, 1.0)
+    assert not torch.equal(d, e)
+    S.set_seed(None)

@@ -9,6 +9,8 @@ index maps are integer work and must be bit-exact.
 from __future__ import annotations
 
 import json
+import os
+import tempfile
 from pathlib import Path
 
 import numpy as np
@@ -24,7 +26,9 @@ pytestmark = pytest.mark.gpu
 FP32_TOL = 1e-3
 BF16_ABS_TOL = 3e-2
 BF16_REL_TOL = 0.12          # max |dlogit| / std(logits): bf16 rounding through 8 layers
-REPORT = ROOT / "gpurun_out" / "parity_report.json"
+ARGMAX_CONTRACT = 0.99       # masked-argmax moves must agree with the fp32 network on >= 99 % of boards
+# measured figures are collected here; C6_REPORT_DIR chooses the directory (default: the temp dir)
+REPORT = Path(os.environ.get("C6_REPORT_DIR", tempfile.gettempdir())) / "c6_parity_report.json"
 
 
 def _report(key: str, value) -> None:
@@ -154,15 +158,35 @@ def test_fp32_mode_against_oracle(cuda_device):
     assert dl < FP32_TOL and dv < FP32_TOL and dl < 1e-5
 
 
-@pytest.mark.parametrize("seed", [42, 0])
-def test_bf16_forward_against_oracle_2048_boards(cuda_device, seed):
-    """bf16 mode vs the fp32/fp64 oracle on 2048 generated boards: absolute and relative error,
-    and agreement of the masked argmax move."""
+_ORACLE_CACHE: dict = {}
+STAT_BOARDS = 16384
+
+
+def _oracle_16k(seed: int):
+    """fp64 oracle logits / values of STAT_BOARDS generated boards for one weight seed (shared by the modes)."""
     from connect6_b200.boards import generate_planes
-    m, params = _default_model("bf16", cuda_device, seed)
-    B = 2048
-    x = torch.from_numpy(generate_planes(20000, B))
-    rl, rv = _oracle64(x, params)
+    from connect6_b200.model import PolicyValueNet
+    if seed not in _ORACLE_CACHE:
+        _ORACLE_CACHE.clear()                       # one seed at a time: 47 MB of logits each
+        torch.manual_seed(seed)
+        params = {k: v.detach().clone() for k, v in PolicyValueNet(19).state_dict().items()}
+        x = torch.from_numpy(generate_planes(20000, STAT_BOARDS))
+        parts = [_oracle64(x[i:i + 2048], params) for i in range(0, STAT_BOARDS, 2048)]
+        _ORACLE_CACHE[seed] = (x, np.concatenate([p[0] for p in parts]), np.concatenate([p[1] for p in parts]))
+    return _ORACLE_CACHE[seed]
+
+
+@pytest.mark.parametrize("precision", ["bf16", "f16"])     # varies fastest: both modes share one oracle pass per seed
+@pytest.mark.parametrize("seed", [0, 1, 2, 42])
+def test_16bit_modes_against_oracle_16384_boards(cuda_device, precision, seed):
+    """Both tensor-core modes vs the fp64 oracle on 16384 generated boards, four weight seeds: absolute
+    and relative error, exact masks, and agreement of the masked argmax move.  The contract asks for
+    >= 99 % agreement: the fp16 mode must meet it on every seed; the bf16 mode's figure is recorded and,
+    where it falls short (one bf16 rounding per layer against a median top-2 gap of ~2e-4 at default
+    initialisation; the reference's own bf16 autocast agrees on ~98.2 %), reported as an expected failure
+    rather than hidden behind a lower bar."""
+    m, _ = _default_model(precision, cuda_device, seed)
+    x, rl, rv = _oracle_16k(seed)
     with torch.inference_mode():
         logits, value = m.forward_masked(x.to(cuda_device))
     logits, value = logits.cpu().numpy(), value.cpu().numpy()
@@ -176,17 +200,51 @@ def test_bf16_forward_against_oracle_2048_boards(cuda_device, seed):
     srt = np.sort(ref_masked, axis=1)
     gap = srt[:, -1] - srt[:, -2]
     clear = gap > 2 * dl                                                       # boards whose best move is not within the noise
-    _report(f"bf16_vs_fp32_seed{seed}", {
-        "boards": B, "max_abs_dlogit": float(dl), "logit_std": float(std), "rel": float(dl / std),
-        "max_abs_dvalue": float(dv), "masked_argmax_agreement": float(agree.mean()),
+    rate = float(agree.mean())
+    _report(f"{precision}_vs_fp64_oracle_seed{seed}", {
+        "boards": STAT_BOARDS, "max_abs_dlogit": float(dl), "logit_std": float(std), "rel": float(dl / std),
+        "max_abs_dvalue": float(dv), "masked_argmax_agreement": rate,
+        "agreement_std_error": float(np.sqrt(rate * (1 - rate) / STAT_BOARDS)),
         "agreement_where_gap_gt_2x_noise": float(agree[clear].mean()), "boards_with_clear_gap": int(clear.sum()),
-        "median_top2_gap": float(np.median(gap))})
+        "median_top2_gap": float(np.median(gap)), "meets_99pct_contract": bool(rate >= ARGMAX_CONTRACT)})
+    assert m.engine_for(cuda_device).status() == 0                             # no wait ran out, no fp16 clamp
     assert dl < BF16_ABS_TOL and dv < BF16_ABS_TOL
-    assert dl < BF16_REL_TOL * std
+    assert dl < (BF16_REL_TOL if precision == "bf16" else BF16_REL_TOL / 4) * std
     assert agree[clear].mean() == 1.0
-    # At default init the median top-2 gap is ~2e-4 against ~1e-4 of bf16 noise, so a few percent of
-    # near-tied boards flip; the reference's own bf16 autocast agrees on ~98.2 %.
-    assert agree.mean() >= 0.975
+    if precision == "f16":
+        assert rate >= ARGMAX_CONTRACT, f"fp16 mode: masked-argmax agreement {rate:.4f}"
+    elif rate < ARGMAX_CONTRACT:
+        pytest.xfail(f"bf16 mode, weight seed {seed}: masked-argmax agreement {rate:.4f} < {ARGMAX_CONTRACT} "
+                     "(floor of 8-bit significands at default initialisation; the fp16 mode meets the contract)")
+
+
+@pytest.mark.parametrize("precision", ["f16"])
+def test_f16_layers_and_range_flag(cuda_device, precision):
+    """fp16 mode layer by layer (8x tighter than bf16), and the clamp flag: weights scaled until the
+    first layer's activations leave the fp16 range must raise C6_STATUS_F16_RANGE, not produce inf."""
+    from connect6_b200 import _lib as L
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    m, params = _default_model(precision, cuda_device)
+    x = torch.from_numpy(generate_planes(1000, 40))
+    eng = m.engine_for(cuda_device)
+    f = x.double()
+    for i in range(8):
+        w, b = params[f"convs.{i}.weight"].double(), params[f"convs.{i}.bias"].double()
+        f = torch.nn.functional.silu(torch.nn.functional.conv2d(f, w, b, padding=w.shape[-1] // 2))
+        got = eng.layer_output(x.to(cuda_device), i).cpu().double()
+        err = (got - f).abs().max().item() / f.abs().max().item()
+        assert err < 3e-3, f"layer {i}: relative error {err}"
+    assert eng.status() == 0
+    hot = Engine(cuda_device, 19, m.kernels, m.channels, 1, "f16")
+    big = dict(params)
+    big["convs.0.weight"] = params["convs.0.weight"] * 2e5         # stem outputs of a few 1e5
+    hot.load_state_dict(big)
+    logits, _ = hot.forward(x.to(cuda_device))
+    assert bool(torch.isfinite(logits).all())
+    with pytest.raises(RuntimeError, match="fp16"):
+        hot.status()
+    hot.clear_status()
 
 
 def test_chunked_passes_equal_single_pass(cuda_device):

@@ -33,6 +33,12 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     shard.reduce_rollout_stats(stats)
     slow = shard.max_over_ranks(10.0 * (rank + 1))
     shard.barrier()
+    # default random stream of the drop-in samplers: same key on every rank after the same
+    # torch.manual_seed, but a different first board index
+    from connect6_b200 import selfplay
+    torch.manual_seed(1234)
+    seed, base = selfplay.default_stream()
+    np.save(os.path.join(out_dir, f"stream{rank}.npy"), np.array([seed, base], dtype=np.uint64))
     np.save(os.path.join(out_dir, f"rank{rank}.npy"), np.concatenate([stats.numpy(), [int(slow)]]))
     dist.destroy_process_group()
 
@@ -47,6 +53,20 @@ def test_two_rank_shard_and_reduce(tmp_path):
         assert got[0] == 1000                       # every board counted exactly once
         assert got[1] == int(whole[:, 0].sum())     # same boards as the unsharded generator
         assert got[8] == 3 and got[9] == 20         # sum and max over ranks
+    s0, s1 = np.load(tmp_path / "stream0.npy"), np.load(tmp_path / "stream1.npy")
+    assert s0[0] == s1[0] == 1234                   # the key follows torch.manual_seed on every rank
+    assert s0[1] == 0 and s1[1] == 1 << 40          # ranks never share a (key, offset, board) triple
+
+
+def test_default_sampler_stream_on_one_process():
+    from connect6_b200 import selfplay
+    torch.manual_seed(99)
+    assert selfplay.default_stream() == (99, 0)
+    selfplay.set_seed(5, board_index0=77)
+    assert selfplay.default_stream() == (5, 77)
+    selfplay.set_seed(None)
+    torch.manual_seed(100)
+    assert selfplay.default_stream() == (100, 0)
 
 
 def test_single_process_is_a_no_op():

@@ -6,6 +6,7 @@ they run -- c6_forward may grow its workspace with cudaMalloc, this one works ou
 different inputs (the array keeps the previous call's contents) and compares each result with
 c6_forward on the same engine.  The file name sorts last so that a run stopping at the first
 failure has already executed every other test.
+The first call is also compared directly with the CPU oracle of the reference's forward.
 """
 from __future__ import annotations
 
@@ -13,6 +14,8 @@ import ctypes as C
 
 import pytest
 import torch
+
+import torch_port as TP
 
 pytestmark = pytest.mark.gpu
 
@@ -48,6 +51,11 @@ def test_forward_noalloc_matches_forward_twice_in_a_row(cuda_device):
             torch.cuda.synchronize(cuda_device)
             assert torch.allclose(logits, want_logits, atol=TOL, rtol=0)
             assert torch.allclose(value, want_value, atol=TOL, rtol=0)
+            if first == 0:   # and against the oracle itself (connect6/model.py:96-111 on CPU, fp64), legal cells only
+                ref_l, ref_v = TP.policy_value_forward(x.cpu().double(), {k: v.double() for k, v in state.items()})
+                legal = ((x[:, 0] == 0) & (x[:, 1] == 0)).flatten(1).cpu()
+                assert (logits.cpu().double() - ref_l)[legal].abs().max().item() < 1e-5
+                assert (value.cpu().double() - ref_v).abs().max().item() < 1e-5
 
         # per-board orientation goes through the same scratch
         x = torch.from_numpy(generate_planes(77, 8)).to(cuda_device)

@@ -38,7 +38,7 @@ HEAD_MACS = 69_312
 INPUT_BUFFERS = 5                       # 5 x 35.5 MB of inputs rotate: larger than the 126 MB L2
 # DRAM traffic of conv_tc_kernel per launch, from the ncu capture summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the 7 launches of one step).
-CONV_TRAFFIC_BYTES_PER_LAUNCH = 633_000_000   # 158.3 MB measured at B = 2048, scaled by boards to 8192
+CONV_TRAFFIC_BYTES_PER_LAUNCH = 626_000_000   # 156.5 MB measured at B = 2048, scaled by boards to 8192
 WEIGHT_SEED = 42
 CPU_SAMPLE_BOARDS = 256
 
@@ -542,6 +542,25 @@ def run_workload(args) -> None:
         boards, flop, scaling = G * T, FLOP_PER_BOARD, "weak"
         step = lambda i: eng.forward_grouped(x, want_value=True)
         desc = "16 stacked default-architecture checkpoints x 512 boards, bf16, per-group logits and values"
+    elif wl == "ensemble":
+        # the ensemble shape the reference trains against (configs/train.yaml: 128 stacked opponents, 4 tables each)
+        from pathlib import Path as _P
+        from connect6_b200.history import HistoricalCheckpoint, HistoricalPolicyEnsemble
+        G, T = 128, 4
+        cfg = {"architecture_version": 4, "kernels": list(DEFAULT_KERNELS), "channels": list(DEFAULT_CHANNELS)}
+        cps = [HistoricalCheckpoint(_P(f"model_update_{g + 1:08d}.pt"), g + 1, state_for(2000 + g), cfg,
+                                    {"board_size": 19, "win_length": 6}) for g in range(G)]
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        ens = HistoricalPolicyEnsemble(cps, dev, dtype=torch.bfloat16)     # connect6/history.py:195-232: stack + cast + upload
+        torch.cuda.synchronize(dev)
+        build_s = time.perf_counter() - t0
+        eng = ens._engine
+        x = torch.from_numpy(generate_planes(rank * G * T, G * T)).reshape(G, T, 3, 19, 19).to(dev)
+        boards, flop, scaling = G * T, FLOP_PER_BOARD, "weak"
+        step = lambda i: ens.forward_grouped(x)
+        desc = (f"128 stacked default-architecture checkpoints x 4 boards, bf16, policy logits; ensemble built from 128 "
+                f"host state_dicts in {build_s:.3f} s, {eng.device_bytes / 1e6:.0f} MB on the device")
     elif wl == "cfg4":
         total = 65536
         lo, hi = shard_range(total, rank, world)
@@ -809,8 +828,9 @@ def main() -> None:
     ap.add_argument("--precision", default="bf16", choices=["bf16", "f16", "fp32"],
                     help="arithmetic mode of the engine for --workload cfg2: bf16 is the contract's benchmark; f16 the "
                          "fp16 tensor-core mode; fp32 the CUDA-core exact mode")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "selfplay", "small"],
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "ensemble", "selfplay", "small"],
                     help="cfg2 (default) is the contract's benchmark; cfg3-5 are BASELINE's other configurations; "
+                         "ensemble is the reference's training shape of the historical opponents (128 models x 4 boards); "
                          "selfplay adds the environment step and bookkeeping around the network; small is a short "
                          "self-ending run of --boards boards for profilers")
     ap.add_argument("--boards", type=int, default=2048, help="boards of --workload small")

@@ -110,6 +110,96 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
   xk[((brow >> 7) * kc + c) * 128 + (brow & 127)] = o;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Direct stem (few boards per weight set): input planes "x-expanded" for the implicit GEMM of
+// conv_tc_kernel's stem mode.  Board images are zero padded to slots/wi rows of pitch wi (cells at rows
+// and columns 0..n-1; the pad columns and rows of one image are the left/top padding of the next) and
+// laid end to end; row R of plane ci holds the 8 consecutive linear positions R .. R+7 of that sequence,
+// so the last rows of an image (and the 8 rows in front of a group's first image) already carry the first
+// cells of the image behind them.  A group's threads write rows [base - 8, base + nb*slots - 8); the 8 rows
+// behind a group's last image are all padding and stay zero.
+// Grid: (ceil(3*slots*nb/256), G); one thread per (plane, row).
+// ------------------------------------------------------------------------------------------------
+__global__ void pack_stem_direct_input_kernel(const InputSrc in, const uint8_t* __restrict__ orient,
+                                              uint4* __restrict__ xe, long long plane_rows, int front, int group_pos,
+                                              int wi, int slots, int n, int nb, long long group_stride, long long board0,
+                                              int f16, int* __restrict__ status) {
+  grid_dep_launch();
+  const int g = blockIdx.y;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long per_plane = (long long)slots * nb;
+  if (idx >= 3 * per_plane) return;
+  const int ci = (int)(idx / per_plane);
+  const long long p = idx - (long long)ci * per_plane - 8;   // row relative to the group's first image
+  const int cells = n * n;
+  // (image t, row r, column c) of the row's first position, stepped along the 8 positions of the row
+  long long pos = p < 0 ? 0 : p;
+  int t = (int)(pos / slots);
+  int q = (int)(pos - (long long)t * slots);
+  int r = q / wi, c = q - r * wi;
+  const int hi = slots / wi;
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float val = 0.f;
+    if (p + e >= 0) {
+      if (r < n && c < n) {
+        const long long src_board = (long long)g * group_stride + board0 + t;
+        const int phase = orient ? (orient[src_board] & 7) : 0;
+        int cell = r * n + c;
+        if (phase) cell = d4_inverse(cell, n, phase);
+        if (cell == 0 && ci == 0 && in.boards != nullptr && input_env(in, src_board) < 0) atomicOr(status, kStatBadIndex);
+        val = input_value(in, src_board, ci, cell, cells);
+      }
+      if (++c == wi) {
+        c = 0;
+        if (++r == hi) { r = 0; ++t; }
+      }
+    }
+    v[e] = val;
+  }
+  uint4 o;
+  o.x = pack_h2(v[0], v[1], f16);
+  o.y = pack_h2(v[2], v[3], f16);
+  o.z = pack_h2(v[4], v[5], f16);
+  o.w = pack_h2(v[6], v[7], f16);
+  xe[(size_t)ci * plane_rows + front + (long long)g * group_pos + p] = o;
+}
+
+// Filter of the first layer for the direct stem: rows [ci][ky][hb][j][co] of 8 elements, element e of the row
+// being filter column kx = 16 hb + 8 j + e (zero for kx >= k0 and for co >= cout).  halves = 2 lays the
+// rows out for CTA pairs: [half][ci][ky][hb][j][co % (cout_p/2)].
+__global__ void pack_stem_direct_weights_kernel(const float* __restrict__ w, uint4* __restrict__ out, int cout, int kside,
+                                                int cout_p, int hx, int halves, int f16) {
+  const int nh = cout_p / halves;
+  const long long total = 3LL * kside * hx * 2 * cout_p;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int col = (int)(idx % nh);
+  long long r = idx / nh;
+  const int j = (int)(r % 2);
+  r /= 2;
+  const int hb = (int)(r % hx);
+  r /= hx;
+  const int ky = (int)(r % kside);
+  r /= kside;
+  const int ci = (int)(r % 3);
+  const int half = (int)(r / 3);
+  const int co = half * nh + col;
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int kx = 16 * hb + 8 * j + e;
+    v[e] = (co < cout && kx < kside) ? w[(((size_t)co * 3 + ci) * kside + ky) * kside + kx] : 0.f;
+  }
+  uint4 o;
+  o.x = pack_h2(v[0], v[1], f16);
+  o.y = pack_h2(v[2], v[3], f16);
+  o.z = pack_h2(v[4], v[5], f16);
+  o.w = pack_h2(v[6], v[7], f16);
+  out[idx] = o;
+}
+
 // fp32 mode: x -> fp32 NCHW copy in view orientation, boards of all groups laid out [g][t].
 __global__ void view_input_f32_kernel(const InputSrc in,
                                       const uint8_t* __restrict__ orient, float* __restrict__ out,

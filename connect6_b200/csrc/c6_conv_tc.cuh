@@ -29,6 +29,17 @@
 // layers run at their MMA or HBM floor.
 // A ring of 2, 4 or 8 TMEM accumulators lets the teams overlap the MMAs of later tiles.  Every wait
 // is bounded: when one runs out the CTA records a status bit, stops, frees TMEM and returns.
+//
+// Direct stem mode (generic instantiation KS = 0 with p.stem set): the first backbone layer
+// (3 input planes, one wide k0 x k0 filter, connect6/model.py:22,56-63) as an implicit GEMM straight from
+// the filter, for passes with few boards per weight set -- the Toeplitz stem GEMM reads 27 MB of expanded
+// weights per model whatever the batch, this mode reads the model's own k0*k0*3*Cout filter.  K runs
+// along the filter's x axis: input plane ci is stored "x-expanded", row p holding the 8 consecutive
+// linear positions p .. p+7 of the zero-padded board image (pitch Wi), so one 128 x N x 16 MMA with
+// A chunk pitch (LBO) = 8 rows covers 16 consecutive kx of one (ci, ky): a "tap" is (ky, 16-wide kx
+// block), its shift (ky - k0/2) * Wi + 16 * block - k0/2, and the filter is zero beyond kx = k0 - 1.
+// A pipeline step is one input plane; output positions are walked in the INPUT geometry and stored to the
+// output planes' own (narrower) geometry, cells only.
 #pragma once
 
 #include "c6_common.cuh"
@@ -70,6 +81,15 @@ struct ConvTcParams {
   int nacc;              // accumulator buffers in the ring: 2, 4 or 8 (twice the issuers when possible)
   int tmem_cols;
   int head;
+  // ---- generalisations used by the direct stem mode (plain layers: the values in brackets) ----
+  long long in_plane_rows; // rows per input plane [= plane_rows]
+  int ntaps;             // MMAs per 16-channel group [kside * kside]
+  int halo_after;        // rows staged behind the 128 tile rows [= halo_rows]
+  int planes_step;       // activation planes per pipeline step [2 * qps]
+  int stem;              // 1: direct stem mode
+  int stem_hx;           // stem: 16-wide kx blocks per filter row
+  int a_lbo_rows;        // stem: rows between the two K chunks of an A operand (8) [0: the stage's plane pitch]
+  int out_front, out_wp, out_slots, out_group_pos;   // stem: geometry of the output planes (wp, slots, front, group_pos describe the input)
   // Single-model engines pass the epilogue vectors by value: kernel parameters live in the
   // constant bank, whose cache is separate from shared memory -- the MMAs already use the whole
   // shared-memory bandwidth, so epilogue reads from shared memory would queue behind them.
@@ -123,10 +143,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   const uint32_t crank = PAIR ? tc::cluster_ctarank() : 0u;
   const bool leader = crank == 0;
   const int nloc = PAIR ? p.n / 2 : p.n;   // weight rows this CTA holds
-  const int taps = p.kside * p.kside;
+  const int taps = p.ntaps;
   const int nq = p.cin >> 4;
-  const int rows = conv_stage_rows(p.halo_rows);
-  const uint32_t a_bytes = 2u * (uint32_t)p.qps * rows * 16u;    // 2 * qps channel-chunk planes per step
+  const int rows = 128 + p.halo_rows + p.halo_after;
+  const uint32_t a_bytes = (uint32_t)p.planes_step * rows * 16u;  // channel-chunk planes of one step (2 * qps)
   const uint32_t wq_bytes = (uint32_t)taps * 2u * nloc * 16u;   // this CTA's weights of one q (16 input channels)
   const int nsteps = nq / p.qps;                                 // pipeline steps per tile
   const uint32_t w_bytes = wq_bytes * nq;
@@ -234,7 +254,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     // together; every ring has received the same number of steps, hence one (position, parity) pair.
     int sl = 0;
     uint32_t ph = 0;
-    const int nplanes = 2 * p.qps;
+    const int nplanes = p.planes_step;
     for (int tb = 0; tb < ntl && ok; tb += p.nissue) {
       for (int step = 0; step < nsteps && ok; ++step) {
         for (int iss = prod; iss < p.nissue; iss += nprod) {
@@ -258,7 +278,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
           }
           const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
           if (lane < nplanes) {
-            const uint4* src = p.in + (size_t)(nplanes * step + lane) * p.plane_rows + row0;
+            const uint4* src = p.in + (size_t)(nplanes * step + lane) * p.in_plane_rows + row0;
             tc::bulk_g2s(dst + (uint32_t)lane * rows * 16u, src, rows * 16u, bar_full(s));
           } else if (lane == nplanes && !p.resident) {
             tc::bulk_g2s(dst + a_bytes, reinterpret_cast<const uint8_t*>(w_group) + (size_t)(p.qps * step) * wq_bytes,
@@ -288,7 +308,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
     const uint32_t idesc = tc::make_idesc_16(PAIR ? 256 : 128, p.n, F16);
     const int kh = p.kside >> 1;
     const uint32_t desc_hi = (uint32_t)(tc::make_desc(0, 0, 128u) >> 32);   // SBO = 128 B, version 1
-    const uint32_t a_lbo_field = ((uint32_t)(rows * 16) >> 4) << 16;          // LBO = plane pitch of a stage
+    const uint32_t a_lbo_field = (uint32_t)(p.a_lbo_rows ? p.a_lbo_rows : rows) << 16;   // LBO (16-byte units) = plane pitch of a stage
     const uint32_t b_lbo_field = ((uint32_t)(nloc * 16) >> 4) << 16;          // LBO = this CTA's Cout rows
     const uint32_t b_step = 2u * (uint32_t)nloc;                               // rows between taps
     const uint32_t w_lo = (tc::smem_u32(s_w) >> 4) | b_lbo_field;
@@ -362,6 +382,19 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
                                ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc,
                                (step | qq | tap) != 0 ? 1u : 0u);
               }
+            } else if (p.stem) {
+              // direct stem: tap = (filter row ky, 16-wide kx block hb)
+              int tap = 0;
+              for (int ky = 0; ky < p.kside; ++ky)
+                for (int hb = 0; hb < p.stem_hx; ++hb, ++tap) {
+                  const uint32_t shift = (uint32_t)(p.halo_rows + (ky - kh) * p.wp + hb * 16 - kh);
+                  if (PAIR)
+                    tc::mma_bf16_pair(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + shift),
+                                      ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc, (step | tap) != 0 ? 1u : 0u);
+                  else
+                    tc::mma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + shift),
+                                 ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)tap * b_step), idesc, (step | tap) != 0 ? 1u : 0u);
+                }
             } else {
               int tap = 0;
               for (int dy = -kh; dy <= kh; ++dy)
@@ -480,7 +513,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
       const int r = slot / p.wp, c = slot - r * p.wp;
       const bool valid = board < p.nboards && r < p.bsize && c < p.bsize;
       const uint32_t taddr = tmem_base + (uint32_t)(acc * p.acc_stride) + ((uint32_t)(quad * 32) << 16);
-      uint4* out_row = p.out + group_row0 + pos;
+      // plain layers write every position of the tile (zeros into the pad slots); the direct stem walks
+      // the input geometry and writes cells only, into the output planes' own geometry
+      const bool store = (KS == 0 && p.stem) ? valid : true;
+      uint4* out_row = (KS == 0 && p.stem)
+                           ? p.out + (long long)p.out_front + (long long)group * p.out_group_pos + (long long)board * p.out_slots + r * p.out_wp + c
+                           : p.out + group_row0 + pos;
       float pol = 0.f, val = 0.f;
       // Up to three 16-channel units are fetched from TMEM with one wait so that their latencies
       // overlap; after the last fetch the accumulator goes back to the MMA warp before the
@@ -557,7 +595,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
                 o.y = valid ? pack_h2<F16>(y[8 * k + 2], y[8 * k + 3]) : 0u;
                 o.z = valid ? pack_h2<F16>(y[8 * k + 4], y[8 * k + 5]) : 0u;
                 o.w = valid ? pack_h2<F16>(y[8 * k + 6], y[8 * k + 7]) : 0u;
-                out_row[(size_t)(u * 2 + k) * p.plane_rows] = o;
+                if (store) out_row[(size_t)(u * 2 + k) * p.plane_rows] = o;
               }
             }
           }

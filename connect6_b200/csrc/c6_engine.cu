@@ -70,8 +70,20 @@ struct C6Engine {
   uint8_t* occ = nullptr;           // [kc_short][mrows] occupancy bits of planes 0/1 (workspace, written by the input pack kernel)
   int kc0 = 0, nt = 0, ntiles = 0, ntot = 0, stem_stages = 0, stem_smem = 0, stem_acc_stride = 0,
       stem_tmem_cols = 0, stem_kcs = 4, stem_pair = 0;
+  // direct stem (conv_tc_kernel's stem mode), taken by passes of at most sd_max_boards boards per group
+  int sd_ok = 0, sd_max_boards = 32, sd_hx = 0, sd_wi = 0, sd_slots = 0, sd_halo_b = 0, sd_halo_a = 0, sd_front = 0;
+  LayerPlan sdp;                    // its pipeline plan
+  uint4* w_sd = nullptr;            // [G][ci][ky][kx block][2][cout_p] filter rows
+  uint4* w_sd_pair = nullptr;       // the same split in two row halves for CTA pairs
+  uint4* xe = nullptr;              // workspace: 3 x-expanded input planes
+  long long xe_plane_rows = 0, sd_last_group_pos = -1;
+  long long xk_rows = 0;              // rows per plane of xk / occ as allocated
+  long long xe_cap = 0, xk_cap = 0;   // boards per group the stem operands of the two paths are sized for
   // weights
-  uint4* wt = nullptr;              // [G][kc0][ntot]
+  uint4* wt = nullptr;              // [G][kc0][ntot] Toeplitz rows of the stem GEMM: 27 MB per model for the default
+                                    // net, so they are allocated and expanded only when a pass first needs them
+  float* w0_raw = nullptr;          // [G][cout*3*k0*k0] the first layer's filter as received (source of that expansion)
+  std::vector<uint8_t> wt_fresh;    // [G] Toeplitz rows match w0_raw
   std::vector<uint4*> wconv;        // per layer [G][rows]
   std::vector<uint4*> wconv_pair;   // per layer, pair mode: [G][2 halves][rows/2]
   bool pair_mode = false;           // tile counts are kept even so that layers may run as CTA pairs
@@ -256,7 +268,24 @@ Geometry geometry(const C6Engine* e, long long nb) {
   return g;
 }
 
+// Tiles of the direct stem walk the INPUT geometry (pitch sd_wi, sd_slots per board image).
+Geometry geometry_sd(const C6Engine* e, long long nb) {
+  Geometry g;
+  const int used = (e->n - 1) * e->sd_wi + e->n;
+  const int tpb = (used + 127) / 128;
+  g.tiles_per_board = tpb * 128 < e->sd_slots ? tpb : 0;
+  g.tiles_per_group = g.tiles_per_board ? (int)(nb * tpb) : (int)((nb * e->sd_slots + 127) / 128);
+  if (e->sdp.pair) g.tiles_per_group += g.tiles_per_group & 1;
+  g.group_pos = g.tiles_per_board
+                    ? round_up_ll((long long)((g.tiles_per_group + tpb - 1) / tpb) * e->sd_slots, 128)
+                    : (long long)g.tiles_per_group * 128;
+  g.mrows_per_group = 0;
+  return g;
+}
+
 void free_workspace(C6Engine* e) {
+  cudaFree(e->xe);
+  e->xe = nullptr;
   cudaFree(e->xk);
   cudaFree(e->occ);
   e->occ = nullptr;
@@ -275,37 +304,123 @@ void free_workspace(C6Engine* e) {
   e->dev_bytes -= e->ws_bytes;
   e->ws_bytes = 0;
   e->cap = 0;
+  e->xe_cap = e->xk_cap = 0;
 }
 
-// Grow the workspace to hold `nb` boards per group.  Synchronises the device when it grows.
-int ensure_workspace(C6Engine* e, long long nb) {
-  if (nb <= e->cap) return C6_OK;
+// Grow the workspace to hold `nb` boards per group; `direct` says which stem path the pass takes (its
+// operand buffers are only allocated for the path in use).  Synchronises the device when anything grows.
+int ensure_workspace(C6Engine* e, long long nb, bool direct) {
+  const bool tc = e->prec != C6_PREC_FP32;
+  if (nb <= e->cap && (!tc || (direct ? nb <= e->xe_cap : nb <= e->xk_cap))) return C6_OK;
   C6_CUDA(e, cudaDeviceSynchronize());
-  free_workspace(e);
-  const Geometry g = geometry(e, nb);
-  if (e->prec != C6_PREC_FP32) {
-    e->plane_rows = (long long)e->front + (long long)e->G * g.group_pos + e->halo_rows;
-    e->mrows = (long long)e->G * g.mrows_per_group;
-    const size_t act_rows = (size_t)(e->cmax_p / 8) * e->plane_rows;
-    int rc;
+  int rc;
+  if (nb > e->cap) {
+    free_workspace(e);
+    const Geometry g = geometry(e, nb);
+    if (tc) {
+      e->plane_rows = (long long)e->front + (long long)e->G * g.group_pos + e->halo_rows;
+      e->mrows = (long long)e->G * g.mrows_per_group;
+      const size_t act_rows = (size_t)(e->cmax_p / 8) * e->plane_rows;
+      if ((rc = dev_alloc(e, &e->act[0], act_rows, true, &e->ws_bytes))) return rc;
+      if ((rc = dev_alloc(e, &e->act[1], act_rows, true, &e->ws_bytes))) return rc;
+      if ((rc = dev_alloc(e, &e->logit_raw, (size_t)e->G * g.group_pos, true, &e->ws_bytes))) return rc;
+      if ((rc = dev_alloc(e, &e->vmap, (size_t)e->G * g.group_pos, true, &e->ws_bytes))) return rc;
+    } else {
+      const size_t boards = (size_t)e->G * nb;
+      if ((rc = dev_alloc(e, &e->f32x, boards * 3 * e->cells, false, &e->ws_bytes))) return rc;
+      if ((rc = dev_alloc(e, &e->f32buf[0], boards * e->cmax * e->cells, false, &e->ws_bytes))) return rc;
+      if ((rc = dev_alloc(e, &e->f32buf[1], boards * e->cmax * e->cells, false, &e->ws_bytes))) return rc;
+      if ((rc = dev_alloc(e, &e->logit_raw, boards * e->cells, false, &e->ws_bytes))) return rc;
+      if ((rc = dev_alloc(e, &e->vmap, boards * e->cells, false, &e->ws_bytes))) return rc;
+    }
+    e->cap = nb;
+    e->last_group_pos = -1;
+  }
+  if (tc && direct && nb > e->xe_cap) {
+    // x-expanded input planes of the direct stem, for the largest pass that path takes
+    if (e->xe) { e->ws_bytes -= (long long)(3 * e->xe_plane_rows * sizeof(uint4)); e->dev_bytes -= (long long)(3 * e->xe_plane_rows * sizeof(uint4)); }
+    cudaFree(e->xe);
+    e->xe = nullptr;
+    const Geometry gs = geometry_sd(e, e->sd_max_boards);
+    e->xe_plane_rows = (long long)e->sd_front + (long long)e->G * gs.group_pos + e->sd_halo_a + 128 + 16;
+    if ((rc = dev_alloc(e, &e->xe, (size_t)3 * e->xe_plane_rows, true, &e->ws_bytes))) return rc;
+    e->xe_cap = e->sd_max_boards;
+    e->sd_last_group_pos = -1;
+  }
+  if (tc && !direct && e->xk_cap < e->cap) {
+    // operand rows and occupancy bits of the stem GEMM, sized like the activation planes
+    if (e->xk) {
+      const long long old = (long long)((size_t)e->kc0 * e->xk_rows * sizeof(uint4) + (size_t)e->kc_short * e->xk_rows);
+      e->ws_bytes -= old;
+      e->dev_bytes -= old;
+    }
+    cudaFree(e->xk);
+    cudaFree(e->occ);
+    e->xk = nullptr;
+    e->occ = nullptr;
+    e->xk_rows = e->mrows;
     if ((rc = dev_alloc(e, &e->xk, (size_t)e->kc0 * e->mrows, true, &e->ws_bytes))) return rc;
     if ((rc = dev_alloc(e, &e->occ, (size_t)e->kc_short * e->mrows, true, &e->ws_bytes))) return rc;
-    if ((rc = dev_alloc(e, &e->act[0], act_rows, true, &e->ws_bytes))) return rc;
-    if ((rc = dev_alloc(e, &e->act[1], act_rows, true, &e->ws_bytes))) return rc;
-    if ((rc = dev_alloc(e, &e->logit_raw, (size_t)e->G * g.group_pos, true, &e->ws_bytes))) return rc;
-    if ((rc = dev_alloc(e, &e->vmap, (size_t)e->G * g.group_pos, true, &e->ws_bytes))) return rc;
-  } else {
-    const size_t boards = (size_t)e->G * nb;
-    int rc;
-    if ((rc = dev_alloc(e, &e->f32x, boards * 3 * e->cells, false, &e->ws_bytes))) return rc;
-    if ((rc = dev_alloc(e, &e->f32buf[0], boards * e->cmax * e->cells, false, &e->ws_bytes))) return rc;
-    if ((rc = dev_alloc(e, &e->f32buf[1], boards * e->cmax * e->cells, false, &e->ws_bytes))) return rc;
-    if ((rc = dev_alloc(e, &e->logit_raw, boards * e->cells, false, &e->ws_bytes))) return rc;
-    if ((rc = dev_alloc(e, &e->vmap, boards * e->cells, false, &e->ws_bytes))) return rc;
+    e->xk_cap = e->cap;
   }
-  e->cap = nb;
-  e->last_group_pos = -1;
   return C6_OK;
+}
+
+// Pipeline shape of one tensor-core layer: `taps` MMAs per 16-channel group, `nq` groups, `rows` staged
+// rows per activation plane, `planes_per_q` planes per group (2; the direct stem: 1), steps of up to
+// `max_qps` groups.  Prefers resident weights and wide steps; every MMA issuer (up to one per two
+// accumulators, at most 4) needs a private ring of at least 2 stages.  False when nothing fits.
+bool plan_tc_layer(const C6Engine* e, LayerPlan& p, int taps, int nq, int rows, int planes_per_q, int max_qps) {
+  const int budget = kSmemLimit - 128 - kConvSmemHeader;
+  const long long wq = (long long)taps * 2 * p.cout_p * 16;
+  const long long wb = wq * nq;
+  p.w_rows_per_group = (size_t)(wb / 16);
+  p.acc_stride = pow2_ceil(p.cout_p);
+  p.nacc = std::min(kMaxAcc, 512 / p.acc_stride);  // 512 TMEM columns in total: 8, 4 or 2 accumulators
+  p.tmem_cols = p.nacc * p.acc_stride;
+  p.pair = 0;
+  const int want = std::max(1, std::min(p.nacc / 2, 4));   // two accumulators per issuer
+  // First choice: CTA pairs with resident weights (each CTA keeps half of the rows).
+  if (e->pair_mode) {
+    for (int qps = max_qps; qps >= 1; --qps) {
+      const long long stage = round_up_ll((long long)planes_per_q * qps * rows * 16, 128);
+      const long long fixed = round_up_ll(wb / 2, 128);
+      if (fixed + 2LL * want * stage > budget) continue;
+      const int ns = (int)std::min<long long>(kMaxStages, (budget - fixed) / stage);
+      p.pair = 1;
+      p.resident = 1;
+      p.qps = qps;
+      p.nissue = want;
+      p.spi = std::min(4, ns / want);
+      p.nstages = p.nissue * p.spi;
+      p.smem = 128 + kConvSmemHeader + (int)fixed + p.nstages * (int)stage;
+      return true;
+    }
+  }
+  for (int resident = 1; resident >= 0; --resident) {
+    for (int qps = max_qps; qps >= 1; --qps) {
+      const long long a_bytes = (long long)planes_per_q * qps * rows * 16;
+      const long long stage = round_up_ll(a_bytes + (resident ? 0 : qps * wq), 128);
+      const long long fixed = resident ? round_up_ll(wb, 128) : 0;
+      if (fixed + 2 * stage > budget) continue;
+      const int ns = (int)std::min<long long>(kMaxStages, (budget - fixed) / stage);
+      if (qps == 2 && ns < 2 * want && resident) {
+        // smaller steps may buy enough stages for all issuers: try qps = 1 first
+        const long long stage1 = round_up_ll((long long)planes_per_q * rows * 16, 128);
+        if ((budget - fixed) / stage1 >= 2 * want) continue;
+      }
+      int nissue = want;
+      while (nissue > 1 && ns < 2 * nissue) nissue >>= 1;
+      p.resident = resident;
+      p.qps = qps;
+      p.nissue = nissue;
+      p.spi = std::min(3, ns / nissue);
+      p.nstages = p.nissue * p.spi;
+      p.smem = 128 + kConvSmemHeader + (int)fixed + p.nstages * (int)stage;
+      return true;
+    }
+  }
+  return false;
 }
 
 int fp32_cit(const LayerPlan& l) { return l.k <= 5 ? std::min(l.cin, 16) : std::min(l.cin, 4); }
@@ -345,6 +460,7 @@ struct RunArgs {
   long long board_index0 = 0;
   long long* action = nullptr;
   float* logprob = nullptr;
+  int direct_stem = 0;       // this call's first layer runs straight from the filter (set by run())
   int stop_layer = -1;       // debug: stop after this backbone layer
   float* layer_out = nullptr;  // debug: fp32 NCHW output of stop_layer
 };
@@ -401,6 +517,103 @@ int launch_finish(C6Engine* e, const RunArgs& a, long long t0, int nb, long long
   return C6_OK;
 }
 
+// Toeplitz rows of weight set `group` from its stored filter (enqueued on `st`).
+int expand_toeplitz(C6Engine* e, int group, cudaStream_t st) {
+  const LayerPlan& p = e->lp[0];
+  const long long total = (long long)e->kc0 * e->ntot;
+  pack_stem_toeplitz_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+      e->w0_raw + (size_t)group * p.cout * 3 * p.k * p.k, e->wt + (size_t)group * e->kc0 * e->ntot, p.cout, p.k, e->n,
+      p.cout_p, e->kc0, e->kc_short, e->ntot, e->nt, e->stem_pair ? 2 : 1, e->f16);
+  C6_LAUNCHED(e, "pack_stem_toeplitz_kernel");
+  e->wt_fresh[group] = 1;
+  return C6_OK;
+}
+
+// The stem GEMM's operand exists and is current (allocates on first use; synchronises the device then).
+int ensure_toeplitz(C6Engine* e, cudaStream_t st) {
+  if (!e->wt) {
+    C6_CUDA(e, cudaDeviceSynchronize());
+    int rc = dev_alloc(e, &e->wt, (size_t)e->G * e->kc0 * e->ntot, true, nullptr);
+    if (rc) return rc;
+  }
+  for (int g = 0; g < e->G; ++g)
+    if (!e->wt_fresh[g]) {
+      int rc = expand_toeplitz(e, g, st);
+      if (rc) return rc;
+    }
+  return C6_OK;
+}
+
+// First backbone layer through conv_tc_kernel's stem mode: pack the x-expanded input planes, then one
+// implicit GEMM straight from the filter into act[0].
+int run_direct_stem(C6Engine* e, const RunArgs& a, long long t0, int nb, const Geometry& g, cudaStream_t st) {
+  const Geometry gs = geometry_sd(e, nb);
+  if (gs.group_pos != e->sd_last_group_pos) {
+    // image bases moved: rows between and behind the images must read as zero padding again
+    C6_CUDA(e, cudaMemsetAsync(e->xe, 0, (size_t)3 * e->xe_plane_rows * sizeof(uint4), st));
+    e->sd_last_group_pos = gs.group_pos;
+  }
+  {
+    const long long total = 3LL * e->sd_slots * nb;
+    ProfScope _ps(e, C6_KIND_PACK, st);
+    pack_stem_direct_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
+        input_of(a), a.orient, e->xe, e->xe_plane_rows, e->sd_front, (int)gs.group_pos, e->sd_wi, e->sd_slots, e->n, nb,
+        a.T, t0, e->f16, e->status_dev);
+    C6_LAUNCHED(e, "pack_stem_direct_input_kernel");
+  }
+  const LayerPlan& lp = e->sdp;
+  ConvTcParams p{};
+  p.in = e->xe;
+  p.in_plane_rows = e->xe_plane_rows;
+  p.out = e->act[0];
+  p.plane_rows = e->plane_rows;
+  p.w = e->w_sd;
+  p.w_pair = e->w_sd_pair;
+  p.bias = e->bias[0];
+  p.status = e->status_dev;
+  p.front = e->sd_front;
+  p.halo_rows = e->sd_halo_b;
+  p.halo_after = e->sd_halo_a;
+  p.cin = 48;                       // three pipeline steps, one input plane each
+  p.n = lp.cout_p;
+  p.kside = lp.k;
+  p.ntaps = lp.k * e->sd_hx;
+  p.planes_step = 1;
+  p.stem = 1;
+  p.stem_hx = e->sd_hx;
+  p.a_lbo_rows = 8;
+  p.wp = e->sd_wi;
+  p.slots = e->sd_slots;
+  p.bsize = e->n;
+  p.nboards = nb;
+  p.tiles_per_group = gs.tiles_per_group;
+  p.tiles_per_board = gs.tiles_per_board;
+  p.group_pos = (int)gs.group_pos;
+  p.out_front = e->front;
+  p.out_wp = e->wp;
+  p.out_slots = e->slots;
+  p.out_group_pos = (int)g.group_pos;
+  p.ctas_per_group = std::max(1, std::min(e->sms / e->G, gs.tiles_per_group));
+  if (lp.pair) p.ctas_per_group = std::max(2, p.ctas_per_group & ~1);
+  p.resident = lp.resident;
+  p.nstages = lp.nstages;
+  p.nissue = lp.nissue;
+  p.spi = lp.spi;
+  p.qps = 1;
+  p.use_const = e->G == 1 ? 1 : 0;
+  if (p.use_const) std::memcpy(p.c_hbias, e->h_bias[0].data(), sizeof(p.c_hbias));
+  p.acc_stride = lp.acc_stride;
+  p.nacc = lp.nacc;
+  p.tmem_cols = lp.tmem_cols;
+  {
+    ProfScope _ps(e, C6_KIND_STEM, st);
+    launch_chain(conv_kernel_for(false, lp.pair != 0, e->f16 != 0, 0), (unsigned)(e->G * p.ctas_per_group), 1u, kConvThreads,
+                 (size_t)lp.smem, st, lp.pair != 0, e->dependent_launch, p);
+  }
+  C6_LAUNCHED(e, "conv_tc_kernel (direct stem)");
+  return C6_OK;
+}
+
 int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStream_t st) {
   const Geometry g = geometry(e, nb);
   if (e->G > 1 && g.group_pos != e->last_group_pos) {
@@ -411,59 +624,71 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
   }
   e->last_group_pos = g.group_pos;
 
-  {  // input planes
-    const long long total = (long long)e->kc0 * nb;
-    ProfScope _ps(e, C6_KIND_PACK, st);
-    pack_stem_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
-        input_of(a), a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->kc_short, e->n, nb, a.T, t0,
-        ++e->stem_epoch, e->p2_epoch, e->occ, e->f16, e->status_dev);
-    C6_LAUNCHED(e, "pack_stem_input_kernel");
-  }
+  // few boards per weight set: the first layer straight from the filter (conv_tc_kernel's stem mode);
+  // otherwise the Toeplitz GEMM
+  const bool direct_stem = a.direct_stem != 0;
   int cur = 0;
-  {  // stem GEMM -> act[0]
-    StemTcParams p{};
-    p.xk = e->xk;
-    p.wt = e->wt;
-    p.bias = e->bias[0];
-    p.out = e->act[0];
-    p.status = e->status_dev;
-    p.wait_cycles = e->wait_counters ? e->wait_dev : nullptr;
-    p.plane_rows = e->plane_rows;
-    p.mrows = e->mrows;
-    p.mrows_per_group = g.mrows_per_group;
-    p.front = e->front;
-    p.group_pos = (int)g.group_pos;
-    p.kc = e->kc0;
-    p.kc_short = e->kc_short;
-    p.p2_epoch = e->p2_epoch;
-    p.epoch = e->stem_epoch;
-    p.kcs = e->stem_kcs;
-    p.ntot = e->ntot;
-    p.nt = e->nt;
-    p.ntiles = e->ntiles;
-    p.mtiles = g.mrows_per_group / 128;
-    p.groups = e->G;
-    p.c1 = e->lp[0].cout_p;
-    p.bsize = e->n;
-    p.wp = e->wp;
-    p.slots = e->slots;
-    p.nboards = nb;
-    p.nstages = e->stem_stages;
-    p.acc_stride = e->stem_acc_stride;
-    p.tmem_cols = e->stem_tmem_cols;
-    ProfScope _ps(e, C6_KIND_STEM, st);
-    if (e->stem_pair) {
-      const long long items = (long long)e->G * (p.mtiles / 2) * p.ntiles;
-      const int grid = 2 * (int)std::min<long long>(e->sms / 2, items);
-      launch_chain(e->f16 ? stem_tc_kernel<true, true> : stem_tc_kernel<true, false>, (unsigned)grid, 1u, kStemThreads,
-                   (size_t)e->stem_smem, st, true, e->dependent_launch, p);
-    } else {
-      const long long items = (long long)e->G * p.mtiles * p.ntiles;
-      const int grid = (int)std::min<long long>(e->sms, items);
-      launch_chain(e->f16 ? stem_tc_kernel<false, true> : stem_tc_kernel<false, false>, (unsigned)grid, 1u, kStemThreads,
-                   (size_t)e->stem_smem, st, false, e->dependent_launch, p);
+  if (direct_stem) {
+    int rc = run_direct_stem(e, a, t0, nb, g, st);
+    if (rc) return rc;
+  } else {
+    {
+      int rc = ensure_toeplitz(e, st);
+      if (rc) return rc;
     }
-    C6_LAUNCHED(e, "stem_tc_kernel");
+    {  // input planes
+      const long long total = (long long)e->kc0 * nb;
+      ProfScope _ps(e, C6_KIND_PACK, st);
+      pack_stem_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
+          input_of(a), a.orient, e->xk, e->mrows, g.mrows_per_group, e->kc0, e->kc_short, e->n, nb, a.T, t0,
+          ++e->stem_epoch, e->p2_epoch, e->occ, e->f16, e->status_dev);
+      C6_LAUNCHED(e, "pack_stem_input_kernel");
+    }
+    {  // stem GEMM -> act[0]
+      StemTcParams p{};
+      p.xk = e->xk;
+      p.wt = e->wt;
+      p.bias = e->bias[0];
+      p.out = e->act[0];
+      p.status = e->status_dev;
+      p.wait_cycles = e->wait_counters ? e->wait_dev : nullptr;
+      p.plane_rows = e->plane_rows;
+      p.mrows = e->mrows;
+      p.mrows_per_group = g.mrows_per_group;
+      p.front = e->front;
+      p.group_pos = (int)g.group_pos;
+      p.kc = e->kc0;
+      p.kc_short = e->kc_short;
+      p.p2_epoch = e->p2_epoch;
+      p.epoch = e->stem_epoch;
+      p.kcs = e->stem_kcs;
+      p.ntot = e->ntot;
+      p.nt = e->nt;
+      p.ntiles = e->ntiles;
+      p.mtiles = g.mrows_per_group / 128;
+      p.groups = e->G;
+      p.c1 = e->lp[0].cout_p;
+      p.bsize = e->n;
+      p.wp = e->wp;
+      p.slots = e->slots;
+      p.nboards = nb;
+      p.nstages = e->stem_stages;
+      p.acc_stride = e->stem_acc_stride;
+      p.tmem_cols = e->stem_tmem_cols;
+      ProfScope _ps(e, C6_KIND_STEM, st);
+      if (e->stem_pair) {
+        const long long items = (long long)e->G * (p.mtiles / 2) * p.ntiles;
+        const int grid = 2 * (int)std::min<long long>(e->sms / 2, items);
+        launch_chain(e->f16 ? stem_tc_kernel<true, true> : stem_tc_kernel<true, false>, (unsigned)grid, 1u, kStemThreads,
+                     (size_t)e->stem_smem, st, true, e->dependent_launch, p);
+      } else {
+        const long long items = (long long)e->G * p.mtiles * p.ntiles;
+        const int grid = (int)std::min<long long>(e->sms, items);
+        launch_chain(e->f16 ? stem_tc_kernel<false, true> : stem_tc_kernel<false, false>, (unsigned)grid, 1u, kStemThreads,
+                     (size_t)e->stem_smem, st, false, e->dependent_launch, p);
+      }
+      C6_LAUNCHED(e, "stem_tc_kernel");
+    }
   }
   const int last = a.stop_layer >= 0 ? a.stop_layer : e->L - 1;
   for (int l = 1; l <= last; ++l) {
@@ -486,6 +711,10 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.cin = lp.cin_p;
     p.n = lp.cout_p;
     p.kside = lp.k;
+    p.in_plane_rows = e->plane_rows;
+    p.ntaps = lp.k * lp.k;
+    p.halo_after = e->halo_rows;
+    p.planes_step = 2 * lp.qps;
     p.wp = e->wp;
     p.slots = e->slots;
     p.bsize = e->n;
@@ -531,7 +760,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     C6_LAUNCHED(e, "unpack_activation_kernel");
     return C6_OK;
   }
-  return launch_finish(e, a, t0, nb, g.group_pos, e->slots, e->wp, e->occ, g.mrows_per_group, st);
+  return launch_finish(e, a, t0, nb, g.group_pos, e->slots, e->wp, direct_stem ? nullptr : e->occ, g.mrows_per_group, st);
 }
 
 int run_pass_fp32(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStream_t st) {
@@ -583,11 +812,15 @@ int run(C6Engine* e, const RunArgs& a, void* stream) {
   C6_CUDA(e, cudaSetDevice(e->device));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long per_pass = std::max<long long>(1, e->chunk / e->G);
-  int rc = ensure_workspace(e, std::min(a.T, per_pass));
+  // The stem path is chosen once per call, from the call's boards per weight set, so that every pass of a
+  // call sums in the same order: the direct stem for small calls, the stem GEMM otherwise.
+  const bool direct = e->prec != C6_PREC_FP32 && e->sd_ok && a.T <= e->sd_max_boards && a.T <= per_pass;
+  int rc = ensure_workspace(e, std::min(a.T, per_pass), direct);
   if (rc) return rc;
   for (long long t0 = 0; t0 < a.T; t0 += per_pass) {
     const int nb = (int)std::min<long long>(per_pass, a.T - t0);
     RunArgs b = a;
+    b.direct_stem = direct ? 1 : 0;
     // outputs are indexed [g*T + t] by the kernels themselves (board0 = t0)
     rc = e->prec != C6_PREC_FP32 ? run_pass_bf16(e, b, t0, nb, st) : run_pass_fp32(e, b, t0, nb, st);
     if (rc) return rc;
@@ -612,6 +845,9 @@ int c6_destroy(C6Engine* e) {
   cudaDeviceSynchronize();
   free_workspace(e);
   cudaFree(e->wt);
+  cudaFree(e->w0_raw);
+  cudaFree(e->w_sd);
+  cudaFree(e->w_sd_pair);
   cudaFree(e->p2_epoch);
   for (auto p : e->wconv) cudaFree(p);
   for (auto p : e->wconv_pair) cudaFree(p);
@@ -721,72 +957,40 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     e->stem_smem = 128 + kStemSmemHeader + e->stem_stages * sstage + kStemPatchBytes;
     e->stem_acc_stride = pow2_ceil(e->nt);
     e->stem_tmem_cols = 2 * e->stem_acc_stride;
-    if ((rc = dev_alloc(e, &e->wt, (size_t)e->G * e->kc0 * e->ntot, true, nullptr))) return bail(rc, "");
+    e->wt_fresh.assign(e->G, 0);
+    if ((rc = dev_alloc(e, &e->w0_raw, (size_t)e->G * e->lp[0].cout * 3 * e->lp[0].k * e->lp[0].k, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->p2_epoch, 1, true, nullptr))) return bail(rc, "");
     if ((rc = dev_alloc(e, &e->bias[0], (size_t)e->G * c1, true, nullptr))) return bail(rc, "");
     // k x k layers
     e->pair_mode = e->sms / e->G >= 2;   // at least one CTA pair per group
     if (const char* v = std::getenv("C6_DEPENDENT_LAUNCH")) e->dependent_launch = std::strcmp(v, "0") != 0;
     const int rows = conv_stage_rows(e->halo_rows);
-    const int budget = kSmemLimit - 128 - kConvSmemHeader;
     for (int l = 1; l < e->L; ++l) {
       LayerPlan& p = e->lp[l];
-      const int taps = p.k * p.k, nq = p.cin_p / 16;
-      const long long wq = (long long)taps * 2 * p.cout_p * 16;
-      const long long wb = wq * nq;
-      p.w_rows_per_group = (size_t)(wb / 16);
-      p.acc_stride = pow2_ceil(p.cout_p);
-      p.nacc = std::min(kMaxAcc, 512 / p.acc_stride);  // 512 TMEM columns in total: 8, 4 or 2 accumulators
-      p.tmem_cols = p.nacc * p.acc_stride;
-      // Pipeline shape: prefer resident weights and 32-channel steps; every MMA issuer (up to one per
-      // accumulator, at most 4) needs a private ring of at least 2 stages.
-      bool planned = false;
-      // First choice: CTA pairs with resident weights (each CTA keeps half of the rows).
-      if (e->pair_mode) {
-        for (int qps = 2; qps >= 1 && !planned; --qps) {
-          const long long stage = round_up_ll(2LL * qps * rows * 16, 128);
-          const long long fixed = round_up_ll(wb / 2, 128);
-          const int want = std::max(1, std::min(p.nacc / 2, 4));
-          if (fixed + 2LL * want * stage > budget) continue;
-          const int ns = (int)std::min<long long>(kMaxStages, (budget - fixed) / stage);
-          p.pair = 1;
-          p.resident = 1;
-          p.qps = qps;
-          p.nissue = want;
-          p.spi = std::min(4, ns / want);
-          p.nstages = p.nissue * p.spi;
-          p.smem = 128 + kConvSmemHeader + (int)fixed + p.nstages * (int)stage;
-          planned = true;
-        }
-      }
-      for (int resident = 1; resident >= 0 && !planned; --resident) {
-        for (int qps = 2; qps >= 1 && !planned; --qps) {
-          const long long a_bytes = 2LL * qps * rows * 16;
-          const long long stage = round_up_ll(a_bytes + (resident ? 0 : qps * wq), 128);
-          const long long fixed = resident ? round_up_ll(wb, 128) : 0;
-          if (fixed + 2 * stage > budget) continue;
-          const int ns = (int)std::min<long long>(kMaxStages, (budget - fixed) / stage);
-          const int want = std::max(1, std::min(p.nacc / 2, 4));   // two accumulators per issuer
-          if (qps == 2 && ns < 2 * want && resident) {
-            // smaller steps may buy enough stages for all issuers: try qps = 1 first
-            const long long stage1 = round_up_ll(2LL * rows * 16, 128);
-            if ((budget - fixed) / stage1 >= 2 * want) continue;
-          }
-          int nissue = want;
-          while (nissue > 1 && ns < 2 * nissue) nissue >>= 1;
-          p.resident = resident;
-          p.qps = qps;
-          p.nissue = nissue;
-          p.spi = std::min(3, ns / nissue);
-          p.nstages = p.nissue * p.spi;
-          p.smem = 128 + kConvSmemHeader + (int)fixed + p.nstages * (int)stage;
-          planned = true;
-        }
-      }
-      if (!planned) return bail(C6_ERR_UNSUPPORTED, "a conv layer does not fit shared memory");
+      if (!plan_tc_layer(e, p, p.k * p.k, p.cin_p / 16, rows, 2, 2))
+        return bail(C6_ERR_UNSUPPORTED, "a conv layer does not fit shared memory");
       if ((rc = dev_alloc(e, &e->wconv[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
       if (p.pair && (rc = dev_alloc(e, &e->wconv_pair[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
       if ((rc = dev_alloc(e, &e->bias[l], (size_t)e->G * p.cout_p, true, nullptr))) return bail(rc, "");
+    }
+    {
+      // Direct stem for passes with few boards per weight set.  Input images: pitch wi >= n + k0/2 so that the
+      // pad columns serve both neighbours, n + k0/2 rows; taps are (filter row, 16-wide kx block).
+      const int k0 = e->lp[0].k, kh = k0 / 2;
+      e->sd_hx = (k0 + 15) / 16;
+      e->sd_wi = round_up(e->n + kh, 8);
+      e->sd_slots = e->sd_wi * (e->n + kh);
+      e->sd_halo_b = round_up(kh * e->sd_wi + kh, 8);
+      e->sd_halo_a = round_up(kh * e->sd_wi + 16 * e->sd_hx - 1 - kh + 8, 8);
+      e->sd_front = e->sd_halo_b;
+      e->sdp = e->lp[0];
+      if (const char* v = std::getenv("C6_STEM_DIRECT_MAX")) e->sd_max_boards = std::max(0, std::atoi(v));
+      e->sd_ok = e->sd_max_boards > 0 &&
+                 plan_tc_layer(e, e->sdp, k0 * e->sd_hx, 3, 128 + e->sd_halo_b + e->sd_halo_a, 1, 1) ? 1 : 0;
+      if (e->sd_ok) {
+        if ((rc = dev_alloc(e, &e->w_sd, (size_t)e->G * e->sdp.w_rows_per_group, true, nullptr))) return bail(rc, "");
+        if (e->sdp.pair && (rc = dev_alloc(e, &e->w_sd_pair, (size_t)e->G * e->sdp.w_rows_per_group, true, nullptr))) return bail(rc, "");
+      }
     }
     const int cl = e->lp[e->L - 1].cout_p;
     if ((rc = dev_alloc(e, &e->head_wp, (size_t)e->G * cl, true, nullptr))) return bail(rc, "");
@@ -848,11 +1052,24 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
   const LayerPlan& p = e->lp[layer];
   if (bf16) {
     if (layer == 0) {
-      const long long total = (long long)e->kc0 * e->ntot;
-      pack_stem_toeplitz_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-          w, e->wt + (size_t)group * e->kc0 * e->ntot, p.cout, p.k, e->n, p.cout_p, e->kc0, e->kc_short, e->ntot, e->nt,
-          e->stem_pair ? 2 : 1, e->f16);
-      C6_LAUNCHED(e, "pack_stem_toeplitz_kernel");
+      const size_t wn = (size_t)p.cout * 3 * p.k * p.k;
+      C6_CUDA(e, cudaMemcpyAsync(e->w0_raw + (size_t)group * wn, w, wn * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      e->wt_fresh[group] = 0;
+      if (e->wt) {
+        int rc = expand_toeplitz(e, group, st);
+        if (rc) return rc;
+      }
+      if (e->sd_ok) {
+        const long long rows = (long long)e->sdp.w_rows_per_group;
+        pack_stem_direct_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+            w, e->w_sd + (size_t)group * rows, p.cout, p.k, p.cout_p, e->sd_hx, 1, e->f16);
+        C6_LAUNCHED(e, "pack_stem_direct_weights_kernel");
+        if (e->sdp.pair) {
+          pack_stem_direct_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+              w, e->w_sd_pair + (size_t)group * rows, p.cout, p.k, p.cout_p, e->sd_hx, 2, e->f16);
+          C6_LAUNCHED(e, "pack_stem_direct_weights_kernel");
+        }
+      }
     } else {
       const long long total = (long long)p.w_rows_per_group;
       pack_conv_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
@@ -867,7 +1084,7 @@ int c6_set_weights(C6Engine* e, int group, int layer, const float* w, const floa
     copy_pad_f32_kernel<<<(p.cout_p + 127) / 128, 128, 0, st>>>(bias, e->bias[layer] + (size_t)group * p.cout_p,
                                                                  p.cout, p.cout_p);
     C6_LAUNCHED(e, "copy_pad_f32_kernel");
-    if (e->G == 1 && layer >= 1) {
+    if (e->G == 1) {
       e->h_bias[layer].assign(256, 0.f);
       C6_CUDA(e, cudaMemcpyAsync(e->h_bias[layer].data(), e->bias[layer], (size_t)p.cout_p * sizeof(float),
                                  cudaMemcpyDeviceToHost, st));
@@ -889,7 +1106,15 @@ int c6_reserve(C6Engine* e, int64_t boards) {
   if (boards <= 0) return fail(e, C6_ERR_ARG, "boards must be positive");
   C6_CUDA(e, cudaSetDevice(e->device));
   const long long per_pass = std::max<long long>(1, e->chunk / e->G);
-  return ensure_workspace(e, std::min<long long>(boards, per_pass));
+  const long long nb = std::min<long long>(boards, per_pass);
+  const bool direct = e->prec != C6_PREC_FP32 && e->sd_ok && boards <= e->sd_max_boards && boards <= per_pass;
+  if (e->prec != C6_PREC_FP32 && !e->wt && !direct) {
+    // calls of this size go through the stem GEMM: allocate its operand now (expanded by the first pass)
+    C6_CUDA(e, cudaDeviceSynchronize());
+    int rc = dev_alloc(e, &e->wt, (size_t)e->G * e->kc0 * e->ntot, true, nullptr);
+    if (rc) return rc;
+  }
+  return ensure_workspace(e, nb, direct);
 }
 
 int c6_forward(C6Engine* e, const void* x, int x_dtype, int64_t B, const uint8_t* orient, float* logits,

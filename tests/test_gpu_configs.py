@@ -125,8 +125,9 @@ def test_config3_grouped_16x512(cuda_device):
     rl, rv = TP.policy_value_forward(x[3, :32].cpu().double(), {k: v.double() for k, v in states[3].items()})
     assert (logits[3, :32].cpu().double() - rl).abs().max().item() < 0.12 * rl.std().item()
     # the training shape of the reference: many models, few tables each (G = 16 here, T = 4)
+    # (4 boards per model take the direct stem, 512 the stem GEMM: same sums in another order)
     l4, _ = eng.forward_grouped(x[:, :4].contiguous())
-    assert torch.equal(l4, logits[:, :4])
+    assert (l4 - logits[:, :4]).abs().max().item() < 0.05 * rl.std().item()
     assert eng.status() == 0 and single.status() == 0
 
 
@@ -141,14 +142,83 @@ def test_training_ensemble_128x4(cuda_device):
     eng = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, G, "bf16")
     for g in range(G):
         eng.load_state_dict(states[g], group=g)
+    # with 4 boards per model the first layer runs straight from each model's own filter: the engine holds
+    # about 1 MB per model (16-bit weights, the fp32 stem filter), not the 27 MB per model of the stem GEMM's
+    # expanded operand
+    assert eng.device_bytes < 150e6, eng.device_bytes
     x = torch.from_numpy(generate_planes(0, G * T)).reshape(G, T, 3, 19, 19).to(cuda_device)
     logits, value = eng.forward_grouped(x, want_value=True)
+    assert eng.device_bytes < 260e6, eng.device_bytes           # + activation workspace for 512 boards
     single = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, 1, "bf16")
     for g in (0, 63, 127):
         single.load_state_dict(states[g])
         l1, v1 = single.forward(x[g])
         assert torch.equal(l1, logits[g]) and torch.equal(v1, value[g])
+        rl, rv = TP.policy_value_forward(x[g].cpu().double(), {k: v.double() for k, v in states[g].items()})
+        assert (logits[g].cpu().double() - rl).abs().max().item() < 0.12 * rl.std().item()
+        assert (value[g].cpu().double() - rv).abs().max().item() < 3e-2
     assert eng.status() == 0 and single.status() == 0
+
+
+@pytest.mark.parametrize("precision", ["bf16", "f16"])
+def test_direct_stem_against_gemm_stem_and_oracle(cuda_device, precision, monkeypatch):
+    """Passes of at most 32 boards per weight set take the direct stem (implicit GEMM from the filter),
+    larger ones the Toeplitz stem GEMM.  Both against the oracle's first layer and against each other, with
+    per-board orientation and a third plane that is not constant; the expanded operand of the stem GEMM is
+    only allocated once a pass needs it."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.engine import Engine
+    from connect6_b200.model import PolicyValueNet
+    state = _state(42)
+    chans = PolicyValueNet.DEFAULT_CHANNELS
+    direct = Engine(cuda_device, 19, KERNELS, chans, 1, precision)
+    direct.load_state_dict(state)
+    monkeypatch.setenv("C6_STEM_DIRECT_MAX", "0")
+    gemm = Engine(cuda_device, 19, KERNELS, chans, 1, precision)
+    gemm.load_state_dict(state)
+    monkeypatch.delenv("C6_STEM_DIRECT_MAX")
+    x = torch.from_numpy(generate_planes(300, 29))
+    x[5:9, 2] += 0.25 * torch.randn(4, 19, 19).round()             # third plane not constant on some boards
+    orient = torch.from_numpy((np.arange(29) % 8).astype(np.uint8)).to(cuda_device)
+    tol = 1e-2 if precision == "bf16" else 2e-3
+    for od in (None, orient):
+        xv = x.numpy().copy()
+        if od is not None:
+            for b in range(29):
+                xv[b] = O.transform_boards(x.numpy()[b], *O.symmetry_for_phase(b % 8))
+        w, bias = state["convs.0.weight"].double(), state["convs.0.bias"].double()
+        want = torch.nn.functional.silu(torch.nn.functional.conv2d(torch.from_numpy(xv).double(), w, bias, padding=11))
+        a = direct.layer_output(x.to(cuda_device), 0, od).cpu().double()
+        b = gemm.layer_output(x.to(cuda_device), 0, od).cpu().double()
+        scale = want.abs().max().item()
+        assert (a - want).abs().max().item() / scale < tol
+        assert (b - want).abs().max().item() / scale < tol
+        assert (a - b).abs().max().item() / scale < tol
+    rl, rv = TP.policy_value_forward(x.double(), {k: v.double() for k, v in state.items()})
+    for eng in (direct, gemm):
+        logits, value = eng.forward(x.to(cuda_device))
+        assert (logits.cpu().double() - rl).abs().max().item() < 0.12 * rl.std().item()
+        assert (value.cpu().double() - rv).abs().max().item() < 3e-2
+    # a 33-board pass is the stem GEMM in both engines: bit-identical, and it is what allocates the operand
+    before = direct.device_bytes
+    x33 = torch.from_numpy(generate_planes(0, 33)).to(cuda_device)
+    l1, v1 = direct.forward(x33)
+    l2, v2 = gemm.forward(x33)
+    assert torch.equal(l1, l2) and torch.equal(v1, v2)
+    assert direct.device_bytes - before > 20e6
+    # raw int8 board input with a gather index through the direct stem equals the plane-fed step
+    from connect6_b200.selfplay import canonical_network_input
+    rng = np.random.default_rng(2)
+    boards = torch.from_numpy(rng.choice([-1, 0, 0, 1], size=(40, 19, 19)).astype(np.int8)).to(cuda_device)
+    player = torch.from_numpy(rng.choice([-1, 1], size=40).astype(np.int8)).to(cuda_device)
+    stones = torch.from_numpy(rng.choice([1, 2], size=40).astype(np.int8)).to(cuda_device)
+    index = torch.from_numpy(rng.permutation(40)[:17].astype(np.int64)).to(cuda_device)
+    planes = canonical_network_input(boards, player, stones)[index]
+    want = direct.forward_step(planes, seed=4, offset=1, want_logits=True)
+    got = direct.forward_step_boards(boards, player, stones, index, seed=4, offset=1, want_logits=True)
+    for w_, g_ in zip(want, got):
+        assert torch.equal(w_, g_)
+    assert direct.status() == 0 and gemm.status() == 0
 
 
 @pytest.mark.parametrize("channels,kernels", [((96, 32), (23, 3)), ((160, 64, 32), (23, 3, 3)), ((256, 32), (23, 1))])

@@ -175,8 +175,13 @@ def test_grouped_default_architecture(cuda_device):
         assert dl < 3e-2 and dl < 0.12 * rl.std().item(), f"group {g}: {dl}"
         assert (value[g].cpu().double() - rv).abs().max().item() < 3e-2
     # another T re-bases the groups inside the workspace: results must not depend on history
-    l2, _ = eng.forward_grouped(x[:, :5].contiguous().to(cuda_device))
-    assert torch.equal(l2, logits[:, :5])
+    l40, _ = eng.forward_grouped(x[:, :40].contiguous().to(cuda_device))
+    assert torch.equal(l40, logits[:, :40])
+    # 5 boards per model take the direct stem (same sums, another order): equal within a fraction of the bf16 noise
+    l5, _ = eng.forward_grouped(x[:, :5].contiguous().to(cuda_device))
+    assert (l5 - logits[:, :5]).abs().max().item() < 0.05 * logits.std().item()
+    l5b, _ = eng.forward_grouped(x[:, :5].contiguous().to(cuda_device))
+    assert torch.equal(l5, l5b)
     l3, _ = eng.forward_grouped(x.to(cuda_device))
     assert torch.equal(l3, logits)
     assert eng.status() == 0
@@ -307,7 +312,8 @@ def test_engine_rejects_misshapen_inputs_and_flags_stale_indices(cuda_device):
         eng.status()
     eng.clear_status()
     assert torch.equal(stale[3][0], good[3][0])                 # the valid entry is unaffected
-    assert torch.equal(stale[3][1], good[3][1]) and torch.equal(stale[3][2], good[3][1])   # skipped entries: an empty board
+    zero = eng.forward(torch.zeros(1, 3, 19, 19, device=dev))[0][0]
+    assert torch.equal(stale[3][1], zero) and torch.equal(stale[3][2], zero)   # skipped entries: all-zero planes
     assert eng.status() == 0
 
 

@@ -622,6 +622,83 @@ def run_workload(args) -> None:
         dist.destroy_process_group()
 
 
+def run_backward(args) -> None:
+    """--workload backward: the backward of one backbone layer (64 -> 96 channels, 3x3, the default net's layer 5)
+    on 8192 boards through conv_layer_backward: dX, dW and db from x, W, b and dL/dy.  Also times PyTorch
+    autograd (cuDNN, bf16 autocast) on the same layer and tensors as the library bar."""
+    import torch
+    from connect6_b200.train_ops import backward_status, conv_layer_backward
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, cin, cout, n = args.boards if args.boards != 2048 else BATCH, 64, 96, 19
+    g = torch.Generator(device=dev).manual_seed(1)
+    x = torch.nn.functional.silu(torch.randn(B, cin, n, n, device=dev, generator=g))
+    w = torch.randn(cout, cin, 3, 3, device=dev, generator=g) * (2.0 / (9 * cin)) ** 0.5
+    b = 0.1 * torch.randn(cout, device=dev, generator=g)
+    dy = torch.randn(B, cout, n, n, device=dev, generator=g) * 1e-3
+    for _ in range(max(3, args.warmup)):
+        conv_layer_backward(x, w, b, dy)
+    torch.cuda.synchronize(dev)
+    sampler = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.time()
+    e0.record()
+    for _ in range(args.steps):
+        dx, dw, db = conv_layer_backward(x, w, b, dy)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    t_end = time.time()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop(t_begin, t_end)
+    status = backward_status(x)
+    # library bar: autograd through cuDNN under bf16 autocast, the reference's own way (connect6/train.py:1047-1119)
+    xl = x.clone().requires_grad_(True)
+    conv = torch.nn.Conv2d(cin, cout, 3, padding=1).to(dev)
+    with torch.no_grad():
+        conv.weight.copy_(w)
+        conv.bias.copy_(b)
+
+    def lib_step():
+        conv.zero_grad(set_to_none=True)
+        xl.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = torch.nn.functional.silu(conv(xl))
+        y.backward(dy.to(y.dtype))
+
+    lib_ms = None
+    try:
+        for _ in range(3):
+            lib_step()
+        torch.cuda.synchronize(dev)
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0.record()
+        for _ in range(10):
+            lib_step()
+        l1.record()
+        torch.cuda.synchronize(dev)
+        lib_ms = l0.elapsed_time(l1) / 10
+    except Exception as exc:  # noqa: BLE001
+        lib_ms = f"{type(exc).__name__}: {exc}"[:160]
+    peaks, peak_kind = load_peaks()
+    peak, peak_source = pick_tensor_peak(peaks, peak_kind, clocks, ms * args.steps * 1e-3)
+    macs = 361 * 9 * cin * cout                     # per board and GEMM
+    algorithmic = 2 * 2 * macs * B                  # data gradient + weight gradient
+    executed = 2 * 3 * macs * B                     # + the forward recomputed for silu'
+    achieved = algorithmic / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "backward of one 64->96 3x3 layer, boards/s (dX, dW, db; bf16 operands, fp32 accumulate)",
+        "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": {"workload": f"conv_layer_backward, B = {B} boards, cin 64, cout 96, 19x19; fp32 NCHW "
+                                                    "tensors in and out (packing and unpacking inside the timed call)"},
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "whole operator (2 conv_tc_kernel launches + wgrad_tc_kernel + packing)",
+                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_source,
+                     "flop_algorithmic": algorithmic, "flop_executed": executed, "traffic": None},
+        "library_gpu_bar": {"ms_per_step": lib_ms, "what": "torch autograd of silu(conv2d) under bf16 autocast (cuDNN), forward + backward"},
+        "device_status": status}), flush=True)
+
+
 def run_small_case(args) -> None:
     """--workload small: a short, self-ending run for profilers -- `--steps` self-play inference steps of the
     default network on `--boards` generated boards (default 2048: the widest activations exceed L2 while
@@ -828,7 +905,7 @@ def main() -> None:
     ap.add_argument("--precision", default="bf16", choices=["bf16", "f16", "fp32"],
                     help="arithmetic mode of the engine for --workload cfg2: bf16 is the contract's benchmark; f16 the "
                          "fp16 tensor-core mode; fp32 the CUDA-core exact mode")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "ensemble", "selfplay", "small"],
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "ensemble", "selfplay", "small", "backward"],
                     help="cfg2 (default) is the contract's benchmark; cfg3-5 are BASELINE's other configurations; "
                          "ensemble is the reference's training shape of the historical opponents (128 models x 4 boards); "
                          "selfplay adds the environment step and bookkeeping around the network; small is a short "
@@ -839,6 +916,10 @@ def main() -> None:
         args.steps = 20 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else args.warmup
         run_reference(args)
+    elif args.workload == "backward":
+        args.steps = 50 if args.steps is None else args.steps
+        args.warmup = 3 if args.warmup is None else args.warmup
+        run_backward(args)
     elif args.workload == "small":
         args.steps = 2 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup

@@ -1,4 +1,4 @@
-"""ctypes binding of the engine's C ABI (include/c6_engine.h, include/c6_env.h, include/c6_debug.h).
+"""ctypes binding of the engine's C ABI (include/c6_engine.h, include/c6_env.h, include/c6_train.h, include/c6_debug.h).
 
 The library is loaded from the package directory (connect6_b200/libc6engine.so).  There is no
 fallback: if the library is missing or a call fails, an exception is raised.
@@ -86,6 +86,10 @@ SIGNATURES = {
     "c6_device_bytes": (_i64, [_vp]),
     "c6_last_error": (C.c_char_p, [_vp]),
     "c6_destroy": (_i, [_vp]),
+    "c6_conv_layer_backward_workspace_bytes": (_i64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, _i64]),
+    "c6_conv_layer_backward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _i64, _vp, _vp, _vp, _vp, _vp, _vp,
+                                    _vp, _vp, _i64, _vp]),
+    "c6_train_last_error": (C.c_char_p, []),
     "c6_env_step": (_i, [C.POINTER(C6EnvState), _vp, C.c_int32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "c6_env_reset": (_i, [C.POINTER(C6EnvState), _vp, _i64, _vp]),
     "c6_env_legal_mask": (_i, [C.POINTER(C6EnvState), _vp, _vp]),

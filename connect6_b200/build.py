@@ -1,6 +1,6 @@
 """Build recipe for the engine's shared library (in-tree, nvcc, sm_100a only).
 
-`python -m connect6_b200.build` compiles connect6_b200/csrc/c6_engine.cu and c6_env.cu into
+`python -m connect6_b200.build` compiles connect6_b200/csrc/c6_engine.cu (which includes the training operators) and c6_env.cu into
 connect6_b200/libc6engine.so.  The library links the CUDA runtime statically and has no
 dependency on libtorch, so it loads with ctypes from any process.  With C6_TIMED_BUILD=1 in the
 environment the clock-counter instantiations of the k x k kernel (include/c6_debug.h) are compiled
@@ -18,7 +18,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libc6engine.so"
 SOURCES = [CSRC / "c6_engine.cu", CSRC / "c6_env.cu"]
-HEADERS = sorted(CSRC.glob("*.cuh")) + sorted((PKG_DIR.parent / "include").glob("*.h"))
+HEADERS = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + sorted((PKG_DIR.parent / "include").glob("*.h"))
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -50,6 +50,7 @@ namespace c6 {
 struct ConvTcParams {
   const uint4* in;       // input planes  [cin/8][plane_rows] of 16-byte rows
   uint4* out;            // output planes [n/8][plane_rows]; unused when head != 0
+  const uint4* aux;      // kEpiDsilu only: planes of the same shape as `out`
   const uint4* w;        // packed weights, per group [cin/16][taps][2][n] rows
   const uint4* w_pair;   // pair mode: per group [2 halves][cin/16][taps][2][n/2] rows
   const float* bias;     // [G][n]
@@ -99,6 +100,7 @@ struct ConvTcParams {
   float c_wv[256];       // value head weights
 };
 
+constexpr int kEpiSilu = 0, kEpiLinear = 1, kEpiDsilu = 2;
 constexpr int kEpiTeams = 4;                   // epilogue teams of four warps (as many as the accumulator ring allows are used)
 constexpr int kEpiWarp0 = 5;                   // first epilogue warp
 constexpr int kProducer2Warp = kEpiWarp0 + 4 * kEpiTeams;
@@ -122,7 +124,14 @@ __host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 *
 // of 8-bit significands, range +-65504: stores saturate and the CTA reports kStatF16Range).
 // TIMED = true compiles the in-kernel clock counters in (p.wait_cycles); the plain instantiation
 // carries none of them: even untaken, they cost the epilogue 2-3 % on the narrow layers.
-template <int KS, bool PAIR, bool F16, bool TIMED>
+// EPI selects what the epilogue makes of z = accumulator + bias:
+//   kEpiSilu    y = silu(z)                      the forward layer
+//   kEpiLinear  y = z                            a plain convolution (the input gradient of a layer: its
+//                                                output gradient convolved with the flipped, transposed filter)
+//   kEpiDsilu   y = aux * silu'(z)               the layer's forward recomputed and turned straight into the
+//                                                gradient at the convolution output: aux holds dL/d(layer output)
+//                                                in the output's own plane layout
+template <int KS, bool PAIR, bool F16, bool TIMED, int EPI = 0>
 __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte aligned view of dynamic shared memory
@@ -542,7 +551,29 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
           const int u = u0 + b;
           if (u < nunits) {
             float y[16];
-            if (p.use_const) {
+            if (EPI != kEpiSilu) {
+              // h = z / 2 as in the forward; the backward operators always read the bias from shared memory
+              uint4 g[2];
+              if (EPI == kEpiDsilu) {
+                const uint4* aux_row = p.aux + (out_row - p.out);
+                g[0] = valid ? aux_row[(size_t)(u * 2) * p.plane_rows] : make_uint4(0, 0, 0, 0);
+                g[1] = valid ? aux_row[(size_t)(u * 2 + 1) * p.plane_rows] : make_uint4(0, 0, 0, 0);
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float h = fmaf(__uint_as_float(v[b][j]), 0.5f, s_bias[u * 16 + j]);
+                if (EPI == kEpiLinear) {
+                  y[j] = h + h;
+                } else {
+                  // silu'(z) = s + z s (1 - s) with s = sigmoid(z) = 0.5 + 0.5 tanh(z / 2)
+                  const float sg = fmaf(0.5f, tanh_approx(h), 0.5f);
+                  const float d = fmaf((h + h) * sg, 1.0f - sg, sg);
+                  const uint32_t w = reinterpret_cast<const uint32_t*>(g)[j >> 1];
+                  const float gy = __uint_as_float((j & 1) ? (w & 0xffff0000u) : (w << 16));   // bf16 -> fp32
+                  y[j] = gy * d;
+                }
+              }
+            } else if (p.use_const) {
 #pragma unroll
               for (int j4 = 0; j4 < 4; ++j4) {
                 const float4 hb = reinterpret_cast<const float4*>(p.c_hbias)[u * 4 + j4];

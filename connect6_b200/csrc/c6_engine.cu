@@ -21,37 +21,14 @@
 #include "c6_aux_kernels.cuh"
 #include "c6_conv_tc.cuh"
 #include "c6_fp32_kernels.cuh"
+#include "c6_host_plan.h"
 #include "c6_stem_tc.cuh"
 
 using namespace c6;
 
 namespace {
 
-constexpr int kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory per CTA on sm_100
-constexpr int kVersion = 10100;
-#ifdef C6_TIMED_BUILD
-constexpr bool kTimedBuild = true;    // the clock-counter instantiations of the k x k kernel are compiled in
-#else
-constexpr bool kTimedBuild = false;
-#endif
-
 thread_local std::string g_create_error = "";
-
-inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
-inline long long round_up_ll(long long v, long long m) { return (v + m - 1) / m * m; }
-inline int pow2_ceil(int v) {
-  int p = 32;
-  while (p < v) p <<= 1;
-  return p;
-}
-
-struct LayerPlan {
-  int k = 0, cin = 0, cout = 0, cin_p = 0, cout_p = 0;
-  // tensor-core plan (layers >= 1)
-  int resident = 0, nstages = 0, smem = 0, acc_stride = 0, tmem_cols = 0, nacc = 2, nissue = 1, spi = 2, qps = 2;
-  int pair = 0;                 // run as 2-CTA clusters (cta_group::2)
-  size_t w_rows_per_group = 0;  // 16-byte rows of packed weights per group
-};
 
 }  // namespace
 
@@ -202,36 +179,6 @@ ConvKernel conv_kernel_for(bool timed, bool pair, bool f16, int k) {
   return conv_kernel_pf<false>(pair, f16, k);
 }
 
-// Launch with optional 2-CTA clusters and optional programmatic dependent launch (the kernel then
-// orders itself behind its predecessor with grid_dep_wait(), so its prologue -- barrier setup, TMEM
-// allocation, resident weights -- overlaps the predecessor's tail).
-template <typename Params>
-void launch_chain(void (*kernel)(Params), unsigned grid_x, unsigned grid_y, unsigned threads, size_t smem,
-                  cudaStream_t st, bool cluster2, bool dependent, const Params& p) {
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(grid_x, grid_y);
-  cfg.blockDim = dim3(threads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attrs[2];
-  int n = 0;
-  if (cluster2) {
-    attrs[n].id = cudaLaunchAttributeClusterDimension;
-    attrs[n].val.clusterDim.x = 2;
-    attrs[n].val.clusterDim.y = 1;
-    attrs[n].val.clusterDim.z = 1;
-    ++n;
-  }
-  if (dependent) {
-    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attrs[n].val.programmaticStreamSerializationAllowed = 1;
-    ++n;
-  }
-  cfg.attrs = attrs;
-  cfg.numAttrs = (unsigned)n;
-  cudaLaunchKernelEx(&cfg, kernel, p);
-}
-
 template <typename T>
 int dev_alloc(C6Engine* e, T** p, size_t count, bool zero, long long* tally) {
   *p = nullptr;
@@ -337,14 +284,14 @@ int ensure_workspace(C6Engine* e, long long nb, bool direct) {
     e->last_group_pos = -1;
   }
   if (tc && direct && nb > e->xe_cap) {
-    // x-expanded input planes of the direct stem, for the largest pass that path takes
+    // x-expanded input planes of the direct stem
     if (e->xe) { e->ws_bytes -= (long long)(3 * e->xe_plane_rows * sizeof(uint4)); e->dev_bytes -= (long long)(3 * e->xe_plane_rows * sizeof(uint4)); }
     cudaFree(e->xe);
     e->xe = nullptr;
-    const Geometry gs = geometry_sd(e, e->sd_max_boards);
+    const Geometry gs = geometry_sd(e, nb);
     e->xe_plane_rows = (long long)e->sd_front + (long long)e->G * gs.group_pos + e->sd_halo_a + 128 + 16;
     if ((rc = dev_alloc(e, &e->xe, (size_t)3 * e->xe_plane_rows, true, &e->ws_bytes))) return rc;
-    e->xe_cap = e->sd_max_boards;
+    e->xe_cap = nb;
     e->sd_last_group_pos = -1;
   }
   if (tc && !direct && e->xk_cap < e->cap) {
@@ -364,63 +311,6 @@ int ensure_workspace(C6Engine* e, long long nb, bool direct) {
     e->xk_cap = e->cap;
   }
   return C6_OK;
-}
-
-// Pipeline shape of one tensor-core layer: `taps` MMAs per 16-channel group, `nq` groups, `rows` staged
-// rows per activation plane, `planes_per_q` planes per group (2; the direct stem: 1), steps of up to
-// `max_qps` groups.  Prefers resident weights and wide steps; every MMA issuer (up to one per two
-// accumulators, at most 4) needs a private ring of at least 2 stages.  False when nothing fits.
-bool plan_tc_layer(const C6Engine* e, LayerPlan& p, int taps, int nq, int rows, int planes_per_q, int max_qps) {
-  const int budget = kSmemLimit - 128 - kConvSmemHeader;
-  const long long wq = (long long)taps * 2 * p.cout_p * 16;
-  const long long wb = wq * nq;
-  p.w_rows_per_group = (size_t)(wb / 16);
-  p.acc_stride = pow2_ceil(p.cout_p);
-  p.nacc = std::min(kMaxAcc, 512 / p.acc_stride);  // 512 TMEM columns in total: 8, 4 or 2 accumulators
-  p.tmem_cols = p.nacc * p.acc_stride;
-  p.pair = 0;
-  const int want = std::max(1, std::min(p.nacc / 2, 4));   // two accumulators per issuer
-  // First choice: CTA pairs with resident weights (each CTA keeps half of the rows).
-  if (e->pair_mode) {
-    for (int qps = max_qps; qps >= 1; --qps) {
-      const long long stage = round_up_ll((long long)planes_per_q * qps * rows * 16, 128);
-      const long long fixed = round_up_ll(wb / 2, 128);
-      if (fixed + 2LL * want * stage > budget) continue;
-      const int ns = (int)std::min<long long>(kMaxStages, (budget - fixed) / stage);
-      p.pair = 1;
-      p.resident = 1;
-      p.qps = qps;
-      p.nissue = want;
-      p.spi = std::min(4, ns / want);
-      p.nstages = p.nissue * p.spi;
-      p.smem = 128 + kConvSmemHeader + (int)fixed + p.nstages * (int)stage;
-      return true;
-    }
-  }
-  for (int resident = 1; resident >= 0; --resident) {
-    for (int qps = max_qps; qps >= 1; --qps) {
-      const long long a_bytes = (long long)planes_per_q * qps * rows * 16;
-      const long long stage = round_up_ll(a_bytes + (resident ? 0 : qps * wq), 128);
-      const long long fixed = resident ? round_up_ll(wb, 128) : 0;
-      if (fixed + 2 * stage > budget) continue;
-      const int ns = (int)std::min<long long>(kMaxStages, (budget - fixed) / stage);
-      if (qps == 2 && ns < 2 * want && resident) {
-        // smaller steps may buy enough stages for all issuers: try qps = 1 first
-        const long long stage1 = round_up_ll((long long)planes_per_q * rows * 16, 128);
-        if ((budget - fixed) / stage1 >= 2 * want) continue;
-      }
-      int nissue = want;
-      while (nissue > 1 && ns < 2 * nissue) nissue >>= 1;
-      p.resident = resident;
-      p.qps = qps;
-      p.nissue = nissue;
-      p.spi = std::min(3, ns / nissue);
-      p.nstages = p.nissue * p.spi;
-      p.smem = 128 + kConvSmemHeader + (int)fixed + p.nstages * (int)stage;
-      return true;
-    }
-  }
-  return false;
 }
 
 int fp32_cit(const LayerPlan& l) { return l.k <= 5 ? std::min(l.cin, 16) : std::min(l.cin, 4); }
@@ -967,7 +857,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     const int rows = conv_stage_rows(e->halo_rows);
     for (int l = 1; l < e->L; ++l) {
       LayerPlan& p = e->lp[l];
-      if (!plan_tc_layer(e, p, p.k * p.k, p.cin_p / 16, rows, 2, 2))
+      if (!plan_tc_layer(e->pair_mode, p, p.k * p.k, p.cin_p / 16, rows, 2, 2))
         return bail(C6_ERR_UNSUPPORTED, "a conv layer does not fit shared memory");
       if ((rc = dev_alloc(e, &e->wconv[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
       if (p.pair && (rc = dev_alloc(e, &e->wconv_pair[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
@@ -986,7 +876,7 @@ int c6_create(const C6Desc* d, C6Engine** out) {
       e->sdp = e->lp[0];
       if (const char* v = std::getenv("C6_STEM_DIRECT_MAX")) e->sd_max_boards = std::max(0, std::atoi(v));
       e->sd_ok = e->sd_max_boards > 0 &&
-                 plan_tc_layer(e, e->sdp, k0 * e->sd_hx, 3, 128 + e->sd_halo_b + e->sd_halo_a, 1, 1) ? 1 : 0;
+                 plan_tc_layer(e->pair_mode, e->sdp, k0 * e->sd_hx, 3, 128 + e->sd_halo_b + e->sd_halo_a, 1, 1) ? 1 : 0;
       if (e->sd_ok) {
         if ((rc = dev_alloc(e, &e->w_sd, (size_t)e->G * e->sdp.w_rows_per_group, true, nullptr))) return bail(rc, "");
         if (e->sdp.pair && (rc = dev_alloc(e, &e->w_sd_pair, (size_t)e->G * e->sdp.w_rows_per_group, true, nullptr))) return bail(rc, "");
@@ -1452,3 +1342,6 @@ int64_t c6_launch_count(const C6Engine* e) { return e ? e->launches : 0; }
 int64_t c6_device_bytes(const C6Engine* e) { return e ? e->dev_bytes : 0; }
 
 }  // extern "C"
+
+// the training-side operators (include/c6_train.h) share this translation unit's kernels
+#include "c6_train_ops.cuh"

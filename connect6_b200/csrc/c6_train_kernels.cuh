@@ -1,0 +1,130 @@
+// Memory-bound helpers of the training-side operators: NCHW fp32 tensors <-> the forward kernels'
+// channel-chunk planes, the flipped / transposed filter of the input-gradient convolution, and the bias
+// gradient (column sums of the gradient planes).
+#pragma once
+
+#include "c6_common.cuh"
+
+namespace c6 {
+
+// x [B, C, n, n] fp32 -> bf16 planes [C_p/8][plane_rows] of 16-byte rows (8 channels of one position), position
+// (b, r, c) at row front + b*slots + r*wp + c.  EVERY slot of every board image is written: cells get their
+// values, pad slots and channels beyond C get zeros, so the planes need no clearing between calls.
+// Grid: ceil(B*slots*(C_p/8) / 256); one thread per (board, plane, slot).
+__global__ void pack_nchw_planes_kernel(const float* __restrict__ x, uint4* __restrict__ planes, long long plane_rows,
+                                        int front, int slots, int wp, int n, int C, int C_p, long long B) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int nq = C_p / 8;
+  if (idx >= B * slots * nq) return;
+  const int slot = (int)(idx % slots);
+  const int q = (int)((idx / slots) % nq);
+  const long long b = idx / ((long long)slots * nq);
+  const int r = slot / wp, c = slot - r * wp;
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int ch = q * 8 + e;
+    v[e] = (r < n && c < n && ch < C) ? x[((b * C + ch) * n + r) * n + c] : 0.f;
+  }
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  planes[(size_t)q * plane_rows + front + b * slots + slot] = o;
+}
+
+// bf16 planes -> fp32 [B, C, n, n] (cells only)
+__global__ void unpack_planes_nchw_kernel(const uint4* __restrict__ planes, long long plane_rows, int front, int slots,
+                                          int wp, int n, int C, long long B, float* __restrict__ out) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cells = n * n;
+  if (idx >= B * C * cells) return;
+  const int cell = (int)(idx % cells);
+  const int ch = (int)((idx / cells) % C);
+  const long long b = idx / ((long long)cells * C);
+  const int r = cell / n, c = cell - r * n;
+  const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(planes + (size_t)(ch >> 3) * plane_rows + front +
+                                                                      b * slots + r * wp + c);
+  out[idx] = __bfloat162float(row[ch & 7]);
+}
+
+// Filter of the input-gradient convolution in the k x k kernel's weight layout: dX = conv(dPre, W') with
+// W'[ci][co][ky][kx] = W[co][ci][k-1-ky][k-1-kx] (W is the layer's [Cout, Cin, k, k] filter), i.e. a layer with
+// Cout input channels and Cin output channels.  Rows [q][tap][j][ci] of 8 bf16 (element e: input channel
+// (2q+j)*8+e of the gradient = an output channel of the layer); halves = 2 splits the rows for CTA pairs as
+// [half][q][tap][j][ci % (cin_p/2)].
+__global__ void pack_dgrad_weights_kernel(const float* __restrict__ w, uint4* __restrict__ out, int cout, int cin,
+                                          int kside, int cout_p, int cin_p, int halves) {
+  const int taps = kside * kside, nh = cin_p / halves;
+  const long long total = (long long)(cout_p / 16) * taps * 2 * cin_p;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int col = (int)(idx % nh);
+  long long r = idx / nh;
+  const int j = (int)(r % 2);
+  r /= 2;
+  const int tap = (int)(r % taps);
+  r /= taps;
+  const int q = (int)(r % (cout_p / 16));
+  const int half = (int)(r / (cout_p / 16));
+  const int ci = half * nh + col;              // output channel of this convolution = input channel of the layer
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int co = (2 * q + j) * 8 + e;        // its input channel = output channel of the layer
+    v[e] = (co < cout && ci < cin) ? w[((size_t)co * cin + ci) * taps + (taps - 1 - tap)] : 0.f;
+  }
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  out[idx] = o;
+}
+
+// Bias gradient, first pass: block (q, s) sums the rows [s*chunk, (s+1)*chunk) of plane q for its 8 channels
+// (fp32) into partial[q][s][8].  Pad slots are zero, so every row may be summed.
+constexpr int kColsumThreads = 256;
+__global__ void __launch_bounds__(kColsumThreads) colsum_planes_kernel(const uint4* __restrict__ planes, long long plane_rows,
+                                                                       long long row0, long long nrows, int nslices,
+                                                                       float* __restrict__ partial) {
+  const int q = blockIdx.x, s = blockIdx.y;
+  const long long chunk = (nrows + nslices - 1) / nslices;
+  const long long lo = row0 + s * chunk, hi = min(row0 + nrows, lo + chunk);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (long long r = lo + threadIdx.x; r < hi; r += kColsumThreads) {
+    const uint4 v = planes[(size_t)q * plane_rows + r];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      acc[2 * k] += __uint_as_float(w[k] << 16);
+      acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+    }
+  }
+  __shared__ float red[kColsumThreads / 32][8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float v = acc[e];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5][e] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    float v = 0.f;
+    for (int wv = 0; wv < kColsumThreads / 32; ++wv) v += red[wv][threadIdx.x];
+    partial[((size_t)q * nslices + s) * 8 + threadIdx.x] = v;
+  }
+}
+
+// second pass: db[ch] = sum over slices, in slice order
+__global__ void colsum_finish_kernel(const float* __restrict__ partial, int nslices, int C, float* __restrict__ db) {
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= C) return;
+  float v = 0.f;
+  for (int s = 0; s < nslices; ++s) v += partial[((size_t)(ch >> 3) * nslices + s) * 8 + (ch & 7)];
+  db[ch] = v;
+}
+
+}  // namespace c6

@@ -1,0 +1,294 @@
+// Training-side operators (include/c6_train.h): the backward pass of one backbone layer.  Host code,
+// compiled as part of c6_engine.cu (one translation unit: the helper kernels are shared).
+//
+// Launch sequence of c6_conv_layer_backward on the caller's stream:
+//   pack filter (forward layout and the flipped / transposed one), pack x and dy into channel-chunk planes
+//   -> conv_tc_kernel<kEpiDsilu>: dPre = dy * silu'(conv(x, W) + b)      (forward recomputed on tensor cores)
+//   -> column sums of dPre                                              = db
+//   -> conv_tc_kernel<kEpiLinear>: dX = conv(dPre, W flipped/transposed)   -> unpack to NCHW
+//   -> wgrad_tc_kernel + wgrad_reduce_kernel                            = dW
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/c6_train.h"
+#include "c6_aux_kernels.cuh"
+#include "c6_conv_tc.cuh"
+#include "c6_host_plan.h"
+#include "c6_train_kernels.cuh"
+#include "c6_wgrad_tc.cuh"
+
+using namespace c6;
+
+namespace {
+
+thread_local std::string g_train_error = "";
+
+int tfail(int code, const std::string& msg) {
+  g_train_error = msg;
+  return code;
+}
+
+#define C6T_CUDA(call)                                                                         \
+  do {                                                                                         \
+    cudaError_t _st = (call);                                                                  \
+    if (_st != cudaSuccess) return tfail(C6_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(_st)); \
+  } while (0)
+
+#define C6T_LAUNCHED(name)                                                                     \
+  do {                                                                                         \
+    cudaError_t _st = cudaGetLastError();                                                      \
+    if (_st != cudaSuccess) return tfail(C6_ERR_CUDA, std::string("launch ") + name + ": " + cudaGetErrorString(_st)); \
+  } while (0)
+
+constexpr int kColsumSlices = 64;
+
+// Shape-derived layout of one call: the forward kernels' padded linear board geometry and the carve-up of
+// the workspace.
+struct BackwardLayout {
+  bool ok = false;
+  int n = 0, k = 0, cin = 0, cout = 0, cin_p = 0, cout_p = 0;
+  int wp = 0, slots = 0, halo_rows = 0, front = 0, tiles = 0, tiles_per_board = 0;
+  long long B = 0, total_pos = 0, plane_rows = 0;
+  LayerPlan fwd, dgrad;           // pipeline plans of the two conv_tc_kernel launches
+  int wg_taps_per_cta = 0, wg_groups = 0, wg_slabs = 0, wg_stages = 0, wg_smem = 0;
+  // workspace offsets in bytes
+  size_t off_bias = 0, off_zero = 0, off_wf = 0, off_wf_pair = 0, off_wd = 0, off_wd_pair = 0, off_x = 0, off_dy = 0,
+         off_dpre = 0, off_dx = 0, off_partial = 0, off_colsum = 0, total = 0;
+};
+
+BackwardLayout make_layout(int n, int k, int cin, int cout, long long B, int sms) {
+  BackwardLayout L;
+  if (n < 1 || n > 32 || k != 3 || cin < 1 || cout < 1 || B < 1) return L;
+  L.n = n; L.k = k; L.cin = cin; L.cout = cout; L.B = B;
+  L.cin_p = round_up(cin, 32);
+  L.cout_p = round_up(cout, 32);
+  if (L.cin_p > 128 || L.cout_p > 128) return L;
+  const int pad = k / 2;
+  L.wp = n + pad;
+  L.slots = L.wp * L.wp;
+  L.halo_rows = round_up(pad * L.wp + pad, 8);
+  L.front = L.halo_rows;
+  const int used = (n - 1) * L.wp + n, tpb = (used + 127) / 128;
+  L.tiles_per_board = tpb * 128 < L.slots ? tpb : 0;
+  long long tiles = L.tiles_per_board ? B * tpb : (B * L.slots + 127) / 128;
+  tiles += tiles & 1;                                      // CTA pairs take tiles two at a time
+  if (tiles > 0x7fffffffLL / 128) return L;
+  L.tiles = (int)tiles;
+  L.total_pos = L.tiles_per_board ? round_up_ll((long long)((tiles + tpb - 1) / tpb) * L.slots, 128) : tiles * 128;
+  L.plane_rows = (long long)L.front + L.total_pos + L.halo_rows + 128;
+  const int rows = conv_stage_rows(L.halo_rows);
+  L.fwd.k = k; L.fwd.cin = cin; L.fwd.cout = cout; L.fwd.cin_p = L.cin_p; L.fwd.cout_p = L.cout_p;
+  L.dgrad.k = k; L.dgrad.cin = cout; L.dgrad.cout = cin; L.dgrad.cin_p = L.cout_p; L.dgrad.cout_p = L.cin_p;
+  if (!plan_tc_layer(sms >= 2, L.fwd, k * k, L.cin_p / 16, rows, 2, 2)) return L;
+  if (!plan_tc_layer(sms >= 2, L.dgrad, k * k, L.cout_p / 16, rows, 2, 2)) return L;
+  L.wg_taps_per_cta = std::min(k * k, 512 / L.cin_p);
+  L.wg_groups = (k * k + L.wg_taps_per_cta - 1) / L.wg_taps_per_cta;
+  L.wg_slabs = std::max(1, sms / L.wg_groups);
+  const int stage = wgrad_stage_bytes(L.cin_p, L.cout_p, L.halo_rows);
+  // 32 KB of slack behind the last stage: the M = 128 operand descriptor addresses 16 channel groups even
+  // when fewer gradient planes exist (those accumulator rows are never read)
+  L.wg_stages = std::min(kWgradMaxStages, (kSmemLimit - 128 - kWgradSmemHeader - 32768) / stage);
+  if (L.wg_stages < 2) return L;
+  L.wg_smem = 128 + kWgradSmemHeader + L.wg_stages * stage + 32768;
+  auto take = [&](size_t bytes) { size_t o = L.total; L.total += (bytes + 255) & ~(size_t)255; return o; };
+  take(256);                                                // status word
+  L.off_bias = take((size_t)L.cout_p * 4);
+  L.off_zero = take((size_t)L.cin_p * 4);
+  L.off_wf = take(L.fwd.w_rows_per_group * 16);
+  L.off_wf_pair = take(L.fwd.w_rows_per_group * 16);
+  L.off_wd = take(L.dgrad.w_rows_per_group * 16);
+  L.off_wd_pair = take(L.dgrad.w_rows_per_group * 16);
+  L.off_x = take((size_t)(L.cin_p / 8) * L.plane_rows * 16);
+  L.off_dy = take((size_t)(L.cout_p / 8) * L.plane_rows * 16);
+  L.off_dpre = take((size_t)(L.cout_p / 8) * L.plane_rows * 16);
+  L.off_dx = take((size_t)(L.cin_p / 8) * L.plane_rows * 16);
+  L.off_partial = take((size_t)L.wg_slabs * k * k * 128 * L.cin_p * 4);
+  L.off_colsum = take((size_t)(L.cout_p / 8) * kColsumSlices * 8 * 4);
+  L.ok = true;
+  return L;
+}
+
+using ConvKernel = void (*)(ConvTcParams);
+
+int launch_conv(const BackwardLayout& L, const LayerPlan& lp, int epi, const uint4* in, uint4* out, const uint4* aux,
+                const uint4* w, const uint4* w_pair, const float* bias, int* status, int sms, cudaStream_t st) {
+  ConvTcParams p{};
+  p.in = in;
+  p.out = out;
+  p.aux = aux;
+  p.w = w;
+  p.w_pair = w_pair;
+  p.bias = bias;
+  p.status = status;
+  p.plane_rows = L.plane_rows;
+  p.in_plane_rows = L.plane_rows;
+  p.front = L.front;
+  p.halo_rows = L.halo_rows;
+  p.halo_after = L.halo_rows;
+  p.cin = lp.cin_p;
+  p.n = lp.cout_p;
+  p.kside = lp.k;
+  p.ntaps = lp.k * lp.k;
+  p.planes_step = 2 * lp.qps;
+  p.wp = L.wp;
+  p.slots = L.slots;
+  p.bsize = L.n;
+  p.nboards = (int)L.B;
+  p.tiles_per_group = L.tiles;
+  p.tiles_per_board = L.tiles_per_board;
+  p.group_pos = (int)L.total_pos;
+  p.ctas_per_group = std::max(1, std::min(sms, L.tiles));
+  if (lp.pair) p.ctas_per_group = std::max(2, p.ctas_per_group & ~1);
+  p.resident = lp.resident;
+  p.nstages = lp.nstages;
+  p.nissue = lp.nissue;
+  p.spi = lp.spi;
+  p.qps = lp.qps;
+  p.acc_stride = lp.acc_stride;
+  p.nacc = lp.nacc;
+  p.tmem_cols = lp.tmem_cols;
+  ConvKernel kernel = lp.pair ? (epi == kEpiDsilu ? conv_tc_kernel<3, true, false, false, kEpiDsilu>
+                                                  : conv_tc_kernel<3, true, false, false, kEpiLinear>)
+                              : (epi == kEpiDsilu ? conv_tc_kernel<3, false, false, false, kEpiDsilu>
+                                                  : conv_tc_kernel<3, false, false, false, kEpiLinear>);
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+    return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+  launch_chain(kernel, (unsigned)p.ctas_per_group, 1u, kConvThreads, (size_t)lp.smem, st, lp.pair != 0, false, p);
+  C6T_LAUNCHED("conv_tc_kernel (backward)");
+  return C6_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* c6_train_last_error(void) { return g_train_error.c_str(); }
+
+int64_t c6_conv_layer_backward_workspace_bytes(int32_t board_size, int32_t kside, int32_t cin, int32_t cout, int64_t B) {
+  const BackwardLayout L = make_layout(board_size, kside, cin, cout, B, 148);
+  return L.ok ? (int64_t)L.total : 0;
+}
+
+int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, int32_t cin, int32_t cout, int64_t B,
+                           const float* x, const float* w, const float* bias, const float* dy, float* dx, float* dw,
+                           float* db, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (B < 0) return tfail(C6_ERR_ARG, "negative board count");
+  if (!x || !w || !dy || !dw || !db || !workspace) return tfail(C6_ERR_ARG, "null pointer");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return tfail(C6_ERR_ARG, "workspace must be 256-byte aligned");
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev)
+    return tfail(C6_ERR_CUDA, "no such CUDA device (this operator has no CPU path)");
+  C6T_CUDA(cudaSetDevice(device));
+  int sms = 0, major = 0;
+  C6T_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  C6T_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  if (major != 10) return tfail(C6_ERR_UNSUPPORTED, "the backward operators need an sm_100 GPU (tcgen05 tensor cores)");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (B == 0) {
+    C6T_CUDA(cudaMemsetAsync(dw, 0, (size_t)cout * cin * kside * kside * sizeof(float), st));
+    C6T_CUDA(cudaMemsetAsync(db, 0, (size_t)cout * sizeof(float), st));
+    return C6_OK;
+  }
+  // the workspace layout must not depend on the device: always planned for 148 SMs, launched on what is there
+  const BackwardLayout L = make_layout(board_size, kside, cin, cout, B, 148);
+  if (!L.ok) return tfail(C6_ERR_UNSUPPORTED, "c6_conv_layer_backward supports k = 3, board_size <= 32, cin and cout <= 128");
+  if (workspace_bytes < (int64_t)L.total) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "workspace of %lld bytes is smaller than the %zu this shape needs", (long long)workspace_bytes, L.total);
+    return tfail(C6_ERR_ARG, buf);
+  }
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  int* status = reinterpret_cast<int*>(ws);
+  float* bias_f = reinterpret_cast<float*>(ws + L.off_bias);
+  float* zero_f = reinterpret_cast<float*>(ws + L.off_zero);
+  uint4* wf = reinterpret_cast<uint4*>(ws + L.off_wf);
+  uint4* wf_pair = reinterpret_cast<uint4*>(ws + L.off_wf_pair);
+  uint4* wd = reinterpret_cast<uint4*>(ws + L.off_wd);
+  uint4* wd_pair = reinterpret_cast<uint4*>(ws + L.off_wd_pair);
+  uint4* xp = reinterpret_cast<uint4*>(ws + L.off_x);
+  uint4* dyp = reinterpret_cast<uint4*>(ws + L.off_dy);
+  uint4* dpre = reinterpret_cast<uint4*>(ws + L.off_dpre);
+  uint4* dxp = reinterpret_cast<uint4*>(ws + L.off_dx);
+  float* partial = reinterpret_cast<float*>(ws + L.off_partial);
+  float* colsum = reinterpret_cast<float*>(ws + L.off_colsum);
+  const int taps = kside * kside;
+
+  // operands
+  copy_pad_f32_kernel<<<(L.cout_p + 127) / 128, 128, 0, st>>>(bias, bias_f, cout, L.cout_p);
+  C6T_LAUNCHED("copy_pad_f32_kernel");
+  {
+    const long long rows = (long long)L.fwd.w_rows_per_group;
+    pack_conv_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(w, wf, cout, cin, kside, L.cout_p, L.cin_p, 0);
+    C6T_LAUNCHED("pack_conv_weights_kernel");
+    pack_conv_weights_pair_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(w, wf_pair, cout, cin, kside, L.cout_p, L.cin_p, 0);
+    C6T_LAUNCHED("pack_conv_weights_pair_kernel");
+    const long long drows = (long long)L.dgrad.w_rows_per_group;
+    pack_dgrad_weights_kernel<<<(unsigned)((drows + 255) / 256), 256, 0, st>>>(w, wd, cout, cin, kside, L.cout_p, L.cin_p, 1);
+    C6T_LAUNCHED("pack_dgrad_weights_kernel");
+    pack_dgrad_weights_kernel<<<(unsigned)((drows + 255) / 256), 256, 0, st>>>(w, wd_pair, cout, cin, kside, L.cout_p, L.cin_p, 2);
+    C6T_LAUNCHED("pack_dgrad_weights_kernel");
+  }
+  {
+    const long long tx = B * L.slots * (L.cin_p / 8), ty = B * L.slots * (L.cout_p / 8);
+    pack_nchw_planes_kernel<<<(unsigned)((tx + 255) / 256), 256, 0, st>>>(x, xp, L.plane_rows, L.front, L.slots, L.wp, L.n, cin, L.cin_p, B);
+    C6T_LAUNCHED("pack_nchw_planes_kernel");
+    pack_nchw_planes_kernel<<<(unsigned)((ty + 255) / 256), 256, 0, st>>>(dy, dyp, L.plane_rows, L.front, L.slots, L.wp, L.n, cout, L.cout_p, B);
+    C6T_LAUNCHED("pack_nchw_planes_kernel");
+  }
+  // dPre = dy * silu'(conv(x, W) + b)
+  int rc = launch_conv(L, L.fwd, kEpiDsilu, xp, dpre, dyp, wf, wf_pair, bias_f, status, sms, st);
+  if (rc) return rc;
+  // db
+  colsum_planes_kernel<<<dim3((unsigned)(L.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre, L.plane_rows, L.front,
+                                                                                                  L.total_pos, kColsumSlices, colsum);
+  C6T_LAUNCHED("colsum_planes_kernel");
+  colsum_finish_kernel<<<(cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, cout, db);
+  C6T_LAUNCHED("colsum_finish_kernel");
+  // dX
+  if (dx) {
+    rc = launch_conv(L, L.dgrad, kEpiLinear, dpre, dxp, nullptr, wd, wd_pair, zero_f, status, sms, st);
+    if (rc) return rc;
+    const long long total = B * cin * L.n * L.n;
+    unpack_planes_nchw_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(dxp, L.plane_rows, L.front, L.slots, L.wp, L.n, cin, B, dx);
+    C6T_LAUNCHED("unpack_planes_nchw_kernel");
+  }
+  // dW
+  {
+    WgradParams p{};
+    p.x = xp;
+    p.dpre = dpre;
+    p.partial = partial;
+    p.status = status;
+    p.plane_rows = L.plane_rows;
+    p.front = L.front;
+    p.halo_rows = L.halo_rows;
+    p.cin = L.cin_p;
+    p.cout = L.cout_p;
+    p.kside = kside;
+    p.wp = L.wp;
+    p.slots = L.slots;
+    p.tiles_per_board = L.tiles_per_board;
+    p.ntiles = L.tiles;
+    p.ntaps = taps;
+    p.taps_per_cta = L.wg_taps_per_cta;
+    p.ngroups = L.wg_groups;
+    p.nslabs = L.wg_slabs;          // planned for 148 SMs: the partial-sum buffer is sized for it
+    p.nstages = L.wg_stages;
+    if (cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+      return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+    wgrad_tc_kernel<<<(unsigned)(p.ngroups * p.nslabs), kWgradThreads, (size_t)L.wg_smem, st>>>(p);
+    C6T_LAUNCHED("wgrad_tc_kernel");
+    const long long total = (long long)cout * cin * taps;
+    wgrad_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, dw, p.nslabs, taps, L.cin_p, cin, cout);
+    C6T_LAUNCHED("wgrad_reduce_kernel");
+  }
+  return C6_OK;
+}
+
+}  // extern "C"

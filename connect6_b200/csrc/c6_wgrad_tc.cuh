@@ -1,0 +1,236 @@
+// Weight gradient of one k x k "same" convolution layer on tcgen05 tensor cores (the backward of
+// connect6/model.py:104-106 as PyTorch's autograd computes it inside the PPO update,
+// connect6/train.py:1047-1119):
+//     dW[co, ci, tap] = sum over positions p of  dPre[p, co] * x[p + shift(tap), ci]
+// with dPre = dL/d(conv output) and shift(tap) = dy * Wp + dx in the padded linear board layout of the
+// forward kernels (pad slots of both operands are zero, so the sum may run over every slot).
+//
+// GEMM view: M = Cout (one 128-row block), N = Cin, K = positions.  Both operands are read straight from
+// the forward layout -- channel-chunk planes whose 16-byte rows hold 8 channels of one position -- as
+// MN-major no-swizzle operands: 8 consecutive positions of 8 channels are 128 contiguous bytes (a core
+// matrix), the next 8 positions follow 128 bytes later (leading byte offset), the next 8 channels one
+// plane later (stride byte offset).  A filter tap is again a pure change of the B descriptor's start
+// address, and each tap accumulates into its own TMEM columns.
+//
+// Work split: a CTA owns a group of taps (as many as fit 512 TMEM columns: floor(512 / Cin), at most
+// k*k) and a contiguous slab of 128-position K tiles; it writes its fp32 partial sums
+// [slab][tap][128][Cin] to global memory and a second kernel adds the slabs up in a fixed order
+// (no atomics: results are reproducible).
+// CTA = 192 threads: warp 0 stages operands with bulk copies, warp 1 issues the MMAs and owns TMEM,
+// warps 2-5 drain the accumulators at the end.  Every wait is bounded.
+#pragma once
+
+#include "c6_common.cuh"
+#include "c6_tc.cuh"
+
+namespace c6 {
+
+struct WgradParams {
+  const uint4* x;       // layer input planes  [cin/8][plane_rows]
+  const uint4* dpre;    // gradient planes     [cout/8][plane_rows]
+  float* partial;       // [nslabs][ntaps][128][cin] fp32
+  int* status;
+  long long plane_rows;
+  int front;            // plane row of position 0
+  int halo_rows;        // rows staged before and after the 128 tile rows of x (multiple of 8, >= kside/2 * (wp + 1))
+  int cin, cout;        // padded to multiples of 32; cout <= 128, cin <= 128
+  int kside, wp;
+  int slots, tiles_per_board, ntiles;   // K tiles of 128 positions, laid out as in the forward kernels
+  int ntaps;            // kside * kside
+  int taps_per_cta;     // taps of one tap group
+  int ngroups, nslabs;  // grid = ngroups * nslabs; CTA b: group b % ngroups, slab b / ngroups
+  int nstages;
+};
+
+constexpr int kWgradThreads = 192;
+constexpr int kWgradSmemHeader = 1024;
+constexpr int kWgradMaxStages = 8;
+
+// Instruction descriptor: D = fp32, A = B = bf16, both MN-major (bits 15 and 16 set).
+__host__ __device__ __forceinline__ uint32_t make_idesc_bf16_mn(int m, int n) {
+  return tc::make_idesc_bf16(m, n) | (1u << 15) | (1u << 16);
+}
+
+__host__ __device__ inline int wgrad_stage_bytes(int cin, int cout, int halo_rows) {
+  return (cout / 8) * 128 * 16 + (cin / 8) * (128 + 2 * halo_rows) * 16;
+}
+
+__global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);   // [0,8) full, [8,16) empty, 16 accumulators ready
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 260);
+  uint8_t* s_stage = smem + kWgradSmemHeader;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = blockIdx.x % p.ngroups, slab = blockIdx.x / p.ngroups;
+  const int tap0 = group * p.taps_per_cta;
+  const int ntap = min(p.taps_per_cta, p.ntaps - tap0);
+  const int t_begin = (int)(((long long)p.ntiles * slab) / p.nslabs);
+  const int t_end = (int)(((long long)p.ntiles * (slab + 1)) / p.nslabs);
+  const int xrows = 128 + 2 * p.halo_rows;
+  const uint32_t a_bytes = (uint32_t)(p.cout / 8) * 128u * 16u;
+  const uint32_t b_bytes = (uint32_t)(p.cin / 8) * xrows * 16u;
+  const uint32_t stage_bytes = a_bytes + b_bytes;     // multiples of 128
+  const uint32_t bar0 = tc::smem_u32(bars);
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (8 + s); };
+  const uint32_t bar_done = bar0 + 8u * 16;
+  auto tile_pos = [&](int tile) {
+    return p.tiles_per_board ? (tile / p.tiles_per_board) * p.slots + (tile % p.tiles_per_board) * 128 : tile * 128;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kWgradMaxStages; ++s) {
+      tc::mbar_init(bar_full(s), 1);
+      tc::mbar_init(bar_empty(s), 1);
+    }
+    tc::mbar_init(bar_done, 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(tmem_slot), 512u);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    // lane i < cout/8 copies gradient plane i (the tile's 128 rows), the next cin/8 lanes one input plane
+    // each (the tile's rows plus the halo on both sides)
+    const int na = p.cout / 8, nb = p.cin / 8;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = t_begin; tile < t_end && ok; ++tile) {
+      int got = 1;
+      if (lane == 0) {
+        got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, 40) ? 1 : 0;
+        if (got) tc::mbar_expect_tx(bar_full(s), stage_bytes);
+      }
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
+        if (lane == 0) atomicOr(p.status, kStatWaitEmpty);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      const long long row0 = (long long)p.front + tile_pos(tile);
+      const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
+      if (lane < na) {
+        tc::bulk_g2s(dst + (uint32_t)lane * 2048u, p.dpre + (size_t)lane * p.plane_rows + row0, 2048u, bar_full(s));
+      } else if (lane < na + nb) {
+        const int q = lane - na;
+        tc::bulk_g2s(dst + a_bytes + (uint32_t)q * xrows * 16u, p.x + (size_t)q * p.plane_rows + row0 - p.halo_rows,
+                     (uint32_t)xrows * 16u, bar_full(s));
+      }
+      if (++s == p.nstages) { s = 0; ph ^= 1u; }
+    }
+    if (!ok && lane == 0) {
+      for (int st = 0; st < p.nstages; ++st) {   // let copies in flight land before shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000) {
+          if (tc::mbar_try_wait(bar_full(st), 0) || tc::mbar_try_wait(bar_full(st), 1)) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    const uint32_t idesc = make_idesc_bf16_mn(128, p.cin);
+    const int kh = p.kside >> 1;
+    // MN-major no-swizzle descriptors: leading byte offset = 128 B (next 8 positions), stride byte offset =
+    // the plane pitch of the staged operand (next 8 channels)
+    const uint32_t a_hi = (uint32_t)(tc::make_desc(0, 128u, 2048u) >> 32);
+    const uint32_t b_hi = (uint32_t)(tc::make_desc(0, 128u, (uint32_t)xrows * 16u) >> 32);
+    const uint32_t lbo_field = (128u >> 4) << 16;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = t_begin; tile < t_end && ok; ++tile) {
+      if (!tc::mbar_wait(bar_full(s), ph, abort_flag)) {
+        if (lane == 0) atomicOr(p.status, kStatWaitFull);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc::fence_after_sync();
+      const uint32_t a_lo0 = (tc::smem_u32(s_stage + (size_t)s * stage_bytes) >> 4) | lbo_field;
+      const uint32_t b_lo0 = a_lo0 + (a_bytes >> 4);
+      if (tc::elect_one()) {
+        for (int ks = 0; ks < 8; ++ks) {            // 16 positions per MMA
+          const uint32_t a_lo = a_lo0 + (uint32_t)ks * 16u;
+          for (int t = 0; t < ntap; ++t) {
+            const int tap = tap0 + t;
+            const int dy = tap / p.kside - kh, dx = tap % p.kside - kh;
+            const uint32_t b_lo = b_lo0 + (uint32_t)(p.halo_rows + ks * 16 + dy * p.wp + dx);
+            tc::mma_bf16(tmem_base + (uint32_t)(t * p.cin), ((uint64_t)a_hi << 32) | a_lo, ((uint64_t)b_hi << 32) | b_lo, idesc,
+                         (tile != t_begin || ks != 0) ? 1u : 0u);
+          }
+        }
+        tc::mma_commit(bar_empty(s));
+        if (tile == t_end - 1) tc::mma_commit(bar_done);
+      }
+      __syncwarp();
+      if (++s == p.nstages) { s = 0; ph ^= 1u; }
+    }
+    if (t_begin >= t_end && lane == 0) tc::mbar_arrive(bar_done);   // an empty slab still releases the epilogue
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    // warp w may read TMEM lanes 32*(w%4)..+31: output channels; each lane writes its rows of the partial sums
+    const int quad = warp & 3;
+    const int co = quad * 32 + lane;
+    if (!tc::mbar_wait(bar_done, 0, abort_flag, 100)) {
+      if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
+      *abort_flag = 1;
+    } else {
+      tc::fence_after_sync();
+      const bool empty = t_begin >= t_end;
+      for (int t = 0; t < ntap; ++t) {
+        float* dst = p.partial + (((size_t)slab * p.ntaps + tap0 + t) * 128 + co) * p.cin;
+        for (int c0 = 0; c0 < p.cin; c0 += 16) {
+          uint32_t v[16];
+          tc::tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(t * p.cin + c0), v);
+          tc::tmem_wait_ld();
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            float4 o;
+            o.x = empty ? 0.f : __uint_as_float(v[j4 * 4 + 0]);
+            o.y = empty ? 0.f : __uint_as_float(v[j4 * 4 + 1]);
+            o.z = empty ? 0.f : __uint_as_float(v[j4 * 4 + 2]);
+            o.w = empty ? 0.f : __uint_as_float(v[j4 * 4 + 3]);
+            reinterpret_cast<float4*>(dst + c0)[j4] = o;
+          }
+        }
+      }
+    }
+  }
+
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, 512u);
+  }
+}
+
+// dW[co][ci][tap] (the reference's [Cout,Cin,K,K] fp32 layout) = sum over slabs of the partial sums, in slab order.
+__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nslabs, int ntaps,
+                                    int cin_p, int cin, int cout) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)cout * cin * ntaps) return;
+  const int tap = (int)(idx % ntaps);
+  const int ci = (int)((idx / ntaps) % cin);
+  const int co = (int)(idx / ((long long)ntaps * cin));
+  float acc = 0.f;
+  for (int s = 0; s < nslabs; ++s) acc += partial[(((size_t)s * ntaps + tap) * 128 + co) * cin_p + ci];
+  dw[idx] = acc;
+}
+
+}  // namespace c6

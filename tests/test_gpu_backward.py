@@ -1,0 +1,106 @@
+"""Backward of one backbone layer through the C ABI (include/c6_train.h) against PyTorch autograd in fp64.
+
+The reference's PPO update differentiates y = silu(conv2d(x, W, b)) with autograd (connect6/train.py:1047-1119,
+connect6/model.py:104-106); the oracle here is exactly that, on CPU in float64.  The operator computes in bf16
+with fp32 accumulation, so the tolerance is stated relative to the spread of each gradient: dX carries one bf16
+rounding of dL/d(pre-activation), of the filter and of the result (measured ~5e-3 of the gradient's standard
+deviation at worst); dW and db are sums over every position of the batch, where the rounding errors average out.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DX_TOL = 3e-2     # max |error| / std(dX)
+DW_TOL = 2e-2     # max |error| / std(dW)
+DB_TOL = 2e-2     # max |error| / max(std(db), |db| scale)
+
+
+def _oracle(x, w, b, dy):
+    x64 = x.double().requires_grad_(True)
+    w64 = w.double().requires_grad_(True)
+    b64 = b.double().requires_grad_(True)
+    y = torch.nn.functional.silu(torch.nn.functional.conv2d(x64, w64, b64, padding=w.shape[-1] // 2))
+    y.backward(dy.double())
+    return x64.grad, w64.grad, b64.grad
+
+
+def _case(B, cin, cout, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.nn.functional.silu(torch.randn(B, cin, n, n, generator=g))            # like a previous layer's output
+    w = torch.randn(cout, cin, 3, 3, generator=g) * (2.0 / (9 * cin)) ** 0.5          # kaiming scale
+    b = 0.1 * torch.randn(cout, generator=g)
+    dy = torch.randn(B, cout, n, n, generator=g) * 1e-3
+    return x, w, b, dy
+
+
+@pytest.mark.parametrize("B,cin,cout,n", [(37, 64, 96, 19), (5, 32, 32, 19), (16, 96, 96, 19), (9, 24, 40, 7), (3, 64, 64, 19)])
+def test_conv_layer_backward_against_autograd(cuda_device, B, cin, cout, n):
+    from connect6_b200.train_ops import backward_status, conv_layer_backward
+    x, w, b, dy = _case(B, cin, cout, n, seed=B + cin)
+    rx, rw, rb = _oracle(x, w, b, dy)
+    for _ in range(2):                                      # second call reuses the workspace
+        dx, dw, db = conv_layer_backward(x.to(cuda_device), w.to(cuda_device), b.to(cuda_device), dy.to(cuda_device))
+    assert backward_status(dx) == 0
+    ex = (dx.cpu().double() - rx).abs().max().item() / rx.std().item()
+    ew = (dw.cpu().double() - rw).abs().max().item() / rw.std().item()
+    eb = (db.cpu().double() - rb).abs().max().item() / max(rb.std().item(), rb.abs().max().item())
+    assert ex < DX_TOL, f"dX: {ex}"
+    assert ew < DW_TOL, f"dW: {ew}"
+    assert eb < DB_TOL, f"db: {eb}"
+    # without dX (first trainable layer) the other two are unchanged
+    none, dw2, db2 = conv_layer_backward(x.to(cuda_device), w.to(cuda_device), b.to(cuda_device), dy.to(cuda_device),
+                                         need_dx=False)
+    assert none is None and torch.equal(dw2, dw) and torch.equal(db2, db)
+
+
+def test_conv_layer_backward_is_linear_in_the_output_gradient(cuda_device):
+    """Size-independent property at a larger batch: the backward is linear in dy (up to bf16 rounding of dy)."""
+    from connect6_b200.train_ops import conv_layer_backward
+    x, w, b, dy = _case(512, 64, 96, 19, seed=3)
+    xd, wd, bd, dyd = (t.to(cuda_device) for t in (x, w, b, dy))
+    dx1, dw1, db1 = conv_layer_backward(xd, wd, bd, dyd)
+    dx2, dw2, db2 = conv_layer_backward(xd, wd, bd, 2.0 * dyd)      # exact in bf16: a power of two
+    assert torch.equal(dx2, 2.0 * dx1) and torch.allclose(dw2, 2.0 * dw1, rtol=1e-5, atol=0) and torch.allclose(db2, 2.0 * db1, rtol=1e-5)
+    zx, zw, zb = conv_layer_backward(xd, wd, bd, torch.zeros_like(dyd))
+    assert not zx.any() and not zw.any() and not zb.any()
+
+
+def test_autograd_function_trains_a_layer(cuda_device):
+    from connect6_b200.train_ops import SiluConv3x3
+    torch.manual_seed(0)
+    conv = torch.nn.Conv2d(64, 96, 3, padding=1).to(cuda_device)
+    x = torch.nn.functional.silu(torch.randn(8, 64, 19, 19, device=cuda_device)).requires_grad_(True)
+    y = SiluConv3x3.apply(x, conv.weight, conv.bias)
+    loss = (y * torch.linspace(-1, 1, 96, device=cuda_device).view(1, 96, 1, 1)).sum() * 1e-3
+    loss.backward()
+    gx, gw, gb = x.grad.clone(), conv.weight.grad.clone(), conv.bias.grad.clone()
+    x.grad = None
+    conv.zero_grad()
+    y2 = torch.nn.functional.silu(conv(x))
+    ((y2 * torch.linspace(-1, 1, 96, device=cuda_device).view(1, 96, 1, 1)).sum() * 1e-3).backward()
+    assert (gx - x.grad).abs().max().item() < DX_TOL * x.grad.std().item()
+    assert (gw - conv.weight.grad).abs().max().item() < DW_TOL * conv.weight.grad.std().item()
+    assert (gb - conv.bias.grad).abs().max().item() < DB_TOL * conv.bias.grad.abs().max().item()
+
+
+def test_conv_layer_backward_rejects_what_it_does_not_support(cuda_device):
+    from connect6_b200.train_ops import conv_layer_backward
+    dev = cuda_device
+    with pytest.raises(ValueError):     # 5x5 filter
+        conv_layer_backward(torch.zeros(2, 8, 19, 19, device=dev), torch.zeros(8, 8, 5, 5, device=dev), None,
+                            torch.zeros(2, 8, 19, 19, device=dev))
+    with pytest.raises(ValueError):     # too wide
+        conv_layer_backward(torch.zeros(2, 192, 19, 19, device=dev), torch.zeros(8, 192, 3, 3, device=dev), None,
+                            torch.zeros(2, 8, 19, 19, device=dev))
+    with pytest.raises(ValueError):     # shapes of different layers
+        conv_layer_backward(torch.zeros(2, 8, 19, 19, device=dev), torch.zeros(8, 16, 3, 3, device=dev), None,
+                            torch.zeros(2, 8, 19, 19, device=dev))
+    with pytest.raises(RuntimeError):
+        conv_layer_backward(torch.zeros(2, 8, 19, 19), torch.zeros(8, 8, 3, 3), None, torch.zeros(2, 8, 19, 19))
+    dx, dw, db = conv_layer_backward(torch.zeros(0, 8, 19, 19, device=dev), torch.zeros(8, 8, 3, 3, device=dev), None,
+                                     torch.zeros(0, 8, 19, 19, device=dev))
+    assert dx.shape == (0, 8, 19, 19) and not dw.any() and not db.any()

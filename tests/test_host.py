@@ -15,7 +15,7 @@ def test_library_exports_every_declared_symbol(engine_lib):
     """Every function declared in include/*.h is exported and bound; no compute calls."""
     from connect6_b200 import _lib
     headers = sorted((ROOT / "include").glob("*.h"))
-    assert [h.name for h in headers] == ["c6_debug.h", "c6_engine.h", "c6_env.h"]
+    assert [h.name for h in headers] == ["c6_debug.h", "c6_engine.h", "c6_env.h", "c6_train.h"]
     header = "\n".join(h.read_text() for h in headers)
     declared = set(re.findall(r"\b(c6_[a-z_0-9]+)\s*\(", header))
     assert declared, "no declarations parsed"

@@ -679,6 +679,20 @@ def run_backward(args) -> None:
         lib_ms = l0.elapsed_time(l1) / 10
     except Exception as exc:  # noqa: BLE001
         lib_ms = f"{type(exc).__name__}: {exc}"[:160]
+    # per-kernel device times of three more calls (CUPTI through torch.profiler; outside the timed region)
+    kernels = {}
+    try:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                conv_layer_backward(x, w, b, dy)
+            torch.cuda.synchronize(dev)
+        for ev in prof.key_averages():
+            t_us = getattr(ev, "device_time_total", None) or getattr(ev, "cuda_time_total", 0.0)
+            if t_us and ("c6::" in ev.key or "Memset" in ev.key or "Memcpy" in ev.key):
+                kernels[ev.key[:70]] = {"ms_per_call": t_us / 3e3, "launches_per_call": ev.count / 3}
+    except Exception as exc:  # noqa: BLE001
+        kernels = {"error": f"{type(exc).__name__}: {exc}"[:160]}
     peaks, peak_kind = load_peaks()
     peak, peak_source = pick_tensor_peak(peaks, peak_kind, clocks, ms * args.steps * 1e-3)
     macs = 361 * 9 * cin * cout                     # per board and GEMM
@@ -695,6 +709,7 @@ def run_backward(args) -> None:
         "roofline": {"bound": "tensor", "kernel": "whole operator (2 conv_tc_kernel launches + wgrad_tc_kernel + packing)",
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_source,
                      "flop_algorithmic": algorithmic, "flop_executed": executed, "traffic": None},
+        "kernels": kernels,
         "library_gpu_bar": {"ms_per_step": lib_ms, "what": "torch autograd of silu(conv2d) under bf16 autocast (cuDNN), forward + backward"},
         "device_status": status}), flush=True)
 

@@ -48,7 +48,7 @@ struct C6Engine {
   int kc0 = 0, nt = 0, ntiles = 0, ntot = 0, stem_stages = 0, stem_smem = 0, stem_acc_stride = 0,
       stem_tmem_cols = 0, stem_kcs = 4, stem_pair = 0;
   // direct stem (conv_tc_kernel's stem mode), taken by passes of at most sd_max_boards boards per group
-  int sd_ok = 0, sd_max_boards = 32, sd_hx = 0, sd_wi = 0, sd_slots = 0, sd_halo_b = 0, sd_halo_a = 0, sd_front = 0;
+  int sd_ok = 0, sd_max_boards = 32, sd_min_groups = 2, sd_hx = 0, sd_wi = 0, sd_slots = 0, sd_halo_b = 0, sd_halo_a = 0, sd_front = 0;
   LayerPlan sdp;                    // its pipeline plan
   uint4* w_sd = nullptr;            // [G][ci][ky][kx block][2][cout_p] filter rows
   uint4* w_sd_pair = nullptr;       // the same split in two row halves for CTA pairs
@@ -874,8 +874,13 @@ int c6_create(const C6Desc* d, C6Engine** out) {
       e->sd_halo_a = round_up(kh * e->sd_wi + 16 * e->sd_hx - 1 - kh + 8, 8);
       e->sd_front = e->sd_halo_b;
       e->sdp = e->lp[0];
+      // Taken by engines with at least sd_min_groups weight sets for calls of at most sd_max_boards boards per
+      // set: that is where the stem GEMM's 27 MB of expanded weights per model cost more than they save.  For a
+      // single model the two paths tie up to about 16 boards and the GEMM wins beyond (measured), so it keeps
+      // the GEMM.  C6_STEM_DIRECT_MAX / C6_STEM_DIRECT_GROUPS override the two thresholds.
       if (const char* v = std::getenv("C6_STEM_DIRECT_MAX")) e->sd_max_boards = std::max(0, std::atoi(v));
-      e->sd_ok = e->sd_max_boards > 0 &&
+      if (const char* v = std::getenv("C6_STEM_DIRECT_GROUPS")) e->sd_min_groups = std::max(1, std::atoi(v));
+      e->sd_ok = e->sd_max_boards > 0 && e->G >= e->sd_min_groups &&
                  plan_tc_layer(e->pair_mode, e->sdp, k0 * e->sd_hx, 3, 128 + e->sd_halo_b + e->sd_halo_a, 1, 1) ? 1 : 0;
       if (e->sd_ok) {
         if ((rc = dev_alloc(e, &e->w_sd, (size_t)e->G * e->sdp.w_rows_per_group, true, nullptr))) return bail(rc, "");

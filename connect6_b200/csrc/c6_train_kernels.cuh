@@ -34,19 +34,23 @@ __global__ void pack_nchw_planes_kernel(const float* __restrict__ x, uint4* __re
   planes[(size_t)q * plane_rows + front + b * slots + slot] = o;
 }
 
-// bf16 planes -> fp32 [B, C, n, n] (cells only)
+// bf16 planes -> fp32 [B, C, n, n] (cells only).  One thread per (board, plane, cell): one 16-byte row in,
+// eight floats out, each store coalesced across the threads of consecutive cells.
 __global__ void unpack_planes_nchw_kernel(const uint4* __restrict__ planes, long long plane_rows, int front, int slots,
                                           int wp, int n, int C, long long B, float* __restrict__ out) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int cells = n * n;
-  if (idx >= B * C * cells) return;
+  const int cells = n * n, nq = (C + 7) / 8;
+  if (idx >= B * nq * cells) return;
   const int cell = (int)(idx % cells);
-  const int ch = (int)((idx / cells) % C);
-  const long long b = idx / ((long long)cells * C);
+  const int q = (int)((idx / cells) % nq);
+  const long long b = idx / ((long long)cells * nq);
   const int r = cell / n, c = cell - r * n;
-  const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(planes + (size_t)(ch >> 3) * plane_rows + front +
-                                                                      b * slots + r * wp + c);
-  out[idx] = __bfloat162float(row[ch & 7]);
+  const uint4 v = planes[(size_t)q * plane_rows + front + b * slots + r * wp + c];
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  float* o = out + ((b * C + q * 8) * cells + cell);
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    if (q * 8 + e < C) o[(size_t)e * cells] = __uint_as_float((e & 1) ? (w[e >> 1] & 0xffff0000u) : (w[e >> 1] << 16));
 }
 
 // Filter of the input-gradient convolution in the k x k kernel's weight layout: dX = conv(dPre, W') with

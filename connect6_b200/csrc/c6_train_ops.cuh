@@ -56,7 +56,7 @@ struct BackwardLayout {
   int wp = 0, slots = 0, halo_rows = 0, front = 0, tiles = 0, tiles_per_board = 0;
   long long B = 0, total_pos = 0, plane_rows = 0;
   LayerPlan fwd, dgrad;           // pipeline plans of the two conv_tc_kernel launches
-  int wg_taps_per_cta = 0, wg_groups = 0, wg_slabs = 0, wg_stages = 0, wg_smem = 0;
+  int wg_taps_per_cta = 0, wg_groups = 0, wg_slabs = 0, wg_stages = 0, wg_smem = 0, wg_tile_rows = 128, wg_tiles = 0;
   // workspace offsets in bytes
   size_t off_bias = 0, off_zero = 0, off_wf = 0, off_wf_pair = 0, off_wd = 0, off_wd_pair = 0, off_x = 0, off_dy = 0,
          off_dpre = 0, off_dx = 0, off_partial = 0, off_colsum = 0, total = 0;
@@ -81,7 +81,7 @@ BackwardLayout make_layout(int n, int k, int cin, int cout, long long B, int sms
   if (tiles > 0x7fffffffLL / 128) return L;
   L.tiles = (int)tiles;
   L.total_pos = L.tiles_per_board ? round_up_ll((long long)((tiles + tpb - 1) / tpb) * L.slots, 128) : tiles * 128;
-  L.plane_rows = (long long)L.front + L.total_pos + L.halo_rows + 128;
+  L.plane_rows = (long long)L.front + L.total_pos + L.halo_rows + 256;   // + one K tile of the weight-gradient kernel
   const int rows = conv_stage_rows(L.halo_rows);
   L.fwd.k = k; L.fwd.cin = cin; L.fwd.cout = cout; L.fwd.cin_p = L.cin_p; L.fwd.cout_p = L.cout_p;
   L.dgrad.k = k; L.dgrad.cin = cout; L.dgrad.cout = cin; L.dgrad.cin_p = L.cout_p; L.dgrad.cout_p = L.cin_p;
@@ -90,12 +90,16 @@ BackwardLayout make_layout(int n, int k, int cin, int cout, long long B, int sms
   L.wg_taps_per_cta = std::min(k * k, 512 / L.cin_p);
   L.wg_groups = (k * k + L.wg_taps_per_cta - 1) / L.wg_taps_per_cta;
   L.wg_slabs = std::max(1, sms / L.wg_groups);
-  const int stage = wgrad_stage_bytes(L.cin_p, L.cout_p, L.halo_rows);
   // 32 KB of slack behind the last stage: the M = 128 operand descriptor addresses 16 channel groups even
-  // when fewer gradient planes exist (those accumulator rows are never read)
-  L.wg_stages = std::min(kWgradMaxStages, (kSmemLimit - 128 - kWgradSmemHeader - 32768) / stage);
+  // when fewer gradient planes exist (those accumulator rows are never read).  K tiles of 256 positions when
+  // two stages of that size fit, else 128.
+  const int room = kSmemLimit - 128 - kWgradSmemHeader - 32768;
+  L.wg_tile_rows = 2 * wgrad_stage_bytes(L.cin_p, L.cout_p, L.halo_rows, 256) <= room ? 256 : 128;
+  const int stage = wgrad_stage_bytes(L.cin_p, L.cout_p, L.halo_rows, L.wg_tile_rows);
+  L.wg_stages = std::min(kWgradMaxStages, room / stage);
   if (L.wg_stages < 2) return L;
   L.wg_smem = 128 + kWgradSmemHeader + L.wg_stages * stage + 32768;
+  L.wg_tiles = (int)((L.total_pos + L.wg_tile_rows - 1) / L.wg_tile_rows);
   auto take = [&](size_t bytes) { size_t o = L.total; L.total += (bytes + 255) & ~(size_t)255; return o; };
   take(256);                                                // status word
   L.off_bias = take((size_t)L.cout_p * 4);
@@ -179,7 +183,7 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
                            const float* x, const float* w, const float* bias, const float* dy, float* dx, float* dw,
                            float* db, void* workspace, int64_t workspace_bytes, void* stream) {
   if (B < 0) return tfail(C6_ERR_ARG, "negative board count");
-  if (!x || !w || !dy || !dw || !db || !workspace) return tfail(C6_ERR_ARG, "null pointer");
+  if (!w || !dw || !db || !workspace || (B > 0 && (!x || !dy))) return tfail(C6_ERR_ARG, "null pointer");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return tfail(C6_ERR_ARG, "workspace must be 256-byte aligned");
   int ndev = 0;
   if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev)
@@ -254,7 +258,7 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
   if (dx) {
     rc = launch_conv(L, L.dgrad, kEpiLinear, dpre, dxp, nullptr, wd, wd_pair, zero_f, status, sms, st);
     if (rc) return rc;
-    const long long total = B * cin * L.n * L.n;
+    const long long total = B * ((cin + 7) / 8) * L.n * L.n;
     unpack_planes_nchw_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(dxp, L.plane_rows, L.front, L.slots, L.wp, L.n, cin, B, dx);
     C6T_LAUNCHED("unpack_planes_nchw_kernel");
   }
@@ -272,9 +276,8 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
     p.cout = L.cout_p;
     p.kside = kside;
     p.wp = L.wp;
-    p.slots = L.slots;
-    p.tiles_per_board = L.tiles_per_board;
-    p.ntiles = L.tiles;
+    p.tile_rows = L.wg_tile_rows;
+    p.ntiles = L.wg_tiles;
     p.ntaps = taps;
     p.taps_per_cta = L.wg_taps_per_cta;
     p.ngroups = L.wg_groups;

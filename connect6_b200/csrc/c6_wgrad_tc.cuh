@@ -13,7 +13,10 @@
 // address, and each tap accumulates into its own TMEM columns.
 //
 // Work split: a CTA owns a group of taps (as many as fit 512 TMEM columns: floor(512 / Cin), at most
-// k*k) and a contiguous slab of 128-position K tiles; it writes its fp32 partial sums
+// k*k) and a contiguous slab of K tiles of `tile_rows` positions (256 when two such stages fit shared
+// memory, else 128: a stage costs one bulk copy per channel-chunk plane whatever its length, and the copy
+// engine's rate of about one copy per 300 clocks, not the tensor pipe, bounds this kernel, so longer tiles
+// are faster; tiles run linearly over all slots, padding included); it writes its fp32 partial sums
 // [slab][tap][128][Cin] to global memory and a second kernel adds the slabs up in a fixed order
 // (no atomics: results are reproducible).
 // CTA = 192 threads: warp 0 stages operands with bulk copies, warp 1 issues the MMAs and owns TMEM,
@@ -35,7 +38,8 @@ struct WgradParams {
   int halo_rows;        // rows staged before and after the 128 tile rows of x (multiple of 8, >= kside/2 * (wp + 1))
   int cin, cout;        // padded to multiples of 32; cout <= 128, cin <= 128
   int kside, wp;
-  int slots, tiles_per_board, ntiles;   // K tiles of 128 positions, laid out as in the forward kernels
+  int tile_rows;        // positions per K tile: 128 or 256
+  int ntiles;           // K tiles: tile t covers positions [t * tile_rows, (t + 1) * tile_rows)
   int ntaps;            // kside * kside
   int taps_per_cta;     // taps of one tap group
   int ngroups, nslabs;  // grid = ngroups * nslabs; CTA b: group b % ngroups, slab b / ngroups
@@ -51,8 +55,8 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_bf16_mn(int m, int n) {
   return tc::make_idesc_bf16(m, n) | (1u << 15) | (1u << 16);
 }
 
-__host__ __device__ inline int wgrad_stage_bytes(int cin, int cout, int halo_rows) {
-  return (cout / 8) * 128 * 16 + (cin / 8) * (128 + 2 * halo_rows) * 16;
+__host__ __device__ inline int wgrad_stage_bytes(int cin, int cout, int halo_rows, int tile_rows) {
+  return (cout / 8) * tile_rows * 16 + (cin / 8) * (tile_rows + 2 * halo_rows) * 16;
 }
 
 __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradParams p) {
@@ -69,17 +73,15 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
   const int ntap = min(p.taps_per_cta, p.ntaps - tap0);
   const int t_begin = (int)(((long long)p.ntiles * slab) / p.nslabs);
   const int t_end = (int)(((long long)p.ntiles * (slab + 1)) / p.nslabs);
-  const int xrows = 128 + 2 * p.halo_rows;
-  const uint32_t a_bytes = (uint32_t)(p.cout / 8) * 128u * 16u;
+  const int xrows = p.tile_rows + 2 * p.halo_rows;
+  const uint32_t a_plane = (uint32_t)p.tile_rows * 16u;
+  const uint32_t a_bytes = (uint32_t)(p.cout / 8) * a_plane;
   const uint32_t b_bytes = (uint32_t)(p.cin / 8) * xrows * 16u;
   const uint32_t stage_bytes = a_bytes + b_bytes;     // multiples of 128
   const uint32_t bar0 = tc::smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
   auto bar_empty = [&](int s) { return bar0 + 8u * (8 + s); };
   const uint32_t bar_done = bar0 + 8u * 16;
-  auto tile_pos = [&](int tile) {
-    return p.tiles_per_board ? (tile / p.tiles_per_board) * p.slots + (tile % p.tiles_per_board) * 128 : tile * 128;
-  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kWgradMaxStages; ++s) {
@@ -101,7 +103,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
-    // lane i < cout/8 copies gradient plane i (the tile's 128 rows), the next cin/8 lanes one input plane
+    // lane i < cout/8 copies gradient plane i (the tile's rows), the next cin/8 lanes one input plane
     // each (the tile's rows plus the halo on both sides)
     const int na = p.cout / 8, nb = p.cin / 8;
     int s = 0;
@@ -120,10 +122,10 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
         ok = false;
         break;
       }
-      const long long row0 = (long long)p.front + tile_pos(tile);
+      const long long row0 = (long long)p.front + (long long)tile * p.tile_rows;
       const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
       if (lane < na) {
-        tc::bulk_g2s(dst + (uint32_t)lane * 2048u, p.dpre + (size_t)lane * p.plane_rows + row0, 2048u, bar_full(s));
+        tc::bulk_g2s(dst + (uint32_t)lane * a_plane, p.dpre + (size_t)lane * p.plane_rows + row0, a_plane, bar_full(s));
       } else if (lane < na + nb) {
         const int q = lane - na;
         tc::bulk_g2s(dst + a_bytes + (uint32_t)q * xrows * 16u, p.x + (size_t)q * p.plane_rows + row0 - p.halo_rows,
@@ -146,7 +148,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
     const int kh = p.kside >> 1;
     // MN-major no-swizzle descriptors: leading byte offset = 128 B (next 8 positions), stride byte offset =
     // the plane pitch of the staged operand (next 8 channels)
-    const uint32_t a_hi = (uint32_t)(tc::make_desc(0, 128u, 2048u) >> 32);
+    const uint32_t a_hi = (uint32_t)(tc::make_desc(0, 128u, a_plane) >> 32);
     const uint32_t b_hi = (uint32_t)(tc::make_desc(0, 128u, (uint32_t)xrows * 16u) >> 32);
     const uint32_t lbo_field = (128u >> 4) << 16;
     int s = 0;
@@ -163,7 +165,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
       const uint32_t a_lo0 = (tc::smem_u32(s_stage + (size_t)s * stage_bytes) >> 4) | lbo_field;
       const uint32_t b_lo0 = a_lo0 + (a_bytes >> 4);
       if (tc::elect_one()) {
-        for (int ks = 0; ks < 8; ++ks) {            // 16 positions per MMA
+        for (int ks = 0; ks < p.tile_rows / 16; ++ks) {            // 16 positions per MMA
           const uint32_t a_lo = a_lo0 + (uint32_t)ks * 16u;
           for (int t = 0; t < ntap; ++t) {
             const int tap = tap0 + t;

@@ -131,9 +131,10 @@ def test_config3_grouped_16x512(cuda_device):
     assert eng.status() == 0 and single.status() == 0
 
 
-def test_training_ensemble_128x4(cuda_device):
+def test_training_ensemble_128x4(cuda_device, monkeypatch):
     """The ensemble shape the reference trains against (connect6/history.py:276-303 with 128 stacked
-    opponents and 4 tables each): every sampled group equals a single-model engine bit for bit."""
+    opponents and 4 tables each): every sampled group equals a single-model engine bit for bit (the single
+    engine is told to take the direct stem too, which by default only many-model engines do)."""
     from connect6_b200.boards import generate_planes
     from connect6_b200.engine import Engine
     from connect6_b200.model import PolicyValueNet
@@ -149,7 +150,9 @@ def test_training_ensemble_128x4(cuda_device):
     x = torch.from_numpy(generate_planes(0, G * T)).reshape(G, T, 3, 19, 19).to(cuda_device)
     logits, value = eng.forward_grouped(x, want_value=True)
     assert eng.device_bytes < 260e6, eng.device_bytes           # + activation workspace for 512 boards
+    monkeypatch.setenv("C6_STEM_DIRECT_GROUPS", "1")
     single = Engine(cuda_device, 19, KERNELS, PolicyValueNet.DEFAULT_CHANNELS, 1, "bf16")
+    monkeypatch.delenv("C6_STEM_DIRECT_GROUPS")
     for g in (0, 63, 127):
         single.load_state_dict(states[g])
         l1, v1 = single.forward(x[g])
@@ -162,17 +165,20 @@ def test_training_ensemble_128x4(cuda_device):
 
 @pytest.mark.parametrize("precision", ["bf16", "f16"])
 def test_direct_stem_against_gemm_stem_and_oracle(cuda_device, precision, monkeypatch):
-    """Passes of at most 32 boards per weight set take the direct stem (implicit GEMM from the filter),
-    larger ones the Toeplitz stem GEMM.  Both against the oracle's first layer and against each other, with
-    per-board orientation and a third plane that is not constant; the expanded operand of the stem GEMM is
-    only allocated once a pass needs it."""
+    """Calls of at most 32 boards per weight set may take the direct stem (implicit GEMM from the filter;
+    the default for engines with several weight sets, forced here for a single model), larger ones the
+    Toeplitz stem GEMM.  Both against the oracle's first layer and against each other, with per-board
+    orientation and a third plane that is not constant; the expanded operand of the stem GEMM is only
+    allocated once a call needs it."""
     from connect6_b200.boards import generate_planes
     from connect6_b200.engine import Engine
     from connect6_b200.model import PolicyValueNet
     state = _state(42)
     chans = PolicyValueNet.DEFAULT_CHANNELS
+    monkeypatch.setenv("C6_STEM_DIRECT_GROUPS", "1")
     direct = Engine(cuda_device, 19, KERNELS, chans, 1, precision)
     direct.load_state_dict(state)
+    monkeypatch.delenv("C6_STEM_DIRECT_GROUPS")
     monkeypatch.setenv("C6_STEM_DIRECT_MAX", "0")
     gemm = Engine(cuda_device, 19, KERNELS, chans, 1, precision)
     gemm.load_state_dict(state)

@@ -249,8 +249,7 @@ def test_f16_layers_and_range_flag(cuda_device, precision):
 
 def test_chunked_passes_equal_single_pass(cuda_device):
     """A batch cut into several internal passes gives bit-identical results, and batches of any size reuse
-    the workspace without stale data.  Calls of up to 32 boards take the direct stem, larger ones the stem
-    GEMM (same sums in another order): across that boundary results agree to a fraction of the bf16 noise."""
+    the workspace without stale data."""
     from connect6_b200.boards import generate_planes
     from connect6_b200.engine import Engine
     m, params = _default_model("bf16", cuda_device)
@@ -260,16 +259,10 @@ def test_chunked_passes_equal_single_pass(cuda_device):
     small.load_state_dict(params)
     parts = small.forward(x)
     assert torch.equal(whole[0], parts[0]) and torch.equal(whole[1], parts[1])
-    sigma = whole[0].std().item()
-    # shrinking and growing batches
+    # shrinking and growing batches reuse the same workspace without stale data
     for b in (1, 2, 3, 64, 65, 7, 33, 32):
         l, v = small.forward(x[:b])
-        if b > 32:
-            assert torch.equal(l, whole[0][:b]) and torch.equal(v, whole[1][:b])
-        else:
-            assert (l - whole[0][:b]).abs().max().item() < 0.05 * sigma and (v - whole[1][:b]).abs().max().item() < 1e-5
-            l2, v2 = m.engine_for(cuda_device).forward(x[:b])          # the same call on the other engine: same path, same bits
-            assert torch.equal(l, l2) and torch.equal(v, v2)
+        assert torch.equal(l, whole[0][:b]) and torch.equal(v, whole[1][:b])
     assert small.status() == 0
 
 

@@ -87,7 +87,7 @@ BackwardLayout make_layout(int n, int k, int cin, int cout, long long B, int sms
   L.dgrad.k = k; L.dgrad.cin = cout; L.dgrad.cout = cin; L.dgrad.cin_p = L.cout_p; L.dgrad.cout_p = L.cin_p;
   if (!plan_tc_layer(sms >= 2, L.fwd, k * k, L.cin_p / 16, rows, 2, 2)) return L;
   if (!plan_tc_layer(sms >= 2, L.dgrad, k * k, L.cout_p / 16, rows, 2, 2)) return L;
-  L.wg_taps_per_cta = std::min(k * k, 512 / L.cin_p);
+  L.wg_taps_per_cta = std::min(std::min(k * k, kWgradMaxTaps), 512 / L.cin_p);
   L.wg_groups = (k * k + L.wg_taps_per_cta - 1) / L.wg_taps_per_cta;
   L.wg_slabs = std::max(1, sms / L.wg_groups);
   // 32 KB of slack behind the last stage: the M = 128 operand descriptor addresses 16 channel groups even

@@ -14,9 +14,9 @@
 //
 // Work split: a CTA owns a group of taps (as many as fit 512 TMEM columns: floor(512 / Cin), at most
 // k*k) and a contiguous slab of K tiles of `tile_rows` positions (256 when two such stages fit shared
-// memory, else 128: a stage costs one bulk copy per channel-chunk plane whatever its length, and the copy
-// engine's rate of about one copy per 300 clocks, not the tensor pipe, bounds this kernel, so longer tiles
-// are faster; tiles run linearly over all slots, padding included); it writes its fp32 partial sums
+// memory, else 128: a stage costs one bulk copy per channel-chunk plane whatever its length, so longer tiles
+// mean fewer copies and barrier rounds; tiles run linearly over all slots, padding included); it writes its
+// fp32 partial sums
 // [slab][tap][128][Cin] to global memory and a second kernel adds the slabs up in a fixed order
 // (no atomics: results are reproducible).
 // CTA = 192 threads: warp 0 stages operands with bulk copies, warp 1 issues the MMAs and owns TMEM,
@@ -49,6 +49,7 @@ struct WgradParams {
 constexpr int kWgradThreads = 192;
 constexpr int kWgradSmemHeader = 1024;
 constexpr int kWgradMaxStages = 8;
+constexpr int kWgradMaxTaps = 9;     // taps one CTA may own (a 3 x 3 filter)
 
 // Instruction descriptor: D = fp32, A = B = bf16, both MN-major (bits 15 and 16 set).
 __host__ __device__ __forceinline__ uint32_t make_idesc_bf16_mn(int m, int n) {
@@ -75,8 +76,9 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
   const int t_end = (int)(((long long)p.ntiles * (slab + 1)) / p.nslabs);
   const int xrows = p.tile_rows + 2 * p.halo_rows;
   const uint32_t a_plane = (uint32_t)p.tile_rows * 16u;
+  const uint32_t b_plane = (uint32_t)xrows * 16u;
   const uint32_t a_bytes = (uint32_t)(p.cout / 8) * a_plane;
-  const uint32_t b_bytes = (uint32_t)(p.cin / 8) * xrows * 16u;
+  const uint32_t b_bytes = (uint32_t)(p.cin / 8) * b_plane;
   const uint32_t stage_bytes = a_bytes + b_bytes;     // multiples of 128
   const uint32_t bar0 = tc::smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
@@ -128,8 +130,8 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
         tc::bulk_g2s(dst + (uint32_t)lane * a_plane, p.dpre + (size_t)lane * p.plane_rows + row0, a_plane, bar_full(s));
       } else if (lane < na + nb) {
         const int q = lane - na;
-        tc::bulk_g2s(dst + a_bytes + (uint32_t)q * xrows * 16u, p.x + (size_t)q * p.plane_rows + row0 - p.halo_rows,
-                     (uint32_t)xrows * 16u, bar_full(s));
+        tc::bulk_g2s(dst + a_bytes + (uint32_t)q * b_plane, p.x + (size_t)q * p.plane_rows + row0 - p.halo_rows, b_plane,
+                     bar_full(s));
       }
       if (++s == p.nstages) { s = 0; ph ^= 1u; }
     }
@@ -149,8 +151,14 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
     // MN-major no-swizzle descriptors: leading byte offset = 128 B (next 8 positions), stride byte offset =
     // the plane pitch of the staged operand (next 8 channels)
     const uint32_t a_hi = (uint32_t)(tc::make_desc(0, 128u, a_plane) >> 32);
-    const uint32_t b_hi = (uint32_t)(tc::make_desc(0, 128u, (uint32_t)xrows * 16u) >> 32);
+    const uint32_t b_hi = (uint32_t)(tc::make_desc(0, 128u, b_plane) >> 32);
     const uint32_t lbo_field = (128u >> 4) << 16;
+    uint32_t tshift[kWgradMaxTaps];      // row of the staged input plane where tap t's operand starts
+#pragma unroll
+    for (int t = 0; t < kWgradMaxTaps; ++t) {
+      const int tap = min(tap0 + t, p.ntaps - 1);
+      tshift[t] = (uint32_t)(p.halo_rows + (tap / p.kside - kh) * p.wp + (tap % p.kside - kh));
+    }
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -167,13 +175,15 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
       if (tc::elect_one()) {
         for (int ks = 0; ks < p.tile_rows / 16; ++ks) {            // 16 positions per MMA
           const uint32_t a_lo = a_lo0 + (uint32_t)ks * 16u;
-          for (int t = 0; t < ntap; ++t) {
-            const int tap = tap0 + t;
-            const int dy = tap / p.kside - kh, dx = tap % p.kside - kh;
-            const uint32_t b_lo = b_lo0 + (uint32_t)(p.halo_rows + ks * 16 + dy * p.wp + dx);
-            tc::mma_bf16(tmem_base + (uint32_t)(t * p.cin), ((uint64_t)a_hi << 32) | a_lo, ((uint64_t)b_hi << 32) | b_lo, idesc,
-                         (tile != t_begin || ks != 0) ? 1u : 0u);
-          }
+          const uint32_t b_lo = b_lo0 + (uint32_t)ks * 16u;
+          const uint32_t acc = (tile != t_begin || ks != 0) ? 1u : 0u;
+          // unrolled over the CTA's taps: the issue loop must stay well below the ~50 clocks an MMA takes,
+          // so the per-tap row shifts live in registers (no division, no table in memory)
+#pragma unroll
+          for (int t = 0; t < kWgradMaxTaps; ++t)
+            if (t < ntap)
+              tc::mma_bf16(tmem_base + (uint32_t)(t * p.cin), ((uint64_t)a_hi << 32) | a_lo,
+                           ((uint64_t)b_hi << 32) | (b_lo + tshift[t]), idesc, acc);
         }
         tc::mma_commit(bar_empty(s));
         if (tile == t_end - 1) tc::mma_commit(bar_done);

@@ -320,14 +320,16 @@ def run_engine(args) -> None:
     host_batches = [torch.from_numpy(generate_planes(first + i * BATCH, BATCH)).pin_memory()
                     for i in range(INPUT_BUFFERS)]
     dev_batches = [h.to(dev) for h in host_batches]
-    stats = torch.zeros(9, dtype=torch.int64, device=dev)
+    reducer = shard.RolloutStatsReducer(dev)
 
     def step(i: int):
         x = dev_batches[i % INPUT_BUFFERS]
         action, logprob, value, _ = eng.forward_step(x, temperature=1.0, seed=0xC6, offset=i,
                                                      board_index0=first + (i % INPUT_BUFFERS) * BATCH)
-        stats[0] = action.numel()          # stand-in for the collector's per-step statistics vector
-        shard.reduce_rollout_stats(stats)
+        # stand-in for the collector's per-step statistics vector: summed over the ranks every step, on NCCL's
+        # own stream, off the compute stream's critical path
+        reducer.buffer()[0] = BATCH
+        reducer.submit()
         return action, logprob, value
 
     for i in range(args.warmup):
@@ -353,10 +355,13 @@ def run_engine(args) -> None:
         eng.profile(sample)
         sampled_steps += sample
         step(args.warmup + i)
+    total_stats = reducer.drain()           # the last step's reduction is inside the timed region
     ev1.record()
     torch.cuda.synchronize(dev)
     t_end = time.time()
     shard.barrier()
+    if int(total_stats[0]) != BATCH * world:
+        raise SystemExit(f"statistics all-reduce returned {int(total_stats[0])}, expected {BATCH * world}")
     elapsed_ms = ev0.elapsed_time(ev1)
     prof = eng.profile_read()
     eng.profile(False)

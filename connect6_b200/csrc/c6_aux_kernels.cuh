@@ -404,8 +404,10 @@ __device__ __forceinline__ float warp_max(float v) {
 // One warp per board; lane l owns the J consecutive actions J*l .. J*l + J-1 and keeps them in
 // registers (J * 32 >= n_actions), so the running sum of the inverse-CDF draw is J additions per
 // lane plus one shuffle scan over the lane totals: no shared memory, no block-wide barrier.
+// The kernel is bound by memory latency, so resident warps are what counts: the small instantiation is held to
+// 96 registers (5 blocks = 20 warps per SM instead of 4 = 16; no spills).
 template <int J>
-__global__ void __launch_bounds__(kFinishThreads) finish_kernel(const FinishParams p) {
+__global__ void __launch_bounds__(kFinishThreads, J <= kFinishSmallJ ? 5 : 1) finish_kernel(const FinishParams p) {
   grid_dep_launch();
   grid_dep_wait();   // raw logits and value maps come from the last conv kernel
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -45,6 +45,44 @@ def reduce_rollout_stats(stats: torch.Tensor) -> torch.Tensor:
     return stats
 
 
+class RolloutStatsReducer:
+    """Per-step sum of the statistics vector over all ranks WITHOUT putting the collective on the compute
+    stream's critical path: `submit()` fills one buffer of a small ring and starts its all-reduce
+    asynchronously (NCCL runs it on its own stream, ordered after the work that produced the buffer), the
+    compute stream carries on; `drain()` waits for everything outstanding and returns the last reduced
+    vector.  A buffer is waited for before it is reused, so at most `depth` reductions are in flight.
+    With one process it degenerates to plain copies."""
+
+    def __init__(self, device: torch.device | str, fields: int = len(ROLLOUT_STATS_FIELDS), depth: int = 4) -> None:
+        self._bufs = [torch.zeros(fields, dtype=torch.int64, device=device) for _ in range(depth)]
+        self._work: list = [None] * depth
+        self._next = 0
+        self._last = 0
+        self._multi = dist.is_initialized() and dist.get_world_size() > 1
+
+    def buffer(self) -> torch.Tensor:
+        """The buffer the next submit() will reduce (write this step's statistics into it first)."""
+        k = self._next
+        if self._work[k] is not None:
+            self._work[k].wait()
+            self._work[k] = None
+        return self._bufs[k]
+
+    def submit(self) -> None:
+        k = self._next
+        if self._multi:
+            self._work[k] = dist.all_reduce(self._bufs[k], op=dist.ReduceOp.SUM, async_op=True)
+        self._last = k
+        self._next = (k + 1) % len(self._bufs)
+
+    def drain(self) -> torch.Tensor:
+        for k, w in enumerate(self._work):
+            if w is not None:
+                w.wait()
+                self._work[k] = None
+        return self._bufs[self._last]
+
+
 def max_over_ranks(value: float, device: torch.device | str = "cpu") -> float:
     """Maximum of a scalar over ranks (timing: the slowest rank defines the step)."""
     if not (dist.is_initialized() and dist.get_world_size() > 1):
@@ -59,5 +97,5 @@ def barrier() -> None:
         dist.barrier()
 
 
-__all__ = ["ROLLOUT_STATS_FIELDS", "init_from_env", "reduce_rollout_stats", "max_over_ranks", "barrier",
-           "shard_range"]
+__all__ = ["ROLLOUT_STATS_FIELDS", "RolloutStatsReducer", "init_from_env", "reduce_rollout_stats", "max_over_ranks",
+           "barrier", "shard_range"]

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is importable:
     python tests/golden/make_golden.py [/path/to/reference]
-It imports `connect6.*` from that path (default: $C6_REFERENCE or /root/reference), runs the
+It imports `connect6.*` from that path (or from $C6_REFERENCE), runs the
 reference's own functions on seeded inputs and stores inputs, weights and outputs as .npz.
 The tests only read the .npz files; they never need the reference.
 """
@@ -18,7 +18,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("C6_REFERENCE", "/root/reference"))
+if len(sys.argv) < 2 and "C6_REFERENCE" not in os.environ:
+    raise SystemExit("usage: python " + sys.argv[0] + " /path/to/the/reference/checkout   (or set C6_REFERENCE)")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["C6_REFERENCE"])
 sys.path.insert(0, str(REF))
 sys.path.insert(1, str(REPO))
 

@@ -2,8 +2,7 @@
 
 Run where the reference checkout is importable:
     python tests/golden/make_golden_env.py [/path/to/reference]
-It imports `connect6.vector_env.VectorConnect6` from that path (default: $C6_REFERENCE or
-/root/reference), plays seeded games with it on CPU and stores the actions, every step's outputs
+It imports `connect6.vector_env.VectorConnect6` from that path (or from $C6_REFERENCE), plays seeded games with it on CPU and stores the actions, every step's outputs
 and state snapshots.  The tests only read the .npz files; they never need the reference.
 
 The collector fixtures (collector_*.npz) pin the finished-game bookkeeping of the reference's
@@ -25,7 +24,9 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("C6_REFERENCE", "/root/reference"))
+if len(sys.argv) < 2 and "C6_REFERENCE" not in os.environ:
+    raise SystemExit("usage: python " + sys.argv[0] + " /path/to/the/reference/checkout   (or set C6_REFERENCE)")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["C6_REFERENCE"])
 sys.path.insert(0, str(REF))
 
 from connect6.vector_env import VectorConnect6  # noqa: E402

@@ -33,6 +33,14 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     shard.reduce_rollout_stats(stats)
     slow = shard.max_over_ranks(10.0 * (rank + 1))
     shard.barrier()
+    # the ring-buffered asynchronous reducer gives the same sums, step after step
+    red = shard.RolloutStatsReducer("cpu", depth=2)
+    for t in range(5):
+        buf = red.buffer()
+        buf.zero_()
+        buf[0] = (rank + 1) * (t + 1)
+        red.submit()
+    assert int(red.drain()[0]) == 3 * 5
     # default random stream of the drop-in samplers: same key on every rank after the same
     # torch.manual_seed, but a different first board index
     from connect6_b200 import selfplay

@@ -11,7 +11,9 @@ Only tests/, the smoke test and the CPU-baseline / reference legs of bench.py
 may import this module.
 
 Reference citations: connect6/model.py:96-111 (forward), connect6/history.py:251-303
-(grouped forward), connect6/train.py:195-203 (masked Categorical).
+(grouped forward), connect6/train.py:195-203 (masked Categorical), connect6/train.py:1047-1119 with
+connect6/model.py:104-106 (autograd backward of one backbone layer -> layer_backward; pinned by
+tests/golden/layer_backward.npz, recorded from a loss.backward() through the reference's own modules).
 """
 from __future__ import annotations
 
@@ -109,3 +111,15 @@ def env_step_torch(boards: torch.Tensor, current_player: torch.Tensor, stones_le
     current_player.copy_(torch.where(switch, -current_player, current_player))
     sign = stay.to(torch.int8) - switch.to(torch.int8)
     return won.to(torch.float32), done, winner, sign, move_count.clone()
+
+
+def layer_backward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, grad_out: torch.Tensor):
+    """What autograd computes for one backbone layer y = silu(conv2d(x, W, b, padding=k//2)) inside the
+    reference's PPO update (connect6/train.py:1047-1119 differentiating connect6/model.py:104-106):
+    (dL/dx, dL/dW, dL/db) from dL/dy, in the dtype of the arguments (use float64 for an oracle)."""
+    x = x.detach().clone().requires_grad_(True)
+    weight = weight.detach().clone().requires_grad_(True)
+    bias = bias.detach().clone().requires_grad_(True)
+    y = F.silu(F.conv2d(x, weight, bias, padding=weight.shape[-1] // 2))
+    y.backward(grad_out.to(y.dtype))
+    return x.grad, weight.grad, bias.grad

@@ -45,8 +45,54 @@ def state_hash(state: dict) -> str:
     return h.hexdigest()
 
 
+def layer_backward_fixture() -> None:
+    """One PPO-style backward through the reference's own modules (connect6/train.py:1047-1119): the
+    reference network in train mode, a loss on logits and values, loss.backward(); a hook on backbone layer
+    2 records what autograd hands that layer (its input, the gradient at its output) and what it produces
+    (gradients of its input, weight and bias)."""
+    torch.manual_seed(11)
+    net = PolicyValueNet(board_size=7, kernels=[5, 3, 3, 3], channels=[16, 24, 40, 16]).train()
+    with torch.no_grad():
+        for p in net.parameters():
+            if p.ndim == 1:
+                p.uniform_(-0.3, 0.3)
+    x = torch.from_numpy(generate_planes(0, 6, board_size=7, max_stones=30))
+    layer = net.convs[2]
+    grabbed = {}
+
+    def fwd_hook(mod, inp, out):
+        grabbed["x_in"] = inp[0].detach().clone()
+        inp[0].register_hook(lambda g: grabbed.__setitem__("dx", g.detach().clone()))
+
+    h1 = layer.register_forward_hook(fwd_hook)
+    # the SiLU module acts in place (connect6/model.py:67), so the gradient at the layer's OUTPUT is the gradient
+    # of the activation's result: hook the activation call that follows convs[2]
+    feats = x
+    acts = []
+    for i, conv in enumerate(net.convs):
+        feats = net.activation(conv(feats))
+        if i == 2:
+            feats.register_hook(lambda g: grabbed.__setitem__("dy", g.detach().clone()))
+        acts.append(feats)
+    logits = net.policy_output(feats).flatten(1)
+    value = net.value_tanh(net.value_output(feats).mean(dim=(-2, -1))).squeeze(1)
+    ref_logits, ref_value = net(x)                       # the reference's own forward gives the same numbers
+    assert torch.allclose(ref_logits, logits) and torch.allclose(ref_value, value)
+    target = torch.arange(6) * 7 % 49
+    loss = torch.nn.functional.cross_entropy(logits, target) + 0.5 * (value - 0.25).pow(2).mean()
+    net.zero_grad()
+    loss.backward()
+    h1.remove()
+    np.savez_compressed(HERE / "layer_backward.npz", x_in=grabbed["x_in"].numpy(), dy=grabbed["dy"].numpy(),
+                        dx=grabbed["dx"].numpy(), weight=layer.weight.detach().numpy(), bias=layer.bias.detach().numpy(),
+                        dw=layer.weight.grad.numpy(), db=layer.bias.grad.numpy(), torch_version=torch.__version__)
+    print("layer_backward: x_in", tuple(grabbed["x_in"].shape), "dy", tuple(grabbed["dy"].shape),
+          "|dw| max", float(layer.weight.grad.abs().max()))
+
+
 def main() -> None:
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    layer_backward_fixture()
 
     # 1. small net with an even-wider-than-board stem: weights stored, random real-valued input
     torch.manual_seed(7)

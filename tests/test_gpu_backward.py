@@ -1,7 +1,9 @@
 """Backward of one backbone layer through the C ABI (include/c6_train.h) against PyTorch autograd in fp64.
 
 The reference's PPO update differentiates y = silu(conv2d(x, W, b)) with autograd (connect6/train.py:1047-1119,
-connect6/model.py:104-106); the oracle here is exactly that, on CPU in float64.  The operator computes in bf16
+connect6/model.py:104-106); the oracle (oracle/torch_port.py:layer_backward) is exactly that, on CPU in float64,
+pinned by gradients recorded from a loss.backward() through the reference's own modules
+(tests/golden/layer_backward.npz).  The operator computes in bf16
 with fp32 accumulation, so the tolerance is stated relative to the spread of each gradient: dX carries one bf16
 rounding of dL/d(pre-activation), of the filter and of the result (measured ~5e-3 of the gradient's standard
 deviation at worst); dW and db are sums over every position of the batch, where the rounding errors average out.
@@ -12,6 +14,9 @@ import numpy as np
 import pytest
 import torch
 
+import torch_port as TP
+from conftest import load_golden
+
 pytestmark = pytest.mark.gpu
 
 DX_TOL = 3e-2     # max |error| / std(dX)
@@ -20,12 +25,20 @@ DB_TOL = 2e-2     # max |error| / max(std(db), |db| scale)
 
 
 def _oracle(x, w, b, dy):
-    x64 = x.double().requires_grad_(True)
-    w64 = w.double().requires_grad_(True)
-    b64 = b.double().requires_grad_(True)
-    y = torch.nn.functional.silu(torch.nn.functional.conv2d(x64, w64, b64, padding=w.shape[-1] // 2))
-    y.backward(dy.double())
-    return x64.grad, w64.grad, b64.grad
+    return TP.layer_backward(x.double(), w.double(), b.double(), dy.double())
+
+
+def test_conv_layer_backward_golden(cuda_device):
+    """Gradients recorded from loss.backward() through the reference's own network (one backbone layer of a
+    7x7 net, 24 -> 40 channels, 6 boards): the operator reproduces them within the bf16 tolerances."""
+    from connect6_b200.train_ops import backward_status, conv_layer_backward
+    g = load_golden("layer_backward.npz")
+    t = lambda k: torch.from_numpy(g[k]).to(cuda_device)
+    dx, dw, db = conv_layer_backward(t("x_in"), t("weight"), t("bias"), t("dy"))
+    assert backward_status(dx) == 0
+    assert np.abs(dx.cpu().numpy() - g["dx"]).max() < DX_TOL * g["dx"].std()
+    assert np.abs(dw.cpu().numpy() - g["dw"]).max() < DW_TOL * g["dw"].std()
+    assert np.abs(db.cpu().numpy() - g["db"]).max() < DB_TOL * np.abs(g["db"]).max()
 
 
 def _case(B, cin, cout, n, seed):

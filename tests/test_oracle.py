@@ -173,3 +173,16 @@ def test_bf16_emulation_is_close_to_fp32():
     assert np.abs(v_bf - g["value"]).max() < 3e-2
     r = O.bf16_round(np.array([1.0, 1.00390625, 1.0 + 2 ** -9, 3.14159], np.float32))
     assert np.array_equal(r, torch.tensor([1.0, 1.00390625, 1.0 + 2 ** -9, 3.14159]).bfloat16().float().numpy())
+
+
+def test_layer_backward_oracle_matches_reference_autograd():
+    """The backward oracle against gradients recorded from loss.backward() through the reference's own network
+    (a hook on one backbone layer: its input, the gradient at its output, the gradients it produced)."""
+    import torch
+    import torch_port as TP
+    g = load_golden("layer_backward.npz")
+    t = lambda k: torch.from_numpy(g[k])
+    dx, dw, db = TP.layer_backward(t("x_in").double(), t("weight").double(), t("bias").double(), t("dy").double())
+    for got, want in ((dx, g["dx"]), (dw, g["dw"]), (db, g["db"])):
+        scale = np.abs(want).max()
+        assert np.abs(got.numpy() - want).max() < 2e-6 * scale + 1e-12

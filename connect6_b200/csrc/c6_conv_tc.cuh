@@ -68,8 +68,7 @@ struct ConvTcParams {
   int wp, slots;         // padded row pitch Wp and slots per board S
   int bsize;             // board side n
   int nboards;           // boards per group in this pass
-  int tiles_per_group;   // tiles this launch computes per group
-  int tile0;             // first tile of this launch inside the group (a launch may cover a range of the boards)
+  int tiles_per_group;
   int tiles_per_board;   // > 0: tile t covers positions (t / tpb) * slots + (t % tpb) * 128 ... + 127 of its group
                          // (the all-padding tail of every board image is never computed); 0: tile t covers 128 t ...
   int group_pos;         // positions reserved per group in the planes
@@ -235,7 +234,6 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
   const long long group_row0 = (long long)p.front + (long long)group * p.group_pos;
   // first position (inside the group) of a tile
   auto tile_pos = [&](int tile) {
-    tile += p.tile0;
     return p.tiles_per_board ? (tile / p.tiles_per_board) * p.slots + (tile % p.tiles_per_board) * 128 : tile * 128;
   };
 

@@ -85,7 +85,6 @@ struct C6Engine {
   long long launches = 0;
   // optional per-kernel timing: event pairs recorded around every launch
   bool profiling = false;
-  int l2_chunk_boards = 0;         // boards per range of the stem / layer 1 / layer 2 interleave (0: off; multiple of 256)
   bool dependent_launch = true;    // programmatic dependent launch along the kernel chain (C6_DEPENDENT_LAUNCH=0 turns it off)
   bool wait_counters = false;      // level 2: also the in-kernel pipeline wait counters
   struct ProfRec { int kind; cudaEvent_t a, b; };
@@ -536,8 +535,8 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
       C6_LAUNCHED(e, "pack_stem_input_kernel");
     }
   }
-  // stem GEMM over board tiles [mt0, mt0 + mtiles) of every group -> act[0]
-  auto launch_stem = [&](int mt0, int mtiles) -> int {
+  // stem GEMM -> act[0]
+  auto launch_stem = [&]() -> int {
       StemTcParams p{};
       p.xk = e->xk;
       p.wt = e->wt;
@@ -558,9 +557,7 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
       p.ntot = e->ntot;
       p.nt = e->nt;
       p.ntiles = e->ntiles;
-      p.mtiles = mtiles;
-      p.mt0 = mt0;
-      p.mtiles_all = g.mrows_per_group / 128;
+      p.mtiles = g.mrows_per_group / 128;
       p.groups = e->G;
       p.c1 = e->lp[0].cout_p;
       p.bsize = e->n;
@@ -585,8 +582,8 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
       C6_LAUNCHED(e, "stem_tc_kernel");
       return C6_OK;
   };
-  // backbone layer l over tiles [tile0, tile0 + tiles) of every group: act[cur] -> act[cur ^ 1]
-  auto launch_layer = [&](int l, int tile0, int tiles) -> int {
+  // backbone layer l: act[cur] -> act[cur ^ 1]
+  auto launch_layer = [&](int l) -> int {
     const LayerPlan& lp = e->lp[l];
     ConvTcParams p{};
     p.in = e->act[cur];
@@ -614,11 +611,10 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     p.slots = e->slots;
     p.bsize = e->n;
     p.nboards = nb;
-    p.tiles_per_group = tiles;
-    p.tile0 = tile0;
+    p.tiles_per_group = g.tiles_per_group;
     p.tiles_per_board = g.tiles_per_board;
     p.group_pos = (int)g.group_pos;
-    p.ctas_per_group = std::max(1, std::min(e->sms / e->G, tiles));
+    p.ctas_per_group = std::max(1, std::min(e->sms / e->G, g.tiles_per_group));
     if (lp.pair) p.ctas_per_group = std::max(2, p.ctas_per_group & ~1);   // whole pairs (tile counts are even)
     p.w_pair = e->wconv_pair[l];
     p.resident = lp.resident;
@@ -648,36 +644,12 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     return C6_OK;
   };
   const int last = a.stop_layer >= 0 ? a.stop_layer : e->L - 1;
-  // The first three kernels are bound by HBM (the 32-channel activations are 26 KB per board).  For large
-  // single-model passes they run board range by board range -- stem, layer 1, layer 2 of one range, then the
-  // next range -- so that a range's intermediate activations (52 MB for 2048 boards) are still in the 126 MB
-  // L2 when the next kernel reads them.  Ranges end at board images, whose own zero padding is the halo, so
-  // a range needs nothing from its neighbours.  The remaining layers run over the whole pass.
-  int first_plain = 1;
-  const int cb = e->l2_chunk_boards;
   if (!direct_stem) {
-    if (cb > 0 && e->G == 1 && nb >= 2 * cb && last >= 2 && g.tiles_per_board > 0) {
-      for (int b0 = 0; b0 < nb; b0 += cb) {
-        const int nbc = std::min(cb, nb - b0);
-        const bool tail = b0 + cb >= nb;
-        const int mt0 = b0 / 128, tile0 = b0 * g.tiles_per_board;
-        int rc = launch_stem(mt0, tail ? g.mrows_per_group / 128 - mt0 : nbc / 128);
-        if (rc) return rc;
-        const int tiles = tail ? g.tiles_per_group - tile0 : nbc * g.tiles_per_board;
-        cur = 0;
-        if ((rc = launch_layer(1, tile0, tiles))) return rc;
-        cur = 1;
-        if ((rc = launch_layer(2, tile0, tiles))) return rc;
-      }
-      cur = 0;
-      first_plain = 3;
-    } else {
-      int rc = launch_stem(0, g.mrows_per_group / 128);
-      if (rc) return rc;
-    }
+    int rc = launch_stem();
+    if (rc) return rc;
   }
-  for (int l = first_plain; l <= last; ++l) {
-    int rc = launch_layer(l, 0, g.tiles_per_group);
+  for (int l = 1; l <= last; ++l) {
+    int rc = launch_layer(l);
     if (rc) return rc;
     if (!(l == e->L - 1 && a.stop_layer < 0)) cur ^= 1;
   }
@@ -894,7 +866,6 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     // k x k layers
     e->pair_mode = e->sms / e->G >= 2;   // at least one CTA pair per group
     if (const char* v = std::getenv("C6_DEPENDENT_LAUNCH")) e->dependent_launch = std::strcmp(v, "0") != 0;
-    if (const char* v = std::getenv("C6_L2_CHUNK_BOARDS")) e->l2_chunk_boards = std::max(0, std::atoi(v)) / 256 * 256;
     const int rows = conv_stage_rows(e->halo_rows);
     for (int l = 1; l < e->L; ++l) {
       LayerPlan& p = e->lp[l];

@@ -45,9 +45,7 @@ struct StemTcParams {
   int ntot;            // rows per T plane (= ntiles * nt)
   int nt;              // outputs per tile (multiple of 32, <= 256)
   int ntiles;
-  int mtiles;          // board tiles of 128 this launch computes per group (even in pair mode)
-  int mt0;             // first of them (a launch may cover a range of the boards)
-  int mtiles_all;      // board tiles per group in xk
+  int mtiles;          // per group (even in pair mode)
   int groups;
   int c1;              // padded stem output channels
   int bsize, wp, slots, nboards;
@@ -148,7 +146,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
     const long long gm = item / p.ntiles;
     const int mp = (int)(gm % mt_items);
     g = (int)(gm / mt_items);
-    mt = p.mt0 + (PAIR ? 2 * mp + (int)crank : mp);
+    mt = PAIR ? 2 * mp + (int)crank : mp;
   };
 
   if (warp == 0) {
@@ -164,7 +162,7 @@ __global__ void __launch_bounds__(kStemThreads, 1) stem_tc_kernel(const StemTcPa
       int g, mt, nt_i;
       decode(item, g, mt, nt_i);
       // tile-major operands: [board tile][K chunk][128] and [group][output tile][half][K chunk][nloc]
-      const uint4* xa = p.xk + ((size_t)g * p.mtiles_all + mt) * p.kc * 128;
+      const uint4* xa = p.xk + ((size_t)g * p.mtiles + mt) * p.kc * 128;
       const uint4* wb = p.wt + (size_t)g * p.kc * p.ntot + (((size_t)nt_i * (PAIR ? 2 : 1) + crank) * p.kc) * nloc;
       for (int ks = 0; ks < ksteps; ++ks) {
         int got = 1;

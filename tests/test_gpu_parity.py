@@ -380,25 +380,3 @@ def test_per_board_orientation_and_inverse_map(cuda_device, precision):
     assert np.abs(v_view.cpu().numpy() - vv).max() < max(tol, 1e-5)
     assert torch.equal(v_view, v_canon)
 
-
-def test_board_range_interleave_gives_identical_results(cuda_device, monkeypatch):
-    """Large single-model passes may run the stem and the first two 3x3 layers board range by board range (so
-    that a range's activations are still in L2 for the next kernel): the same tiles computed in another
-    launch order, hence bit-identical results, ragged last range included."""
-    from connect6_b200.boards import generate_planes
-    from connect6_b200.engine import Engine
-    m, params = _default_model("bf16", cuda_device)
-    x = torch.from_numpy(generate_planes(4000, 1000)).to(cuda_device)
-    monkeypatch.setenv("C6_L2_CHUNK_BOARDS", "0")
-    plain = Engine(cuda_device, 19, m.kernels, m.channels, 1, "bf16")
-    plain.load_state_dict(params)
-    want = plain.forward_step(x, seed=8, offset=2, want_logits=True)
-    for chunk, count in (("256", 1000), ("512", 1000), ("256", 777), ("256", 512)):
-        monkeypatch.setenv("C6_L2_CHUNK_BOARDS", chunk)
-        ranged = Engine(cuda_device, 19, m.kernels, m.channels, 1, "bf16")
-        ranged.load_state_dict(params)
-        got = ranged.forward_step(x[:count], seed=8, offset=2, want_logits=True)
-        for w, g in zip(want, got):
-            assert torch.equal(w[:count], g)
-        assert ranged.launch_count > plain.launch_count or count < 2 * int(chunk)
-        assert ranged.status() == 0

@@ -3,9 +3,11 @@
 // One engine = one architecture (board, kernels, channels), G stacked weight sets and one
 // arithmetic mode.  A forward call is cut into passes of at most `chunk` boards; a pass is a
 // fixed launch sequence on the caller's stream:
-//   bf16:  pack input -> stem GEMM (tcgen05) -> k x k conv layers (tcgen05, last one fused with
-//          both heads) -> finishing kernel
-//   fp32:  view copy -> direct conv layers (CUDA cores) -> head maps -> finishing kernel
+//   bf16 / fp16:  pack input -> stem GEMM (tcgen05) -> k x k conv layers (tcgen05, last one fused
+//                 with both heads) -> finishing kernel; engines with several weight sets run the
+//                 first layer of small calls straight from the filter instead (conv_tc_kernel's
+//                 stem mode behind its own pack kernel)
+//   fp32:         view copy -> direct conv layers (CUDA cores) -> head maps -> finishing kernel
 #include <cuda_runtime.h>
 
 #include <algorithm>

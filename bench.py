@@ -635,13 +635,13 @@ def run_backward(args) -> None:
     from connect6_b200.train_ops import backward_status, conv_layer_backward
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    B, cin, cout, n = args.boards if args.boards != 2048 else BATCH, 64, 96, 19
+    B, cin, cout, n = (args.boards or BATCH), 64, 96, 19
     g = torch.Generator(device=dev).manual_seed(1)
     x = torch.nn.functional.silu(torch.randn(B, cin, n, n, device=dev, generator=g))
     w = torch.randn(cout, cin, 3, 3, device=dev, generator=g) * (2.0 / (9 * cin)) ** 0.5
     b = 0.1 * torch.randn(cout, device=dev, generator=g)
     dy = torch.randn(B, cout, n, n, device=dev, generator=g) * 1e-3
-    for _ in range(max(3, args.warmup)):
+    for _ in range(args.warmup):
         conv_layer_backward(x, w, b, dy)
     torch.cuda.synchronize(dev)
     sampler = ClockSampler(0)
@@ -672,6 +672,8 @@ def run_backward(args) -> None:
 
     lib_ms = None
     try:
+        if args.no_library_bar:
+            raise RuntimeError("skipped (--no-library-bar)")
         for _ in range(3):
             lib_step()
         torch.cuda.synchronize(dev)
@@ -687,6 +689,8 @@ def run_backward(args) -> None:
     # per-kernel device times of three more calls (CUPTI through torch.profiler; outside the timed region)
     kernels = {}
     try:
+        if args.no_library_bar:
+            raise RuntimeError("skipped (--no-library-bar)")
         from torch.profiler import ProfilerActivity, profile
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             for _ in range(3):
@@ -706,7 +710,7 @@ def run_backward(args) -> None:
     achieved = algorithmic / (ms * 1e-3) / 1e12
     print(json.dumps({
         "metric": "backward of one 64->96 3x3 layer, boards/s (dX, dW, db; bf16 operands, fp32 accumulate)",
-        "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": {"workload": f"conv_layer_backward, B = {B} boards, cin 64, cout 96, 19x19; fp32 NCHW "
                                                     "tensors in and out (packing and unpacking inside the timed call)"},
@@ -730,6 +734,7 @@ def run_small_case(args) -> None:
     dev = torch.device("cuda", 0)
     torch.manual_seed(WEIGHT_SEED)
     model = PolicyValueNet(19, engine_precision=args.precision).to(dev).eval()
+    args.boards = args.boards or 2048
     x = torch.from_numpy(generate_planes(0, args.boards)).to(dev)
     for i in range(args.warmup):
         model.selfplay_step(x, seed=1, offset=i)
@@ -930,7 +935,7 @@ def main() -> None:
                          "ensemble is the reference's training shape of the historical opponents (128 models x 4 boards); "
                          "selfplay adds the environment step and bookkeeping around the network; small is a short "
                          "self-ending run of --boards boards for profilers")
-    ap.add_argument("--boards", type=int, default=2048, help="boards of --workload small")
+    ap.add_argument("--boards", type=int, default=None, help="boards of --workload small (default 2048) and backward (default 8192)")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = 20 if args.steps is None else args.steps

@@ -29,6 +29,10 @@ class PolicyValueNet(nn.Module):
     the last stone of the turn".  Output: (logits [B, n*n] unmasked, value [B] in [-1, 1]).
     Mirrors connect6/model.py:9-111.
 
+    `engine_backward=True` routes the backward of the 3x3 backbone layers in the grad-enabled forward (the PPO
+    update, connect6/train.py:1047-1119) through the library's tensor-core kernels; parameters, optimizer and
+    `loss.backward()` stay PyTorch's.
+
     `engine_precision` selects the engine's arithmetic: "bf16" (tcgen05 tensor cores, the
     default), "f16" (the same kernels with fp16 weights and activations: 11-bit significands,
     for callers that need the fp32 network's moves) or "fp32" (CUDA cores, reference-exact to
@@ -40,7 +44,8 @@ class PolicyValueNet(nn.Module):
     INPUT_CHANNELS = 3
 
     def __init__(self, board_size: int = 19, kernels: Sequence[int] | None = None,
-                 channels: Sequence[int] | None = None, engine_precision: str = "bf16") -> None:
+                 channels: Sequence[int] | None = None, engine_precision: str = "bf16",
+                 engine_backward: bool = False) -> None:
         super().__init__()
         self.board_size = int(board_size)
         self.action_size = self.board_size ** 2
@@ -59,6 +64,9 @@ class PolicyValueNet(nn.Module):
         self.kernels = ks
         self.channels = cs
         self.engine_precision = engine_precision
+        # True: in the grad-enabled forward (the PPO update) the backward of every 3x3 layer of up to 128
+        # channels runs on the library's tensor-core kernels (train_ops.SiluConv3x3) instead of cuDNN's
+        self.engine_backward = bool(engine_backward)
 
         widths = (self.input_channels,) + cs
         self.convs = nn.ModuleList(
@@ -114,8 +122,14 @@ class PolicyValueNet(nn.Module):
     def forward_autograd(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         """Differentiable forward on the PyTorch modules (training only; not the engine)."""
         feats = x
+        use_engine = self.engine_backward and x.is_cuda
+        if use_engine:
+            from .train_ops import SiluConv3x3, supports_layer
         for conv in self.convs:
-            feats = self.activation(conv(feats))
+            if use_engine and supports_layer(conv, self.board_size):
+                feats = SiluConv3x3.apply(feats, conv.weight, conv.bias)
+            else:
+                feats = self.activation(conv(feats))
         logits = self.policy_output(feats).flatten(1)
         value = self.value_tanh(self.value_output(feats).mean(dim=(-2, -1))).squeeze(1)
         return logits, value

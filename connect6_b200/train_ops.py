@@ -81,4 +81,12 @@ class SiluConv3x3(torch.autograd.Function):
     def backward(ctx, grad_out):
         x, weight, bias = ctx.saved_tensors
         dx, dw, db = conv_layer_backward(x, weight, bias, grad_out, need_dx=ctx.needs_input_grad[0])
-        return dx, dw, (db if bias is not None else None)
+        # autograd wants each gradient in its tensor's own dtype (bf16 activations under autocast, fp32 parameters)
+        return (None if dx is None else dx.to(x.dtype)), dw.to(weight.dtype), (db.to(bias.dtype) if bias is not None else None)
+
+
+def supports_layer(conv: torch.nn.Conv2d, board_size: int) -> bool:
+    """Whether `conv_layer_backward` covers this layer: 3x3, stride 1, 'same' padding, at most 128 channels."""
+    return (tuple(conv.kernel_size) == (3, 3) and tuple(conv.stride) == (1, 1) and tuple(conv.padding) == (1, 1)
+            and tuple(conv.dilation) == (1, 1) and conv.groups == 1 and conv.in_channels <= 128
+            and conv.out_channels <= 128 and board_size <= 32)

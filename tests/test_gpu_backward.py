@@ -119,3 +119,37 @@ def test_conv_layer_backward_rejects_what_it_does_not_support(cuda_device):
     dx, dw, db = conv_layer_backward(torch.zeros(0, 8, 19, 19, device=dev), torch.zeros(8, 8, 3, 3, device=dev), None,
                                      torch.zeros(0, 8, 19, 19, device=dev))
     assert dx.shape == (0, 8, 19, 19) and not dw.any() and not db.any()
+
+
+def test_whole_network_gradients_with_engine_backward(cuda_device):
+    """PolicyValueNet(engine_backward=True): a PPO-style loss.backward() whose seven 3x3 layers take the library's
+    backward gives the parameter gradients of plain autograd (fp32 on the same GPU); the stem and the heads stay on
+    autograd.  The gradient passes through up to seven bf16 layer backwards before it reaches the early layers
+    (one bf16 rounding of dL/dx per layer), so the bound is on the root-mean-square error (2 % of each gradient's
+    scale) and, for the worst of the thousands of elements of a tensor, 10 %."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.model import PolicyValueNet
+    torch.manual_seed(3)
+    plain = PolicyValueNet(19).to(cuda_device).train()
+    ours = PolicyValueNet(19, engine_backward=True).to(cuda_device).train()
+    ours.load_state_dict(plain.state_dict())
+    with torch.no_grad():                       # default-init heads (std 0.01) would leave the gradients tiny
+        for m in (plain, ours):
+            m.policy_output.weight.mul_(30.0)
+            m.value_output.weight.mul_(30.0)
+    x = torch.from_numpy(generate_planes(0, 48)).to(cuda_device)
+    target = (torch.arange(48, device=cuda_device) * 37) % 361
+    grads = []
+    for m in (plain, ours):
+        logits, value = m(x)
+        assert logits.requires_grad
+        loss = torch.nn.functional.cross_entropy(logits, target) + 0.5 * (value - 0.3).pow(2).mean()
+        m.zero_grad()
+        loss.backward()
+        grads.append({k: p.grad.detach().clone() for k, p in m.named_parameters()})
+    for name, ref in grads[0].items():
+        got = grads[1][name]
+        scale = max(ref.std().item(), ref.abs().max().item() * 0.1) if ref.numel() > 1 else abs(ref.item())
+        err = (got - ref).abs().max().item()
+        rms = (got - ref).pow(2).mean().sqrt().item()
+        assert err < 0.1 * scale and rms < 0.02 * scale, f"{name}: max {err}, rms {rms} vs scale {scale}"

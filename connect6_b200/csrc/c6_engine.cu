@@ -21,6 +21,7 @@
 #include "../../include/c6_debug.h"
 #include "../../include/c6_engine.h"
 #include "c6_aux_kernels.cuh"
+#include "c6_conv2_fused.cuh"
 #include "c6_conv_tc.cuh"
 #include "c6_fp32_kernels.cuh"
 #include "c6_host_plan.h"
@@ -87,6 +88,8 @@ struct C6Engine {
   long long launches = 0;
   // optional per-kernel timing: event pairs recorded around every launch
   bool profiling = false;
+  int fuse12 = 0;                  // layers 1 and 2 run as one kernel (conv2_fused_kernel), the intermediate in shared memory
+  int fuse12_smem = 0;
   bool dependent_launch = true;    // programmatic dependent launch along the kernel chain (C6_DEPENDENT_LAUNCH=0 turns it off)
   bool wait_counters = false;      // level 2: also the in-kernel pipeline wait counters
   struct ProfRec { int kind; cudaEvent_t a, b; };
@@ -650,7 +653,40 @@ int run_pass_bf16(C6Engine* e, const RunArgs& a, long long t0, int nb, cudaStrea
     int rc = launch_stem();
     if (rc) return rc;
   }
-  for (int l = 1; l <= last; ++l) {
+  int first_plain = 1;
+  if (e->fuse12 && last >= 2 && g.tiles_per_board > 0) {
+    // layers 1 and 2 in one kernel: act[0] -> act[1], the 32-channel intermediate stays in shared memory
+    Conv2FusedParams p{};
+    p.in = e->act[0];
+    p.out = e->act[1];
+    p.w1_pair = e->wconv_pair[1];
+    p.w2_pair = e->wconv_pair[2];
+    p.status = e->status_dev;
+    p.plane_rows = e->plane_rows;
+    p.front = e->front;
+    p.halo_rows = e->halo_rows;
+    p.cin = e->lp[1].cin_p;
+    p.c1 = e->lp[1].cout_p;
+    p.c2 = e->lp[2].cout_p;
+    p.wp = e->wp;
+    p.slots = e->slots;
+    p.bsize = e->n;
+    p.nboards = nb;
+    p.tiles_per_board = g.tiles_per_board;
+    p.board_pairs = (nb + 1) / 2;
+    std::memcpy(p.c_hb1, e->h_bias[1].data(), sizeof(p.c_hb1));
+    std::memcpy(p.c_hb2, e->h_bias[2].data(), sizeof(p.c_hb2));
+    {
+      ProfScope _ps(e, C6_KIND_CONV0 + 1, st);
+      const int grid = 2 * std::max(1, std::min(e->sms / 2, p.board_pairs));
+      launch_chain(e->f16 ? conv2_fused_kernel<true> : conv2_fused_kernel<false>, (unsigned)grid, 1u, kFusedThreads,
+                   (size_t)e->fuse12_smem, st, true, e->dependent_launch, p);
+    }
+    C6_LAUNCHED(e, "conv2_fused_kernel");
+    cur = 1;
+    first_plain = 3;
+  }
+  for (int l = first_plain; l <= last; ++l) {
     int rc = launch_layer(l);
     if (rc) return rc;
     if (!(l == e->L - 1 && a.stop_layer < 0)) cur ^= 1;
@@ -876,6 +912,20 @@ int c6_create(const C6Desc* d, C6Engine** out) {
       if ((rc = dev_alloc(e, &e->wconv[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
       if (p.pair && (rc = dev_alloc(e, &e->wconv_pair[l], (size_t)e->G * p.w_rows_per_group, true, nullptr))) return bail(rc, "");
       if ((rc = dev_alloc(e, &e->bias[l], (size_t)e->G * p.cout_p, true, nullptr))) return bail(rc, "");
+    }
+    {
+      // Layers 1 and 2 fused (narrow networks: 32 -> 32 -> at most 64 channels, 3 x 3 both, one weight set, CTA pairs,
+      // board images of at most three tiles); C6_FUSE12=0 turns it off.
+      const int used = (e->n - 1) * e->wp + e->n, tpb = (used + 127) / 128;
+      const bool shape_ok = e->L >= 4 && e->G == 1 && e->pair_mode && e->lp[1].k == 3 && e->lp[2].k == 3 && e->lp[1].cin_p == 32 &&
+                            e->lp[1].cout_p == 32 && e->lp[2].cout_p <= 64 && tpb * 128 < e->slots && tpb <= kFusedMaxTiles &&
+                            e->lp[1].pair && e->lp[2].pair;
+      e->fuse12_smem = shape_ok ? fused_smem_bytes(32, 32, e->lp[2].cout_p, tpb, e->halo_rows) : 0;
+      e->fuse12 = shape_ok && e->fuse12_smem <= kSmemLimit ? 1 : 0;
+      if (const char* v = std::getenv("C6_FUSE12")) e->fuse12 = e->fuse12 && std::strcmp(v, "0") != 0;
+      if (e->fuse12 && (cudaFuncSetAttribute(conv2_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
+                        cudaFuncSetAttribute(conv2_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess))
+        return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
     }
     {
       // Direct stem for passes with few boards per weight set.  Input images: pitch wi >= n + k0/2 so that the

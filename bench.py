@@ -37,8 +37,8 @@ CONV_LAYER_MACS = [18_333_024, 3_326_976, 6_653_952, 13_307_904, 13_307_904, 19_
 HEAD_MACS = 69_312
 INPUT_BUFFERS = 5                       # 5 x 35.5 MB of inputs rotate: larger than the 126 MB L2
 # DRAM traffic of conv_tc_kernel per launch, from the ncu capture summarised under profiles/
-# (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the 7 launches of one step).
-CONV_TRAFFIC_BYTES_PER_LAUNCH = 626_000_000   # 156.5 MB measured at B = 2048, scaled by boards to 8192
+# (dram__bytes_read.sum + dram__bytes_write.sum per layer at B = 2048, scaled by boards to 8192).
+CONV_TRAFFIC_MB_B2048 = [59.4, 95.0, 154.8, 155.2, 202.4, 261.8, 166.6]   # backbone layers 1..7, one launch each
 WEIGHT_SEED = 42
 CPU_SAMPLE_BOARDS = 256
 
@@ -433,9 +433,16 @@ def run_engine(args) -> None:
     ms_per_step = elapsed_ms / args.steps
     # dominant kernel: the backbone layers after the stem (7 launches per step): conv_tc_kernel on the
     # tensor cores, conv_fp32_kernel on the CUDA cores in fp32 mode
-    conv_ms = sum(ms for k, (ms, n) in prof.items() if k.startswith("conv"))
-    conv_launches = sum(n for k, (ms, n) in prof.items() if k.startswith("conv"))
-    conv_flop_per_step = 2 * (sum(CONV_LAYER_MACS[1:]) + (HEAD_MACS if precision != "fp32" else 0)) * BATCH
+    # Layers l and l + 1 that run as one launch of conv2_fused_kernel are recorded as "conv<l>" with no "conv<l+1>"
+    # entry.  The roofline covers the conv_tc_kernel launches that follow the fused pairs (layers 5-7 of the default
+    # network); the fused launches are reported under "kernels".
+    fused_first = [l for l in (1, 3, 5) if precision != "fp32" and f"conv{l}" in prof and f"conv{l + 1}" not in prof]
+    first_tc = max(fused_first) + 2 if fused_first else 1
+    tc_keys = [k for k in prof if k.startswith("conv") and int(k[4:]) >= first_tc]
+    conv_ms = sum(prof[k][0] for k in tc_keys)
+    conv_launches = sum(prof[k][1] for k in tc_keys)
+    conv_flop_per_step = 2 * (sum(CONV_LAYER_MACS[first_tc:]) + (HEAD_MACS if precision != "fp32" else 0)) * BATCH
+    conv_traffic = int(sum(CONV_TRAFFIC_MB_B2048[first_tc - 1:]) / (8 - first_tc) * 1e6 * BATCH / 2048)
     burst = float(peaks["bf16_tflops"])
     if precision == "fp32":
         # no measured fp32 figure exists for this pool: nominal FMA rate, 148 SMs x 128 lanes x 2 x max SM clock
@@ -449,11 +456,11 @@ def run_engine(args) -> None:
         flop_per_launch = conv_flop_per_step * sampled_steps / conv_launches
         achieved = flop_per_launch / (avg_ms * 1e-3) / 1e12
         roof = {"bound": "tensor" if precision != "fp32" else "fp32 FMA (CUDA cores)",
-                "kernel": ("conv_tc_kernel (backbone layers 1-7 + fused heads)" if precision != "fp32"
+                "kernel": (f"conv_tc_kernel (backbone layers {first_tc}-7 + fused heads)" if precision != "fp32"
                            else "conv_fp32_kernel (backbone layers 1-7)"),
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": peak_source,
-                "traffic": CONV_TRAFFIC_BYTES_PER_LAUNCH if precision != "fp32" else None,
+                "traffic": conv_traffic if precision != "fp32" else None,
                 "launches": conv_launches, "avg_launch_ms": avg_ms,
                 "timed_with": f"CUDA events around every launch of {sampled_steps} of the {args.steps} timed steps",
                 "flop_per_launch": flop_per_launch}
@@ -469,6 +476,9 @@ def run_engine(args) -> None:
         elif k.startswith("conv"):
             li = int(k[4:])
             macs = CONV_LAYER_MACS[li] + (HEAD_MACS if li == 7 else 0)
+            if li in fused_first:
+                macs += CONV_LAYER_MACS[li + 1]
+                entry["kernel"] = f"conv2_fused_kernel (layers {li} + {li + 1}, intermediate in shared memory)"
             entry["tflops_nominal"] = 2 * macs * BATCH / (ms / sampled_steps * 1e-3) / 1e12
         kernels[k] = entry
     whole_tflops = value / world * FLOP_PER_BOARD / 1e12

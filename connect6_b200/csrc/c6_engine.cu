@@ -915,14 +915,14 @@ int c6_create(const C6Desc* d, C6Engine** out) {
     }
     {
       // Layers 1 and 2 fused (narrow networks: 32 -> 32 -> at most 64 channels, 3 x 3 both, one weight set, CTA pairs,
-      // board images of at most three tiles); C6_FUSE12=0 turns it off.
+      // board images of at most three tiles); C6_FUSE_PAIRS=0 turns it off.
       const int used = (e->n - 1) * e->wp + e->n, tpb = (used + 127) / 128;
       const bool shape_ok = e->L >= 4 && e->G == 1 && e->pair_mode && e->lp[1].k == 3 && e->lp[2].k == 3 && e->lp[1].cin_p == 32 &&
                             e->lp[1].cout_p == 32 && e->lp[2].cout_p <= 64 && tpb * 128 < e->slots && tpb <= kFusedMaxTiles &&
                             e->lp[1].pair && e->lp[2].pair;
       e->fuse12_smem = shape_ok ? fused_smem_bytes(32, 32, e->lp[2].cout_p, tpb, e->halo_rows) : 0;
       e->fuse12 = shape_ok && e->fuse12_smem <= kSmemLimit ? 1 : 0;
-      if (const char* v = std::getenv("C6_FUSE12")) e->fuse12 = e->fuse12 && std::strcmp(v, "0") != 0;
+      if (const char* v = std::getenv("C6_FUSE_PAIRS")) e->fuse12 = e->fuse12 && std::strcmp(v, "0") != 0;
       if (e->fuse12 && (cudaFuncSetAttribute(conv2_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess ||
                         cudaFuncSetAttribute(conv2_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess))
         return bail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");

@@ -385,23 +385,24 @@ def test_per_board_orientation_and_inverse_map(cuda_device, precision):
 @pytest.mark.parametrize("precision", ["bf16", "f16"])
 def test_fused_layer_pair_equals_separate_layers(cuda_device, precision, monkeypatch):
     """Layers 1 and 2 of the default network run as one kernel with the 32-channel intermediate in shared memory
-    (conv2_fused_kernel); C6_FUSE12=0 runs them as two launches.  Same MMAs in the same order, same epilogue
-    arithmetic: the results must be bit-identical, for odd board counts (half-used CTA pairs) and for batches
-    that leave most CTAs without work as well."""
+    (conv2_fused_kernel); C6_FUSE_PAIRS=0 runs every layer as its own launch.  Same MMAs in the same order, same
+    epilogue arithmetic: the results must be bit-identical, for odd board counts (half-used CTA pairs) and for
+    batches that leave most CTAs without work as well."""
     from connect6_b200.boards import generate_planes
     from connect6_b200.engine import Engine
     m, params = _default_model(precision, cuda_device)
     fused = m.engine_for(cuda_device)
-    monkeypatch.setenv("C6_FUSE12", "0")
+    monkeypatch.setenv("C6_FUSE_PAIRS", "0")
     plain = Engine(cuda_device, 19, m.kernels, m.channels, 1, precision)
     plain.load_state_dict(params)
-    monkeypatch.delenv("C6_FUSE12")
+    monkeypatch.delenv("C6_FUSE_PAIRS")
     x = torch.from_numpy(generate_planes(9000, 1501)).to(cuda_device)
     for b in (1501, 1, 2, 3, 147, 148, 149, 600):
         got = fused.forward_step(x[:b], seed=3, offset=7, want_logits=True)
         want = plain.forward_step(x[:b], seed=3, offset=7, want_logits=True)
         for g, w in zip(got, want):
             assert torch.equal(g, w), b
-        assert torch.equal(fused.layer_output(x[:b], 2), plain.layer_output(x[:b], 2))
-    assert fused.launch_count < plain.launch_count
+        for layer in (2, 4):
+            assert torch.equal(fused.layer_output(x[:b], layer), plain.layer_output(x[:b], layer)), (b, layer)
+    assert fused.launch_count < plain.launch_count   # one launch fewer per forward
     assert fused.status() == 0 and plain.status() == 0

@@ -1,5 +1,6 @@
-// Training-side operators (include/c6_train.h): the backward pass of one backbone layer.  Host code,
-// compiled as part of c6_engine.cu (one translation unit: the helper kernels are shared).
+// Training-side operators (include/c6_train.h): the backward pass of one backbone layer, and forward + backward of
+// a whole stack of 3 x 3 layers with the activations and gradients kept in the kernels' own plane layout between
+// layers.  Host code, compiled as part of c6_engine.cu (one translation unit: the helper kernels are shared).
 //
 // Launch sequence of c6_conv_layer_backward on the caller's stream:
 //   pack filter (forward layout and the flipped / transposed one), pack x and dy into channel-chunk planes
@@ -157,14 +158,117 @@ int launch_conv(const BackwardLayout& L, const LayerPlan& lp, int epi, const uin
   p.acc_stride = lp.acc_stride;
   p.nacc = lp.nacc;
   p.tmem_cols = lp.tmem_cols;
-  ConvKernel kernel = lp.pair ? (epi == kEpiDsilu ? conv_tc_kernel<3, true, false, false, kEpiDsilu>
-                                                  : conv_tc_kernel<3, true, false, false, kEpiLinear>)
-                              : (epi == kEpiDsilu ? conv_tc_kernel<3, false, false, false, kEpiDsilu>
-                                                  : conv_tc_kernel<3, false, false, false, kEpiLinear>);
+  ConvKernel kernel = lp.pair ? (epi == kEpiDsilu   ? conv_tc_kernel<3, true, false, false, kEpiDsilu>
+                                 : epi == kEpiLinear ? conv_tc_kernel<3, true, false, false, kEpiLinear>
+                                                     : conv_tc_kernel<3, true, false, false, kEpiSilu>)
+                              : (epi == kEpiDsilu   ? conv_tc_kernel<3, false, false, false, kEpiDsilu>
+                                 : epi == kEpiLinear ? conv_tc_kernel<3, false, false, false, kEpiLinear>
+                                                     : conv_tc_kernel<3, false, false, false, kEpiSilu>);
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
     return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   launch_chain(kernel, (unsigned)p.ctas_per_group, 1u, kConvThreads, (size_t)lp.smem, st, lp.pair != 0, false, p);
   C6T_LAUNCHED("conv_tc_kernel (backward)");
+  return C6_OK;
+}
+
+
+// dW = sum over positions of dPre (x) shifted x: wgrad_tc_kernel into per-slab partial sums, then the fixed-order reduction.
+int launch_wgrad(const BackwardLayout& L, const uint4* xp, const uint4* dpre, float* partial, float* dw, int* status,
+                 cudaStream_t st) {
+  const int taps = L.k * L.k;
+  WgradParams p{};
+  p.x = xp;
+  p.dpre = dpre;
+  p.partial = partial;
+  p.status = status;
+  p.plane_rows = L.plane_rows;
+  p.front = L.front;
+  p.halo_rows = L.halo_rows;
+  p.cin = L.cin_p;
+  p.cout = L.cout_p;
+  p.kside = L.k;
+  p.wp = L.wp;
+  p.tile_rows = L.wg_tile_rows;
+  p.ntiles = L.wg_tiles;
+  p.ntaps = taps;
+  p.taps_per_cta = L.wg_taps_per_cta;
+  p.ngroups = L.wg_groups;
+  p.nslabs = L.wg_slabs;          // planned for 148 SMs: the partial-sum buffer is sized for it
+  p.nstages = L.wg_stages;
+  if (cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+    return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+  wgrad_tc_kernel<<<(unsigned)(p.ngroups * p.nslabs), kWgradThreads, (size_t)L.wg_smem, st>>>(p);
+  C6T_LAUNCHED("wgrad_tc_kernel");
+  const long long total = (long long)L.cout * L.cin * taps;
+  wgrad_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, dw, p.nslabs, taps, L.cin_p, L.cin, L.cout);
+  C6T_LAUNCHED("wgrad_reduce_kernel");
+  return C6_OK;
+}
+
+// A stack of consecutive 3 x 3 layers (the backbone after the stem) differentiated as a whole: every layer's input
+// activation is kept as channel-chunk planes by the forward call, gradients travel between layers in the same layout.
+struct StackLayout {
+  bool ok = false;
+  int L = 0, cmax_p = 0;
+  BackwardLayout lay[C6_MAX_LAYERS];      // per layer: pipeline plans; the board geometry is the same for all
+  size_t off_bias[C6_MAX_LAYERS] = {}, off_wf[C6_MAX_LAYERS] = {}, off_wf_pair[C6_MAX_LAYERS] = {}, off_wd[C6_MAX_LAYERS] = {},
+         off_wd_pair[C6_MAX_LAYERS] = {}, off_act[C6_MAX_LAYERS + 1] = {};
+  size_t off_zero = 0, off_grad[2] = {}, off_dpre = 0, off_partial = 0, off_colsum = 0, total = 0;
+};
+
+StackLayout make_stack_layout(int n, int nlayers, const int32_t* channels, long long B) {
+  StackLayout S;
+  if (nlayers < 1 || nlayers > C6_MAX_LAYERS || !channels) return S;
+  S.L = nlayers;
+  size_t partial_max = 0, colsum_max = 0;
+  for (int l = 0; l < nlayers; ++l) {
+    S.lay[l] = make_layout(n, 3, channels[l], channels[l + 1], B, 148);
+    if (!S.lay[l].ok) return S;
+    S.cmax_p = std::max(S.cmax_p, std::max(S.lay[l].cin_p, S.lay[l].cout_p));
+    partial_max = std::max(partial_max, (size_t)S.lay[l].wg_slabs * 9 * 128 * S.lay[l].cin_p * 4);
+    colsum_max = std::max(colsum_max, (size_t)(S.lay[l].cout_p / 8) * kColsumSlices * 8 * 4);
+  }
+  const long long plane_rows = S.lay[0].plane_rows;
+  auto take = [&](size_t bytes) { size_t o = S.total; S.total += (bytes + 255) & ~(size_t)255; return o; };
+  take(256);                                                // status word
+  S.off_zero = take((size_t)S.cmax_p * 4);
+  for (int l = 0; l < nlayers; ++l) {
+    const BackwardLayout& L = S.lay[l];
+    S.off_bias[l] = take((size_t)L.cout_p * 4);
+    S.off_wf[l] = take(L.fwd.w_rows_per_group * 16);
+    S.off_wf_pair[l] = take(L.fwd.w_rows_per_group * 16);
+    S.off_wd[l] = take(L.dgrad.w_rows_per_group * 16);
+    S.off_wd_pair[l] = take(L.dgrad.w_rows_per_group * 16);
+  }
+  for (int l = 0; l <= nlayers; ++l) {
+    const int cp = l < nlayers ? S.lay[l].cin_p : S.lay[l - 1].cout_p;
+    S.off_act[l] = take((size_t)(cp / 8) * plane_rows * 16);
+  }
+  S.off_grad[0] = take((size_t)(S.cmax_p / 8) * plane_rows * 16);
+  S.off_grad[1] = take((size_t)(S.cmax_p / 8) * plane_rows * 16);
+  S.off_dpre = take((size_t)(S.cmax_p / 8) * plane_rows * 16);
+  S.off_partial = take(partial_max);
+  S.off_colsum = take(colsum_max);
+  S.ok = true;
+  return S;
+}
+
+int check_stack_call(int32_t device, const StackLayout& S, void* workspace, int64_t workspace_bytes, int* sms) {
+  if (!S.ok) return tfail(C6_ERR_UNSUPPORTED, "the backbone operators support 1..16 layers of 3 x 3, board_size <= 32, at most 128 channels");
+  if (!workspace) return tfail(C6_ERR_ARG, "null pointer");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return tfail(C6_ERR_ARG, "workspace must be 256-byte aligned");
+  if (workspace_bytes < (int64_t)S.total) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "workspace of %lld bytes is smaller than the %zu this shape needs", (long long)workspace_bytes, S.total);
+    return tfail(C6_ERR_ARG, buf);
+  }
+  int ndev = 0, major = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev)
+    return tfail(C6_ERR_CUDA, "no such CUDA device (this operator has no CPU path)");
+  C6T_CUDA(cudaSetDevice(device));
+  C6T_CUDA(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, device));
+  C6T_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  if (major != 10) return tfail(C6_ERR_UNSUPPORTED, "the backward operators need an sm_100 GPU (tcgen05 tensor cores)");
   return C6_OK;
 }
 
@@ -263,33 +367,128 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
     C6T_LAUNCHED("unpack_planes_nchw_kernel");
   }
   // dW
+  rc = launch_wgrad(L, xp, dpre, partial, dw, status, st);
+  if (rc) return rc;
+  return C6_OK;
+}
+
+int64_t c6_backbone_workspace_bytes(int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B) {
+  if (B < 1) return 0;
+  const StackLayout S = make_stack_layout(board_size, nlayers, channels, B);
+  return S.ok ? (int64_t)S.total : 0;
+}
+
+int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B,
+                        const float* x, const float* const* w, const float* const* bias, float* y, void* workspace,
+                        int64_t workspace_bytes, void* stream) {
+  if (B < 1) return tfail(C6_ERR_ARG, "board count must be positive");
+  if (!x || !w || !bias || !y || !channels) return tfail(C6_ERR_ARG, "null pointer");
+  const StackLayout S = make_stack_layout(board_size, nlayers, channels, B);
+  int sms = 0;
+  int rc = check_stack_call(device, S, workspace, workspace_bytes, &sms);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  int* status = reinterpret_cast<int*>(ws);
+  for (int l = 0; l < nlayers; ++l) {
+    const BackwardLayout& L = S.lay[l];
+    if (!w[l]) return tfail(C6_ERR_ARG, "null weight pointer");
+    float* bias_f = reinterpret_cast<float*>(ws + S.off_bias[l]);
+    copy_pad_f32_kernel<<<(L.cout_p + 127) / 128, 128, 0, st>>>(bias[l], bias_f, L.cout, L.cout_p);
+    C6T_LAUNCHED("copy_pad_f32_kernel");
+    const long long rows = (long long)L.fwd.w_rows_per_group, drows = (long long)L.dgrad.w_rows_per_group;
+    pack_conv_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+        w[l], reinterpret_cast<uint4*>(ws + S.off_wf[l]), L.cout, L.cin, 3, L.cout_p, L.cin_p, 0);
+    C6T_LAUNCHED("pack_conv_weights_kernel");
+    pack_conv_weights_pair_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+        w[l], reinterpret_cast<uint4*>(ws + S.off_wf_pair[l]), L.cout, L.cin, 3, L.cout_p, L.cin_p, 0);
+    C6T_LAUNCHED("pack_conv_weights_pair_kernel");
+    pack_dgrad_weights_kernel<<<(unsigned)((drows + 255) / 256), 256, 0, st>>>(
+        w[l], reinterpret_cast<uint4*>(ws + S.off_wd[l]), L.cout, L.cin, 3, L.cout_p, L.cin_p, 1);
+    C6T_LAUNCHED("pack_dgrad_weights_kernel");
+    pack_dgrad_weights_kernel<<<(unsigned)((drows + 255) / 256), 256, 0, st>>>(
+        w[l], reinterpret_cast<uint4*>(ws + S.off_wd_pair[l]), L.cout, L.cin, 3, L.cout_p, L.cin_p, 2);
+    C6T_LAUNCHED("pack_dgrad_weights_kernel");
+  }
+  const BackwardLayout& L0 = S.lay[0];
   {
-    WgradParams p{};
-    p.x = xp;
-    p.dpre = dpre;
-    p.partial = partial;
-    p.status = status;
-    p.plane_rows = L.plane_rows;
-    p.front = L.front;
-    p.halo_rows = L.halo_rows;
-    p.cin = L.cin_p;
-    p.cout = L.cout_p;
-    p.kside = kside;
-    p.wp = L.wp;
-    p.tile_rows = L.wg_tile_rows;
-    p.ntiles = L.wg_tiles;
-    p.ntaps = taps;
-    p.taps_per_cta = L.wg_taps_per_cta;
-    p.ngroups = L.wg_groups;
-    p.nslabs = L.wg_slabs;          // planned for 148 SMs: the partial-sum buffer is sized for it
-    p.nstages = L.wg_stages;
-    if (cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
-      return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
-    wgrad_tc_kernel<<<(unsigned)(p.ngroups * p.nslabs), kWgradThreads, (size_t)L.wg_smem, st>>>(p);
-    C6T_LAUNCHED("wgrad_tc_kernel");
-    const long long total = (long long)cout * cin * taps;
-    wgrad_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, dw, p.nslabs, taps, L.cin_p, cin, cout);
-    C6T_LAUNCHED("wgrad_reduce_kernel");
+    const long long t = B * L0.slots * (L0.cin_p / 8);
+    pack_nchw_planes_kernel<<<(unsigned)((t + 255) / 256), 256, 0, st>>>(
+        x, reinterpret_cast<uint4*>(ws + S.off_act[0]), L0.plane_rows, L0.front, L0.slots, L0.wp, L0.n, L0.cin, L0.cin_p, B);
+    C6T_LAUNCHED("pack_nchw_planes_kernel");
+  }
+  for (int l = 0; l < nlayers; ++l) {
+    const BackwardLayout& L = S.lay[l];
+    rc = launch_conv(L, L.fwd, kEpiSilu, reinterpret_cast<const uint4*>(ws + S.off_act[l]),
+                     reinterpret_cast<uint4*>(ws + S.off_act[l + 1]), nullptr, reinterpret_cast<const uint4*>(ws + S.off_wf[l]),
+                     reinterpret_cast<const uint4*>(ws + S.off_wf_pair[l]), reinterpret_cast<const float*>(ws + S.off_bias[l]),
+                     status, sms, st);
+    if (rc) return rc;
+  }
+  {
+    const BackwardLayout& L = S.lay[nlayers - 1];
+    const long long total = B * ((L.cout + 7) / 8) * L.n * L.n;
+    unpack_planes_nchw_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+        reinterpret_cast<const uint4*>(ws + S.off_act[nlayers]), L.plane_rows, L.front, L.slots, L.wp, L.n, L.cout, B, y);
+    C6T_LAUNCHED("unpack_planes_nchw_kernel");
+  }
+  return C6_OK;
+}
+
+int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B,
+                         const float* dy, float* dx, float* const* dw, float* const* db, void* workspace,
+                         int64_t workspace_bytes, void* stream) {
+  if (B < 1) return tfail(C6_ERR_ARG, "board count must be positive");
+  if (!dy || !dw || !db || !channels) return tfail(C6_ERR_ARG, "null pointer");
+  const StackLayout S = make_stack_layout(board_size, nlayers, channels, B);
+  int sms = 0;
+  int rc = check_stack_call(device, S, workspace, workspace_bytes, &sms);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  int* status = reinterpret_cast<int*>(ws);
+  const float* zero_f = reinterpret_cast<const float*>(ws + S.off_zero);
+  uint4* dpre = reinterpret_cast<uint4*>(ws + S.off_dpre);
+  float* partial = reinterpret_cast<float*>(ws + S.off_partial);
+  float* colsum = reinterpret_cast<float*>(ws + S.off_colsum);
+  int cur = 0;
+  {
+    const BackwardLayout& L = S.lay[nlayers - 1];
+    const long long t = B * L.slots * (L.cout_p / 8);
+    pack_nchw_planes_kernel<<<(unsigned)((t + 255) / 256), 256, 0, st>>>(
+        dy, reinterpret_cast<uint4*>(ws + S.off_grad[cur]), L.plane_rows, L.front, L.slots, L.wp, L.n, L.cout, L.cout_p, B);
+    C6T_LAUNCHED("pack_nchw_planes_kernel");
+  }
+  for (int l = nlayers - 1; l >= 0; --l) {
+    const BackwardLayout& L = S.lay[l];
+    if (!dw[l] || !db[l]) return tfail(C6_ERR_ARG, "null gradient pointer");
+    const uint4* act = reinterpret_cast<const uint4*>(ws + S.off_act[l]);
+    // dPre = dY * silu'(conv(act, W) + b)
+    rc = launch_conv(L, L.fwd, kEpiDsilu, act, dpre, reinterpret_cast<const uint4*>(ws + S.off_grad[cur]),
+                     reinterpret_cast<const uint4*>(ws + S.off_wf[l]), reinterpret_cast<const uint4*>(ws + S.off_wf_pair[l]),
+                     reinterpret_cast<const float*>(ws + S.off_bias[l]), status, sms, st);
+    if (rc) return rc;
+    colsum_planes_kernel<<<dim3((unsigned)(L.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre, L.plane_rows, L.front,
+                                                                                                    L.total_pos, kColsumSlices, colsum);
+    C6T_LAUNCHED("colsum_planes_kernel");
+    colsum_finish_kernel<<<(L.cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, L.cout, db[l]);
+    C6T_LAUNCHED("colsum_finish_kernel");
+    rc = launch_wgrad(L, act, dpre, partial, dw[l], status, st);
+    if (rc) return rc;
+    if (l > 0 || dx) {
+      rc = launch_conv(L, L.dgrad, kEpiLinear, dpre, reinterpret_cast<uint4*>(ws + S.off_grad[cur ^ 1]), nullptr,
+                       reinterpret_cast<const uint4*>(ws + S.off_wd[l]), reinterpret_cast<const uint4*>(ws + S.off_wd_pair[l]),
+                       zero_f, status, sms, st);
+      if (rc) return rc;
+      cur ^= 1;
+    }
+  }
+  if (dx) {
+    const BackwardLayout& L = S.lay[0];
+    const long long total = B * ((L.cin + 7) / 8) * L.n * L.n;
+    unpack_planes_nchw_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+        reinterpret_cast<const uint4*>(ws + S.off_grad[cur]), L.plane_rows, L.front, L.slots, L.wp, L.n, L.cin, B, dx);
+    C6T_LAUNCHED("unpack_planes_nchw_kernel");
   }
   return C6_OK;
 }

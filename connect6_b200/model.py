@@ -123,9 +123,19 @@ class PolicyValueNet(nn.Module):
         """Differentiable forward on the PyTorch modules (training only; not the engine)."""
         feats = x
         use_engine = self.engine_backward and x.is_cuda
+        convs = list(self.convs)
         if use_engine:
-            from .train_ops import SiluConv3x3, supports_layer
-        for conv in self.convs:
+            from .train_ops import SiluConv3x3, SiluConvStack, supports_layer
+            # the longest run of library-supported 3x3 layers that ends at the last layer goes through the library as
+            # ONE operator (forward and backward, activations kept in the kernels' layout); layers before it one by one
+            first = len(convs)
+            while first > 0 and supports_layer(convs[first - 1], self.board_size):
+                first -= 1
+        for i, conv in enumerate(convs):
+            if use_engine and i == first and len(convs) - first >= 2 and x.shape[0] > 0:
+                params = [p for c in convs[first:] for p in (c.weight, c.bias)]
+                feats = SiluConvStack.apply(feats, *params)
+                break
             if use_engine and supports_layer(conv, self.board_size):
                 feats = SiluConv3x3.apply(feats, conv.weight, conv.bias)
             else:

@@ -5,9 +5,14 @@ The reference differentiates its network with PyTorch autograd inside the PPO mi
 y = silu(conv2d(x, W, b)) (connect6/model.py:104-106) on tcgen05 tensor cores: dX, dW and db from x, W, b
 and dL/dy.  `SiluConv3x3` wraps it as a torch.autograd.Function whose forward is PyTorch's own (the
 parameters stay ordinary nn.Parameters), so a layer can be switched over without touching the optimizer.
+`SiluConvStack` does forward AND backward of a whole run of consecutive 3x3 layers in the library: the
+forward keeps every layer's input in the kernels' own 16-bit plane layout, the backward walks the stack
+with the gradient in that layout, and only the ends of the stack are NCHW tensors.
 CUDA only: there is no CPU implementation in this package.
 """
 from __future__ import annotations
+
+import ctypes as C
 
 import torch
 
@@ -90,3 +95,127 @@ def supports_layer(conv: torch.nn.Conv2d, board_size: int) -> bool:
     return (tuple(conv.kernel_size) == (3, 3) and tuple(conv.stride) == (1, 1) and tuple(conv.padding) == (1, 1)
             and tuple(conv.dilation) == (1, 1) and conv.groups == 1 and conv.in_channels <= 128
             and conv.out_channels <= 128 and board_size <= 32)
+
+
+# ---- a stack of 3x3 layers ---------------------------------------------------------------------------
+_stack_pool: dict[tuple, list[torch.Tensor]] = {}
+
+
+class _StackLease:
+    """A zero-initialised workspace of one stack shape, taken from a pool for the time between a forward call
+    and the end of its autograd graph; handed back when the lease is garbage-collected.  The operators keep the
+    zero padding they rely on intact, so a returned buffer is reused without clearing."""
+
+    def __init__(self, device: torch.device, n: int, channels: tuple[int, ...], B: int) -> None:
+        self.key = (device.index, n, channels, B)
+        pool = _stack_pool.setdefault(self.key, [])
+        if pool:
+            self.ws = pool.pop()
+        else:
+            arr = (C.c_int32 * len(channels))(*channels)
+            need = int(L.load().c6_backbone_workspace_bytes(n, len(channels) - 1, arr, B))
+            if need == 0:
+                raise ValueError(f"SiluConvStack supports 1..16 layers of 3x3, board size <= 32, at most 128 channels; "
+                                 f"got n={n}, channels={channels}")
+            self.ws = torch.zeros((need + 7) // 8, dtype=torch.int64, device=device)
+
+    def __del__(self) -> None:
+        try:
+            pool = _stack_pool.setdefault(self.key, [])
+            if len(pool) < 2:
+                pool.append(self.ws)
+        except Exception:   # interpreter shutdown
+            pass
+
+
+def _ptr_array(tensors) -> "C.Array":
+    return (C.c_void_p * len(tensors))(*[None if t is None else t.data_ptr() for t in tensors])
+
+
+def _train_fail(rc: int, what: str):
+    msg = L.load().c6_train_last_error().decode("utf-8", "replace")
+    return (ValueError if rc in (L.C6_ERR_ARG, L.C6_ERR_UNSUPPORTED) else RuntimeError)(f"{what} failed: {msg}")
+
+
+def stack_forward(x: torch.Tensor, weights, biases):
+    """y = the layers y_l = silu(conv2d(y_{l-1}, weights[l], biases[l], padding=1)) applied in turn to x
+    [B, c0, n, n]; returns (y fp32 [B, cL, n, n], lease) -- the lease holds the saved activations for
+    `stack_backward`."""
+    if not x.is_cuda:
+        raise RuntimeError(f"stack_forward: expected CUDA tensors, got {x.device} (no CPU path in this package)")
+    if x.ndim != 4 or x.shape[2] != x.shape[3] or len(weights) != len(biases) or not weights:
+        raise ValueError("stack_forward: x [B,c0,n,n], one weight [c_out,c_in,3,3] and one bias (or None) per layer")
+    B, c0, n, _ = x.shape
+    channels = [c0]
+    for w, b in zip(weights, biases):
+        if w.ndim != 4 or tuple(w.shape[1:]) != (channels[-1], 3, 3) or (b is not None and tuple(b.shape) != (w.shape[0],)):
+            raise ValueError("stack_forward: the layers' shapes do not chain (3x3 filters, c_in of a layer = c_out of the one before)")
+        channels.append(int(w.shape[0]))
+    if B == 0:
+        return x.new_zeros((0, channels[-1], n, n), dtype=torch.float32), None
+    dev = x.device
+    f32 = lambda t: None if t is None else t.detach().to(device=dev, dtype=torch.float32).contiguous()
+    x = f32(x)
+    ws_ = [f32(w) for w in weights]
+    bs_ = [f32(b) for b in biases]
+    lease = _StackLease(dev, n, tuple(channels), B)
+    y = torch.empty((B, channels[-1], n, n), device=dev, dtype=torch.float32)
+    arr = (C.c_int32 * len(channels))(*channels)
+    with torch.cuda.device(dev):
+        rc = L.load().c6_backbone_forward(dev.index, n, len(ws_), arr, B, x.data_ptr(), _ptr_array(ws_), _ptr_array(bs_),
+                                          y.data_ptr(), lease.ws.data_ptr(), lease.ws.numel() * 8,
+                                          torch.cuda.current_stream(dev).cuda_stream)
+    if rc != L.C6_OK:
+        raise _train_fail(rc, "c6_backbone_forward")
+    return y, lease
+
+
+def stack_backward(lease: _StackLease, grad_out: torch.Tensor, need_dx: bool = True):
+    """(dx or None, [dw_l], [db_l]) of the stack whose forward produced `lease`, given grad_out = dL/dy."""
+    dev_index, n, channels, B = lease.key
+    dev = grad_out.device
+    if not grad_out.is_cuda or dev.index != dev_index or tuple(grad_out.shape) != (B, channels[-1], n, n):
+        raise ValueError("stack_backward: grad_out does not belong to this forward call")
+    grad_out = grad_out.detach().to(dtype=torch.float32).contiguous()
+    dx = torch.empty((B, channels[0], n, n), device=dev, dtype=torch.float32) if need_dx else None
+    dws = [torch.empty((channels[l + 1], channels[l], 3, 3), device=dev, dtype=torch.float32) for l in range(len(channels) - 1)]
+    dbs = [torch.empty(channels[l + 1], device=dev, dtype=torch.float32) for l in range(len(channels) - 1)]
+    arr = (C.c_int32 * len(channels))(*channels)
+    with torch.cuda.device(dev):
+        rc = L.load().c6_backbone_backward(dev_index, n, len(dws), arr, B, grad_out.data_ptr(), L.ptr(dx), _ptr_array(dws),
+                                           _ptr_array(dbs), lease.ws.data_ptr(), lease.ws.numel() * 8,
+                                           torch.cuda.current_stream(dev).cuda_stream)
+    if rc != L.C6_OK:
+        raise _train_fail(rc, "c6_backbone_backward")
+    return dx, dws, dbs
+
+
+def stack_status(lease: _StackLease) -> int:
+    """Device status word of a stack workspace (synchronises)."""
+    return int(lease.ws[0].item()) & 0xFFFFFFFF
+
+
+class SiluConvStack(torch.autograd.Function):
+    """features = the 3x3 backbone layers applied to x, forward and backward on the library's tensor-core kernels.
+    Call as SiluConvStack.apply(x, w_1, b_1, w_2, b_2, ...)."""
+
+    @staticmethod
+    def forward(ctx, x, *params):
+        weights, biases = list(params[0::2]), list(params[1::2])
+        y, lease = stack_forward(x, weights, biases)
+        ctx.lease = lease
+        ctx.dtypes = (x.dtype, [p.dtype for p in params])
+        ctx.nparams = len(params)
+        return y.to(x.dtype) if x.dtype != torch.float32 else y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        if ctx.lease is None:   # empty batch
+            return (None,) * (1 + ctx.nparams)
+        dx, dws, dbs = stack_backward(ctx.lease, grad_out, need_dx=ctx.needs_input_grad[0])
+        xdt, pdts = ctx.dtypes
+        grads = [None if dx is None else dx.to(xdt)]
+        for l, (dw, db) in enumerate(zip(dws, dbs)):
+            grads.append(dw.to(pdts[2 * l]) if ctx.needs_input_grad[1 + 2 * l] else None)
+            grads.append(db.to(pdts[2 * l + 1]) if ctx.needs_input_grad[2 + 2 * l] else None)
+        return tuple(grads)

@@ -6,7 +6,7 @@
  * the PPO minibatch update (connect6/train.py:1032-1147: forward at 1047-1048, loss.backward() at
  * 1115-1119); per backbone layer y = silu(conv2d(x, W, b)) (connect6/model.py:104-106) autograd runs
  * cuDNN's data-gradient and weight-gradient convolutions plus elementwise kernels.  The entry points
- * below do that work for one layer with this library's own kernels.  Same conventions as c6_engine.h:
+ * below do that work, for one layer or for a stack of layers, with this library's own kernels.  Same conventions as c6_engine.h:
  * extern "C", plain DEVICE pointers and sizes, int status (0 = C6_OK), work enqueued on the stream
  * handed in (a cudaStream_t passed as void*), no synchronisation, no allocation.
  */
@@ -47,7 +47,36 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
                            float* dx, float* dw, float* db, void* workspace, int64_t workspace_bytes,
                            void* stream);
 
-/* Last error text of the calling thread's most recent failing c6_conv_layer_backward call. Never null. */
+/* ---- a whole stack of 3 x 3 layers -------------------------------------------------------------------
+ * Replaces, for the backbone layers after the stem: the grad-enabled forward of the PPO minibatch update
+ * (the loop of connect6/model.py:104-106 as run from connect6/train.py:1047-1048) and autograd's backward
+ * through it (connect6/train.py:1115-1119).  Layer l (0-based, l < nlayers) maps channels[l] ->
+ * channels[l + 1] with a 3 x 3 "same" convolution, bias and SiLU.  The forward call keeps every layer's
+ * input as 16-bit channel-chunk planes inside the workspace; the backward call walks the stack from the top
+ * with the gradient staying in that layout between layers, so only the stack's ends are converted from and
+ * to NCHW fp32.  Per layer the arithmetic is c6_conv_layer_backward's.
+ * Supported: 1 <= nlayers <= C6_MAX_LAYERS, n <= 32, every channel count <= 128.
+ * workspace: c6_backbone_workspace_bytes() bytes (0: unsupported shape), 256-byte aligned, ZERO-FILLED before its
+ * first use with a given shape; a forward call followed by its backward call must use the same workspace
+ * with nothing else written to it in between; the pair keeps the zero padding intact, so the buffer can be
+ * reused for the same shape without clearing.  The first 4 bytes are a status word like the engine's. */
+int64_t c6_backbone_workspace_bytes(int32_t board_size, int32_t nlayers, const int32_t* channels /* HOST, nlayers + 1 */,
+                                    int64_t B);
+
+/* x fp32 [B, channels[0], n, n] -> y fp32 [B, channels[nlayers], n, n].  w and bias are HOST arrays of
+ * nlayers DEVICE pointers (w[l] fp32 [channels[l+1], channels[l], 3, 3]; bias[l] fp32 [channels[l+1]] or null). */
+int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B,
+                        const float* x, const float* const* w, const float* const* bias, float* y, void* workspace,
+                        int64_t workspace_bytes, void* stream);
+
+/* dy fp32 [B, channels[nlayers], n, n] = dL/dy of the preceding c6_backbone_forward on this workspace.
+ * Outputs: dx fp32 [B, channels[0], n, n] (nullable); dw and db HOST arrays of nlayers DEVICE pointers
+ * (dw[l] fp32 like w[l], db[l] fp32 [channels[l+1]]). */
+int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B,
+                         const float* dy, float* dx, float* const* dw, float* const* db, void* workspace,
+                         int64_t workspace_bytes, void* stream);
+
+/* Last error text of the calling thread's most recent failing call of this header. Never null. */
 const char* c6_train_last_error(void);
 
 #ifdef __cplusplus

@@ -123,3 +123,17 @@ def layer_backward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, gr
     y = F.silu(F.conv2d(x, weight, bias, padding=weight.shape[-1] // 2))
     y.backward(grad_out.to(y.dtype))
     return x.grad, weight.grad, bias.grad
+
+
+def stack_backward(x: torch.Tensor, weights, biases, grad_out: torch.Tensor):
+    """What autograd computes for a run of backbone layers y_l = silu(conv2d(y_{l-1}, W_l, b_l, padding=k//2))
+    (the loop of connect6/model.py:104-106 differentiated by connect6/train.py:1115-1119):
+    (y, dL/dx, [dL/dW_l], [dL/db_l]) from dL/dy, in the dtype of the arguments (use float64 for an oracle)."""
+    x = x.detach().clone().requires_grad_(True)
+    weights = [w.detach().clone().requires_grad_(True) for w in weights]
+    biases = [b.detach().clone().requires_grad_(True) for b in biases]
+    y = x
+    for w, b in zip(weights, biases):
+        y = F.silu(F.conv2d(y, w, b, padding=w.shape[-1] // 2))
+    y.backward(grad_out.to(y.dtype))
+    return y.detach(), x.grad, [w.grad for w in weights], [b.grad for b in biases]

@@ -90,9 +90,37 @@ def layer_backward_fixture() -> None:
           "|dw| max", float(layer.weight.grad.abs().max()))
 
 
+def network_backward_fixture() -> None:
+    """Parameter gradients of one PPO-style loss.backward() through the reference's own network (a 9x9 net with a
+    5x5 stem and four 3x3 layers, 8 boards): every parameter's gradient, the weights and the inputs."""
+    torch.manual_seed(23)
+    kernels, channels = [5, 3, 3, 3, 3], [16, 24, 40, 32, 24]
+    net = PolicyValueNet(board_size=9, kernels=kernels, channels=channels).train()
+    with torch.no_grad():
+        for p in net.parameters():
+            if p.ndim == 1:
+                p.uniform_(-0.3, 0.3)
+        net.policy_output.weight.mul_(30.0)      # default-init heads (std 0.01) would leave the gradients tiny
+        net.value_output.weight.mul_(30.0)
+    x = torch.from_numpy(generate_planes(0, 8, board_size=9, max_stones=50))
+    logits, value = net(x)
+    target = torch.arange(8) * 11 % 81
+    loss = torch.nn.functional.cross_entropy(logits, target) + 0.5 * (value - 0.25).pow(2).mean()
+    net.zero_grad()
+    loss.backward()
+    np.savez_compressed(HERE / "network_backward.npz", x=x.numpy(), target=target.numpy(), loss=float(loss),
+                        kernels=np.array(kernels), channels=np.array(channels), board_size=9,
+                        torch_version=torch.__version__,
+                        **{"w::" + k: v for k, v in state_np(net).items()},
+                        **{"g::" + k: p.grad.numpy() for k, p in net.named_parameters()})
+    print("network_backward: loss", float(loss), "|g| max per tensor",
+          [round(float(p.grad.abs().max()), 5) for p in net.parameters()][:6])
+
+
 def main() -> None:
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     layer_backward_fixture()
+    network_backward_fixture()
 
     # 1. small net with an even-wider-than-board stem: weights stored, random real-valued input
     torch.manual_seed(7)

@@ -121,10 +121,93 @@ def test_conv_layer_backward_rejects_what_it_does_not_support(cuda_device):
     assert dx.shape == (0, 8, 19, 19) and not dw.any() and not db.any()
 
 
+STACK_RMS_TOL = 2e-2    # rms error / scale of each gradient, through up to seven bf16 layer backwards
+STACK_MAX_TOL = 1e-1    # worst element / scale
+
+
+def _check_stack(got, ref, name):
+    ref = ref.double()
+    scale = max(ref.std().item(), ref.abs().max().item() * 0.1) if ref.numel() > 1 else abs(ref.item())
+    err = (got.cpu().double() - ref).abs().max().item()
+    rms = (got.cpu().double() - ref).pow(2).mean().sqrt().item()
+    assert err < STACK_MAX_TOL * scale and rms < STACK_RMS_TOL * scale, f"{name}: max {err}, rms {rms} vs scale {scale}"
+
+
+@pytest.mark.parametrize("B,n,channels", [(37, 19, (32, 32, 64, 64, 64, 96, 96, 96)), (5, 19, (32, 64)), (9, 7, (24, 40, 16)),
+                                          (300, 19, (64, 96, 96))])
+def test_layer_stack_forward_backward_against_autograd(cuda_device, B, n, channels):
+    """c6_backbone_forward / c6_backbone_backward (a whole run of 3x3 layers, activations and gradients kept in the
+    kernels' plane layout between layers) against autograd in fp64 (oracle/torch_port.py:stack_backward)."""
+    from connect6_b200.train_ops import stack_backward, stack_forward, stack_status
+    gen = torch.Generator().manual_seed(B + n)
+    x = torch.nn.functional.silu(torch.randn(B, channels[0], n, n, generator=gen))
+    ws = [torch.randn(channels[l + 1], channels[l], 3, 3, generator=gen) * (2.0 / (9 * channels[l])) ** 0.5 for l in range(len(channels) - 1)]
+    bs = [0.1 * torch.randn(channels[l + 1], generator=gen) for l in range(len(channels) - 1)]
+    dy = torch.randn(B, channels[-1], n, n, generator=gen) * 1e-3
+    ry, rx, rws, rbs = TP.stack_backward(x.double(), [w.double() for w in ws], [b.double() for b in bs], dy.double())
+    dev = cuda_device
+    for _ in range(2):                                      # the second round reuses the workspace
+        y, lease = stack_forward(x.to(dev), [w.to(dev) for w in ws], [b.to(dev) for b in bs])
+        dx, dws, dbs = stack_backward(lease, dy.to(dev))
+        assert stack_status(lease) == 0
+        del lease
+    # forward: one bf16 rounding per layer (relative 2^-9 of a value) on top of bf16 weights and inputs
+    assert (y.cpu().double() - ry).abs().max().item() < 2.0 ** -7 * ry.abs().max().item() * len(ws) ** 0.5 + 1e-3
+    _check_stack(dx, rx, "dx")
+    for l in range(len(ws)):
+        _check_stack(dws[l], rws[l], f"dw[{l}]")
+        _check_stack(dbs[l], rbs[l], f"db[{l}]")
+    # without dX the parameter gradients are unchanged
+    y2, lease = stack_forward(x.to(dev), [w.to(dev) for w in ws], [b.to(dev) for b in bs])
+    none, dws2, dbs2 = stack_backward(lease, dy.to(dev), need_dx=False)
+    assert none is None and torch.equal(y2, y)
+    assert all(torch.equal(a, b) for a, b in zip(dws2, dws)) and all(torch.equal(a, b) for a, b in zip(dbs2, dbs))
+
+
+def test_layer_stack_rejects_what_it_does_not_support(cuda_device):
+    from connect6_b200.train_ops import stack_forward
+    dev = cuda_device
+    z = lambda *s: torch.zeros(*s, device=dev)
+    with pytest.raises(ValueError):     # 5x5 filter
+        stack_forward(z(2, 8, 19, 19), [z(8, 8, 5, 5)], [None])
+    with pytest.raises(ValueError):     # layers that do not chain
+        stack_forward(z(2, 8, 19, 19), [z(16, 8, 3, 3), z(8, 8, 3, 3)], [None, None])
+    with pytest.raises(ValueError):     # too wide
+        stack_forward(z(2, 8, 19, 19), [z(192, 8, 3, 3)], [None])
+    with pytest.raises(RuntimeError):   # no CPU path
+        stack_forward(torch.zeros(2, 8, 19, 19), [torch.zeros(8, 8, 3, 3)], [None])
+    y, lease = stack_forward(z(0, 8, 19, 19), [z(8, 8, 3, 3)], [None])
+    assert y.shape == (0, 8, 19, 19) and lease is None
+
+
+def test_network_gradients_golden(cuda_device):
+    """Every parameter gradient of a PPO-style loss.backward() recorded from the reference's own network
+    (tests/golden/network_backward.npz: 9x9 board, 5x5 stem, four 3x3 layers, 8 boards), reproduced by
+    PolicyValueNet(engine_backward=True): the four 3x3 layers run forward and backward as one library operator, the
+    stem and heads on autograd."""
+    from connect6_b200.model import PolicyValueNet
+    g = load_golden("network_backward.npz")
+    net = PolicyValueNet(int(g["board_size"]), [int(k) for k in g["kernels"]], [int(c) for c in g["channels"]],
+                         engine_backward=True).to(cuda_device).train()
+    net.load_state_dict({k[3:]: torch.from_numpy(g[k]) for k in g if k.startswith("w::")})
+    logits, value = net(torch.from_numpy(g["x"]).to(cuda_device))
+    loss = torch.nn.functional.cross_entropy(logits, torch.from_numpy(g["target"]).to(cuda_device)) + 0.5 * (value - 0.25).pow(2).mean()
+    assert abs(float(loss) - float(g["loss"])) < 2e-2 * abs(float(g["loss"]))
+    net.zero_grad()
+    loss.backward()
+    for name, p in net.named_parameters():
+        # 8 x 81 positions only: the bf16 roundings average out less than in a real batch (twice the tolerances)
+        ref = torch.from_numpy(g["g::" + name]).double()
+        scale = max(ref.std().item(), ref.abs().max().item() * 0.1) if ref.numel() > 1 else abs(ref.item())
+        err = (p.grad.cpu().double() - ref).abs().max().item()
+        rms = (p.grad.cpu().double() - ref).pow(2).mean().sqrt().item()
+        assert err < 2 * STACK_MAX_TOL * scale and rms < 2 * STACK_RMS_TOL * scale, f"{name}: max {err}, rms {rms} vs {scale}"
+
+
 def test_whole_network_gradients_with_engine_backward(cuda_device):
-    """PolicyValueNet(engine_backward=True): a PPO-style loss.backward() whose seven 3x3 layers take the library's
-    backward gives the parameter gradients of plain autograd (fp32 on the same GPU); the stem and the heads stay on
-    autograd.  The gradient passes through up to seven bf16 layer backwards before it reaches the early layers
+    """PolicyValueNet(engine_backward=True): a PPO-style loss.backward() whose seven 3x3 layers run forward and
+    backward as one library operator (train_ops.SiluConvStack) gives the parameter gradients of plain autograd (fp32
+    on the same GPU); the stem and the heads stay on autograd.  The gradient passes through up to seven bf16 layer backwards before it reaches the early layers
     (one bf16 rounding of dL/dx per layer), so the bound is on the root-mean-square error (2 % of each gradient's
     scale) and, for the worst of the thousands of elements of a tensor, 10 %."""
     from connect6_b200.boards import generate_planes

@@ -186,3 +186,33 @@ def test_layer_backward_oracle_matches_reference_autograd():
     for got, want in ((dx, g["dx"]), (dw, g["dw"]), (db, g["db"])):
         scale = np.abs(want).max()
         assert np.abs(got.numpy() - want).max() < 2e-6 * scale + 1e-12
+
+
+def test_stack_backward_oracle_matches_reference_autograd():
+    """The oracle for a run of layers (oracle/torch_port.py:stack_backward), driven by the head gradients that the
+    recorded loss implies, against every backbone gradient recorded from loss.backward() through the reference's
+    own network (tests/golden/network_backward.npz)."""
+    import torch
+    import torch_port as TP
+    g = load_golden("network_backward.npz")
+    params = {k[3:]: torch.from_numpy(g[k]).double() for k in g if k.startswith("w::")}
+    x = torch.from_numpy(g["x"]).double()
+    target = torch.from_numpy(g["target"])
+    # stem forward, then the 3x3 layers as one stack; heads and loss differentiated by hand-written torch ops
+    w0, b0 = params["convs.0.weight"], params["convs.0.bias"]
+    a0 = torch.nn.functional.silu(torch.nn.functional.conv2d(x, w0, b0, padding=w0.shape[-1] // 2))
+    L = len(g["kernels"])
+    ws = [params[f"convs.{i}.weight"] for i in range(1, L)]
+    bs = [params[f"convs.{i}.bias"] for i in range(1, L)]
+    feats, _, _, _ = TP.stack_backward(a0, ws, bs, torch.zeros(a0.shape[0], ws[-1].shape[0], 9, 9, dtype=torch.float64))
+    f = feats.clone().requires_grad_(True)
+    logits = torch.nn.functional.conv2d(f, params["policy_output.weight"], params["policy_output.bias"]).flatten(1)
+    value = torch.tanh(torch.nn.functional.conv2d(f, params["value_output.weight"], params["value_output.bias"]).mean(dim=(-2, -1))).squeeze(1)
+    loss = torch.nn.functional.cross_entropy(logits, target) + 0.5 * (value - 0.25).pow(2).mean()
+    assert abs(float(loss) - float(g["loss"])) < 1e-5
+    loss.backward()
+    _, da0, dws, dbs = TP.stack_backward(a0, ws, bs, f.grad)
+    for i in range(1, L):
+        for got, key in ((dws[i - 1], f"g::convs.{i}.weight"), (dbs[i - 1], f"g::convs.{i}.bias")):
+            want = g[key]
+            assert np.abs(got.numpy() - want).max() < 5e-6 * np.abs(want).max() + 1e-12, key

@@ -224,11 +224,10 @@ __global__ void view_input_f32_kernel(const InputSrc in,
 
 // k x k layer -> rows [q][tap][j][co] of 8 bf16: element e of the row is input channel
 // (2q+j)*8+e.  Channels beyond the real counts are zero.
-__global__ void pack_conv_weights_kernel(const float* __restrict__ w, uint4* __restrict__ out,
-                                         int cout, int cin, int kside, int cout_p, int cin_p, int f16) {
+__device__ __forceinline__ void pack_conv_weights_row(long long idx, const float* __restrict__ w, uint4* __restrict__ out,
+                                                      int cout, int cin, int kside, int cout_p, int cin_p, int f16) {
   const int taps = kside * kside;
   const long long total = (long long)(cin_p / 16) * taps * 2 * cout_p;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int co = (int)(idx % cout_p);
   long long r = idx / cout_p;
@@ -249,13 +248,16 @@ __global__ void pack_conv_weights_kernel(const float* __restrict__ w, uint4* __r
   o.w = pack_h2(v[6], v[7], f16);
   out[idx] = o;
 }
+__global__ void pack_conv_weights_kernel(const float* __restrict__ w, uint4* __restrict__ out,
+                                         int cout, int cin, int kside, int cout_p, int cin_p, int f16) {
+  pack_conv_weights_row((long long)blockIdx.x * blockDim.x + threadIdx.x, w, out, cout, cin, kside, cout_p, cin_p, f16);
+}
 
 // Same rows for the CTA-pair kernel: [half][q][tap][j][co % (cout_p/2)], half = co / (cout_p/2).
-__global__ void pack_conv_weights_pair_kernel(const float* __restrict__ w, uint4* __restrict__ out,
-                                              int cout, int cin, int kside, int cout_p, int cin_p, int f16) {
+__device__ __forceinline__ void pack_conv_weights_pair_row(long long idx, const float* __restrict__ w, uint4* __restrict__ out,
+                                                           int cout, int cin, int kside, int cout_p, int cin_p, int f16) {
   const int taps = kside * kside, nh = cout_p / 2;
   const long long total = (long long)(cin_p / 16) * taps * 2 * cout_p;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int col = (int)(idx % nh);
   long long r = idx / nh;
@@ -278,6 +280,10 @@ __global__ void pack_conv_weights_pair_kernel(const float* __restrict__ w, uint4
   o.z = pack_h2(v[4], v[5], f16);
   o.w = pack_h2(v[6], v[7], f16);
   out[idx] = o;
+}
+__global__ void pack_conv_weights_pair_kernel(const float* __restrict__ w, uint4* __restrict__ out,
+                                              int cout, int cin, int kside, int cout_p, int cin_p, int f16) {
+  pack_conv_weights_pair_row((long long)blockIdx.x * blockDim.x + threadIdx.x, w, out, cout, cin, kside, cout_p, cin_p, f16);
 }
 
 // Stem -> Toeplitz rows (row o = cell_out*c1 + co, element e of chunk c: see stem_k_decode) laid out

@@ -58,11 +58,10 @@ __global__ void unpack_planes_nchw_kernel(const uint4* __restrict__ planes, long
 // Cout input channels and Cin output channels.  Rows [q][tap][j][ci] of 8 bf16 (element e: input channel
 // (2q+j)*8+e of the gradient = an output channel of the layer); halves = 2 splits the rows for CTA pairs as
 // [half][q][tap][j][ci % (cin_p/2)].
-__global__ void pack_dgrad_weights_kernel(const float* __restrict__ w, uint4* __restrict__ out, int cout, int cin,
-                                          int kside, int cout_p, int cin_p, int halves) {
+__device__ __forceinline__ void pack_dgrad_weights_row(long long idx, const float* __restrict__ w, uint4* __restrict__ out,
+                                                       int cout, int cin, int kside, int cout_p, int cin_p, int halves) {
   const int taps = kside * kside, nh = cin_p / halves;
   const long long total = (long long)(cout_p / 16) * taps * 2 * cin_p;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int col = (int)(idx % nh);
   long long r = idx / nh;
@@ -85,6 +84,35 @@ __global__ void pack_dgrad_weights_kernel(const float* __restrict__ w, uint4* __
   o.z = pack_bf16x2(v[4], v[5]);
   o.w = pack_bf16x2(v[6], v[7]);
   out[idx] = o;
+}
+__global__ void pack_dgrad_weights_kernel(const float* __restrict__ w, uint4* __restrict__ out, int cout, int cin,
+                                          int kside, int cout_p, int cin_p, int halves) {
+  pack_dgrad_weights_row((long long)blockIdx.x * blockDim.x + threadIdx.x, w, out, cout, cin, kside, cout_p, cin_p, halves);
+}
+
+// Every operand a stack of 3 x 3 layers needs from its parameters, in ONE launch: grid (row blocks, layer, what) with
+// what = 0 forward filter, 1 the same for CTA pairs, 2 flipped/transposed filter of the data gradient, 3 the same for
+// CTA pairs, 4 bias padded to the kernels' channel granule.
+struct StackPackParams {
+  struct Layer {
+    const float* w;
+    const float* bias;     // nullable: zeros
+    uint4 *wf, *wf_pair, *wd, *wd_pair;
+    float* bias_f;
+    int cout, cin, cout_p, cin_p;
+  } layer[C6_MAX_LAYERS];
+};
+__global__ void pack_stack_weights_kernel(const StackPackParams p) {
+  const StackPackParams::Layer& L = p.layer[blockIdx.y];
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  switch (blockIdx.z) {
+    case 0: pack_conv_weights_row(idx, L.w, L.wf, L.cout, L.cin, 3, L.cout_p, L.cin_p, 0); break;
+    case 1: pack_conv_weights_pair_row(idx, L.w, L.wf_pair, L.cout, L.cin, 3, L.cout_p, L.cin_p, 0); break;
+    case 2: pack_dgrad_weights_row(idx, L.w, L.wd, L.cout, L.cin, 3, L.cout_p, L.cin_p, 1); break;
+    case 3: pack_dgrad_weights_row(idx, L.w, L.wd_pair, L.cout, L.cin, 3, L.cout_p, L.cin_p, 2); break;
+    default:
+      if (idx < L.cout_p) L.bias_f[idx] = (L.bias != nullptr && idx < L.cout) ? L.bias[idx] : 0.f;
+  }
 }
 
 // Bias gradient, first pass: block (q, s) sums the rows [s*chunk, (s+1)*chunk) of plane q for its 8 channels

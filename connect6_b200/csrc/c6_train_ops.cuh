@@ -166,7 +166,10 @@ int launch_conv(const BackwardLayout& L, const LayerPlan& lp, int epi, const uin
                                                      : conv_tc_kernel<3, false, false, false, kEpiSilu>);
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
     return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
-  launch_chain(kernel, (unsigned)p.ctas_per_group, 1u, kConvThreads, (size_t)lp.smem, st, lp.pair != 0, false, p);
+  // programmatic dependent launch: the kernel's prologue (barriers, TMEM, weight copies) overlaps the tail of the launch
+  // before it; every role that touches activations waits for that launch to complete (griddepcontrol.wait) first.  The
+  // weights were packed at least two launches earlier.
+  launch_chain(kernel, (unsigned)p.ctas_per_group, 1u, kConvThreads, (size_t)lp.smem, st, lp.pair != 0, true, p);
   C6T_LAUNCHED("conv_tc_kernel (backward)");
   return C6_OK;
 }
@@ -390,25 +393,25 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   int* status = reinterpret_cast<int*>(ws);
-  for (int l = 0; l < nlayers; ++l) {
-    const BackwardLayout& L = S.lay[l];
-    if (!w[l]) return tfail(C6_ERR_ARG, "null weight pointer");
-    float* bias_f = reinterpret_cast<float*>(ws + S.off_bias[l]);
-    copy_pad_f32_kernel<<<(L.cout_p + 127) / 128, 128, 0, st>>>(bias[l], bias_f, L.cout, L.cout_p);
-    C6T_LAUNCHED("copy_pad_f32_kernel");
-    const long long rows = (long long)L.fwd.w_rows_per_group, drows = (long long)L.dgrad.w_rows_per_group;
-    pack_conv_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
-        w[l], reinterpret_cast<uint4*>(ws + S.off_wf[l]), L.cout, L.cin, 3, L.cout_p, L.cin_p, 0);
-    C6T_LAUNCHED("pack_conv_weights_kernel");
-    pack_conv_weights_pair_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
-        w[l], reinterpret_cast<uint4*>(ws + S.off_wf_pair[l]), L.cout, L.cin, 3, L.cout_p, L.cin_p, 0);
-    C6T_LAUNCHED("pack_conv_weights_pair_kernel");
-    pack_dgrad_weights_kernel<<<(unsigned)((drows + 255) / 256), 256, 0, st>>>(
-        w[l], reinterpret_cast<uint4*>(ws + S.off_wd[l]), L.cout, L.cin, 3, L.cout_p, L.cin_p, 1);
-    C6T_LAUNCHED("pack_dgrad_weights_kernel");
-    pack_dgrad_weights_kernel<<<(unsigned)((drows + 255) / 256), 256, 0, st>>>(
-        w[l], reinterpret_cast<uint4*>(ws + S.off_wd_pair[l]), L.cout, L.cin, 3, L.cout_p, L.cin_p, 2);
-    C6T_LAUNCHED("pack_dgrad_weights_kernel");
+  {
+    StackPackParams pp{};
+    long long max_rows = 0;
+    for (int l = 0; l < nlayers; ++l) {
+      const BackwardLayout& L = S.lay[l];
+      if (!w[l]) return tfail(C6_ERR_ARG, "null weight pointer");
+      StackPackParams::Layer& q = pp.layer[l];
+      q.w = w[l];
+      q.bias = bias[l];
+      q.wf = reinterpret_cast<uint4*>(ws + S.off_wf[l]);
+      q.wf_pair = reinterpret_cast<uint4*>(ws + S.off_wf_pair[l]);
+      q.wd = reinterpret_cast<uint4*>(ws + S.off_wd[l]);
+      q.wd_pair = reinterpret_cast<uint4*>(ws + S.off_wd_pair[l]);
+      q.bias_f = reinterpret_cast<float*>(ws + S.off_bias[l]);
+      q.cout = L.cout; q.cin = L.cin; q.cout_p = L.cout_p; q.cin_p = L.cin_p;
+      max_rows = std::max(max_rows, std::max((long long)L.fwd.w_rows_per_group, (long long)L.dgrad.w_rows_per_group));
+    }
+    pack_stack_weights_kernel<<<dim3((unsigned)((max_rows + 255) / 256), (unsigned)nlayers, 5u), 256, 0, st>>>(pp);
+    C6T_LAUNCHED("pack_stack_weights_kernel");
   }
   const BackwardLayout& L0 = S.lay[0];
   {

@@ -199,6 +199,9 @@ def test_network_gradients_golden(cuda_device):
         # 8 x 81 positions only: the bf16 roundings average out less than in a real batch (twice the tolerances)
         ref = torch.from_numpy(g["g::" + name]).double()
         scale = max(ref.std().item(), ref.abs().max().item() * 0.1) if ref.numel() > 1 else abs(ref.item())
+        # the policy head's bias gradient is a sum of (softmax - one-hot) over the actions: zero but for rounding (5e-8
+        # in the recording), so it only has an absolute bound
+        scale = max(scale, 1e-5)
         err = (p.grad.cpu().double() - ref).abs().max().item()
         rms = (p.grad.cpu().double() - ref).pow(2).mean().sqrt().item()
         assert err < 2 * STACK_MAX_TOL * scale and rms < 2 * STACK_RMS_TOL * scale, f"{name}: max {err}, rms {rms} vs {scale}"
@@ -233,6 +236,7 @@ def test_whole_network_gradients_with_engine_backward(cuda_device):
     for name, ref in grads[0].items():
         got = grads[1][name]
         scale = max(ref.std().item(), ref.abs().max().item() * 0.1) if ref.numel() > 1 else abs(ref.item())
+        scale = max(scale, 1e-5)    # the policy bias gradient is zero but for rounding (a sum of softmax - one-hot)
         err = (got - ref).abs().max().item()
         rms = (got - ref).pow(2).mean().sqrt().item()
         assert err < 0.1 * scale and rms < 0.02 * scale, f"{name}: max {err}, rms {rms} vs scale {scale}"

@@ -734,21 +734,25 @@ def run_backward(args) -> None:
 
 
 def run_backbone_train(args) -> None:
-    """--workload backbone: forward + backward of the default network's seven 3x3 backbone layers (32 -> 32 -> 64 -> 64
-    -> 64 -> 96 -> 96 -> 96 channels) as ONE library operator (train_ops.stack_forward / stack_backward: activations
-    and gradients stay in the kernels' plane layout between layers) on `--boards` boards (default 8192; the reference's
-    PPO minibatch is 256).  Also times PyTorch autograd (cuDNN, bf16 autocast) on the same stack as the library bar."""
+    """--workload backbone: forward + backward of the default network's backbone -- the 23x23 stem on the 3 input planes
+    and the seven 3x3 layers (3 -> 32 -> 32 -> 64 -> 64 -> 64 -> 96 -> 96 -> 96 channels) -- as ONE library operator
+    (train_ops.stack_forward / stack_backward: activations and gradients stay in the kernels' plane layout between
+    layers) on `--boards` boards (default 8192; the reference's PPO minibatch is 256).  Also times PyTorch autograd
+    (cuDNN, bf16 autocast) on the same stack as the library bar."""
     import torch
     from connect6_b200.train_ops import stack_backward, stack_forward, stack_status
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    from connect6_b200.boards import generate_planes
     B, n = (args.boards or BATCH), 19
-    channels = [32, 32, 64, 64, 64, 96, 96, 96]
+    channels = [3, 32, 32, 64, 64, 64, 96, 96, 96]
+    ks = [23, 3, 3, 3, 3, 3, 3, 3]
+    nl = len(ks)
     g = torch.Generator(device=dev).manual_seed(1)
-    x = torch.nn.functional.silu(torch.randn(B, channels[0], n, n, device=dev, generator=g))
-    ws = [torch.randn(channels[l + 1], channels[l], 3, 3, device=dev, generator=g) * (2.0 / (9 * channels[l])) ** 0.5
-          for l in range(7)]
-    bs = [0.1 * torch.randn(channels[l + 1], device=dev, generator=g) for l in range(7)]
+    x = torch.from_numpy(generate_planes(0, B)).to(dev)
+    ws = [torch.randn(channels[l + 1], channels[l], ks[l], ks[l], device=dev, generator=g) * (2.0 / (ks[l] ** 2 * channels[l])) ** 0.5
+          for l in range(nl)]
+    bs = [0.1 * torch.randn(channels[l + 1], device=dev, generator=g) for l in range(nl)]
     dy = torch.randn(B, channels[-1], n, n, device=dev, generator=g) * 1e-3
 
     def step():
@@ -779,17 +783,16 @@ def run_backbone_train(args) -> None:
     torch.cuda.synchronize(dev)
     fwd_ms = e0.elapsed_time(em) / max(1, args.steps // 2)
     # library bar: the same stack through torch modules and autograd under bf16 autocast (connect6/train.py:1047-1119)
-    convs = [torch.nn.Conv2d(channels[l], channels[l + 1], 3, padding=1).to(dev) for l in range(7)]
+    convs = [torch.nn.Conv2d(channels[l], channels[l + 1], ks[l], padding=ks[l] // 2).to(dev) for l in range(nl)]
     with torch.no_grad():
         for c, w, b in zip(convs, ws, bs):
             c.weight.copy_(w)
             c.bias.copy_(b)
-    xl = x.clone().requires_grad_(True)
+    xl = x.clone()
 
     def lib_step():
         for c in convs:
             c.zero_grad(set_to_none=True)
-        xl.grad = None
         with torch.autocast("cuda", dtype=torch.bfloat16):
             f = xl
             for c in convs:
@@ -829,23 +832,24 @@ def run_backbone_train(args) -> None:
         kernels = {"error": f"{type(exc).__name__}: {exc}"[:160]}
     peaks, peak_kind = load_peaks()
     peak, peak_source = pick_tensor_peak(peaks, peak_kind, clocks, ms * args.steps * 1e-3)
-    macs = sum(361 * 9 * channels[l] * channels[l + 1] for l in range(7))      # per board, one pass
-    algorithmic = 2 * 3 * macs * B                  # forward + data gradient + weight gradient
-    executed = 2 * 4 * macs * B                     # + the forward recomputed for silu'
+    macs = sum(361 * ks[l] ** 2 * channels[l] * channels[l + 1] for l in range(nl))      # per board, one pass
+    stem_macs = 361 * ks[0] ** 2 * channels[0] * channels[1]
+    algorithmic = 2 * (3 * macs - stem_macs) * B    # forward + data gradient (not for the stem) + weight gradient
+    executed = 2 * (4 * macs - stem_macs) * B       # + the forward recomputed for silu'
     achieved = algorithmic / (ms * 1e-3) / 1e12
     print(json.dumps({
-        "metric": "forward + backward of the seven 3x3 backbone layers, boards/s (bf16 operands, fp32 accumulate)",
+        "metric": "forward + backward of the backbone (23x23 stem + seven 3x3 layers), boards/s (bf16 operands, fp32 accumulate)",
         "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "forward_ms": fwd_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"stack_forward + stack_backward, B = {B} boards, channels {channels}, 19x19; fp32 NCHW "
                                "tensors at the ends of the stack (packing and unpacking inside the timed calls)"},
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "whole operator pair (per layer: 3 conv_tc_kernel launches + wgrad_tc_kernel)",
+        "roofline": {"bound": "tensor", "kernel": "whole operator pair (per layer: 3 conv_tc_kernel launches + wgrad_tc_kernel; the stem: 2 + 1)",
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_source,
                      "flop_algorithmic": algorithmic, "flop_executed": executed, "traffic": None},
         "kernels": kernels,
-        "library_gpu_bar": {"ms_per_step": lib_ms, "what": "torch autograd of the same seven silu(conv2d) layers under bf16 autocast (cuDNN), forward + backward"},
+        "library_gpu_bar": {"ms_per_step": lib_ms, "what": "torch autograd of the same eight silu(conv2d) layers under bf16 autocast (cuDNN), forward + backward"},
         "device_status": status}), flush=True)
 
 

@@ -89,11 +89,15 @@ SIGNATURES = {
     "c6_conv_layer_backward_workspace_bytes": (_i64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, _i64]),
     "c6_conv_layer_backward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _i64, _vp, _vp, _vp, _vp, _vp, _vp,
                                     _vp, _vp, _i64, _vp]),
-    "c6_backbone_workspace_bytes": (_i64, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), _i64]),
-    "c6_backbone_forward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), _i64, _vp, C.POINTER(_vp),
+    "c6_backbone_workspace_bytes": (_i64, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64]),
+    "c6_backbone_forward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64, _vp, C.POINTER(_vp),
                                  C.POINTER(_vp), _vp, _vp, _i64, _vp]),
-    "c6_backbone_backward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), _i64, _vp, _vp, C.POINTER(_vp),
-                                  C.POINTER(_vp), _vp, _i64, _vp]),
+    "c6_backbone_backward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64, _vp, _vp,
+                                  C.POINTER(_vp), C.POINTER(_vp), _vp, _i64, _vp]),
+    "c6_backbone_heads_forward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64, _vp, _vp, _vp, _vp,
+                                       _vp, _vp, _vp, _i64, _vp]),
+    "c6_backbone_heads_backward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64, _vp, _vp, _vp, _vp,
+                                        _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "c6_train_last_error": (C.c_char_p, []),
     "c6_env_step": (_i, [C.POINTER(C6EnvState), _vp, C.c_int32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "c6_env_reset": (_i, [C.POINTER(C6EnvState), _vp, _i64, _vp]),

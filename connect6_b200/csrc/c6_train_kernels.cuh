@@ -90,6 +90,154 @@ __global__ void pack_dgrad_weights_kernel(const float* __restrict__ w, uint4* __
   pack_dgrad_weights_row((long long)blockIdx.x * blockDim.x + threadIdx.x, w, out, cout, cin, kside, cout_p, cin_p, halves);
 }
 
+// Gradient planes from the layers' padded board geometry (pitch wp, `slots` per image, first row `front`) into the
+// direct stem's input geometry (pitch dst_wi, dst_slots per image, first row 0): cells only -- the destination's
+// padding is zero from the start and never written.  One thread per (board, 8-channel plane, cell).
+__global__ void repack_planes_geometry_kernel(const uint4* __restrict__ src, long long src_plane_rows, int src_front,
+                                              int src_slots, int src_wp, uint4* __restrict__ dst, long long dst_plane_rows,
+                                              int dst_slots, int dst_wi, int n, int nq, long long B) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cells = n * n;
+  if (idx >= B * nq * cells) return;
+  const int cell = (int)(idx % cells);
+  const int q = (int)((idx / cells) % nq);
+  const long long b = idx / ((long long)cells * nq);
+  const int r = cell / n, c = cell - r * n;
+  dst[(size_t)q * dst_plane_rows + b * dst_slots + r * dst_wi + c] =
+      src[(size_t)q * src_plane_rows + src_front + b * src_slots + r * src_wp + c];
+}
+
+// The two 1 x 1 heads (connect6/model.py:70-75,108-110) on feature planes.  One block per board:
+//   logits[b][cell] = sum_ch wp[ch] f[b][ch][cell] + bp,   value[b] = tanh(mean_cell(sum_ch wv[ch] f[b][ch][cell]) + bv).
+constexpr int kHeadThreads = 128;
+__global__ void __launch_bounds__(kHeadThreads) heads_forward_kernel(const uint4* __restrict__ planes, long long plane_rows, int front,
+                                                                     int slots, int wp_pitch, int n, int C, int nq,
+                                                                     const float* __restrict__ wp, const float* __restrict__ bp,
+                                                                     const float* __restrict__ wv, const float* __restrict__ bv,
+                                                                     float* __restrict__ logits, float* __restrict__ value) {
+  __shared__ float s_wp[128], s_wv[128], s_red[kHeadThreads / 32];
+  for (int i = threadIdx.x; i < nq * 8; i += kHeadThreads) {
+    s_wp[i] = i < C ? wp[i] : 0.f;
+    s_wv[i] = i < C ? wv[i] : 0.f;
+  }
+  __syncthreads();
+  const long long b = blockIdx.x;
+  const int cells = n * n;
+  const float pb = bp[0];
+  float vsum = 0.f;
+  for (int cell = threadIdx.x; cell < cells; cell += kHeadThreads) {
+    const int r = cell / n, c = cell - r * n;
+    const uint4* row = planes + front + b * slots + r * wp_pitch + c;
+    float pol = pb;
+    for (int q = 0; q < nq; ++q) {
+      const uint4 v = row[(size_t)q * plane_rows];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float f = __uint_as_float((e & 1) ? (w[e >> 1] & 0xffff0000u) : (w[e >> 1] << 16));
+        pol = fmaf(f, s_wp[q * 8 + e], pol);
+        vsum = fmaf(f, s_wv[q * 8 + e], vsum);
+      }
+    }
+    logits[b * cells + cell] = pol;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) vsum += __shfl_xor_sync(0xffffffffu, vsum, o);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = vsum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < kHeadThreads / 32; ++i) s += s_red[i];
+    value[b] = tanhf(s / (float)cells + bv[0]);
+  }
+}
+
+// Backward of the heads.  Given dL/dlogits [B][cells], dL/dvalue [B] and the forward's value [B]:
+//   du_b = dvalue_b (1 - value_b^2)                (gradient at the pre-tanh mean)
+//   dfeat[b][ch][cell] = dlogits[b][cell] wp[ch] + du_b wv[ch] / cells          -> 16-bit gradient planes (cells only)
+//   dwp[ch] = sum_{b,cell} dlogits f,   dwv[ch] = sum_b du_b / cells sum_cell f,   dbp = sum dlogits,   dbv = sum_b du_b
+// Block i walks boards i, i + gridDim.x, ... once per 8-channel plane and leaves its partial sums in
+// partial[i][nq*16 + 2] (per plane: 8 dwp, 8 dwv; then dbp, dbv); heads_backward_finish_kernel adds the blocks in order.
+__global__ void __launch_bounds__(kHeadThreads) heads_backward_kernel(const uint4* __restrict__ planes, uint4* __restrict__ grad,
+                                                                      long long plane_rows, int front, int slots, int wp_pitch, int n,
+                                                                      int C, int nq, long long B, const float* __restrict__ wp,
+                                                                      const float* __restrict__ wv, const float* __restrict__ dlogits,
+                                                                      const float* __restrict__ dvalue, const float* __restrict__ value,
+                                                                      float* __restrict__ partial) {
+  __shared__ float s_red[kHeadThreads / 32][18];
+  const int cells = n * n, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_cells = 1.f / (float)cells;
+  float* my_partial = partial + (size_t)blockIdx.x * (nq * 16 + 2);
+  for (int q = 0; q < nq; ++q) {
+    float wpq[8], wvq[8], acc[18];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      wpq[e] = q * 8 + e < C ? wp[q * 8 + e] : 0.f;
+      wvq[e] = q * 8 + e < C ? wv[q * 8 + e] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 18; ++e) acc[e] = 0.f;
+    for (long long b = blockIdx.x; b < B; b += gridDim.x) {
+      const float v = value[b];
+      const float du = dvalue[b] * (1.f - v * v);
+      const float dus = du * inv_cells;
+      if (threadIdx.x == 0) acc[17] += du;
+      for (int cell = threadIdx.x; cell < cells; cell += kHeadThreads) {
+        const int r = cell / n, c = cell - r * n;
+        const size_t row = (size_t)q * plane_rows + front + b * slots + r * wp_pitch + c;
+        const float dl = dlogits[b * cells + cell];
+        acc[16] += dl;
+        const uint4 fv = planes[row];
+        const uint32_t w[4] = {fv.x, fv.y, fv.z, fv.w};
+        float g[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float f = __uint_as_float((e & 1) ? (w[e >> 1] & 0xffff0000u) : (w[e >> 1] << 16));
+          acc[e] = fmaf(dl, f, acc[e]);
+          acc[8 + e] = fmaf(dus, f, acc[8 + e]);
+          g[e] = fmaf(dl, wpq[e], dus * wvq[e]);
+        }
+        uint4 o;
+        o.x = pack_bf16x2(g[0], g[1]);
+        o.y = pack_bf16x2(g[2], g[3]);
+        o.z = pack_bf16x2(g[4], g[5]);
+        o.w = pack_bf16x2(g[6], g[7]);
+        grad[row] = o;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 18; ++e) {
+      float s = acc[e];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0) s_red[warp][e] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x < 18) {
+      float s = 0.f;
+      for (int i = 0; i < kHeadThreads / 32; ++i) s += s_red[i][threadIdx.x];
+      if (threadIdx.x < 16) my_partial[q * 16 + threadIdx.x] = s;
+      else if (q == 0) my_partial[nq * 16 + (threadIdx.x - 16)] = s;
+    }
+    __syncthreads();
+  }
+}
+__global__ void heads_backward_finish_kernel(const float* __restrict__ partial, int nblocks, int nq, int C, float* __restrict__ dwp,
+                                             float* __restrict__ dbp, float* __restrict__ dwv, float* __restrict__ dbv) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;    // 0..2C+1
+  if (i >= 2 * C + 2) return;
+  const int stride = nq * 16 + 2;
+  int col;
+  float* dst;
+  if (i < C) { col = (i >> 3) * 16 + (i & 7); dst = dwp + i; }
+  else if (i < 2 * C) { const int ch = i - C; col = (ch >> 3) * 16 + 8 + (ch & 7); dst = dwv + ch; }
+  else if (i == 2 * C) { col = nq * 16; dst = dbp; }
+  else { col = nq * 16 + 1; dst = dbv; }
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(size_t)b * stride + col];
+  *dst = s;
+}
+
 // Every operand a stack of 3 x 3 layers needs from its parameters, in ONE launch: grid (row blocks, layer, what) with
 // what = 0 forward filter, 1 the same for CTA pairs, 2 flipped/transposed filter of the data gradient, 3 the same for
 // CTA pairs, 4 bias padded to the kernels' channel granule.

@@ -48,6 +48,7 @@ int tfail(int code, const std::string& msg) {
   } while (0)
 
 constexpr int kColsumSlices = 64;
+constexpr int kHeadBlocks = 592;     // blocks of the heads' backward kernel (4 per SM of a B200), each leaves one row of partial sums
 
 // Shape-derived layout of one call: the forward kernels' padded linear board geometry and the carve-up of
 // the workspace.
@@ -198,6 +199,9 @@ int launch_wgrad(const BackwardLayout& L, const uint4* xp, const uint4* dpre, fl
   p.ngroups = L.wg_groups;
   p.nslabs = L.wg_slabs;          // planned for 148 SMs: the partial-sum buffer is sized for it
   p.nstages = L.wg_stages;
+  p.halo_after = L.halo_rows;
+  p.dpre_plane_rows = L.plane_rows;
+  p.dpre_front = L.front;
   if (cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
     return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   wgrad_tc_kernel<<<(unsigned)(p.ngroups * p.nslabs), kWgradThreads, (size_t)L.wg_smem, st>>>(p);
@@ -208,34 +212,204 @@ int launch_wgrad(const BackwardLayout& L, const uint4* xp, const uint4* dpre, fl
   return C6_OK;
 }
 
-// A stack of consecutive 3 x 3 layers (the backbone after the stem) differentiated as a whole: every layer's input
-// activation is kept as channel-chunk planes by the forward call, gradients travel between layers in the same layout.
-struct StackLayout {
+
+// The first layer as the direct stem (conv_tc_kernel's stem mode on x-expanded input planes, see c6_aux_kernels.cuh):
+// geometry of the input images, pipeline plan, and the plan of its weight gradient (wgrad_tc_kernel's stem mode).
+struct StemLayout {
   bool ok = false;
-  int L = 0, cmax_p = 0;
-  BackwardLayout lay[C6_MAX_LAYERS];      // per layer: pipeline plans; the board geometry is the same for all
-  size_t off_bias[C6_MAX_LAYERS] = {}, off_wf[C6_MAX_LAYERS] = {}, off_wf_pair[C6_MAX_LAYERS] = {}, off_wd[C6_MAX_LAYERS] = {},
-         off_wd_pair[C6_MAX_LAYERS] = {}, off_act[C6_MAX_LAYERS + 1] = {};
-  size_t off_zero = 0, off_grad[2] = {}, off_dpre = 0, off_partial = 0, off_colsum = 0, total = 0;
+  int k = 0, kh = 0, hx = 0, wi = 0, slots = 0, halo_b = 0, halo_a = 0, front = 0, cout = 0, cout_p = 0;
+  int tiles_per_board = 0, tiles = 0;
+  long long group_pos = 0, xe_plane_rows = 0, dsd_plane_rows = 0;
+  LayerPlan plan;
+  int nkxb = 0, nkyb = 0, wg_ntaps = 0, wg_taps_per_cta = 0, wg_groups = 0, wg_slabs = 0, wg_stages = 0, wg_smem = 0,
+      wg_tile_rows = 256, wg_tiles = 0, wg_halo_a = 0;
 };
 
-StackLayout make_stack_layout(int n, int nlayers, const int32_t* channels, long long B) {
+StemLayout make_stem_layout(int n, int k0, int cout, long long B) {
+  StemLayout S;
+  if (k0 < 3 || (k0 & 1) == 0 || k0 > 31 || n < 1 || n > 32 || cout < 1 || B < 1) return S;
+  S.k = k0; S.kh = k0 / 2; S.cout = cout;
+  S.cout_p = round_up(cout, 32);
+  if (S.cout_p > 64) return S;
+  S.hx = (k0 + 15) / 16;
+  S.wi = round_up(n + S.kh, 8);
+  S.slots = S.wi * (n + S.kh);
+  S.halo_b = round_up(S.kh * S.wi + S.kh, 8);
+  S.halo_a = round_up(S.kh * S.wi + 16 * S.hx - 1 - S.kh + 8, 8);
+  S.front = S.halo_b;
+  S.plan.k = k0; S.plan.cin = 3; S.plan.cout = cout; S.plan.cin_p = 48; S.plan.cout_p = S.cout_p;
+  if (!plan_tc_layer(true, S.plan, k0 * S.hx, 3, 128 + S.halo_b + S.halo_a, 1, 1)) return S;
+  const int used = (n - 1) * S.wi + n, tpb = (used + 127) / 128;
+  S.tiles_per_board = tpb * 128 < S.slots ? tpb : 0;
+  long long tiles = S.tiles_per_board ? B * tpb : (B * S.slots + 127) / 128;
+  if (S.plan.pair) tiles += tiles & 1;
+  if (tiles > 0x7fffffffLL / 128) return S;
+  S.tiles = (int)tiles;
+  S.group_pos = S.tiles_per_board ? round_up_ll((long long)((tiles + tpb - 1) / tpb) * S.slots, 128) : tiles * 128;
+  // weight gradient: taps = (input plane, 8 filter columns, 16 filter rows)
+  S.nkxb = (k0 + 7) / 8;
+  S.nkyb = (k0 + 15) / 16;
+  S.wg_ntaps = 3 * S.nkxb * S.nkyb;
+  S.wg_taps_per_cta = std::min(std::min(kWgradMaxTaps, 512 / S.cout_p), S.wg_ntaps);
+  S.wg_groups = (S.wg_ntaps + S.wg_taps_per_cta - 1) / S.wg_taps_per_cta;
+  S.wg_slabs = std::max(1, 148 / S.wg_groups);
+  S.wg_halo_a = round_up((16 * S.nkyb - 1 - S.kh) * S.wi + (8 * S.nkxb - 1 - S.kh) + 8, 8);
+  const int room = kSmemLimit - 128 - kWgradSmemHeader;
+  S.wg_tile_rows = 2 * wgrad_stem_stage_bytes(S.cout_p, S.halo_b, S.wg_halo_a, 256) <= room ? 256 : 128;
+  const int stage = wgrad_stem_stage_bytes(S.cout_p, S.halo_b, S.wg_halo_a, S.wg_tile_rows);
+  S.wg_stages = std::min(kWgradMaxStages, room / stage);
+  if (S.wg_stages < 2) return S;
+  S.wg_smem = 128 + kWgradSmemHeader + S.wg_stages * stage;
+  S.wg_tiles = (int)((B * S.slots + S.wg_tile_rows - 1) / S.wg_tile_rows);
+  S.dsd_plane_rows = (long long)S.wg_tiles * S.wg_tile_rows;
+  S.xe_plane_rows = (long long)S.front + std::max(S.group_pos + S.halo_a + 128 + 16, S.dsd_plane_rows + S.wg_halo_a + 16);
+  S.ok = true;
+  return S;
+}
+
+// One launch of the direct stem: epi = kEpiSilu (forward, out = the first activation planes) or kEpiDsilu (forward
+// recomputed, out = aux * silu'(.) at the cells).  `out` and `aux` are in the layers' geometry G.
+int launch_stem_conv(const StemLayout& S, const BackwardLayout& G, int epi, const uint4* xe, uint4* out, const uint4* aux,
+                     const uint4* w, const uint4* w_pair, const float* bias, int* status, int n, long long B, int sms,
+                     cudaStream_t st) {
+  const LayerPlan& lp = S.plan;
+  ConvTcParams p{};
+  p.in = xe;
+  p.in_plane_rows = S.xe_plane_rows;
+  p.out = out;
+  p.aux = aux;
+  p.plane_rows = G.plane_rows;
+  p.w = w;
+  p.w_pair = w_pair;
+  p.bias = bias;
+  p.status = status;
+  p.front = S.front;
+  p.halo_rows = S.halo_b;
+  p.halo_after = S.halo_a;
+  p.cin = 48;                       // three pipeline steps, one input plane each
+  p.n = lp.cout_p;
+  p.kside = lp.k;
+  p.ntaps = lp.k * S.hx;
+  p.planes_step = 1;
+  p.stem = 1;
+  p.stem_hx = S.hx;
+  p.a_lbo_rows = 8;
+  p.wp = S.wi;
+  p.slots = S.slots;
+  p.bsize = n;
+  p.nboards = (int)B;
+  p.tiles_per_group = S.tiles;
+  p.tiles_per_board = S.tiles_per_board;
+  p.group_pos = (int)S.group_pos;
+  p.out_front = G.front;
+  p.out_wp = G.wp;
+  p.out_slots = G.slots;
+  p.out_group_pos = (int)G.total_pos;
+  p.ctas_per_group = std::max(1, std::min(sms, S.tiles));
+  if (lp.pair) p.ctas_per_group = std::max(2, p.ctas_per_group & ~1);
+  p.resident = lp.resident;
+  p.nstages = lp.nstages;
+  p.nissue = lp.nissue;
+  p.spi = lp.spi;
+  p.qps = 1;
+  p.acc_stride = lp.acc_stride;
+  p.nacc = lp.nacc;
+  p.tmem_cols = lp.tmem_cols;
+  ConvKernel kernel = lp.pair ? (epi == kEpiDsilu ? conv_tc_kernel<0, true, false, false, kEpiDsilu>
+                                                  : conv_tc_kernel<0, true, false, false, kEpiSilu>)
+                              : (epi == kEpiDsilu ? conv_tc_kernel<0, false, false, false, kEpiDsilu>
+                                                  : conv_tc_kernel<0, false, false, false, kEpiSilu>);
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+    return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+  launch_chain(kernel, (unsigned)p.ctas_per_group, 1u, kConvThreads, (size_t)lp.smem, st, lp.pair != 0, true, p);
+  C6T_LAUNCHED("conv_tc_kernel (direct stem)");
+  return C6_OK;
+}
+
+// dW of the stem from the x-expanded input planes and the gradient planes in the input geometry.
+int launch_stem_wgrad(const StemLayout& S, const uint4* xe, const uint4* dsd, float* partial, float* dw, int* status,
+                      cudaStream_t st) {
+  WgradParams p{};
+  p.x = xe;
+  p.dpre = dsd;
+  p.partial = partial;
+  p.status = status;
+  p.plane_rows = S.xe_plane_rows;
+  p.front = S.front;
+  p.halo_rows = S.halo_b;
+  p.halo_after = S.wg_halo_a;
+  p.dpre_plane_rows = S.dsd_plane_rows;
+  p.dpre_front = 0;
+  p.cin = 0;
+  p.cout = S.cout_p;
+  p.kside = S.k;
+  p.wp = S.wi;
+  p.tile_rows = S.wg_tile_rows;
+  p.ntiles = S.wg_tiles;
+  p.ntaps = S.wg_ntaps;
+  p.taps_per_cta = S.wg_taps_per_cta;
+  p.ngroups = S.wg_groups;
+  p.nslabs = S.wg_slabs;
+  p.nstages = S.wg_stages;
+  p.stem_k = S.k;
+  p.stem_wi = S.wi;
+  p.stem_nkxb = S.nkxb;
+  p.stem_nkyb = S.nkyb;
+  if (cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+    return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+  wgrad_tc_kernel<<<(unsigned)(p.ngroups * p.nslabs), kWgradThreads, (size_t)S.wg_smem, st>>>(p);
+  C6T_LAUNCHED("wgrad_tc_kernel (stem)");
+  const long long total = (long long)S.cout * 3 * S.k * S.k;
+  wgrad_reduce_stem_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, dw, p.nslabs, p.ntaps, S.cout_p, S.cout, S.k,
+                                                                           S.nkxb, S.nkyb);
+  C6T_LAUNCHED("wgrad_reduce_stem_kernel");
+  return C6_OK;
+}
+
+// A stack of layers differentiated as a whole: an optional first-layer stem (stem_kside x stem_kside on 3 input planes,
+// run as the direct stem) followed by 3 x 3 layers.  Every layer's input activation is kept as channel-chunk planes by
+// the forward call (the stem's input as its x-expanded planes), gradients travel between layers in the same layout.
+struct StackLayout {
+  bool ok = false;
+  int L = 0, first = 0, cmax_p = 0;       // layers in all; index of the first 3 x 3 layer (1 with a stem, else 0)
+  StemLayout stem;
+  BackwardLayout lay[C6_MAX_LAYERS];      // 3 x 3 layers l >= first: pipeline plans; the board geometry is the same for all
+  size_t off_bias[C6_MAX_LAYERS] = {}, off_wf[C6_MAX_LAYERS] = {}, off_wf_pair[C6_MAX_LAYERS] = {}, off_wd[C6_MAX_LAYERS] = {},
+         off_wd_pair[C6_MAX_LAYERS] = {}, off_act[C6_MAX_LAYERS + 1] = {};
+  size_t off_zero = 0, off_grad[2] = {}, off_dpre = 0, off_partial = 0, off_colsum = 0, off_xe = 0, off_dsd = 0, off_heads = 0, total = 0;
+};
+
+StackLayout make_stack_layout(int n, int nlayers, const int32_t* channels, int stem_kside, long long B) {
   StackLayout S;
-  if (nlayers < 1 || nlayers > C6_MAX_LAYERS || !channels) return S;
+  if (nlayers < 1 || nlayers > C6_MAX_LAYERS || !channels || stem_kside < 0) return S;
   S.L = nlayers;
-  size_t partial_max = 0, colsum_max = 0;
-  for (int l = 0; l < nlayers; ++l) {
+  S.first = stem_kside > 0 ? 1 : 0;
+  if (S.first) {
+    if (nlayers < 2 || channels[0] != 3) return S;     // a stem reads the 3 input planes and feeds at least one 3 x 3 layer
+    S.stem = make_stem_layout(n, stem_kside, channels[1], B);
+    if (!S.stem.ok) return S;
+  }
+  size_t partial_max = S.first ? (size_t)S.stem.wg_slabs * S.stem.wg_ntaps * 128 * S.stem.cout_p * 4 : 0, colsum_max = 0;
+  for (int l = S.first; l < nlayers; ++l) {
     S.lay[l] = make_layout(n, 3, channels[l], channels[l + 1], B, 148);
     if (!S.lay[l].ok) return S;
     S.cmax_p = std::max(S.cmax_p, std::max(S.lay[l].cin_p, S.lay[l].cout_p));
     partial_max = std::max(partial_max, (size_t)S.lay[l].wg_slabs * 9 * 128 * S.lay[l].cin_p * 4);
     colsum_max = std::max(colsum_max, (size_t)(S.lay[l].cout_p / 8) * kColsumSlices * 8 * 4);
   }
-  const long long plane_rows = S.lay[0].plane_rows;
+  colsum_max = std::max(colsum_max, (size_t)(S.lay[S.first].cin_p / 8) * kColsumSlices * 8 * 4);
+  const long long plane_rows = S.lay[S.first].plane_rows;
   auto take = [&](size_t bytes) { size_t o = S.total; S.total += (bytes + 255) & ~(size_t)255; return o; };
   take(256);                                                // status word
   S.off_zero = take((size_t)S.cmax_p * 4);
-  for (int l = 0; l < nlayers; ++l) {
+  if (S.first) {
+    S.off_bias[0] = take((size_t)S.stem.cout_p * 4);
+    S.off_wf[0] = take(S.stem.plan.w_rows_per_group * 16);
+    S.off_wf_pair[0] = take(S.stem.plan.w_rows_per_group * 16);
+    S.off_xe = take((size_t)3 * S.stem.xe_plane_rows * 16);
+    S.off_dsd = take((size_t)(S.stem.cout_p / 8) * S.stem.dsd_plane_rows * 16);
+  }
+  for (int l = S.first; l < nlayers; ++l) {
     const BackwardLayout& L = S.lay[l];
     S.off_bias[l] = take((size_t)L.cout_p * 4);
     S.off_wf[l] = take(L.fwd.w_rows_per_group * 16);
@@ -243,7 +417,7 @@ StackLayout make_stack_layout(int n, int nlayers, const int32_t* channels, long 
     S.off_wd[l] = take(L.dgrad.w_rows_per_group * 16);
     S.off_wd_pair[l] = take(L.dgrad.w_rows_per_group * 16);
   }
-  for (int l = 0; l <= nlayers; ++l) {
+  for (int l = S.first; l <= nlayers; ++l) {
     const int cp = l < nlayers ? S.lay[l].cin_p : S.lay[l - 1].cout_p;
     S.off_act[l] = take((size_t)(cp / 8) * plane_rows * 16);
   }
@@ -252,12 +426,15 @@ StackLayout make_stack_layout(int n, int nlayers, const int32_t* channels, long 
   S.off_dpre = take((size_t)(S.cmax_p / 8) * plane_rows * 16);
   S.off_partial = take(partial_max);
   S.off_colsum = take(colsum_max);
+  S.off_heads = take((size_t)kHeadBlocks * ((S.lay[nlayers - 1].cout_p / 8) * 16 + 2) * 4);
   S.ok = true;
   return S;
 }
 
 int check_stack_call(int32_t device, const StackLayout& S, void* workspace, int64_t workspace_bytes, int* sms) {
-  if (!S.ok) return tfail(C6_ERR_UNSUPPORTED, "the backbone operators support 1..16 layers of 3 x 3, board_size <= 32, at most 128 channels");
+  if (!S.ok)
+    return tfail(C6_ERR_UNSUPPORTED, "the backbone operators support 1..16 layers of 3 x 3 with at most 128 channels, board_size <= 32, "
+                                     "optionally behind an odd k x k stem (k <= 31) from 3 planes to at most 64 channels");
   if (!workspace) return tfail(C6_ERR_ARG, "null pointer");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return tfail(C6_ERR_ARG, "workspace must be 256-byte aligned");
   if (workspace_bytes < (int64_t)S.total) {
@@ -375,18 +552,19 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
   return C6_OK;
 }
 
-int64_t c6_backbone_workspace_bytes(int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B) {
+int64_t c6_backbone_workspace_bytes(int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                                    int64_t B) {
   if (B < 1) return 0;
-  const StackLayout S = make_stack_layout(board_size, nlayers, channels, B);
+  const StackLayout S = make_stack_layout(board_size, nlayers, channels, stem_kside, B);
   return S.ok ? (int64_t)S.total : 0;
 }
 
-int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B,
-                        const float* x, const float* const* w, const float* const* bias, float* y, void* workspace,
-                        int64_t workspace_bytes, void* stream) {
+int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                        int64_t B, const float* x, const float* const* w, const float* const* bias, float* y,
+                        void* workspace, int64_t workspace_bytes, void* stream) {
   if (B < 1) return tfail(C6_ERR_ARG, "board count must be positive");
-  if (!x || !w || !bias || !y || !channels) return tfail(C6_ERR_ARG, "null pointer");
-  const StackLayout S = make_stack_layout(board_size, nlayers, channels, B);
+  if (!x || !w || !bias || !channels) return tfail(C6_ERR_ARG, "null pointer");
+  const StackLayout S = make_stack_layout(board_size, nlayers, channels, stem_kside, B);
   int sms = 0;
   int rc = check_stack_call(device, S, workspace, workspace_bytes, &sms);
   if (rc) return rc;
@@ -396,10 +574,10 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
   {
     StackPackParams pp{};
     long long max_rows = 0;
-    for (int l = 0; l < nlayers; ++l) {
+    for (int l = S.first; l < nlayers; ++l) {
       const BackwardLayout& L = S.lay[l];
       if (!w[l]) return tfail(C6_ERR_ARG, "null weight pointer");
-      StackPackParams::Layer& q = pp.layer[l];
+      StackPackParams::Layer& q = pp.layer[l - S.first];
       q.w = w[l];
       q.bias = bias[l];
       q.wf = reinterpret_cast<uint4*>(ws + S.off_wf[l]);
@@ -410,17 +588,41 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
       q.cout = L.cout; q.cin = L.cin; q.cout_p = L.cout_p; q.cin_p = L.cin_p;
       max_rows = std::max(max_rows, std::max((long long)L.fwd.w_rows_per_group, (long long)L.dgrad.w_rows_per_group));
     }
-    pack_stack_weights_kernel<<<dim3((unsigned)((max_rows + 255) / 256), (unsigned)nlayers, 5u), 256, 0, st>>>(pp);
+    pack_stack_weights_kernel<<<dim3((unsigned)((max_rows + 255) / 256), (unsigned)(nlayers - S.first), 5u), 256, 0, st>>>(pp);
     C6T_LAUNCHED("pack_stack_weights_kernel");
   }
-  const BackwardLayout& L0 = S.lay[0];
-  {
+  const BackwardLayout& L0 = S.lay[S.first];
+  if (S.first) {
+    // the stem: bias, filter rows for the direct stem (whole and split for CTA pairs), x-expanded input planes, convolution
+    const StemLayout& T = S.stem;
+    if (!w[0]) return tfail(C6_ERR_ARG, "null weight pointer");
+    copy_pad_f32_kernel<<<(T.cout_p + 127) / 128, 128, 0, st>>>(bias[0], reinterpret_cast<float*>(ws + S.off_bias[0]), T.cout, T.cout_p);
+    C6T_LAUNCHED("copy_pad_f32_kernel");
+    const long long rows = (long long)T.plan.w_rows_per_group;
+    pack_stem_direct_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+        w[0], reinterpret_cast<uint4*>(ws + S.off_wf[0]), T.cout, T.k, T.cout_p, T.hx, 1, 0);
+    C6T_LAUNCHED("pack_stem_direct_weights_kernel");
+    pack_stem_direct_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+        w[0], reinterpret_cast<uint4*>(ws + S.off_wf_pair[0]), T.cout, T.k, T.cout_p, T.hx, 2, 0);
+    C6T_LAUNCHED("pack_stem_direct_weights_kernel");
+    InputSrc in{};
+    in.x = x;
+    const long long total = 3LL * T.slots * B;
+    pack_stem_direct_input_kernel<<<dim3((unsigned)((total + 255) / 256), 1u), 256, 0, st>>>(
+        in, nullptr, reinterpret_cast<uint4*>(ws + S.off_xe), T.xe_plane_rows, T.front, (int)T.group_pos, T.wi, T.slots, board_size,
+        (int)B, B, 0, 0, status);
+    C6T_LAUNCHED("pack_stem_direct_input_kernel");
+    rc = launch_stem_conv(T, L0, kEpiSilu, reinterpret_cast<const uint4*>(ws + S.off_xe), reinterpret_cast<uint4*>(ws + S.off_act[1]),
+                          nullptr, reinterpret_cast<const uint4*>(ws + S.off_wf[0]), reinterpret_cast<const uint4*>(ws + S.off_wf_pair[0]),
+                          reinterpret_cast<const float*>(ws + S.off_bias[0]), status, board_size, B, sms, st);
+    if (rc) return rc;
+  } else {
     const long long t = B * L0.slots * (L0.cin_p / 8);
     pack_nchw_planes_kernel<<<(unsigned)((t + 255) / 256), 256, 0, st>>>(
         x, reinterpret_cast<uint4*>(ws + S.off_act[0]), L0.plane_rows, L0.front, L0.slots, L0.wp, L0.n, L0.cin, L0.cin_p, B);
     C6T_LAUNCHED("pack_nchw_planes_kernel");
   }
-  for (int l = 0; l < nlayers; ++l) {
+  for (int l = S.first; l < nlayers; ++l) {
     const BackwardLayout& L = S.lay[l];
     rc = launch_conv(L, L.fwd, kEpiSilu, reinterpret_cast<const uint4*>(ws + S.off_act[l]),
                      reinterpret_cast<uint4*>(ws + S.off_act[l + 1]), nullptr, reinterpret_cast<const uint4*>(ws + S.off_wf[l]),
@@ -428,7 +630,7 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
                      status, sms, st);
     if (rc) return rc;
   }
-  {
+  if (y) {
     const BackwardLayout& L = S.lay[nlayers - 1];
     const long long total = B * ((L.cout + 7) / 8) * L.n * L.n;
     unpack_planes_nchw_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
@@ -438,12 +640,56 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
   return C6_OK;
 }
 
-int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B,
-                         const float* dy, float* dx, float* const* dw, float* const* db, void* workspace,
+int c6_backbone_heads_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                              int64_t B, const float* wp, const float* bp, const float* wv, const float* bv, float* logits,
+                              float* value, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (B < 1) return tfail(C6_ERR_ARG, "board count must be positive");
+  if (!wp || !bp || !wv || !bv || !logits || !value || !channels) return tfail(C6_ERR_ARG, "null pointer");
+  const StackLayout S = make_stack_layout(board_size, nlayers, channels, stem_kside, B);
+  int sms = 0;
+  int rc = check_stack_call(device, S, workspace, workspace_bytes, &sms);
+  if (rc) return rc;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  const BackwardLayout& L = S.lay[nlayers - 1];
+  heads_forward_kernel<<<(unsigned)B, kHeadThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(ws + S.off_act[nlayers]), L.plane_rows, L.front, L.slots, L.wp, L.n, L.cout, L.cout_p / 8, wp, bp,
+      wv, bv, logits, value);
+  C6T_LAUNCHED("heads_forward_kernel");
+  return C6_OK;
+}
+
+int c6_backbone_heads_backward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                               int64_t B, const float* wp, const float* wv, const float* dlogits, const float* dvalue,
+                               const float* value, float* dwp, float* dbp, float* dwv, float* dbv, void* workspace,
+                               int64_t workspace_bytes, void* stream) {
+  if (B < 1) return tfail(C6_ERR_ARG, "board count must be positive");
+  if (!wp || !wv || !dlogits || !dvalue || !value || !dwp || !dbp || !dwv || !dbv || !channels) return tfail(C6_ERR_ARG, "null pointer");
+  const StackLayout S = make_stack_layout(board_size, nlayers, channels, stem_kside, B);
+  int sms = 0;
+  int rc = check_stack_call(device, S, workspace, workspace_bytes, &sms);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  const BackwardLayout& L = S.lay[nlayers - 1];
+  const int nq = L.cout_p / 8;
+  const int nblocks = (int)std::min<long long>(B, kHeadBlocks);
+  float* partial = reinterpret_cast<float*>(ws + S.off_heads);
+  heads_backward_kernel<<<(unsigned)nblocks, kHeadThreads, 0, st>>>(
+      reinterpret_cast<const uint4*>(ws + S.off_act[nlayers]), reinterpret_cast<uint4*>(ws + S.off_grad[0]), L.plane_rows, L.front,
+      L.slots, L.wp, L.n, L.cout, nq, B, wp, wv, dlogits, dvalue, value, partial);
+  C6T_LAUNCHED("heads_backward_kernel");
+  heads_backward_finish_kernel<<<(2 * L.cout + 2 + 127) / 128, 128, 0, st>>>(partial, nblocks, nq, L.cout, dwp, dbp, dwv, dbv);
+  C6T_LAUNCHED("heads_backward_finish_kernel");
+  return C6_OK;
+}
+
+int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                         int64_t B, const float* dy, float* dx, float* const* dw, float* const* db, void* workspace,
                          int64_t workspace_bytes, void* stream) {
   if (B < 1) return tfail(C6_ERR_ARG, "board count must be positive");
-  if (!dy || !dw || !db || !channels) return tfail(C6_ERR_ARG, "null pointer");
-  const StackLayout S = make_stack_layout(board_size, nlayers, channels, B);
+  if (!dw || !db || !channels) return tfail(C6_ERR_ARG, "null pointer");
+  if (stem_kside > 0 && dx) return tfail(C6_ERR_ARG, "with a stem the stack starts at the network input, which has no gradient: dx must be null");
+  const StackLayout S = make_stack_layout(board_size, nlayers, channels, stem_kside, B);
   int sms = 0;
   int rc = check_stack_call(device, S, workspace, workspace_bytes, &sms);
   if (rc) return rc;
@@ -455,14 +701,14 @@ int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, co
   float* partial = reinterpret_cast<float*>(ws + S.off_partial);
   float* colsum = reinterpret_cast<float*>(ws + S.off_colsum);
   int cur = 0;
-  {
+  if (dy) {   // null: c6_backbone_heads_backward has left the gradient of the features in the workspace
     const BackwardLayout& L = S.lay[nlayers - 1];
     const long long t = B * L.slots * (L.cout_p / 8);
     pack_nchw_planes_kernel<<<(unsigned)((t + 255) / 256), 256, 0, st>>>(
         dy, reinterpret_cast<uint4*>(ws + S.off_grad[cur]), L.plane_rows, L.front, L.slots, L.wp, L.n, L.cout, L.cout_p, B);
     C6T_LAUNCHED("pack_nchw_planes_kernel");
   }
-  for (int l = nlayers - 1; l >= 0; --l) {
+  for (int l = nlayers - 1; l >= S.first; --l) {
     const BackwardLayout& L = S.lay[l];
     if (!dw[l] || !db[l]) return tfail(C6_ERR_ARG, "null gradient pointer");
     const uint4* act = reinterpret_cast<const uint4*>(ws + S.off_act[l]);
@@ -486,7 +732,31 @@ int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, co
       cur ^= 1;
     }
   }
-  if (dx) {
+  if (S.first) {
+    // the stem: dPre_0 = dY_0 * silu'(.) with its forward recomputed by the direct stem, db_0 its column sums, dW_0 from the
+    // x-expanded input planes and dPre_0 moved into the input geometry
+    const StemLayout& T = S.stem;
+    const BackwardLayout& G = S.lay[1];
+    if (!dw[0] || !db[0]) return tfail(C6_ERR_ARG, "null gradient pointer");
+    const uint4* xe = reinterpret_cast<const uint4*>(ws + S.off_xe);
+    uint4* dsd = reinterpret_cast<uint4*>(ws + S.off_dsd);
+    rc = launch_stem_conv(T, G, kEpiDsilu, xe, dpre, reinterpret_cast<const uint4*>(ws + S.off_grad[cur]),
+                          reinterpret_cast<const uint4*>(ws + S.off_wf[0]), reinterpret_cast<const uint4*>(ws + S.off_wf_pair[0]),
+                          reinterpret_cast<const float*>(ws + S.off_bias[0]), status, board_size, B, sms, st);
+    if (rc) return rc;
+    colsum_planes_kernel<<<dim3((unsigned)(T.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre, G.plane_rows, G.front,
+                                                                                                    G.total_pos, kColsumSlices, colsum);
+    C6T_LAUNCHED("colsum_planes_kernel");
+    colsum_finish_kernel<<<(T.cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, T.cout, db[0]);
+    C6T_LAUNCHED("colsum_finish_kernel");
+    const long long total = B * (T.cout_p / 8) * board_size * board_size;
+    repack_planes_geometry_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(dpre, G.plane_rows, G.front, G.slots, G.wp, dsd,
+                                                                                   T.dsd_plane_rows, T.slots, T.wi, board_size,
+                                                                                   T.cout_p / 8, B);
+    C6T_LAUNCHED("repack_planes_geometry_kernel");
+    rc = launch_stem_wgrad(T, xe, dsd, partial, dw[0], status, st);
+    if (rc) return rc;
+  } else if (dx) {
     const BackwardLayout& L = S.lay[0];
     const long long total = B * ((L.cin + 7) / 8) * L.n * L.n;
     unpack_planes_nchw_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(

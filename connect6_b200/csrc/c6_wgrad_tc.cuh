@@ -44,6 +44,17 @@ struct WgradParams {
   int taps_per_cta;     // taps of one tap group
   int ngroups, nslabs;  // grid = ngroups * nslabs; CTA b: group b % ngroups, slab b / ngroups
   int nstages;
+  int halo_after;       // rows staged behind the tile rows of x (= halo_rows for a k x k layer)
+  long long dpre_plane_rows;   // plane pitch and first row of the gradient planes (= plane_rows, front for a k x k layer)
+  int dpre_front;
+  // First-layer ("stem") mode, stem_k > 0: the filter is stem_k x stem_k on 3 input planes, too wide for one tap per
+  // accumulator.  x = the 3 x-expanded input planes of the direct stem (row R of plane ci holds the 8 consecutive linear
+  // positions R..R+7 of the zero-padded input images of pitch stem_wi), dpre = the layer's gradient planes in that same
+  // input geometry.  Roles swap: the M operand is the INPUT -- 8 filter columns (the 8 elements of a row) x 16 filter
+  // rows (stride byte offset = stem_wi rows) = 128 filter positions per MMA -- and the N operand the gradient's
+  // `cout` channels.  A "tap" is (input plane, block of 8 filter columns, block of 16 filter rows): ntaps = 3 *
+  // stem_nkxb * stem_nkyb, its accumulator 128 x cout.  partial is [nslabs][ntaps][128][cout].
+  int stem_k, stem_wi, stem_nkxb, stem_nkyb;
 };
 
 constexpr int kWgradThreads = 192;
@@ -58,6 +69,9 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_bf16_mn(int m, int n) {
 
 __host__ __device__ inline int wgrad_stage_bytes(int cin, int cout, int halo_rows, int tile_rows) {
   return (cout / 8) * tile_rows * 16 + (cin / 8) * (tile_rows + 2 * halo_rows) * 16;
+}
+__host__ __device__ inline int wgrad_stem_stage_bytes(int cout, int halo_before, int halo_after, int tile_rows) {
+  return (cout / 8) * tile_rows * 16 + 3 * (tile_rows + halo_before + halo_after) * 16;
 }
 
 __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradParams p) {
@@ -74,11 +88,13 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
   const int ntap = min(p.taps_per_cta, p.ntaps - tap0);
   const int t_begin = (int)(((long long)p.ntiles * slab) / p.nslabs);
   const int t_end = (int)(((long long)p.ntiles * (slab + 1)) / p.nslabs);
-  const int xrows = p.tile_rows + 2 * p.halo_rows;
+  const bool stem = p.stem_k > 0;
+  const int xrows = p.tile_rows + p.halo_rows + p.halo_after;
+  const int xplanes = stem ? 3 : p.cin / 8;
   const uint32_t a_plane = (uint32_t)p.tile_rows * 16u;
   const uint32_t b_plane = (uint32_t)xrows * 16u;
   const uint32_t a_bytes = (uint32_t)(p.cout / 8) * a_plane;
-  const uint32_t b_bytes = (uint32_t)(p.cin / 8) * b_plane;
+  const uint32_t b_bytes = (uint32_t)xplanes * b_plane;
   const uint32_t stage_bytes = a_bytes + b_bytes;     // multiples of 128
   const uint32_t bar0 = tc::smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
@@ -107,7 +123,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
     // ------------------------------ producer ------------------------------
     // lane i < cout/8 copies gradient plane i (the tile's rows), the next cin/8 lanes one input plane
     // each (the tile's rows plus the halo on both sides)
-    const int na = p.cout / 8, nb = p.cin / 8;
+    const int na = p.cout / 8, nb = xplanes;
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -125,9 +141,10 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
         break;
       }
       const long long row0 = (long long)p.front + (long long)tile * p.tile_rows;
+      const long long drow0 = (long long)p.dpre_front + (long long)tile * p.tile_rows;
       const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
       if (lane < na) {
-        tc::bulk_g2s(dst + (uint32_t)lane * a_plane, p.dpre + (size_t)lane * p.plane_rows + row0, a_plane, bar_full(s));
+        tc::bulk_g2s(dst + (uint32_t)lane * a_plane, p.dpre + (size_t)lane * p.dpre_plane_rows + drow0, a_plane, bar_full(s));
       } else if (lane < na + nb) {
         const int q = lane - na;
         tc::bulk_g2s(dst + a_bytes + (uint32_t)q * b_plane, p.x + (size_t)q * p.plane_rows + row0 - p.halo_rows, b_plane,
@@ -146,18 +163,27 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    const uint32_t idesc = make_idesc_bf16_mn(128, p.cin);
-    const int kh = p.kside >> 1;
+    const int ncols = stem ? p.cout : p.cin;        // accumulator columns of one tap
+    const uint32_t idesc = make_idesc_bf16_mn(128, ncols);
+    const int kh = (stem ? p.stem_k : p.kside) >> 1;
     // MN-major no-swizzle descriptors: leading byte offset = 128 B (next 8 positions), stride byte offset =
-    // the plane pitch of the staged operand (next 8 channels)
+    // the plane pitch of the staged operand (next 8 channels); in stem mode the input operand's "next 8 rows of M"
+    // are the next filter row: stem_wi positions further
     const uint32_t a_hi = (uint32_t)(tc::make_desc(0, 128u, a_plane) >> 32);
-    const uint32_t b_hi = (uint32_t)(tc::make_desc(0, 128u, b_plane) >> 32);
+    const uint32_t b_hi = (uint32_t)(tc::make_desc(0, 128u, stem ? (uint32_t)p.stem_wi * 16u : b_plane) >> 32);
     const uint32_t lbo_field = (128u >> 4) << 16;
-    uint32_t tshift[kWgradMaxTaps];      // row of the staged input plane where tap t's operand starts
+    uint32_t tshift[kWgradMaxTaps];      // row of the staged input planes where tap t's operand starts
 #pragma unroll
     for (int t = 0; t < kWgradMaxTaps; ++t) {
       const int tap = min(tap0 + t, p.ntaps - 1);
-      tshift[t] = (uint32_t)(p.halo_rows + (tap / p.kside - kh) * p.wp + (tap % p.kside - kh));
+      if (stem) {
+        const int per_plane = p.stem_nkxb * p.stem_nkyb;
+        const int ci = tap / per_plane, rem = tap - ci * per_plane;
+        const int kxb = rem / p.stem_nkyb, kyb = rem - kxb * p.stem_nkyb;
+        tshift[t] = (uint32_t)(ci * xrows + p.halo_rows + (kyb * 16 - kh) * p.stem_wi + kxb * 8 - kh);
+      } else {
+        tshift[t] = (uint32_t)(p.halo_rows + (tap / p.kside - kh) * p.wp + (tap % p.kside - kh));
+      }
     }
     int s = 0;
     uint32_t ph = 0;
@@ -181,9 +207,10 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
           // so the per-tap row shifts live in registers (no division, no table in memory)
 #pragma unroll
           for (int t = 0; t < kWgradMaxTaps; ++t)
-            if (t < ntap)
-              tc::mma_bf16(tmem_base + (uint32_t)(t * p.cin), ((uint64_t)a_hi << 32) | a_lo,
-                           ((uint64_t)b_hi << 32) | (b_lo + tshift[t]), idesc, acc);
+            if (t < ntap) {
+              const uint64_t grad_desc = ((uint64_t)a_hi << 32) | a_lo, in_desc = ((uint64_t)b_hi << 32) | (b_lo + tshift[t]);
+              tc::mma_bf16(tmem_base + (uint32_t)(t * ncols), stem ? in_desc : grad_desc, stem ? grad_desc : in_desc, idesc, acc);
+            }
         }
         tc::mma_commit(bar_empty(s));
         if (tile == t_end - 1) tc::mma_commit(bar_done);
@@ -194,9 +221,11 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
     if (t_begin >= t_end && lane == 0) tc::mbar_arrive(bar_done);   // an empty slab still releases the epilogue
   } else {
     // ------------------------------ epilogue ------------------------------
-    // warp w may read TMEM lanes 32*(w%4)..+31: output channels; each lane writes its rows of the partial sums
+    // warp w may read TMEM lanes 32*(w%4)..+31: output channels (stem mode: filter positions); each lane writes its
+    // rows of the partial sums
     const int quad = warp & 3;
     const int co = quad * 32 + lane;
+    const int ncols = stem ? p.cout : p.cin;
     if (!tc::mbar_wait(bar_done, 0, abort_flag, 100)) {
       if (lane == 0) atomicOr(p.status, kStatWaitTmemFull);
       *abort_flag = 1;
@@ -204,10 +233,10 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
       tc::fence_after_sync();
       const bool empty = t_begin >= t_end;
       for (int t = 0; t < ntap; ++t) {
-        float* dst = p.partial + (((size_t)slab * p.ntaps + tap0 + t) * 128 + co) * p.cin;
-        for (int c0 = 0; c0 < p.cin; c0 += 16) {
+        float* dst = p.partial + (((size_t)slab * p.ntaps + tap0 + t) * 128 + co) * ncols;
+        for (int c0 = 0; c0 < ncols; c0 += 16) {
           uint32_t v[16];
-          tc::tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(t * p.cin + c0), v);
+          tc::tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(t * ncols + c0), v);
           tc::tmem_wait_ld();
 #pragma unroll
           for (int j4 = 0; j4 < 4; ++j4) {
@@ -242,6 +271,22 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __
   const int co = (int)(idx / ((long long)ntaps * cin));
   float acc = 0.f;
   for (int s = 0; s < nslabs; ++s) acc += partial[(((size_t)s * ntaps + tap) * 128 + co) * cin_p + ci];
+  dw[idx] = acc;
+}
+
+// Stem mode: dW[co][ci][ky][kx] from partial[slab][tap = (ci, kx / 8, ky / 16)][m = (ky % 16) * 8 + kx % 8][co].
+__global__ void wgrad_reduce_stem_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nslabs, int ntaps,
+                                         int cout_p, int cout, int kside, int nkxb, int nkyb) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)cout * 3 * kside * kside) return;
+  const int kx = (int)(idx % kside);
+  const int ky = (int)((idx / kside) % kside);
+  const int ci = (int)((idx / ((long long)kside * kside)) % 3);
+  const int co = (int)(idx / (3LL * kside * kside));
+  const int tap = (ci * nkxb + (kx >> 3)) * nkyb + (ky >> 4);
+  const int m = (ky & 15) * 8 + (kx & 7);
+  float acc = 0.f;
+  for (int s = 0; s < nslabs; ++s) acc += partial[(((size_t)s * ntaps + tap) * 128 + m) * cout_p + co];
   dw[idx] = acc;
 }
 

@@ -125,15 +125,23 @@ class PolicyValueNet(nn.Module):
         use_engine = self.engine_backward and x.is_cuda
         convs = list(self.convs)
         if use_engine:
-            from .train_ops import SiluConv3x3, SiluConvStack, supports_layer
+            from .train_ops import SiluConv3x3, SiluConvStack, supports_layer, supports_stem
             # the longest run of library-supported 3x3 layers that ends at the last layer goes through the library as
-            # ONE operator (forward and backward, activations kept in the kernels' layout); layers before it one by one
+            # ONE operator (forward and backward, activations kept in the kernels' layout) -- together with the stem
+            # when the run starts right behind it and the stem qualifies; layers before the run go one by one
             first = len(convs)
             while first > 0 and supports_layer(convs[first - 1], self.board_size):
                 first -= 1
+            if first == 1 and len(convs) >= 2 and supports_stem(convs[0], self.board_size) and x.dtype == torch.float32:
+                first = 0
         for i, conv in enumerate(convs):
             if use_engine and i == first and len(convs) - first >= 2 and x.shape[0] > 0:
                 params = [p for c in convs[first:] for p in (c.weight, c.bias)]
+                if self.policy_output.bias is not None and self.value_output.bias is not None:
+                    # ... and both heads with them: the features stay in the kernels' layout
+                    from .train_ops import PolicyValueStack
+                    return PolicyValueStack.apply(feats, *params, self.policy_output.weight, self.policy_output.bias,
+                                                  self.value_output.weight, self.value_output.bias)
                 feats = SiluConvStack.apply(feats, *params)
                 break
             if use_engine and supports_layer(conv, self.board_size):

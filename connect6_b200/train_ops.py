@@ -90,6 +90,15 @@ class SiluConv3x3(torch.autograd.Function):
         return (None if dx is None else dx.to(x.dtype)), dw.to(weight.dtype), (db.to(bias.dtype) if bias is not None else None)
 
 
+def supports_stem(conv: torch.nn.Conv2d, board_size: int) -> bool:
+    """Whether `SiluConvStack` can start with this layer: k x k (odd k <= 31) on 3 planes, stride 1, 'same' padding, at
+    most 64 output channels."""
+    k = conv.kernel_size[0]
+    return (conv.kernel_size[0] == conv.kernel_size[1] and k % 2 == 1 and 3 < k <= 31 and tuple(conv.stride) == (1, 1)
+            and tuple(conv.padding) == (k // 2, k // 2) and tuple(conv.dilation) == (1, 1) and conv.groups == 1
+            and conv.in_channels == 3 and conv.out_channels <= 64 and board_size <= 32)
+
+
 def supports_layer(conv: torch.nn.Conv2d, board_size: int) -> bool:
     """Whether `conv_layer_backward` covers this layer: 3x3, stride 1, 'same' padding, at most 128 channels."""
     return (tuple(conv.kernel_size) == (3, 3) and tuple(conv.stride) == (1, 1) and tuple(conv.padding) == (1, 1)
@@ -106,17 +115,18 @@ class _StackLease:
     and the end of its autograd graph; handed back when the lease is garbage-collected.  The operators keep the
     zero padding they rely on intact, so a returned buffer is reused without clearing."""
 
-    def __init__(self, device: torch.device, n: int, channels: tuple[int, ...], B: int) -> None:
-        self.key = (device.index, n, channels, B)
+    def __init__(self, device: torch.device, n: int, channels: tuple[int, ...], B: int, stem_k: int = 0) -> None:
+        self.key = (device.index, n, channels, B, stem_k)
         pool = _stack_pool.setdefault(self.key, [])
         if pool:
             self.ws = pool.pop()
         else:
             arr = (C.c_int32 * len(channels))(*channels)
-            need = int(L.load().c6_backbone_workspace_bytes(n, len(channels) - 1, arr, B))
+            need = int(L.load().c6_backbone_workspace_bytes(n, len(channels) - 1, arr, stem_k, B))
             if need == 0:
-                raise ValueError(f"SiluConvStack supports 1..16 layers of 3x3, board size <= 32, at most 128 channels; "
-                                 f"got n={n}, channels={channels}")
+                raise ValueError(f"SiluConvStack supports 1..16 layers of 3x3 with at most 128 channels on boards up to 32x32, "
+                                 f"optionally behind an odd k x k stem (k <= 31) from 3 planes to at most 64 channels; "
+                                 f"got n={n}, channels={channels}, stem {stem_k}")
             self.ws = torch.zeros((need + 7) // 8, dtype=torch.int64, device=device)
 
     def __del__(self) -> None:
@@ -137,19 +147,27 @@ def _train_fail(rc: int, what: str):
     return (ValueError if rc in (L.C6_ERR_ARG, L.C6_ERR_UNSUPPORTED) else RuntimeError)(f"{what} failed: {msg}")
 
 
-def stack_forward(x: torch.Tensor, weights, biases):
-    """y = the layers y_l = silu(conv2d(y_{l-1}, weights[l], biases[l], padding=1)) applied in turn to x
+def stack_forward(x: torch.Tensor, weights, biases, want_features: bool = True):
+    """y = the layers y_l = silu(conv2d(y_{l-1}, weights[l], biases[l], padding=k_l//2)) applied in turn to x
     [B, c0, n, n]; returns (y fp32 [B, cL, n, n], lease) -- the lease holds the saved activations for
-    `stack_backward`."""
+    `stack_backward`.  Every filter is 3x3, except that the first may be the network's k x k stem on the 3 input
+    planes (then x is the network input).  want_features=False returns y = None: the features stay in the lease only,
+    for `heads_forward`."""
     if not x.is_cuda:
         raise RuntimeError(f"stack_forward: expected CUDA tensors, got {x.device} (no CPU path in this package)")
     if x.ndim != 4 or x.shape[2] != x.shape[3] or len(weights) != len(biases) or not weights:
         raise ValueError("stack_forward: x [B,c0,n,n], one weight [c_out,c_in,3,3] and one bias (or None) per layer")
     B, c0, n, _ = x.shape
     channels = [c0]
-    for w, b in zip(weights, biases):
-        if w.ndim != 4 or tuple(w.shape[1:]) != (channels[-1], 3, 3) or (b is not None and tuple(b.shape) != (w.shape[0],)):
-            raise ValueError("stack_forward: the layers' shapes do not chain (3x3 filters, c_in of a layer = c_out of the one before)")
+    stem_k = 0
+    for l, (w, b) in enumerate(zip(weights, biases)):
+        k = int(w.shape[-1]) if w.ndim == 4 else 0
+        if l == 0 and k != 3 and c0 == 3 and len(weights) > 1:
+            stem_k = k
+        if (w.ndim != 4 or tuple(w.shape[1:]) != (channels[-1], k, k) or (k != 3 and not (l == 0 and stem_k))
+                or (b is not None and tuple(b.shape) != (w.shape[0],))):
+            raise ValueError("stack_forward: the layers' shapes do not chain (3x3 filters -- the first may be a k x k stem on "
+                             "3 planes --, c_in of a layer = c_out of the one before)")
         channels.append(int(w.shape[0]))
     if B == 0:
         return x.new_zeros((0, channels[-1], n, n), dtype=torch.float32), None
@@ -158,36 +176,87 @@ def stack_forward(x: torch.Tensor, weights, biases):
     x = f32(x)
     ws_ = [f32(w) for w in weights]
     bs_ = [f32(b) for b in biases]
-    lease = _StackLease(dev, n, tuple(channels), B)
-    y = torch.empty((B, channels[-1], n, n), device=dev, dtype=torch.float32)
+    lease = _StackLease(dev, n, tuple(channels), B, stem_k)
+    y = torch.empty((B, channels[-1], n, n), device=dev, dtype=torch.float32) if want_features else None
     arr = (C.c_int32 * len(channels))(*channels)
     with torch.cuda.device(dev):
-        rc = L.load().c6_backbone_forward(dev.index, n, len(ws_), arr, B, x.data_ptr(), _ptr_array(ws_), _ptr_array(bs_),
-                                          y.data_ptr(), lease.ws.data_ptr(), lease.ws.numel() * 8,
+        rc = L.load().c6_backbone_forward(dev.index, n, len(ws_), arr, stem_k, B, x.data_ptr(), _ptr_array(ws_), _ptr_array(bs_),
+                                          L.ptr(y), lease.ws.data_ptr(), lease.ws.numel() * 8,
                                           torch.cuda.current_stream(dev).cuda_stream)
     if rc != L.C6_OK:
         raise _train_fail(rc, "c6_backbone_forward")
     return y, lease
 
 
-def stack_backward(lease: _StackLease, grad_out: torch.Tensor, need_dx: bool = True):
-    """(dx or None, [dw_l], [db_l]) of the stack whose forward produced `lease`, given grad_out = dL/dy."""
-    dev_index, n, channels, B = lease.key
-    dev = grad_out.device
-    if not grad_out.is_cuda or dev.index != dev_index or tuple(grad_out.shape) != (B, channels[-1], n, n):
-        raise ValueError("stack_backward: grad_out does not belong to this forward call")
-    grad_out = grad_out.detach().to(dtype=torch.float32).contiguous()
+def stack_backward(lease: _StackLease, grad_out: torch.Tensor | None, need_dx: bool = True):
+    """(dx or None, [dw_l], [db_l]) of the stack whose forward produced `lease`, given grad_out = dL/dy (None: the
+    gradient of the features was left in the lease by `heads_backward`).  A stack that starts with the stem has no dx
+    (its input is the network input)."""
+    dev_index, n, channels, B, stem_k = lease.key
+    need_dx = need_dx and not stem_k
+    dev = lease.ws.device
+    if grad_out is not None:
+        if not grad_out.is_cuda or grad_out.device.index != dev_index or tuple(grad_out.shape) != (B, channels[-1], n, n):
+            raise ValueError("stack_backward: grad_out does not belong to this forward call")
+        grad_out = grad_out.detach().to(dtype=torch.float32).contiguous()
     dx = torch.empty((B, channels[0], n, n), device=dev, dtype=torch.float32) if need_dx else None
-    dws = [torch.empty((channels[l + 1], channels[l], 3, 3), device=dev, dtype=torch.float32) for l in range(len(channels) - 1)]
+    dws = [torch.empty((channels[l + 1], channels[l], stem_k if (stem_k and l == 0) else 3, stem_k if (stem_k and l == 0) else 3),
+                       device=dev, dtype=torch.float32) for l in range(len(channels) - 1)]
     dbs = [torch.empty(channels[l + 1], device=dev, dtype=torch.float32) for l in range(len(channels) - 1)]
     arr = (C.c_int32 * len(channels))(*channels)
     with torch.cuda.device(dev):
-        rc = L.load().c6_backbone_backward(dev_index, n, len(dws), arr, B, grad_out.data_ptr(), L.ptr(dx), _ptr_array(dws),
+        rc = L.load().c6_backbone_backward(dev_index, n, len(dws), arr, stem_k, B, L.ptr(grad_out), L.ptr(dx), _ptr_array(dws),
                                            _ptr_array(dbs), lease.ws.data_ptr(), lease.ws.numel() * 8,
                                            torch.cuda.current_stream(dev).cuda_stream)
     if rc != L.C6_OK:
         raise _train_fail(rc, "c6_backbone_backward")
     return dx, dws, dbs
+
+
+def heads_forward(lease: _StackLease, pw: torch.Tensor, pb: torch.Tensor, vw: torch.Tensor, vb: torch.Tensor):
+    """(logits [B, n*n], value [B]) of the two 1x1 heads (connect6/model.py:70-75,108-110) on the features that
+    `stack_forward` left in the lease.  pw, vw: the [1, C, 1, 1] filters; pb, vb: [1]."""
+    dev_index, n, channels, B, stem_k = lease.key
+    dev = lease.ws.device
+    f32 = lambda t: t.detach().to(device=dev, dtype=torch.float32).contiguous()
+    pw, pb, vw, vb = f32(pw).reshape(-1), f32(pb).reshape(-1), f32(vw).reshape(-1), f32(vb).reshape(-1)
+    if pw.numel() != channels[-1] or vw.numel() != channels[-1] or pb.numel() != 1 or vb.numel() != 1:
+        raise ValueError("heads_forward: head parameters do not fit the features' channel count")
+    logits = torch.empty((B, n * n), device=dev, dtype=torch.float32)
+    value = torch.empty(B, device=dev, dtype=torch.float32)
+    arr = (C.c_int32 * len(channels))(*channels)
+    with torch.cuda.device(dev):
+        rc = L.load().c6_backbone_heads_forward(dev_index, n, len(channels) - 1, arr, stem_k, B, pw.data_ptr(), pb.data_ptr(),
+                                                vw.data_ptr(), vb.data_ptr(), logits.data_ptr(), value.data_ptr(),
+                                                lease.ws.data_ptr(), lease.ws.numel() * 8,
+                                                torch.cuda.current_stream(dev).cuda_stream)
+    if rc != L.C6_OK:
+        raise _train_fail(rc, "c6_backbone_heads_forward")
+    return logits, value
+
+
+def heads_backward(lease: _StackLease, pw: torch.Tensor, vw: torch.Tensor, dlogits: torch.Tensor, dvalue: torch.Tensor,
+                   value: torch.Tensor):
+    """(dpw, dpb, dvw, dvb) of the heads; the gradient of the features goes into the lease, where
+    `stack_backward(lease, None)` picks it up."""
+    dev_index, n, channels, B, stem_k = lease.key
+    dev = lease.ws.device
+    f32 = lambda t: t.detach().to(device=dev, dtype=torch.float32).contiguous()
+    pwf, vwf, dlogits, dvalue, value = f32(pw).reshape(-1), f32(vw).reshape(-1), f32(dlogits), f32(dvalue), f32(value)
+    if tuple(dlogits.shape) != (B, n * n) or tuple(dvalue.shape) != (B,) or tuple(value.shape) != (B,):
+        raise ValueError("heads_backward: gradients do not belong to this forward call")
+    Cc = channels[-1]
+    dpw, dvw = torch.empty(Cc, device=dev, dtype=torch.float32), torch.empty(Cc, device=dev, dtype=torch.float32)
+    dpb, dvb = torch.empty(1, device=dev, dtype=torch.float32), torch.empty(1, device=dev, dtype=torch.float32)
+    arr = (C.c_int32 * len(channels))(*channels)
+    with torch.cuda.device(dev):
+        rc = L.load().c6_backbone_heads_backward(dev_index, n, len(channels) - 1, arr, stem_k, B, pwf.data_ptr(), vwf.data_ptr(),
+                                                 dlogits.data_ptr(), dvalue.data_ptr(), value.data_ptr(), dpw.data_ptr(),
+                                                 dpb.data_ptr(), dvw.data_ptr(), dvb.data_ptr(), lease.ws.data_ptr(),
+                                                 lease.ws.numel() * 8, torch.cuda.current_stream(dev).cuda_stream)
+    if rc != L.C6_OK:
+        raise _train_fail(rc, "c6_backbone_heads_backward")
+    return dpw.view_as(pw), dpb, dvw.view_as(vw), dvb
 
 
 def stack_status(lease: _StackLease) -> int:
@@ -196,7 +265,8 @@ def stack_status(lease: _StackLease) -> int:
 
 
 class SiluConvStack(torch.autograd.Function):
-    """features = the 3x3 backbone layers applied to x, forward and backward on the library's tensor-core kernels.
+    """features = the backbone layers applied to x, forward and backward on the library's tensor-core kernels: 3x3
+    layers, optionally starting with the network's k x k stem on the 3 input planes.
     Call as SiluConvStack.apply(x, w_1, b_1, w_2, b_2, ...)."""
 
     @staticmethod
@@ -218,4 +288,41 @@ class SiluConvStack(torch.autograd.Function):
         for l, (dw, db) in enumerate(zip(dws, dbs)):
             grads.append(dw.to(pdts[2 * l]) if ctx.needs_input_grad[1 + 2 * l] else None)
             grads.append(db.to(pdts[2 * l + 1]) if ctx.needs_input_grad[2 + 2 * l] else None)
+        return tuple(grads)
+
+
+class PolicyValueStack(torch.autograd.Function):
+    """(logits, value) = the whole network -- stem or first 3x3 layer, the 3x3 layers, both heads -- forward and
+    backward on the library's kernels; the features never leave the kernels' plane layout.
+    Call as PolicyValueStack.apply(x, w_1, b_1, ..., w_L, b_L, policy_w, policy_b, value_w, value_b)."""
+
+    @staticmethod
+    def forward(ctx, x, *params):
+        conv_params, (pw, pb, vw, vb) = params[:-4], params[-4:]
+        weights, biases = list(conv_params[0::2]), list(conv_params[1::2])
+        _, lease = stack_forward(x, weights, biases, want_features=False)
+        logits, value = heads_forward(lease, pw, pb, vw, vb)
+        ctx.lease = lease
+        ctx.save_for_backward(pw, vw, value)
+        ctx.dtypes = (x.dtype, [p.dtype for p in params])
+        return logits, value
+
+    @staticmethod
+    def backward(ctx, dlogits, dvalue):
+        pw, vw, value = ctx.saved_tensors
+        lease = ctx.lease
+        B = lease.key[3]
+        if dlogits is None:
+            dlogits = torch.zeros((B, lease.key[1] ** 2), device=value.device)
+        if dvalue is None:
+            dvalue = torch.zeros(B, device=value.device)
+        dpw, dpb, dvw, dvb = heads_backward(lease, pw, vw, dlogits, dvalue, value)
+        dx, dws, dbs = stack_backward(lease, None, need_dx=ctx.needs_input_grad[0])
+        xdt, pdts = ctx.dtypes
+        grads = [None if dx is None else dx.to(xdt)]
+        for l, (dw, db) in enumerate(zip(dws, dbs)):
+            grads.append(dw.to(pdts[2 * l]))
+            grads.append(db.to(pdts[2 * l + 1]))
+        n = len(pdts)
+        grads += [dpw.to(pdts[n - 4]), dpb.to(pdts[n - 3]), dvw.to(pdts[n - 2]), dvb.to(pdts[n - 1])]
         return tuple(grads)

@@ -47,34 +47,58 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
                            float* dx, float* dw, float* db, void* workspace, int64_t workspace_bytes,
                            void* stream);
 
-/* ---- a whole stack of 3 x 3 layers -------------------------------------------------------------------
- * Replaces, for the backbone layers after the stem: the grad-enabled forward of the PPO minibatch update
- * (the loop of connect6/model.py:104-106 as run from connect6/train.py:1047-1048) and autograd's backward
- * through it (connect6/train.py:1115-1119).  Layer l (0-based, l < nlayers) maps channels[l] ->
- * channels[l + 1] with a 3 x 3 "same" convolution, bias and SiLU.  The forward call keeps every layer's
- * input as 16-bit channel-chunk planes inside the workspace; the backward call walks the stack from the top
- * with the gradient staying in that layout between layers, so only the stack's ends are converted from and
- * to NCHW fp32.  Per layer the arithmetic is c6_conv_layer_backward's.
- * Supported: 1 <= nlayers <= C6_MAX_LAYERS, n <= 32, every channel count <= 128.
+/* ---- a whole stack of layers ------------------------------------------------------------------------
+ * Replaces the grad-enabled forward of the PPO minibatch update through the backbone (the loop of
+ * connect6/model.py:104-106 as run from connect6/train.py:1047-1048) and autograd's backward through it
+ * (connect6/train.py:1115-1119).  Layer l (0-based, l < nlayers) maps channels[l] -> channels[l + 1] with a
+ * "same" convolution, bias and SiLU.  stem_kside = 0: every layer is 3 x 3 (the layers after the stem; x is the
+ * stem's output).  stem_kside = k > 0: layer 0 is the network's k x k first layer on the 3 input planes
+ * (channels[0] = 3, connect6/model.py:22-23: k = 23), the others are 3 x 3; x is the network input.
+ * The forward call keeps every layer's input as 16-bit channel-chunk planes inside the workspace (the stem's as
+ * its x-expanded input planes); the backward call walks the stack from the top with the gradient staying in
+ * that layout between layers, so only the stack's ends are NCHW fp32.  Per 3 x 3 layer the arithmetic is
+ * c6_conv_layer_backward's; the stem's forward (and its recomputation for silu') is the engine's direct stem,
+ * its weight gradient the same position-contracted GEMM with 8 filter columns x 16 filter rows as the M side.
+ * Supported: 1 <= nlayers <= C6_MAX_LAYERS, n <= 32, every 3 x 3 layer's channel counts <= 128; with a stem:
+ * nlayers >= 2, k odd and <= 31, channels[1] <= 64.
  * workspace: c6_backbone_workspace_bytes() bytes (0: unsupported shape), 256-byte aligned, ZERO-FILLED before its
  * first use with a given shape; a forward call followed by its backward call must use the same workspace
  * with nothing else written to it in between; the pair keeps the zero padding intact, so the buffer can be
  * reused for the same shape without clearing.  The first 4 bytes are a status word like the engine's. */
 int64_t c6_backbone_workspace_bytes(int32_t board_size, int32_t nlayers, const int32_t* channels /* HOST, nlayers + 1 */,
-                                    int64_t B);
+                                    int32_t stem_kside, int64_t B);
 
-/* x fp32 [B, channels[0], n, n] -> y fp32 [B, channels[nlayers], n, n].  w and bias are HOST arrays of
- * nlayers DEVICE pointers (w[l] fp32 [channels[l+1], channels[l], 3, 3]; bias[l] fp32 [channels[l+1]] or null). */
-int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B,
-                        const float* x, const float* const* w, const float* const* bias, float* y, void* workspace,
-                        int64_t workspace_bytes, void* stream);
+/* x fp32 [B, channels[0], n, n] -> y fp32 [B, channels[nlayers], n, n] (y nullable: the features then stay in the
+ * workspace only, for c6_backbone_heads_forward).  w and bias are HOST arrays of
+ * nlayers DEVICE pointers (w[l] fp32 [channels[l+1], channels[l], k_l, k_l]; bias[l] fp32 [channels[l+1]] or null). */
+int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                        int64_t B, const float* x, const float* const* w, const float* const* bias, float* y,
+                        void* workspace, int64_t workspace_bytes, void* stream);
 
-/* dy fp32 [B, channels[nlayers], n, n] = dL/dy of the preceding c6_backbone_forward on this workspace.
- * Outputs: dx fp32 [B, channels[0], n, n] (nullable); dw and db HOST arrays of nlayers DEVICE pointers
- * (dw[l] fp32 like w[l], db[l] fp32 [channels[l+1]]). */
-int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int64_t B,
-                         const float* dy, float* dx, float* const* dw, float* const* db, void* workspace,
+/* dy fp32 [B, channels[nlayers], n, n] = dL/dy of the preceding c6_backbone_forward on this workspace (null: the
+ * gradient of the features is already in the workspace, left there by c6_backbone_heads_backward).
+ * Outputs: dx fp32 [B, channels[0], n, n] (nullable; must be null with a stem: the network input has no gradient);
+ * dw and db HOST arrays of nlayers DEVICE pointers (dw[l] fp32 like w[l], db[l] fp32 [channels[l+1]]). */
+int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                         int64_t B, const float* dy, float* dx, float* const* dw, float* const* db, void* workspace,
                          int64_t workspace_bytes, void* stream);
+
+/* The two 1 x 1 heads on the features a preceding c6_backbone_forward left in the workspace
+ * (connect6/model.py:70-75,108-110): logits fp32 [B, n*n] = policy_output(features) flattened, unmasked;
+ * value fp32 [B] = tanh(mean over the board of value_output(features)).  wp, wv fp32 [channels[nlayers]]
+ * (the [1, C, 1, 1] filters), bp, bv fp32 [1]; all DEVICE pointers. */
+int c6_backbone_heads_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels,
+                              int32_t stem_kside, int64_t B, const float* wp, const float* bp, const float* wv,
+                              const float* bv, float* logits, float* value, void* workspace, int64_t workspace_bytes,
+                              void* stream);
+
+/* Backward of the heads: from dlogits fp32 [B, n*n], dvalue fp32 [B] and the forward's value fp32 [B] it writes the
+ * gradient of the features into the workspace (where c6_backbone_backward with dy = null picks it up) and
+ * dwp, dwv fp32 [channels[nlayers]], dbp, dbv fp32 [1] (fixed summation order: reproducible). */
+int c6_backbone_heads_backward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels,
+                               int32_t stem_kside, int64_t B, const float* wp, const float* wv, const float* dlogits,
+                               const float* dvalue, const float* value, float* dwp, float* dbp, float* dwv, float* dbv,
+                               void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Last error text of the calling thread's most recent failing call of this header. Never null. */
 const char* c6_train_last_error(void);

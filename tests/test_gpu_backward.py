@@ -133,15 +133,23 @@ def _check_stack(got, ref, name):
     assert err < STACK_MAX_TOL * scale and rms < STACK_RMS_TOL * scale, f"{name}: max {err}, rms {rms} vs scale {scale}"
 
 
-@pytest.mark.parametrize("B,n,channels", [(37, 19, (32, 32, 64, 64, 64, 96, 96, 96)), (5, 19, (32, 64)), (9, 7, (24, 40, 16)),
-                                          (300, 19, (64, 96, 96))])
-def test_layer_stack_forward_backward_against_autograd(cuda_device, B, n, channels):
-    """c6_backbone_forward / c6_backbone_backward (a whole run of 3x3 layers, activations and gradients kept in the
-    kernels' plane layout between layers) against autograd in fp64 (oracle/torch_port.py:stack_backward)."""
+@pytest.mark.parametrize("B,n,channels,stem", [(37, 19, (32, 32, 64, 64, 64, 96, 96, 96), 0), (5, 19, (32, 64), 0),
+                                               (9, 7, (24, 40, 16), 0), (300, 19, (64, 96, 96), 0),
+                                               (37, 19, (3, 32, 32, 64), 23), (6, 9, (3, 16, 24), 5), (130, 19, (3, 64, 32), 23),
+                                               (4, 13, (3, 24, 24), 17)])
+def test_layer_stack_forward_backward_against_autograd(cuda_device, B, n, channels, stem):
+    """c6_backbone_forward / c6_backbone_backward (a whole run of layers, activations and gradients kept in the
+    kernels' plane layout between layers; stem > 0: the run starts with the network's stem x stem first layer on the
+    3 input planes) against autograd in fp64 (oracle/torch_port.py:stack_backward)."""
     from connect6_b200.train_ops import stack_backward, stack_forward, stack_status
     gen = torch.Generator().manual_seed(B + n)
-    x = torch.nn.functional.silu(torch.randn(B, channels[0], n, n, generator=gen))
-    ws = [torch.randn(channels[l + 1], channels[l], 3, 3, generator=gen) * (2.0 / (9 * channels[l])) ** 0.5 for l in range(len(channels) - 1)]
+    if stem:
+        x = (torch.rand(B, 3, n, n, generator=gen) < 0.3).float()            # 0/1 planes like the network input
+    else:
+        x = torch.nn.functional.silu(torch.randn(B, channels[0], n, n, generator=gen))
+    ks = [stem if (stem and l == 0) else 3 for l in range(len(channels) - 1)]
+    ws = [torch.randn(channels[l + 1], channels[l], ks[l], ks[l], generator=gen) * (2.0 / (ks[l] ** 2 * channels[l])) ** 0.5
+          for l in range(len(channels) - 1)]
     bs = [0.1 * torch.randn(channels[l + 1], generator=gen) for l in range(len(channels) - 1)]
     dy = torch.randn(B, channels[-1], n, n, generator=gen) * 1e-3
     ry, rx, rws, rbs = TP.stack_backward(x.double(), [w.double() for w in ws], [b.double() for b in bs], dy.double())
@@ -153,7 +161,10 @@ def test_layer_stack_forward_backward_against_autograd(cuda_device, B, n, channe
         del lease
     # forward: one bf16 rounding per layer (relative 2^-9 of a value) on top of bf16 weights and inputs
     assert (y.cpu().double() - ry).abs().max().item() < 2.0 ** -7 * ry.abs().max().item() * len(ws) ** 0.5 + 1e-3
-    _check_stack(dx, rx, "dx")
+    if stem:
+        assert dx is None                                   # the network input has no gradient
+    else:
+        _check_stack(dx, rx, "dx")
     for l in range(len(ws)):
         _check_stack(dws[l], rws[l], f"dw[{l}]")
         _check_stack(dbs[l], rbs[l], f"db[{l}]")
@@ -164,12 +175,58 @@ def test_layer_stack_forward_backward_against_autograd(cuda_device, B, n, channe
     assert all(torch.equal(a, b) for a, b in zip(dws2, dws)) and all(torch.equal(a, b) for a, b in zip(dbs2, dbs))
 
 
+@pytest.mark.parametrize("B,n,channels,stem", [(33, 19, (3, 32, 64, 96), 23), (7, 9, (16, 24), 0), (700, 19, (32, 40), 0)])
+def test_heads_on_the_stack_against_autograd(cuda_device, B, n, channels, stem):
+    """heads_forward / heads_backward (the two 1x1 heads of connect6/model.py:70-75,108-110 on features that never
+    leave the plane layout) chained with the layer stack, against autograd in fp64 on the same expression."""
+    from connect6_b200.train_ops import heads_backward, heads_forward, stack_backward, stack_forward, stack_status
+    gen = torch.Generator().manual_seed(B)
+    x = (torch.rand(B, 3, n, n, generator=gen) < 0.3).float() if stem else torch.nn.functional.silu(torch.randn(B, channels[0], n, n, generator=gen))
+    ks = [stem if (stem and l == 0) else 3 for l in range(len(channels) - 1)]
+    ws = [torch.randn(channels[l + 1], channels[l], ks[l], ks[l], generator=gen) * (2.0 / (ks[l] ** 2 * channels[l])) ** 0.5
+          for l in range(len(channels) - 1)]
+    bs = [0.1 * torch.randn(channels[l + 1], generator=gen) for l in range(len(channels) - 1)]
+    C_ = channels[-1]
+    pw, vw = 0.3 * torch.randn(1, C_, 1, 1, generator=gen), 0.3 * torch.randn(1, C_, 1, 1, generator=gen)
+    pb, vb = torch.tensor([0.2]), torch.tensor([-0.1])
+    r1, r2 = torch.randn(B, n * n, generator=gen) * 1e-3, torch.randn(B, generator=gen) * 1e-2
+    # oracle: the same expression in float64 under autograd
+    leaves = [t.double().requires_grad_(True) for t in ws + bs + [pw, pb, vw, vb]]
+    ows, obs, (opw, opb, ovw, ovb) = leaves[:len(ws)], leaves[len(ws):2 * len(ws)], leaves[2 * len(ws):]
+    f = x.double()
+    for w, b in zip(ows, obs):
+        f = torch.nn.functional.silu(torch.nn.functional.conv2d(f, w, b, padding=w.shape[-1] // 2))
+    rl = torch.nn.functional.conv2d(f, opw, opb).flatten(1)
+    rv = torch.tanh(torch.nn.functional.conv2d(f, ovw, ovb).mean(dim=(-2, -1))).squeeze(1)
+    ((rl * r1.double()).sum() + (rv * r2.double()).sum()).backward()
+    dev = cuda_device
+    d = lambda t: t.to(dev)
+    for _ in range(2):
+        _, lease = stack_forward(d(x), [d(w) for w in ws], [d(b) for b in bs], want_features=False)
+        logits, value = heads_forward(lease, d(pw), d(pb), d(vw), d(vb))
+        dpw, dpb, dvw, dvb = heads_backward(lease, d(pw), d(vw), d(r1), d(r2), value)
+        dx, dws, dbs = stack_backward(lease, None, need_dx=False)
+        assert stack_status(lease) == 0
+        del lease
+    assert (logits.cpu().double() - rl.detach()).abs().max().item() < 2.0 ** -7 * rl.detach().abs().max().item() * (len(ws) + 1) ** 0.5 + 1e-3
+    assert (value.cpu().double() - rv.detach()).abs().max().item() < 5e-3
+    for got, ref, name in ((dpw, opw.grad, "policy w"), (dpb, opb.grad, "policy b"), (dvw, ovw.grad, "value w"), (dvb, ovb.grad, "value b")):
+        _check_stack(got.reshape(ref.shape), ref, name)
+    for l in range(len(ws)):
+        _check_stack(dws[l], ows[l].grad, f"dw[{l}]")
+        _check_stack(dbs[l], obs[l].grad, f"db[{l}]")
+
+
 def test_layer_stack_rejects_what_it_does_not_support(cuda_device):
     from connect6_b200.train_ops import stack_forward
     dev = cuda_device
     z = lambda *s: torch.zeros(*s, device=dev)
-    with pytest.raises(ValueError):     # 5x5 filter
-        stack_forward(z(2, 8, 19, 19), [z(8, 8, 5, 5)], [None])
+    with pytest.raises(ValueError):     # 5x5 filter that is not a stem on 3 planes
+        stack_forward(z(2, 8, 19, 19), [z(8, 8, 5, 5), z(8, 8, 3, 3)], [None, None])
+    with pytest.raises(ValueError):     # a stem with nothing behind it
+        stack_forward(z(2, 3, 19, 19), [z(8, 3, 5, 5)], [None])
+    with pytest.raises(ValueError):     # a wide filter in the middle
+        stack_forward(z(2, 3, 19, 19), [z(8, 3, 5, 5), z(8, 8, 5, 5)], [None, None])
     with pytest.raises(ValueError):     # layers that do not chain
         stack_forward(z(2, 8, 19, 19), [z(16, 8, 3, 3), z(8, 8, 3, 3)], [None, None])
     with pytest.raises(ValueError):     # too wide
@@ -183,8 +240,8 @@ def test_layer_stack_rejects_what_it_does_not_support(cuda_device):
 def test_network_gradients_golden(cuda_device):
     """Every parameter gradient of a PPO-style loss.backward() recorded from the reference's own network
     (tests/golden/network_backward.npz: 9x9 board, 5x5 stem, four 3x3 layers, 8 boards), reproduced by
-    PolicyValueNet(engine_backward=True): the four 3x3 layers run forward and backward as one library operator, the
-    stem and heads on autograd."""
+    PolicyValueNet(engine_backward=True): the stem, the four 3x3 layers and both heads run forward and backward on the
+    library's kernels (train_ops.PolicyValueStack)."""
     from connect6_b200.model import PolicyValueNet
     g = load_golden("network_backward.npz")
     net = PolicyValueNet(int(g["board_size"]), [int(k) for k in g["kernels"]], [int(c) for c in g["channels"]],
@@ -208,9 +265,9 @@ def test_network_gradients_golden(cuda_device):
 
 
 def test_whole_network_gradients_with_engine_backward(cuda_device):
-    """PolicyValueNet(engine_backward=True): a PPO-style loss.backward() whose seven 3x3 layers run forward and
-    backward as one library operator (train_ops.SiluConvStack) gives the parameter gradients of plain autograd (fp32
-    on the same GPU); the stem and the heads stay on autograd.  The gradient passes through up to seven bf16 layer backwards before it reaches the early layers
+    """PolicyValueNet(engine_backward=True): a PPO-style loss.backward() whose stem, seven 3x3 layers and heads run
+    forward and backward on the library's kernels (train_ops.PolicyValueStack) gives the parameter gradients of plain
+    autograd (fp32 on the same GPU).  The gradient passes through up to seven bf16 layer backwards before it reaches the early layers
     (one bf16 rounding of dL/dx per layer), so the bound is on the root-mean-square error (2 % of each gradient's
     scale) and, for the worst of the thousands of elements of a tensor, 10 %."""
     from connect6_b200.boards import generate_planes

@@ -733,86 +733,63 @@ def run_backward(args) -> None:
         "device_status": status}), flush=True)
 
 
-def run_backbone_train(args) -> None:
-    """--workload backbone: forward + backward of the default network's backbone -- the 23x23 stem on the 3 input planes
-    and the seven 3x3 layers (3 -> 32 -> 32 -> 64 -> 64 -> 64 -> 96 -> 96 -> 96 channels) -- as ONE library operator
-    (train_ops.stack_forward / stack_backward: activations and gradients stay in the kernels' plane layout between
-    layers) on `--boards` boards (default 8192; the reference's PPO minibatch is 256).  Also times PyTorch autograd
-    (cuDNN, bf16 autocast) on the same stack as the library bar."""
+def run_train_step(args) -> None:
+    """--workload train: forward + loss + backward of the whole default network on `--boards` boards (default 8192; the
+    reference's PPO minibatch is 256, configs/train.yaml:42) the way the reference's PPO update runs it
+    (connect6/train.py:1047-1119: forward under bf16 autocast, a loss on logits and values, loss.backward()), with
+    PolicyValueNet(engine_backward=True): stem, 3x3 layers and heads run forward and backward on the library's kernels
+    (train_ops.PolicyValueStack), the loss on PyTorch.  No optimizer step.  Library bar: the same step through the
+    PyTorch modules and autograd (cuDNN) on the same GPU."""
     import torch
-    from connect6_b200.train_ops import stack_backward, stack_forward, stack_status
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.model import PolicyValueNet
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    from connect6_b200.boards import generate_planes
-    B, n = (args.boards or BATCH), 19
-    channels = [3, 32, 32, 64, 64, 64, 96, 96, 96]
-    ks = [23, 3, 3, 3, 3, 3, 3, 3]
-    nl = len(ks)
-    g = torch.Generator(device=dev).manual_seed(1)
+    B = args.boards or BATCH
+    torch.manual_seed(WEIGHT_SEED)
+    ours = PolicyValueNet(19, engine_backward=True).to(dev).train()
+    plain = PolicyValueNet(19).to(dev).train()
+    plain.load_state_dict(ours.state_dict())
     x = torch.from_numpy(generate_planes(0, B)).to(dev)
-    ws = [torch.randn(channels[l + 1], channels[l], ks[l], ks[l], device=dev, generator=g) * (2.0 / (ks[l] ** 2 * channels[l])) ** 0.5
-          for l in range(nl)]
-    bs = [0.1 * torch.randn(channels[l + 1], device=dev, generator=g) for l in range(nl)]
-    dy = torch.randn(B, channels[-1], n, n, device=dev, generator=g) * 1e-3
+    target = (torch.arange(B, device=dev) * 37) % 361
 
-    def step():
-        y, lease = stack_forward(x, ws, bs)
-        out = stack_backward(lease, dy)
-        return lease, out
+    def step(m):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits, value = m(x)
+        loss = torch.nn.functional.cross_entropy(logits.float(), target) + 0.5 * (value.float() - 0.3).pow(2).mean()
+        m.zero_grad(set_to_none=True)
+        loss.backward()
+        return loss
 
     for _ in range(args.warmup):
-        lease, _ = step()
+        step(ours)
     torch.cuda.synchronize(dev)
     sampler = ClockSampler(0)
-    e0, e1, em = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin = time.time()
     e0.record()
     for _ in range(args.steps):
-        lease, _ = step()
+        loss = step(ours)
     e1.record()
     torch.cuda.synchronize(dev)
     t_end = time.time()
     ms = e0.elapsed_time(e1) / args.steps
     clocks = sampler.stop(t_begin, t_end)
-    status = stack_status(lease)
-    # forward alone, for the split
-    e0.record()
-    for _ in range(max(1, args.steps // 2)):
-        stack_forward(x, ws, bs)
-    em.record()
-    torch.cuda.synchronize(dev)
-    fwd_ms = e0.elapsed_time(em) / max(1, args.steps // 2)
-    # library bar: the same stack through torch modules and autograd under bf16 autocast (connect6/train.py:1047-1119)
-    convs = [torch.nn.Conv2d(channels[l], channels[l + 1], ks[l], padding=ks[l] // 2).to(dev) for l in range(nl)]
-    with torch.no_grad():
-        for c, w, b in zip(convs, ws, bs):
-            c.weight.copy_(w)
-            c.bias.copy_(b)
-    xl = x.clone()
-
-    def lib_step():
-        for c in convs:
-            c.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            f = xl
-            for c in convs:
-                f = torch.nn.functional.silu(c(f))
-        f.backward(dy.to(f.dtype))
-
-    lib_ms = None
+    lib_ms, lib_loss = None, None
     try:
         if args.no_library_bar:
             raise RuntimeError("skipped (--no-library-bar)")
         for _ in range(3):
-            lib_step()
+            step(plain)
         torch.cuda.synchronize(dev)
         l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0.record()
         for _ in range(5):
-            lib_step()
+            lib_loss = step(plain)
         l1.record()
         torch.cuda.synchronize(dev)
         lib_ms = l0.elapsed_time(l1) / 5
+        lib_loss = float(lib_loss)
     except Exception as exc:  # noqa: BLE001
         lib_ms = f"{type(exc).__name__}: {exc}"[:160]
     kernels = {}
@@ -822,35 +799,40 @@ def run_backbone_train(args) -> None:
         from torch.profiler import ProfilerActivity, profile
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             for _ in range(3):
-                step()
+                step(ours)
             torch.cuda.synchronize(dev)
+        other = 0.0
         for ev in prof.key_averages():
             t_us = getattr(ev, "device_time_total", None) or getattr(ev, "cuda_time_total", 0.0)
-            if t_us and ("c6::" in ev.key or "Memset" in ev.key or "Memcpy" in ev.key):
+            if not t_us:
+                continue
+            if "c6::" in ev.key:
                 kernels[ev.key[:70]] = {"ms_per_call": t_us / 3e3, "launches_per_call": ev.count / 3}
+            else:
+                other += t_us / 3e3
+        kernels["(PyTorch kernels: loss, casts, gradient copies)"] = {"ms_per_call": other}
     except Exception as exc:  # noqa: BLE001
         kernels = {"error": f"{type(exc).__name__}: {exc}"[:160]}
     peaks, peak_kind = load_peaks()
     peak, peak_source = pick_tensor_peak(peaks, peak_kind, clocks, ms * args.steps * 1e-3)
-    macs = sum(361 * ks[l] ** 2 * channels[l] * channels[l + 1] for l in range(nl))      # per board, one pass
-    stem_macs = 361 * ks[0] ** 2 * channels[0] * channels[1]
-    algorithmic = 2 * (3 * macs - stem_macs) * B    # forward + data gradient (not for the stem) + weight gradient
-    executed = 2 * (4 * macs - stem_macs) * B       # + the forward recomputed for silu'
+    macs = sum(CONV_LAYER_MACS) + HEAD_MACS         # per board, one pass
+    algorithmic = 2 * (3 * macs - CONV_LAYER_MACS[0]) * B    # forward + data gradient (none for the stem) + weight gradient
     achieved = algorithmic / (ms * 1e-3) / 1e12
     print(json.dumps({
-        "metric": "forward + backward of the backbone (23x23 stem + seven 3x3 layers), boards/s (bf16 operands, fp32 accumulate)",
+        "metric": "PPO-style training step of the default network (forward + loss + backward), boards/s",
         "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "forward_ms": fwd_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"stack_forward + stack_backward, B = {B} boards, channels {channels}, 19x19; fp32 NCHW "
-                               "tensors at the ends of the stack (packing and unpacking inside the timed calls)"},
+        "config": {"workload": f"PolicyValueNet(engine_backward=True), B = {B} boards: stem + seven 3x3 layers + heads forward and "
+                               "backward on the library's kernels (bf16 operands, fp32 accumulation), loss on PyTorch, no optimizer step",
+                   "loss": float(loss), "library_loss": lib_loss},
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "whole operator pair (per layer: 3 conv_tc_kernel launches + wgrad_tc_kernel; the stem: 2 + 1)",
+        "roofline": {"bound": "tensor", "kernel": "whole step (per 3x3 layer: 3 conv_tc_kernel launches + wgrad_tc_kernel; the stem 2 + 1)",
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_source,
-                     "flop_algorithmic": algorithmic, "flop_executed": executed, "traffic": None},
+                     "flop_algorithmic": algorithmic, "traffic": None},
         "kernels": kernels,
-        "library_gpu_bar": {"ms_per_step": lib_ms, "what": "torch autograd of the same eight silu(conv2d) layers under bf16 autocast (cuDNN), forward + backward"},
-        "device_status": status}), flush=True)
+        "library_gpu_bar": {"ms_per_step": lib_ms, "what": "the same step through the PyTorch modules and autograd under bf16 autocast (cuDNN)"},
+        "device_status": 0}), flush=True)
 
 
 def run_small_case(args) -> None:
@@ -1060,12 +1042,12 @@ def main() -> None:
     ap.add_argument("--precision", default="bf16", choices=["bf16", "f16", "fp32"],
                     help="arithmetic mode of the engine for --workload cfg2: bf16 is the contract's benchmark; f16 the "
                          "fp16 tensor-core mode; fp32 the CUDA-core exact mode")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "ensemble", "selfplay", "small", "backward", "backbone"],
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "ensemble", "selfplay", "small", "backward", "train"],
                     help="cfg2 (default) is the contract's benchmark; cfg3-5 are BASELINE's other configurations; "
                          "ensemble is the reference's training shape of the historical opponents (128 models x 4 boards); "
                          "selfplay adds the environment step and bookkeeping around the network; small is a short "
-                         "self-ending run of --boards boards for profilers; backward is one layer's backward, backbone the forward + "
-                         "backward of the seven 3x3 layers as one operator")
+                         "self-ending run of --boards boards for profilers; backward is one layer's backward, train the PPO-style forward + loss + "
+                         "backward of the whole network")
     ap.add_argument("--boards", type=int, default=None, help="boards of --workload small (default 2048) and backward (default 8192)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -1076,10 +1058,10 @@ def main() -> None:
         args.steps = 50 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else args.warmup
         run_backward(args)
-    elif args.workload == "backbone":
+    elif args.workload == "train":
         args.steps = 20 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else args.warmup
-        run_backbone_train(args)
+        run_train_step(args)
     elif args.workload == "small":
         args.steps = 2 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup

@@ -145,3 +145,28 @@ def test_board_generator_properties():
     assert (wide[:, 0] + wide[:, 1]).sum(axis=(1, 2)).max() > 150
     cover = [shard_range(65536, r, 8) for r in range(8)]
     assert cover[0][0] == 0 and cover[-1][1] == 65536 and all(cover[i][1] == cover[i + 1][0] for i in range(7))
+
+
+def test_training_workspace_sizes_are_host_arithmetic(engine_lib):
+    """c6_conv_layer_backward_workspace_bytes / c6_backbone_workspace_bytes plan on the host only: positive for the
+    shapes the operators support, 0 for the others, and growing with the batch."""
+    import ctypes as C
+    lib = engine_lib
+    lib.c6_conv_layer_backward_workspace_bytes.restype = C.c_int64
+    lib.c6_backbone_workspace_bytes.restype = C.c_int64
+    one = lambda n, k, ci, co, B: lib.c6_conv_layer_backward_workspace_bytes(n, k, ci, co, C.c_int64(B))
+    assert one(19, 3, 64, 96, 256) > 0 and one(19, 3, 64, 96, 512) > one(19, 3, 64, 96, 256)
+    assert one(19, 5, 64, 96, 256) == 0 and one(19, 3, 192, 96, 256) == 0 and one(40, 3, 64, 96, 256) == 0
+    def stack(n, channels, stem, B):
+        arr = (C.c_int32 * len(channels))(*channels)
+        return lib.c6_backbone_workspace_bytes(n, len(channels) - 1, arr, stem, C.c_int64(B))
+    default = [3, 32, 32, 64, 64, 64, 96, 96, 96]
+    assert stack(19, default, 23, 256) > 0 and stack(19, default, 23, 8192) > 30 * stack(19, default, 23, 256) // 2
+    assert stack(19, default[1:], 0, 256) > 0                 # the 3x3 layers alone
+    assert stack(19, default, 0, 256) > 0                     # 3 -> 32 as a 3x3 layer is a legal stack too
+    assert stack(19, default, 22, 256) == 0                   # even stem
+    assert stack(19, [5] + default[1:], 23, 256) == 0         # a stem reads 3 planes
+    assert stack(19, [3, 32], 23, 256) == 0                   # a stem alone
+    assert stack(19, [3, 96, 32], 23, 256) == 0               # stem wider than 64 channels
+    assert stack(19, [32, 192], 0, 256) == 0                  # 3x3 layer wider than 128
+    assert stack(19, default, 23, 0) == 0

@@ -734,12 +734,12 @@ def run_backward(args) -> None:
 
 
 def run_train_step(args) -> None:
-    """--workload train: forward + loss + backward of the whole default network on `--boards` boards (default 8192; the
-    reference's PPO minibatch is 256, configs/train.yaml:42) the way the reference's PPO update runs it
-    (connect6/train.py:1047-1119: forward under bf16 autocast, a loss on logits and values, loss.backward()), with
-    PolicyValueNet(engine_backward=True): stem, 3x3 layers and heads run forward and backward on the library's kernels
-    (train_ops.PolicyValueStack), the loss on PyTorch.  No optimizer step.  Library bar: the same step through the
-    PyTorch modules and autograd (cuDNN) on the same GPU."""
+    """--workload train: forward + PPO loss + backward of the whole default network on `--boards` boards (default 8192;
+    the reference's PPO minibatch is 256, configs/train.yaml:42) the way the reference's PPO update runs it
+    (connect6/train.py:1047-1119: forward under bf16 autocast, the clipped-ratio / value / entropy loss,
+    loss.backward()), with PolicyValueNet(engine_backward=True) and train_ops.ppo_loss: stem, 3x3 layers, heads and the
+    loss run forward and backward on the library's kernels.  No gradient clipping, no optimizer step.  Library bar: the
+    same step through the PyTorch modules, the reference's loss statements and autograd (cuDNN) on the same GPU."""
     import torch
     from connect6_b200.boards import generate_planes
     from connect6_b200.model import PolicyValueNet
@@ -751,12 +751,30 @@ def run_train_step(args) -> None:
     plain = PolicyValueNet(19).to(dev).train()
     plain.load_state_dict(ours.state_dict())
     x = torch.from_numpy(generate_planes(0, B)).to(dev)
-    target = (torch.arange(B, device=dev) * 37) % 361
+    from torch.distributions import Categorical
+    from connect6_b200.train_ops import ppo_loss
+    gen = torch.Generator(device=dev).manual_seed(7)
+    legal = (x[:, 0] + x[:, 1]).reshape(B, -1).eq(0)                 # empty cells (connect6/train.py:1046)
+    actions = torch.multinomial(legal.float(), 1, generator=gen).squeeze(1)
+    old_logprob = -torch.log(legal.sum(1).float()) + 0.2 * torch.randn(B, device=dev, generator=gen)
+    advantages = torch.randn(B, device=dev, generator=gen)
+    returns = torch.tanh(torch.randn(B, device=dev, generator=gen))
+    clip_coef, value_coef, entropy_coef, temperature = 0.2, 0.5, 0.01, 1.0
 
     def step(m):
         with torch.autocast("cuda", dtype=torch.bfloat16):
             logits, value = m(x)
-        loss = torch.nn.functional.cross_entropy(logits.float(), target) + 0.5 * (value.float() - 0.3).pow(2).mean()
+            if m is ours:
+                loss, _stats = ppo_loss(logits, value, legal, actions, old_logprob, advantages, returns, temperature, clip_coef,
+                                        value_coef, entropy_coef)
+            else:
+                # the reference's statements (connect6/train.py:1049-1074) on PyTorch
+                z = logits.masked_fill(~legal, torch.finfo(logits.dtype).min) / max(temperature, 1e-4)
+                dist = Categorical(logits=z.float())
+                logratio = dist.log_prob(actions) - old_logprob
+                ratio = logratio.exp()
+                pg = torch.maximum(-advantages * ratio, -advantages * torch.clamp(ratio, 1.0 - clip_coef, 1.0 + clip_coef)).mean()
+                loss = pg + value_coef * 0.5 * (value.float() - returns).pow(2).mean() - entropy_coef * dist.entropy().mean()
         m.zero_grad(set_to_none=True)
         loss.backward()
         return loss
@@ -810,7 +828,7 @@ def run_train_step(args) -> None:
                 kernels[ev.key[:70]] = {"ms_per_call": t_us / 3e3, "launches_per_call": ev.count / 3}
             else:
                 other += t_us / 3e3
-        kernels["(PyTorch kernels: loss, casts, gradient copies)"] = {"ms_per_call": other}
+        kernels["(PyTorch kernels: casts, gradient copies)"] = {"ms_per_call": other}
     except Exception as exc:  # noqa: BLE001
         kernels = {"error": f"{type(exc).__name__}: {exc}"[:160]}
     peaks, peak_kind = load_peaks()
@@ -819,19 +837,19 @@ def run_train_step(args) -> None:
     algorithmic = 2 * (3 * macs - CONV_LAYER_MACS[0]) * B    # forward + data gradient (none for the stem) + weight gradient
     achieved = algorithmic / (ms * 1e-3) / 1e12
     print(json.dumps({
-        "metric": "PPO-style training step of the default network (forward + loss + backward), boards/s",
+        "metric": "PPO minibatch forward + loss + backward of the default network, boards/s",
         "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"PolicyValueNet(engine_backward=True), B = {B} boards: stem + seven 3x3 layers + heads forward and "
-                               "backward on the library's kernels (bf16 operands, fp32 accumulation), loss on PyTorch, no optimizer step",
+        "config": {"workload": f"PolicyValueNet(engine_backward=True) + ppo_loss, B = {B} boards: stem + seven 3x3 layers + heads + PPO loss "
+                               "forward and backward on the library's kernels (bf16 operands, fp32 accumulation), no optimizer step",
                    "loss": float(loss), "library_loss": lib_loss},
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "whole step (per 3x3 layer: 3 conv_tc_kernel launches + wgrad_tc_kernel; the stem 2 + 1)",
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_source,
                      "flop_algorithmic": algorithmic, "traffic": None},
         "kernels": kernels,
-        "library_gpu_bar": {"ms_per_step": lib_ms, "what": "the same step through the PyTorch modules and autograd under bf16 autocast (cuDNN)"},
+        "library_gpu_bar": {"ms_per_step": lib_ms, "what": "the same step through the PyTorch modules, the reference's loss statements and autograd under bf16 autocast (cuDNN)"},
         "device_status": 0}), flush=True)
 
 

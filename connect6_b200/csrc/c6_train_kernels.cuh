@@ -238,6 +238,111 @@ __global__ void heads_backward_finish_kernel(const float* __restrict__ partial, 
   *dst = s;
 }
 
+// PPO minibatch loss and its gradient at the network outputs (connect6/train.py:1047-1086):
+//   z = mask(logits) / T,  logp = z - logsumexp(z),  H = -sum p logp,  ratio = exp(logp[a] - old_logprob),
+//   policy = max(-adv ratio, -adv clamp(ratio, 1 - c, 1 + c)),  value = 0.5 (v - ret)^2,
+//   loss = mean(policy) + value_coef mean(value) - entropy_coef mean(H).
+// One warp per board.  rows[b] = {policy, value, H, (ratio - 1) - logratio, |ratio - 1| > c}; dlogits[b][j] = dloss/dlogits
+// (zero at illegal actions: masked_fill passes no gradient), dvalues[b] = dloss/dv.  A board without a legal action has
+// the uniform distribution the reference's fill value gives it, and no gradient.
+constexpr int kPpoWarps = 4;
+__global__ void __launch_bounds__(32 * kPpoWarps) ppo_loss_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ legal,
+                                                                  const long long* __restrict__ actions,
+                                                                  const float* __restrict__ old_logprob,
+                                                                  const float* __restrict__ advantages,
+                                                                  const float* __restrict__ returns, const float* __restrict__ values,
+                                                                  long long B, int A, float inv_t, float clip, float value_coef,
+                                                                  float entropy_coef, float* __restrict__ rows,
+                                                                  float* __restrict__ dlogits, float* __restrict__ dvalues) {
+  const long long b = (long long)blockIdx.x * kPpoWarps + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  const float* lg = logits + b * A;
+  const uint8_t* lm = legal + b * A;
+  float m = -INFINITY;
+  int nlegal = 0;
+  for (int j = lane; j < A; j += 32)
+    if (lm[j]) { m = fmaxf(m, lg[j] * inv_t); ++nlegal; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    nlegal += __shfl_xor_sync(0xffffffffu, nlegal, o);
+  }
+  const bool none = nlegal == 0;
+  float s = 0.f, t = 0.f;
+  if (!none)
+    for (int j = lane; j < A; j += 32)
+      if (lm[j]) {
+        const float z = lg[j] * inv_t, e = expf(z - m);
+        s += e;
+        t = fmaf(e, z, t);
+      }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    t += __shfl_xor_sync(0xffffffffu, t, o);
+  }
+  const float lse = none ? 0.f : m + logf(s);
+  const float H = none ? logf((float)A) : lse - t / s;
+  const int a = (int)actions[b];
+  const float logp_a = none ? -logf((float)A) : ((a >= 0 && a < A && lm[a]) ? lg[a] * inv_t - lse : -INFINITY);
+  const float logratio = logp_a - old_logprob[b];
+  const float ratio = expf(logratio);
+  const float adv = advantages[b];
+  const float pg1 = -adv * ratio, pg2 = -adv * fminf(fmaxf(ratio, 1.f - clip), 1.f + clip);
+  const bool inside = ratio >= 1.f - clip && ratio <= 1.f + clip;
+  const float inv_b = 1.f / (float)B;
+  const float g = (inside || pg1 > pg2) ? -adv * ratio * inv_b : 0.f;      // dloss / dlogp[a]
+  const float ce = entropy_coef * inv_b;
+  const float v = values[b], ret = returns[b];
+  if (lane == 0) {
+    float* r = rows + b * 5;
+    r[0] = fmaxf(pg1, pg2);
+    r[1] = 0.5f * (v - ret) * (v - ret);
+    r[2] = H;
+    r[3] = (ratio - 1.f) - logratio;
+    r[4] = fabsf(ratio - 1.f) > clip ? 1.f : 0.f;
+    dvalues[b] = value_coef * (v - ret) * inv_b;
+  }
+  float* dl = dlogits + b * A;
+  for (int j = lane; j < A; j += 32) {
+    float d = 0.f;
+    if (!none && lm[j]) {
+      const float logp = lg[j] * inv_t - lse, p = expf(logp);
+      d = (g * ((j == a ? 1.f : 0.f) - p) + ce * p * (logp + H)) * inv_t;
+    }
+    dl[j] = d;
+  }
+}
+// stats = {loss, mean policy, mean value, mean H, approx_kl, clipfrac}: column sums of rows in a fixed order
+__global__ void __launch_bounds__(256) ppo_loss_reduce_kernel(const float* __restrict__ rows, long long B, float value_coef,
+                                                              float entropy_coef, float* __restrict__ stats) {
+  __shared__ float s_part[5][256];
+  float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+  for (long long b = threadIdx.x; b < B; b += 256)
+#pragma unroll
+    for (int c = 0; c < 5; ++c) acc[c] += rows[b * 5 + c];
+#pragma unroll
+  for (int c = 0; c < 5; ++c) s_part[c][threadIdx.x] = acc[c];
+  __syncthreads();
+  for (int w = 128; w > 0; w >>= 1) {
+    if (threadIdx.x < w)
+#pragma unroll
+      for (int c = 0; c < 5; ++c) s_part[c][threadIdx.x] += s_part[c][threadIdx.x + w];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const float inv_b = 1.f / (float)B;
+    const float pol = s_part[0][0] * inv_b, val = s_part[1][0] * inv_b, ent = s_part[2][0] * inv_b;
+    stats[0] = pol + value_coef * val - entropy_coef * ent;
+    stats[1] = pol;
+    stats[2] = val;
+    stats[3] = ent;
+    stats[4] = s_part[3][0] * inv_b;
+    stats[5] = s_part[4][0] * inv_b;
+  }
+}
+
 // Every operand a stack of 3 x 3 layers needs from its parameters, in ONE launch: grid (row blocks, layer, what) with
 // what = 0 forward filter, 1 the same for CTA pairs, 2 flipped/transposed filter of the data gradient, 3 the same for
 // CTA pairs, 4 bias padded to the kernels' channel granule.

@@ -766,4 +766,28 @@ int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, co
   return C6_OK;
 }
 
+int c6_ppo_loss(int32_t device, int64_t B, int32_t A, const float* logits, const uint8_t* legal, const int64_t* actions,
+                const float* old_logprob, const float* advantages, const float* returns, const float* values,
+                float temperature, float clip_coef, float value_coef, float entropy_coef, float* stats, float* dlogits,
+                float* dvalues, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (B < 1 || A < 1) return tfail(C6_ERR_ARG, "board and action counts must be positive");
+  if (!logits || !legal || !actions || !old_logprob || !advantages || !returns || !values || !stats || !dlogits || !dvalues || !workspace)
+    return tfail(C6_ERR_ARG, "null pointer");
+  if (workspace_bytes < (int64_t)(B * 5 * sizeof(float))) return tfail(C6_ERR_ARG, "workspace smaller than 20 bytes per board");
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev)
+    return tfail(C6_ERR_CUDA, "no such CUDA device (this operator has no CPU path)");
+  C6T_CUDA(cudaSetDevice(device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  float* rows = reinterpret_cast<float*>(workspace);
+  const float inv_t = 1.f / std::max(temperature, 1e-4f);      // connect6/train.py:1049-1051
+  ppo_loss_kernel<<<(unsigned)((B + kPpoWarps - 1) / kPpoWarps), 32 * kPpoWarps, 0, st>>>(
+      logits, legal, reinterpret_cast<const long long*>(actions), old_logprob, advantages, returns, values, B, A, inv_t, clip_coef,
+      value_coef, entropy_coef, rows, dlogits, dvalues);
+  C6T_LAUNCHED("ppo_loss_kernel");
+  ppo_loss_reduce_kernel<<<1, 256, 0, st>>>(rows, B, value_coef, entropy_coef, stats);
+  C6T_LAUNCHED("ppo_loss_reduce_kernel");
+  return C6_OK;
+}
+
 }  // extern "C"

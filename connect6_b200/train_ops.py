@@ -326,3 +326,57 @@ class PolicyValueStack(torch.autograd.Function):
         n = len(pdts)
         grads += [dpw.to(pdts[n - 4]), dpb.to(pdts[n - 3]), dvw.to(pdts[n - 2]), dvb.to(pdts[n - 1])]
         return tuple(grads)
+
+
+# ---- PPO minibatch loss ------------------------------------------------------------------------------
+class _PpoLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, values, legal, actions, old_logprob, advantages, returns, temperature, clip_coef, value_coef,
+                entropy_coef):
+        if not logits.is_cuda:
+            raise RuntimeError(f"ppo_loss: expected CUDA tensors, got {logits.device} (no CPU path in this package)")
+        if logits.ndim != 2 or tuple(legal.shape) != tuple(logits.shape):
+            raise ValueError("ppo_loss: logits and legal must be [B, A]")
+        B, A = logits.shape
+        for name, v in (("values", values), ("actions", actions), ("old_logprob", old_logprob), ("advantages", advantages), ("returns", returns)):
+            if tuple(v.shape) != (B,):
+                raise ValueError(f"ppo_loss: {name} must be [B]")
+        dev = logits.device
+        f32 = lambda v: v.detach().to(device=dev, dtype=torch.float32).contiguous()
+        lg, vv, old, adv, ret = f32(logits), f32(values), f32(old_logprob), f32(advantages), f32(returns)
+        lm = legal.detach().to(device=dev, dtype=torch.uint8).contiguous()
+        act = actions.detach().to(device=dev, dtype=torch.int64).contiguous()
+        stats = torch.empty(6, device=dev, dtype=torch.float32)
+        dlogits = torch.empty_like(lg)
+        dvalues = torch.empty_like(vv)
+        if B == 0:
+            raise ValueError("ppo_loss: empty minibatch")
+        ws = torch.empty(B * 5, device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev):
+            rc = L.load().c6_ppo_loss(dev.index, B, A, lg.data_ptr(), lm.data_ptr(), act.data_ptr(), old.data_ptr(), adv.data_ptr(),
+                                      ret.data_ptr(), vv.data_ptr(), float(temperature), float(clip_coef), float(value_coef),
+                                      float(entropy_coef), stats.data_ptr(), dlogits.data_ptr(), dvalues.data_ptr(), ws.data_ptr(),
+                                      ws.numel() * 4, torch.cuda.current_stream(dev).cuda_stream)
+        if rc != L.C6_OK:
+            raise _train_fail(rc, "c6_ppo_loss")
+        ctx.save_for_backward(dlogits, dvalues)
+        ctx.dtypes = (logits.dtype, values.dtype)
+        ctx.mark_non_differentiable(stats)
+        return stats[0].clone(), stats
+
+    @staticmethod
+    def backward(ctx, grad_loss, _grad_stats):
+        dlogits, dvalues = ctx.saved_tensors
+        return ((grad_loss * dlogits).to(ctx.dtypes[0]), (grad_loss * dvalues).to(ctx.dtypes[1])) + (None,) * 9
+
+
+def ppo_loss(logits: torch.Tensor, values: torch.Tensor, legal: torch.Tensor, actions: torch.Tensor, old_logprob: torch.Tensor,
+             advantages: torch.Tensor, returns: torch.Tensor, temperature: float = 1.0, clip_coef: float = 0.2,
+             value_coef: float = 0.5, entropy_coef: float = 0.01):
+    """(loss, stats) of one PPO minibatch from the network's outputs, as connect6/train.py:1047-1094 computes them:
+    loss = clipped-ratio policy loss + value_coef * 0.5 (v - ret)^2 - entropy_coef * entropy over the masked,
+    temperature-scaled action distribution; stats = [loss, policy loss, value loss, entropy, approx_kl, clipfrac]
+    (a device tensor: no synchronisation).  `loss` is differentiable with respect to logits and values: one kernel
+    computes the loss and both gradients, `loss.backward()` only scales them."""
+    return _PpoLoss.apply(logits, values, legal, actions, old_logprob, advantages, returns, temperature, clip_coef,
+                          value_coef, entropy_coef)

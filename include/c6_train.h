@@ -100,6 +100,23 @@ int c6_backbone_heads_backward(int32_t device, int32_t board_size, int32_t nlaye
                                const float* dvalue, const float* value, float* dwp, float* dbp, float* dwv, float* dbv,
                                void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Replaces: the loss of one PPO minibatch and autograd's backward from it to the network outputs
+ * (connect6/train.py:1047-1086, 1115-1119): masked and temperature-scaled logits -> Categorical log-probability of
+ * the taken action and entropy, clipped-ratio policy loss, squared-error value loss,
+ *   loss = mean(policy) + value_coef * mean(value) - entropy_coef * mean(entropy),
+ * plus the two statistics of connect6/train.py:1088-1094.
+ *   logits fp32 [B, A] unmasked, legal uint8 [B, A] (non-zero = legal), actions int64 [B], old_logprob, advantages,
+ *   returns, values fp32 [B]; temperature is floored at 1e-4 like the reference.
+ * Outputs: stats fp32 [6] = {loss, policy loss, value loss, entropy, approx_kl, clipfrac}; dlogits fp32 [B, A] and
+ * dvalues fp32 [B] = d loss / d logits, d loss / d values (zero at illegal actions).  Sums run in a fixed order.
+ * A board without any legal action (a finished game: never part of a real minibatch) is given the uniform
+ * distribution and no gradient.
+ * workspace: 20 bytes per board.  All pointers DEVICE pointers. */
+int c6_ppo_loss(int32_t device, int64_t B, int32_t A, const float* logits, const uint8_t* legal, const int64_t* actions,
+                const float* old_logprob, const float* advantages, const float* returns, const float* values,
+                float temperature, float clip_coef, float value_coef, float entropy_coef, float* stats, float* dlogits,
+                float* dvalues, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Last error text of the calling thread's most recent failing call of this header. Never null. */
 const char* c6_train_last_error(void);
 

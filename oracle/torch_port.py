@@ -137,3 +137,32 @@ def stack_backward(x: torch.Tensor, weights, biases, grad_out: torch.Tensor):
         y = F.silu(F.conv2d(y, w, b, padding=w.shape[-1] // 2))
     y.backward(grad_out.to(y.dtype))
     return y.detach(), x.grad, [w.grad for w in weights], [b.grad for b in biases]
+
+
+def ppo_loss(logits: torch.Tensor, legal: torch.Tensor, actions: torch.Tensor, old_logprob: torch.Tensor,
+             advantages: torch.Tensor, returns: torch.Tensor, values: torch.Tensor, temperature: float, clip_coef: float,
+             value_coef: float, entropy_coef: float) -> dict:
+    """The loss of one PPO minibatch as connect6/train.py:1047-1094 computes it from the network outputs, and what
+    loss.backward() (connect6/train.py:1115-1119) hands back to them: dict with loss, policy_loss, value_loss, entropy,
+    approx_kl, clipfrac (scalars) and dlogits, dvalues.  dtype of `logits` (use float64 for an oracle)."""
+    from torch.distributions import Categorical
+    logits = logits.detach().clone().requires_grad_(True)
+    values = values.detach().clone().requires_grad_(True)
+    z = logits.masked_fill(~legal, torch.finfo(logits.dtype).min) / max(temperature, 1e-4)
+    dist = Categorical(logits=z)
+    new_logprob = dist.log_prob(actions)
+    entropy = dist.entropy().mean()
+    logratio = new_logprob - old_logprob
+    ratio = logratio.exp()
+    pg1 = -advantages * ratio
+    pg2 = -advantages * torch.clamp(ratio, 1.0 - clip_coef, 1.0 + clip_coef)
+    policy_loss = torch.maximum(pg1, pg2).mean()
+    value_loss = 0.5 * (values - returns).pow(2).mean()
+    loss = policy_loss + value_coef * value_loss - entropy_coef * entropy
+    loss.backward()
+    with torch.no_grad():
+        approx_kl = ((ratio - 1.0) - logratio).mean()
+        clipfrac = ((ratio - 1.0).abs() > clip_coef).to(logits.dtype).mean()
+    return {"loss": loss.detach(), "policy_loss": policy_loss.detach(), "value_loss": value_loss.detach(),
+            "entropy": entropy.detach(), "approx_kl": approx_kl, "clipfrac": clipfrac, "dlogits": logits.grad,
+            "dvalues": values.grad}

@@ -117,10 +117,76 @@ def network_backward_fixture() -> None:
           [round(float(p.grad.abs().max()), 5) for p in net.parameters()][:6])
 
 
+def reference_ppo_loss_code():
+    """Code objects compiled from the reference's own statements inside train() (connect6/train.py): the body of the
+    autocast block of the PPO minibatch after the model call (masked logits ... loss) and the two statistics of the
+    no_grad block behind it.  Nothing of the reference's text is stored: the statements are found by their shape."""
+    import ast
+    tree = ast.parse((REF / "connect6" / "train.py").read_text())
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "train")
+    loss_with = stats_with = None
+    for node in ast.walk(fn):
+        if isinstance(node, ast.With) and node.body and isinstance(node.body[0], ast.Assign):
+            first = ast.unparse(node.body[0])
+            if first.startswith("new_logits, new_values = model("):
+                loss_with = node
+            elif first.startswith("approx_kl_tensor ="):
+                stats_with = node
+    assert loss_with is not None and stats_with is not None
+    loss_nodes = loss_with.body[1:]
+    stats_nodes = [n for n in stats_with.body if isinstance(n, ast.Assign) and ast.unparse(n.targets[0]) in ("approx_kl_tensor", "clipfrac_tensor")]
+    assert ast.unparse(loss_nodes[-1].targets[0]) == "loss" and len(stats_nodes) == 2
+    print(f"ppo loss statements: lines {loss_nodes[0].lineno}-{loss_nodes[-1].end_lineno} and {stats_nodes[0].lineno}-"
+          f"{stats_nodes[-1].end_lineno} of connect6/train.py")
+
+    def code(nodes, tag):
+        mod = ast.Module(body=list(nodes), type_ignores=[])
+        return compile(ast.fix_missing_locations(mod), f"<reference train.py: {tag}>", "exec")
+
+    return code(loss_nodes, "ppo loss"), code(stats_nodes, "ppo statistics")
+
+
+def ppo_loss_fixture() -> None:
+    """The reference's own PPO-loss statements run on random network outputs (two cases: temperature 1 and 0.7), with
+    loss.backward() to the logits and values."""
+    import types
+    import connect6.train as RT
+    loss_code, stats_code = reference_ppo_loss_code()
+    out = {}
+    for case, (B, A, temperature, clip_coef, value_coef, entropy_coef, seed) in enumerate(
+            [(48, 361, 1.0, 0.2, 0.5, 0.01, 5), (31, 81, 0.7, 0.1, 1.0, 0.02, 6)]):
+        g = torch.Generator().manual_seed(seed)
+        logits = (torch.randn(B, A, generator=g) * 1.5).requires_grad_(True)
+        values = torch.tanh(torch.randn(B, generator=g)).requires_grad_(True)
+        legal = torch.rand(B, A, generator=g) < 0.7
+        actions = torch.stack([torch.nonzero(legal[b]).flatten()[int(torch.randint(int(legal[b].sum()), (1,), generator=g))] for b in range(B)])
+        with torch.no_grad():
+            lp = torch.log_softmax(logits.masked_fill(~legal, torch.finfo(torch.float32).min) / temperature, -1)
+            old = lp.gather(1, actions[:, None]).squeeze(1) + 0.3 * torch.randn(B, generator=g)   # ratios on both sides of the clip range
+        adv, ret = torch.randn(B, generator=g), torch.tanh(torch.randn(B, generator=g))
+        ns = {"torch": torch, "Categorical": RT.Categorical, "mask_logits": RT.mask_logits, "new_logits": logits, "new_values": values,
+              "mb_legal": legal, "mb_actions": actions, "temperature": temperature, "buffer": types.SimpleNamespace(logprobs=old),
+              "idx": torch.arange(B), "local_idx": torch.arange(B), "advantages": adv, "returns": ret, "clip_coef": clip_coef,
+              "value_coef": value_coef, "entropy_coef": entropy_coef}
+        exec(loss_code, ns)
+        ns["loss"].backward()
+        with torch.no_grad():
+            exec(stats_code, ns)
+        p = f"c{case}_"
+        out.update({p + "logits": logits.detach().numpy(), p + "values": values.detach().numpy(), p + "legal": legal.numpy(),
+                    p + "actions": actions.numpy(), p + "old_logprob": old.numpy(), p + "advantages": adv.numpy(), p + "returns": ret.numpy(),
+                    p + "coefs": np.array([temperature, clip_coef, value_coef, entropy_coef], dtype=np.float64),
+                    p + "stats": np.array([float(ns[k]) for k in ("loss", "policy_loss", "value_loss", "entropy", "approx_kl_tensor", "clipfrac_tensor")]),
+                    p + "dlogits": logits.grad.numpy(), p + "dvalues": values.grad.numpy()})
+        print(f"ppo_loss case {case}: loss {float(ns['loss']):.6f}, clipfrac {float(ns['clipfrac_tensor']):.3f}")
+    np.savez_compressed(HERE / "ppo_loss.npz", ncases=2, torch_version=torch.__version__, **out)
+
+
 def main() -> None:
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     layer_backward_fixture()
     network_backward_fixture()
+    ppo_loss_fixture()
 
     # 1. small net with an even-wider-than-board stem: weights stored, random real-valued input
     torch.manual_seed(7)

@@ -297,3 +297,53 @@ def test_whole_network_gradients_with_engine_backward(cuda_device):
         err = (got - ref).abs().max().item()
         rms = (got - ref).pow(2).mean().sqrt().item()
         assert err < 0.1 * scale and rms < 0.02 * scale, f"{name}: max {err}, rms {rms} vs scale {scale}"
+
+
+def test_ppo_loss_golden_and_oracle(cuda_device):
+    """c6_ppo_loss (one kernel: loss components, statistics, gradients at the network outputs) against the values the
+    reference's own statements gave (tests/golden/ppo_loss.npz) and, on a larger random minibatch, the float64 oracle."""
+    from connect6_b200.train_ops import ppo_loss
+    dev = cuda_device
+    g = load_golden("ppo_loss.npz")
+    for case in range(int(g["ncases"])):
+        p = f"c{case}_"
+        t = lambda k: torch.from_numpy(g[p + k]).to(dev)
+        coefs = [float(v) for v in g[p + "coefs"]]
+        logits, values = t("logits").requires_grad_(True), t("values").requires_grad_(True)
+        loss, stats = ppo_loss(logits, values, t("legal"), t("actions"), t("old_logprob"), t("advantages"), t("returns"), *coefs)
+        loss.backward()
+        assert np.abs(stats.cpu().numpy() - g[p + "stats"]).max() < 2e-5
+        assert abs(float(loss) - g[p + "stats"][0]) < 2e-5
+        assert np.abs(logits.grad.cpu().numpy() - g[p + "dlogits"]).max() < 1e-6 + 1e-4 * np.abs(g[p + "dlogits"]).max()
+        assert np.abs(values.grad.cpu().numpy() - g[p + "dvalues"]).max() < 1e-7
+    # larger case against the oracle, with one board whose ratio is far outside the range
+    gen = torch.Generator().manual_seed(9)
+    B, A = 1000, 361
+    logits = torch.randn(B, A, generator=gen) * 2.0
+    legal = torch.rand(B, A, generator=gen) < 0.6
+    actions = torch.stack([torch.nonzero(legal[b]).flatten()[0] if legal[b].any() else torch.tensor(0) for b in range(B)])
+    lp = torch.log_softmax(logits.masked_fill(~legal, torch.finfo(torch.float32).min), -1).gather(1, actions[:, None]).squeeze(1)
+    old = lp + 0.3 * torch.randn(B, generator=gen)
+    old[11] -= 3.0
+    adv, ret, values = torch.randn(B, generator=gen), torch.tanh(torch.randn(B, generator=gen)), torch.tanh(torch.randn(B, generator=gen))
+    r = TP.ppo_loss(logits.double(), legal, actions, old.double(), adv.double(), ret.double(), values.double(), 1.0, 0.2, 0.5, 0.01)
+    lg, vv = logits.to(dev).requires_grad_(True), values.to(dev).requires_grad_(True)
+    loss, stats = ppo_loss(lg, vv, legal.to(dev), actions.to(dev), old.to(dev), adv.to(dev), ret.to(dev), 1.0, 0.2, 0.5, 0.01)
+    (2.0 * loss).backward()                                 # the gradients scale with what flows into the loss
+    want = np.array([float(r[k]) for k in ("loss", "policy_loss", "value_loss", "entropy", "approx_kl", "clipfrac")])
+    assert np.abs(stats.cpu().numpy() - want).max() < 5e-5
+    assert (lg.grad.cpu().double() - 2.0 * r["dlogits"]).abs().max().item() < 1e-7 + 1e-4 * r["dlogits"].abs().max().item()
+    assert (vv.grad.cpu().double() - 2.0 * r["dvalues"]).abs().max().item() < 1e-8
+    # A board without any legal action (terminal: never part of a real minibatch) gets the uniform distribution and no
+    # gradient; the reference's own arithmetic degenerates there (its fill value absorbs the normaliser), so only
+    # finiteness is checked.
+    legal2 = legal.clone()
+    legal2[7] = False
+    lg2 = logits.to(dev).requires_grad_(True)
+    loss2, stats2 = ppo_loss(lg2, vv.detach(), legal2.to(dev), actions.to(dev), old.to(dev), adv.to(dev), ret.to(dev), 1.0, 0.2, 0.5, 0.01)
+    loss2.backward()
+    assert torch.isfinite(stats2).all() and not lg2.grad[7].any() and torch.isfinite(lg2.grad).all()
+    with pytest.raises(RuntimeError):
+        ppo_loss(logits, values, legal, actions, old, adv, ret)
+    with pytest.raises(ValueError):
+        ppo_loss(lg, vv[:5], legal.to(dev), actions.to(dev), old.to(dev), adv.to(dev), ret.to(dev))

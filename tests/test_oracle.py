@@ -216,3 +216,22 @@ def test_stack_backward_oracle_matches_reference_autograd():
         for got, key in ((dws[i - 1], f"g::convs.{i}.weight"), (dbs[i - 1], f"g::convs.{i}.bias")):
             want = g[key]
             assert np.abs(got.numpy() - want).max() < 5e-6 * np.abs(want).max() + 1e-12, key
+
+
+def test_ppo_loss_oracle_matches_reference_statements():
+    """oracle/torch_port.py:ppo_loss against the reference's own loss statements (compiled out of connect6/train.py by
+    tests/golden/make_golden.py and run on random network outputs): every loss component, both statistics and the
+    gradients that loss.backward() hands to logits and values."""
+    import torch
+    import torch_port as TP
+    g = load_golden("ppo_loss.npz")
+    for case in range(int(g["ncases"])):
+        p = f"c{case}_"
+        t = lambda k: torch.from_numpy(g[p + k])
+        temperature, clip_coef, value_coef, entropy_coef = (float(v) for v in g[p + "coefs"])
+        r = TP.ppo_loss(t("logits"), t("legal"), t("actions"), t("old_logprob"), t("advantages"), t("returns"), t("values"),
+                        temperature, clip_coef, value_coef, entropy_coef)
+        got = np.array([float(r[k]) for k in ("loss", "policy_loss", "value_loss", "entropy", "approx_kl", "clipfrac")])
+        assert np.abs(got - g[p + "stats"]).max() < 1e-6
+        assert np.abs(r["dlogits"].numpy() - g[p + "dlogits"]).max() < 1e-8
+        assert np.abs(r["dvalues"].numpy() - g[p + "dvalues"]).max() < 1e-8

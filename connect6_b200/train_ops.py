@@ -131,9 +131,12 @@ class _StackLease:
 
     def __del__(self) -> None:
         try:
-            pool = _stack_pool.setdefault(self.key, [])
+            pool = _stack_pool.pop(self.key, [])          # re-inserted last: the dict keeps the keys in order of use
             if len(pool) < 2:
                 pool.append(self.ws)
+            _stack_pool[self.key] = pool
+            while len(_stack_pool) > 4:                   # shapes no longer in use give their memory back
+                _stack_pool.pop(next(iter(_stack_pool)))
         except Exception:   # interpreter shutdown
             pass
 

@@ -50,7 +50,8 @@ namespace c6 {
 struct ConvTcParams {
   const uint4* in;       // input planes  [cin/8][plane_rows] of 16-byte rows
   uint4* out;            // output planes [n/8][plane_rows]; unused when head != 0
-  const uint4* aux;      // kEpiDsilu only: planes of the same shape as `out`
+  const uint4* aux;      // kEpiDsilu, kEpiLinearMul: planes of the same shape as `out`
+  uint4* out2;           // kEpiSiluSave: second output, planes of the same shape as `out`
   const uint4* w;        // packed weights, per group [cin/16][taps][2][n] rows
   const uint4* w_pair;   // pair mode: per group [2 halves][cin/16][taps][2][n/2] rows
   const float* bias;     // [G][n]
@@ -100,7 +101,7 @@ struct ConvTcParams {
   float c_wv[256];       // value head weights
 };
 
-constexpr int kEpiSilu = 0, kEpiLinear = 1, kEpiDsilu = 2;
+constexpr int kEpiSilu = 0, kEpiLinear = 1, kEpiDsilu = 2, kEpiSiluSave = 3, kEpiLinearMul = 4;
 constexpr int kEpiTeams = 4;                   // epilogue teams of four warps (as many as the accumulator ring allows are used)
 constexpr int kEpiWarp0 = 5;                   // first epilogue warp
 constexpr int kProducer2Warp = kEpiWarp0 + 4 * kEpiTeams;
@@ -131,6 +132,10 @@ __host__ __device__ inline int conv_stage_rows(int halo_rows) { return 128 + 2 *
 //   kEpiDsilu   y = aux * silu'(z)               the layer's forward recomputed and turned straight into the
 //                                                gradient at the convolution output: aux holds dL/d(layer output)
 //                                                in the output's own plane layout
+//   kEpiSiluSave  y = silu(z), out2 = silu'(z)   the forward layer of a training step: the derivative is kept (same
+//                                                layout as y) so that the backward needs no recomputation
+//   kEpiLinearMul y = z * aux                    the input gradient of a layer times the saved silu' of the layer below:
+//                                                the gradient at that layer's convolution output in one pass
 template <int KS, bool PAIR, bool F16, bool TIMED, int EPI = 0>
 __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -551,10 +556,31 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
           const int u = u0 + b;
           if (u < nunits) {
             float y[16];
-            if (EPI != kEpiSilu) {
+            if (EPI == kEpiSiluSave) {
+              // y = silu(z) as in the forward, and silu'(z) = s + z s (1 - s), s = sigmoid(z) = 0.5 + 0.5 tanh(z / 2), from
+              // the same tanh; the derivative is stored at once (8 channels at a time: registers are scarce)
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {
+                float d[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float h = fmaf(__uint_as_float(v[b][8 * k + j]), 0.5f, s_bias[u * 16 + 8 * k + j]);
+                  const float t = tanh_approx(h);
+                  y[8 * k + j] = fmaf(h, t, h);
+                  const float sg = fmaf(0.5f, t, 0.5f);
+                  d[j] = fmaf((h + h) * sg, 1.0f - sg, sg);
+                }
+                uint4 o2;
+                o2.x = valid ? pack_h2<F16>(d[0], d[1]) : 0u;
+                o2.y = valid ? pack_h2<F16>(d[2], d[3]) : 0u;
+                o2.z = valid ? pack_h2<F16>(d[4], d[5]) : 0u;
+                o2.w = valid ? pack_h2<F16>(d[6], d[7]) : 0u;
+                if (store) (p.out2 + (out_row - p.out))[(size_t)(u * 2 + k) * p.plane_rows] = o2;
+              }
+            } else if (EPI != kEpiSilu) {
               // h = z / 2 as in the forward; the backward operators always read the bias from shared memory
               uint4 g[2];
-              if (EPI == kEpiDsilu) {
+              if (EPI == kEpiDsilu || EPI == kEpiLinearMul) {
                 const uint4* aux_row = p.aux + (out_row - p.out);
                 g[0] = valid ? aux_row[(size_t)(u * 2) * p.plane_rows] : make_uint4(0, 0, 0, 0);
                 g[1] = valid ? aux_row[(size_t)(u * 2 + 1) * p.plane_rows] : make_uint4(0, 0, 0, 0);
@@ -564,6 +590,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const ConvTcPa
                 const float h = fmaf(__uint_as_float(v[b][j]), 0.5f, s_bias[u * 16 + j]);
                 if (EPI == kEpiLinear) {
                   y[j] = h + h;
+                } else if (EPI == kEpiLinearMul) {
+                  const uint32_t w = reinterpret_cast<const uint32_t*>(g)[j >> 1];
+                  y[j] = (h + h) * __uint_as_float((j & 1) ? (w & 0xffff0000u) : (w << 16));
                 } else {
                   // silu'(z) = s + z s (1 - s) with s = sigmoid(z) = 0.5 + 0.5 tanh(z / 2)
                   const float sg = fmaf(0.5f, tanh_approx(h), 0.5f);

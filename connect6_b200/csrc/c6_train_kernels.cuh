@@ -154,11 +154,13 @@ __global__ void __launch_bounds__(kHeadThreads) heads_forward_kernel(const uint4
 
 // Backward of the heads.  Given dL/dlogits [B][cells], dL/dvalue [B] and the forward's value [B]:
 //   du_b = dvalue_b (1 - value_b^2)                (gradient at the pre-tanh mean)
-//   dfeat[b][ch][cell] = dlogits[b][cell] wp[ch] + du_b wv[ch] / cells          -> 16-bit gradient planes (cells only)
+//   dfeat[b][ch][cell] = dlogits[b][cell] wp[ch] + du_b wv[ch] / cells;  grad = dfeat * der (the last layer's saved
+//   silu') = the gradient at the last convolution's output                        -> 16-bit gradient planes (cells only)
 //   dwp[ch] = sum_{b,cell} dlogits f,   dwv[ch] = sum_b du_b / cells sum_cell f,   dbp = sum dlogits,   dbv = sum_b du_b
 // Block i walks boards i, i + gridDim.x, ... once per 8-channel plane and leaves its partial sums in
 // partial[i][nq*16 + 2] (per plane: 8 dwp, 8 dwv; then dbp, dbv); heads_backward_finish_kernel adds the blocks in order.
-__global__ void __launch_bounds__(kHeadThreads) heads_backward_kernel(const uint4* __restrict__ planes, uint4* __restrict__ grad,
+__global__ void __launch_bounds__(kHeadThreads) heads_backward_kernel(const uint4* __restrict__ planes, const uint4* __restrict__ der,
+                                                                      uint4* __restrict__ grad,
                                                                       long long plane_rows, int front, int slots, int wp_pitch, int n,
                                                                       int C, int nq, long long B, const float* __restrict__ wp,
                                                                       const float* __restrict__ wv, const float* __restrict__ dlogits,
@@ -187,15 +189,16 @@ __global__ void __launch_bounds__(kHeadThreads) heads_backward_kernel(const uint
         const size_t row = (size_t)q * plane_rows + front + b * slots + r * wp_pitch + c;
         const float dl = dlogits[b * cells + cell];
         acc[16] += dl;
-        const uint4 fv = planes[row];
-        const uint32_t w[4] = {fv.x, fv.y, fv.z, fv.w};
+        const uint4 fv = planes[row], dv = der[row];
+        const uint32_t w[4] = {fv.x, fv.y, fv.z, fv.w}, wd[4] = {dv.x, dv.y, dv.z, dv.w};
         float g[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float f = __uint_as_float((e & 1) ? (w[e >> 1] & 0xffff0000u) : (w[e >> 1] << 16));
+          const float d = __uint_as_float((e & 1) ? (wd[e >> 1] & 0xffff0000u) : (wd[e >> 1] << 16));
           acc[e] = fmaf(dl, f, acc[e]);
           acc[8 + e] = fmaf(dus, f, acc[8 + e]);
-          g[e] = fmaf(dl, wpq[e], dus * wvq[e]);
+          g[e] = fmaf(dl, wpq[e], dus * wvq[e]) * d;    // times the last layer's saved silu': dL/d(its convolution output)
         }
         uint4 o;
         o.x = pack_bf16x2(g[0], g[1]);
@@ -340,6 +343,20 @@ __global__ void __launch_bounds__(256) ppo_loss_reduce_kernel(const float* __res
     stats[3] = ent;
     stats[4] = s_part[3][0] * inv_b;
     stats[5] = s_part[4][0] * inv_b;
+  }
+}
+
+// out = a * b element by element over `rows` 16-byte rows of 8 bf16 (gradient planes times saved silu' planes).
+__global__ void mul_planes_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out, long long rows) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 x = a[i], y = b[i];
+    const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      o[k] = pack_bf16x2(__uint_as_float(xs[k] << 16) * __uint_as_float(ys[k] << 16),
+                         __uint_as_float(xs[k] & 0xffff0000u) * __uint_as_float(ys[k] & 0xffff0000u));
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 

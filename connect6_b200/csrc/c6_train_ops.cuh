@@ -123,11 +123,13 @@ BackwardLayout make_layout(int n, int k, int cin, int cout, long long B, int sms
 using ConvKernel = void (*)(ConvTcParams);
 
 int launch_conv(const BackwardLayout& L, const LayerPlan& lp, int epi, const uint4* in, uint4* out, const uint4* aux,
-                const uint4* w, const uint4* w_pair, const float* bias, int* status, int sms, cudaStream_t st) {
+                const uint4* w, const uint4* w_pair, const float* bias, int* status, int sms, cudaStream_t st,
+                uint4* out2 = nullptr) {
   ConvTcParams p{};
   p.in = in;
   p.out = out;
   p.aux = aux;
+  p.out2 = out2;
   p.w = w;
   p.w_pair = w_pair;
   p.bias = bias;
@@ -159,12 +161,14 @@ int launch_conv(const BackwardLayout& L, const LayerPlan& lp, int epi, const uin
   p.acc_stride = lp.acc_stride;
   p.nacc = lp.nacc;
   p.tmem_cols = lp.tmem_cols;
-  ConvKernel kernel = lp.pair ? (epi == kEpiDsilu   ? conv_tc_kernel<3, true, false, false, kEpiDsilu>
-                                 : epi == kEpiLinear ? conv_tc_kernel<3, true, false, false, kEpiLinear>
-                                                     : conv_tc_kernel<3, true, false, false, kEpiSilu>)
-                              : (epi == kEpiDsilu   ? conv_tc_kernel<3, false, false, false, kEpiDsilu>
-                                 : epi == kEpiLinear ? conv_tc_kernel<3, false, false, false, kEpiLinear>
-                                                     : conv_tc_kernel<3, false, false, false, kEpiSilu>);
+  static const ConvKernel table[2][5] = {
+      {conv_tc_kernel<3, false, false, false, kEpiSilu>, conv_tc_kernel<3, false, false, false, kEpiLinear>,
+       conv_tc_kernel<3, false, false, false, kEpiDsilu>, conv_tc_kernel<3, false, false, false, kEpiSiluSave>,
+       conv_tc_kernel<3, false, false, false, kEpiLinearMul>},
+      {conv_tc_kernel<3, true, false, false, kEpiSilu>, conv_tc_kernel<3, true, false, false, kEpiLinear>,
+       conv_tc_kernel<3, true, false, false, kEpiDsilu>, conv_tc_kernel<3, true, false, false, kEpiSiluSave>,
+       conv_tc_kernel<3, true, false, false, kEpiLinearMul>}};
+  ConvKernel kernel = table[lp.pair ? 1 : 0][epi];
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
     return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   // programmatic dependent launch: the kernel's prologue (barriers, TMEM, weight copies) overlaps the tail of the launch
@@ -267,17 +271,16 @@ StemLayout make_stem_layout(int n, int k0, int cout, long long B) {
   return S;
 }
 
-// One launch of the direct stem: epi = kEpiSilu (forward, out = the first activation planes) or kEpiDsilu (forward
-// recomputed, out = aux * silu'(.) at the cells).  `out` and `aux` are in the layers' geometry G.
-int launch_stem_conv(const StemLayout& S, const BackwardLayout& G, int epi, const uint4* xe, uint4* out, const uint4* aux,
-                     const uint4* w, const uint4* w_pair, const float* bias, int* status, int n, long long B, int sms,
-                     cudaStream_t st) {
+// The direct stem's forward of a training step: out = the first activation planes, out2 = silu' of the same positions,
+// both in the layers' geometry G (cells only).
+int launch_stem_conv(const StemLayout& S, const BackwardLayout& G, const uint4* xe, uint4* out, uint4* out2, const uint4* w,
+                     const uint4* w_pair, const float* bias, int* status, int n, long long B, int sms, cudaStream_t st) {
   const LayerPlan& lp = S.plan;
   ConvTcParams p{};
   p.in = xe;
   p.in_plane_rows = S.xe_plane_rows;
   p.out = out;
-  p.aux = aux;
+  p.out2 = out2;
   p.plane_rows = G.plane_rows;
   p.w = w;
   p.w_pair = w_pair;
@@ -315,10 +318,7 @@ int launch_stem_conv(const StemLayout& S, const BackwardLayout& G, int epi, cons
   p.acc_stride = lp.acc_stride;
   p.nacc = lp.nacc;
   p.tmem_cols = lp.tmem_cols;
-  ConvKernel kernel = lp.pair ? (epi == kEpiDsilu ? conv_tc_kernel<0, true, false, false, kEpiDsilu>
-                                                  : conv_tc_kernel<0, true, false, false, kEpiSilu>)
-                              : (epi == kEpiDsilu ? conv_tc_kernel<0, false, false, false, kEpiDsilu>
-                                                  : conv_tc_kernel<0, false, false, false, kEpiSilu>);
+  ConvKernel kernel = lp.pair ? conv_tc_kernel<0, true, false, false, kEpiSiluSave> : conv_tc_kernel<0, false, false, false, kEpiSiluSave>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
     return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   launch_chain(kernel, (unsigned)p.ctas_per_group, 1u, kConvThreads, (size_t)lp.smem, st, lp.pair != 0, true, p);
@@ -375,7 +375,7 @@ struct StackLayout {
   StemLayout stem;
   BackwardLayout lay[C6_MAX_LAYERS];      // 3 x 3 layers l >= first: pipeline plans; the board geometry is the same for all
   size_t off_bias[C6_MAX_LAYERS] = {}, off_wf[C6_MAX_LAYERS] = {}, off_wf_pair[C6_MAX_LAYERS] = {}, off_wd[C6_MAX_LAYERS] = {},
-         off_wd_pair[C6_MAX_LAYERS] = {}, off_act[C6_MAX_LAYERS + 1] = {};
+         off_wd_pair[C6_MAX_LAYERS] = {}, off_act[C6_MAX_LAYERS + 1] = {}, off_der[C6_MAX_LAYERS] = {};
   size_t off_zero = 0, off_grad[2] = {}, off_dpre = 0, off_partial = 0, off_colsum = 0, off_xe = 0, off_dsd = 0, off_heads = 0, total = 0;
 };
 
@@ -420,6 +420,10 @@ StackLayout make_stack_layout(int n, int nlayers, const int32_t* channels, int s
   for (int l = S.first; l <= nlayers; ++l) {
     const int cp = l < nlayers ? S.lay[l].cin_p : S.lay[l - 1].cout_p;
     S.off_act[l] = take((size_t)(cp / 8) * plane_rows * 16);
+  }
+  for (int l = 0; l < nlayers; ++l) {      // silu' of every layer's output, kept by the forward for the backward
+    const int cp = l < S.first ? S.stem.cout_p : S.lay[l].cout_p;
+    S.off_der[l] = take((size_t)(cp / 8) * plane_rows * 16);
   }
   S.off_grad[0] = take((size_t)(S.cmax_p / 8) * plane_rows * 16);
   S.off_grad[1] = take((size_t)(S.cmax_p / 8) * plane_rows * 16);
@@ -612,9 +616,10 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
         in, nullptr, reinterpret_cast<uint4*>(ws + S.off_xe), T.xe_plane_rows, T.front, (int)T.group_pos, T.wi, T.slots, board_size,
         (int)B, B, 0, 0, status);
     C6T_LAUNCHED("pack_stem_direct_input_kernel");
-    rc = launch_stem_conv(T, L0, kEpiSilu, reinterpret_cast<const uint4*>(ws + S.off_xe), reinterpret_cast<uint4*>(ws + S.off_act[1]),
-                          nullptr, reinterpret_cast<const uint4*>(ws + S.off_wf[0]), reinterpret_cast<const uint4*>(ws + S.off_wf_pair[0]),
-                          reinterpret_cast<const float*>(ws + S.off_bias[0]), status, board_size, B, sms, st);
+    rc = launch_stem_conv(T, L0, reinterpret_cast<const uint4*>(ws + S.off_xe), reinterpret_cast<uint4*>(ws + S.off_act[1]),
+                          reinterpret_cast<uint4*>(ws + S.off_der[0]), reinterpret_cast<const uint4*>(ws + S.off_wf[0]),
+                          reinterpret_cast<const uint4*>(ws + S.off_wf_pair[0]), reinterpret_cast<const float*>(ws + S.off_bias[0]),
+                          status, board_size, B, sms, st);
     if (rc) return rc;
   } else {
     const long long t = B * L0.slots * (L0.cin_p / 8);
@@ -624,10 +629,10 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
   }
   for (int l = S.first; l < nlayers; ++l) {
     const BackwardLayout& L = S.lay[l];
-    rc = launch_conv(L, L.fwd, kEpiSilu, reinterpret_cast<const uint4*>(ws + S.off_act[l]),
+    rc = launch_conv(L, L.fwd, kEpiSiluSave, reinterpret_cast<const uint4*>(ws + S.off_act[l]),
                      reinterpret_cast<uint4*>(ws + S.off_act[l + 1]), nullptr, reinterpret_cast<const uint4*>(ws + S.off_wf[l]),
                      reinterpret_cast<const uint4*>(ws + S.off_wf_pair[l]), reinterpret_cast<const float*>(ws + S.off_bias[l]),
-                     status, sms, st);
+                     status, sms, st, reinterpret_cast<uint4*>(ws + S.off_der[l]));
     if (rc) return rc;
   }
   if (y) {
@@ -675,7 +680,8 @@ int c6_backbone_heads_backward(int32_t device, int32_t board_size, int32_t nlaye
   const int nblocks = (int)std::min<long long>(B, kHeadBlocks);
   float* partial = reinterpret_cast<float*>(ws + S.off_heads);
   heads_backward_kernel<<<(unsigned)nblocks, kHeadThreads, 0, st>>>(
-      reinterpret_cast<const uint4*>(ws + S.off_act[nlayers]), reinterpret_cast<uint4*>(ws + S.off_grad[0]), L.plane_rows, L.front,
+      reinterpret_cast<const uint4*>(ws + S.off_act[nlayers]), reinterpret_cast<const uint4*>(ws + S.off_der[nlayers - 1]),
+      reinterpret_cast<uint4*>(ws + S.off_grad[0]), L.plane_rows, L.front,
       L.slots, L.wp, L.n, L.cout, nq, B, wp, wv, dlogits, dvalue, value, partial);
   C6T_LAUNCHED("heads_backward_kernel");
   heads_backward_finish_kernel<<<(2 * L.cout + 2 + 127) / 128, 128, 0, st>>>(partial, nblocks, nq, L.cout, dwp, dbp, dwv, dbv);
@@ -700,32 +706,40 @@ int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, co
   uint4* dpre = reinterpret_cast<uint4*>(ws + S.off_dpre);
   float* partial = reinterpret_cast<float*>(ws + S.off_partial);
   float* colsum = reinterpret_cast<float*>(ws + S.off_colsum);
+  // P[cur] holds dPre_l = dL/d(convolution output of layer l) on entry to layer l's step
   int cur = 0;
-  if (dy) {   // null: c6_backbone_heads_backward has left the gradient of the features in the workspace
+  if (dy) {   // null: c6_backbone_heads_backward has left dPre of the last layer in the workspace
     const BackwardLayout& L = S.lay[nlayers - 1];
     const long long t = B * L.slots * (L.cout_p / 8);
-    pack_nchw_planes_kernel<<<(unsigned)((t + 255) / 256), 256, 0, st>>>(
-        dy, reinterpret_cast<uint4*>(ws + S.off_grad[cur]), L.plane_rows, L.front, L.slots, L.wp, L.n, L.cout, L.cout_p, B);
+    pack_nchw_planes_kernel<<<(unsigned)((t + 255) / 256), 256, 0, st>>>(dy, dpre, L.plane_rows, L.front, L.slots, L.wp, L.n, L.cout,
+                                                                         L.cout_p, B);
     C6T_LAUNCHED("pack_nchw_planes_kernel");
+    const long long rows = (long long)(L.cout_p / 8) * L.plane_rows;
+    mul_planes_kernel<<<(unsigned)std::min<long long>((rows + 255) / 256, 4096), 256, 0, st>>>(
+        dpre, reinterpret_cast<const uint4*>(ws + S.off_der[nlayers - 1]), reinterpret_cast<uint4*>(ws + S.off_grad[cur]), rows);
+    C6T_LAUNCHED("mul_planes_kernel");
   }
   for (int l = nlayers - 1; l >= S.first; --l) {
     const BackwardLayout& L = S.lay[l];
     if (!dw[l] || !db[l]) return tfail(C6_ERR_ARG, "null gradient pointer");
     const uint4* act = reinterpret_cast<const uint4*>(ws + S.off_act[l]);
-    // dPre = dY * silu'(conv(act, W) + b)
-    rc = launch_conv(L, L.fwd, kEpiDsilu, act, dpre, reinterpret_cast<const uint4*>(ws + S.off_grad[cur]),
-                     reinterpret_cast<const uint4*>(ws + S.off_wf[l]), reinterpret_cast<const uint4*>(ws + S.off_wf_pair[l]),
-                     reinterpret_cast<const float*>(ws + S.off_bias[l]), status, sms, st);
-    if (rc) return rc;
-    colsum_planes_kernel<<<dim3((unsigned)(L.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre, L.plane_rows, L.front,
+    const uint4* dpre_l = reinterpret_cast<const uint4*>(ws + S.off_grad[cur]);
+    colsum_planes_kernel<<<dim3((unsigned)(L.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre_l, L.plane_rows, L.front,
                                                                                                     L.total_pos, kColsumSlices, colsum);
     C6T_LAUNCHED("colsum_planes_kernel");
     colsum_finish_kernel<<<(L.cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, L.cout, db[l]);
     C6T_LAUNCHED("colsum_finish_kernel");
-    rc = launch_wgrad(L, act, dpre, partial, dw[l], status, st);
+    rc = launch_wgrad(L, act, dpre_l, partial, dw[l], status, st);
     if (rc) return rc;
-    if (l > 0 || dx) {
-      rc = launch_conv(L, L.dgrad, kEpiLinear, dpre, reinterpret_cast<uint4*>(ws + S.off_grad[cur ^ 1]), nullptr,
+    if (l > 0) {
+      // the layer below exists: its dPre = (data gradient of this layer) * (its saved silu'), in one pass
+      rc = launch_conv(L, L.dgrad, kEpiLinearMul, dpre_l, reinterpret_cast<uint4*>(ws + S.off_grad[cur ^ 1]),
+                       reinterpret_cast<const uint4*>(ws + S.off_der[l - 1]), reinterpret_cast<const uint4*>(ws + S.off_wd[l]),
+                       reinterpret_cast<const uint4*>(ws + S.off_wd_pair[l]), zero_f, status, sms, st);
+      if (rc) return rc;
+      cur ^= 1;
+    } else if (dx) {
+      rc = launch_conv(L, L.dgrad, kEpiLinear, dpre_l, reinterpret_cast<uint4*>(ws + S.off_grad[cur ^ 1]), nullptr,
                        reinterpret_cast<const uint4*>(ws + S.off_wd[l]), reinterpret_cast<const uint4*>(ws + S.off_wd_pair[l]),
                        zero_f, status, sms, st);
       if (rc) return rc;
@@ -733,24 +747,20 @@ int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, co
     }
   }
   if (S.first) {
-    // the stem: dPre_0 = dY_0 * silu'(.) with its forward recomputed by the direct stem, db_0 its column sums, dW_0 from the
-    // x-expanded input planes and dPre_0 moved into the input geometry
+    // the stem: db_0 = column sums of dPre_0, dW_0 from the x-expanded input planes and dPre_0 moved into the input geometry
     const StemLayout& T = S.stem;
     const BackwardLayout& G = S.lay[1];
     if (!dw[0] || !db[0]) return tfail(C6_ERR_ARG, "null gradient pointer");
     const uint4* xe = reinterpret_cast<const uint4*>(ws + S.off_xe);
+    const uint4* dpre0 = reinterpret_cast<const uint4*>(ws + S.off_grad[cur]);
     uint4* dsd = reinterpret_cast<uint4*>(ws + S.off_dsd);
-    rc = launch_stem_conv(T, G, kEpiDsilu, xe, dpre, reinterpret_cast<const uint4*>(ws + S.off_grad[cur]),
-                          reinterpret_cast<const uint4*>(ws + S.off_wf[0]), reinterpret_cast<const uint4*>(ws + S.off_wf_pair[0]),
-                          reinterpret_cast<const float*>(ws + S.off_bias[0]), status, board_size, B, sms, st);
-    if (rc) return rc;
-    colsum_planes_kernel<<<dim3((unsigned)(T.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre, G.plane_rows, G.front,
+    colsum_planes_kernel<<<dim3((unsigned)(T.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre0, G.plane_rows, G.front,
                                                                                                     G.total_pos, kColsumSlices, colsum);
     C6T_LAUNCHED("colsum_planes_kernel");
     colsum_finish_kernel<<<(T.cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, T.cout, db[0]);
     C6T_LAUNCHED("colsum_finish_kernel");
     const long long total = B * (T.cout_p / 8) * board_size * board_size;
-    repack_planes_geometry_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(dpre, G.plane_rows, G.front, G.slots, G.wp, dsd,
+    repack_planes_geometry_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(dpre0, G.plane_rows, G.front, G.slots, G.wp, dsd,
                                                                                    T.dsd_plane_rows, T.slots, T.wi, board_size,
                                                                                    T.cout_p / 8, B);
     C6T_LAUNCHED("repack_planes_geometry_kernel");

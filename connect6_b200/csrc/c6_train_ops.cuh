@@ -367,8 +367,9 @@ int launch_stem_wgrad(const StemLayout& S, const uint4* xe, const uint4* dsd, fl
 }
 
 // A stack of layers differentiated as a whole: an optional first-layer stem (stem_kside x stem_kside on 3 input planes,
-// run as the direct stem) followed by 3 x 3 layers.  Every layer's input activation is kept as channel-chunk planes by
-// the forward call (the stem's input as its x-expanded planes), gradients travel between layers in the same layout.
+// run as the direct stem) followed by 3 x 3 layers.  Every layer's input activation and the derivative silu' of its
+// output are kept as channel-chunk planes by the forward call (the stem's input as its x-expanded planes); gradients
+// travel between layers in the same layout, as dL/d(convolution output) of the layer about to be processed.
 struct StackLayout {
   bool ok = false;
   int L = 0, first = 0, cmax_p = 0;       // layers in all; index of the first 3 x 3 layer (1 with a stem, else 0)

@@ -56,9 +56,11 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
  * (channels[0] = 3, connect6/model.py:22-23: k = 23), the others are 3 x 3; x is the network input.
  * The forward call keeps every layer's input as 16-bit channel-chunk planes inside the workspace (the stem's as
  * its x-expanded input planes); the backward call walks the stack from the top with the gradient staying in
- * that layout between layers, so only the stack's ends are NCHW fp32.  Per 3 x 3 layer the arithmetic is
- * c6_conv_layer_backward's; the stem's forward (and its recomputation for silu') is the engine's direct stem,
- * its weight gradient the same position-contracted GEMM with 8 filter columns x 16 filter rows as the M side.
+ * that layout between layers, so only the stack's ends are NCHW fp32.  Arithmetic as in c6_conv_layer_backward
+ * (bf16 operands, fp32 accumulation), except that no forward is recomputed: the forward call also keeps silu' of
+ * every layer's pre-activation (one bf16 rounding), and a layer's data-gradient convolution multiplies by the
+ * saved silu' of the layer below in its epilogue.  The stem's forward is the engine's direct stem, its weight
+ * gradient the same position-contracted GEMM with 8 filter columns x 16 filter rows as the M side.
  * Supported: 1 <= nlayers <= C6_MAX_LAYERS, n <= 32, every 3 x 3 layer's channel counts <= 128; with a stem:
  * nlayers >= 2, k odd and <= 31, channels[1] <= 64.
  * workspace: c6_backbone_workspace_bytes() bytes (0: unsupported shape), 256-byte aligned, ZERO-FILLED before its

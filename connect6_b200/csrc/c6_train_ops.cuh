@@ -259,13 +259,16 @@ StemLayout make_stem_layout(int n, int k0, int cout, long long B) {
   S.wg_slabs = std::max(1, 148 / S.wg_groups);
   S.wg_halo_a = round_up((16 * S.nkyb - 1 - S.kh) * S.wi + (8 * S.nkxb - 1 - S.kh) + 8, 8);
   const int room = kSmemLimit - 128 - kWgradSmemHeader;
-  S.wg_tile_rows = 2 * wgrad_stem_stage_bytes(S.cout_p, S.halo_b, S.wg_halo_a, 256) <= room ? 256 : 128;
+  // K tiles of 128 positions aligned to the board images (the rows behind an image's last cell are padding: the
+  // gradient is zero there), or, for geometries whose images are no longer than their tiles, 256 positions running
+  // linearly over everything
+  S.wg_tile_rows = S.tiles_per_board ? 128 : (2 * wgrad_stem_stage_bytes(S.cout_p, S.halo_b, S.wg_halo_a, 256) <= room ? 256 : 128);
   const int stage = wgrad_stem_stage_bytes(S.cout_p, S.halo_b, S.wg_halo_a, S.wg_tile_rows);
   S.wg_stages = std::min(kWgradMaxStages, room / stage);
   if (S.wg_stages < 2) return S;
   S.wg_smem = 128 + kWgradSmemHeader + S.wg_stages * stage;
-  S.wg_tiles = (int)((B * S.slots + S.wg_tile_rows - 1) / S.wg_tile_rows);
-  S.dsd_plane_rows = (long long)S.wg_tiles * S.wg_tile_rows;
+  S.wg_tiles = S.tiles_per_board ? (int)(B * S.tiles_per_board) : (int)((B * S.slots + S.wg_tile_rows - 1) / S.wg_tile_rows);
+  S.dsd_plane_rows = round_up_ll(B * S.slots + S.wg_tile_rows, 128);
   S.xe_plane_rows = (long long)S.front + std::max(S.group_pos + S.halo_a + 128 + 16, S.dsd_plane_rows + S.wg_halo_a + 16);
   S.ok = true;
   return S;
@@ -355,6 +358,8 @@ int launch_stem_wgrad(const StemLayout& S, const uint4* xe, const uint4* dsd, fl
   p.stem_wi = S.wi;
   p.stem_nkxb = S.nkxb;
   p.stem_nkyb = S.nkyb;
+  p.tiles_per_board = S.tiles_per_board;
+  p.board_rows = S.slots;
   if (cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
     return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   wgrad_tc_kernel<<<(unsigned)(p.ngroups * p.nslabs), kWgradThreads, (size_t)S.wg_smem, st>>>(p);

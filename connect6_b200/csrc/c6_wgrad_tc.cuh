@@ -55,6 +55,10 @@ struct WgradParams {
   // `cout` channels.  A "tap" is (input plane, block of 8 filter columns, block of 16 filter rows): ntaps = 3 *
   // stem_nkxb * stem_nkyb, its accumulator 128 x cout.  partial is [nslabs][ntaps][128][cout].
   int stem_k, stem_wi, stem_nkxb, stem_nkyb;
+  // tiles_per_board > 0: K tiles are aligned to board images of `board_rows` positions, tile t covers the positions
+  // [(t / tiles_per_board) * board_rows + (t % tiles_per_board) * tile_rows, ... + tile_rows): the all-padding tail of an
+  // image is never multiplied.  0: tiles run linearly over all positions.
+  int tiles_per_board, board_rows;
 };
 
 constexpr int kWgradThreads = 192;
@@ -140,8 +144,11 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
         ok = false;
         break;
       }
-      const long long row0 = (long long)p.front + (long long)tile * p.tile_rows;
-      const long long drow0 = (long long)p.dpre_front + (long long)tile * p.tile_rows;
+      const long long pos0 = p.tiles_per_board > 0
+                                 ? (long long)(tile / p.tiles_per_board) * p.board_rows + (long long)(tile % p.tiles_per_board) * p.tile_rows
+                                 : (long long)tile * p.tile_rows;
+      const long long row0 = (long long)p.front + pos0;
+      const long long drow0 = (long long)p.dpre_front + pos0;
       const uint32_t dst = tc::smem_u32(s_stage + (size_t)s * stage_bytes);
       if (lane < na) {
         tc::bulk_g2s(dst + (uint32_t)lane * a_plane, p.dpre + (size_t)lane * p.dpre_plane_rows + drow0, a_plane, bar_full(s));

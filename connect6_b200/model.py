@@ -120,7 +120,10 @@ class PolicyValueNet(nn.Module):
         return logits, value
 
     def forward_autograd(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-        """Differentiable forward on the PyTorch modules (training only; not the engine)."""
+        """Differentiable forward (training only; not the inference engine).  By default on the PyTorch modules; with
+        `engine_backward=True` and CUDA tensors the layers the library supports -- for the default architecture the whole
+        network: stem, 3x3 layers, heads -- run forward and backward on its kernels (train_ops.PolicyValueStack), the
+        parameters staying ordinary nn.Parameters whose .grad the backward fills."""
         feats = x
         use_engine = self.engine_backward and x.is_cuda
         convs = list(self.convs)

@@ -59,6 +59,7 @@ struct BackwardLayout {
   long long B = 0, total_pos = 0, plane_rows = 0;
   LayerPlan fwd, dgrad;           // pipeline plans of the two conv_tc_kernel launches
   int wg_taps_per_cta = 0, wg_groups = 0, wg_slabs = 0, wg_stages = 0, wg_smem = 0, wg_tile_rows = 128, wg_tiles = 0;
+  int wg_bias_tap = -1;           // >= 0: the weight-gradient kernel also produces the bias gradient (see WgradParams)
   // workspace offsets in bytes
   size_t off_bias = 0, off_zero = 0, off_wf = 0, off_wf_pair = 0, off_wd = 0, off_wd_pair = 0, off_x = 0, off_dy = 0,
          off_dpre = 0, off_dx = 0, off_partial = 0, off_colsum = 0, total = 0;
@@ -96,8 +97,18 @@ BackwardLayout make_layout(int n, int k, int cin, int cout, long long B, int sms
   // when fewer gradient planes exist (those accumulator rows are never read).  K tiles of 256 positions when
   // two stages of that size fit, else 128.
   const int room = kSmemLimit - 128 - kWgradSmemHeader - 32768;
-  L.wg_tile_rows = 2 * wgrad_stage_bytes(L.cin_p, L.cout_p, L.halo_rows, 256) <= room ? 256 : 128;
-  const int stage = wgrad_stage_bytes(L.cin_p, L.cout_p, L.halo_rows, L.wg_tile_rows);
+  // the bias gradient rides on the last tap of group 0 when 16 more accumulator columns fit; a tap fewer per CTA is
+  // taken for that if it needs no further tap group
+  {
+    int t2 = L.wg_taps_per_cta;
+    while (t2 > 1 && t2 * L.cin_p + 16 > 512) --t2;
+    if ((k * k + t2 - 1) / t2 == L.wg_groups) L.wg_taps_per_cta = t2;
+  }
+  const int taps0 = std::min(L.wg_taps_per_cta, k * k);
+  const bool with_bias = taps0 * L.cin_p + 16 <= 512;
+  L.wg_bias_tap = with_bias ? taps0 - 1 : -1;
+  L.wg_tile_rows = 2 * wgrad_stage_bytes(L.cin_p, L.cout_p, L.halo_rows, 256, with_bias) <= room ? 256 : 128;
+  const int stage = wgrad_stage_bytes(L.cin_p, L.cout_p, L.halo_rows, L.wg_tile_rows, with_bias);
   L.wg_stages = std::min(kWgradMaxStages, room / stage);
   if (L.wg_stages < 2) return L;
   L.wg_smem = 128 + kWgradSmemHeader + L.wg_stages * stage + 32768;
@@ -114,7 +125,7 @@ BackwardLayout make_layout(int n, int k, int cin, int cout, long long B, int sms
   L.off_dy = take((size_t)(L.cout_p / 8) * L.plane_rows * 16);
   L.off_dpre = take((size_t)(L.cout_p / 8) * L.plane_rows * 16);
   L.off_dx = take((size_t)(L.cin_p / 8) * L.plane_rows * 16);
-  L.off_partial = take((size_t)L.wg_slabs * k * k * 128 * L.cin_p * 4);
+  L.off_partial = take((size_t)L.wg_slabs * k * k * 128 * L.cin_p * 4 + (size_t)L.wg_slabs * 128 * 4);
   L.off_colsum = take((size_t)(L.cout_p / 8) * kColsumSlices * 8 * 4);
   L.ok = true;
   return L;
@@ -181,8 +192,10 @@ int launch_conv(const BackwardLayout& L, const LayerPlan& lp, int epi, const uin
 
 
 // dW = sum over positions of dPre (x) shifted x: wgrad_tc_kernel into per-slab partial sums, then the fixed-order reduction.
+// With db and a layout that fuses it (L.wg_bias_tap >= 0) the same launches also produce the bias gradient; the caller
+// checks L.wg_bias_tap and runs the column-sum kernels otherwise.
 int launch_wgrad(const BackwardLayout& L, const uint4* xp, const uint4* dpre, float* partial, float* dw, int* status,
-                 cudaStream_t st) {
+                 cudaStream_t st, float* db = nullptr) {
   const int taps = L.k * L.k;
   WgradParams p{};
   p.x = xp;
@@ -206,12 +219,17 @@ int launch_wgrad(const BackwardLayout& L, const uint4* xp, const uint4* dpre, fl
   p.halo_after = L.halo_rows;
   p.dpre_plane_rows = L.plane_rows;
   p.dpre_front = L.front;
+  const bool with_bias = db != nullptr && L.wg_bias_tap >= 0;
+  float* bias_partial = partial + (size_t)L.wg_slabs * taps * 128 * L.cin_p;
+  p.bias_tap = L.wg_bias_tap;      // the stage layout carries the ones planes whenever the layout says so
+  p.bias_partial = bias_partial;
   if (cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
     return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   wgrad_tc_kernel<<<(unsigned)(p.ngroups * p.nslabs), kWgradThreads, (size_t)L.wg_smem, st>>>(p);
   C6T_LAUNCHED("wgrad_tc_kernel");
   const long long total = (long long)L.cout * L.cin * taps;
-  wgrad_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, dw, p.nslabs, taps, L.cin_p, L.cin, L.cout);
+  wgrad_reduce_kernel<<<(unsigned)((total + L.cout + 255) / 256), 256, 0, st>>>(partial, dw, p.nslabs, taps, L.cin_p, L.cin, L.cout,
+                                                                               with_bias ? bias_partial : nullptr, db);
   C6T_LAUNCHED("wgrad_reduce_kernel");
   return C6_OK;
 }
@@ -360,6 +378,7 @@ int launch_stem_wgrad(const StemLayout& S, const uint4* xe, const uint4* dsd, fl
   p.stem_nkyb = S.nkyb;
   p.tiles_per_board = S.tiles_per_board;
   p.board_rows = S.slots;
+  p.bias_tap = -1;
   if (cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
     return tfail(C6_ERR_CUDA, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   wgrad_tc_kernel<<<(unsigned)(p.ngroups * p.nslabs), kWgradThreads, (size_t)S.wg_smem, st>>>(p);
@@ -400,7 +419,7 @@ StackLayout make_stack_layout(int n, int nlayers, const int32_t* channels, int s
     S.lay[l] = make_layout(n, 3, channels[l], channels[l + 1], B, 148);
     if (!S.lay[l].ok) return S;
     S.cmax_p = std::max(S.cmax_p, std::max(S.lay[l].cin_p, S.lay[l].cout_p));
-    partial_max = std::max(partial_max, (size_t)S.lay[l].wg_slabs * 9 * 128 * S.lay[l].cin_p * 4);
+    partial_max = std::max(partial_max, (size_t)S.lay[l].wg_slabs * 9 * 128 * S.lay[l].cin_p * 4 + (size_t)S.lay[l].wg_slabs * 128 * 4);
     colsum_max = std::max(colsum_max, (size_t)(S.lay[l].cout_p / 8) * kColsumSlices * 8 * 4);
   }
   colsum_max = std::max(colsum_max, (size_t)(S.lay[S.first].cin_p / 8) * kColsumSlices * 8 * 4);
@@ -542,12 +561,14 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
   // dPre = dy * silu'(conv(x, W) + b)
   int rc = launch_conv(L, L.fwd, kEpiDsilu, xp, dpre, dyp, wf, wf_pair, bias_f, status, sms, st);
   if (rc) return rc;
-  // db
-  colsum_planes_kernel<<<dim3((unsigned)(L.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre, L.plane_rows, L.front,
-                                                                                                  L.total_pos, kColsumSlices, colsum);
-  C6T_LAUNCHED("colsum_planes_kernel");
-  colsum_finish_kernel<<<(cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, cout, db);
-  C6T_LAUNCHED("colsum_finish_kernel");
+  // db: with the weight gradient when its accumulators have room for the bias columns, else a pass of its own
+  if (L.wg_bias_tap < 0) {
+    colsum_planes_kernel<<<dim3((unsigned)(L.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre, L.plane_rows, L.front,
+                                                                                                    L.total_pos, kColsumSlices, colsum);
+    C6T_LAUNCHED("colsum_planes_kernel");
+    colsum_finish_kernel<<<(cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, cout, db);
+    C6T_LAUNCHED("colsum_finish_kernel");
+  }
   // dX
   if (dx) {
     rc = launch_conv(L, L.dgrad, kEpiLinear, dpre, dxp, nullptr, wd, wd_pair, zero_f, status, sms, st);
@@ -557,7 +578,7 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
     C6T_LAUNCHED("unpack_planes_nchw_kernel");
   }
   // dW
-  rc = launch_wgrad(L, xp, dpre, partial, dw, status, st);
+  rc = launch_wgrad(L, xp, dpre, partial, dw, status, st, db);
   if (rc) return rc;
   return C6_OK;
 }
@@ -730,12 +751,14 @@ int c6_backbone_backward(int32_t device, int32_t board_size, int32_t nlayers, co
     if (!dw[l] || !db[l]) return tfail(C6_ERR_ARG, "null gradient pointer");
     const uint4* act = reinterpret_cast<const uint4*>(ws + S.off_act[l]);
     const uint4* dpre_l = reinterpret_cast<const uint4*>(ws + S.off_grad[cur]);
-    colsum_planes_kernel<<<dim3((unsigned)(L.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre_l, L.plane_rows, L.front,
-                                                                                                    L.total_pos, kColsumSlices, colsum);
-    C6T_LAUNCHED("colsum_planes_kernel");
-    colsum_finish_kernel<<<(L.cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, L.cout, db[l]);
-    C6T_LAUNCHED("colsum_finish_kernel");
-    rc = launch_wgrad(L, act, dpre_l, partial, dw[l], status, st);
+    if (L.wg_bias_tap < 0) {     // no room for the bias columns in the weight-gradient kernel's accumulators: a pass of its own
+      colsum_planes_kernel<<<dim3((unsigned)(L.cout_p / 8), kColsumSlices), kColsumThreads, 0, st>>>(dpre_l, L.plane_rows, L.front,
+                                                                                                      L.total_pos, kColsumSlices, colsum);
+      C6T_LAUNCHED("colsum_planes_kernel");
+      colsum_finish_kernel<<<(L.cout + 127) / 128, 128, 0, st>>>(colsum, kColsumSlices, L.cout, db[l]);
+      C6T_LAUNCHED("colsum_finish_kernel");
+    }
+    rc = launch_wgrad(L, act, dpre_l, partial, dw[l], status, st, db[l]);
     if (rc) return rc;
     if (l > 0) {
       // the layer below exists: its dPre = (data gradient of this layer) * (its saved silu'), in one pass

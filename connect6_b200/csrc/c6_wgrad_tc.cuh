@@ -59,6 +59,13 @@ struct WgradParams {
   // [(t / tiles_per_board) * board_rows + (t % tiles_per_board) * tile_rows, ... + tile_rows): the all-padding tail of an
   // image is never multiplied.  0: tiles run linearly over all positions.
   int tiles_per_board, board_rows;
+  // bias_tap >= 0 (k x k mode only): the bias gradient db[co] = sum over positions of dPre[p][co] rides along as 16 more
+  // accumulator columns of tap `bias_tap` of tap group 0 (its last tap, so that the columns lie behind every other
+  // accumulator): two more "input planes" behind the staged ones hold 1.0 in every element, so the tap's MMA with
+  // N = cin + 16 adds up dPre itself.  The CTAs of group 0 write column cin of that accumulator to
+  // bias_partial[slab][128]; the reduction kernel adds the slabs.  -1: no bias gradient here.
+  int bias_tap;
+  float* bias_partial;
 };
 
 constexpr int kWgradThreads = 192;
@@ -71,8 +78,9 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_bf16_mn(int m, int n) {
   return tc::make_idesc_bf16(m, n) | (1u << 15) | (1u << 16);
 }
 
-__host__ __device__ inline int wgrad_stage_bytes(int cin, int cout, int halo_rows, int tile_rows) {
-  return (cout / 8) * tile_rows * 16 + (cin / 8) * (tile_rows + 2 * halo_rows) * 16;
+// with_bias: two more planes (the ones that sum dPre into the bias gradient) behind the input planes
+__host__ __device__ inline int wgrad_stage_bytes(int cin, int cout, int halo_rows, int tile_rows, bool with_bias = false) {
+  return (cout / 8) * tile_rows * 16 + (cin / 8 + (with_bias ? 2 : 0)) * (tile_rows + 2 * halo_rows) * 16;
 }
 __host__ __device__ inline int wgrad_stem_stage_bytes(int cout, int halo_before, int halo_after, int tile_rows) {
   return (cout / 8) * tile_rows * 16 + 3 * (tile_rows + halo_before + halo_after) * 16;
@@ -97,9 +105,11 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
   const int xplanes = stem ? 3 : p.cin / 8;
   const uint32_t a_plane = (uint32_t)p.tile_rows * 16u;
   const uint32_t b_plane = (uint32_t)xrows * 16u;
+  const bool with_bias = !stem && p.bias_tap >= 0;
   const uint32_t a_bytes = (uint32_t)(p.cout / 8) * a_plane;
   const uint32_t b_bytes = (uint32_t)xplanes * b_plane;
-  const uint32_t stage_bytes = a_bytes + b_bytes;     // multiples of 128
+  const uint32_t tx_bytes = a_bytes + b_bytes;         // what the bulk copies of one stage deliver
+  const uint32_t stage_bytes = tx_bytes + (with_bias ? 2u * b_plane : 0u);     // multiples of 128
   const uint32_t bar0 = tc::smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
   auto bar_empty = [&](int s) { return bar0 + 8u * (8 + s); };
@@ -118,6 +128,15 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
     tc::tmem_alloc(tc::smem_u32(tmem_slot), 512u);
     tc::tmem_relinquish();
   }
+  if (with_bias) {
+    // the two planes of ones behind the input planes of every stage: written once, no copy ever lands on them
+    const uint32_t ones = 0x3F803F80u;   // bf16 1.0 twice
+    for (int s = 0; s < p.nstages; ++s) {
+      uint4* dst = reinterpret_cast<uint4*>(s_stage + (size_t)s * stage_bytes + tx_bytes);
+      for (int i = threadIdx.x; i < 2 * xrows; i += kWgradThreads) dst[i] = make_uint4(ones, ones, ones, ones);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -135,7 +154,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
       int got = 1;
       if (lane == 0) {
         got = tc::mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, 40) ? 1 : 0;
-        if (got) tc::mbar_expect_tx(bar_full(s), stage_bytes);
+        if (got) tc::mbar_expect_tx(bar_full(s), tx_bytes);
       }
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) {
@@ -172,6 +191,8 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
     // ------------------------------ MMA issuer ------------------------------
     const int ncols = stem ? p.cout : p.cin;        // accumulator columns of one tap
     const uint32_t idesc = make_idesc_bf16_mn(128, ncols);
+    const uint32_t idesc_bias = make_idesc_bf16_mn(128, ncols + 16);      // the tap that also sums dPre itself
+    const int bias_t = (with_bias && group == 0) ? p.bias_tap : -1;
     const int kh = (stem ? p.stem_k : p.kside) >> 1;
     // MN-major no-swizzle descriptors: leading byte offset = 128 B (next 8 positions), stride byte offset =
     // the plane pitch of the staged operand (next 8 channels); in stem mode the input operand's "next 8 rows of M"
@@ -216,7 +237,8 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
           for (int t = 0; t < kWgradMaxTaps; ++t)
             if (t < ntap) {
               const uint64_t grad_desc = ((uint64_t)a_hi << 32) | a_lo, in_desc = ((uint64_t)b_hi << 32) | (b_lo + tshift[t]);
-              tc::mma_bf16(tmem_base + (uint32_t)(t * ncols), stem ? in_desc : grad_desc, stem ? grad_desc : in_desc, idesc, acc);
+              tc::mma_bf16(tmem_base + (uint32_t)(t * ncols), stem ? in_desc : grad_desc, stem ? grad_desc : in_desc,
+                           t == bias_t ? idesc_bias : idesc, acc);
             }
         }
         tc::mma_commit(bar_empty(s));
@@ -256,6 +278,12 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
           }
         }
       }
+      if (with_bias && group == 0) {
+        uint32_t v[16];
+        tc::tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(p.bias_tap * ncols + ncols), v);
+        tc::tmem_wait_ld();
+        p.bias_partial[(size_t)slab * 128 + co] = empty ? 0.f : __uint_as_float(v[0]);
+      }
     }
   }
 
@@ -268,17 +296,38 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
   }
 }
 
-// dW[co][ci][tap] (the reference's [Cout,Cin,K,K] fp32 layout) = sum over slabs of the partial sums, in slab order.
+// sum of p[s * stride] over the slabs in a fixed order: four interleaved running sums (slab s goes to sum s % 4) so that
+// four loads are in flight, added up as (s0 + s1) + (s2 + s3) -- the same association on every run
+__device__ __forceinline__ float sum_slabs(const float* __restrict__ p, size_t stride, int nslabs) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int s = 0;
+  for (; s + 4 <= nslabs; s += 4) {
+    a0 += p[(size_t)s * stride];
+    a1 += p[(size_t)(s + 1) * stride];
+    a2 += p[(size_t)(s + 2) * stride];
+    a3 += p[(size_t)(s + 3) * stride];
+  }
+  if (s < nslabs) a0 += p[(size_t)s * stride];
+  if (s + 1 < nslabs) a1 += p[(size_t)(s + 1) * stride];
+  if (s + 2 < nslabs) a2 += p[(size_t)(s + 2) * stride];
+  return (a0 + a1) + (a2 + a3);
+}
+
+// dW[co][ci][tap] (the reference's [Cout,Cin,K,K] fp32 layout) = sum over slabs of the partial sums, in a fixed order.
+// With bias_partial: the threads behind the last weight add up db[co] = sum over slabs of bias_partial[slab][co].
 __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nslabs, int ntaps,
-                                    int cin_p, int cin, int cout) {
+                                    int cin_p, int cin, int cout, const float* __restrict__ bias_partial,
+                                    float* __restrict__ db) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (long long)cout * cin * ntaps) return;
+  const long long nw = (long long)cout * cin * ntaps;
+  if (idx >= nw) {
+    if (bias_partial != nullptr && idx - nw < cout) db[idx - nw] = sum_slabs(bias_partial + (idx - nw), 128, nslabs);
+    return;
+  }
   const int tap = (int)(idx % ntaps);
   const int ci = (int)((idx / ntaps) % cin);
   const int co = (int)(idx / ((long long)ntaps * cin));
-  float acc = 0.f;
-  for (int s = 0; s < nslabs; ++s) acc += partial[(((size_t)s * ntaps + tap) * 128 + co) * cin_p + ci];
-  dw[idx] = acc;
+  dw[idx] = sum_slabs(partial + ((size_t)tap * 128 + co) * cin_p + ci, (size_t)ntaps * 128 * cin_p, nslabs);
 }
 
 // Stem mode: dW[co][ci][ky][kx] from partial[slab][tap = (ci, kx / 8, ky / 16)][m = (ky % 16) * 8 + kx % 8][co].
@@ -292,9 +341,7 @@ __global__ void wgrad_reduce_stem_kernel(const float* __restrict__ partial, floa
   const int co = (int)(idx / (3LL * kside * kside));
   const int tap = (ci * nkxb + (kx >> 3)) * nkyb + (ky >> 4);
   const int m = (ky & 15) * 8 + (kx & 7);
-  float acc = 0.f;
-  for (int s = 0; s < nslabs; ++s) acc += partial[(((size_t)s * ntaps + tap) * 128 + m) * cout_p + co];
-  dw[idx] = acc;
+  dw[idx] = sum_slabs(partial + ((size_t)tap * 128 + m) * cout_p + co, (size_t)ntaps * 128 * cout_p, nslabs);
 }
 
 }  // namespace c6

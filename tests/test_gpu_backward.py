@@ -347,3 +347,50 @@ def test_ppo_loss_golden_and_oracle(cuda_device):
         ppo_loss(logits, values, legal, actions, old, adv, ret)
     with pytest.raises(ValueError):
         ppo_loss(lg, vv[:5], legal.to(dev), actions.to(dev), old.to(dev), adv.to(dev), ret.to(dev))
+
+
+def test_ppo_updates_track_the_autograd_path(cuda_device):
+    """Five optimizer steps of a PPO minibatch loop (forward under bf16 autocast, ppo_loss, backward, gradient clipping,
+    AdamW) with the network and the loss on the library's kernels against the same loop through the PyTorch modules and
+    the reference's loss statements: the losses stay together, and the parameters end up close."""
+    from torch.distributions import Categorical
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.model import PolicyValueNet
+    from connect6_b200.train_ops import ppo_loss
+    dev = cuda_device
+    torch.manual_seed(5)
+    plain = PolicyValueNet(19).to(dev).train()
+    ours = PolicyValueNet(19, engine_backward=True).to(dev).train()
+    ours.load_state_dict(plain.state_dict())
+    B = 64
+    x = torch.from_numpy(generate_planes(0, B)).to(dev)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    legal = (x[:, 0] + x[:, 1]).reshape(B, -1).eq(0)
+    actions = torch.multinomial(legal.float(), 1, generator=gen).squeeze(1)
+    old = -torch.log(legal.sum(1).float()) + 0.1 * torch.randn(B, device=dev, generator=gen)
+    adv, ret = torch.randn(B, device=dev, generator=gen), torch.tanh(torch.randn(B, device=dev, generator=gen))
+    losses = {}
+    for name, m in (("plain", plain), ("ours", ours)):
+        opt = torch.optim.AdamW(m.parameters(), lr=3e-4)
+        losses[name] = []
+        for _ in range(5):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                logits, value = m(x)
+                if m is ours:
+                    loss, stats = ppo_loss(logits, value, legal, actions, old, adv, ret, 1.0, 0.2, 0.5, 0.01)
+                else:
+                    z = logits.masked_fill(~legal, torch.finfo(logits.dtype).min)
+                    dist = Categorical(logits=z.float())
+                    ratio = (dist.log_prob(actions) - old).exp()
+                    pg = torch.maximum(-adv * ratio, -adv * torch.clamp(ratio, 0.8, 1.2)).mean()
+                    loss = pg + 0.5 * 0.5 * (value.float() - ret).pow(2).mean() - 0.01 * dist.entropy().mean()
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+            torch.nn.utils.clip_grad_norm_(m.parameters(), 0.5)
+            opt.step()
+            losses[name].append(float(loss))
+    assert all(abs(a - b) < 5e-3 + 0.02 * abs(a) for a, b in zip(losses["plain"], losses["ours"])), losses
+    for (k, p), (_, q) in zip(plain.named_parameters(), ours.named_parameters()):
+        # AdamW's first steps move every parameter by about lr per step whatever the gradient's size: the two runs may
+        # differ by a few lr where a gradient component is noise-sized, never by more
+        assert (p - q).abs().max().item() <= 5 * 2 * 3e-4 + 1e-6, k

@@ -21,6 +21,16 @@ from . import _lib as L
 _workspaces: dict[tuple, torch.Tensor] = {}
 
 
+def _f32(t: torch.Tensor | None, dev: torch.device) -> torch.Tensor | None:
+    """t as a contiguous fp32 tensor on dev without autograd history; t itself when it already is one (the usual case:
+    no dispatcher call on the hot path of a 256-board minibatch, which is bound by host time)."""
+    if t is None:
+        return None
+    if t.dtype is torch.float32 and t.device == dev and t.is_contiguous():
+        return t.detach() if t.requires_grad else t
+    return t.detach().to(device=dev, dtype=torch.float32).contiguous()
+
+
 def _workspace(device: torch.device, n: int, k: int, cin: int, cout: int, B: int) -> torch.Tensor:
     """Zero-filled scratch for one shape, kept and reused: the operator maintains the zero padding it
     relies on, so the buffer is cleared only once."""
@@ -52,7 +62,7 @@ def conv_layer_backward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tenso
     if cin_w != cin or k != k2 or tuple(grad_out.shape) != (B, cout, n, n) or (bias is not None and tuple(bias.shape) != (cout,)):
         raise ValueError("conv_layer_backward: shapes of x, weight, bias and grad_out do not belong to one layer")
     dev = x.device
-    f32 = lambda t: None if t is None else t.detach().to(device=dev, dtype=torch.float32).contiguous()
+    f32 = lambda t: _f32(t, dev)
     x, weight, bias, grad_out = f32(x), f32(weight), f32(bias), f32(grad_out)
     dx = torch.empty_like(x) if need_dx else None
     dw = torch.empty_like(weight)
@@ -175,7 +185,7 @@ def stack_forward(x: torch.Tensor, weights, biases, want_features: bool = True):
     if B == 0:
         return x.new_zeros((0, channels[-1], n, n), dtype=torch.float32), None
     dev = x.device
-    f32 = lambda t: None if t is None else t.detach().to(device=dev, dtype=torch.float32).contiguous()
+    f32 = lambda t: _f32(t, dev)
     x = f32(x)
     ws_ = [f32(w) for w in weights]
     bs_ = [f32(b) for b in biases]
@@ -221,7 +231,7 @@ def heads_forward(lease: _StackLease, pw: torch.Tensor, pb: torch.Tensor, vw: to
     `stack_forward` left in the lease.  pw, vw: the [1, C, 1, 1] filters; pb, vb: [1]."""
     dev_index, n, channels, B, stem_k = lease.key
     dev = lease.ws.device
-    f32 = lambda t: t.detach().to(device=dev, dtype=torch.float32).contiguous()
+    f32 = lambda t: _f32(t, dev)
     pw, pb, vw, vb = f32(pw).reshape(-1), f32(pb).reshape(-1), f32(vw).reshape(-1), f32(vb).reshape(-1)
     if pw.numel() != channels[-1] or vw.numel() != channels[-1] or pb.numel() != 1 or vb.numel() != 1:
         raise ValueError("heads_forward: head parameters do not fit the features' channel count")
@@ -244,7 +254,7 @@ def heads_backward(lease: _StackLease, pw: torch.Tensor, vw: torch.Tensor, dlogi
     `stack_backward(lease, None)` picks it up."""
     dev_index, n, channels, B, stem_k = lease.key
     dev = lease.ws.device
-    f32 = lambda t: t.detach().to(device=dev, dtype=torch.float32).contiguous()
+    f32 = lambda t: _f32(t, dev)
     pwf, vwf, dlogits, dvalue, value = f32(pw).reshape(-1), f32(vw).reshape(-1), f32(dlogits), f32(dvalue), f32(value)
     if tuple(dlogits.shape) != (B, n * n) or tuple(dvalue.shape) != (B,) or tuple(value.shape) != (B,):
         raise ValueError("heads_backward: gradients do not belong to this forward call")
@@ -345,7 +355,7 @@ class _PpoLoss(torch.autograd.Function):
             if tuple(v.shape) != (B,):
                 raise ValueError(f"ppo_loss: {name} must be [B]")
         dev = logits.device
-        f32 = lambda v: v.detach().to(device=dev, dtype=torch.float32).contiguous()
+        f32 = lambda v: _f32(v, dev)
         lg, vv, old, adv, ret = f32(logits), f32(values), f32(old_logprob), f32(advantages), f32(returns)
         lm = legal.detach().to(device=dev, dtype=torch.uint8).contiguous()
         act = actions.detach().to(device=dev, dtype=torch.int64).contiguous()

@@ -394,3 +394,52 @@ def test_ppo_updates_track_the_autograd_path(cuda_device):
         # AdamW's first steps move every parameter by about lr per step whatever the gradient's size: the two runs may
         # differ by a few lr where a gradient component is noise-sized, never by more
         assert (p - q).abs().max().item() <= 5 * 2 * 3e-4 + 1e-6, k
+
+
+def test_training_step_under_a_cuda_graph(cuda_device):
+    """Forward + ppo_loss + backward of PolicyValueNet(engine_backward=True) captured once in a CUDA graph and replayed:
+    the library's training entry points only enqueue work on the stream they are given (no allocation, no
+    synchronisation), so the whole step is capturable; the replayed gradients equal the eager ones bit for bit (every
+    reduction runs in a fixed order)."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.model import PolicyValueNet
+    from connect6_b200.train_ops import ppo_loss
+    dev = cuda_device
+    torch.manual_seed(2)
+    m = PolicyValueNet(19, engine_backward=True).to(dev).train()
+    B = 32
+    x = torch.from_numpy(generate_planes(0, B)).to(dev)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    legal = (x[:, 0] + x[:, 1]).reshape(B, -1).eq(0)
+    actions = torch.multinomial(legal.float(), 1, generator=gen).squeeze(1)
+    old = -torch.log(legal.sum(1).float())
+    adv, ret = torch.randn(B, device=dev, generator=gen), torch.zeros(B, device=dev)
+
+    def step():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits, value = m(x)
+            loss, _ = ppo_loss(logits, value, legal, actions, old, adv, ret)
+        loss.backward()
+        return loss
+
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            m.zero_grad(set_to_none=True)
+            eager_loss = step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    eager = [p.grad.detach().clone() for p in m.parameters()]
+    m.zero_grad(set_to_none=True)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        graph_loss = step()
+    for _ in range(2):
+        for p in m.parameters():
+            p.grad.zero_()          # the captured backward accumulates into these very tensors
+        graph.replay()
+    torch.cuda.synchronize(dev)
+    assert float(graph_loss) == float(eager_loss)
+    for p, ref in zip(m.parameters(), eager):
+        assert torch.equal(p.grad, ref)

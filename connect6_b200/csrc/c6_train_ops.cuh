@@ -534,7 +534,6 @@ int c6_conv_layer_backward(int32_t device, int32_t board_size, int32_t kside, in
   uint4* dxp = reinterpret_cast<uint4*>(ws + L.off_dx);
   float* partial = reinterpret_cast<float*>(ws + L.off_partial);
   float* colsum = reinterpret_cast<float*>(ws + L.off_colsum);
-  const int taps = kside * kside;
 
   // operands
   copy_pad_f32_kernel<<<(L.cout_p + 127) / 128, 128, 0, st>>>(bias, bias_f, cout, L.cout_p);

@@ -785,13 +785,17 @@ def run_train_step(args) -> None:
     sampler = ClockSampler(0)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin = time.time()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     e0.record()
-    for _ in range(args.steps):
+    marks[0].record()
+    for i in range(args.steps):
         loss = step(ours)
+        marks[i + 1].record()
     e1.record()
     torch.cuda.synchronize(dev)
     t_end = time.time()
     ms = e0.elapsed_time(e1) / args.steps
+    per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps))
     clocks = sampler.stop(t_begin, t_end)
     lib_ms, lib_loss = None, None
     try:
@@ -839,7 +843,8 @@ def run_train_step(args) -> None:
     print(json.dumps({
         "metric": "PPO minibatch forward + loss + backward of the default network, boards/s",
         "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms, "step_ms": {"min": per_step[0], "median": per_step[len(per_step) // 2], "max": per_step[-1]},
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"PolicyValueNet(engine_backward=True) + ppo_loss, B = {B} boards: stem + seven 3x3 layers + heads + PPO loss "
                                "forward and backward on the library's kernels (bf16 operands, fp32 accumulation), no optimizer step",

@@ -236,9 +236,17 @@ __global__ void heads_backward_finish_kernel(const float* __restrict__ partial, 
   else if (i < 2 * C) { const int ch = i - C; col = (ch >> 3) * 16 + 8 + (ch & 7); dst = dwv + ch; }
   else if (i == 2 * C) { col = nq * 16; dst = dbp; }
   else { col = nq * 16 + 1; dst = dbv; }
-  float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(size_t)b * stride + col];
-  *dst = s;
+  // four interleaved running sums in a fixed association, so that four loads are in flight
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int b = 0;
+  for (; b + 4 <= nblocks; b += 4) {
+    a0 += partial[(size_t)b * stride + col];
+    a1 += partial[(size_t)(b + 1) * stride + col];
+    a2 += partial[(size_t)(b + 2) * stride + col];
+    a3 += partial[(size_t)(b + 3) * stride + col];
+  }
+  for (; b < nblocks; ++b) a0 += partial[(size_t)b * stride + col];
+  *dst = (a0 + a1) + (a2 + a3);
 }
 
 // PPO minibatch loss and its gradient at the network outputs (connect6/train.py:1047-1086):

@@ -19,8 +19,8 @@
 // fp32 partial sums
 // [slab][tap][128][Cin] to global memory and a second kernel adds the slabs up in a fixed order
 // (no atomics: results are reproducible).
-// CTA = 192 threads: warp 0 stages operands with bulk copies, warp 1 issues the MMAs and owns TMEM,
-// warps 2-5 drain the accumulators at the end.  Every wait is bounded.
+// CTA = 256 threads: warp 0 stages operands with bulk copies, warps 1, 6 and 7 issue the MMAs (each every third tap
+// of the CTA; warp 1 owns TMEM), warps 2-5 drain the accumulators at the end.  Every wait is bounded.
 #pragma once
 
 #include "c6_common.cuh"
@@ -68,7 +68,8 @@ struct WgradParams {
   float* bias_partial;
 };
 
-constexpr int kWgradThreads = 192;
+constexpr int kWgradIssuers = 3;     // MMA-issuing warps: issuer i takes the taps t of the CTA with t % kWgradIssuers == i
+constexpr int kWgradThreads = 32 * (6 + kWgradIssuers - 1);   // warp 0 producer, warp 1 and warps 6.. MMA issuers, warps 2-5 epilogue
 constexpr int kWgradSmemHeader = 1024;
 constexpr int kWgradMaxStages = 8;
 constexpr int kWgradMaxTaps = 9;     // taps one CTA may own (a 3 x 3 filter)
@@ -118,9 +119,9 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
   if (threadIdx.x == 0) {
     for (int s = 0; s < kWgradMaxStages; ++s) {
       tc::mbar_init(bar_full(s), 1);
-      tc::mbar_init(bar_empty(s), 1);
+      tc::mbar_init(bar_empty(s), kWgradIssuers);      // one commit per issuer
     }
-    tc::mbar_init(bar_done, 1);
+    tc::mbar_init(bar_done, kWgradIssuers);
     *abort_flag = 0;
     tc::fence_barrier_init();
   }
@@ -187,8 +188,10 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
+  } else if (warp == 1 || warp >= 6) {
+    // ------------------------------ MMA issuers ------------------------------
+    // several warps, each issues the MMAs of its share of the CTA's taps: one thread's issue rate does not feed the pipe
+    const int which = warp == 1 ? 0 : warp - 5;
     const int ncols = stem ? p.cout : p.cin;        // accumulator columns of one tap
     const uint32_t idesc = make_idesc_bf16_mn(128, ncols);
     const uint32_t idesc_bias = make_idesc_bf16_mn(128, ncols + 16);      // the tap that also sums dPre itself
@@ -235,7 +238,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
           // so the per-tap row shifts live in registers (no division, no table in memory)
 #pragma unroll
           for (int t = 0; t < kWgradMaxTaps; ++t)
-            if (t < ntap) {
+            if (t < ntap && t % kWgradIssuers == which) {
               const uint64_t grad_desc = ((uint64_t)a_hi << 32) | a_lo, in_desc = ((uint64_t)b_hi << 32) | (b_lo + tshift[t]);
               tc::mma_bf16(tmem_base + (uint32_t)(t * ncols), stem ? in_desc : grad_desc, stem ? grad_desc : in_desc,
                            t == bias_t ? idesc_bias : idesc, acc);
@@ -247,8 +250,8 @@ __global__ void __launch_bounds__(kWgradThreads, 1) wgrad_tc_kernel(const WgradP
       __syncwarp();
       if (++s == p.nstages) { s = 0; ph ^= 1u; }
     }
-    if (t_begin >= t_end && lane == 0) tc::mbar_arrive(bar_done);   // an empty slab still releases the epilogue
-  } else {
+    if (t_begin >= t_end && lane == 0) tc::mbar_arrive(bar_done);   // an empty slab still releases the epilogue (one arrival per issuer)
+  } else if (warp >= 2 && warp <= 5) {
     // ------------------------------ epilogue ------------------------------
     // warp w may read TMEM lanes 32*(w%4)..+31: output channels (stem mode: filter positions); each lane writes its
     // rows of the partial sums

@@ -368,6 +368,78 @@ __global__ void mul_planes_kernel(const uint4* __restrict__ a, const uint4* __re
   }
 }
 
+// Gradient clipping by global norm + AdamW for a whole parameter list in two launches (connect6/train.py:1121-1145:
+// nn.utils.clip_grad_norm_(model.parameters(), max_grad_norm) then torch.optim.AdamW.step()).
+//   total = sqrt(sum over all tensors of g^2);  coef = min(1, max_norm / (total + 1e-6));  g <- g * coef  (written back)
+//   p <- p (1 - lr wd);  m <- b1 m + (1 - b1) g;  v <- b2 v + (1 - b2) g^2;
+//   p <- p - (lr / (1 - b1^t)) * m / (sqrt(v) / sqrt(1 - b2^t) + eps)
+// The tensors are addressed as one flat index space (offset[i] = first flat index of tensor i).  Kernel 1 leaves one
+// partial sum of squares per block; every block of kernel 2 adds them up in block order (the same value everywhere,
+// the same on every run).  A non-finite norm (overflowed or NaN gradients) leaves parameters and moments untouched;
+// the norm is reported either way.
+constexpr int kOptMaxTensors = 48;
+constexpr int kOptThreads = 256;
+struct OptTensors {
+  float* p[kOptMaxTensors];
+  float* g[kOptMaxTensors];
+  float* m[kOptMaxTensors];
+  float* v[kOptMaxTensors];
+  long long offset[kOptMaxTensors + 1];
+  int n;
+};
+__device__ __forceinline__ int opt_find(const OptTensors& T, long long i) {
+  int t = 0;
+  while (t + 1 < T.n && i >= T.offset[t + 1]) ++t;
+  return t;
+}
+__global__ void __launch_bounds__(kOptThreads) grad_sumsq_kernel(const OptTensors T, float* __restrict__ partial) {
+  __shared__ float s_red[kOptThreads / 32];
+  const long long total = T.offset[T.n];
+  const long long per_block = (total + gridDim.x - 1) / gridDim.x;
+  const long long lo = per_block * blockIdx.x, hi = min(total, lo + per_block);
+  float acc = 0.f;
+  for (long long i = lo + threadIdx.x; i < hi; i += kOptThreads) {
+    const int t = opt_find(T, i);
+    const float g = T.g[t][i - T.offset[t]];
+    acc = fmaf(g, g, acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int w = 0; w < kOptThreads / 32; ++w) s += s_red[w];
+    partial[blockIdx.x] = s;
+  }
+}
+__global__ void __launch_bounds__(kOptThreads) clip_adamw_kernel(const OptTensors T, const float* __restrict__ partial, int npartial,
+                                                                 float lr, float beta1, float beta2, float eps, float weight_decay,
+                                                                 float max_norm, float bias1, float bias2_sqrt,
+                                                                 float* __restrict__ grad_norm) {
+  float sumsq = 0.f;
+  for (int b = 0; b < npartial; ++b) sumsq += partial[b];
+  const float norm = sqrtf(sumsq);
+  if (blockIdx.x == 0 && threadIdx.x == 0) *grad_norm = norm;
+  if (!(norm <= 3.0e38f)) return;                      // inf or NaN: no step
+  const float coef = max_norm > 0.f ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+  const float step_size = lr / bias1;
+  const long long total = T.offset[T.n];
+  for (long long i = (long long)blockIdx.x * kOptThreads + threadIdx.x; i < total; i += (long long)gridDim.x * kOptThreads) {
+    const int t = opt_find(T, i);
+    const long long k = i - T.offset[t];
+    const float g = T.g[t][k] * coef;
+    float p = T.p[t][k] * (1.f - lr * weight_decay);
+    const float m = beta1 * T.m[t][k] + (1.f - beta1) * g;
+    const float v = beta2 * T.v[t][k] + (1.f - beta2) * g * g;
+    p -= step_size * (m / (sqrtf(v) / bias2_sqrt + eps));
+    T.g[t][k] = g;
+    T.m[t][k] = m;
+    T.v[t][k] = v;
+    T.p[t][k] = p;
+  }
+}
+
 // Every operand a stack of 3 x 3 layers needs from its parameters, in ONE launch: grid (row blocks, layer, what) with
 // what = 0 forward filter, 1 the same for CTA pairs, 2 flipped/transposed filter of the data gradient, 3 the same for
 // CTA pairs, 4 bias padded to the kernels' channel granule.

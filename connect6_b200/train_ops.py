@@ -393,3 +393,71 @@ def ppo_loss(logits: torch.Tensor, values: torch.Tensor, legal: torch.Tensor, ac
     computes the loss and both gradients, `loss.backward()` only scales them."""
     return _PpoLoss.apply(logits, values, legal, actions, old_logprob, advantages, returns, temperature, clip_coef,
                           value_coef, entropy_coef)
+
+
+# ---- gradient clipping + AdamW -----------------------------------------------------------------------
+class ClipAdamW(torch.optim.Optimizer):
+    """torch.optim.AdamW with nn.utils.clip_grad_norm_ folded in, for a model's whole parameter list in two kernel
+    launches (connect6/train.py:476-481 sets the optimizer up, :1121-1145 clips and steps).  `step()` returns the total
+    gradient norm BEFORE clipping as a device tensor (what clip_grad_norm_ returns) without synchronising; a
+    non-finite norm leaves the parameters untouched.  The state (`step`, `exp_avg`, `exp_avg_sq` per parameter) and
+    `state_dict()` have torch.optim.AdamW's layout, so checkpoints move between the two.  One parameter group per
+    call of the kernel; fp32 CUDA parameters only."""
+
+    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2,
+                 max_grad_norm: float = 0.0) -> None:
+        if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
+            raise ValueError("ClipAdamW: invalid hyper-parameter")
+        super().__init__(params, dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
+                                      amsgrad=False, maximize=False, foreach=None, capturable=False, differentiable=False,
+                                      fused=None))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        if closure is not None:
+            raise RuntimeError("ClipAdamW.step takes no closure")
+        norms = []
+        for group in self.param_groups:
+            ps = [p for p in group["params"] if p.grad is not None]
+            if not ps:
+                continue
+            dev = ps[0].device
+            for p in ps:
+                if not p.is_cuda or p.dtype != torch.float32 or p.device != dev or not p.is_contiguous() or not p.grad.is_contiguous() \
+                        or p.grad.dtype != torch.float32:
+                    raise RuntimeError("ClipAdamW: contiguous fp32 CUDA parameters and gradients on one device only (no CPU path)")
+                st = self.state[p]
+                if not st:
+                    st["step"] = torch.tensor(0.0)
+                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+            steps = {int(self.state[p]["step"]) for p in ps}
+            if len(steps) != 1:
+                raise RuntimeError("ClipAdamW: the parameters of a group must have been stepped together")
+            step = steps.pop() + 1
+            norm = torch.empty(1, device=dev, dtype=torch.float32)
+            pool = self.__dict__.setdefault("_c6_workspaces", {})
+            ws = pool.get(dev)
+            if ws is None:
+                ws = pool[dev] = torch.empty(148, device=dev, dtype=torch.float32)
+            b1, b2 = group["betas"]
+            for lo in range(0, len(ps), 48):
+                chunk = ps[lo:lo + 48]
+                if len(ps) > 48:
+                    raise RuntimeError("ClipAdamW: at most 48 parameter tensors per group")
+                sizes = (C.c_int64 * len(chunk))(*[p.numel() for p in chunk])
+                with torch.cuda.device(dev):
+                    rc = L.load().c6_clip_adamw_step(dev.index, len(chunk), sizes, _ptr_array(chunk), _ptr_array([p.grad for p in chunk]),
+                                                     _ptr_array([self.state[p]["exp_avg"] for p in chunk]),
+                                                     _ptr_array([self.state[p]["exp_avg_sq"] for p in chunk]), float(group["lr"]),
+                                                     float(b1), float(b2), float(group["eps"]), float(group["weight_decay"]),
+                                                     float(group["max_grad_norm"]), step, norm.data_ptr(), ws.data_ptr(),
+                                                     ws.numel() * 4, torch.cuda.current_stream(dev).cuda_stream)
+                if rc != L.C6_OK:
+                    raise _train_fail(rc, "c6_clip_adamw_step")
+            for p in ps:
+                self.state[p]["step"] += 1
+            norms.append(norm)
+        if not norms:
+            return None
+        return norms[0][0] if len(norms) == 1 else torch.stack([n[0] for n in norms])

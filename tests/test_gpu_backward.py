@@ -443,3 +443,56 @@ def test_training_step_under_a_cuda_graph(cuda_device):
     assert float(graph_loss) == float(eager_loss)
     for p, ref in zip(m.parameters(), eager):
         assert torch.equal(p.grad, ref)
+
+
+def test_clip_adamw_matches_torch(cuda_device):
+    """train_ops.ClipAdamW (c6_clip_adamw_step: global-norm clipping + AdamW in two launches) against
+    nn.utils.clip_grad_norm_ + torch.optim.AdamW with the reference's hyper-parameters (connect6/train.py:476-481,
+    configs/train.yaml:55-62) over four steps, two of them with gradients large enough to be clipped; then the state
+    moves into a torch.optim.AdamW and both continue in step."""
+    from connect6_b200.model import PolicyValueNet
+    from connect6_b200.train_ops import ClipAdamW
+    dev = cuda_device
+    torch.manual_seed(4)
+    a = PolicyValueNet(19).to(dev)
+    b = PolicyValueNet(19).to(dev)
+    b.load_state_dict(a.state_dict())
+    kw = dict(lr=2.5e-4, weight_decay=1e-4, eps=1e-5)
+    ref = torch.optim.AdamW(a.parameters(), **kw)
+    ours = ClipAdamW(b.parameters(), max_grad_norm=2.0, **kw)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    for it in range(4):
+        scale = 10.0 if it % 2 else 1e-2               # clipped / not clipped
+        for pa, pb in zip(a.parameters(), b.parameters()):
+            g = scale * torch.randn(pa.shape, device=dev, generator=gen)
+            pa.grad, pb.grad = g.clone(), g.clone()
+        want_norm = torch.nn.utils.clip_grad_norm_(a.parameters(), 2.0, error_if_nonfinite=True)
+        ref.step()
+        got_norm = ours.step()
+        assert abs(float(got_norm) - float(want_norm)) < 1e-4 * float(want_norm)
+        for pa, pb in zip(a.parameters(), b.parameters()):
+            assert torch.allclose(pb.grad, pa.grad, rtol=1e-5, atol=1e-9)            # clipped in place like clip_grad_norm_
+            assert (pa - pb).abs().max().item() < 2e-7 + 1e-6 * pa.abs().max().item()
+    # the state has AdamW's layout: a torch optimizer continues from it
+    cont = torch.optim.AdamW(b.parameters(), **kw)
+    sd = ours.state_dict()
+    for g_ in sd["param_groups"]:
+        g_.pop("max_grad_norm")
+    cont.load_state_dict(sd)
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        g = 1e-2 * torch.randn(pa.shape, device=dev, generator=gen)
+        pa.grad, pb.grad = g.clone(), g.clone()
+    ref.step()
+    cont.step()
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        assert (pa - pb).abs().max().item() < 4e-7 + 1e-6 * pa.abs().max().item()
+    # a non-finite gradient: the norm says so, nothing moves
+    before = [p.detach().clone() for p in b.parameters()]
+    next(iter(b.parameters())).grad[0, 0, 0, 0] = float("inf")
+    n = ours.step()
+    assert not torch.isfinite(n)
+    assert all(torch.equal(p, q) for p, q in zip(b.parameters(), before))
+    cpu_p = torch.nn.Parameter(torch.zeros(3))
+    cpu_p.grad = torch.zeros(3)
+    with pytest.raises(RuntimeError):       # no CPU path
+        ClipAdamW([cpu_p], lr=1e-3).step()

@@ -814,6 +814,34 @@ def run_train_step(args) -> None:
         lib_loss = float(lib_loss)
     except Exception as exc:  # noqa: BLE001
         lib_ms = f"{type(exc).__name__}: {exc}"[:160]
+    # the whole minibatch update: + gradient clipping and AdamW (connect6/train.py:1121-1145), ClipAdamW against
+    # clip_grad_norm_ + torch.optim.AdamW, hyper-parameters of configs/train.yaml
+    update_ms = {}
+    try:
+        if args.no_library_bar:
+            raise RuntimeError("skipped (--no-library-bar)")
+        from connect6_b200.train_ops import ClipAdamW
+        kw = dict(lr=2.5e-4, weight_decay=1e-4, eps=1e-5)
+        opts = {"library": (ours, ClipAdamW(ours.parameters(), max_grad_norm=2.0, **kw)),
+                "pytorch": (plain, torch.optim.AdamW(plain.parameters(), **kw))}
+        for name, (m, opt) in opts.items():
+            def update():
+                step(m)
+                if name == "pytorch":
+                    torch.nn.utils.clip_grad_norm_(m.parameters(), 2.0)
+                opt.step()
+            for _ in range(3):
+                update()
+            torch.cuda.synchronize(dev)
+            u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            u0.record()
+            for _ in range(10):
+                update()
+            u1.record()
+            torch.cuda.synchronize(dev)
+            update_ms[name] = u0.elapsed_time(u1) / 10
+    except Exception as exc:  # noqa: BLE001
+        update_ms = {"error": f"{type(exc).__name__}: {exc}"[:160]}
     kernels = {}
     try:
         if args.no_library_bar:
@@ -854,6 +882,7 @@ def run_train_step(args) -> None:
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_source,
                      "flop_algorithmic": algorithmic, "traffic": None},
         "kernels": kernels,
+        "update_ms": {**update_ms, "what": "the step plus gradient clipping and AdamW: train_ops.ClipAdamW / clip_grad_norm_ + torch.optim.AdamW"},
         "library_gpu_bar": {"ms_per_step": lib_ms, "what": "the same step through the PyTorch modules, the reference's loss statements and autograd under bf16 autocast (cuDNN)"},
         "device_status": 0}), flush=True)
 

@@ -92,6 +92,8 @@ SIGNATURES = {
     "c6_backbone_workspace_bytes": (_i64, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64]),
     "c6_backbone_forward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64, _vp, C.POINTER(_vp),
                                  C.POINTER(_vp), _vp, _vp, _i64, _vp]),
+    "c6_backbone_forward_boards": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64, _vp, _vp, _vp, _i64, _vp,
+                                        C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _i64, _vp]),
     "c6_backbone_backward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64, _vp, _vp,
                                   C.POINTER(_vp), C.POINTER(_vp), _vp, _i64, _vp]),
     "c6_backbone_heads_forward": (_i, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, _i64, _vp, _vp, _vp, _vp,

@@ -591,11 +591,12 @@ int64_t c6_backbone_workspace_bytes(int32_t board_size, int32_t nlayers, const i
   return S.ok ? (int64_t)S.total : 0;
 }
 
-int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
-                        int64_t B, const float* x, const float* const* w, const float* const* bias, float* y,
-                        void* workspace, int64_t workspace_bytes, void* stream) {
+static int backbone_forward_impl(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                                 int64_t B, const InputSrc& in, const float* const* w, const float* const* bias, float* y,
+                                 void* workspace, int64_t workspace_bytes, void* stream) {
+  const float* x = static_cast<const float*>(in.x);
   if (B < 1) return tfail(C6_ERR_ARG, "board count must be positive");
-  if (!x || !w || !bias || !channels) return tfail(C6_ERR_ARG, "null pointer");
+  if (!w || !bias || !channels) return tfail(C6_ERR_ARG, "null pointer");
   const StackLayout S = make_stack_layout(board_size, nlayers, channels, stem_kside, B);
   int sms = 0;
   int rc = check_stack_call(device, S, workspace, workspace_bytes, &sms);
@@ -637,8 +638,6 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
     pack_stem_direct_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
         w[0], reinterpret_cast<uint4*>(ws + S.off_wf_pair[0]), T.cout, T.k, T.cout_p, T.hx, 2, 0);
     C6T_LAUNCHED("pack_stem_direct_weights_kernel");
-    InputSrc in{};
-    in.x = x;
     const long long total = 3LL * T.slots * B;
     pack_stem_direct_input_kernel<<<dim3((unsigned)((total + 255) / 256), 1u), 256, 0, st>>>(
         in, nullptr, reinterpret_cast<uint4*>(ws + S.off_xe), T.xe_plane_rows, T.front, (int)T.group_pos, T.wi, T.slots, board_size,
@@ -650,6 +649,7 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
                           status, board_size, B, sms, st);
     if (rc) return rc;
   } else {
+    if (!x) return tfail(C6_ERR_ARG, "null pointer");
     const long long t = B * L0.slots * (L0.cin_p / 8);
     pack_nchw_planes_kernel<<<(unsigned)((t + 255) / 256), 256, 0, st>>>(
         x, reinterpret_cast<uint4*>(ws + S.off_act[0]), L0.plane_rows, L0.front, L0.slots, L0.wp, L0.n, L0.cin, L0.cin_p, B);
@@ -671,6 +671,31 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
     C6T_LAUNCHED("unpack_planes_nchw_kernel");
   }
   return C6_OK;
+}
+
+int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                        int64_t B, const float* x, const float* const* w, const float* const* bias, float* y,
+                        void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!x) return tfail(C6_ERR_ARG, "null pointer");
+  InputSrc in{};
+  in.x = x;
+  return backbone_forward_impl(device, board_size, nlayers, channels, stem_kside, B, in, w, bias, y, workspace, workspace_bytes, stream);
+}
+
+int c6_backbone_forward_boards(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,
+                               int64_t B, const int8_t* boards, const int8_t* current_player, const int8_t* stones_left,
+                               int64_t num_envs, const int64_t* index, const float* const* w, const float* const* bias, float* y,
+                               void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!boards || !current_player || !stones_left) return tfail(C6_ERR_ARG, "null pointer");
+  if (stem_kside <= 0) return tfail(C6_ERR_ARG, "board input feeds the network's first layer: stem_kside must be given");
+  if (num_envs < 1 || (!index && B > num_envs)) return tfail(C6_ERR_ARG, "more boards than environments and no index");
+  InputSrc in{};
+  in.boards = boards;
+  in.player = current_player;
+  in.stones_left = stones_left;
+  in.index = reinterpret_cast<const long long*>(index);
+  in.num_envs = num_envs;
+  return backbone_forward_impl(device, board_size, nlayers, channels, stem_kside, B, in, w, bias, y, workspace, workspace_bytes, stream);
 }
 
 int c6_backbone_heads_forward(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels, int32_t stem_kside,

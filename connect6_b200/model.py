@@ -210,6 +210,30 @@ class PolicyValueNet(nn.Module):
             board_index0=board_index0, orient=orient, inverse_map=inverse_map, want_logits=want_logits)
 
 
+    def forward_from_boards(self, boards: torch.Tensor, current_player: torch.Tensor, stones_left: torch.Tensor,
+                            index: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """forward(canonical_network_input(boards[index], current_player[index], stones_left[index])) -- what the PPO
+        minibatch computes from its buffer (connect6/train.py:1038-1048) -- without materialising the gathered state or
+        the planes when the grad-enabled forward runs on the library's kernels (`engine_backward=True`): the first kernel
+        reads the int8 state directly.  Otherwise the planes are built and `forward` is called."""
+        convs = list(self.convs)
+        if (self.engine_backward and boards.is_cuda and torch.is_grad_enabled() and any(p.requires_grad for p in self.parameters())
+                and boards.dtype == torch.int8 and len(convs) >= 2):
+            from .train_ops import PolicyValueStackFromBoards, supports_layer, supports_stem
+            if supports_stem(convs[0], self.board_size) and all(supports_layer(c, self.board_size) for c in convs[1:]) \
+                    and (index is None or index.numel() > 0) and boards.shape[0] > 0:
+                params = [p for c in convs for p in (c.weight, c.bias)]
+                idx = (torch.empty(0, dtype=torch.int64, device=boards.device) if index is None
+                       else index.to(device=boards.device, dtype=torch.int64))
+                return PolicyValueStackFromBoards.apply(
+                    boards, current_player.to(device=boards.device, dtype=torch.int8),
+                    stones_left.to(device=boards.device, dtype=torch.int8), idx, *params, self.policy_output.weight,
+                    self.policy_output.bias, self.value_output.weight, self.value_output.bias)
+        from .selfplay import canonical_network_input
+        if index is not None:
+            boards, current_player, stones_left = boards[index], current_player[index], stones_left[index]
+        return self.forward(canonical_network_input(boards, current_player, stones_left))
+
     @torch.no_grad()
     def selfplay_step_from_boards(self, boards: torch.Tensor, current_player: torch.Tensor, stones_left: torch.Tensor,
                                   index: torch.Tensor | None = None, **kwargs):

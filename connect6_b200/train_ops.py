@@ -272,6 +272,53 @@ def heads_backward(lease: _StackLease, pw: torch.Tensor, vw: torch.Tensor, dlogi
     return dpw.view_as(pw), dpb, dvw.view_as(vw), dvb
 
 
+def stack_forward_boards(boards: torch.Tensor, current_player: torch.Tensor, stones_left: torch.Tensor,
+                         index: torch.Tensor | None, weights, biases, want_features: bool = True):
+    """`stack_forward` for a stack that starts with the network's stem, fed with the environment's raw int8 state
+    (boards [E, n, n], current_player [E], stones_left [E]) and an optional int64 index [B] selecting the boards --
+    what the PPO minibatch holds in its buffer (connect6/train.py:1038-1046): the gather and canonical_network_input
+    (connect6/vector_env.py:196-218) happen inside the first kernel."""
+    if not boards.is_cuda:
+        raise RuntimeError(f"stack_forward_boards: expected CUDA tensors, got {boards.device} (no CPU path in this package)")
+    if boards.ndim != 3 or boards.shape[1] != boards.shape[2] or boards.dtype != torch.int8:
+        raise ValueError("stack_forward_boards: boards must be int8 [E, n, n]")
+    E, n, _ = boards.shape
+    for name, v in (("current_player", current_player), ("stones_left", stones_left)):
+        if tuple(v.shape) != (E,) or v.dtype != torch.int8 or v.device != boards.device:
+            raise ValueError(f"stack_forward_boards: {name} must be int8 [E] on the boards' device")
+    if index is not None and (index.ndim != 1 or index.dtype != torch.int64 or index.device != boards.device):
+        raise ValueError("stack_forward_boards: index must be int64 [B] on the boards' device")
+    if len(weights) != len(biases) or len(weights) < 2 or weights[0].ndim != 4 or weights[0].shape[1] != 3:
+        raise ValueError("stack_forward_boards: the stack must start with the stem on the 3 input planes and have a 3x3 layer behind it")
+    B = E if index is None else int(index.shape[0])
+    stem_k = int(weights[0].shape[-1])
+    channels = [3]
+    for l, (w, b) in enumerate(zip(weights, biases)):
+        k = stem_k if l == 0 else 3
+        if w.ndim != 4 or tuple(w.shape[1:]) != (channels[-1], k, k) or (b is not None and tuple(b.shape) != (w.shape[0],)):
+            raise ValueError("stack_forward_boards: the layers' shapes do not chain (a k x k stem on 3 planes, then 3x3 filters)")
+        channels.append(int(w.shape[0]))
+    dev = boards.device
+    if B == 0:
+        return torch.zeros((0, channels[-1], n, n), device=dev), None
+    f32 = lambda t: _f32(t, dev)
+    ws_ = [f32(w) for w in weights]
+    bs_ = [f32(b) for b in biases]
+    boards, current_player, stones_left = boards.contiguous(), current_player.contiguous(), stones_left.contiguous()
+    index = None if index is None else index.contiguous()
+    lease = _StackLease(dev, n, tuple(channels), B, stem_k)
+    y = torch.empty((B, channels[-1], n, n), device=dev, dtype=torch.float32) if want_features else None
+    arr = (C.c_int32 * len(channels))(*channels)
+    with torch.cuda.device(dev):
+        rc = L.load().c6_backbone_forward_boards(dev.index, n, len(ws_), arr, stem_k, B, boards.data_ptr(), current_player.data_ptr(),
+                                                 stones_left.data_ptr(), E, L.ptr(index), _ptr_array(ws_), _ptr_array(bs_), L.ptr(y),
+                                                 lease.ws.data_ptr(), lease.ws.numel() * 8,
+                                                 torch.cuda.current_stream(dev).cuda_stream)
+    if rc != L.C6_OK:
+        raise _train_fail(rc, "c6_backbone_forward_boards")
+    return y, lease
+
+
 def stack_status(lease: _StackLease) -> int:
     """Device status word of a stack workspace (synchronises)."""
     return int(lease.ws[0].item()) & 0xFFFFFFFF
@@ -461,3 +508,41 @@ class ClipAdamW(torch.optim.Optimizer):
         if not norms:
             return None
         return norms[0][0] if len(norms) == 1 else torch.stack([n[0] for n in norms])
+
+
+class PolicyValueStackFromBoards(torch.autograd.Function):
+    """`PolicyValueStack` fed with the environment's raw int8 state instead of network-input planes (see
+    `stack_forward_boards`).  Call as PolicyValueStackFromBoards.apply(boards, current_player, stones_left, index,
+    w_1, b_1, ..., policy_w, policy_b, value_w, value_b); index may be an empty tensor for "every board"."""
+
+    @staticmethod
+    def forward(ctx, boards, current_player, stones_left, index, *params):
+        conv_params, (pw, pb, vw, vb) = params[:-4], params[-4:]
+        weights, biases = list(conv_params[0::2]), list(conv_params[1::2])
+        _, lease = stack_forward_boards(boards, current_player, stones_left, index if index.numel() else None, weights, biases,
+                                        want_features=False)
+        logits, value = heads_forward(lease, pw, pb, vw, vb)
+        ctx.lease = lease
+        ctx.save_for_backward(pw, vw, value)
+        ctx.pdtypes = [p.dtype for p in params]
+        return logits, value
+
+    @staticmethod
+    def backward(ctx, dlogits, dvalue):
+        pw, vw, value = ctx.saved_tensors
+        lease = ctx.lease
+        B = lease.key[3]
+        if dlogits is None:
+            dlogits = torch.zeros((B, lease.key[1] ** 2), device=value.device)
+        if dvalue is None:
+            dvalue = torch.zeros(B, device=value.device)
+        dpw, dpb, dvw, dvb = heads_backward(lease, pw, vw, dlogits, dvalue, value)
+        _, dws, dbs = stack_backward(lease, None, need_dx=False)
+        pd = ctx.pdtypes
+        grads = [None, None, None, None]
+        for l, (dw, db) in enumerate(zip(dws, dbs)):
+            grads.append(dw.to(pd[2 * l]))
+            grads.append(db.to(pd[2 * l + 1]))
+        n = len(pd)
+        grads += [dpw.to(pd[n - 4]), dpb.to(pd[n - 3]), dvw.to(pd[n - 2]), dvb.to(pd[n - 1])]
+        return tuple(grads)

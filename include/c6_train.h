@@ -77,6 +77,17 @@ int c6_backbone_forward(int32_t device, int32_t board_size, int32_t nlayers, con
                         int64_t B, const float* x, const float* const* w, const float* const* bias, float* y,
                         void* workspace, int64_t workspace_bytes, void* stream);
 
+/* c6_backbone_forward for a stack that starts with the stem (stem_kside > 0), fed with the environment's raw state
+ * instead of network-input planes: boards int8 [num_envs, n, n], current_player and stones_left int8 [num_envs], and an
+ * optional int64 index [B] selecting the boards (null: boards 0..B-1).  The planes of canonical_network_input
+ * (connect6/vector_env.py:196-218; the PPO minibatch builds them at connect6/train.py:1038-1046 after gathering
+ * buffer.boards[idx]) are formed inside the first kernel.  An index entry outside [0, num_envs) reads as an empty
+ * board and raises C6_STATUS_BAD_INDEX in the workspace's status word. */
+int c6_backbone_forward_boards(int32_t device, int32_t board_size, int32_t nlayers, const int32_t* channels,
+                               int32_t stem_kside, int64_t B, const int8_t* boards, const int8_t* current_player,
+                               const int8_t* stones_left, int64_t num_envs, const int64_t* index, const float* const* w,
+                               const float* const* bias, float* y, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* dy fp32 [B, channels[nlayers], n, n] = dL/dy of the preceding c6_backbone_forward on this workspace (null: the
  * gradient of the features is already in the workspace, left there by c6_backbone_heads_backward).
  * Outputs: dx fp32 [B, channels[0], n, n] (nullable; must be null with a stem: the network input has no gradient);

@@ -496,3 +496,37 @@ def test_clip_adamw_matches_torch(cuda_device):
     cpu_p.grad = torch.zeros(3)
     with pytest.raises(RuntimeError):       # no CPU path
         ClipAdamW([cpu_p], lr=1e-3).step()
+
+
+def test_training_forward_from_the_buffer_state(cuda_device):
+    """PolicyValueNet.forward_from_boards with engine_backward=True (the stem kernel reads the int8 state and the
+    minibatch index directly) gives the logits, values and parameter gradients of the same network fed with
+    canonical_network_input(boards[index], ...) -- bit for bit: the planes are 0/1 either way."""
+    from connect6_b200.model import PolicyValueNet
+    from connect6_b200.selfplay import canonical_network_input
+    dev = cuda_device
+    torch.manual_seed(8)
+    m = PolicyValueNet(19, engine_backward=True).to(dev).train()
+    gen = torch.Generator().manual_seed(3)
+    E = 50
+    boards = torch.randint(-1, 2, (E, 19, 19), generator=gen).to(torch.int8).to(dev)
+    player = (torch.randint(0, 2, (E,), generator=gen) * 2 - 1).to(torch.int8).to(dev)
+    stones = torch.randint(1, 3, (E,), generator=gen).to(torch.int8).to(dev)
+    index = torch.randperm(E, generator=gen)[:21].to(dev)
+    results = []
+    for from_state in (True, False):
+        m.zero_grad(set_to_none=True)
+        if from_state:
+            logits, value = m.forward_from_boards(boards, player, stones, index)
+        else:
+            logits, value = m(canonical_network_input(boards[index], player[index], stones[index]))
+        (logits.square().mean() + value.sum()).backward()
+        results.append((logits.detach().clone(), value.detach().clone(), [p.grad.detach().clone() for p in m.parameters()]))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    assert all(torch.equal(a, b) for a, b in zip(results[0][2], results[1][2]))
+    # no index: every environment; no grad: the inference engine
+    logits, _ = m.forward_from_boards(boards, player, stones)
+    assert logits.shape == (E, 361) and logits.requires_grad
+    with torch.no_grad():
+        lg, _ = m.forward_from_boards(boards, player, stones, index)
+    assert lg.shape == (21, 361) and not lg.requires_grad

@@ -546,3 +546,37 @@ class PolicyValueStackFromBoards(torch.autograd.Function):
         n = len(pd)
         grads += [dpw.to(pd[n - 4]), dpb.to(pd[n - 3]), dvw.to(pd[n - 2]), dvb.to(pd[n - 1])]
         return tuple(grads)
+
+
+def ppo_minibatch_update(model, optimizer, boards: torch.Tensor, players: torch.Tensor, stones_left: torch.Tensor,
+                         actions: torch.Tensor, old_logprob: torch.Tensor, advantages: torch.Tensor, returns: torch.Tensor,
+                         idx: torch.Tensor, local_idx: torch.Tensor | None = None, *, temperature: float = 1.0,
+                         clip_coef: float = 0.2, value_coef: float = 0.5, entropy_coef: float = 0.01):
+    """One minibatch of the PPO update as the body of the reference's loop does it (connect6/train.py:1036-1145):
+    gather the minibatch `idx` from the buffer tensors (boards int8 [N, n, n], players, stones_left int8 [N], actions,
+    old_logprob [N]) and `local_idx` (default: idx) from advantages / returns, forward, loss, backward, gradient
+    clipping and optimizer step.  With PolicyValueNet(engine_backward=True) and a ClipAdamW optimizer every kernel of
+    it is the library's.  Returns (stats, grad_norm): stats = device tensor [loss, policy loss, value loss, entropy,
+    approx_kl, clipfrac], grad_norm = the total gradient norm before clipping; nothing is synchronised -- the caller's
+    KL watchdog reads stats[4:6] when it wants to."""
+    local_idx = idx if local_idx is None else local_idx
+    mb_boards = boards[idx]
+    legal = mb_boards.reshape(mb_boards.shape[0], -1).eq(0)            # connect6/train.py:1046
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        if hasattr(model, "forward_from_boards"):
+            logits, values = model.forward_from_boards(boards, players, stones_left, idx)
+        else:
+            from .selfplay import canonical_network_input
+            logits, values = model(canonical_network_input(mb_boards, players[idx], stones_left[idx]))
+        loss, stats = ppo_loss(logits.float(), values.float(), legal, actions[idx].long(), old_logprob[idx],
+                               advantages[local_idx], returns[local_idx], temperature, clip_coef, value_coef, entropy_coef)
+    optimizer.zero_grad(set_to_none=True)
+    loss.backward()
+    if isinstance(optimizer, ClipAdamW):
+        grad_norm = optimizer.step()
+    else:
+        max_norm = optimizer.param_groups[0].get("max_grad_norm", 0.0)
+        params = [p for g in optimizer.param_groups for p in g["params"]]
+        grad_norm = torch.nn.utils.clip_grad_norm_(params, max_norm if max_norm > 0 else float("inf"))
+        optimizer.step()
+    return stats, grad_norm

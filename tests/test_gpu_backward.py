@@ -530,3 +530,35 @@ def test_training_forward_from_the_buffer_state(cuda_device):
     with torch.no_grad():
         lg, _ = m.forward_from_boards(boards, player, stones, index)
     assert lg.shape == (21, 361) and not lg.requires_grad
+
+
+def test_ppo_minibatch_update_helper(cuda_device):
+    """train_ops.ppo_minibatch_update (the body of the reference's minibatch loop as one call) run on a buffer-shaped
+    state: three updates with PolicyValueNet(engine_backward=True) + ClipAdamW against the same helper driving the plain
+    model with torch.optim.AdamW -- statistics and gradient norms stay together."""
+    from connect6_b200.model import PolicyValueNet
+    from connect6_b200.train_ops import ClipAdamW, ppo_minibatch_update
+    dev = cuda_device
+    torch.manual_seed(6)
+    plain = PolicyValueNet(19).to(dev).train()
+    ours = PolicyValueNet(19, engine_backward=True).to(dev).train()
+    ours.load_state_dict(plain.state_dict())
+    gen = torch.Generator().manual_seed(2)
+    N = 96
+    boards = torch.randint(-1, 2, (N, 19, 19), generator=gen).to(torch.int8).to(dev)
+    players = (torch.randint(0, 2, (N,), generator=gen) * 2 - 1).to(torch.int8).to(dev)
+    stones = torch.randint(1, 3, (N,), generator=gen).to(torch.int8).to(dev)
+    legal = boards.reshape(N, -1).eq(0)
+    actions = torch.multinomial(legal.float().cpu(), 1, generator=gen).squeeze(1).to(dev)
+    old = (-torch.log(legal.sum(1).float())).to(dev)
+    adv, ret = torch.randn(N, generator=gen).to(dev), torch.tanh(torch.randn(N, generator=gen)).to(dev)
+    kw = dict(lr=2.5e-4, weight_decay=1e-4, eps=1e-5)
+    o_plain = torch.optim.AdamW(plain.parameters(), **kw)
+    o_plain.param_groups[0]["max_grad_norm"] = 2.0
+    o_ours = ClipAdamW(ours.parameters(), max_grad_norm=2.0, **kw)
+    for it in range(3):
+        idx = torch.randperm(N, generator=gen)[:32].to(dev)
+        s1, n1 = ppo_minibatch_update(plain, o_plain, boards, players, stones, actions, old, adv, ret, idx)
+        s2, n2 = ppo_minibatch_update(ours, o_ours, boards, players, stones, actions, old, adv, ret, idx)
+        assert (s1 - s2).abs().max().item() < 5e-3 + 0.02 * s1.abs().max().item(), (it, s1, s2)
+        assert abs(float(n1) - float(n2)) < 0.05 * float(n1) + 1e-4

@@ -118,52 +118,49 @@ __global__ void pack_stem_input_kernel(const InputSrc in,
 // so the last rows of an image (and the 8 rows in front of a group's first image) already carry the first
 // cells of the image behind them.  A group's threads write rows [base - 8, base + nb*slots - 8); the 8 rows
 // behind a group's last image are all padding and stay zero.
-// Grid: (ceil(3*slots*nb/256), G); one thread per (plane, row).
+// Grid: (nb, G), one block per board image: the block first stages the board's three planes (in view orientation) in
+// shared memory with coalesced loads, then its threads build the image's 3 * slots rows from there.  Block t writes the
+// rows [t*slots - 8, (t+1)*slots - 8) of each plane: what lies in front of its image in those rows is the tail padding
+// of the image before (zero).
 // ------------------------------------------------------------------------------------------------
-__global__ void pack_stem_direct_input_kernel(const InputSrc in, const uint8_t* __restrict__ orient,
-                                              uint4* __restrict__ xe, long long plane_rows, int front, int group_pos,
-                                              int wi, int slots, int n, int nb, long long group_stride, long long board0,
-                                              int f16, int* __restrict__ status) {
+constexpr int kPackDirectThreads = 256;
+constexpr int kPackDirectMaxCells = 32 * 32;
+__global__ void __launch_bounds__(kPackDirectThreads) pack_stem_direct_input_kernel(
+    const InputSrc in, const uint8_t* __restrict__ orient, uint4* __restrict__ xe, long long plane_rows, int front, int group_pos,
+    int wi, int slots, int n, int nb, long long group_stride, long long board0, int f16, int* __restrict__ status) {
+  __shared__ float s_x[3 * kPackDirectMaxCells];
   grid_dep_launch();
-  const int g = blockIdx.y;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long per_plane = (long long)slots * nb;
-  if (idx >= 3 * per_plane) return;
-  const int ci = (int)(idx / per_plane);
-  const long long p = idx - (long long)ci * per_plane - 8;   // row relative to the group's first image
+  const int g = blockIdx.y, t = blockIdx.x;
   const int cells = n * n;
-  // (image t, row r, column c) of the row's first position, stepped along the 8 positions of the row
-  long long pos = p < 0 ? 0 : p;
-  int t = (int)(pos / slots);
-  int q = (int)(pos - (long long)t * slots);
-  int r = q / wi, c = q - r * wi;
-  const int hi = slots / wi;
-  float v[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    float val = 0.f;
-    if (p + e >= 0) {
-      if (r < n && c < n) {
-        const long long src_board = (long long)g * group_stride + board0 + t;
-        const int phase = orient ? (orient[src_board] & 7) : 0;
-        int cell = r * n + c;
-        if (phase) cell = d4_inverse(cell, n, phase);
-        if (cell == 0 && ci == 0 && in.boards != nullptr && input_env(in, src_board) < 0) atomicOr(status, kStatBadIndex);
-        val = input_value(in, src_board, ci, cell, cells);
-      }
-      if (++c == wi) {
-        c = 0;
-        if (++r == hi) { r = 0; ++t; }
-      }
-    }
-    v[e] = val;
+  const long long src_board = (long long)g * group_stride + board0 + t;
+  const int phase = orient ? (orient[src_board] & 7) : 0;
+  if (threadIdx.x == 0 && in.boards != nullptr && input_env(in, src_board) < 0) atomicOr(status, kStatBadIndex);
+  for (int i = threadIdx.x; i < 3 * cells; i += kPackDirectThreads) {
+    const int ci = i / cells, cell = i - ci * cells;
+    s_x[i] = input_value(in, src_board, ci, phase ? d4_inverse(cell, n, phase) : cell, cells);
   }
-  uint4 o;
-  o.x = pack_h2(v[0], v[1], f16);
-  o.y = pack_h2(v[2], v[3], f16);
-  o.z = pack_h2(v[4], v[5], f16);
-  o.w = pack_h2(v[6], v[7], f16);
-  xe[(size_t)ci * plane_rows + front + (long long)g * group_pos + p] = o;
+  __syncthreads();
+  for (int i = threadIdx.x; i < 3 * slots; i += kPackDirectThreads) {
+    const int ci = i / slots, p = i - ci * slots - 8;       // row relative to this image's first position
+    int q = p < 0 ? 0 : p;
+    int r = q / wi, c = q - r * wi;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float val = 0.f;
+      if (p + e >= 0) {
+        if (r < n && c < n) val = s_x[ci * cells + r * n + c];
+        if (++c == wi) { c = 0; ++r; }
+      }
+      v[e] = val;
+    }
+    uint4 o;
+    o.x = pack_h2(v[0], v[1], f16);
+    o.y = pack_h2(v[2], v[3], f16);
+    o.z = pack_h2(v[4], v[5], f16);
+    o.w = pack_h2(v[6], v[7], f16);
+    xe[(size_t)ci * plane_rows + front + (long long)g * group_pos + (long long)t * slots + p] = o;
+  }
 }
 
 // Filter of the first layer for the direct stem: rows [ci][ky][hb][j][co] of 8 elements, element e of the row

@@ -449,9 +449,8 @@ int run_direct_stem(C6Engine* e, const RunArgs& a, long long t0, int nb, const G
     e->sd_last_group_pos = gs.group_pos;
   }
   {
-    const long long total = 3LL * e->sd_slots * nb;
     ProfScope _ps(e, C6_KIND_PACK, st);
-    pack_stem_direct_input_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)e->G), 256, 0, st>>>(
+    pack_stem_direct_input_kernel<<<dim3((unsigned)nb, (unsigned)e->G), kPackDirectThreads, 0, st>>>(
         input_of(a), a.orient, e->xe, e->xe_plane_rows, e->sd_front, (int)gs.group_pos, e->sd_wi, e->sd_slots, e->n, nb,
         a.T, t0, e->f16, e->status_dev);
     C6_LAUNCHED(e, "pack_stem_direct_input_kernel");

@@ -638,8 +638,7 @@ static int backbone_forward_impl(int32_t device, int32_t board_size, int32_t nla
     pack_stem_direct_weights_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
         w[0], reinterpret_cast<uint4*>(ws + S.off_wf_pair[0]), T.cout, T.k, T.cout_p, T.hx, 2, 0);
     C6T_LAUNCHED("pack_stem_direct_weights_kernel");
-    const long long total = 3LL * T.slots * B;
-    pack_stem_direct_input_kernel<<<dim3((unsigned)((total + 255) / 256), 1u), 256, 0, st>>>(
+    pack_stem_direct_input_kernel<<<dim3((unsigned)B, 1u), kPackDirectThreads, 0, st>>>(
         in, nullptr, reinterpret_cast<uint4*>(ws + S.off_xe), T.xe_plane_rows, T.front, (int)T.group_pos, T.wi, T.slots, board_size,
         (int)B, B, 0, 0, status);
     C6T_LAUNCHED("pack_stem_direct_input_kernel");

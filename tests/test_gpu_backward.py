@@ -562,3 +562,45 @@ def test_ppo_minibatch_update_helper(cuda_device):
         s2, n2 = ppo_minibatch_update(ours, o_ours, boards, players, stones, actions, old, adv, ret, idx)
         assert (s1 - s2).abs().max().item() < 5e-3 + 0.02 * s1.abs().max().item(), (it, s1, s2)
         assert abs(float(n1) - float(n2)) < 0.05 * float(n1) + 1e-4
+
+
+def test_network_backward_properties_at_4096_boards(cuda_device):
+    """Size-independent properties of the whole-network backward at a batch the fp64 oracle cannot afford: the parameter
+    gradients of a batch are the sums of the gradients of its halves (fp32 sums in another order: 1e-3 of each tensor's
+    scale, the bf16 operands being the same numbers either way), they are linear in the output gradients (a factor 2
+    is exact in bf16 up to the fp32 roundings of the sums), and a zero output gradient gives zero everywhere."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.train_ops import heads_backward, heads_forward, stack_backward, stack_forward, stack_status
+    dev = cuda_device
+    torch.manual_seed(12)
+    from connect6_b200.model import PolicyValueNet
+    net = PolicyValueNet(19).to(dev)
+    ws = [c.weight.detach() for c in net.convs]
+    bs = [c.bias.detach() + 0.05 for c in net.convs]
+    pw, pb, vw, vb = (net.policy_output.weight.detach() * 30, net.policy_output.bias.detach(), net.value_output.weight.detach() * 30,
+                      net.value_output.bias.detach())
+    B = 4096
+    x = torch.from_numpy(generate_planes(0, B)).to(dev)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    dl = torch.randn(B, 361, device=dev, generator=gen) * 1e-3
+    dv = torch.randn(B, device=dev, generator=gen) * 1e-2
+
+    def grads(sl, scale=1.0):
+        _, lease = stack_forward(x[sl], ws, bs, want_features=False)
+        _, value = heads_forward(lease, pw, pb, vw, vb)
+        hg = heads_backward(lease, pw, vw, scale * dl[sl], scale * dv[sl], value)
+        _, dws, dbs = stack_backward(lease, None, need_dx=False)
+        assert stack_status(lease) == 0
+        return [g.clone() for g in list(hg) + dws + dbs]
+
+    whole = grads(slice(0, B))
+    first, second = grads(slice(0, B // 2)), grads(slice(B // 2, B))
+    for w, a, b in zip(whole, first, second):
+        scale = max(w.abs().max().item(), 1e-6)
+        assert (w - (a + b)).abs().max().item() < 1e-3 * scale
+    doubled = grads(slice(0, B), 2.0)
+    for w, d in zip(whole, doubled):
+        scale = max(w.abs().max().item(), 1e-6)
+        assert (d - 2.0 * w).abs().max().item() < 1e-4 * scale
+    zero = grads(slice(0, B), 0.0)
+    assert all(not z.any() for z in zero)

@@ -103,7 +103,7 @@ SIGNATURES = {
     "c6_ppo_loss": (_i, [C.c_int32, _i64, C.c_int32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_float, C.c_float, C.c_float, C.c_float,
                          _vp, _vp, _vp, _vp, _i64, _vp]),
     "c6_clip_adamw_step": (_i, [C.c_int32, C.c_int32, C.POINTER(_i64), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
-                                C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _i64, _vp, _vp, _i64, _vp]),
+                                C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _i64, _vp, _vp, _vp, _i64, _vp]),
     "c6_train_last_error": (C.c_char_p, []),
     "c6_env_step": (_i, [C.POINTER(C6EnvState), _vp, C.c_int32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "c6_env_reset": (_i, [C.POINTER(C6EnvState), _vp, _i64, _vp]),

@@ -376,7 +376,8 @@ __global__ void mul_planes_kernel(const uint4* __restrict__ a, const uint4* __re
 // The tensors are addressed as one flat index space (offset[i] = first flat index of tensor i).  Kernel 1 leaves one
 // partial sum of squares per block; every block of kernel 2 adds them up in block order (the same value everywhere,
 // the same on every run).  A non-finite norm (overflowed or NaN gradients) leaves parameters and moments untouched;
-// the norm is reported either way.
+// the norm is reported either way.  With step_device the 1-based update count is kept on the device (kernel 1 adds one,
+// kernel 2 derives the bias corrections from it), so that a captured graph can be replayed.
 constexpr int kOptMaxTensors = 48;
 constexpr int kOptThreads = 256;
 struct OptTensors {
@@ -392,8 +393,10 @@ __device__ __forceinline__ int opt_find(const OptTensors& T, long long i) {
   while (t + 1 < T.n && i >= T.offset[t + 1]) ++t;
   return t;
 }
-__global__ void __launch_bounds__(kOptThreads) grad_sumsq_kernel(const OptTensors T, float* __restrict__ partial) {
+__global__ void __launch_bounds__(kOptThreads) grad_sumsq_kernel(const OptTensors T, float* __restrict__ partial,
+                                                                 float* __restrict__ step_device) {
   __shared__ float s_red[kOptThreads / 32];
+  if (step_device != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *step_device += 1.f;   // the update kernel reads the new count
   const long long total = T.offset[T.n];
   const long long per_block = (total + gridDim.x - 1) / gridDim.x;
   const long long lo = per_block * blockIdx.x, hi = min(total, lo + per_block);
@@ -416,7 +419,13 @@ __global__ void __launch_bounds__(kOptThreads) grad_sumsq_kernel(const OptTensor
 __global__ void __launch_bounds__(kOptThreads) clip_adamw_kernel(const OptTensors T, const float* __restrict__ partial, int npartial,
                                                                  float lr, float beta1, float beta2, float eps, float weight_decay,
                                                                  float max_norm, float bias1, float bias2_sqrt,
+                                                                 const float* __restrict__ step_device,
                                                                  float* __restrict__ grad_norm) {
+  if (step_device != nullptr) {        // the update count lives on the device (CUDA-graph replays): bias corrections from it
+    const float t = *step_device;
+    bias1 = 1.f - powf(beta1, t);
+    bias2_sqrt = sqrtf(1.f - powf(beta2, t));
+  }
   float sumsq = 0.f;
   for (int b = 0; b < npartial; ++b) sumsq += partial[b];
   const float norm = sqrtf(sumsq);

@@ -856,11 +856,11 @@ int c6_ppo_loss(int32_t device, int64_t B, int32_t A, const float* logits, const
 
 int c6_clip_adamw_step(int32_t device, int32_t ntensors, const int64_t* sizes, float* const* params, float* const* grads,
                        float* const* exp_avg, float* const* exp_avg_sq, float lr, float beta1, float beta2, float eps,
-                       float weight_decay, float max_grad_norm, int64_t step, float* grad_norm, void* workspace,
-                       int64_t workspace_bytes, void* stream) {
+                       float weight_decay, float max_grad_norm, int64_t step, float* step_device, float* grad_norm,
+                       void* workspace, int64_t workspace_bytes, void* stream) {
   if (ntensors < 1 || ntensors > kOptMaxTensors) return tfail(C6_ERR_ARG, "between 1 and 48 parameter tensors per call");
   if (!sizes || !params || !grads || !exp_avg || !exp_avg_sq || !grad_norm || !workspace) return tfail(C6_ERR_ARG, "null pointer");
-  if (step < 1) return tfail(C6_ERR_ARG, "step counts from 1");
+  if (!step_device && step < 1) return tfail(C6_ERR_ARG, "step counts from 1");
   constexpr int kBlocks = 148;
   if (workspace_bytes < (int64_t)(kBlocks * sizeof(float))) return tfail(C6_ERR_ARG, "workspace smaller than 592 bytes");
   int ndev = 0;
@@ -879,12 +879,13 @@ int c6_clip_adamw_step(int32_t device, int32_t ntensors, const int64_t* sizes, f
   T.offset[ntensors] = off;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   float* partial = reinterpret_cast<float*>(workspace);
-  grad_sumsq_kernel<<<kBlocks, kOptThreads, 0, st>>>(T, partial);
+  grad_sumsq_kernel<<<kBlocks, kOptThreads, 0, st>>>(T, partial, step_device);
   C6T_LAUNCHED("grad_sumsq_kernel");
-  const double b1t = 1.0 - std::pow((double)beta1, (double)step), b2t = 1.0 - std::pow((double)beta2, (double)step);
+  const double tt = (double)std::max<int64_t>(step, 1);
+  const double b1t = 1.0 - std::pow((double)beta1, tt), b2t = 1.0 - std::pow((double)beta2, tt);
   const int blocks = (int)std::min<long long>((off + kOptThreads - 1) / kOptThreads, 4 * kBlocks);
   clip_adamw_kernel<<<std::max(blocks, 1), kOptThreads, 0, st>>>(T, partial, kBlocks, lr, beta1, beta2, eps, weight_decay, max_grad_norm,
-                                                              (float)b1t, (float)std::sqrt(b2t), grad_norm);
+                                                              (float)b1t, (float)std::sqrt(b2t), step_device, grad_norm);
   C6T_LAUNCHED("clip_adamw_kernel");
   return C6_OK;
 }

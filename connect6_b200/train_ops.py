@@ -452,11 +452,13 @@ class ClipAdamW(torch.optim.Optimizer):
     call of the kernel; fp32 CUDA parameters only."""
 
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2,
-                 max_grad_norm: float = 0.0) -> None:
+                 max_grad_norm: float = 0.0, capturable: bool = False) -> None:
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
             raise ValueError("ClipAdamW: invalid hyper-parameter")
+        # capturable=True keeps the update count on the device (like torch.optim.AdamW's flag of that name), so that a
+        # step captured in a CUDA graph can be replayed; the learning rate then is the value at capture time
         super().__init__(params, dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
-                                      amsgrad=False, maximize=False, foreach=None, capturable=False, differentiable=False,
+                                      amsgrad=False, maximize=False, foreach=None, capturable=bool(capturable), differentiable=False,
                                       fused=None))
 
     @torch.no_grad()
@@ -475,13 +477,23 @@ class ClipAdamW(torch.optim.Optimizer):
                     raise RuntimeError("ClipAdamW: contiguous fp32 CUDA parameters and gradients on one device only (no CPU path)")
                 st = self.state[p]
                 if not st:
-                    st["step"] = torch.tensor(0.0)
+                    st["step"] = torch.zeros((), device=dev) if group["capturable"] else torch.tensor(0.0)
                     st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
                     st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
-            steps = {int(self.state[p]["step"]) for p in ps}
-            if len(steps) != 1:
-                raise RuntimeError("ClipAdamW: the parameters of a group must have been stepped together")
-            step = steps.pop() + 1
+            step_dev = None
+            if group["capturable"]:
+                # one device counter for the group: every parameter's "step" entry is that tensor
+                step_dev = self.state[ps[0]]["step"]
+                if not step_dev.is_cuda:
+                    step_dev = step_dev.to(dev)
+                for p in ps:
+                    self.state[p]["step"] = step_dev
+                step = 0
+            else:
+                steps = {int(self.state[p]["step"]) for p in ps}
+                if len(steps) != 1:
+                    raise RuntimeError("ClipAdamW: the parameters of a group must have been stepped together")
+                step = steps.pop() + 1
             norm = torch.empty(1, device=dev, dtype=torch.float32)
             pool = self.__dict__.setdefault("_c6_workspaces", {})
             ws = pool.get(dev)
@@ -498,12 +510,13 @@ class ClipAdamW(torch.optim.Optimizer):
                                                      _ptr_array([self.state[p]["exp_avg"] for p in chunk]),
                                                      _ptr_array([self.state[p]["exp_avg_sq"] for p in chunk]), float(group["lr"]),
                                                      float(b1), float(b2), float(group["eps"]), float(group["weight_decay"]),
-                                                     float(group["max_grad_norm"]), step, norm.data_ptr(), ws.data_ptr(),
+                                                     float(group["max_grad_norm"]), step, L.ptr(step_dev), norm.data_ptr(), ws.data_ptr(),
                                                      ws.numel() * 4, torch.cuda.current_stream(dev).cuda_stream)
                 if rc != L.C6_OK:
                     raise _train_fail(rc, "c6_clip_adamw_step")
-            for p in ps:
-                self.state[p]["step"] += 1
+            if step_dev is None:
+                for p in ps:
+                    self.state[p]["step"] += 1
             norms.append(norm)
         if not norms:
             return None

@@ -134,7 +134,9 @@ int c6_ppo_loss(int32_t device, int64_t B, int32_t A, const float* logits, const
  * (connect6/train.py:1121-1145, optimizer set up at connect6/train.py:476-481) for a whole parameter list, in two
  * launches.  sizes: HOST array of ntensors element counts; params, grads, exp_avg, exp_avg_sq: HOST arrays of
  * ntensors DEVICE pointers to fp32 tensors of those sizes (1 <= ntensors <= 48).  step: the 1-based number of this
- * update (bias corrections 1 - beta^step).  max_grad_norm <= 0: no clipping.
+ * update (bias corrections 1 - beta^step); or step_device (DEVICE, fp32 [1], nullable): the number of updates done so far,
+ * kept on the device -- the call adds one and derives the bias corrections from it, `step` is ignored (for a call
+ * sequence that is captured in a CUDA graph and replayed).  max_grad_norm <= 0: no clipping.
  * Effects: grads scaled in place by min(1, max_grad_norm / (total_norm + 1e-6)) like clip_grad_norm_; params and both
  * moments updated in place with PyTorch's AdamW arithmetic (decoupled weight decay); grad_norm (DEVICE, fp32 [1]) =
  * the total norm BEFORE clipping.  A non-finite norm leaves params and moments untouched (the reference raises there:
@@ -142,8 +144,8 @@ int c6_ppo_loss(int32_t device, int64_t B, int32_t A, const float* logits, const
  * workspace: 592 bytes. */
 int c6_clip_adamw_step(int32_t device, int32_t ntensors, const int64_t* sizes, float* const* params, float* const* grads,
                        float* const* exp_avg, float* const* exp_avg_sq, float lr, float beta1, float beta2, float eps,
-                       float weight_decay, float max_grad_norm, int64_t step, float* grad_norm, void* workspace,
-                       int64_t workspace_bytes, void* stream);
+                       float weight_decay, float max_grad_norm, int64_t step, float* step_device, float* grad_norm,
+                       void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Last error text of the calling thread's most recent failing call of this header. Never null. */
 const char* c6_train_last_error(void);

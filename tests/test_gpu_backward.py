@@ -604,3 +604,59 @@ def test_network_backward_properties_at_4096_boards(cuda_device):
         assert (d - 2.0 * w).abs().max().item() < 1e-4 * scale
     zero = grads(slice(0, B), 0.0)
     assert all(not z.any() for z in zero)
+
+
+def test_whole_update_under_a_cuda_graph_with_clip_adamw(cuda_device):
+    """ClipAdamW(capturable=True) keeps its update count on the device: forward + ppo_loss + backward + clipping + AdamW
+    captured once and replayed three times moves the parameters exactly like three eager updates of a twin model (bias
+    corrections included: they change with every replay)."""
+    from connect6_b200.boards import generate_planes
+    from connect6_b200.model import PolicyValueNet
+    from connect6_b200.train_ops import ClipAdamW, ppo_loss
+    dev = cuda_device
+    torch.manual_seed(9)
+    a = PolicyValueNet(19, engine_backward=True).to(dev).train()
+    b = PolicyValueNet(19, engine_backward=True).to(dev).train()
+    b.load_state_dict(a.state_dict())
+    B = 32
+    x = torch.from_numpy(generate_planes(0, B)).to(dev)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    legal = (x[:, 0] + x[:, 1]).reshape(B, -1).eq(0)
+    actions = torch.multinomial(legal.float(), 1, generator=gen).squeeze(1)
+    old = -torch.log(legal.sum(1).float())
+    adv, ret = torch.randn(B, device=dev, generator=gen), torch.zeros(B, device=dev)
+    kw = dict(lr=2.5e-4, weight_decay=1e-4, eps=1e-5, max_grad_norm=2.0)
+    # both with the device-side update count: the same arithmetic eagerly and replayed (the host-side count rounds its
+    # bias corrections in double precision, and training amplifies even that difference within a few updates)
+    oa, ob = ClipAdamW(a.parameters(), capturable=True, **kw), ClipAdamW(b.parameters(), capturable=True, **kw)
+
+    def update(m, opt):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits, value = m(x)
+            loss, _ = ppo_loss(logits, value, legal, actions, old, adv, ret)
+        loss.backward()
+        return opt.step()
+
+    for _ in range(4):                        # eager: four updates
+        oa.zero_grad(set_to_none=True)
+        update(a, oa)
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        ob.zero_grad(set_to_none=True)
+        update(b, ob)                         # the first update runs eagerly on the side stream (allocates the state)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    for p in b.parameters():
+        p.grad.zero_()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        update(b, ob)                         # captured, not executed
+    for _ in range(3):
+        for p in b.parameters():
+            p.grad.zero_()
+        graph.replay()
+    torch.cuda.synchronize(dev)
+    assert float(ob.state[next(iter(b.parameters()))]["step"]) == 4.0
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        assert torch.equal(pa, pb)
